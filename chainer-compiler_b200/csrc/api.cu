@@ -1,0 +1,655 @@
+// C-ABI entry points of the contraction ops (MatMulInteger, QLinearMatMul, ConvInteger, QLinearConv):
+// argument validation, convolution geometry, path selection, workspace carving, and the small
+// pre-pass kernels that feed the tensor-core kernel (operand repacking and zero-point terms).
+#include <string.h>
+
+#include "common.h"
+#include "kernels.h"
+
+namespace chxq {
+namespace {
+
+inline size_t align_up(size_t v, size_t a) {
+    return (v + a - 1) / a * a;
+}
+
+template <bool kSigned>
+__device__ __forceinline__ int ldq(const void* p, int64_t i) {
+    return kSigned ? (int)static_cast<const int8_t*>(p)[i] : (int)static_cast<const uint8_t*>(p)[i];
+}
+__device__ __forceinline__ int ldq_rt(const void* p, int64_t i, int is_signed) {
+    return is_signed ? (int)static_cast<const int8_t*>(p)[i] : (int)static_cast<const uint8_t*>(p)[i];
+}
+__device__ __forceinline__ int zp_at(const ZpSpec& z, int64_t i, int is_signed) {
+    if (z.len == 0) return 0;
+    if (z.ptr == nullptr) return z.scalar;
+    return ldq_rt(z.ptr, z.len == 1 ? 0 : i, is_signed);
+}
+
+// B[K, N] (row-major) -> Bt[N, k_pad] (K-major rows, zero padded), through a 32x32 shared tile.
+__global__ void __launch_bounds__(256) transpose_b_kernel(const uint8_t* __restrict__ b, int64_t K, int64_t N, int64_t k_pad, uint8_t* __restrict__ bt) {
+    __shared__ uint8_t tile[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+    const int64_t k0 = (int64_t)blockIdx.y * 32, n0 = (int64_t)blockIdx.x * 32;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t k = k0 + ty * 4 + i, n = n0 + tx;
+        tile[ty * 4 + i][tx] = (k < K && n < N) ? b[k * N + n] : (uint8_t)0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t n = n0 + ty * 4 + i, k = k0 + tx;
+        if (n < N && k < k_pad) bt[n * k_pad + k] = tile[tx][ty * 4 + i];
+    }
+}
+
+// T[n] = sum_k za[k] * b[k, n]; zbn[n] = zb[n] widened.  One thread per column.
+__global__ void __launch_bounds__(256) gemm_col_terms_kernel(
+        const void* __restrict__ b, int b_signed, int a_signed, int64_t K, int64_t N, ZpSpec za, ZpSpec zb, int32_t* __restrict__ T,
+        int32_t* __restrict__ zbn) {
+    const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    unsigned t = 0u;
+    if (za.len > 0) {
+        for (int64_t k = 0; k < K; ++k) t += (unsigned)zp_at(za, k, a_signed) * (unsigned)ldq_rt(b, k * N + n, b_signed);
+    }
+    T[n] = (int32_t)t;
+    zbn[n] = zp_at(zb, n, b_signed);
+}
+
+// R[m] = sum_k (a[m, k] - za[k]).  One warp per row.
+__global__ void __launch_bounds__(256) gemm_row_terms_kernel(const void* __restrict__ a, int a_signed, int64_t M, int64_t K, ZpSpec za, int32_t* __restrict__ R) {
+    const int64_t m = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (m >= M) return;
+    int s = 0;
+    for (int64_t k = lane; k < K; k += 32) s += ldq_rt(a, m * K + k, a_signed) - zp_at(za, k, a_signed);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) R[m] = s;
+}
+
+// OIHW weights -> K-major rows [M][tap * c_pitch + c], zero padded to k_total.  One thread per output byte.
+__global__ void __launch_bounds__(256) pack_weights_kernel(
+        const uint8_t* __restrict__ w, int M, int C, int taps, int c_pitch, int k_total, uint8_t* __restrict__ out) {
+    const int64_t total = (int64_t)M * k_total;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int k = (int)(i % k_total);
+        const int m = (int)(i / k_total);
+        const int tap = k / c_pitch, c = k % c_pitch;
+        uint8_t v = 0;
+        if (tap < taps && c < C) v = w[((int64_t)m * C + c) * taps + tap];
+        out[i] = v;
+    }
+}
+
+// wsum[m] = sum of the raw quantized weights of output channel m; zw32[m] = widened zero point;
+// *any_nonzero |= (zw[m] != 0).  One warp per channel.
+__global__ void __launch_bounds__(256) weight_terms_kernel(
+        const void* __restrict__ w, int w_signed, int M, int inner, ZpSpec zw, int32_t* __restrict__ wsum, int32_t* __restrict__ zw32,
+        int32_t* __restrict__ any_nonzero) {
+    const int m = (int)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    const int lane = threadIdx.x & 31;
+    if (m >= M) return;
+    int s = 0;
+    for (int i = lane; i < inner; i += 32) s += ldq_rt(w, (int64_t)m * inner + i, w_signed);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+        wsum[m] = s;
+        const int z = zp_at(zw, m, w_signed);
+        zw32[m] = z;
+        if (z != 0) atomicOr(any_nonzero, 1);
+    }
+}
+
+// Row sums of an explicit im2col matrix: R[r] = sum_{k < k_real...} A[r, k] - k_real * x_zp
+// (padded columns are zero, so summing the whole row is the same).  One warp per row, 16 bytes per lane.
+__global__ void __launch_bounds__(256) rowsum_matrix_kernel(const uint8_t* __restrict__ a, int a_signed, int64_t rows, int k_pad, int sub, int32_t* __restrict__ R) {
+    const int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    int s = 0;
+    const uint4* p = reinterpret_cast<const uint4*>(a + r * k_pad);
+    for (int i = lane; i < k_pad / 16; i += 32) {
+        const uint4 v = p[i];
+        if (a_signed) {
+            s = __dp4a((int)v.x, 0x01010101, s); s = __dp4a((int)v.y, 0x01010101, s);
+            s = __dp4a((int)v.z, 0x01010101, s); s = __dp4a((int)v.w, 0x01010101, s);
+        } else {
+            unsigned u = (unsigned)s;
+            u = __dp4a(v.x, 0x01010101u, u); u = __dp4a(v.y, 0x01010101u, u);
+            u = __dp4a(v.z, 0x01010101u, u); u = __dp4a(v.w, 0x01010101u, u);
+            s = (int)u;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) R[r] = s - sub;
+}
+
+// Receptive-field sums of an NHWC map for the direct path:
+// S[pos] = sum over taps inside the map and channels of (x - x_zp).  One thread per output position.
+__global__ void __launch_bounds__(256) conv_possum_kernel(
+        const uint8_t* __restrict__ x, int x_signed, int N, int H, int W, int C, int64_t cs, int KH, int KW, int sh, int sw, int pt, int pl, int Ho,
+        int Wo, int x_zp, int32_t* __restrict__ S) {
+    const int64_t total = (int64_t)N * Ho * Wo;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int wo = (int)(idx % Wo);
+    const int64_t r = idx / Wo;
+    const int ho = (int)(r % Ho);
+    const int n = (int)(r / Ho);
+    int s = 0;
+    for (int kh = 0; kh < KH; ++kh) {
+        const int hi = ho * sh - pt + kh;
+        if (hi < 0 || hi >= H) continue;
+        for (int kw = 0; kw < KW; ++kw) {
+            const int wi = wo * sw - pl + kw;
+            if (wi < 0 || wi >= W) continue;
+            const uint8_t* p = x + (((int64_t)n * H + hi) * W + wi) * cs;
+            for (int c = 0; c < C; ++c) s += (x_signed ? (int)(int8_t)p[c] : (int)p[c]) - x_zp;
+        }
+    }
+    S[idx] = s;
+}
+
+inline int blocks_for(int64_t threads_needed, int block = 256) {
+    int64_t b = (threads_needed + block - 1) / block;
+    if (b < 1) b = 1;
+    if (b > 1048576) b = 1048576;
+    return (int)b;
+}
+
+// ---------------------------------------------------------------------------------------------
+// GEMM dispatch shared by MatMulInteger and QLinearMatMul.
+// ---------------------------------------------------------------------------------------------
+struct GemmWs {
+    size_t bt_off, t_off, zbn_off, r_off, total;
+    int bk;
+    int64_t k_pad;
+};
+
+GemmWs gemm_ws_layout(int64_t M, int64_t N, int64_t K) {
+    GemmWs w;
+    w.bk = choose_bk((int)(K > (1 << 20) ? 128 : K));
+    w.k_pad = (K + w.bk - 1) / w.bk * w.bk;
+    size_t off = 0;
+    w.bt_off = off; off += align_up((size_t)N * (size_t)w.k_pad, 256);
+    w.t_off = off; off += align_up((size_t)N * 4, 256);
+    w.zbn_off = off; off += align_up((size_t)N * 4, 256);
+    w.r_off = off; off += align_up((size_t)M * 4, 256);
+    w.total = off;
+    return w;
+}
+
+bool gemm_tc_eligible(const void* a, int64_t M, int64_t N, int64_t K) {
+    return K % 16 == 0 && K >= 16 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && M >= 1 && N >= 1 && M < (1ll << 31) && N < (1ll << 31) &&
+           K < (1ll << 31);
+}
+
+int gemm_dispatch(
+        const char* op, const void* a, bool a_signed, const void* b, bool b_signed, int64_t batch, int64_t M, int64_t N, int64_t K,
+        const ZpSpec& za, const ZpSpec& zb, const EpiArgs& epi, void* y, size_t y_elem, void* workspace, size_t workspace_bytes, int path,
+        cudaStream_t s) {
+    if (batch == 0 || M == 0 || N == 0) return CHXQ_OK;
+    const bool tc_ok = gemm_tc_eligible(a, M, N, K) && ((M * K) % 16 == 0 || batch == 1);
+    bool use_tc = path == CHXQ_PATH_TENSOR || (path == CHXQ_PATH_AUTO && tc_ok);
+    if (path == CHXQ_PATH_TENSOR && !tc_ok)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "%s: tensor-core path needs K %% 16 == 0 and a 16-byte aligned A (M=%lld N=%lld K=%lld)", op,
+                         (long long)M, (long long)N, (long long)K);
+    if (use_tc) {
+        const GemmWs ws = gemm_ws_layout(M, N, K);
+        if (workspace == nullptr || workspace_bytes < ws.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) {
+            if (path == CHXQ_PATH_TENSOR)
+                return set_error(CHXQ_ERR_WORKSPACE, "%s: tensor-core path needs %zu bytes of 256-byte aligned workspace (got %zu)", op, ws.total,
+                                 workspace_bytes);
+            use_tc = false;
+        }
+    }
+    if (!use_tc) return launch_gemm_simt(a, a_signed, b, b_signed, batch, M, N, K, za, zb, epi, y, s);
+
+    const GemmWs ws = gemm_ws_layout(M, N, K);
+    uint8_t* wsp = static_cast<uint8_t*>(workspace);
+    uint8_t* bt = wsp + ws.bt_off;
+    int32_t* T = reinterpret_cast<int32_t*>(wsp + ws.t_off);
+    int32_t* zbn = reinterpret_cast<int32_t*>(wsp + ws.zbn_off);
+    int32_t* R = reinterpret_cast<int32_t*>(wsp + ws.r_off);
+    for (int64_t bi = 0; bi < batch; ++bi) {
+        const uint8_t* ab = static_cast<const uint8_t*>(a) + bi * M * K;
+        const uint8_t* bb = static_cast<const uint8_t*>(b) + bi * K * N;
+        dim3 tgrid((unsigned)((N + 31) / 32), (unsigned)((ws.k_pad + 31) / 32)), tblock(32, 8);
+        if (tgrid.y > 65535) return set_error(CHXQ_ERR_UNSUPPORTED, "%s: K too large for the repacking grid", op);
+        transpose_b_kernel<<<tgrid, tblock, 0, s>>>(bb, K, N, ws.k_pad, bt);
+        const bool need_cols = za.len > 0 || zb.len > 0;
+        if (need_cols) gemm_col_terms_kernel<<<blocks_for(N), 256, 0, s>>>(bb, b_signed, a_signed, K, N, za, zb, T, zbn);
+        if (zb.len > 0) gemm_row_terms_kernel<<<blocks_for(M * 32), 256, 0, s>>>(ab, a_signed, M, K, za, R);
+        CHXQ_LAUNCH_CHECK();
+        TcProblem p{};
+        p.a = ab; p.a_signed = a_signed; p.C = (int)K; p.a_cs = K; p.W = (int)M; p.H = 1; p.N = 1;
+        p.b = bt; p.b_signed = b_signed; p.cols = (int)N; p.c_pad = (int)ws.k_pad; p.bk = ws.bk;
+        p.KH = 1; p.KW = 1; p.pad_top = 0; p.pad_left = 0;
+        p.Wo = (int)M; p.Ho = 1; p.No = 1; p.Wb = 128; p.Hb = 1; p.Nb = 1; p.bn = 0;
+        p.y = static_cast<uint8_t*>(y) + (size_t)bi * M * N * y_elem;
+        p.ldc = N;
+        p.col_corr = za.len > 0 ? T : nullptr;
+        p.col_scale = 1;
+        p.col_mul = zb.len > 0 ? zbn : nullptr;
+        p.row_corr = zb.len > 0 ? R : nullptr;
+        p.epi = epi;
+        if (epi.residual) p.epi.residual = epi.residual + (size_t)bi * M * N;
+        const int rc = launch_tc_igemm(p, s);
+        if (rc != CHXQ_OK) return rc;
+    }
+    return CHXQ_OK;
+}
+
+int check_zp_len(const char* op, const char* which, const void* ptr, int64_t len, int64_t axis_len) {
+    if (len == 0) return CHXQ_OK;
+    if (ptr == nullptr) return set_error(CHXQ_ERR_INVALID_ARGUMENT, "%s: %s has length %lld but a null pointer", op, which, (long long)len);
+    if (len != 1 && len != axis_len)
+        return set_error(CHXQ_ERR_INVALID_ARGUMENT, "%s: %s has %lld elements; expected 1 or %lld", op, which, (long long)len, (long long)axis_len);
+    return CHXQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Convolution dispatch shared by ConvInteger and QLinearConv.
+// ---------------------------------------------------------------------------------------------
+int validate_geom(const char* op, const chxq_conv_geom* g) {
+    CHXQ_CHECK_ARG(g != nullptr, "%s: null geometry", op);
+    CHXQ_CHECK_ARG(g->N >= 0 && g->C > 0 && g->H > 0 && g->W > 0 && g->M > 0 && g->KH > 0 && g->KW > 0, "%s: bad tensor extents", op);
+    CHXQ_CHECK_ARG(g->group >= 1 && g->C % g->group == 0 && g->M % g->group == 0, "%s: channels (%d, %d) not divisible by group %d", op, g->C,
+                   g->M, g->group);
+    CHXQ_CHECK_ARG(g->stride_h >= 1 && g->stride_w >= 1, "%s: strides must be positive", op);
+    CHXQ_CHECK_ARG(is_q8(g->x_dtype) && is_q8(g->w_dtype), "%s: x and w must be uint8 or int8", op);
+    CHXQ_CHECK_ARG((g->x_layout == CHXQ_NCHW || g->x_layout == CHXQ_NHWC) && (g->y_layout == CHXQ_NCHW || g->y_layout == CHXQ_NHWC),
+                   "%s: unknown layout", op);
+    const int Ho = (g->H + g->pad_top + g->pad_bottom - g->KH) / g->stride_h + 1;
+    const int Wo = (g->W + g->pad_left + g->pad_right - g->KW) / g->stride_w + 1;
+    CHXQ_CHECK_ARG(g->H + g->pad_top + g->pad_bottom >= g->KH && g->W + g->pad_left + g->pad_right >= g->KW, "%s: kernel larger than padded input",
+                   op);
+    CHXQ_CHECK_ARG(Ho == g->Ho && Wo == g->Wo, "%s: output extent (%d, %d) does not match the geometry (%d, %d)", op, g->Ho, g->Wo, Ho, Wo);
+    CHXQ_CHECK_ARG(g->x_cstride == 0 || (g->x_layout == CHXQ_NHWC && g->x_cstride >= g->C), "%s: bad x channel stride", op);
+    CHXQ_CHECK_ARG(g->y_cstride == 0 || (g->y_layout == CHXQ_NHWC && g->y_cstride >= g->M), "%s: bad y channel stride", op);
+    return CHXQ_OK;
+}
+
+struct ConvWs {
+    size_t pack_off, wsum_off, zw_off, flag_off, pack_total;  // packed-weight blob
+    size_t im2col_bytes, rowsum_bytes;
+};
+
+ConvWs conv_ws_layout(const chxq_conv_geom& g, const TcConvPlan& pl) {
+    ConvWs w{};
+    size_t off = 0;
+    w.pack_off = off; off += align_up((size_t)g.M * (size_t)pl.k_total, 1024);
+    w.wsum_off = off; off += align_up((size_t)g.M * 4, 256);
+    w.zw_off = off; off += align_up((size_t)g.M * 4, 256);
+    w.flag_off = off; off += 256;
+    w.pack_total = off;
+    const size_t rows = (size_t)g.N * g.Ho * g.Wo;
+    w.im2col_bytes = align_up(rows * (size_t)pl.k_total, 1024);
+    w.rowsum_bytes = align_up(rows * 4, 256);
+    return w;
+}
+
+bool needs_im2col(const chxq_conv_geom& g, const TcConvPlan& pl, int x_zp) {
+    if (pl.path == kTcIm2col) return true;
+    const bool padded = g.pad_top || g.pad_left || g.pad_bottom || g.pad_right;
+    return pl.path == kTcDirect && padded && x_zp != 0;
+}
+
+int pack_weights(const void* w, const chxq_conv_geom& g, const TcConvPlan& pl, const ZpSpec& zw, uint8_t* blob, cudaStream_t s) {
+    const ConvWs L = conv_ws_layout(g, pl);
+    const int taps = g.KH * g.KW;
+    int32_t* flag = reinterpret_cast<int32_t*>(blob + L.flag_off);
+    CHXQ_CUDA(cudaMemsetAsync(flag, 0, 4, s));
+    pack_weights_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, g.C, taps, pl.c_pitch, pl.k_total,
+                                                                              blob + L.pack_off);
+    weight_terms_kernel<<<blocks_for((int64_t)g.M * 32), 256, 0, s>>>(w, g.w_dtype == CHXQ_INT8, g.M, g.C * taps, zw,
+                                                                     reinterpret_cast<int32_t*>(blob + L.wsum_off),
+                                                                     reinterpret_cast<int32_t*>(blob + L.zw_off), flag);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+// Runs a planned convolution on the tensor-core kernel from a packed weight blob.
+int conv_tc_run(
+        const void* x, const uint8_t* blob, const chxq_conv_geom& g, const TcConvPlan& pl, int x_zp, bool zw_zero, const EpiArgs& epi, void* y,
+        uint8_t* scratch, size_t scratch_bytes, cudaStream_t s) {
+    const ConvWs L = conv_ws_layout(g, pl);
+    const int taps = g.KH * g.KW;
+    const int64_t rows = (int64_t)g.N * g.Ho * g.Wo;
+    if (rows == 0) return CHXQ_OK;
+    const bool im2col = needs_im2col(g, pl, x_zp);
+    const size_t need = (im2col ? L.im2col_bytes : 0) + (zw_zero ? 0 : L.rowsum_bytes);
+    if (need > 0 && (scratch == nullptr || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u)))
+        return set_error(CHXQ_ERR_WORKSPACE, "convolution: tensor-core path needs %zu bytes of 256-byte aligned workspace (got %zu)", need,
+                         scratch_bytes);
+    const int64_t xcs = g.x_cstride > 0 ? g.x_cstride : g.C;
+    const int64_t ycs = g.y_cstride > 0 ? g.y_cstride : g.M;
+    const bool x_signed = g.x_dtype == CHXQ_INT8;
+    TcProblem p{};
+    int32_t* rowsum = nullptr;
+    if (im2col) {
+        uint8_t* A = scratch;
+        int rc = launch_im2col(x, g, pl.c_pitch, pl.k_total, x_zp & 0xff, A, s);
+        if (rc != CHXQ_OK) return rc;
+        if (!zw_zero) {
+            rowsum = reinterpret_cast<int32_t*>(scratch + L.im2col_bytes);
+            rowsum_matrix_kernel<<<blocks_for(rows * 32), 256, 0, s>>>(A, x_signed, rows, pl.k_total, taps * g.C * x_zp, rowsum);
+            CHXQ_LAUNCH_CHECK();
+        }
+        if (rows >= (1ll << 31)) return set_error(CHXQ_ERR_UNSUPPORTED, "convolution: too many output positions");
+        p.a = A; p.C = pl.k_total; p.a_cs = pl.k_total; p.W = (int)rows; p.H = 1; p.N = 1;
+        p.c_pad = pl.k_total; p.KH = 1; p.KW = 1; p.pad_top = 0; p.pad_left = 0;
+        p.Wo = (int)rows; p.Ho = 1; p.No = 1; p.Wb = 128; p.Hb = 1; p.Nb = 1;
+    } else {
+        if (!zw_zero) {
+            rowsum = reinterpret_cast<int32_t*>(scratch);
+            conv_possum_kernel<<<blocks_for(rows), 256, 0, s>>>(static_cast<const uint8_t*>(x), x_signed, g.N, g.H, g.W, g.C, xcs, g.KH, g.KW,
+                                                              g.stride_h, g.stride_w, g.pad_top, g.pad_left, g.Ho, g.Wo, x_zp, rowsum);
+            CHXQ_LAUNCH_CHECK();
+        }
+        p.a = x; p.C = g.C; p.a_cs = xcs;
+        if (pl.Wb == 128 && taps == 1) {
+            p.W = (int)((int64_t)g.N * g.H * g.W); p.H = 1; p.N = 1;
+            p.Wo = (int)rows; p.Ho = 1; p.No = 1;
+        } else {
+            p.W = g.W; p.H = g.H; p.N = g.N;
+            p.Wo = g.Wo; p.Ho = g.Ho; p.No = g.N;
+        }
+        p.c_pad = pl.c_pitch; p.KH = g.KH; p.KW = g.KW; p.pad_top = g.pad_top; p.pad_left = g.pad_left;
+        p.Wb = pl.Wb; p.Hb = pl.Hb; p.Nb = pl.Nb;
+    }
+    p.a_signed = x_signed;
+    p.b = blob + L.pack_off; p.b_signed = g.w_dtype == CHXQ_INT8; p.cols = g.M; p.bk = pl.bk; p.bn = 0;
+    p.y = y; p.ldc = ycs;
+    p.col_corr = x_zp != 0 ? reinterpret_cast<const int32_t*>(blob + L.wsum_off) : nullptr;
+    p.col_scale = x_zp;
+    p.col_mul = zw_zero ? nullptr : reinterpret_cast<const int32_t*>(blob + L.zw_off);
+    p.row_corr = zw_zero ? nullptr : rowsum;
+    p.epi = epi;
+    return launch_tc_igemm(p, s);
+}
+
+int conv_dispatch(
+        const char* op, const void* x, const void* w, const chxq_conv_geom* g, int has_x_zp, int x_zp, const ZpSpec& zw, const EpiArgs& epi,
+        void* y, void* workspace, size_t workspace_bytes, int path, cudaStream_t s) {
+    int rc = validate_geom(op, g);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(x && w && y, "%s: null buffer", op);
+    CHXQ_CHECK_ARG(path == CHXQ_PATH_AUTO || path == CHXQ_PATH_SIMT || path == CHXQ_PATH_TENSOR, "%s: bad path", op);
+    const int xz = has_x_zp ? x_zp : 0;
+    const TcConvPlan pl = plan_tc_conv(*g);
+    const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    bool use_tc = path != CHXQ_PATH_SIMT && pl.path != kTcNone && aligned;
+    if (path == CHXQ_PATH_TENSOR && !use_tc)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "%s: the tensor-core path needs group == 1, NHWC output and a 16-byte aligned input", op);
+    if (use_tc) {
+        const ConvWs L = conv_ws_layout(*g, pl);
+        const bool zw_zero = zw.len == 0;  // a zero point that is present is not read back: treat it as non-zero
+        const size_t need = L.pack_total + (needs_im2col(*g, pl, xz) ? L.im2col_bytes : 0) + (zw_zero ? 0 : L.rowsum_bytes);
+        if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) {
+            if (path == CHXQ_PATH_TENSOR)
+                return set_error(CHXQ_ERR_WORKSPACE, "%s: tensor-core path needs %zu bytes of 256-byte aligned workspace (got %zu)", op, need,
+                                 workspace_bytes);
+            use_tc = false;
+        } else {
+            uint8_t* blob = static_cast<uint8_t*>(workspace);
+            rc = pack_weights(w, *g, pl, zw, blob, s);
+            if (rc != CHXQ_OK) return rc;
+            return conv_tc_run(x, blob, *g, pl, xz, zw_zero, epi, y, blob + L.pack_total, workspace_bytes - L.pack_total, s);
+        }
+    }
+    return launch_conv_simt(x, w, *g, has_x_zp, x_zp, zw.ptr, zw.len, epi, y, s);
+}
+
+int fill_requant(const char* op, const chxq_qconv_params* p, const chxq_conv_geom* g, EpiArgs* e) {
+    CHXQ_CHECK_ARG(p != nullptr, "%s: null parameters", op);
+    CHXQ_CHECK_ARG(is_q8(p->y_dtype), "%s: y_zero_point dtype must be uint8 or int8", op);
+    const bool ys = p->y_dtype == CHXQ_INT8;
+    CHXQ_CHECK_ARG(p->y_zero_point >= (ys ? -128 : 0) && p->y_zero_point <= (ys ? 127 : 255), "%s: y zero point %d out of range", op,
+                   p->y_zero_point);
+    const bool xs = g->x_dtype == CHXQ_INT8;
+    CHXQ_CHECK_ARG(p->x_zero_point >= (xs ? -128 : 0) && p->x_zero_point <= (xs ? 127 : 255), "%s: x zero point %d out of range", op,
+                   p->x_zero_point);
+    // runtime/ops/quantize.cc:76-88: per-channel needs one scale and zero point per output channel, else both are 0-d.
+    CHXQ_CHECK_ARG(p->w_params_len == 1 || p->w_params_len == g->M, "%s: w_scale / w_zero_point must have 1 or M=%d elements (got %lld)", op,
+                   g->M, (long long)p->w_params_len);
+    CHXQ_CHECK_ARG(p->w_scale != nullptr && p->w_zero_point != nullptr, "%s: null weight scale or zero point", op);
+    CHXQ_CHECK_ARG(p->round_mode == CHXQ_ROUND_REF_HALF_UP || p->round_mode == CHXQ_ROUND_RNE, "%s: bad round_mode", op);
+    CHXQ_CHECK_ARG(p->residual == nullptr || p->y_dtype == CHXQ_UINT8, "%s: the residual tail needs a uint8 output", op);
+    memset(e, 0, sizeof(*e));
+    e->mode = kEpiRequant;
+    e->x_scale = p->x_scale;
+    e->w_scale = p->w_scale;
+    e->w_per_channel = p->w_params_len != 1;
+    e->bias = p->bias;
+    e->rq.y_scale = p->y_scale;
+    e->rq.y_zp_f = (float)p->y_zero_point;
+    e->rq.y_has_zp = p->y_zero_point != 0;
+    e->rq.y_signed = ys;
+    e->rq.round_mode = p->round_mode;
+    e->rq.clamp_hi_q = p->clamp_hi_q;
+    e->residual = static_cast<const uint8_t*>(p->residual);
+    e->rq.res_scale = p->res_scale;
+    e->rq.res_zp_f = (float)p->res_zero_point;
+    e->rq.res_has_zp = p->res_zero_point != 0;
+    e->rq.res_relu = p->res_relu;
+    e->rq.out_scale = p->out_scale;
+    e->rq.out_zp_f = (float)p->out_zero_point;
+    e->rq.out_has_zp = p->out_zero_point != 0;
+    return CHXQ_OK;
+}
+
+}  // namespace
+}  // namespace chxq
+
+using namespace chxq;
+
+extern "C" size_t chxq_matmul_integer_workspace(int64_t batch, int64_t M, int64_t N, int64_t K) {
+    (void)batch;
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return gemm_ws_layout(M, N, K).total;
+}
+
+extern "C" int chxq_matmul_integer(
+        const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t batch, int64_t M, int64_t N, int64_t K, const void* a_zero_point,
+        int64_t a_zp_len, const void* b_zero_point, int64_t b_zp_len, int32_t* y, void* workspace, size_t workspace_bytes, int32_t path,
+        void* stream) {
+    CHXQ_CHECK_ARG(is_q8(a_dtype) && is_q8(b_dtype), "MatMulInteger: operands must be uint8 or int8 (got %d, %d)", a_dtype, b_dtype);
+    CHXQ_CHECK_ARG(batch >= 0 && M >= 0 && N >= 0 && K >= 0, "MatMulInteger: negative extent");
+    CHXQ_CHECK_ARG(path == CHXQ_PATH_AUTO || path == CHXQ_PATH_SIMT || path == CHXQ_PATH_TENSOR, "MatMulInteger: bad path");
+    int rc = check_zp_len("MatMulInteger", "a_zero_point", a_zero_point, a_zp_len, K);
+    if (rc != CHXQ_OK) return rc;
+    rc = check_zp_len("MatMulInteger", "b_zero_point", b_zero_point, b_zp_len, N);
+    if (rc != CHXQ_OK) return rc;
+    if (batch * M * N == 0) return CHXQ_OK;
+    CHXQ_CHECK_ARG(y != nullptr && (K == 0 || (a && b)), "MatMulInteger: null buffer");
+    cudaStream_t s = as_stream(stream);
+    if (K == 0) {
+        CHXQ_CUDA(cudaMemsetAsync(y, 0, (size_t)batch * M * N * 4, s));
+        return CHXQ_OK;
+    }
+    EpiArgs epi{};
+    epi.mode = kEpiInt32;
+    const ZpSpec za{a_zero_point, a_zp_len, 0}, zb{b_zero_point, b_zp_len, 0};
+    return gemm_dispatch("MatMulInteger", a, a_dtype == CHXQ_INT8, b, b_dtype == CHXQ_INT8, batch, M, N, K, za, zb, epi, y, 4, workspace,
+                         workspace_bytes, path, s);
+}
+
+extern "C" int chxq_qlinear_matmul(
+        const void* a, int32_t a_dtype, float a_scale, int32_t a_zero_point, const void* b, int32_t b_dtype, float b_scale, int32_t b_zero_point,
+        float y_scale, int32_t y_zero_point, int32_t y_dtype, int64_t M, int64_t N, int64_t K, int32_t round_mode, void* y, void* workspace,
+        size_t workspace_bytes, int32_t path, void* stream) {
+    CHXQ_CHECK_ARG(is_q8(a_dtype) && is_q8(b_dtype) && is_q8(y_dtype), "QLinearMatMul: a, b and y must be uint8 or int8");
+    CHXQ_CHECK_ARG(M >= 0 && N >= 0 && K > 0, "QLinearMatMul: bad extents");
+    CHXQ_CHECK_ARG(path == CHXQ_PATH_AUTO || path == CHXQ_PATH_SIMT || path == CHXQ_PATH_TENSOR, "QLinearMatMul: bad path");
+    CHXQ_CHECK_ARG(round_mode == CHXQ_ROUND_REF_HALF_UP || round_mode == CHXQ_ROUND_RNE, "QLinearMatMul: bad round_mode");
+    const bool ys = y_dtype == CHXQ_INT8;
+    CHXQ_CHECK_ARG(y_zero_point >= (ys ? -128 : 0) && y_zero_point <= (ys ? 127 : 255), "QLinearMatMul: y zero point %d out of range", y_zero_point);
+    if (M * N == 0) return CHXQ_OK;
+    CHXQ_CHECK_ARG(a && b && y, "QLinearMatMul: null buffer");
+    EpiArgs epi{};
+    epi.mode = kEpiRequant;
+    epi.w_scale = nullptr;
+    epi.mult_scalar = a_scale * b_scale;  // fp32 product, as dequantized operands carry it
+    epi.rq.y_scale = y_scale;
+    epi.rq.y_zp_f = (float)y_zero_point;
+    epi.rq.y_has_zp = y_zero_point != 0;
+    epi.rq.y_signed = ys;
+    epi.rq.round_mode = round_mode;
+    epi.rq.clamp_hi_q = -1;
+    const ZpSpec za{nullptr, a_zero_point != 0 ? 1 : 0, a_zero_point}, zb{nullptr, b_zero_point != 0 ? 1 : 0, b_zero_point};
+    return gemm_dispatch("QLinearMatMul", a, a_dtype == CHXQ_INT8, b, b_dtype == CHXQ_INT8, 1, M, N, K, za, zb, epi, y, 1, workspace,
+                         workspace_bytes, path, as_stream(stream));
+}
+
+extern "C" int chxq_conv_resolve_geometry(
+        int32_t N, int32_t C, int32_t H, int32_t W, int32_t M, int32_t Cg, int32_t KH, int32_t KW, const int64_t* strides, int32_t n_strides,
+        const int64_t* pads, int32_t n_pads, int32_t group, const char* auto_pad, chxq_conv_geom* out) {
+    CHXQ_CHECK_ARG(out != nullptr, "conv geometry: null output");
+    CHXQ_CHECK_ARG(group >= 1 && (int64_t)Cg * group == C, "conv geometry: weight has %d input channels per group, input has %d channels in %d groups",
+                   Cg, C, group);
+    CHXQ_CHECK_ARG(n_strides == 0 || n_strides == 2, "conv geometry: strides must be empty or have one value per spatial dim");
+    CHXQ_CHECK_ARG(n_pads == 0 || n_pads == 2, "conv geometry: pads must be empty or have one value per spatial dim (begin == end)");
+    memset(out, 0, sizeof(*out));
+    // ComplementStride / ComplementPad (runtime/chainerx_util.cc:180-200): empty -> 1 / 0.
+    const int64_t sh = n_strides ? strides[0] : 1, sw = n_strides ? strides[1] : 1;
+    int64_t pt = n_pads ? pads[0] : 0, pl = n_pads ? pads[1] : 0;
+    int64_t pb = pt, pr = pl;
+    CHXQ_CHECK_ARG(sh >= 1 && sw >= 1, "conv geometry: strides must be positive");
+    if (auto_pad && auto_pad[0] && strcmp(auto_pad, "NOTSET") != 0) {
+        // CalculateAutoPad (runtime/chainerx_util.cc:276-311) knows SAME_UPPER only.
+        CHXQ_CHECK_ARG(strcmp(auto_pad, "SAME_UPPER") == 0, "conv geometry: auto_pad '%s' is not supported (SAME_UPPER only)", auto_pad);
+        const int64_t th = (H + sh - 1) / sh, tw = (W + sw - 1) / sw;
+        const int64_t nh = (th - 1) * sh + KH - H, nw = (tw - 1) * sw + KW - W;
+        pt = nh / 2; pb = nh - pt;
+        pl = nw / 2; pr = nw - pl;
+        if (!(pb > 0 || pr > 0)) {  // no end padding is materialised: begin pads apply to both sides
+            pb = pt;
+            pr = pl;
+        }
+    }
+    CHXQ_CHECK_ARG(H + pt + pb >= KH && W + pl + pr >= KW, "conv geometry: kernel larger than padded input");
+    out->N = N; out->C = C; out->H = H; out->W = W; out->M = M; out->KH = KH; out->KW = KW;
+    out->stride_h = (int32_t)sh; out->stride_w = (int32_t)sw;
+    out->pad_top = (int32_t)pt; out->pad_left = (int32_t)pl; out->pad_bottom = (int32_t)pb; out->pad_right = (int32_t)pr;
+    out->group = group;
+    out->Ho = (int32_t)((H + pt + pb - KH) / sh + 1);
+    out->Wo = (int32_t)((W + pl + pr - KW) / sw + 1);
+    out->x_dtype = CHXQ_UINT8; out->w_dtype = CHXQ_INT8;
+    out->x_layout = CHXQ_NCHW; out->y_layout = CHXQ_NCHW;
+    return CHXQ_OK;
+}
+
+extern "C" size_t chxq_conv_workspace(const chxq_conv_geom* g) {
+    if (!g || validate_geom("conv workspace", g) != CHXQ_OK) return 0;
+    const TcConvPlan pl = plan_tc_conv(*g);
+    if (pl.path == kTcNone) return 0;
+    const ConvWs L = conv_ws_layout(*g, pl);
+    const bool padded = g->pad_top || g->pad_left || g->pad_bottom || g->pad_right;
+    // Worst case over zero points: an explicit im2col matrix when the direct path cannot express the
+    // padding value, and per-position sums when the weight zero point is non-zero.
+    const size_t im2col = (pl.path == kTcIm2col || padded) ? L.im2col_bytes : 0;
+    return L.pack_total + im2col + L.rowsum_bytes;
+}
+
+extern "C" int chxq_conv_integer(
+        const void* x, const void* w, const chxq_conv_geom* g, int32_t has_x_zp, int32_t x_zero_point, const void* w_zero_point,
+        int64_t w_zp_len, int32_t* y, void* workspace, size_t workspace_bytes, int32_t path, void* stream) {
+    int rc = validate_geom("ConvInteger", g);
+    if (rc != CHXQ_OK) return rc;
+    rc = check_zp_len("ConvInteger", "w_zero_point", w_zero_point, w_zp_len, g->M);
+    if (rc != CHXQ_OK) return rc;
+    EpiArgs epi{};
+    epi.mode = kEpiInt32;
+    const ZpSpec zw{w_zero_point, w_zp_len, 0};
+    return conv_dispatch("ConvInteger", x, w, g, has_x_zp, x_zero_point, zw, epi, y, workspace, workspace_bytes, path, as_stream(stream));
+}
+
+extern "C" int chxq_qlinear_conv(
+        const void* x, const void* w, const chxq_conv_geom* g, const chxq_qconv_params* p, void* y, void* workspace, size_t workspace_bytes,
+        int32_t path, void* stream) {
+    int rc = validate_geom("QLinearConv", g);
+    if (rc != CHXQ_OK) return rc;
+    EpiArgs epi;
+    rc = fill_requant("QLinearConv", p, g, &epi);
+    if (rc != CHXQ_OK) return rc;
+    const ZpSpec zw{p->w_zero_point, p->w_params_len, 0};
+    return conv_dispatch("QLinearConv", x, w, g, 1, p->x_zero_point, zw, epi, y, workspace, workspace_bytes, path, as_stream(stream));
+}
+
+extern "C" size_t chxq_conv_prepack_bytes(const chxq_conv_geom* g) {
+    if (!g || validate_geom("conv prepack", g) != CHXQ_OK) return 0;
+    const TcConvPlan pl = plan_tc_conv(*g);
+    if (pl.path == kTcNone) return 0;
+    return conv_ws_layout(*g, pl).pack_total;
+}
+
+extern "C" int chxq_conv_prepack(
+        const void* w, const chxq_conv_geom* g, const void* w_zero_point, int64_t w_zp_len, void* packed, size_t packed_bytes, int32_t* eligible,
+        void* stream) {
+    int rc = validate_geom("conv prepack", g);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(eligible != nullptr, "conv prepack: null eligible pointer");
+    *eligible = 0;
+    rc = check_zp_len("conv prepack", "w_zero_point", w_zero_point, w_zp_len, g->M);
+    if (rc != CHXQ_OK) return rc;
+    const TcConvPlan pl = plan_tc_conv(*g);
+    if (pl.path == kTcNone) return CHXQ_OK;
+    const ConvWs L = conv_ws_layout(*g, pl);
+    CHXQ_CHECK_ARG(w && packed && packed_bytes >= L.pack_total && (reinterpret_cast<uintptr_t>(packed) & 255u) == 0,
+                   "conv prepack: need %zu bytes of 256-byte aligned memory", L.pack_total);
+    cudaStream_t s = as_stream(stream);
+    uint8_t* blob = static_cast<uint8_t*>(packed);
+    const ZpSpec zw{w_zero_point, w_zp_len, 0};
+    rc = pack_weights(w, *g, pl, zw, blob, s);
+    if (rc != CHXQ_OK) return rc;
+    int32_t flag = 0;
+    CHXQ_CUDA(cudaMemcpyAsync(&flag, blob + L.flag_off, 4, cudaMemcpyDeviceToHost, s));
+    CHXQ_CUDA(cudaStreamSynchronize(s));
+    *eligible = 1 | (flag == 0 ? 2 : 0);
+    return CHXQ_OK;
+}
+
+static int packed_common(const char* op, const void* x, const void* packed, const chxq_conv_geom* g, int32_t packed_flags, TcConvPlan* pl) {
+    int rc = validate_geom(op, g);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(x && packed, "%s: null buffer", op);
+    CHXQ_CHECK_ARG((packed_flags & 1) != 0, "%s: these weights were not packed for the tensor-core path", op);
+    *pl = plan_tc_conv(*g);
+    if (pl->path == kTcNone || (reinterpret_cast<uintptr_t>(x) & 15u))
+        return set_error(CHXQ_ERR_UNSUPPORTED, "%s: geometry or input alignment is not eligible for the tensor-core path", op);
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_qlinear_conv_packed(
+        const void* x, const void* packed, const chxq_conv_geom* g, const chxq_qconv_params* p, int32_t packed_flags, void* y, void* workspace,
+        size_t workspace_bytes, void* stream) {
+    TcConvPlan pl;
+    int rc = packed_common("QLinearConv(packed)", x, packed, g, packed_flags, &pl);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(y != nullptr, "QLinearConv(packed): null output");
+    EpiArgs epi;
+    rc = fill_requant("QLinearConv(packed)", p, g, &epi);
+    if (rc != CHXQ_OK) return rc;
+    return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, p->x_zero_point, (packed_flags & 2) != 0, epi, y,
+                       static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream));
+}
+
+extern "C" int chxq_conv_integer_packed(
+        const void* x, const void* packed, const chxq_conv_geom* g, int32_t has_x_zp, int32_t x_zero_point, int32_t packed_flags, int32_t* y,
+        void* workspace, size_t workspace_bytes, void* stream) {
+    TcConvPlan pl;
+    int rc = packed_common("ConvInteger(packed)", x, packed, g, packed_flags, &pl);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(y != nullptr, "ConvInteger(packed): null output");
+    EpiArgs epi{};
+    epi.mode = kEpiInt32;
+    return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, has_x_zp ? x_zero_point : 0, (packed_flags & 2) != 0, epi, y,
+                       static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream));
+}

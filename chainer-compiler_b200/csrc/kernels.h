@@ -1,0 +1,81 @@
+// Internal launch interfaces between the translation units of libchxq.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/chxq.h"
+#include "epilogue.cuh"
+
+namespace chxq {
+
+// ---- CUDA-core kernels (simt.cu) ----
+// A zero point as the ops receive it: absent (len 0), one value (len 1; read from `ptr`, or `scalar`
+// when ptr is null) or a device vector of the operand's dtype aligned with the operand's last axis.
+struct ZpSpec {
+    const void* ptr;
+    int64_t len;
+    int scalar;
+};
+
+int launch_gemm_simt(
+        const void* a, bool a_signed, const void* b, bool b_signed, int64_t batch, int64_t M, int64_t N, int64_t K, const ZpSpec& za,
+        const ZpSpec& zb, const EpiArgs& epi, void* y, cudaStream_t s);
+int launch_conv_simt(
+        const void* x, const void* w, const chxq_conv_geom& g, int has_x_zp, int x_zp, const void* w_zp, int64_t w_zp_len, const EpiArgs& epi,
+        void* y, cudaStream_t s);
+// A[row, k], row = (n, ho, wo), k = tap * c_pitch + c, row length k_pad (multiple of 16); padding
+// positions hold pad_byte, columns with c >= C or tap >= KH*KW hold 0.
+int launch_im2col(const void* x, const chxq_conv_geom& g, int c_pitch, int k_pad, int pad_byte, void* a, cudaStream_t s);
+
+// ---- tcgen05 implicit-GEMM kernel (tc_igemm.cu) ----
+// Problem: D[row, col] = sum_k A[row, k] * B[col, k] over u8/s8 operands, both K-major.
+// A is read through a 4-D tensor map {C, W, H, N} (an NHWC activation, or a plain matrix with
+// W = rows and H = N = 1); a tile is a box of Wb x Hb x Nb = 128 output positions and the K loop
+// walks taps (kh, kw) x channel chunks, shifting the box by the tap offset (stride-1 convolution
+// with zero fill outside the map).  B is a packed weight matrix [cols, taps * c_pad].
+struct TcProblem {
+    // A operand
+    const void* a;
+    int a_signed;
+    int C;            // channels (K extent per tap) present in memory
+    int64_t a_cs;     // bytes between consecutive W positions
+    int W, H, N;      // extents of the A map
+    // B operand
+    const void* b;    // [cols][taps * c_pad]
+    int b_signed;
+    int cols;
+    int c_pad;        // per-tap K extent in B (multiple of bk)
+    int bk;           // 32 / 64 / 128
+    // convolution taps (1,1,0,0 for a plain GEMM)
+    int KH, KW, pad_top, pad_left;
+    // output extents (positions) and tile box
+    int Wo, Ho, No;
+    int Wb, Hb, Nb;
+    int bn;           // 64 / 128 / 256 ; 0 = choose
+    // output
+    void* y;
+    int64_t ldc;      // elements between consecutive output positions
+    // zero-point terms: acc = raw - col_scale * col_corr[col] - col_mul[col] * row_corr[pos]
+    const int32_t* col_corr;
+    int col_scale;
+    const int32_t* col_mul;
+    const int32_t* row_corr;
+    EpiArgs epi;
+};
+
+int launch_tc_igemm(const TcProblem& p, cudaStream_t s);
+
+// Tensor-core planning shared by pre-packing and execution.
+enum TcConvPath : int { kTcNone = 0, kTcDirect = 1, kTcIm2col = 2 };
+struct TcConvPlan {
+    int path;
+    int bk;
+    int c_pitch;   // K index = tap * c_pitch + c
+    int k_total;   // packed row length (multiple of bk)
+    int Wb, Hb, Nb;
+};
+TcConvPlan plan_tc_conv(const chxq_conv_geom& g);
+int choose_bk(int k);
+
+}  // namespace chxq

@@ -1,0 +1,73 @@
+// Device-side arithmetic shared by every kernel that quantizes or dequantizes a value.
+// Each function states the reference lines whose fp32 operation order it keeps; the explicit
+// __f*_rn intrinsics stop the compiler from contracting a*b+c into one rounding.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace chxq {
+
+// One element of quantize_array (runtime/ops/quantize.cc:29-34): t = x / s; (+zp); min(hi);
+// max(lo); + 0.5f; truncate.  ROUND_RNE instead gives saturate(rint(x / s) + zp).
+template <bool kSigned>
+__device__ __forceinline__ int quantize_one(float x, float scale, float zp_f, bool has_zp, int round_mode) {
+    const float lo = kSigned ? -128.f : 0.f;
+    const float hi = kSigned ? 127.f : 255.f;
+    float t = __fdiv_rn(x, scale);
+    if (round_mode != 0) {
+        t = __fadd_rn(rintf(t), zp_f);
+        t = fminf(t, hi);
+        t = fmaxf(lo, t);
+        return (int)t;
+    }
+    if (has_zp) t = __fadd_rn(t, zp_f);
+    t = t < hi ? t : hi;
+    t = lo > t ? lo : t;
+    t = __fadd_rn(t, 0.5f);
+    return (int)t;  // cvt.rzi: C++ static_cast truncation, as AsType does
+}
+
+__device__ __forceinline__ int quantize_any(float x, float scale, float zp_f, bool has_zp, int round_mode, bool is_signed) {
+    return is_signed ? quantize_one<true>(x, scale, zp_f, has_zp, round_mode) : quantize_one<false>(x, scale, zp_f, has_zp, round_mode);
+}
+
+// dequantize_array (runtime/ops/quantize.cc:37-44).
+__device__ __forceinline__ float dequantize_one(int q, float scale, float zp_f, bool has_zp) {
+    float v = (float)q;
+    if (has_zp) v = __fsub_rn(v, zp_f);
+    return __fmul_rn(v, scale);
+}
+
+// Parameters of a requantizing epilogue (QLinearConv / QLinearMatMul and the fused residual tail).
+struct RequantParams {
+    float y_scale;
+    float y_zp_f;
+    int y_has_zp;
+    int y_signed;
+    int round_mode;
+    int clamp_hi_q;  // -1 = off
+    // residual tail (res == nullptr: off)
+    float res_scale, res_zp_f;
+    int res_has_zp;
+    int res_relu;
+    float out_scale, out_zp_f;
+    int out_has_zp;
+};
+
+// acc (exact int32, bias already added) -> quantized output value.
+__device__ __forceinline__ int requant_one(int acc, float mult, const RequantParams& p) {
+    const float yf = __fmul_rn((float)acc, mult);
+    int q = quantize_any(yf, p.y_scale, p.y_zp_f, p.y_has_zp != 0, p.round_mode, p.y_signed != 0);
+    if (p.clamp_hi_q >= 0 && q > p.clamp_hi_q) q = p.clamp_hi_q;
+    return q;
+}
+
+// DequantizeLinear(y), DequantizeLinear(r), Add, Relu, QuantizeLinear on one element.
+__device__ __forceinline__ int residual_one(int q, int r, const RequantParams& p) {
+    float v = __fadd_rn(dequantize_one(q, p.y_scale, p.y_zp_f, p.y_has_zp != 0), dequantize_one(r, p.res_scale, p.res_zp_f, p.res_has_zp != 0));
+    if (p.res_relu) v = v > 0.f ? v : 0.f;
+    return quantize_one<false>(v, p.out_scale, p.out_zp_f, p.out_has_zp != 0, p.round_mode);
+}
+
+}  // namespace chxq

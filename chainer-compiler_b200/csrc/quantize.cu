@@ -1,0 +1,317 @@
+// QuantizeLinear / DequantizeLinear and the other single-pass, HBM-bound elementwise kernels.
+//
+// Every kernel here moves each byte once: 128-bit loads and stores, 16 elements per thread per
+// step, enough independent loads in flight per thread to cover HBM latency.  The reference runs
+// QuantizeLinear as five or six separate full-tensor ChainerX passes (runtime/ops/quantize.cc:29-34)
+// and DequantizeLinear as two or three (:37-44).
+#include <stdarg.h>
+
+#include "common.h"
+#include "qmath.cuh"
+
+namespace chxq {
+
+static thread_local char g_err[1024] = "";
+
+int set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+__device__ int g_device_status = 0;
+
+int* device_status_ptr() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
+    return p;
+}
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <bool kSigned>
+__global__ void __launch_bounds__(kThreads) quantize_vec16_kernel(
+        const float4* __restrict__ x, int64_t n16, float scale, float zp_f, int has_zp, int round_mode, uint4* __restrict__ y) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = __ldcs(x + i * 4 + j);
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t q0 = (uint32_t)quantize_one<kSigned>(v[j].x, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
+            const uint32_t q1 = (uint32_t)quantize_one<kSigned>(v[j].y, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
+            const uint32_t q2 = (uint32_t)quantize_one<kSigned>(v[j].z, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
+            const uint32_t q3 = (uint32_t)quantize_one<kSigned>(v[j].w, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
+            w[j] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+        }
+        y[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+template <bool kSigned>
+__global__ void __launch_bounds__(kThreads) quantize_scalar_kernel(
+        const float* __restrict__ x, int64_t begin, int64_t n, float scale, float zp_f, int has_zp, int round_mode, uint8_t* __restrict__ y) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        y[i] = (uint8_t)quantize_one<kSigned>(x[i], scale, zp_f, has_zp != 0, round_mode);
+    }
+}
+
+template <bool kSigned>
+__global__ void __launch_bounds__(kThreads) dequantize_vec16_kernel(
+        const uint4* __restrict__ x, int64_t n16, float scale, float zp_f, int has_zp, float4* __restrict__ y) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        const uint4 q = __ldcs(x + i);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float4 o;
+            auto get = [&](int b) -> int {
+                const uint32_t u = (w[j] >> (8 * b)) & 0xffu;
+                return kSigned ? (int)(int8_t)u : (int)u;
+            };
+            o.x = dequantize_one(get(0), scale, zp_f, has_zp != 0);
+            o.y = dequantize_one(get(1), scale, zp_f, has_zp != 0);
+            o.z = dequantize_one(get(2), scale, zp_f, has_zp != 0);
+            o.w = dequantize_one(get(3), scale, zp_f, has_zp != 0);
+            __stcs(y + i * 4 + j, o);
+        }
+    }
+}
+
+template <bool kSigned>
+__global__ void __launch_bounds__(kThreads) dequantize_scalar_kernel(
+        const uint8_t* __restrict__ x, int64_t begin, int64_t n, float scale, float zp_f, int has_zp, float* __restrict__ y) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int q = kSigned ? (int)(int8_t)x[i] : (int)x[i];
+        y[i] = dequantize_one(q, scale, zp_f, has_zp != 0);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) qadd_u8_kernel(
+        const uint8_t* __restrict__ a, const uint8_t* __restrict__ b, int64_t n, RequantParams p, uint8_t* __restrict__ y, int vec_ok) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t n16 = vec_ok ? n / 16 : 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        const uint4 qa = __ldcs(reinterpret_cast<const uint4*>(a) + i);
+        const uint4 qb = __ldcs(reinterpret_cast<const uint4*>(b) + i);
+        const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
+        uint32_t wo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t o = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int va = (wa[j] >> (8 * k)) & 0xff, vb = (wb[j] >> (8 * k)) & 0xff;
+                o |= ((uint32_t)residual_one(va, vb, p) & 0xffu) << (8 * k);
+            }
+            wo[j] = o;
+        }
+        reinterpret_cast<uint4*>(y)[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+    for (int64_t i = n16 * 16 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        y[i] = (uint8_t)residual_one(a[i], b[i], p);
+    }
+}
+
+// One pass min/max: per-thread float4 loads, warp shuffles, one atomic pair per block on
+// order-preserving integer keys.
+__device__ __forceinline__ unsigned f2key(float f) {
+    unsigned u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key2f(unsigned k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+__global__ void minmax_init_kernel(unsigned* keys) {
+    keys[0] = 0xffffffffu;  // min key
+    keys[1] = 0u;           // max key
+}
+
+__global__ void __launch_bounds__(kThreads) minmax_kernel(const float* __restrict__ x, int64_t n, unsigned* keys, int vec_ok) {
+    float mn = INFINITY, mx = -INFINITY;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t n4 = vec_ok ? n / 4 : 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(x) + i);
+        mn = fminf(fminf(mn, v.x), fminf(v.y, fminf(v.z, v.w)));
+        mx = fmaxf(fmaxf(mx, v.x), fmaxf(v.y, fmaxf(v.z, v.w)));
+    }
+    for (int64_t i = n4 * 4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        mn = fminf(mn, x[i]);
+        mx = fmaxf(mx, x[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicMin(&keys[0], f2key(mn));
+        atomicMax(&keys[1], f2key(mx));
+    }
+}
+
+__global__ void minmax_finish_kernel(const unsigned* keys, float* out2) {
+    out2[0] = key2f(keys[0]);
+    out2[1] = key2f(keys[1]);
+}
+
+inline int grid_for(int64_t work_items, int per_sm = 8) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int64_t blocks = (work_items + kThreads - 1) / kThreads;
+    int64_t cap = (int64_t)sms * per_sm;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+inline bool aligned16(const void* p) {
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+}  // namespace
+}  // namespace chxq
+
+using namespace chxq;
+
+extern "C" const char* chxq_last_error(void) {
+    return chxq::g_err;
+}
+
+extern "C" int chxq_version(void) {
+    return 100;
+}
+
+extern "C" int chxq_device_status(void* stream) {
+    CHXQ_CUDA(cudaStreamSynchronize(as_stream(stream)));
+    int* dptr = device_status_ptr();
+    if (!dptr) return set_error(CHXQ_ERR_CUDA, "device status word is unavailable");
+    int h = 0;
+    CHXQ_CUDA(cudaMemcpy(&h, dptr, sizeof(int), cudaMemcpyDeviceToHost));
+    if (h != 0) {
+        int zero = 0;
+        CHXQ_CUDA(cudaMemcpy(dptr, &zero, sizeof(int), cudaMemcpyHostToDevice));
+        return set_error(CHXQ_ERR_DEVICE_TIMEOUT, "a bounded device-side wait expired (code %d)", h);
+    }
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_quantize_linear(
+        const float* x, int64_t n, float y_scale, int32_t y_zero_point, int32_t y_dtype, int32_t round_mode, void* y, void* stream) {
+    CHXQ_CHECK_ARG(n >= 0, "QuantizeLinear: negative element count");
+    CHXQ_CHECK_ARG(is_q8(y_dtype), "QuantizeLinear: y_zero_point dtype must be uint8 or int8 (got %d)", y_dtype);
+    const bool sgn = y_dtype == CHXQ_INT8;
+    // runtime/ops/quantize.cc:26-27: the zero point must lie inside the output range.
+    CHXQ_CHECK_ARG(y_zero_point >= (sgn ? -128 : 0) && y_zero_point <= (sgn ? 127 : 255), "QuantizeLinear: zero point %d out of range",
+                   y_zero_point);
+    CHXQ_CHECK_ARG(round_mode == CHXQ_ROUND_REF_HALF_UP || round_mode == CHXQ_ROUND_RNE, "QuantizeLinear: bad round_mode");
+    if (n == 0) return CHXQ_OK;
+    CHXQ_CHECK_ARG(x && y, "QuantizeLinear: null buffer");
+    cudaStream_t s = as_stream(stream);
+    const float zp_f = (float)y_zero_point;
+    const int has_zp = y_zero_point != 0;
+    int64_t done = 0;
+    if (aligned16(x) && aligned16(y) && n >= 16) {
+        const int64_t n16 = n / 16;
+        const int grid = grid_for(n16, 8);
+        if (sgn)
+            quantize_vec16_kernel<true><<<grid, kThreads, 0, s>>>(reinterpret_cast<const float4*>(x), n16, y_scale, zp_f, has_zp, round_mode,
+                                                                  reinterpret_cast<uint4*>(y));
+        else
+            quantize_vec16_kernel<false><<<grid, kThreads, 0, s>>>(reinterpret_cast<const float4*>(x), n16, y_scale, zp_f, has_zp,
+                                                                   round_mode, reinterpret_cast<uint4*>(y));
+        CHXQ_LAUNCH_CHECK();
+        done = n16 * 16;
+    }
+    if (done < n) {
+        const int grid = grid_for(n - done, 8);
+        if (sgn)
+            quantize_scalar_kernel<true><<<grid, kThreads, 0, s>>>(x, done, n, y_scale, zp_f, has_zp, round_mode, static_cast<uint8_t*>(y));
+        else
+            quantize_scalar_kernel<false><<<grid, kThreads, 0, s>>>(x, done, n, y_scale, zp_f, has_zp, round_mode, static_cast<uint8_t*>(y));
+        CHXQ_LAUNCH_CHECK();
+    }
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_dequantize_linear(
+        const void* x, int32_t x_dtype, int64_t n, float x_scale, int32_t x_zero_point, float* y, void* stream) {
+    CHXQ_CHECK_ARG(n >= 0, "DequantizeLinear: negative element count");
+    CHXQ_CHECK_ARG(is_q8(x_dtype), "DequantizeLinear: x must be uint8 or int8 (got dtype %d)", x_dtype);
+    if (n == 0) return CHXQ_OK;
+    CHXQ_CHECK_ARG(x && y, "DequantizeLinear: null buffer");
+    cudaStream_t s = as_stream(stream);
+    const bool sgn = x_dtype == CHXQ_INT8;
+    const float zp_f = (float)x_zero_point;
+    const int has_zp = x_zero_point != 0;
+    int64_t done = 0;
+    if (aligned16(x) && aligned16(y) && n >= 16) {
+        const int64_t n16 = n / 16;
+        const int grid = grid_for(n16, 8);
+        if (sgn)
+            dequantize_vec16_kernel<true><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint4*>(x), n16, x_scale, zp_f, has_zp,
+                                                                    reinterpret_cast<float4*>(y));
+        else
+            dequantize_vec16_kernel<false><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint4*>(x), n16, x_scale, zp_f, has_zp,
+                                                                     reinterpret_cast<float4*>(y));
+        CHXQ_LAUNCH_CHECK();
+        done = n16 * 16;
+    }
+    if (done < n) {
+        const int grid = grid_for(n - done, 8);
+        if (sgn)
+            dequantize_scalar_kernel<true><<<grid, kThreads, 0, s>>>(static_cast<const uint8_t*>(x), done, n, x_scale, zp_f, has_zp, y);
+        else
+            dequantize_scalar_kernel<false><<<grid, kThreads, 0, s>>>(static_cast<const uint8_t*>(x), done, n, x_scale, zp_f, has_zp, y);
+        CHXQ_LAUNCH_CHECK();
+    }
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_qadd_u8(
+        const uint8_t* a, float a_scale, int32_t a_zp, const uint8_t* b, float b_scale, int32_t b_zp, int64_t n, float y_scale, int32_t y_zp,
+        int32_t relu, int32_t round_mode, uint8_t* y, void* stream) {
+    CHXQ_CHECK_ARG(n >= 0, "qadd: negative element count");
+    if (n == 0) return CHXQ_OK;
+    CHXQ_CHECK_ARG(a && b && y, "qadd: null buffer");
+    RequantParams p{};
+    p.y_scale = a_scale;
+    p.y_zp_f = (float)a_zp;
+    p.y_has_zp = a_zp != 0;
+    p.res_scale = b_scale;
+    p.res_zp_f = (float)b_zp;
+    p.res_has_zp = b_zp != 0;
+    p.res_relu = relu;
+    p.out_scale = y_scale;
+    p.out_zp_f = (float)y_zp;
+    p.out_has_zp = y_zp != 0;
+    p.round_mode = round_mode;
+    const int vec_ok = aligned16(a) && aligned16(b) && aligned16(y);
+    qadd_u8_kernel<<<grid_for((n + 15) / 16, 8), kThreads, 0, as_stream(stream)>>>(a, b, n, p, y, vec_ok);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_minmax_f32(const float* x, int64_t n, float* out2, void* stream) {
+    CHXQ_CHECK_ARG(n > 0 && x && out2, "minmax: empty input or null buffer");
+    cudaStream_t s = as_stream(stream);
+    // out2 doubles as the key scratch (two 32-bit words), converted in place at the end.
+    unsigned* keys = reinterpret_cast<unsigned*>(out2);
+    minmax_init_kernel<<<1, 1, 0, s>>>(keys);
+    minmax_kernel<<<grid_for((n + 3) / 4, 4), kThreads, 0, s>>>(x, n, keys, aligned16(x));
+    minmax_finish_kernel<<<1, 1, 0, s>>>(keys, out2);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}

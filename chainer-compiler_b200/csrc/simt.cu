@@ -1,0 +1,476 @@
+// General CUDA-core kernels: any shape, layout, group count and zero-point form of MatMulInteger,
+// QLinearMatMul, ConvInteger and QLinearConv, plus the small glue kernels of a quantized CNN graph.
+// These are the catch-all path behind the tcgen05 kernels (tc_igemm.cu) and the on-device second
+// opinion the tensor-core results are compared with; they are not the fast path.
+#include "common.h"
+#include "epilogue.cuh"
+#include "kernels.h"
+
+namespace chxq {
+namespace {
+
+template <bool kSigned>
+__device__ __forceinline__ int ldq(const void* p, int64_t i) {
+    return kSigned ? (int)static_cast<const int8_t*>(p)[i] : (int)static_cast<const uint8_t*>(p)[i];
+}
+
+__device__ __forceinline__ int ldq_rt(const void* p, int64_t i, int is_signed) {
+    return is_signed ? (int)static_cast<const int8_t*>(p)[i] : (int)static_cast<const uint8_t*>(p)[i];
+}
+
+// ---------------------------------------------------------------------------------------------
+// GEMM: y[b, m, n] = sum_k (a[b,m,k] - za[k]) * (b[b,k,n] - zb[n]).  32x32 output tile per block,
+// zero points subtracted while staging into shared memory, int32 wrap-around accumulation.
+// ---------------------------------------------------------------------------------------------
+constexpr int kGT = 32;
+
+template <bool kASigned, bool kBSigned>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(
+        const void* __restrict__ a, const void* __restrict__ b, int64_t M, int64_t N, int64_t K, ZpSpec zas, ZpSpec zbs, EpiArgs epi,
+        void* __restrict__ y) {
+    __shared__ int As[kGT][kGT + 1];
+    __shared__ int Bs[kGT][kGT + 1];
+    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+    const int64_t m0 = (int64_t)blockIdx.y * kGT, n0 = (int64_t)blockIdx.x * kGT;
+    const int64_t bt = blockIdx.z;
+    const int64_t a_off = bt * M * K, b_off = bt * K * N, y_off = bt * M * N;
+    unsigned acc[4] = {0u, 0u, 0u, 0u};
+    const int64_t n = n0 + tx;
+    const void* za = zas.ptr;
+    const int64_t za_len = zas.len;
+    int zbn = 0;
+    if (zbs.len > 0 && n < N) zbn = zbs.ptr ? ldq<kBSigned>(zbs.ptr, zbs.len == 1 ? 0 : n) : zbs.scalar;
+    for (int64_t k0 = 0; k0 < K; k0 += kGT) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = ty * 4 + i;
+            const int64_t m = m0 + r, k = k0 + tx;
+            int v = 0;
+            if (m < M && k < K) {
+                v = ldq<kASigned>(a, a_off + m * K + k);
+                if (za_len > 0) v -= za ? ldq<kASigned>(za, za_len == 1 ? 0 : k) : zas.scalar;
+            }
+            As[r][tx] = v;
+            const int64_t kb = k0 + r;
+            int w = 0;
+            if (kb < K && n < N) w = ldq<kBSigned>(b, b_off + kb * N + n) - zbn;
+            Bs[r][tx] = w;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < kGT; ++kk) {
+            const unsigned bv = (unsigned)Bs[kk][tx];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] += (unsigned)As[ty * 4 + i][kk] * bv;
+        }
+        __syncthreads();
+    }
+    if (n >= N) return;
+    const float mult = epi.mode == kEpiRequant ? epi_mult(epi, (int)n) : 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+        const int64_t o = y_off + m * N + n;
+        if (epi.mode == kEpiInt32) {
+            static_cast<int32_t*>(y)[o] = (int32_t)acc[i];
+        } else {
+            const int bias = epi.bias ? epi.bias[n] : 0;
+            const int q = epi_requant(epi, (int)acc[i], mult, bias, epi.residual ? epi.residual[o] : 0);
+            static_cast<uint8_t*>(y)[o] = (uint8_t)q;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Direct convolution, one thread per output element.  The output's fastest axis is the thread's
+// fastest axis (channel for NHWC, column for NCHW) so stores coalesce.
+// ---------------------------------------------------------------------------------------------
+struct ConvDesc {
+    int N, C, H, W, M, KH, KW, sh, sw, pt, pl, Ho, Wo, group;
+    int x_nhwc, y_nhwc, x_cs, y_cs;  // channel strides (NHWC)
+    int x_signed, w_signed;
+    int has_x_zp, x_zp;
+    int64_t w_zp_len;
+};
+
+__global__ void __launch_bounds__(256) conv_simt_kernel(
+        const void* __restrict__ x, const void* __restrict__ w, const void* __restrict__ w_zp, ConvDesc d, EpiArgs epi, void* __restrict__ y) {
+    const int64_t total = (int64_t)d.N * d.M * d.Ho * d.Wo;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int Cg = d.C / d.group, Mg = d.M / d.group;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        int n, m, ho, wo;
+        int64_t r = idx;
+        if (d.y_nhwc) {
+            m = (int)(r % d.M); r /= d.M;
+            wo = (int)(r % d.Wo); r /= d.Wo;
+            ho = (int)(r % d.Ho); r /= d.Ho;
+            n = (int)r;
+        } else {
+            wo = (int)(r % d.Wo); r /= d.Wo;
+            ho = (int)(r % d.Ho); r /= d.Ho;
+            m = (int)(r % d.M); r /= d.M;
+            n = (int)r;
+        }
+        const int g = m / Mg;
+        const int zw = d.w_zp_len == 0 ? 0 : ldq_rt(w_zp, d.w_zp_len == 1 ? 0 : m, d.w_signed);
+        unsigned acc = 0u;
+        for (int kh = 0; kh < d.KH; ++kh) {
+            const int hi = ho * d.sh - d.pt + kh;
+            if (hi < 0 || hi >= d.H) continue;
+            for (int kw = 0; kw < d.KW; ++kw) {
+                const int wi = wo * d.sw - d.pl + kw;
+                if (wi < 0 || wi >= d.W) continue;
+                for (int c = 0; c < Cg; ++c) {
+                    const int ci = g * Cg + c;
+                    const int64_t xo = d.x_nhwc ? (((int64_t)n * d.H + hi) * d.W + wi) * d.x_cs + ci
+                                                : (((int64_t)n * d.C + ci) * d.H + hi) * d.W + wi;
+                    int xv = ldq_rt(x, xo, d.x_signed);
+                    if (d.has_x_zp) xv -= d.x_zp;
+                    const int wv = ldq_rt(w, (((int64_t)m * Cg + c) * d.KH + kh) * d.KW + kw, d.w_signed) - zw;
+                    acc += (unsigned)xv * (unsigned)wv;
+                }
+            }
+        }
+        const int64_t o = d.y_nhwc ? (((int64_t)n * d.Ho + ho) * d.Wo + wo) * d.y_cs + m : (((int64_t)n * d.M + m) * d.Ho + ho) * d.Wo + wo;
+        if (epi.mode == kEpiInt32) {
+            static_cast<int32_t*>(y)[o] = (int32_t)acc;
+        } else {
+            const float mult = epi_mult(epi, m);
+            const int bias = epi.bias ? epi.bias[m] : 0;
+            const int q = epi_requant(epi, (int)acc, mult, bias, epi.residual ? epi.residual[o] : 0);
+            static_cast<uint8_t*>(y)[o] = (uint8_t)q;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// im2col: A[row, k] with row = (n, ho, wo), k = tap * c_pitch + c (tap = kh*KW + kw), rows k_pad
+// bytes long.  Columns with c >= C or tap >= KH*KW are zero.  Positions that fall into the
+// convolution's padding are written as pad_byte = x_zp, i.e. as 0 in the zero-point-subtracted
+// domain, which is where the reference pads (runtime/ops/quantize.cc:123-125 subtract the zero
+// point before chainerx::Conv zero-pads).  One thread writes 16 consecutive bytes of one row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) im2col_kernel(
+        const uint8_t* __restrict__ x, ConvDesc d, int c_pitch, int k_pad, int pad_byte, uint8_t* __restrict__ a) {
+    const int chunks = k_pad / 16;
+    const int64_t rows = (int64_t)d.N * d.Ho * d.Wo;
+    const int64_t total = rows * chunks;
+    const int taps = d.KH * d.KW;
+    const bool fast_ok = d.x_nhwc && (d.C % 16 == 0) && (c_pitch % 16 == 0) && (d.x_cs % 16 == 0);
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int ch = (int)(idx % chunks);
+        const int64_t r = idx / chunks;
+        const int wo = (int)(r % d.Wo);
+        const int64_t r2 = r / d.Wo;
+        const int ho = (int)(r2 % d.Ho);
+        const int n = (int)(r2 / d.Ho);
+        uint32_t out[4] = {0u, 0u, 0u, 0u};
+        const int kbase = ch * 16;
+        if (fast_ok) {
+            // 16 consecutive channels of one tap.
+            const int tap = kbase / c_pitch, c0 = kbase % c_pitch;
+            if (tap < taps && c0 < d.C) {
+                const int kh = tap / d.KW, kw = tap % d.KW;
+                const int hi = ho * d.sh - d.pt + kh, wi = wo * d.sw - d.pl + kw;
+                if (hi >= 0 && hi < d.H && wi >= 0 && wi < d.W) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(x + (((int64_t)n * d.H + hi) * d.W + wi) * d.x_cs + c0);
+                    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+                } else {
+                    const uint32_t pb = (uint32_t)pad_byte * 0x01010101u;
+                    out[0] = out[1] = out[2] = out[3] = pb;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int k = kbase + j;
+                const int tap = k / c_pitch, c = k % c_pitch;
+                uint32_t v = 0u;
+                if (tap < taps && c < d.C) {
+                    const int kh = tap / d.KW, kw = tap % d.KW;
+                    const int hi = ho * d.sh - d.pt + kh, wi = wo * d.sw - d.pl + kw;
+                    if (hi >= 0 && hi < d.H && wi >= 0 && wi < d.W) {
+                        const int64_t xo = d.x_nhwc ? (((int64_t)n * d.H + hi) * d.W + wi) * d.x_cs + c
+                                                    : (((int64_t)n * d.C + c) * d.H + hi) * d.W + wi;
+                        v = x[xo];
+                    } else {
+                        v = (uint32_t)pad_byte;
+                    }
+                }
+                out[j >> 2] |= v << (8 * (j & 3));
+            }
+        }
+        *reinterpret_cast<uint4*>(a + r * k_pad + kbase) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Glue kernels (NHWC u8 maps, 16 channels = one 128-bit word per thread where channels allow).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t vmax_u8x4(uint32_t a, uint32_t b) {
+    return __vmaxu4(a, b);
+}
+
+__global__ void __launch_bounds__(256) maxpool_u8_nhwc_kernel(
+        const uint8_t* __restrict__ x, int N, int H, int W, int C, int k, int s, int p, int Ho, int Wo, uint8_t* __restrict__ y) {
+    const int cv = C / 16;
+    const int64_t total = (int64_t)N * Ho * Wo * cv;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int c16 = (int)(idx % cv);
+        int64_t r = idx / cv;
+        const int wo = (int)(r % Wo); r /= Wo;
+        const int ho = (int)(r % Ho);
+        const int n = (int)(r / Ho);
+        uint4 best = make_uint4(0u, 0u, 0u, 0u);
+        for (int kh = 0; kh < k; ++kh) {
+            const int hi = ho * s - p + kh;
+            if (hi < 0 || hi >= H) continue;
+            for (int kw = 0; kw < k; ++kw) {
+                const int wi = wo * s - p + kw;
+                if (wi < 0 || wi >= W) continue;
+                const uint4 v = *reinterpret_cast<const uint4*>(x + (((int64_t)n * H + hi) * W + wi) * C + c16 * 16);
+                best.x = vmax_u8x4(best.x, v.x);
+                best.y = vmax_u8x4(best.y, v.y);
+                best.z = vmax_u8x4(best.z, v.z);
+                best.w = vmax_u8x4(best.w, v.w);
+            }
+        }
+        *reinterpret_cast<uint4*>(y + (((int64_t)n * Ho + ho) * Wo + wo) * C + c16 * 16) = best;
+    }
+}
+
+__global__ void __launch_bounds__(256) maxpool_u8_nhwc_scalar_kernel(
+        const uint8_t* __restrict__ x, int N, int H, int W, int C, int k, int s, int p, int Ho, int Wo, uint8_t* __restrict__ y) {
+    const int64_t total = (int64_t)N * Ho * Wo * C;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int c = (int)(idx % C);
+        int64_t r = idx / C;
+        const int wo = (int)(r % Wo); r /= Wo;
+        const int ho = (int)(r % Ho);
+        const int n = (int)(r / Ho);
+        int best = 0;
+        for (int kh = 0; kh < k; ++kh) {
+            const int hi = ho * s - p + kh;
+            if (hi < 0 || hi >= H) continue;
+            for (int kw = 0; kw < k; ++kw) {
+                const int wi = wo * s - p + kw;
+                if (wi < 0 || wi >= W) continue;
+                best = max(best, (int)x[(((int64_t)n * H + hi) * W + wi) * C + c]);
+            }
+        }
+        y[idx] = (uint8_t)best;
+    }
+}
+
+// y[n, c] = (float(sum_i (x[n,i,c] - zp)) / float(HW)) * scale.  One thread per (n, c); threads of
+// a warp read consecutive channels, so every load instruction is a coalesced row segment.
+__global__ void __launch_bounds__(256) global_avgpool_dq_kernel(
+        const uint8_t* __restrict__ x, int N, int HW, int C, float scale, int zp, float* __restrict__ y) {
+    const int64_t total = (int64_t)N * C;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int c = (int)(idx % C);
+    const int n = (int)(idx / C);
+    int s = 0;
+    const uint8_t* p = x + (int64_t)n * HW * C + c;
+    for (int i = 0; i < HW; ++i) s += (int)p[(int64_t)i * C] - zp;
+    y[idx] = __fmul_rn(__fdiv_rn((float)s, (float)HW), scale);
+}
+
+// fp32 Linear: y[n,o] = sum_k x[n,k] w[o,k] + b[o], k ascending with separate multiply and add
+// (the order the CPU restatement uses), 32x32 tiles through shared memory.
+__global__ void __launch_bounds__(256) linear_f32_kernel(
+        const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, int N, int K, int O, float* __restrict__ y) {
+    __shared__ float Xs[32][33];
+    __shared__ float Ws[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+    const int n0 = blockIdx.y * 32, o0 = blockIdx.x * 32;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k0 = 0; k0 < K; k0 += 32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = ty * 4 + i;
+            Xs[r][tx] = (n0 + r < N && k0 + tx < K) ? x[(int64_t)(n0 + r) * K + k0 + tx] : 0.f;
+            Ws[r][tx] = (o0 + r < O && k0 + tx < K) ? w[(int64_t)(o0 + r) * K + k0 + tx] : 0.f;
+        }
+        __syncthreads();
+        const int kmax = min(32, K - k0);
+        for (int kk = 0; kk < kmax; ++kk) {
+            const float wv = Ws[tx][kk];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(Xs[ty * 4 + i][kk], wv));
+        }
+        __syncthreads();
+    }
+    const int o = o0 + tx;
+    if (o >= O) return;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int n = n0 + ty * 4 + i;
+        if (n < N) y[(int64_t)n * O + o] = __fadd_rn(acc[i], b ? b[o] : 0.f);
+    }
+}
+
+// NCHW <-> NHWC transposes through a 32x32 shared tile over the (C, H*W) plane.
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_chw_kernel(const T* __restrict__ x, int C, int HW, int in_ld, int out_ld, int to_nhwc, T* __restrict__ y) {
+    // to_nhwc: x is [N][C][HW] -> y [N][HW][out_ld];  else x is [N][HW][in_ld] -> y [N][C][HW]
+    __shared__ T tile[32][33];
+    const int n = blockIdx.z;
+    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+    const int rows = to_nhwc ? C : HW, cols = to_nhwc ? HW : C;  // input is [rows][cols(+ld)]
+    const int64_t in_row_ld = to_nhwc ? HW : in_ld;
+    const int64_t out_row_ld = to_nhwc ? out_ld : HW;
+    const int64_t in_base = (int64_t)n * rows * in_row_ld;
+    const int64_t out_base = (int64_t)n * cols * out_row_ld;
+    const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + ty * 4 + i, c = c0 + tx;
+        if (r < rows && c < cols) tile[ty * 4 + i][tx] = x[in_base + (int64_t)r * in_row_ld + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = c0 + ty * 4 + i, r = r0 + tx;
+        if (r < rows && c < cols) y[out_base + (int64_t)c * out_row_ld + r] = tile[tx][ty * 4 + i];
+    }
+}
+
+inline int grid_1d(int64_t total, int threads = 256, int per_sm = 16) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int64_t blocks = (total + threads - 1) / threads;
+    const int64_t cap = (int64_t)sms * per_sm;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+}  // namespace
+
+int launch_gemm_simt(
+        const void* a, bool a_signed, const void* b, bool b_signed, int64_t batch, int64_t M, int64_t N, int64_t K, const ZpSpec& za,
+        const ZpSpec& zb, const EpiArgs& epi, void* y, cudaStream_t s) {
+    if (M == 0 || N == 0 || batch == 0) return CHXQ_OK;
+    if ((M + kGT - 1) / kGT > 65535 || batch > 65535) return set_error(CHXQ_ERR_UNSUPPORTED, "SIMT GEMM: M or batch too large for the grid");
+    dim3 grid((unsigned)((N + kGT - 1) / kGT), (unsigned)((M + kGT - 1) / kGT), (unsigned)batch), block(32, 8);
+    if (a_signed) {
+        if (b_signed)
+            gemm_simt_kernel<true, true><<<grid, block, 0, s>>>(a, b, M, N, K, za, zb, epi, y);
+        else
+            gemm_simt_kernel<true, false><<<grid, block, 0, s>>>(a, b, M, N, K, za, zb, epi, y);
+    } else {
+        if (b_signed)
+            gemm_simt_kernel<false, true><<<grid, block, 0, s>>>(a, b, M, N, K, za, zb, epi, y);
+        else
+            gemm_simt_kernel<false, false><<<grid, block, 0, s>>>(a, b, M, N, K, za, zb, epi, y);
+    }
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+static ConvDesc make_desc(const chxq_conv_geom& g, int has_x_zp, int x_zp, int64_t w_zp_len) {
+    ConvDesc d;
+    d.N = g.N; d.C = g.C; d.H = g.H; d.W = g.W; d.M = g.M; d.KH = g.KH; d.KW = g.KW;
+    d.sh = g.stride_h; d.sw = g.stride_w; d.pt = g.pad_top; d.pl = g.pad_left; d.Ho = g.Ho; d.Wo = g.Wo; d.group = g.group;
+    d.x_nhwc = g.x_layout == CHXQ_NHWC;
+    d.y_nhwc = g.y_layout == CHXQ_NHWC;
+    d.x_cs = g.x_cstride > 0 ? g.x_cstride : g.C;
+    d.y_cs = g.y_cstride > 0 ? g.y_cstride : g.M;
+    d.x_signed = g.x_dtype == CHXQ_INT8;
+    d.w_signed = g.w_dtype == CHXQ_INT8;
+    d.has_x_zp = has_x_zp;
+    d.x_zp = x_zp;
+    d.w_zp_len = w_zp_len;
+    return d;
+}
+
+int launch_conv_simt(
+        const void* x, const void* w, const chxq_conv_geom& g, int has_x_zp, int x_zp, const void* w_zp, int64_t w_zp_len, const EpiArgs& epi,
+        void* y, cudaStream_t s) {
+    const int64_t total = (int64_t)g.N * g.M * g.Ho * g.Wo;
+    if (total == 0) return CHXQ_OK;
+    ConvDesc d = make_desc(g, has_x_zp, x_zp, w_zp_len);
+    conv_simt_kernel<<<grid_1d(total, 256, 32), 256, 0, s>>>(x, w, w_zp, d, epi, y);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+int launch_im2col(const void* x, const chxq_conv_geom& g, int c_pitch, int k_pad, int pad_byte, void* a, cudaStream_t s) {
+    ConvDesc d = make_desc(g, 0, 0, 0);
+    const int64_t total = (int64_t)g.N * g.Ho * g.Wo * (k_pad / 16);
+    if (total == 0) return CHXQ_OK;
+    im2col_kernel<<<grid_1d(total, 256, 32), 256, 0, s>>>(static_cast<const uint8_t*>(x), d, c_pitch, k_pad, pad_byte, static_cast<uint8_t*>(a));
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+}  // namespace chxq
+
+using namespace chxq;
+
+extern "C" int chxq_maxpool_u8_nhwc(
+        const uint8_t* x, int32_t N, int32_t H, int32_t W, int32_t C, int32_t k, int32_t stride, int32_t pad, int32_t Ho, int32_t Wo, uint8_t* y,
+        void* stream) {
+    CHXQ_CHECK_ARG(x && y, "MaxPool: null buffer");
+    CHXQ_CHECK_ARG(N > 0 && H > 0 && W > 0 && C > 0 && k > 0 && stride > 0 && pad >= 0 && Ho > 0 && Wo > 0, "MaxPool: bad geometry");
+    CHXQ_CHECK_ARG((Ho - 1) * stride - pad < H && (Wo - 1) * stride - pad < W, "MaxPool: output window starts outside the input");
+    cudaStream_t s = as_stream(stream);
+    const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0;
+    if (vec)
+        maxpool_u8_nhwc_kernel<<<grid_1d((int64_t)N * Ho * Wo * (C / 16)), 256, 0, s>>>(x, N, H, W, C, k, stride, pad, Ho, Wo, y);
+    else
+        maxpool_u8_nhwc_scalar_kernel<<<grid_1d((int64_t)N * Ho * Wo * C), 256, 0, s>>>(x, N, H, W, C, k, stride, pad, Ho, Wo, y);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_global_avgpool_dq_nhwc(const uint8_t* x, int32_t N, int32_t HW, int32_t C, float scale, int32_t zp, float* y, void* stream) {
+    CHXQ_CHECK_ARG(x && y && N > 0 && HW > 0 && C > 0, "AveragePool: bad arguments");
+    const int64_t total = (int64_t)N * C;
+    global_avgpool_dq_kernel<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(x, N, HW, C, scale, zp, y);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_linear_f32(const float* x, const float* w, const float* b, int32_t N, int32_t K, int32_t O, float* y, void* stream) {
+    CHXQ_CHECK_ARG(x && w && y && N > 0 && K > 0 && O > 0, "Linear: bad arguments");
+    dim3 grid((O + 31) / 32, (N + 31) / 32), block(32, 8);
+    linear_f32_kernel<<<grid, block, 0, as_stream(stream)>>>(x, w, b, N, K, O, y);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+static int transpose_dispatch(const void* x, int elem_bytes, int N, int C, int H, int W, int c_stride, void* y, int to_nhwc, void* stream) {
+    CHXQ_CHECK_ARG(x && y && N > 0 && C > 0 && H > 0 && W > 0, "layout transform: bad arguments");
+    CHXQ_CHECK_ARG(elem_bytes == 1 || elem_bytes == 4, "layout transform: element size must be 1 or 4 bytes");
+    const int ld = c_stride > 0 ? c_stride : C;
+    CHXQ_CHECK_ARG(ld >= C, "layout transform: channel stride smaller than C");
+    CHXQ_CHECK_ARG(N <= 65535, "layout transform: batch too large for the grid");
+    const int HW = H * W;
+    const int rows = to_nhwc ? C : HW, cols = to_nhwc ? HW : C;
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32, N), block(32, 8);
+    CHXQ_CHECK_ARG(grid.y <= 65535, "layout transform: map too large for the grid");
+    cudaStream_t s = as_stream(stream);
+    if (elem_bytes == 1)
+        transpose_chw_kernel<uint8_t><<<grid, block, 0, s>>>(static_cast<const uint8_t*>(x), C, HW, ld, ld, to_nhwc, static_cast<uint8_t*>(y));
+    else
+        transpose_chw_kernel<uint32_t><<<grid, block, 0, s>>>(static_cast<const uint32_t*>(x), C, HW, ld, ld, to_nhwc, static_cast<uint32_t*>(y));
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_nchw_to_nhwc(const void* x, int32_t elem_bytes, int32_t N, int32_t C, int32_t H, int32_t W, int32_t c_stride, void* y, void* stream) {
+    return transpose_dispatch(x, elem_bytes, N, C, H, W, c_stride, y, 1, stream);
+}
+
+extern "C" int chxq_nhwc_to_nchw(const void* x, int32_t elem_bytes, int32_t N, int32_t C, int32_t H, int32_t W, int32_t c_stride, void* y, void* stream) {
+    return transpose_dispatch(x, elem_bytes, N, C, H, W, c_stride, y, 0, stream);
+}

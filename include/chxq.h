@@ -1,0 +1,269 @@
+/*
+ * chxq.h - C ABI of libchxq.so: hand-written sm_100a CUDA kernels for the quantized-inference
+ * VM ops of chainer-compiler (QuantizeLinear, DequantizeLinear, QLinearConv, QLinearMatMul,
+ * ConvInteger, MatMulInteger) and its fused elementwise groups (ElementWiseNvrtc).
+ *
+ * Conventions
+ *  - Every pointer named x/w/y/a/b/bias/..._zp/..._scale that is not marked "host" is a DEVICE
+ *    pointer on the current CUDA device.  `stream` is a cudaStream_t passed as void*.
+ *  - Functions return CHXQ_OK (0) or an error code; chxq_last_error() gives the thread-local
+ *    message.  Nothing here aborts, allocates outputs, or synchronises unless it says so.
+ *    The reference's op bodies CHECK()/abort on the same conditions (common/log.h:31-44); a
+ *    C++ op body translates a non-zero status back into CHECK/exception.
+ *  - Scalars the reference receives as VM `Scalar` arguments (runtime/chxvm_defs.py SCALAR /
+ *    OPTIONAL_SCALAR kinds) are passed by value from the host.  Array-kind zero points and
+ *    scales stay on the device and are never read back by the host.
+ *  - Dtype codes are the reference's (compiler/dtype.h:14-26).
+ *  - A device-side wait that expires (bounded mbarrier spin in the tensor-core kernels) sets a
+ *    status word that chxq_device_status() returns; kernels never trap or hang.
+ */
+#ifndef CHXQ_H_
+#define CHXQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CHXQ_OK 0
+#define CHXQ_ERR_INVALID_ARGUMENT 1
+#define CHXQ_ERR_UNSUPPORTED 2
+#define CHXQ_ERR_CUDA 3
+#define CHXQ_ERR_JIT 4
+#define CHXQ_ERR_DEVICE_TIMEOUT 5
+#define CHXQ_ERR_WORKSPACE 6
+
+/* compiler/dtype.h:14-26 */
+#define CHXQ_BOOL 1
+#define CHXQ_INT8 2
+#define CHXQ_INT16 3
+#define CHXQ_INT32 4
+#define CHXQ_INT64 5
+#define CHXQ_UINT8 6
+#define CHXQ_FLOAT16 7
+#define CHXQ_FLOAT32 8
+#define CHXQ_FLOAT64 9
+
+/* Rounding of QuantizeLinear and of every requantizing epilogue. */
+#define CHXQ_ROUND_REF_HALF_UP 0 /* (t + 0.5f) then truncation: runtime/ops/quantize.cc:33-34 */
+#define CHXQ_ROUND_RNE 1         /* saturate(rint(x / s) + zp), round-half-to-even (ONNX) */
+
+/* Activation layouts.  The reference is NCHW throughout; NHWC is this library's fast layout. */
+#define CHXQ_NCHW 0
+#define CHXQ_NHWC 1
+
+/* Kernel family selection (argument `path`). */
+#define CHXQ_PATH_AUTO 0   /* tensor-core kernel when the problem is eligible, else SIMT */
+#define CHXQ_PATH_SIMT 1   /* general CUDA-core kernels (any shape, layout, zero point) */
+#define CHXQ_PATH_TENSOR 2 /* tcgen05 kernels only; CHXQ_ERR_UNSUPPORTED when not eligible */
+
+const char* chxq_last_error(void);
+int chxq_version(void);
+
+/* Reads (and clears) the device-side status word of the current device.  SYNCHRONISES `stream`.
+ * Returns CHXQ_OK or CHXQ_ERR_DEVICE_TIMEOUT. */
+int chxq_device_status(void* stream);
+
+/* ---- QuantizeLinear: runtime/chxvm_defs.py:451-453, body runtime/ops/quantize.cc:16-35,48-53.
+ * y_dtype is the dtype of y_zero_point (CHXQ_UINT8 when the optional zero point is absent). */
+int chxq_quantize_linear(const float* x, int64_t n, float y_scale, int32_t y_zero_point, int32_t y_dtype, int32_t round_mode, void* y,
+                         void* stream);
+
+/* ---- DequantizeLinear: runtime/chxvm_defs.py:454-456, body runtime/ops/quantize.cc:37-44,55-60. */
+int chxq_dequantize_linear(const void* x, int32_t x_dtype, int64_t n, float x_scale, int32_t x_zero_point, float* y, void* stream);
+
+/* ---- MatMulInteger: runtime/chxvm_defs.py:462-465, body runtime/ops/quantize.cc:96-114 with
+ * NumpyMatMul (runtime/chainerx_util.cc:210-230).  a: [batch,M,K], b: [batch,K,N] (u8 or i8,
+ * row-major), y: int32 [batch,M,N].  Zero points are device arrays of the operand's dtype with
+ * length 0 (NULL), 1, or K for a / N for b (numpy broadcasting against the last axis). */
+size_t chxq_matmul_integer_workspace(int64_t batch, int64_t M, int64_t N, int64_t K);
+int chxq_matmul_integer(const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
+                        const void* a_zero_point, int64_t a_zp_len, const void* b_zero_point, int64_t b_zp_len, int32_t* y,
+                        void* workspace, size_t workspace_bytes, int32_t path, void* stream);
+
+/* ---- QLinearMatMul: has no VM op in the reference; ReplaceQLinearMatMul
+ * (compiler/simplifier.cc:675-694) expands it to DequantizeLinear x2, MatMul, QuantizeLinear
+ * with scalar parameters.  This entry computes that chain's result from the exact int32
+ * accumulator: y = Q(float(acc) * (a_scale * b_scale); y_scale, y_zero_point). */
+int chxq_qlinear_matmul(const void* a, int32_t a_dtype, float a_scale, int32_t a_zero_point, const void* b, int32_t b_dtype,
+                        float b_scale, int32_t b_zero_point, float y_scale, int32_t y_zero_point, int32_t y_dtype, int64_t M, int64_t N,
+                        int64_t K, int32_t round_mode, void* y, void* workspace, size_t workspace_bytes, int32_t path, void* stream);
+
+/* ---- Convolution geometry: ComplementStride/ComplementPad (runtime/chainerx_util.cc:180-200),
+ * CalculateAutoPad (:276-311), output size of chainerx::Conv (cover_all = false). */
+typedef struct chxq_conv_geom {
+    int32_t N, C, H, W;       /* input  */
+    int32_t M, KH, KW;        /* weight [M, C/group, KH, KW] (OIHW, as the reference stores it) */
+    int32_t stride_h, stride_w;
+    int32_t pad_top, pad_left, pad_bottom, pad_right;
+    int32_t group;
+    int32_t Ho, Wo;           /* output */
+    int32_t x_dtype, w_dtype; /* CHXQ_UINT8 / CHXQ_INT8 */
+    int32_t x_layout, y_layout; /* CHXQ_NCHW / CHXQ_NHWC */
+    int32_t x_cstride, y_cstride; /* NHWC only: bytes/elements between pixels (>= C resp. M); 0 = dense */
+} chxq_conv_geom;
+
+/* Host-only.  strides/pads: n_strides, n_pads in {0, 2} (empty -> 1 / 0; pads are begin == end as
+ * compiler/chxvm/simple_node_emitter.cc:76-86 requires); auto_pad "" / "NOTSET" / "SAME_UPPER". */
+int chxq_conv_resolve_geometry(int32_t N, int32_t C, int32_t H, int32_t W, int32_t M, int32_t Cg, int32_t KH, int32_t KW,
+                               const int64_t* strides, int32_t n_strides, const int64_t* pads, int32_t n_pads, int32_t group,
+                               const char* auto_pad, chxq_conv_geom* out);
+
+/* ---- ConvInteger: runtime/chxvm_defs.py:466-469, body runtime/ops/quantize.cc:116-146.
+ * x_zero_point is a host scalar (OPTIONAL_SCALAR; has_x_zp = 0 when absent); w_zero_point is a
+ * device array of w's dtype, length 0 (NULL), 1 or M.  Zero padding is applied after the zero
+ * point is subtracted, as the reference does.  y: int32, layout g->y_layout. */
+/* Worst-case workspace of the tensor-core path for this geometry (weights repacked per call by the
+ * unpacked entries, explicit im2col matrix, per-position sums); 0 when only CUDA-core kernels apply.
+ * The unpacked entries fall back to the CUDA-core kernels when given less (path AUTO). */
+size_t chxq_conv_workspace(const chxq_conv_geom* g);
+int chxq_conv_integer(const void* x, const void* w, const chxq_conv_geom* g, int32_t has_x_zp, int32_t x_zero_point,
+                      const void* w_zero_point, int64_t w_zp_len, int32_t* y, void* workspace, size_t workspace_bytes, int32_t path,
+                      void* stream);
+
+/* ---- QLinearConv: runtime/chxvm_defs.py:457-461, body runtime/ops/quantize.cc:62-94.
+ * The result is computed from the exact int32 accumulator:
+ *   acc = sum (x - x_zp)(w - w_zp[m]) + bias[m]
+ *   y   = Q(float(acc) * (x_scale * w_scale[m]); y_scale, y_zp)
+ * which is the reference's dequantize -> fp32 conv -> quantize chain with exact sums (at most
+ * one quantization step apart where fp32 accumulation error crosses a rounding boundary).
+ * bias follows ONNX (int32, scale x_scale*w_scale[m]); the reference's own bias handling passes
+ * the raw int32 values to the fp32 conv and is untested there.
+ * Fusions that have no counterpart in the reference (all disabled when zero / NULL):
+ *   clamp_hi_q >= 0 : output additionally clamped to <= clamp_hi_q (ReLU6 in the quantized domain;
+ *                     ReLU itself is the saturation at y_zp == 0).
+ *   residual        : u8 map with the output's shape/layout; the epilogue then evaluates, per
+ *                     element, Q(relu(DQ(y; y_scale, y_zp) + DQ(r; res_scale, res_zp)); out_scale, out_zp),
+ *                     i.e. the DequantizeLinear, DequantizeLinear, Add, Relu, QuantizeLinear nodes that
+ *                     follow the convolution in a residual block. */
+typedef struct chxq_qconv_params {
+    float x_scale;
+    int32_t x_zero_point;
+    const float* w_scale;     /* device, length w_params_len */
+    const void* w_zero_point; /* device, dtype of w, length w_params_len */
+    int64_t w_params_len;     /* 1 (per tensor) or M (per output channel) */
+    float y_scale;
+    int32_t y_zero_point;
+    int32_t y_dtype;          /* CHXQ_UINT8 / CHXQ_INT8: dtype of y_zero_point */
+    const int32_t* bias;      /* device, length M, or NULL */
+    int32_t round_mode;
+    int32_t clamp_hi_q;       /* -1 = off */
+    const void* residual;     /* device u8, or NULL */
+    float res_scale;
+    int32_t res_zero_point;
+    int32_t res_relu;
+    float out_scale;
+    int32_t out_zero_point;
+} chxq_qconv_params;
+
+int chxq_qlinear_conv(const void* x, const void* w, const chxq_conv_geom* g, const chxq_qconv_params* p, void* y, void* workspace,
+                      size_t workspace_bytes, int32_t path, void* stream);
+
+/* Weight pre-packing for the tensor-core path (the reference re-dequantizes the weights on every
+ * call, runtime/ops/quantize.cc:74-88; constants are packed once here instead).  Packs OIHW
+ * weights into K-major rows plus per-channel weight sums and widened zero points.  SYNCHRONISES
+ * the stream once to learn whether every weight zero point is zero.  *flags receives
+ *   bit 0: the geometry is eligible for the packed tensor-core entries below (else use the
+ *          unpacked entry, which falls back to the CUDA-core kernels), and
+ *   bit 1: every weight zero point is zero (the per-position input sums are then skipped).
+ * Pass the same flags back to the packed entries.  Their workspace (256-byte aligned, size from
+ * chxq_conv_workspace) holds the im2col matrix and per-position sums when the geometry or the
+ * zero points need them. */
+size_t chxq_conv_prepack_bytes(const chxq_conv_geom* g);
+int chxq_conv_prepack(const void* w, const chxq_conv_geom* g, const void* w_zero_point, int64_t w_zp_len, void* packed,
+                      size_t packed_bytes, int32_t* flags, void* stream);
+int chxq_qlinear_conv_packed(const void* x, const void* packed, const chxq_conv_geom* g, const chxq_qconv_params* p, int32_t packed_flags,
+                             void* y, void* workspace, size_t workspace_bytes, void* stream);
+int chxq_conv_integer_packed(const void* x, const void* packed, const chxq_conv_geom* g, int32_t has_x_zp, int32_t x_zero_point,
+                             int32_t packed_flags, int32_t* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- Fused elementwise groups.
+ * chxq_eltwise_codegen replaces BuildNvrtcProgram (compiler/nvrtc_builder.cc:91-206): same
+ * inputs (the group's nodes in any order, its input and output values), output = CUDA C source
+ * of one single-pass, 128-bit vectorised, grid-stride kernel `fusion<id>` (+ `fusion<id>_s`, the
+ * scalar variant for unaligned buffers).  Node ops: compiler/nvrtc_builder.cc:35-87. */
+#define CHXQ_EW_IDENTITY 0
+#define CHXQ_EW_TANH 1
+#define CHXQ_EW_EXP 2
+#define CHXQ_EW_SIGMOID 3
+#define CHXQ_EW_ADD 4
+#define CHXQ_EW_SUB 5
+#define CHXQ_EW_MUL 6
+#define CHXQ_EW_DIV 7
+#define CHXQ_EW_CONSTANT 8
+
+typedef struct chxq_ew_node {
+    int32_t op;        /* CHXQ_EW_* */
+    int32_t inputs[2]; /* value ids; unused = -1 */
+    int32_t output;    /* value id */
+    double constant;   /* CHXQ_EW_CONSTANT only */
+} chxq_ew_node;
+
+/* Host-only.  value_names[v] is the graph name of value id v (used, cleansed, as identifier, as the
+ * reference does).  Writes a NUL-terminated string of at most buf_len bytes; *needed receives the
+ * size required (including the NUL).  dtype: CHXQ_FLOAT16/32/64. */
+int chxq_eltwise_codegen(const chxq_ew_node* nodes, int32_t n_nodes, const int32_t* input_ids, int32_t n_inputs,
+                         const int32_t* output_ids, int32_t n_outputs, const char* const* value_names, int32_t n_values, int32_t dtype,
+                         int32_t fusion_id, char* buf, size_t buf_len, size_t* needed);
+
+/* ElementWiseNvrtc: runtime/chxvm_defs.py:431-434, body runtime/ops/nvrtc.cc:90-161.  `code` is the
+ * text produced by chxq_eltwise_codegen; it is compiled for sm_100a on first use and cached by its
+ * full text, as the reference caches (runtime/ops/nvrtc.cc:41-84).  All buffers hold n elements of
+ * `dtype` (the op body broadcasts and contiguizes first, as the reference's does at :103-112). */
+int chxq_eltwise_run(const char* code, int32_t fusion_id, const void* const* inputs /*host array*/, int32_t n_inputs,
+                     void* const* outputs /*host array*/, int32_t n_outputs, int64_t n, int32_t dtype, void* stream);
+
+/* Fusion grouping: FuseElementwiseOperations (compiler/fusion_elementwise.cc:10-40) +
+ * FuseAllConnectedNodes (compiler/fusion.cc:165-214).  Host-only.  The graph is given as flat
+ * arrays; group_of_node[i] receives 0 (not fused) or the 1-based group id. */
+typedef struct chxq_graph_node {
+    const char* op_type;      /* ONNX op name, e.g. "Add", "Tanh", "Constant" */
+    const int32_t* inputs;    /* value ids */
+    int32_t n_inputs;
+    const int32_t* outputs;   /* value ids */
+    int32_t n_outputs;
+    int32_t is_grad;          /* Node::IsGradNode() */
+    int32_t const_is_float;   /* Constant only */
+    int64_t const_num_elements; /* Constant only */
+} chxq_graph_node;
+
+typedef struct chxq_graph_value {
+    int32_t dtype;            /* CHXQ_* or 0 = unknown */
+    int32_t is_graph_output;
+} chxq_graph_value;
+
+int chxq_fuse_elementwise(const chxq_graph_node* nodes, int32_t n_nodes, const chxq_graph_value* values, int32_t n_values,
+                          int32_t* group_of_node, int32_t* n_groups);
+
+/* Weight quantizer of the --quantize pass: QuantizeData (compiler/quantize.cc:70-89) and its
+ * per-output-channel form QuantizeWeightConvolution (:98-129).  HOST pointers (the pass runs at
+ * compile time).  w: [M, inner] fp32; to_int8 != 0: symmetric int8 (scale = 2*max|w|/254, zp 0);
+ * else asymmetric uint8.  per_channel == 0 quantizes the whole tensor with one scale (scales[0]). */
+int chxq_quantize_weights_host(const float* w, int64_t M, int64_t inner, int32_t to_int8, int32_t per_channel, void* q, float* scales,
+                               int32_t* zero_points);
+
+/* ---- Glue ops a quantized CNN graph runs between the int8 ops (reference bodies are one-line
+ * ChainerX calls; kernels here work on NHWC u8 maps). */
+/* MaxPool (runtime/ops/pooling.cc:47-60) on u8 NHWC; cover_all as Chainer's max_pooling_2d. */
+int chxq_maxpool_u8_nhwc(const uint8_t* x, int32_t N, int32_t H, int32_t W, int32_t C, int32_t k, int32_t stride, int32_t pad, int32_t Ho,
+                         int32_t Wo, uint8_t* y, void* stream);
+/* Global AveragePool (pooling.cc:62-75) fused with DequantizeLinear: y[n,c] = mean((q - zp)) * scale. */
+int chxq_global_avgpool_dq_nhwc(const uint8_t* x, int32_t N, int32_t HW, int32_t C, float scale, int32_t zp, float* y, void* stream);
+/* Linear / Gemm (runtime/ops/connection.cc:12-15): y[n,o] = sum_k x[n,k] w[o,k] + b[o], fp32. */
+int chxq_linear_f32(const float* x, const float* w, const float* b, int32_t N, int32_t K, int32_t O, float* y, void* stream);
+/* DequantizeLinear, DequantizeLinear, Add, (Relu), QuantizeLinear of two u8 maps in one pass. */
+int chxq_qadd_u8(const uint8_t* a, float a_scale, int32_t a_zp, const uint8_t* b, float b_scale, int32_t b_zp, int64_t n, float y_scale,
+                 int32_t y_zp, int32_t relu, int32_t round_mode, uint8_t* y, void* stream);
+/* NCHW <-> NHWC transposes of 1-byte and 4-byte maps (boundary conversions). */
+int chxq_nchw_to_nhwc(const void* x, int32_t elem_bytes, int32_t N, int32_t C, int32_t H, int32_t W, int32_t c_stride, void* y, void* stream);
+int chxq_nhwc_to_nchw(const void* x, int32_t elem_bytes, int32_t N, int32_t C, int32_t H, int32_t W, int32_t c_stride, void* y, void* stream);
+/* ReduceMin + ReduceMax of an fp32 tensor in one pass (the dynamic-quantization parameter
+ * sub-graph of compiler/quantize.cc:172-202); out[0] = min, out[1] = max, both on the device. */
+int chxq_minmax_f32(const float* x, int64_t n, float* out2, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHXQ_H_ */
