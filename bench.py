@@ -1,0 +1,323 @@
+"""Benchmark of the quantized-inference hot path: int8 ResNet-50 v1 inference, batch 256 per GPU, 3x224x224.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One JSON line on stdout (rank 0).  `value` is whole-job img/s with the fp32 input batch resident in HBM; `e2e` is the same
+metric through the public host-buffer call (pinned host input copied in, logits copied out, inside the timed region).
+Data are synthetic: uniform [0,1) images and randomly initialised weights of the ResNet-50 v1 architecture.
+`--impl reference` times the reference's own algorithm for the path (dequantize -> fp32 convolution -> quantize per
+QLinearConv) as restated by the CPU oracle, on the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+IMAGE = 224
+BATCH_PER_GPU = 256
+METRIC = "int8 ResNet-50 img/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="chxq", choices=["chxq", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU")
+    ap.add_argument("--cpu-sample", type=int, default=8, help="images of the CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_sustained=p["bf16_tflops_sustained"], bf16_burst=p["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_sustained=1400.0, bf16_burst=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out = self.proc.communicate(timeout=5)[0]
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = self.proc.communicate()[0]
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_params(orc, networks, seed, sample):
+    """Network parameters for the CPU arm without touching a GPU: same architecture and initialisation; activation scales
+    calibrated on the sample with the oracle's own ops."""
+    import __graft_entry__ as entry
+    entry.load_package()
+    from chainer_compiler_b200 import models
+    import torch
+    net = models.ResNet50Int8(batch=sample.shape[0], device="cpu", seed=seed, image=IMAGE)
+    xq = orc.quantize_linear(sample, net.in_scale, 0)
+
+    def calib(c, x, x_scale, relu):
+        c.x_scale = np.float32(x_scale)
+        mult = (np.float32(x_scale) * c.w_scale).astype(np.float32)
+        c.bias_q = np.rint(c.b_f.astype(np.float64) / mult.astype(np.float64)).clip(-2**31, 2**31 - 1).astype(np.int32)
+        acc = orc.conv_integer(x, c.w_q, 0, None, strides=(c.stride, c.stride), pads=(c.pad, c.pad))
+        yf = (acc + c.bias_q.reshape(1, -1, 1, 1)).astype(np.float32) * mult.reshape(1, -1, 1, 1)
+        lo, hi = float(yf.min()), float(yf.max())
+        if relu:
+            c.y_scale, c.y_zp = np.float32(max(hi, 1e-6) / 255.0), 0
+        else:
+            lo, hi = min(lo, 0.0), max(hi, 0.0)
+            c.y_scale = np.float32(max(hi - lo, 1e-6) / 255.0)
+            c.y_zp = int(np.clip(np.rint(-lo / float(c.y_scale)), 0, 255))
+        return orc.requantize(acc, x_scale, c.w_scale, c.y_scale, c.y_zp, bias=c.bias_q, channel_axis=1)
+
+    h = calib(net.stem, xq, net.in_scale, True)
+    h = orc.maxpool_u8(h, 3, 2, 0, cover_all=True)
+    h_scale = net.stem.y_scale
+    for b in net.blocks:
+        h1 = calib(b["conv1"], h, h_scale, True)
+        h2 = calib(b["conv2"], h1, b["conv1"].y_scale, True)
+        h3 = calib(b["conv3"], h2, b["conv2"].y_scale, False)
+        if b["proj"] is not None:
+            sc = calib(b["proj"], h, h_scale, False)
+            sc_scale, sc_zp = b["proj"].y_scale, b["proj"].y_zp
+        else:
+            sc, sc_scale, sc_zp = h, h_scale, 0
+        sf = (h3.astype(np.float32) - b["conv3"].y_zp) * b["conv3"].y_scale + (sc.astype(np.float32) - sc_zp) * np.float32(sc_scale)
+        b["out_scale"] = np.float32(max(float(np.maximum(sf, 0).max()), 1e-6) / 255.0)
+        b["res"] = (sc_scale, sc_zp)
+        h = orc.qadd_relu(h3, b["conv3"].y_scale, b["conv3"].y_zp, sc, sc_scale, sc_zp, b["out_scale"], 0, relu=True)
+        h_scale = b["out_scale"]
+    net.final_scale = h_scale
+    del torch
+    return net.export_numpy()
+
+
+def time_cpu(orc, networks, params, sample, repeats=1):
+    """Seconds per forward of the reference-algorithm chain (first run discarded, as tools/run_onnx.cc:468-469 of the reference does)."""
+    networks.resnet50_forward(params, sample[:1], mode="emulate")
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        networks.resnet50_forward(params, sample, mode="emulate")
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def run_reference(args):
+    """CPU arm: rank 0 alone works; other ranks exit 0 without work."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import __graft_entry__ as entry
+    orc = entry.load_oracle()
+    from oracle import networks
+    cores = orc.num_threads()
+    n_img = 2
+    rng = np.random.default_rng(0)
+    sample = rng.uniform(0, 1, (n_img, 3, IMAGE, IMAGE)).astype(np.float32)
+    params = cpu_reference_params(orc, networks, 0, sample)
+    for _ in range(max(1, min(args.warmup, 2))):
+        networks.resnet50_forward(params, sample, mode="emulate")
+    times = []
+    budget_t0 = time.perf_counter()
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        networks.resnet50_forward(params, sample, mode="emulate")
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - budget_t0 > 150:  # keep the whole run within a few minutes
+            break
+    ms = 1000.0 * float(np.mean(times))
+    value = n_img / (ms / 1000.0)
+    sample_txt = "%d images of 3x%dx%d per step through the oracle's QLinearConv chain (dequantize, fp32 conv, quantize), %d steps timed" % (
+        n_img, IMAGE, IMAGE, len(times))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "img/s", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "ResNet-50 v1 int8 inference, 3x224x224 (configs[4]); CPU sample of %d images per step" % n_img,
+                   "batch_per_gpu": args.batch, "note": "the reference binary cannot be built here (ChainerX/ONNX/protobuf submodules empty); "
+                   "this is the oracle restatement of its algorithm on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "img/s", "cores": cores, "kind": "port", "sample": sample_txt},
+        "e2e": {"value": value, "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_chxq(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    from chainer_compiler_b200 import dataparallel as dp, models, ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
+    rank, local_rank, world = dp.init()
+    if world != args.gpus:
+        raise SystemExit("--gpus %d does not match WORLD_SIZE %d" % (args.gpus, world))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    L = pkg.lib()
+
+    # Same seeded weights on every rank; every rank works on its own seeded images (weak scaling: 256 images per GPU).
+    net = models.ResNet50Int8(batch=args.batch, device=dev, seed=0, image=IMAGE)
+    eng = dp.InferenceEngine(net, world)
+    gen = torch.Generator(device="cpu").manual_seed(1234)
+    calib = torch.rand((args.batch, 3, IMAGE, IMAGE), generator=gen, dtype=torch.float32)
+    eng.prepare(calib.to(dev))
+    gen_r = torch.Generator(device="cpu").manual_seed(99 + rank)
+    host_x = torch.rand((args.batch, 3, IMAGE, IMAGE), generator=gen_r, dtype=torch.float32).pin_memory()
+    eng.x_dev.copy_(host_x)
+    ops.device_status()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # kernels per step (counted on one eager pass; a graph replay launches the same kernels)
+    c0 = L.chxq_launch_count()
+    net.forward(eng.x_dev)
+    torch.cuda.synchronize(dev)
+    launches_per_step = int(L.chxq_launch_count() - c0)
+
+    # ---- device-resident timed region -----------------------------------------------------------------
+    for _ in range(max(3, args.warmup)):
+        eng.step_device()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        eng.step_device()
+    e1.record()
+    barrier()
+    ms_total = dp.max_over_ranks(e0.elapsed_time(e1), dev, world)
+    clocks = sampler.stop() if rank == 0 else None
+    ops.device_status()
+    ms_per_step = ms_total / args.steps
+    value = args.batch * world / (ms_per_step / 1000.0)
+
+    # ---- end to end through the public host-buffer call ---------------------------------------------------
+    for _ in range(2):
+        eng.run_host(host_x)
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        eng.run_host(host_x)
+    e1.record()
+    barrier()
+    e2e_ms = dp.max_over_ranks(e0.elapsed_time(e1), dev, world) / args.steps
+    e2e_wall_ms = 1000.0 * (time.perf_counter() - t0) / args.steps
+    e2e_value = args.batch * world / (e2e_ms / 1000.0)
+    h2d = host_x.numel() * 4
+    d2h = eng.host_logits.numel() * 4
+
+    # ---- roofline of the dominant kernel (tcgen05 implicit GEMM), timed with CUDA events per launch ---------
+    roof = cpu = None
+    if rank == 0:
+        L.chxq_tc_profile(1)
+        prof_steps = 3
+        for _ in range(prof_steps):
+            net.forward(eng.x_dev)
+        import ctypes
+        tms, n, macs = ctypes.c_double(), ctypes.c_int64(), ctypes.c_double()
+        L.chxq_tc_profile_read(ctypes.byref(tms), ctypes.byref(n), ctypes.byref(macs))
+        L.chxq_tc_profile(0)
+        pk = peaks()
+        achieved = 2.0 * macs.value / (tms.value / 1000.0) / 1e12
+        peak = 2.0 * pk["bf16_sustained"]
+        roof = {"bound": "tensor", "kernel": "tc_igemm_kernel (tcgen05 kind::i8 implicit GEMM, all convolutions)", "achieved": achieved,
+                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s; the file has no int8 entry; int8 ops counted as 2 per MAC)" % pk["source"],
+                "launches_per_step": int(n.value // prof_steps), "kernel_ms_per_step": tms.value / prof_steps,
+                "share_of_step": (tms.value / prof_steps) / ms_per_step, "algorithmic_gop_per_step": 2.0 * macs.value / prof_steps / 1e9}
+        if not args.no_cpu_baseline:
+            orc = entry.load_oracle()
+            from oracle import networks
+            sample = host_x[: args.cpu_sample].numpy()
+            params = net.export_numpy()
+            sec = time_cpu(orc, networks, params, sample)
+            cpu = {"value": args.cpu_sample / sec, "unit": "img/s", "cores": orc.num_threads(), "kind": "port",
+                   "sample": "%d of the %d images of one step through the oracle's reference-algorithm chain (dequantize, fp32 conv, quantize per "
+                             "QLinearConv), one timed pass after a discarded first run" % (args.cpu_sample, args.batch)}
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "ResNet-50 v1 int8 inference (configs[4]): batch %d per GPU, 3x224x224 fp32 NCHW input -> QuantizeLinear -> 53 "
+                                   "QLinearConv (per-channel int8 weights, uint8 activations, bias, ReLU, residual tails fused) -> fp32 FC logits"
+                                   % args.batch,
+                       "batch_per_gpu": args.batch, "global_batch": args.batch * world, "parallelism": "dp%d" % world,
+                       "l2": "inputs (154 MB fp32 per step) and activations are larger than the 126 MB L2; no explicit flush",
+                       "gop_per_image": 2.0 * net.macs_per_image() / 1e9, "cuda_graph": True},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "wall_ms_per_step": e2e_wall_ms},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": roof,
+            "cpu_baseline": cpu,
+            "tops": 2.0 * net.macs_per_image() * args.batch * world / (ms_per_step / 1000.0) / 1e12,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_chxq(args)
+
+
+if __name__ == "__main__":
+    main()

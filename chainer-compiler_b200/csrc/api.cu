@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(256) conv_possum_kernel(
 inline int blocks_for(int64_t threads_needed, int block = 256) {
     int64_t b = (threads_needed + block - 1) / block;
     if (b < 1) b = 1;
-    if (b > 1048576) b = 1048576;
+    if (b > 2147483647ll) b = 2147483647ll;
     return (int)b;
 }
 
@@ -226,6 +226,7 @@ int gemm_dispatch(
         const bool need_cols = za.len > 0 || zb.len > 0;
         if (need_cols) gemm_col_terms_kernel<<<blocks_for(N), 256, 0, s>>>(bb, b_signed, a_signed, K, N, za, zb, T, zbn);
         if (zb.len > 0) gemm_row_terms_kernel<<<blocks_for(M * 32), 256, 0, s>>>(ab, a_signed, M, K, za, R);
+        count_launch((need_cols ? 1 : 0) + (zb.len > 0 ? 1 : 0));
         CHXQ_LAUNCH_CHECK();
         TcProblem p{};
         p.a = ab; p.a_signed = a_signed; p.C = (int)K; p.a_cs = K; p.W = (int)M; p.H = 1; p.N = 1;
@@ -239,6 +240,7 @@ int gemm_dispatch(
         p.col_mul = zb.len > 0 ? zbn : nullptr;
         p.row_corr = zb.len > 0 ? R : nullptr;
         p.epi = epi;
+        p.alg_macs = (double)M * (double)N * (double)K;
         if (epi.residual) p.epi.residual = epi.residual + (size_t)bi * M * N;
         const int rc = launch_tc_igemm(p, s);
         if (rc != CHXQ_OK) return rc;
@@ -311,6 +313,7 @@ int pack_weights(const void* w, const chxq_conv_geom& g, const TcConvPlan& pl, c
     weight_terms_kernel<<<blocks_for((int64_t)g.M * 32), 256, 0, s>>>(w, g.w_dtype == CHXQ_INT8, g.M, g.C * taps, zw,
                                                                      reinterpret_cast<int32_t*>(blob + L.wsum_off),
                                                                      reinterpret_cast<int32_t*>(blob + L.zw_off), flag);
+    count_launch(1);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }
@@ -372,6 +375,7 @@ int conv_tc_run(
     p.col_mul = zw_zero ? nullptr : reinterpret_cast<const int32_t*>(blob + L.zw_off);
     p.row_corr = zw_zero ? nullptr : rowsum;
     p.epi = epi;
+    p.alg_macs = (double)rows * g.M * g.C * taps;
     return launch_tc_igemm(p, s);
 }
 
@@ -383,6 +387,8 @@ int conv_dispatch(
     CHXQ_CHECK_ARG(x && w && y, "%s: null buffer", op);
     CHXQ_CHECK_ARG(path == CHXQ_PATH_AUTO || path == CHXQ_PATH_SIMT || path == CHXQ_PATH_TENSOR, "%s: bad path", op);
     const int xz = has_x_zp ? x_zp : 0;
+    if (path == CHXQ_PATH_AUTO && g->group > 1 && epi.mode == kEpiRequant && depthwise_eligible(*g, x, y, epi.residual))
+        return launch_depthwise(x, w, *g, xz, zw.ptr, zw.len, epi, y, s);
     const TcConvPlan pl = plan_tc_conv(*g);
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     bool use_tc = path != CHXQ_PATH_SIMT && pl.path != kTcNone && aligned;
@@ -556,6 +562,14 @@ extern "C" size_t chxq_conv_workspace(const chxq_conv_geom* g) {
     // padding value, and per-position sums when the weight zero point is non-zero.
     const size_t im2col = (pl.path == kTcIm2col || padded) ? L.im2col_bytes : 0;
     return L.pack_total + im2col + L.rowsum_bytes;
+}
+
+extern "C" size_t chxq_conv_packed_workspace(const chxq_conv_geom* g, int32_t x_zero_point, int32_t packed_flags) {
+    if (!g || validate_geom("conv workspace", g) != CHXQ_OK) return 0;
+    const TcConvPlan pl = plan_tc_conv(*g);
+    if (pl.path == kTcNone) return 0;
+    const ConvWs L = conv_ws_layout(*g, pl);
+    return (needs_im2col(*g, pl, x_zero_point) ? L.im2col_bytes : 0) + ((packed_flags & 2) ? 0 : L.rowsum_bytes);
 }
 
 extern "C" int chxq_conv_integer(

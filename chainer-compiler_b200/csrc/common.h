@@ -25,6 +25,9 @@ inline cudaStream_t as_stream(void* s) {
 // Device status word (one per device; set by kernels whose bounded waits expire).
 int* device_status_ptr();
 
+// Process-wide count of kernels this library has launched (chxq_launch_count()).
+void count_launch(int n = 1);
+
 #define CHXQ_CHECK_ARG(cond, ...)                                         \
     do {                                                                  \
         if (!(cond)) return ::chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
@@ -37,6 +40,10 @@ int* device_status_ptr();
             return ::chxq::set_error(CHXQ_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); \
     } while (0)
 
-#define CHXQ_LAUNCH_CHECK() CHXQ_CUDA(cudaGetLastError())
+#define CHXQ_LAUNCH_CHECK()            \
+    do {                               \
+        ::chxq::count_launch(1);       \
+        CHXQ_CUDA(cudaGetLastError()); \
+    } while (0)
 
 }  // namespace chxq

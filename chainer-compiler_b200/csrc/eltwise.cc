@@ -410,5 +410,6 @@ extern "C" int chxq_eltwise_run(
     CUresult cr = driver().LaunchKernel(aligned ? fn.vec : fn.scalar, (unsigned)blocks, 1, 1, 256, 1, 1, 0, reinterpret_cast<CUstream>(stream),
                                         args.data(), nullptr);
     if (cr != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuLaunchKernel(fusion%d) failed with %d", fusion_id, (int)cr);
+    count_launch(1);
     return CHXQ_OK;
 }

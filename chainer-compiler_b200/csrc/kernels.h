@@ -28,6 +28,12 @@ int launch_conv_simt(
 // positions hold pad_byte, columns with c >= C or tap >= KH*KW hold 0.
 int launch_im2col(const void* x, const chxq_conv_geom& g, int c_pitch, int k_pad, int pad_byte, void* a, cudaStream_t s);
 
+// ---- depthwise kernel (depthwise.cu): group == C == M, NHWC, requantizing epilogue ----
+bool depthwise_eligible(const chxq_conv_geom& g, const void* x, const void* y, const void* residual);
+int launch_depthwise(
+        const void* x, const void* w, const chxq_conv_geom& g, int x_zp, const void* w_zp, int64_t w_zp_len, const EpiArgs& epi, void* y,
+        cudaStream_t s);
+
 // ---- tcgen05 implicit-GEMM kernel (tc_igemm.cu) ----
 // Problem: D[row, col] = sum_k A[row, k] * B[col, k] over u8/s8 operands, both K-major.
 // A is read through a 4-D tensor map {C, W, H, N} (an NHWC activation, or a plain matrix with
@@ -62,6 +68,7 @@ struct TcProblem {
     const int32_t* col_mul;
     const int32_t* row_corr;
     EpiArgs epi;
+    double alg_macs;  // multiply-accumulates of the problem as the op defines it (no padding), for profiling
 };
 
 int launch_tc_igemm(const TcProblem& p, cudaStream_t s);

@@ -6,6 +6,8 @@
 // and DequantizeLinear as two or three (:37-44).
 #include <stdarg.h>
 
+#include <atomic>
+
 #include "common.h"
 #include "qmath.cuh"
 
@@ -23,10 +25,22 @@ int set_error(int code, const char* fmt, ...) {
 
 __device__ int g_device_status = 0;
 
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) {
+    g_launches.fetch_add(n, std::memory_order_relaxed);
+}
+
 int* device_status_ptr() {
-    int* p = nullptr;
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
-    return p;
+    // Resolved once per device (symbol lookup is not something to repeat inside a stream capture).
+    static int* cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cache[dev] == nullptr) {
+        int* p = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
+        cache[dev] = p;
+    }
+    return cache[dev];
 }
 
 namespace {
@@ -194,6 +208,10 @@ extern "C" int chxq_version(void) {
     return 100;
 }
 
+extern "C" int64_t chxq_launch_count(void) {
+    return (int64_t)chxq::g_launches.load(std::memory_order_relaxed);
+}
+
 extern "C" int chxq_device_status(void* stream) {
     CHXQ_CUDA(cudaStreamSynchronize(as_stream(stream)));
     int* dptr = device_status_ptr();
@@ -312,6 +330,7 @@ extern "C" int chxq_minmax_f32(const float* x, int64_t n, float* out2, void* str
     minmax_init_kernel<<<1, 1, 0, s>>>(keys);
     minmax_kernel<<<grid_for((n + 3) / 4, 4), kThreads, 0, s>>>(x, n, keys, aligned16(x));
     minmax_finish_kernel<<<1, 1, 0, s>>>(keys, out2);
+    count_launch(2);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }

@@ -16,6 +16,9 @@
 // for copies in flight, frees its TMEM and returns.  Nothing traps.
 #include <cuda.h>
 
+#include <mutex>
+#include <vector>
+
 #include "common.h"
 #include "kernels.h"
 
@@ -469,6 +472,16 @@ int num_sms() {
     return sms;
 }
 
+// Optional per-launch timing with CUDA events on the launching stream (chxq_tc_profile / chxq_tc_profile_read).
+struct ProfRec {
+    cudaEvent_t e0, e1;
+    double macs;
+};
+bool g_prof_on = false;
+std::vector<ProfRec> g_prof;
+std::mutex g_prof_mu;
+double g_cur_macs = 0.0;
+
 template <int BN, int BK>
 int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int total_tiles, cudaStream_t s) {
     using Cfg = TcConfig<BN, BK>;
@@ -480,7 +493,19 @@ int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const int grid = total_tiles < num_sms() ? total_tiles : num_sms();
+    ProfRec rec{};
+    if (g_prof_on) {
+        CHXQ_CUDA(cudaEventCreate(&rec.e0));
+        CHXQ_CUDA(cudaEventCreate(&rec.e1));
+        rec.macs = g_cur_macs;
+        CHXQ_CUDA(cudaEventRecord(rec.e0, s));
+    }
     tc_igemm_kernel<BN, BK><<<grid, 192, Cfg::kSmemBytes, s>>>(tmA, tmB, p);
+    if (g_prof_on) {
+        CHXQ_CUDA(cudaEventRecord(rec.e1, s));
+        std::lock_guard<std::mutex> lock(g_prof_mu);
+        g_prof.push_back(rec);
+    }
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }
@@ -628,6 +653,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
                             swizzle_for(q.bk), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed with %d", (int)r);
     }
+    g_cur_macs = q.alg_macs;
     switch (bn) {
         case 256: return launch_bn<256>(q.bk, tmA, tmB, p, (int)total_tiles, s);
         case 128: return launch_bn<128>(q.bk, tmA, tmB, p, (int)total_tiles, s);
@@ -637,3 +663,31 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
 }
 
 }  // namespace chxq
+
+// Profiling of the tensor-core kernel: while enabled, every launch is bracketed by CUDA events on its stream.
+extern "C" int chxq_tc_profile(int32_t enable) {
+    std::lock_guard<std::mutex> lock(chxq::g_prof_mu);
+    chxq::g_prof_on = enable != 0;
+    return CHXQ_OK;
+}
+
+// Synchronises the device, sums the recorded launches and clears them.
+extern "C" int chxq_tc_profile_read(double* total_ms, int64_t* launches, double* total_macs) {
+    using namespace chxq;
+    CHXQ_CUDA(cudaDeviceSynchronize());
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    double ms = 0.0, macs = 0.0;
+    for (auto& r : g_prof) {
+        float t = 0.f;
+        CHXQ_CUDA(cudaEventElapsedTime(&t, r.e0, r.e1));
+        ms += t;
+        macs += r.macs;
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+    }
+    if (total_ms) *total_ms = ms;
+    if (launches) *launches = (int64_t)g_prof.size();
+    if (total_macs) *total_macs = macs;
+    g_prof.clear();
+    return CHXQ_OK;
+}

@@ -1,0 +1,279 @@
+"""Synthetic int8 networks built from the quantized VM ops (the benchmark configurations).
+
+Weights are random with the stated initialisation (no checkpoint or dataset is involved); batch
+norms are folded into the preceding convolution before quantization; weights are quantized per
+output channel with the reference's weight quantizer (``compiler/quantize.cc:70-129``); activation
+scales are calibrated once, offline, on one seeded batch.  Convolution outputs that feed a residual
+addition (no ReLU in front of them) get an asymmetric uint8 zero point so that their negative half is
+representable; every other activation has zero point 0, where ReLU is the saturation at 0.
+
+The op sequence per bottleneck block is the one a QLinear-mode graph holds:
+``QLinearConv`` x3 (+ projection), then ``DequantizeLinear, DequantizeLinear, Add, Relu, QuantizeLinear``;
+``forward`` runs that tail inside the last convolution's epilogue, ``forward_unfused`` runs it as the
+separate one-pass kernel -- both give bit-identical maps.
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib, ops
+from ._lib import check, lib
+
+# (blocks, mid channels, out channels, stride of the first block): scripts/resnet50.py:86-90 of the reference.
+RESNET50_STAGES = [(3, 64, 256, 1), (4, 128, 512, 2), (6, 256, 1024, 2), (3, 512, 2048, 2)]
+
+
+def quantize_weights(w, per_channel=True, to_int8=True):
+    """fp32 OIHW / [M, inner] weights -> (q, scales[M or 1], zero_points[M or 1]) with the reference's weight quantizer."""
+    w = np.ascontiguousarray(w, np.float32)
+    M = w.shape[0]
+    inner = w.size // M
+    q = np.empty(w.shape, np.int8 if to_int8 else np.uint8)
+    n = M if per_channel else 1
+    s = np.empty(n, np.float32)
+    z = np.empty(n, np.int32)
+    check(lib().chxq_quantize_weights_host(w.ctypes.data, M, inner, int(to_int8), int(per_channel), q.ctypes.data, s.ctypes.data, z.ctypes.data))
+    return q, s, z
+
+
+class _Conv:
+    """One convolution of the network: float parameters, their quantized form and the packed device copy."""
+
+    def __init__(self, name, cin, cout, k, stride, pad, rng, he_fan_in=None):
+        self.name, self.cin, self.cout, self.k, self.stride, self.pad = name, cin, cout, k, stride, pad
+        fan_in = he_fan_in or cin * k * k
+        w = rng.standard_normal((cout, cin, k, k), dtype=np.float32) * np.float32(np.sqrt(2.0 / fan_in))
+        # batch norm of a trained network, folded: w' = w * g / sqrt(v + eps), b' = beta - mean * g / sqrt(v + eps)
+        gamma = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+        beta = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+        mean = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+        var = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+        inv = gamma / np.sqrt(var + np.float32(2e-5))
+        self.w_f = (w * inv[:, None, None, None]).astype(np.float32)
+        self.b_f = (beta - mean * inv).astype(np.float32)
+        self.w_q, self.w_scale, wz = quantize_weights(self.w_f, per_channel=True, to_int8=True)
+        self.w_zp = wz.astype(np.int8)
+        # filled by calibration
+        self.x_scale = None
+        self.y_scale = None
+        self.y_zp = 0
+        self.bias_q = None
+        self.packed = None
+        self.dev = {}
+
+
+class ResNet50Int8:
+    """ResNet-50 v1 (stride on the first 1x1 of a stage and on its projection, scripts/resnet50.py:12-31,75-104 of the
+    reference), int8 weights per channel, uint8 activations per tensor, fp32 classifier."""
+
+    def __init__(self, batch, device, seed=0, image=224, num_classes=1000, width_mult=1.0):
+        self.batch, self.device, self.image = int(batch), torch.device(device), int(image)
+        rng = np.random.default_rng(seed)
+        wm = lambda c: max(16, int(c * width_mult) // 16 * 16)  # noqa: E731
+        self.stem = _Conv("conv1", 3, wm(64), 7, 2, 3, rng)
+        self.blocks = []
+        cin = wm(64)
+        for si, (n_blocks, mid, cout, stride) in enumerate(RESNET50_STAGES):
+            mid, cout = wm(mid), wm(cout)
+            for bi in range(n_blocks):
+                s = stride if bi == 0 else 1
+                nm = "res%d_%d" % (si + 2, bi)
+                blk = {
+                    "conv1": _Conv(nm + "_conv1", cin, mid, 1, s, 0, rng),
+                    "conv2": _Conv(nm + "_conv2", mid, mid, 3, 1, 1, rng),
+                    "conv3": _Conv(nm + "_conv3", mid, cout, 1, 1, 0, rng),
+                    "proj": _Conv(nm + "_proj", cin, cout, 1, s, 0, rng) if bi == 0 else None,
+                    "out_scale": None,
+                }
+                self.blocks.append(blk)
+                cin = cout
+        self.feat = cin
+        self.fc_w = (rng.standard_normal((num_classes, cin), dtype=np.float32) * np.float32(0.01))
+        self.fc_b = np.zeros(num_classes, np.float32)
+        self.in_scale = np.float32(1.0 / 255.0)
+        self.calibrated = False
+        self._graph = None
+
+    # ---- enumeration helpers -------------------------------------------------------------------
+    def convs(self):
+        yield self.stem
+        for b in self.blocks:
+            for k in ("conv1", "conv2", "conv3", "proj"):
+                if b[k] is not None:
+                    yield b[k]
+
+    def macs_per_image(self):
+        """Multiply-accumulates of one image (convolutions + classifier)."""
+        total = 0
+        hw = self.image // 2  # stem output 112
+        total += self.stem.cout * 3 * 49 * hw * hw
+        hw = (hw - 3 + 1) // 2 + 1  # max pool 3x3/2, cover_all
+        for b in self.blocks:
+            s = b["conv1"].stride
+            ho = (hw - 1) // s + 1
+            total += b["conv1"].cin * b["conv1"].cout * ho * ho
+            total += b["conv2"].cin * b["conv2"].cout * 9 * ho * ho
+            total += b["conv3"].cin * b["conv3"].cout * ho * ho
+            if b["proj"] is not None:
+                total += b["proj"].cin * b["proj"].cout * ho * ho
+            hw = ho
+        total += self.fc_w.size
+        return total
+
+    # ---- device upload / packing -----------------------------------------------------------------
+    def _upload(self, c, x_shape, x_nchw=False):
+        dev = self.device
+        c.dev["w"] = torch.from_numpy(c.w_q).to(dev)
+        c.dev["w_scale"] = torch.from_numpy(c.w_scale).to(dev)
+        c.dev["w_zp"] = torch.from_numpy(c.w_zp).to(dev)
+        c.packed = ops.PackedConv(c.dev["w"], c.dev["w_zp"], x_shape, strides=(c.stride, c.stride), pads=(c.pad, c.pad),
+                                  x_layout=_lib.NCHW if x_nchw else _lib.NHWC)
+        if not c.packed.eligible:
+            raise _lib.ChxqError(_lib.ERR_UNSUPPORTED, "%s is not eligible for the tensor-core path" % c.name)
+        return (c.packed.g.N, c.packed.g.M, c.packed.g.Ho, c.packed.g.Wo)
+
+    def _conv_acc(self, c, x):
+        """Exact int32 accumulator of convolution c over the uint8 map x (ConvInteger on the packed weights)."""
+        g = c.packed.g
+        y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.int32, device=self.device, memory_format=torch.channels_last)
+        ws_bytes = lib().chxq_conv_packed_workspace(ctypes.byref(g), 0, c.packed.flags)
+        ws = ops.workspace(ws_bytes, self.device)
+        check(lib().chxq_conv_integer_packed(ops._ptr(x), ops._ptr(c.packed.blob), ctypes.byref(g), 1, 0, c.packed.flags, ops._ptr(y),
+                                             ops._ptr(ws), ws_bytes, ops._stream()))
+        return y
+
+    def _calibrate_conv(self, c, x, x_scale, relu):
+        """Sets the bias, the output scale and zero point of c from the batch x; returns the quantized output."""
+        c.x_scale = np.float32(x_scale)
+        mult = (np.float32(x_scale) * c.w_scale).astype(np.float32)
+        c.bias_q = np.rint(c.b_f.astype(np.float64) / mult.astype(np.float64)).astype(np.int64).clip(-2**31, 2**31 - 1).astype(np.int32)
+        c.dev["bias"] = torch.from_numpy(c.bias_q).to(self.device)
+        acc = self._conv_acc(c, x)
+        yf = (acc + c.dev["bias"].view(1, -1, 1, 1)).float() * torch.from_numpy(mult).to(self.device).view(1, -1, 1, 1)
+        hi = float(yf.amax().item())
+        lo = float(yf.amin().item())
+        del yf, acc
+        if relu:
+            c.y_scale = np.float32(max(hi, 1e-6) / 255.0)
+            c.y_zp = 0
+        else:
+            lo, hi = min(lo, 0.0), max(hi, 0.0)
+            c.y_scale = np.float32(max(hi - lo, 1e-6) / 255.0)
+            c.y_zp = int(np.clip(np.rint(-lo / float(c.y_scale)), 0, 255))
+        return self._run_conv(c, x)
+
+    def _run_conv(self, c, x, residual=None, res_scale=1.0, res_zp=0, out_scale=1.0, out=None):
+        return ops.QLinearConvPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
+                                     b=c.dev["bias"], residual=residual, res_scale=res_scale, res_zero_point=res_zp, res_relu=True,
+                                     out_scale=out_scale, out_zero_point=0, out=out)
+
+    def calibrate(self, x):
+        """Uploads and packs the weights, then walks the network once over the fp32 NCHW batch x to fix every scale."""
+        assert tuple(x.shape) == (self.batch, 3, self.image, self.image) and x.dtype == torch.float32
+        xq = ops.QuantizeLinear(x.contiguous(), self.in_scale, np.uint8(0))
+        shape = self._upload(self.stem, tuple(xq.shape), x_nchw=True)
+        h = self._calibrate_conv(self.stem, xq, self.in_scale, relu=True)
+        h = ops.MaxPoolU8(h, 3, 2, 0, cover_all=True)
+        h_scale = self.stem.y_scale
+        shape = tuple(h.shape)
+        for b in self.blocks:
+            s1 = self._upload(b["conv1"], shape)
+            h1 = self._calibrate_conv(b["conv1"], h, h_scale, relu=True)
+            self._upload(b["conv2"], s1)
+            h2 = self._calibrate_conv(b["conv2"], h1, b["conv1"].y_scale, relu=True)
+            s3 = self._upload(b["conv3"], tuple(h2.shape))
+            h3 = self._calibrate_conv(b["conv3"], h2, b["conv2"].y_scale, relu=False)
+            if b["proj"] is not None:
+                self._upload(b["proj"], shape)
+                sc = self._calibrate_conv(b["proj"], h, h_scale, relu=False)
+                sc_scale, sc_zp = b["proj"].y_scale, b["proj"].y_zp
+            else:
+                sc, sc_scale, sc_zp = h, h_scale, 0
+            # scale of the block output: max of relu(DQ(h3) + DQ(sc)) over the batch
+            sf = (h3.float() - b["conv3"].y_zp) * float(b["conv3"].y_scale) + (sc.float() - sc_zp) * float(sc_scale)
+            b["out_scale"] = np.float32(max(float(sf.clamp_min(0).amax().item()), 1e-6) / 255.0)
+            del sf
+            b["res"] = (sc_scale, sc_zp)
+            h = ops.QAddU8(h3, b["conv3"].y_scale, b["conv3"].y_zp, sc, sc_scale, sc_zp, b["out_scale"], 0, relu=True)
+            h_scale = b["out_scale"]
+            shape = s3
+        self.dev_fc_w = torch.from_numpy(self.fc_w).to(self.device)
+        self.dev_fc_b = torch.from_numpy(self.fc_b).to(self.device)
+        self.final_scale = h_scale
+        self.calibrated = True
+        torch.cuda.synchronize(self.device)
+
+    # ---- inference ----------------------------------------------------------------------------------
+    def forward(self, x, fused=True, taps=None):
+        """fp32 NCHW batch -> fp32 logits [N, classes].  taps (a dict) receives intermediate uint8 maps when given."""
+        assert self.calibrated
+        xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
+        h = self._run_conv(self.stem, xq)
+        if taps is not None:
+            taps["stem"] = h
+        h = ops.MaxPoolU8(h, 3, 2, 0, cover_all=True)
+        h_scale = self.stem.y_scale
+        for i, b in enumerate(self.blocks):
+            h1 = self._run_conv(b["conv1"], h)
+            h2 = self._run_conv(b["conv2"], h1)
+            if b["proj"] is not None:
+                sc = self._run_conv(b["proj"], h)
+            else:
+                sc = h
+            sc_scale, sc_zp = b["res"]
+            if fused:
+                h = self._run_conv(b["conv3"], h2, residual=sc, res_scale=sc_scale, res_zp=sc_zp, out_scale=b["out_scale"])
+            else:
+                h3 = self._run_conv(b["conv3"], h2)
+                h = ops.QAddU8(h3, b["conv3"].y_scale, b["conv3"].y_zp, sc, sc_scale, sc_zp, b["out_scale"], 0, relu=True)
+            h_scale = b["out_scale"]
+            if taps is not None:
+                taps["block%d" % i] = h
+        pooled = ops.GlobalAveragePoolDequant(h, h_scale, 0)
+        logits = ops.Linear(pooled, self.dev_fc_w, self.dev_fc_b)
+        if taps is not None:
+            taps["pooled"] = pooled
+        return logits
+
+    def capture(self, x_static):
+        """Captures forward(x_static) into a CUDA graph; returns (graph, logits).  Replaying needs no host work per layer."""
+        self.forward(x_static)  # warm-up: JIT-free, but sizes the workspace and sets kernel attributes outside the capture
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            logits = self.forward(x_static)
+        return g, logits
+
+    def export_numpy(self):
+        """Everything the CPU oracle needs to run the same network."""
+        def conv(c):
+            return dict(name=c.name, w=c.w_q, w_scale=c.w_scale, w_zp=c.w_zp.astype(np.int32), bias=c.bias_q, x_scale=c.x_scale,
+                        y_scale=c.y_scale, y_zp=c.y_zp, stride=c.stride, pad=c.pad)
+        return dict(in_scale=self.in_scale, stem=conv(self.stem),
+                    blocks=[dict(conv1=conv(b["conv1"]), conv2=conv(b["conv2"]), conv3=conv(b["conv3"]),
+                                 proj=conv(b["proj"]) if b["proj"] is not None else None, res=b["res"], out_scale=b["out_scale"])
+                            for b in self.blocks],
+                    fc_w=self.fc_w, fc_b=self.fc_b, final_scale=self.final_scale)
+
+
+class QuantizedMLP:
+    """784-1000-1000-10 MLP: QuantizeLinear -> (QLinearMatMul -> ReLU)x2 -> QLinearMatMul -> DequantizeLinear.
+    Weights N(0, 0.05), per-tensor symmetric int8 (scale = max|w| / 127, zero point 0); activations uint8 with
+    scale 1/255 and zero point 0, where the uint8 saturation at 0 is the ReLU."""
+
+    def __init__(self, device, seed=0, sizes=(784, 1000, 1000, 10)):
+        rng = np.random.default_rng(seed)
+        self.device = torch.device(device)
+        self.layers = []
+        for fin, fout in zip(sizes[:-1], sizes[1:]):
+            w = (rng.standard_normal((fin, fout)) * 0.05).astype(np.float32)  # [K, N] as MatMul consumes it
+            q, s, z = quantize_weights(w.reshape(1, -1), per_channel=False, to_int8=True)
+            self.layers.append(dict(w_q=q.reshape(fin, fout), w_scale=np.float32(s[0]), dev=torch.from_numpy(q.reshape(fin, fout)).to(self.device)))
+        self.act_scale = np.float32(1.0 / 255.0)
+
+    def forward(self, x, path=_lib.PATH_AUTO):
+        h = ops.QuantizeLinear(x, self.act_scale, np.uint8(0))
+        for l in self.layers:
+            h = ops.QLinearMatMul(h, self.act_scale, np.uint8(0), l["dev"], l["w_scale"], np.int8(0), self.act_scale, np.uint8(0), path=path)
+        return ops.DequantizeLinear(h, self.act_scale, np.uint8(0))

@@ -1,0 +1,441 @@
+"""Host-side mirror of the reference's VM op bodies for the quantized hot path.
+
+Each function has the name, argument order and argument meaning of the corresponding entry of
+the reference's op table (``runtime/chxvm_defs.py:431-434,451-469``) and does what the reference's
+``XxxOp::RunImpl`` does around the arithmetic: validate, allocate a fresh output, call the kernel.
+The arithmetic itself runs in ``libchxq.so`` through the C ABI; PyTorch supplies device memory and
+the current stream only.  There is no fallback: without a CUDA device or without the built
+library every op raises.
+
+Array arguments are ``torch`` CUDA tensors, logically NCHW / row-major as in the reference.
+Activation maps that are ``channels_last`` in memory take the NHWC kernels (tensor cores,
+depthwise kernel) and yield ``channels_last`` outputs; plain contiguous NCHW maps take the general
+CUDA-core kernels.  ``Scalar`` arguments are Python / numpy scalars; a zero point carries its dtype
+as a numpy scalar (``np.uint8(3)``, ``np.int8(-1)``) the way ``StrictScalar`` does in the reference
+(``runtime/strict_scalar.h:8-34``).
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import (FLOAT16, FLOAT32, FLOAT64, INT8, NCHW, NHWC, PATH_AUTO, PATH_SIMT, PATH_TENSOR, ROUND_REF, ROUND_RNE, UINT8,  # noqa: F401
+                   ChxqError, ConvGeom, QConvParams, check, lib)
+
+_TORCH_Q = {torch.uint8: UINT8, torch.int8: INT8}
+_TORCH_F = {torch.float16: FLOAT16, torch.float32: FLOAT32, torch.float64: FLOAT64}
+_workspaces = {}
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "chxq ops run on CUDA tensors only (no CPU path exists)")
+
+
+def _qcode(t, what):
+    if t.dtype not in _TORCH_Q:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "%s must be uint8 or int8, got %s" % (what, t.dtype))
+    return _TORCH_Q[t.dtype]
+
+
+def workspace(nbytes, device):
+    """Grow-only scratch buffer per device, 256-byte aligned (the op body owns scratch, as it owns outputs)."""
+    if nbytes == 0:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _zp_scalar(zp, default_dtype=np.uint8):
+    """(value, chxq dtype code) of an OptionalScalar zero point."""
+    if zp is None:
+        return 0, (UINT8 if default_dtype == np.uint8 else INT8)
+    if isinstance(zp, torch.Tensor):
+        if zp.numel() != 1:
+            raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "a Scalar zero point must have one element")
+        return int(zp.item()), _qcode(zp, "zero point")
+    dt = np.asarray(zp).dtype
+    if dt == np.int8:
+        return int(zp), INT8
+    if dt == np.uint8:
+        return int(zp), UINT8
+    # plain Python ints carry no dtype: the reference's default is uint8 (runtime/ops/quantize.cc:50-51)
+    return int(zp), (UINT8 if default_dtype == np.uint8 else INT8)
+
+
+def _is_channels_last(t):
+    return t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last) and not (t.is_contiguous() and t.shape[1] != 1)
+
+
+def QuantizeLinear(x, y_scale, y_zero_point=None, round_mode=ROUND_REF):
+    """runtime/chxvm_defs.py:451-453; body runtime/ops/quantize.cc:16-35,48-53."""
+    _require_cuda(x)
+    if x.dtype != torch.float32:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QuantizeLinear: x must be float32, got %s" % x.dtype)
+    zp, code = _zp_scalar(y_zero_point)
+    if not (x.is_contiguous() or _is_channels_last(x)):
+        x = x.contiguous()
+    y = torch.empty_like(x, dtype=torch.uint8 if code == UINT8 else torch.int8)
+    check(lib().chxq_quantize_linear(_ptr(x), x.numel(), float(y_scale), zp, code, round_mode, _ptr(y), _stream()))
+    return y
+
+
+def DequantizeLinear(x, x_scale, x_zero_point=None):
+    """runtime/chxvm_defs.py:454-456; body runtime/ops/quantize.cc:37-44,55-60."""
+    _require_cuda(x)
+    code = _qcode(x, "DequantizeLinear: x")
+    zp, _ = _zp_scalar(x_zero_point)
+    if not (x.is_contiguous() or _is_channels_last(x)):
+        x = x.contiguous()
+    y = torch.empty_like(x, dtype=torch.float32)
+    check(lib().chxq_dequantize_linear(_ptr(x), code, x.numel(), float(x_scale), zp, _ptr(y), _stream()))
+    return y
+
+
+def _zp_array(zp, like, what):
+    """OptionalArray zero point: device tensor of the operand's dtype with ndim <= 1."""
+    if zp is None:
+        return None, 0
+    if not isinstance(zp, torch.Tensor):
+        zp = torch.as_tensor(np.asarray(zp), device=like.device)
+    _require_cuda(zp)
+    if zp.dim() > 1:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "%s must have at most one dimension" % what)  # runtime/ops/quantize.cc:105,109
+    if zp.dtype != like.dtype:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "%s must have the operand's dtype %s, got %s" % (what, like.dtype, zp.dtype))
+    zp = zp.contiguous().reshape(-1)
+    return zp, zp.numel()
+
+
+def MatMulInteger(a, b, a_zero_point=None, b_zero_point=None, path=PATH_AUTO):
+    """runtime/chxvm_defs.py:462-465; body runtime/ops/quantize.cc:96-114."""
+    _require_cuda(a, b)
+    ca, cb = _qcode(a, "MatMulInteger: a"), _qcode(b, "MatMulInteger: b")
+    if a.dim() < 2 or b.dim() < 2:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "MatMulInteger: operands need at least two dimensions")
+    if a.dim() > 2 and a.shape[:-2] != b.shape[:-2]:
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "MatMulInteger: batched operands need equal leading dimensions")
+    if a.dim() != b.dim():
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "MatMulInteger: operands need the same number of dimensions")
+    M, K = a.shape[-2], a.shape[-1]
+    K2, N = b.shape[-2], b.shape[-1]
+    if K != K2:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "MatMulInteger: inner dimensions differ (%d vs %d)" % (K, K2))
+    batch = 1
+    for d in a.shape[:-2]:
+        batch *= d
+    a, b = a.contiguous(), b.contiguous()
+    za, za_len = _zp_array(a_zero_point, a, "a_zero_point")
+    zb, zb_len = _zp_array(b_zero_point, b, "b_zero_point")
+    y = torch.empty(tuple(a.shape[:-2]) + (M, N), dtype=torch.int32, device=a.device)
+    ws_bytes = lib().chxq_matmul_integer_workspace(batch, M, N, K) if path != PATH_SIMT else 0
+    ws = workspace(ws_bytes, a.device)
+    check(lib().chxq_matmul_integer(_ptr(a), ca, _ptr(b), cb, batch, M, N, K, _ptr(za), za_len, _ptr(zb), zb_len, _ptr(y), _ptr(ws), ws_bytes,
+                                    path, _stream()))
+    return y
+
+
+def QLinearMatMul(a, a_scale, a_zero_point, b, b_scale, b_zero_point, y_scale, y_zero_point, round_mode=ROUND_REF, path=PATH_AUTO):
+    """ONNX QLinearMatMul.  The reference has no VM op for it: compiler/simplifier.cc:675-694 rewrites the
+    node into DequantizeLinear, DequantizeLinear, MatMul, QuantizeLinear with scalar parameters; this is
+    that chain as one kernel."""
+    _require_cuda(a, b)
+    ca, cb = _qcode(a, "QLinearMatMul: a"), _qcode(b, "QLinearMatMul: b")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearMatMul: expected [M,K] x [K,N]")
+    M, K = a.shape
+    N = b.shape[1]
+    za, _ = _zp_scalar(a_zero_point)
+    zb, _ = _zp_scalar(b_zero_point)
+    zy, cy = _zp_scalar(y_zero_point)
+    a, b = a.contiguous(), b.contiguous()
+    y = torch.empty((M, N), dtype=torch.uint8 if cy == UINT8 else torch.int8, device=a.device)
+    ws_bytes = lib().chxq_matmul_integer_workspace(1, M, N, K) if path != PATH_SIMT else 0
+    ws = workspace(ws_bytes, a.device)
+    check(lib().chxq_qlinear_matmul(_ptr(a), ca, float(a_scale), za, _ptr(b), cb, float(b_scale), zb, float(y_scale), zy, cy, M, N, K, round_mode,
+                                    _ptr(y), _ptr(ws), ws_bytes, path, _stream()))
+    return y
+
+
+def conv_geometry(x, w, strides, pads, group, auto_pad):
+    """Geometry of a convolution the way the reference resolves it (runtime/chainerx_util.cc:180-200,276-311)."""
+    return conv_geometry_from_shapes(tuple(x.shape), _qcode(x, "x"), tuple(w.shape), _qcode(w, "w"), strides, pads, group, auto_pad)
+
+
+def conv_geometry_from_shapes(x_shape, x_code, w_shape, w_code, strides, pads, group, auto_pad):
+    if len(x_shape) != 4 or len(w_shape) != 4:
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "convolutions over 2 spatial dimensions only")
+    N, C, H, W = x_shape
+    M, Cg, KH, KW = w_shape
+    g = ConvGeom()
+    s = (ctypes.c_int64 * 2)(*(list(strides) + [1, 1])[:2])
+    p = (ctypes.c_int64 * 2)(*(list(pads) + [0, 0])[:2])
+    check(lib().chxq_conv_resolve_geometry(N, C, H, W, M, Cg, KH, KW, s, len(strides), p, len(pads), group, (auto_pad or "").encode(),
+                                           ctypes.byref(g)))
+    g.x_dtype = x_code
+    g.w_dtype = w_code
+    return g
+
+
+def _conv_io(x, g, out_dtype):
+    """Pick layouts: channels_last maps use the NHWC kernels."""
+    if _is_channels_last(x):
+        g.x_layout = g.y_layout = NHWC
+        y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=out_dtype, device=x.device, memory_format=torch.channels_last)
+    else:
+        x = x.contiguous()
+        g.x_layout = g.y_layout = NCHW
+        y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=out_dtype, device=x.device)
+    return x, y
+
+
+def ConvInteger(x, w, x_zero_point=None, w_zero_point=None, strides=(), pads=(), group=1, auto_pad="", path=PATH_AUTO):
+    """runtime/chxvm_defs.py:466-469; body runtime/ops/quantize.cc:116-146."""
+    _require_cuda(x, w)
+    g = conv_geometry(x, w, strides, pads, group, auto_pad)
+    x, y = _conv_io(x, g, torch.int32)
+    w = w.contiguous()
+    zx, _ = _zp_scalar(x_zero_point)
+    zw, zw_len = _zp_array(w_zero_point, w, "w_zero_point")
+    ws_bytes = lib().chxq_conv_workspace(ctypes.byref(g)) if path != PATH_SIMT else 0
+    ws = workspace(ws_bytes, x.device)
+    check(lib().chxq_conv_integer(_ptr(x), _ptr(w), ctypes.byref(g), int(x_zero_point is not None), zx, _ptr(zw), zw_len, _ptr(y), _ptr(ws),
+                                  ws_bytes, path, _stream()))
+    return y
+
+
+def _qconv_params(x, w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, residual, res_scale,
+                  res_zero_point, res_relu, out_scale, out_zero_point, keep):
+    p = QConvParams()
+    zx, _ = _zp_scalar(x_zero_point)
+    zy, cy = _zp_scalar(y_zero_point)
+    if not isinstance(w_scale, torch.Tensor):
+        w_scale = torch.as_tensor(np.asarray(w_scale, np.float32), device=x.device)
+    if not isinstance(w_zero_point, torch.Tensor):
+        w_zero_point = torch.as_tensor(np.asarray(w_zero_point), device=x.device)
+    _require_cuda(w_scale, w_zero_point)
+    # runtime/ops/quantize.cc:76-77: scale and zero point agree in size and rank; rank is 0 or 1.
+    if w_scale.numel() != w_zero_point.numel() or w_scale.dim() != w_zero_point.dim() or w_scale.dim() > 1:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConv: w_scale and w_zero_point must both be 0-d or both be 1-d of equal length")
+    if w_scale.dim() == 1 and w_scale.shape[0] != w.shape[0]:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConv: per-channel w_scale needs one entry per output channel")  # :79
+    if w_scale.dtype != torch.float32 or w_zero_point.dtype != w.dtype:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConv: w_scale must be float32 and w_zero_point must have w's dtype")
+    w_scale, w_zero_point = w_scale.contiguous(), w_zero_point.contiguous()
+    keep.extend([w_scale, w_zero_point])
+    p.x_scale, p.x_zero_point = float(x_scale), zx
+    p.w_scale, p.w_zero_point, p.w_params_len = w_scale.data_ptr(), w_zero_point.data_ptr(), w_scale.numel()
+    p.y_scale, p.y_zero_point, p.y_dtype = float(y_scale), zy, cy
+    if b is not None:
+        _require_cuda(b)
+        if b.dtype != torch.int32 or b.numel() != w.shape[0]:
+            raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConv: bias must be int32 with one entry per output channel")
+        b = b.contiguous()
+        keep.append(b)
+        p.bias = b.data_ptr()
+    p.round_mode = round_mode
+    p.clamp_hi_q = -1 if clamp_hi_q is None else int(clamp_hi_q)
+    if residual is not None:
+        _require_cuda(residual)
+        p.residual = residual.data_ptr()
+        p.res_scale, p.res_zero_point, p.res_relu = float(res_scale), int(res_zero_point), int(bool(res_relu))
+        p.out_scale, p.out_zero_point = float(out_scale), int(out_zero_point)
+    return p, cy
+
+
+def QLinearConv(x, x_scale, x_zero_point, w, w_scale, w_zero_point, y_scale, y_zero_point, b=None, strides=(), pads=(), group=1,
+                auto_pad="", round_mode=ROUND_REF, path=PATH_AUTO, clamp_hi_q=None, residual=None, res_scale=1.0, res_zero_point=0,
+                res_relu=True, out_scale=1.0, out_zero_point=0):
+    """runtime/chxvm_defs.py:457-461; body runtime/ops/quantize.cc:62-94.
+
+    The keyword arguments after ``auto_pad`` have no counterpart in the reference: ``clamp_hi_q`` folds a
+    ReLU6 into the output range, ``residual`` (+ scales) fuses the DequantizeLinear, DequantizeLinear, Add,
+    Relu, QuantizeLinear nodes that follow the convolution of a residual block into the epilogue.
+    """
+    _require_cuda(x, w)
+    g = conv_geometry(x, w, strides, pads, group, auto_pad)
+    keep = []
+    p, cy = _qconv_params(x, w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, residual,
+                          res_scale, res_zero_point, res_relu, out_scale, out_zero_point, keep)
+    x, y = _conv_io(x, g, torch.uint8 if cy == UINT8 else torch.int8)
+    if residual is not None:
+        if residual.shape != y.shape or residual.dtype != torch.uint8 or _is_channels_last(residual) != (g.y_layout == NHWC):
+            raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConv: residual must be a uint8 map with the output's shape and layout")
+    w = w.contiguous()
+    ws_bytes = lib().chxq_conv_workspace(ctypes.byref(g)) if path != PATH_SIMT else 0
+    ws = workspace(ws_bytes, x.device)
+    check(lib().chxq_qlinear_conv(_ptr(x), _ptr(w), ctypes.byref(g), ctypes.byref(p), _ptr(y), _ptr(ws), ws_bytes, path, _stream()))
+    return y
+
+
+class PackedConv:
+    """Constant weights of one QLinearConv / ConvInteger, packed once for the tensor-core path."""
+
+    def __init__(self, w, w_zero_point, x_shape, strides=(), pads=(), group=1, auto_pad="", x_dtype=torch.uint8, x_layout=NHWC):
+        _require_cuda(w)
+        self.w = w.contiguous()
+        self.g = conv_geometry_from_shapes(tuple(x_shape), _TORCH_Q[x_dtype], tuple(self.w.shape), _qcode(self.w, "w"), strides, pads, group,
+                                           auto_pad)
+        self.g.x_layout, self.g.y_layout = x_layout, NHWC
+        self.zw, self.zw_len = _zp_array(w_zero_point, self.w, "w_zero_point")
+        nbytes = lib().chxq_conv_prepack_bytes(ctypes.byref(self.g))
+        self.flags = 0
+        self.blob = None
+        if nbytes:
+            self.blob = torch.empty(int(nbytes), dtype=torch.uint8, device=w.device)
+            flags = ctypes.c_int32(0)
+            check(lib().chxq_conv_prepack(_ptr(self.w), ctypes.byref(self.g), _ptr(self.zw), self.zw_len, _ptr(self.blob), nbytes,
+                                          ctypes.byref(flags), _stream()))
+            self.flags = flags.value
+
+    @property
+    def eligible(self):
+        return bool(self.flags & 1)
+
+
+def QLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b=None, round_mode=ROUND_REF,
+                      clamp_hi_q=None, residual=None, res_scale=1.0, res_zero_point=0, res_relu=True, out_scale=1.0, out_zero_point=0,
+                      out=None):
+    """QLinearConv with weights packed by PackedConv; x must be a channels_last map of the packed geometry."""
+    _require_cuda(x)
+    g = packed.g
+    layout_ok = _is_channels_last(x) if g.x_layout == NHWC else x.is_contiguous()
+    if tuple(x.shape) != (g.N, g.C, g.H, g.W) or not layout_ok:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConvPacked: x does not match the packed geometry / layout")
+    keep = []
+    p, cy = _qconv_params(x, packed.w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, residual,
+                          res_scale, res_zero_point, res_relu, out_scale, out_zero_point, keep)
+    y = out if out is not None else torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.uint8 if cy == UINT8 else torch.int8, device=x.device,
+                                                 memory_format=torch.channels_last)
+    if not packed.eligible:
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "QLinearConvPacked: this geometry is not eligible for the packed tensor-core path")
+    ws_bytes = lib().chxq_conv_packed_workspace(ctypes.byref(g), p.x_zero_point, packed.flags)
+    ws = workspace(ws_bytes, x.device)
+    check(lib().chxq_qlinear_conv_packed(_ptr(x), _ptr(packed.blob), ctypes.byref(g), ctypes.byref(p), packed.flags, _ptr(y), _ptr(ws),
+                                         ws_bytes, _stream()))
+    return y
+
+
+def ElementWiseNvrtc(inputs, num_outputs, code, fusion_id):
+    """runtime/chxvm_defs.py:431-434; body runtime/ops/nvrtc.cc:90-161: broadcast every input to the common
+    shape, make it contiguous, allocate num_outputs arrays of that shape and dtype, run the generated kernel."""
+    if not inputs:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "ElementWiseNvrtc: no inputs")
+    _require_cuda(*inputs)
+    dtype = inputs[0].dtype
+    if dtype not in _TORCH_F:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "ElementWiseNvrtc: dtype %s is not a float type" % dtype)
+    for t in inputs:
+        if t.dtype != dtype:
+            raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "ElementWiseNvrtc: all inputs must share one dtype")  # runtime/ops/nvrtc.cc:102
+    shape = torch.broadcast_shapes(*[tuple(t.shape) for t in inputs])
+    ins = [(t if tuple(t.shape) == tuple(shape) else t.broadcast_to(shape)).contiguous() for t in inputs]
+    outs = [torch.empty(shape, dtype=dtype, device=ins[0].device) for _ in range(num_outputs)]
+    n = ins[0].numel()
+    in_ptrs = (ctypes.c_void_p * len(ins))(*[t.data_ptr() for t in ins])
+    out_ptrs = (ctypes.c_void_p * len(outs))(*[t.data_ptr() for t in outs])
+    check(lib().chxq_eltwise_run(code.encode() if isinstance(code, str) else code, fusion_id, in_ptrs, len(ins), out_ptrs, len(outs), n,
+                                 _TORCH_F[dtype], _stream()))
+    return outs
+
+
+# ---- glue ops of a quantized CNN graph -------------------------------------------------------------
+
+def MaxPoolU8(x, kernel, stride, pad=0, cover_all=False):
+    """MaxPool (runtime/ops/pooling.cc:47-60) on a uint8 channels_last map."""
+    _require_cuda(x)
+    if x.dtype != torch.uint8 or not _is_channels_last(x):
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "MaxPoolU8: expected a uint8 channels_last map")
+    N, C, H, W = x.shape
+
+    def osz(i):
+        return (i + 2 * pad - kernel + (stride - 1 if cover_all else 0)) // stride + 1
+
+    Ho, Wo = osz(H), osz(W)
+    y = torch.empty((N, C, Ho, Wo), dtype=torch.uint8, device=x.device, memory_format=torch.channels_last)
+    check(lib().chxq_maxpool_u8_nhwc(_ptr(x), N, H, W, C, kernel, stride, pad, Ho, Wo, _ptr(y), _stream()))
+    return y
+
+
+def GlobalAveragePoolDequant(x, x_scale, x_zero_point=0):
+    """DequantizeLinear followed by a global AveragePool (runtime/ops/pooling.cc:62-75) of a uint8 channels_last map -> [N, C] fp32."""
+    _require_cuda(x)
+    if x.dtype != torch.uint8 or not _is_channels_last(x):
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "GlobalAveragePoolDequant: expected a uint8 channels_last map")
+    N, C, H, W = x.shape
+    y = torch.empty((N, C), dtype=torch.float32, device=x.device)
+    check(lib().chxq_global_avgpool_dq_nhwc(_ptr(x), N, H * W, C, float(x_scale), int(x_zero_point), _ptr(y), _stream()))
+    return y
+
+
+def Linear(x, w, b=None):
+    """runtime/ops/connection.cc:12-15 (fp32): y = x w^T + b."""
+    _require_cuda(x, w, b)
+    x, w = x.contiguous(), w.contiguous()
+    y = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+    check(lib().chxq_linear_f32(_ptr(x), _ptr(w), _ptr(b.contiguous()) if b is not None else None, x.shape[0], x.shape[1], w.shape[0], _ptr(y),
+                                _stream()))
+    return y
+
+
+def QAddU8(a, a_scale, a_zero_point, b, b_scale, b_zero_point, y_scale, y_zero_point=0, relu=True, round_mode=ROUND_REF):
+    """DequantizeLinear(a), DequantizeLinear(b), Add, Relu, QuantizeLinear in one pass (same memory layout in and out)."""
+    _require_cuda(a, b)
+    if a.shape != b.shape or a.dtype != torch.uint8 or b.dtype != torch.uint8 or a.stride() != b.stride():
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QAddU8: operands must be uint8 maps of equal shape and layout")
+    y = torch.empty_like(a)
+    check(lib().chxq_qadd_u8(_ptr(a), float(a_scale), int(a_zero_point), _ptr(b), float(b_scale), int(b_zero_point), a.numel(), float(y_scale),
+                             int(y_zero_point), int(bool(relu)), round_mode, _ptr(y), _stream()))
+    return y
+
+
+def to_channels_last(x):
+    """NCHW -> NHWC copy of a 1- or 4-byte map through the library's transpose kernel."""
+    _require_cuda(x)
+    if _is_channels_last(x):
+        return x
+    x = x.contiguous()
+    N, C, H, W = x.shape
+    y = torch.empty_like(x, memory_format=torch.channels_last)
+    check(lib().chxq_nchw_to_nhwc(_ptr(x), x.element_size(), N, C, H, W, 0, _ptr(y), _stream()))
+    return y
+
+
+def to_contiguous_nchw(x):
+    _require_cuda(x)
+    if x.is_contiguous():
+        return x
+    if not _is_channels_last(x):
+        return x.contiguous()
+    N, C, H, W = x.shape
+    y = torch.empty((N, C, H, W), dtype=x.dtype, device=x.device)
+    check(lib().chxq_nhwc_to_nchw(_ptr(x), x.element_size(), N, C, H, W, 0, _ptr(y), _stream()))
+    return y
+
+
+def MinMax(x):
+    """ReduceMin and ReduceMax of an fp32 tensor in one pass -> device tensor [min, max]."""
+    _require_cuda(x)
+    x = x.contiguous()
+    out = torch.empty(2, dtype=torch.float32, device=x.device)
+    check(lib().chxq_minmax_f32(_ptr(x), x.numel(), _ptr(out), _stream()))
+    return out
+
+
+def device_status():
+    """Raises if a bounded device-side wait expired since the last call (synchronises the stream)."""
+    check(lib().chxq_device_status(_stream()))

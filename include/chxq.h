@@ -62,6 +62,16 @@ extern "C" {
 const char* chxq_last_error(void);
 int chxq_version(void);
 
+/* Number of kernels this library has launched in this process so far. */
+int64_t chxq_launch_count(void);
+
+/* Timing of the tensor-core kernel: while enabled, each launch is bracketed by CUDA events on its
+ * own stream (do not enable during stream capture).  chxq_tc_profile_read SYNCHRONISES the device,
+ * returns the summed duration, the launch count and the summed multiply-accumulates (as the ops
+ * define them, without padding) of the launches recorded since the last read, and clears them. */
+int chxq_tc_profile(int32_t enable);
+int chxq_tc_profile_read(double* total_ms, int64_t* launches, double* total_macs);
+
 /* Reads (and clears) the device-side status word of the current device.  SYNCHRONISES `stream`.
  * Returns CHXQ_OK or CHXQ_ERR_DEVICE_TIMEOUT. */
 int chxq_device_status(void* stream);
@@ -172,6 +182,8 @@ int chxq_qlinear_conv(const void* x, const void* w, const chxq_conv_geom* g, con
  * chxq_conv_workspace) holds the im2col matrix and per-position sums when the geometry or the
  * zero points need them. */
 size_t chxq_conv_prepack_bytes(const chxq_conv_geom* g);
+/* Exact workspace of the packed entries for this geometry, activation zero point and pack flags. */
+size_t chxq_conv_packed_workspace(const chxq_conv_geom* g, int32_t x_zero_point, int32_t packed_flags);
 int chxq_conv_prepack(const void* w, const chxq_conv_geom* g, const void* w_zero_point, int64_t w_zp_len, void* packed,
                       size_t packed_bytes, int32_t* flags, void* stream);
 int chxq_qlinear_conv_packed(const void* x, const void* packed, const chxq_conv_geom* g, const chxq_qconv_params* p, int32_t packed_flags,

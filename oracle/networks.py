@@ -1,0 +1,56 @@
+"""CPU restatement of the benchmark networks as chains of the oracle's ops (TEST INFRASTRUCTURE ONLY; PARITY UNPINNED,
+see chxq_oracle.c).  `params` is what ``models.ResNet50Int8.export_numpy()`` returns.
+
+mode="emulate": every QLinearConv runs as the reference does (runtime/ops/quantize.cc:62-94: dequantize, fp32 convolution,
+quantize) -- this is the reference's CPU path and what the bench times as the CPU baseline.
+mode="exact": every QLinearConv requantizes the exact int32 accumulator -- the arithmetic of the CUDA kernels, which the
+GPU results must match bit for bit.
+"""
+import numpy as np
+
+from . import oracle as orc
+
+
+def _qconv(c, x, mode):
+    wz = np.asarray(c["w_zp"], np.int32)
+    if mode == "emulate":
+        return orc.qlinear_conv(x, c["x_scale"], 0, c["w"], c["w_scale"], wz, c["y_scale"], c["y_zp"], b=c["bias"],
+                                strides=(c["stride"], c["stride"]), pads=(c["pad"], c["pad"]))
+    acc = orc.conv_integer(x, c["w"], 0, wz, strides=(c["stride"], c["stride"]), pads=(c["pad"], c["pad"]))
+    return orc.requantize(acc, c["x_scale"], c["w_scale"], c["y_scale"], c["y_zp"], bias=c["bias"], channel_axis=1)
+
+
+def resnet50_forward(params, x, mode="exact", taps=None):
+    """x: fp32 NCHW.  Returns fp32 logits.  taps (dict) receives the uint8 NCHW maps 'stem', 'block<i>' and 'pooled'."""
+    xq = orc.quantize_linear(x, params["in_scale"], 0)
+    h = _qconv(params["stem"], xq, mode)
+    if taps is not None:
+        taps["stem"] = h
+    h = orc.maxpool_u8(h, 3, 2, 0, cover_all=True)
+    h_scale = params["stem"]["y_scale"]
+    for i, b in enumerate(params["blocks"]):
+        h1 = _qconv(b["conv1"], h, mode)
+        h2 = _qconv(b["conv2"], h1, mode)
+        h3 = _qconv(b["conv3"], h2, mode)
+        sc = _qconv(b["proj"], h, mode) if b["proj"] is not None else h
+        sc_scale, sc_zp = b["res"]
+        h = orc.qadd_relu(h3, b["conv3"]["y_scale"], b["conv3"]["y_zp"], sc, sc_scale, sc_zp, b["out_scale"], 0, relu=True)
+        h_scale = b["out_scale"]
+        if taps is not None:
+            taps["block%d" % i] = h
+    pooled = orc.global_avgpool_dq(h, h_scale, 0)
+    if taps is not None:
+        taps["pooled"] = pooled
+    return orc.linear_f32(pooled, params["fc_w"], params["fc_b"])
+
+
+def mlp_forward(layers, act_scale, x, mode="emulate"):
+    """QuantizeLinear -> QLinearMatMul x n -> DequantizeLinear; layers: list of dict(w_q [K,N] int8, w_scale)."""
+    h = orc.quantize_linear(x, act_scale, 0)
+    for l in layers:
+        if mode == "emulate":
+            h = orc.qlinear_matmul(h, act_scale, 0, l["w_q"], l["w_scale"], 0, act_scale, 0)
+        else:
+            acc = orc.matmul_integer(h, l["w_q"])
+            h = orc.requantize(acc, act_scale, np.array([l["w_scale"]], np.float32), act_scale, 0)
+    return orc.dequantize_linear(h, act_scale, 0)

@@ -1,0 +1,242 @@
+"""ConvInteger / QLinearConv: CUDA-core, depthwise and tcgen05 kernels against the CPU oracle.
+int32 accumulators bit-exact; requantized outputs bit-exact against the integer-domain oracle and at most one step from the
+fp32-emulating oracle (the reference's dequantize -> fp32 conv -> quantize), mismatch counts printed."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import lsb_report
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "hotpath_vectors.npz")
+SIMT, TENSOR, AUTO = 1, 2, 0
+
+
+def _t(a, dev, cl=False):
+    if a is None:
+        return None
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    return t.contiguous(memory_format=torch.channels_last) if cl else t
+
+
+def _rand(rng, shape, dtype, lo=None, hi=None):
+    lo = np.iinfo(dtype).min if lo is None else lo
+    hi = np.iinfo(dtype).max if hi is None else hi
+    return rng.integers(lo, hi + 1, shape).astype(dtype)
+
+
+@pytest.mark.parametrize("N,C,H,W,M,k,stride,pad,group,auto_pad", [
+    (2, 8, 9, 11, 12, 3, (2, 1), (1, 1), 2, ""),
+    (1, 3, 16, 16, 8, 7, (2, 2), (3, 3), 1, ""),
+    (2, 6, 7, 7, 6, 3, (1, 1), (1, 1), 6, ""),
+    (1, 4, 10, 10, 5, 5, (), (), 1, "SAME_UPPER"),
+    (2, 4, 9, 9, 4, 2, (2, 2), (), 1, "SAME_UPPER"),
+    (1, 16, 5, 5, 32, 1, (), (), 1, ""),
+])
+@pytest.mark.parametrize("cl", [False, True])
+def test_conv_integer_simt(ops, orc, dev, N, C, H, W, M, k, stride, pad, group, auto_pad, cl):
+    rng = np.random.default_rng(C * 100 + M)
+    x = _rand(rng, (N, C, H, W), np.uint8)
+    w = _rand(rng, (M, C // group, k, k), np.int8)
+    for zx, zw in ((None, None), (7, _rand(rng, M, np.int8, -9, 9)), (128, np.array([3], np.int8))):
+        y = ops.ConvInteger(_t(x, dev, cl), _t(w, dev), None if zx is None else np.uint8(zx), _t(zw, dev), stride, pad, group, auto_pad, path=SIMT)
+        want = orc.conv_integer(x, w, zx, zw, stride, pad, group, auto_pad)
+        assert y.shape == want.shape and np.array_equal(y.cpu().numpy(), want)
+
+
+# (N, C, H, W, M, k, stride, pad): direct TMA path when stride 1, im2col path otherwise
+TC_CASES = [
+    (2, 64, 8, 8, 64, 1, 1, 0),      # 1x1, flattened positions
+    (3, 128, 7, 7, 256, 1, 1, 0),    # odd map, ragged position tile, BN 256
+    (2, 64, 8, 8, 64, 3, 1, 1),      # 3x3, box 8x8x2
+    (5, 32, 7, 7, 48, 3, 1, 1),      # odd map: box 1x1x128 over 5 images, bk 32, ragged N tile
+    (2, 48, 12, 12, 80, 3, 1, 1),    # C = 48 -> bk 32 + zero-filled chunk? (48 = 32 + 16), box 4x4x8
+    (2, 144, 6, 6, 32, 1, 1, 0),     # C = 144 -> ragged last K chunk filled by TMA
+    (2, 256, 14, 14, 128, 3, 1, 1),  # box 2x2x32, bk 128
+    (4, 64, 16, 16, 128, 1, 2, 0),   # stride 2 1x1 -> im2col (gather)
+    (2, 16, 9, 9, 24, 3, 2, 1),      # stride 2 3x3 -> im2col, M = 24 (ragged column tile, scalar stores)
+    (1, 64, 10, 10, 64, 5, 1, 2),    # 5x5
+]
+
+
+@pytest.mark.parametrize("N,C,H,W,M,k,stride,pad", TC_CASES)
+def test_conv_integer_tensor(ops, orc, dev, N, C, H, W, M, k, stride, pad):
+    rng = np.random.default_rng(C + M + H)
+    x = _rand(rng, (N, C, H, W), np.uint8)
+    w = _rand(rng, (M, C, k, k), np.int8)
+    y = ops.ConvInteger(_t(x, dev, True), _t(w, dev), None, None, (stride, stride), (pad, pad), path=TENSOR)
+    ops.device_status()
+    assert y.is_contiguous(memory_format=torch.channels_last)
+    want = orc.conv_integer(x, w, None, None, (stride, stride), (pad, pad))
+    assert np.array_equal(y.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("N,C,H,W,M,k,stride,pad", [TC_CASES[2], TC_CASES[4], TC_CASES[8], TC_CASES[0]])
+@pytest.mark.parametrize("zx,zwmode,wdt", [(128, None, np.int8), (0, "vec", np.uint8), (9, "vec", np.int8), (200, "scalar", np.uint8)])
+def test_conv_integer_tensor_zero_points(ops, orc, dev, N, C, H, W, M, k, stride, pad, zx, zwmode, wdt):
+    """Zero points on the tensor-core path: x_zp with padding needs the explicit pad value (im2col); w_zp needs the
+    per-position input sums."""
+    rng = np.random.default_rng(zx + M)
+    x = _rand(rng, (N, C, H, W), np.uint8)
+    w = _rand(rng, (M, C, k, k), wdt)
+    zw = None if zwmode is None else (_rand(rng, M, wdt, 0, 20) if zwmode == "vec" else _rand(rng, 1, wdt, 1, 20))
+    y = ops.ConvInteger(_t(x, dev, True), _t(w, dev), np.uint8(zx), _t(zw, dev), (stride, stride), (pad, pad), path=TENSOR)
+    ops.device_status()
+    want = orc.conv_integer(x, w, zx, zw, (stride, stride), (pad, pad))
+    assert np.array_equal(y.cpu().numpy(), want)
+
+
+def test_conv_integer_stem_nchw_input_packed(ops, orc, dev, pkg):
+    """7x7 / 2 stem over a 3-channel NCHW map (im2col path) through the packed entry, NHWC output."""
+    import ctypes
+    from chainer_compiler_b200 import _lib
+    rng = np.random.default_rng(8)
+    x = _rand(rng, (3, 3, 30, 30), np.uint8)
+    w = _rand(rng, (64, 3, 7, 7), np.int8)
+    pk = ops.PackedConv(_t(w, dev), None, x.shape, (2, 2), (3, 3), x_layout=_lib.NCHW)
+    assert pk.eligible and (pk.flags & 2)
+    g = pk.g
+    y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.int32, device=dev, memory_format=torch.channels_last)
+    nb = pkg.lib().chxq_conv_packed_workspace(ctypes.byref(g), 0, pk.flags)
+    ws = ops.workspace(nb, dev)
+    _lib.check(pkg.lib().chxq_conv_integer_packed(ops._ptr(_t(x, dev)), ops._ptr(pk.blob), ctypes.byref(g), 1, 0, pk.flags, ops._ptr(y), ops._ptr(ws),
+                                                  nb, ops._stream()))
+    ops.device_status()
+    assert np.array_equal(y.cpu().numpy(), orc.conv_integer(x, w, 0, None, (2, 2), (3, 3)))
+
+
+@pytest.mark.parametrize("path,cl", [(SIMT, False), (SIMT, True), (TENSOR, True)])
+@pytest.mark.parametrize("N,C,H,W,M,k,stride,pad", [TC_CASES[2], TC_CASES[3], TC_CASES[8], TC_CASES[1]])
+def test_qlinear_conv(ops, orc, dev, path, cl, N, C, H, W, M, k, stride, pad):
+    rng = np.random.default_rng(M * 7 + k)
+    x = _rand(rng, (N, C, H, W), np.uint8)
+    w = _rand(rng, (M, C, k, k), np.int8, -127, 127)
+    ws = rng.uniform(0.0005, 0.002, M).astype(np.float32)
+    wz = np.zeros(M, np.int8)
+    bias = _rand(rng, M, np.int32, -3000, 3000)
+    sx, sy = 0.02, 0.09
+    for zx, zy, mode in ((0, 0, 0), (0, 17, 1), (5, 3, 0)):
+        y = ops.QLinearConv(_t(x, dev, cl), sx, np.uint8(zx), _t(w, dev), _t(ws, dev), _t(wz, dev), sy, np.uint8(zy), _t(bias, dev),
+                            (stride, stride), (pad, pad), round_mode=mode, path=path)
+        ops.device_status()
+        y = y.cpu().numpy()
+        acc = orc.conv_integer(x, w, zx, wz, (stride, stride), (pad, pad))
+        exact = orc.requantize(acc, sx, ws, sy, zy, bias=bias, channel_axis=1, round_mode=mode)
+        assert np.array_equal(y, exact), "integer-domain requantization must be bit-exact"
+        emul = orc.qlinear_conv(x, sx, zx, w, ws, wz, sy, zy, b=bias, strides=(stride, stride), pads=(pad, pad), round_mode=mode)
+        mx, cnt, tot = lsb_report(y, emul)
+        print("QLinearConv C%d M%d k%d: %d of %d differ from the fp32-emulating chain, max %d LSB" % (C, M, k, cnt, tot, mx))
+        assert mx <= 1
+
+
+def test_qlinear_conv_per_tensor_weights_int8_output_and_nonzero_wzp(ops, orc, dev):
+    rng = np.random.default_rng(12)
+    x = _rand(rng, (2, 32, 6, 6), np.int8)  # int8 activations
+    w = _rand(rng, (32, 32, 3, 3), np.uint8)  # asymmetric uint8 weights, per-tensor
+    ws, wz = np.array(0.003, np.float32), np.array(120, np.uint8)
+    for path, cl in ((SIMT, False), (TENSOR, True)):
+        y = ops.QLinearConv(_t(x, dev, cl), 0.05, np.int8(-4), _t(w, dev), _t(ws, dev), _t(wz, dev), 0.4, np.int8(-9), None, (1, 1), (1, 1), path=path)
+        ops.device_status()
+        assert y.dtype == torch.int8
+        acc = orc.conv_integer(x, w, -4, wz.reshape(1), (1, 1), (1, 1))
+        exact = orc.requantize(acc, 0.05, ws.reshape(1), 0.4, -9, channel_axis=1, y_dtype=np.int8)
+        assert np.array_equal(y.cpu().numpy(), exact)
+        emul = orc.qlinear_conv(x, 0.05, -4, w, ws, wz, 0.4, -9, strides=(1, 1), pads=(1, 1), y_dtype=np.int8)
+        assert lsb_report(y.cpu().numpy(), emul)[0] <= 1
+
+
+def test_qlinear_conv_rejects(ops, dev):
+    x = torch.zeros((1, 8, 4, 4), dtype=torch.uint8, device=dev)
+    w = torch.zeros((8, 8, 3, 3), dtype=torch.int8, device=dev)
+    s8, z8 = torch.ones(8, device=dev), torch.zeros(8, dtype=torch.int8, device=dev)
+    with pytest.raises(ops.ChxqError):  # per-channel length != M (quantize.cc:79)
+        ops.QLinearConv(x, 1.0, np.uint8(0), w, torch.ones(5, device=dev), torch.zeros(5, dtype=torch.int8, device=dev), 1.0, np.uint8(0))
+    with pytest.raises(ops.ChxqError):  # scale / zero point ranks differ (quantize.cc:76-77)
+        ops.QLinearConv(x, 1.0, np.uint8(0), w, s8, torch.zeros((), dtype=torch.int8, device=dev), 1.0, np.uint8(0))
+    with pytest.raises(ops.ChxqError):  # group does not divide the channels
+        ops.QLinearConv(x, 1.0, np.uint8(0), w, s8, z8, 1.0, np.uint8(0), group=3)
+    with pytest.raises(ops.ChxqError):
+        ops.QLinearConv(x, 1.0, np.uint8(0), w, s8, z8, 1.0, np.uint8(0), auto_pad="VALID")
+    with pytest.raises(ops.ChxqError):  # kernel larger than the padded input
+        ops.QLinearConv(x, 1.0, np.uint8(0), torch.zeros((8, 8, 7, 7), dtype=torch.int8, device=dev), s8, z8, 1.0, np.uint8(0))
+    y = ops.QLinearConv(torch.zeros((0, 8, 4, 4), dtype=torch.uint8, device=dev), 1.0, np.uint8(0), w, s8, z8, 1.0, np.uint8(0), pads=(1, 1))
+    assert y.shape == (0, 8, 4, 4)
+
+
+@pytest.mark.parametrize("path", [SIMT, TENSOR])
+def test_qlinear_conv_fused_residual_and_clamp(ops, orc, dev, path):
+    """The epilogue fusions equal the separate ops bit for bit: QLinearConv, then DequantizeLinear x2 + Add + Relu +
+    QuantizeLinear (residual tail); and the ReLU6 clamp in the quantized domain."""
+    rng = np.random.default_rng(13)
+    x = _rand(rng, (2, 64, 8, 8), np.uint8)
+    w = _rand(rng, (128, 64, 1, 1), np.int8)
+    ws = rng.uniform(0.0005, 0.002, 128).astype(np.float32)
+    wz = np.zeros(128, np.int8)
+    r = _rand(rng, (2, 128, 8, 8), np.uint8)
+    xt, wt, wst, wzt, rt = _t(x, dev, True), _t(w, dev), _t(ws, dev), _t(wz, dev), _t(r, dev, True)
+    plain = ops.QLinearConv(xt, 0.02, np.uint8(0), wt, wst, wzt, 0.05, np.uint8(121), path=path)
+    tail = ops.QAddU8(plain, 0.05, 121, rt, 0.03, 14, 0.04, 0, relu=True)
+    fused = ops.QLinearConv(xt, 0.02, np.uint8(0), wt, wst, wzt, 0.05, np.uint8(121), path=path, residual=rt, res_scale=0.03, res_zero_point=14,
+                            out_scale=0.04, out_zero_point=0)
+    ops.device_status()
+    assert torch.equal(fused, tail)
+    acc = orc.conv_integer(x, w, 0, wz)
+    y1 = orc.requantize(acc, 0.02, ws, 0.05, 121, channel_axis=1)
+    assert np.array_equal(fused.cpu().numpy(), orc.qadd_relu(y1, 0.05, 121, r, 0.03, 14, 0.04, 0, relu=True))
+    clamped = ops.QLinearConv(xt, 0.02, np.uint8(0), wt, wst, wzt, 0.05, np.uint8(0), path=path, clamp_hi_q=120)
+    want = orc.requantize(acc, 0.02, ws, 0.05, 0, channel_axis=1, clamp_hi_q=120)
+    assert np.array_equal(clamped.cpu().numpy(), want) and want.max() == 120
+
+
+@pytest.mark.parametrize("C,H,W,k,stride,pad", [(32, 14, 14, 3, 1, 1), (96, 15, 13, 3, 2, 1), (144, 7, 7, 3, 1, 1), (16, 9, 9, 5, 1, 2)])
+def test_depthwise_qlinear_conv(ops, orc, dev, C, H, W, k, stride, pad):
+    rng = np.random.default_rng(C + k)
+    x = _rand(rng, (3, C, H, W), np.uint8)
+    w = _rand(rng, (C, 1, k, k), np.int8, -127, 127)
+    ws = rng.uniform(0.001, 0.004, C).astype(np.float32)
+    wz = np.zeros(C, np.int8)
+    bias = _rand(rng, C, np.int32, -500, 500)
+    for zx, clamp in ((0, -1), (6, 150)):
+        args = (0.02, np.uint8(zx), _t(w, dev), _t(ws, dev), _t(wz, dev), 0.03, np.uint8(0), _t(bias, dev), (stride, stride), (pad, pad), C)
+        fast = ops.QLinearConv(_t(x, dev, True), *args, path=AUTO, clamp_hi_q=None if clamp < 0 else clamp)  # depthwise kernel
+        slow = ops.QLinearConv(_t(x, dev, False), *args, path=SIMT, clamp_hi_q=None if clamp < 0 else clamp)  # generic kernel, NCHW
+        acc = orc.conv_integer(x, w, zx, wz, (stride, stride), (pad, pad), C)
+        exact = orc.requantize(acc, 0.02, ws, 0.03, 0, bias=bias, channel_axis=1, clamp_hi_q=clamp)
+        assert np.array_equal(fast.cpu().numpy(), exact) and np.array_equal(slow.cpu().numpy(), exact)
+        emul = orc.qlinear_conv(x, 0.02, zx, w, ws, wz, 0.03, 0, b=bias, strides=(stride, stride), pads=(pad, pad), group=C, clamp_hi_q=clamp)
+        assert lsb_report(exact, emul)[0] <= 1
+
+
+def test_golden_conv(ops, dev):
+    g = np.load(GOLDEN)
+    x, w, zw = g["cv_x"], g["cv_w"], g["cv_zw"]
+    for cl in (False, True):
+        y = ops.ConvInteger(_t(x, dev, cl), _t(w, dev), np.uint8(7), _t(zw, dev), (2, 1), (1, 1), 2, path=SIMT)
+        assert np.array_equal(y.cpu().numpy(), g["cv_y"])
+        y = ops.ConvInteger(_t(x, dev, cl), _t(w, dev), np.uint8(7), None, (2, 2), (), 2, "SAME_UPPER", path=SIMT)
+        assert np.array_equal(y.cpu().numpy(), g["cv_y_same"])
+        y = ops.QLinearConv(_t(x, dev, cl), 0.02, np.uint8(7), _t(w, dev), _t(g["qc_ws"], dev), _t(zw, dev), 0.04, np.uint8(9), _t(g["qc_bias"], dev),
+                            (1, 1), (1, 1), 2, path=SIMT).cpu().numpy()
+        assert np.array_equal(y, g["qc_y_exact"]) and np.abs(y.astype(int) - g["qc_y"].astype(int)).max() <= 1
+
+
+def test_conv_full_size_layer_properties(ops, dev):
+    """One ResNet-50 layer at benchmark size (256 x 64 x 56 x 56, 3x3 -> 64): linearity in the weights
+    (conv(x, w1) + conv(x, w2) == conv(x, w1 + w2) on int32 accumulators) and agreement of a strided sample of output
+    positions with the CUDA-core kernel run on the same data."""
+    gen = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randint(0, 256, (256, 64, 56, 56), dtype=torch.uint8, device=dev, generator=gen).contiguous(memory_format=torch.channels_last)
+    w1 = torch.randint(-60, 61, (64, 64, 3, 3), dtype=torch.int8, device=dev, generator=gen)
+    w2 = torch.randint(-60, 61, (64, 64, 3, 3), dtype=torch.int8, device=dev, generator=gen)
+    y1 = ops.ConvInteger(x, w1, None, None, (1, 1), (1, 1), path=TENSOR)
+    y2 = ops.ConvInteger(x, w2, None, None, (1, 1), (1, 1), path=TENSOR)
+    y12 = ops.ConvInteger(x, (w1 + w2), None, None, (1, 1), (1, 1), path=TENSOR)
+    ops.device_status()
+    assert torch.equal(y1 + y2, y12)
+    xs = x[:2].contiguous(memory_format=torch.channels_last)
+    ref = ops.ConvInteger(xs, w1, None, None, (1, 1), (1, 1), path=SIMT)
+    assert torch.equal(y1[:2], ref)
+    xs = x[254:].contiguous(memory_format=torch.channels_last)
+    assert torch.equal(y1[254:], ops.ConvInteger(xs, w1, None, None, (1, 1), (1, 1), path=SIMT))
