@@ -384,6 +384,7 @@ int conv_dispatch(
         void* y, void* workspace, size_t workspace_bytes, int path, cudaStream_t s) {
     int rc = validate_geom(op, g);
     if (rc != CHXQ_OK) return rc;
+    if ((int64_t)g->N * g->M * g->Ho * g->Wo == 0) return CHXQ_OK;  // empty batch: nothing to compute
     CHXQ_CHECK_ARG(x && w && y, "%s: null buffer", op);
     CHXQ_CHECK_ARG(path == CHXQ_PATH_AUTO || path == CHXQ_PATH_SIMT || path == CHXQ_PATH_TENSOR, "%s: bad path", op);
     const int xz = has_x_zp ? x_zp : 0;

@@ -8,6 +8,18 @@
 
 namespace chxq {
 
+// Saturating float -> uint8 conversions (one instruction each): floor / nearest-even, clamped to [0, 255].
+__device__ __forceinline__ int cvt_floor_sat_u8(float t) {
+    uint32_t q;
+    asm("cvt.rmi.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(t));
+    return (int)q;
+}
+__device__ __forceinline__ int cvt_rne_sat_u8(float t) {
+    uint32_t q;
+    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(t));
+    return (int)q;
+}
+
 // One element of quantize_array (runtime/ops/quantize.cc:29-34): t = x / s; (+zp); min(hi);
 // max(lo); + 0.5f; truncate.  ROUND_RNE instead gives saturate(rint(x / s) + zp).
 template <bool kSigned>
@@ -15,6 +27,14 @@ __device__ __forceinline__ int quantize_one(float x, float scale, float zp_f, bo
     const float lo = kSigned ? -128.f : 0.f;
     const float hi = kSigned ? 127.f : 255.f;
     float t = __fdiv_rn(x, scale);
+    if (!kSigned) {
+        // uint8: clamp, +0.5f and truncation fold into one saturating conversion with the same result for every
+        // input: clamp(t) + 0.5f >= 0.5 makes the truncation a floor, and floor(t + 0.5f) saturated to [0, 255]
+        // agrees with it on both sides of the clamp.  (Not so for int8, where truncation is toward zero.)
+        if (round_mode != 0) return cvt_rne_sat_u8(__fadd_rn(rintf(t), zp_f));
+        if (has_zp) t = __fadd_rn(t, zp_f);
+        return cvt_floor_sat_u8(__fadd_rn(t, 0.5f));
+    }
     if (round_mode != 0) {
         t = __fadd_rn(rintf(t), zp_f);
         t = fminf(t, hi);
@@ -61,6 +81,11 @@ __device__ __forceinline__ int requant_one(int acc, float mult, const RequantPar
     int q = quantize_any(yf, p.y_scale, p.y_zp_f, p.y_has_zp != 0, p.round_mode, p.y_signed != 0);
     if (p.clamp_hi_q >= 0 && q > p.clamp_hi_q) q = p.clamp_hi_q;
     return q;
+}
+
+// requant_one for a uint8 output without the optional upper clamp (the caller applies it).
+__device__ __forceinline__ int requant_u8_fast(int acc, float mult, const RequantParams& p) {
+    return quantize_one<false>(__fmul_rn((float)acc, mult), p.y_scale, p.y_zp_f, p.y_has_zp != 0, p.round_mode);
 }
 
 // DequantizeLinear(y), DequantizeLinear(r), Add, Relu, QuantizeLinear on one element.

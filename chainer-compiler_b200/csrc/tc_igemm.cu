@@ -2,14 +2,16 @@
 // in shared memory by TMA (no cluster multicast anywhere), zero-point terms, per-channel requantize,
 // bias, ReLU clamp and the residual tail applied in the epilogue straight out of TMEM.
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      : TMA producer (one elected lane): A box {bk, Wb, Hb, Nb} of an NHWC map / matrix,
 //                 B box {bk, BN} of the packed weights, ring of kStages shared-memory stages.
 //   warp 1      : allocates TMEM, issues tcgen05.mma (one elected lane), M = 128, N = BN, K = 32 per
 //                 instruction; accumulators are double-buffered in TMEM (2 x BN columns) so the
 //                 epilogue of tile i overlaps the main loop of tile i + 1.
-//   warps 2..5  : epilogue; warp w owns TMEM lanes 32*(w % 4) .. +31 (one output position per thread),
-//                 reads 32 columns per tcgen05.ld, applies the epilogue and stores 128-bit vectors.
+//   warps 2..9  : epilogue; warp w may read TMEM lanes 32*(w % 4) .. +31 (one output position per thread), two
+//                 warps per lane quarter split the 32-column chunks; each reads a chunk per tcgen05.ld (the next
+//                 chunk's read overlapping this chunk's arithmetic), applies the epilogue from per-warp cached
+//                 per-channel parameters and stores 128-bit vectors.
 //
 // Every mbarrier wait is bounded: after ~2 s without progress the waiting thread raises the CTA's
 // abort flag and the device status word, every role leaves its loop, the CTA waits a bounded time
@@ -190,16 +192,18 @@ struct TcConfig {
     static constexpr int kStageA = 128 * BK;
     static constexpr int kStageB = BN * BK;
     static constexpr int kStageBytes = kStageA + kStageB;
-    static constexpr int kStagesRaw = (196 * 1024) / kStageBytes;
+    static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
     // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
     static constexpr int kBarBytes = (2 * kStages + 4) * 8;
-    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kBarBytes + 16 /*tmem ptr + abort*/;
+    static constexpr int kParamOffset = ((kStages * kStageBytes + kBarBytes + 16 + 15) / 16) * 16;  // per-warp epilogue parameter caches
+    static constexpr int kParamBytes = 8 * (BN / 2) * 8;
+    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kParamOffset + kParamBytes;
 };
 
 template <int BN, int BK>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
     using Cfg = TcConfig<BN, BK>;
     constexpr int kStages = Cfg::kStages;
@@ -227,7 +231,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+            mbar_init(tempty_bar(a), 8);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -315,13 +319,24 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else {
         // ---------------- epilogue warps ----------------
-        // Warps are independent of one another here (no cross-warp barrier), so a warp that sees the
-        // abort flag can leave on its own; within a warp the decision is made uniform with a vote
-        // because tcgen05.ld is a warp-wide (.sync.aligned) instruction.
+        // Eight warps: warp w may touch TMEM lanes 32*(w % 4) .. +31 only, so two warps share each lane quarter and
+        // split the tile's 32-column chunks between them (even / odd).  Warps are independent of one another (no
+        // cross-warp barrier): a warp that sees the abort flag leaves on its own; within a warp the decision is made
+        // uniform with a vote because tcgen05.ld is a warp-wide (.sync.aligned) instruction.
+        constexpr int kChunks = BN / 32;            // 32-column chunks per tile
+        constexpr int kMine = kChunks / 2;          // chunks per warp
+        const int e = warp - 2;                     // 0..7
         const int quarter = warp & 3;
+        const int half = e >> 2;                    // which chunks (even / odd) this warp owns
         const int row = quarter * 32 + lane;
         const int w_l = row % p.Wb, h_l = (row / p.Wb) % p.Hb, n_l = row / (p.Wb * p.Hb);
         const bool requant = p.epi.mode == kEpiRequant;
+        // Per-warp cache of the per-column parameters of the chunks this warp owns: {mult, bias - col_scale*col_corr}.
+        float2* s_par = reinterpret_cast<float2*>(smem + Cfg::kParamOffset) + e * (BN / 2);
+        int cached_ct = -1;
+        const RequantParams rq = p.epi.rq;
+        const bool fast_u8 = requant && !rq.y_signed && p.col_mul == nullptr;
+        const int hi_q = rq.clamp_hi_q >= 0 ? rq.clamp_hi_q : 255;
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const int acc = it & 1;
@@ -338,26 +353,47 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int col0 = ct * BN;
             const uint32_t rowc = (row_ok && p.row_corr) ? (uint32_t)p.row_corr[pos] : 0u;
 
+            if (ct != cached_ct) {
+                __syncwarp();
+                for (int j = lane; j < BN / 2; j += 32) {
+                    const int c = col0 + ((j >> 5) * 2 + half) * 32 + (j & 31);
+                    float m = 0.f;
+                    uint32_t bz = 0u;
+                    if (c < p.cols) {
+                        if (requant) m = epi_mult(p.epi, c);
+                        if (requant && p.epi.bias) bz = (uint32_t)p.epi.bias[c];
+                        if (p.col_corr) bz -= (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];
+                    }
+                    s_par[j] = make_float2(m, __uint_as_float(bz));
+                }
+                __syncwarp();
+                cached_ct = ct;
+            }
+
             const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4);
             if (!__all_sync(0xffffffffu, got)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                uint32_t r[32];
-                __syncwarp();
-                tmem_ld_32x32b_x32(taddr + (uint32_t)(ch * 32), r);
+            uint32_t rbuf[2][32];
+            __syncwarp();
+            tmem_ld_32x32b_x32(taddr + (uint32_t)(half * 32), rbuf[0]);
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) {
+                uint32_t(&r)[32] = rbuf[i & 1];
                 tmem_ld_wait();
+                if (i + 1 < kMine) {  // next chunk's TMEM read overlaps this chunk's arithmetic
+                    __syncwarp();
+                    tmem_ld_32x32b_x32(taddr + (uint32_t)(((i + 1) * 2 + half) * 32), rbuf[(i + 1) & 1]);
+                }
+                const int ch = i * 2 + half;
                 const int cbase = col0 + ch * 32;
                 if (row_ok && cbase < p.cols) {
                     const bool full_chunk = cbase + 32 <= p.cols;
                     const int64_t o = pos * p.ldc + cbase;
-                    // Zero-point terms (int32 wrap-around): acc = raw - col_scale*col_corr[c] - col_mul[c]*row_corr[pos].
-                    if (p.col_corr) {
+                    const float2* par = s_par + i * 32;
+                    // acc = raw + (bias - col_scale*col_corr[c]) - col_mul[c]*row_corr[pos]   (int32 wrap-around)
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (full_chunk || cbase + j < p.cols) r[j] -= (uint32_t)p.col_scale * (uint32_t)__ldg(p.col_corr + cbase + j);
-                    }
+                    for (int j = 0; j < 32; ++j) r[j] += __float_as_uint(par[j].y);
                     if (p.col_mul) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
@@ -377,40 +413,44 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     } else {
                         uint8_t* yo = static_cast<uint8_t*>(p.y) + o;
                         const uint8_t* ro = p.epi.residual ? p.epi.residual + o : nullptr;
-                        if (full_chunk && p.vec_ok) {
-                            uint32_t resw[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-                            if (ro) {
+                        const bool vec = full_chunk && p.vec_ok;
+                        uint32_t resw[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+                        if (ro) {
+                            if (vec) {
                                 const uint4 r0 = reinterpret_cast<const uint4*>(ro)[0], r1 = reinterpret_cast<const uint4*>(ro)[1];
                                 resw[0] = r0.x; resw[1] = r0.y; resw[2] = r0.z; resw[3] = r0.w;
                                 resw[4] = r1.x; resw[5] = r1.y; resw[6] = r1.z; resw[7] = r1.w;
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (cbase + j < p.cols) resw[j >> 2] |= (uint32_t)ro[j] << (8 * (j & 3));
                             }
-                            uint32_t outw[8];
+                        }
+                        uint32_t outw[8];
 #pragma unroll
-                            for (int wv = 0; wv < 8; ++wv) {
-                                uint32_t o32 = 0u;
+                        for (int wv = 0; wv < 8; ++wv) {
+                            uint32_t o32 = 0u;
 #pragma unroll
-                                for (int b = 0; b < 4; ++b) {
-                                    const int j = wv * 4 + b, c = cbase + j;
-                                    const uint32_t bias = p.epi.bias ? (uint32_t)__ldg(p.epi.bias + c) : 0u;
-                                    int q = requant_one((int)(r[j] + bias), epi_mult(p.epi, c), p.epi.rq);
-                                    if (ro) q = residual_one(q, (int)((resw[wv] >> (8 * b)) & 0xffu), p.epi.rq);
-                                    o32 |= ((uint32_t)q & 0xffu) << (8 * b);
+                            for (int b = 0; b < 4; ++b) {
+                                const int j = wv * 4 + b;
+                                int q;
+                                if (fast_u8) {
+                                    q = min(requant_u8_fast((int)r[j], par[j].x, rq), hi_q);
+                                } else {
+                                    q = requant_one((int)r[j], par[j].x, rq);
                                 }
-                                outw[wv] = o32;
+                                if (ro) q = residual_one(q, (int)((resw[wv] >> (8 * b)) & 0xffu), rq);
+                                o32 |= ((uint32_t)q & 0xffu) << (8 * b);
                             }
+                            outw[wv] = o32;
+                        }
+                        if (vec) {
                             reinterpret_cast<uint4*>(yo)[0] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
                             reinterpret_cast<uint4*>(yo)[1] = make_uint4(outw[4], outw[5], outw[6], outw[7]);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int c = cbase + j;
-                                if (c < p.cols) {
-                                    const uint32_t bias = p.epi.bias ? (uint32_t)p.epi.bias[c] : 0u;
-                                    int q = requant_one((int)(r[j] + bias), epi_mult(p.epi, c), p.epi.rq);
-                                    if (ro) q = residual_one(q, (int)ro[j], p.epi.rq);
-                                    yo[j] = (uint8_t)q;
-                                }
-                            }
+                            for (int j = 0; j < 32; ++j)
+                                if (cbase + j < p.cols) yo[j] = (uint8_t)(outw[j >> 2] >> (8 * (j & 3)));
                         }
                     }
                 }
@@ -500,7 +540,7 @@ int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p
         rec.macs = g_cur_macs;
         CHXQ_CUDA(cudaEventRecord(rec.e0, s));
     }
-    tc_igemm_kernel<BN, BK><<<grid, 192, Cfg::kSmemBytes, s>>>(tmA, tmB, p);
+    tc_igemm_kernel<BN, BK><<<grid, 320, Cfg::kSmemBytes, s>>>(tmA, tmB, p);
     if (g_prof_on) {
         CHXQ_CUDA(cudaEventRecord(rec.e1, s));
         std::lock_guard<std::mutex> lock(g_prof_mu);

@@ -68,11 +68,14 @@ def _zp_scalar(zp, default_dtype=np.uint8):
         if zp.numel() != 1:
             raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "a Scalar zero point must have one element")
         return int(zp.item()), _qcode(zp, "zero point")
-    dt = np.asarray(zp).dtype
-    if dt == np.int8:
-        return int(zp), INT8
-    if dt == np.uint8:
-        return int(zp), UINT8
+    if isinstance(zp, (np.generic, np.ndarray)):
+        dt = np.asarray(zp).dtype
+        if dt == np.int8:
+            return int(zp), INT8
+        if dt == np.uint8:
+            return int(zp), UINT8
+        # runtime/ops/quantize.cc:19-25: the zero point's dtype is uint8 or int8, anything else CHECK-fails
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "a zero point must be uint8 or int8, got %s" % dt)
     # plain Python ints carry no dtype: the reference's default is uint8 (runtime/ops/quantize.cc:50-51)
     return int(zp), (UINT8 if default_dtype == np.uint8 else INT8)
 

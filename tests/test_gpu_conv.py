@@ -17,7 +17,7 @@ SIMT, TENSOR, AUTO = 1, 2, 0
 def _t(a, dev, cl=False):
     if a is None:
         return None
-    t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    t = torch.from_numpy(np.array(a)).to(dev)  # np.array keeps 0-d arrays 0-d
     return t.contiguous(memory_format=torch.channels_last) if cl else t
 
 
