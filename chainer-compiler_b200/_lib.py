@@ -48,7 +48,7 @@ class QConvParams(ctypes.Structure):
         ("y_scale", ctypes.c_float), ("y_zero_point", ctypes.c_int32), ("y_dtype", ctypes.c_int32),
         ("bias", ctypes.c_void_p), ("round_mode", ctypes.c_int32), ("clamp_hi_q", ctypes.c_int32),
         ("residual", ctypes.c_void_p), ("res_scale", ctypes.c_float), ("res_zero_point", ctypes.c_int32), ("res_relu", ctypes.c_int32),
-        ("out_scale", ctypes.c_float), ("out_zero_point", ctypes.c_int32),
+        ("out_scale", ctypes.c_float), ("out_zero_point", ctypes.c_int32), ("fold_scales", ctypes.c_int32),
     ]
 
 

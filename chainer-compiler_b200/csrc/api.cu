@@ -292,7 +292,7 @@ ConvWs conv_ws_layout(const chxq_conv_geom& g, const TcConvPlan& pl) {
     w.flag_off = off; off += 256;
     w.pack_total = off;
     const size_t rows = (size_t)g.N * g.Ho * g.Wo;
-    w.im2col_bytes = align_up(rows * (size_t)pl.k_total, 1024);
+    w.im2col_bytes = align_up(rows * (size_t)pl.a_pitch, 1024);
     w.rowsum_bytes = align_up(rows * 4, 256);
     return w;
 }
@@ -338,15 +338,15 @@ int conv_tc_run(
     int32_t* rowsum = nullptr;
     if (im2col) {
         uint8_t* A = scratch;
-        int rc = launch_im2col(x, g, pl.c_pitch, pl.k_total, x_zp & 0xff, A, s);
+        int rc = launch_im2col(x, g, pl.c_pitch, pl.a_pitch, x_zp & 0xff, A, s);
         if (rc != CHXQ_OK) return rc;
         if (!zw_zero) {
             rowsum = reinterpret_cast<int32_t*>(scratch + L.im2col_bytes);
-            rowsum_matrix_kernel<<<blocks_for(rows * 32), 256, 0, s>>>(A, x_signed, rows, pl.k_total, taps * g.C * x_zp, rowsum);
+            rowsum_matrix_kernel<<<blocks_for(rows * 32), 256, 0, s>>>(A, x_signed, rows, pl.a_pitch, taps * g.C * x_zp, rowsum);
             CHXQ_LAUNCH_CHECK();
         }
         if (rows >= (1ll << 31)) return set_error(CHXQ_ERR_UNSUPPORTED, "convolution: too many output positions");
-        p.a = A; p.C = pl.k_total; p.a_cs = pl.k_total; p.W = (int)rows; p.H = 1; p.N = 1;
+        p.a = A; p.C = pl.a_pitch; p.a_cs = pl.a_pitch; p.W = (int)rows; p.H = 1; p.N = 1;
         p.c_pad = pl.k_total; p.KH = 1; p.KW = 1; p.pad_top = 0; p.pad_left = 0;
         p.Wo = (int)rows; p.Ho = 1; p.No = 1; p.Wb = 128; p.Hb = 1; p.Nb = 1;
     } else {
@@ -449,6 +449,12 @@ int fill_requant(const char* op, const chxq_qconv_params* p, const chxq_conv_geo
     e->rq.out_scale = p->out_scale;
     e->rq.out_zp_f = (float)p->out_zero_point;
     e->rq.out_has_zp = p->out_zero_point != 0;
+    if (p->fold_scales) {
+        CHXQ_CHECK_ARG(p->y_dtype == CHXQ_UINT8, "%s: folded requantization needs a uint8 output", op);
+        e->rq.fold = 1;
+        e->rq.y_over_out = p->residual ? p->y_scale / p->out_scale : 0.f;
+        e->rq.res_over_out = p->residual ? p->res_scale / p->out_scale : 0.f;
+    }
     return CHXQ_OK;
 }
 

@@ -79,7 +79,8 @@ struct TcConvPlan {
     int path;
     int bk;
     int c_pitch;   // K index = tap * c_pitch + c
-    int k_total;   // packed row length (multiple of bk)
+    int k_total;   // packed weight row length (multiple of bk)
+    int a_pitch;   // row length of the explicit im2col matrix (multiple of 16; the K tail up to k_total is TMA zero fill)
     int Wb, Hb, Nb;
 };
 TcConvPlan plan_tc_conv(const chxq_conv_geom& g);

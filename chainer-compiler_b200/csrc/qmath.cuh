@@ -73,6 +73,11 @@ struct RequantParams {
     int res_relu;
     float out_scale, out_zp_f;
     int out_has_zp;
+    // Folded arithmetic (fold != 0): one multiplier per channel, (x_scale * w_scale[m]) / y_scale, instead of a multiply
+    // and a divide per element; the residual tail uses the pre-divided scales below.
+    int fold;
+    float y_over_out;    // y_scale / out_scale
+    float res_over_out;  // res_scale / out_scale
 };
 
 // acc (exact int32, bias already added) -> quantized output value.
@@ -86,6 +91,30 @@ __device__ __forceinline__ int requant_one(int acc, float mult, const RequantPar
 // requant_one for a uint8 output without the optional upper clamp (the caller applies it).
 __device__ __forceinline__ int requant_u8_fast(int acc, float mult, const RequantParams& p) {
     return quantize_one<false>(__fmul_rn((float)acc, mult), p.y_scale, p.y_zp_f, p.y_has_zp != 0, p.round_mode);
+}
+
+// Folded requantization of a uint8 output: t = float(acc) * m with m = (x_scale * w_scale[c]) / y_scale computed once per
+// channel; then the zero point, the rounding and the saturation exactly as quantize_one does them.
+__device__ __forceinline__ int requant_u8_fold(int acc, float m, const RequantParams& p) {
+    float t = __fmul_rn((float)acc, m);
+    if (p.round_mode != 0) return cvt_rne_sat_u8(__fadd_rn(rintf(t), p.y_zp_f));
+    if (p.y_has_zp) t = __fadd_rn(t, p.y_zp_f);
+    return cvt_floor_sat_u8(__fadd_rn(t, 0.5f));
+}
+
+// Folded residual tail: v = (q - y_zp) * (y_scale / out_scale) + (r - res_zp) * (res_scale / out_scale) with the second
+// product fused into the sum (one rounding), Relu, then zero point, rounding and saturation of the output.
+__device__ __forceinline__ int residual_fold(int q, int r, const RequantParams& p) {
+    float u = (float)q;
+    if (p.y_has_zp) u = __fsub_rn(u, p.y_zp_f);
+    u = __fmul_rn(u, p.y_over_out);
+    float w = (float)r;
+    if (p.res_has_zp) w = __fsub_rn(w, p.res_zp_f);
+    float v = __fmaf_rn(w, p.res_over_out, u);
+    if (p.res_relu) v = v > 0.f ? v : 0.f;
+    if (p.round_mode != 0) return cvt_rne_sat_u8(__fadd_rn(rintf(v), p.out_zp_f));
+    if (p.out_has_zp) v = __fadd_rn(v, p.out_zp_f);
+    return cvt_floor_sat_u8(__fadd_rn(v, 0.5f));
 }
 
 // DequantizeLinear(y), DequantizeLinear(r), Add, Relu, QuantizeLinear on one element.

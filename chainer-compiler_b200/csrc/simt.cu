@@ -207,6 +207,52 @@ __global__ void __launch_bounds__(256) im2col_kernel(
     }
 }
 
+// im2col of an NCHW map (small channel counts: the network stem).  One block per (n, ho): the KH input rows of every
+// channel are staged in shared memory (padding columns and rows filled with pad_byte), then the Wo matrix rows of this
+// output row -- contiguous in A -- are written with coalesced 128-bit stores, each byte gathered through a per-k offset table.
+__global__ void __launch_bounds__(256) im2col_nchw_rows_kernel(
+        const uint8_t* __restrict__ x, ConvDesc d, int a_pitch, int pad_byte, int wspan, uint8_t* __restrict__ a) {
+    extern __shared__ __align__(16) uint8_t sm[];
+    int16_t* off = reinterpret_cast<int16_t*>(sm);                 // [a_pitch] offset of column k inside the staged rows, -1 = zero
+    uint8_t* rows = sm + ((a_pitch * 2 + 15) & ~15);                // [C][KH][wspan]
+    const int n = blockIdx.x / d.Ho, ho = blockIdx.x % d.Ho;
+    const int K = d.KH * d.KW * d.C;
+    for (int k = threadIdx.x; k < a_pitch; k += blockDim.x) {
+        int o = -1;
+        if (k < K) {
+            const int tap = k / d.C, c = k % d.C;
+            const int kh = tap / d.KW, kw = tap % d.KW;
+            o = (c * d.KH + kh) * wspan + kw;
+        }
+        off[k] = (int16_t)o;
+    }
+    const int hi0 = ho * d.sh - d.pt;
+    for (int i = threadIdx.x; i < d.C * d.KH * wspan; i += blockDim.x) {
+        const int col = i % wspan;
+        const int r = i / wspan;
+        const int kh = r % d.KH, c = r / d.KH;
+        const int hi = hi0 + kh, wi = col - d.pl;
+        uint8_t v = (uint8_t)pad_byte;
+        if (hi >= 0 && hi < d.H && wi >= 0 && wi < d.W) v = x[(((int64_t)n * d.C + c) * d.H + hi) * d.W + wi];
+        rows[i] = v;
+    }
+    __syncthreads();
+    const int cpr = a_pitch / 16;
+    uint8_t* out = a + ((int64_t)n * d.Ho + ho) * d.Wo * a_pitch;
+    for (int idx = threadIdx.x; idx < d.Wo * cpr; idx += blockDim.x) {
+        const int wo = idx / cpr, j = idx - wo * cpr;
+        const int base = wo * d.sw;
+        uint32_t w4[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {
+            const int o = off[j * 16 + b];
+            const uint32_t v = o >= 0 ? rows[o + base] : 0u;
+            w4[b >> 2] |= v << (8 * (b & 3));
+        }
+        *reinterpret_cast<uint4*>(out + (int64_t)idx * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Glue kernels (NHWC u8 maps, 16 channels = one 128-bit word per thread where channels allow).
 // ---------------------------------------------------------------------------------------------
@@ -407,6 +453,17 @@ int launch_im2col(const void* x, const chxq_conv_geom& g, int c_pitch, int k_pad
     ConvDesc d = make_desc(g, 0, 0, 0);
     const int64_t total = (int64_t)g.N * g.Ho * g.Wo * (k_pad / 16);
     if (total == 0) return CHXQ_OK;
+    if (!d.x_nhwc && c_pitch == g.C && k_pad < 32768) {
+        // NCHW input with dense K: stage whole input rows per (n, ho).
+        const int wspan = (g.Wo - 1) * g.stride_w + g.KW;
+        const size_t smem = ((size_t)(k_pad * 2 + 15) & ~(size_t)15) + (size_t)g.C * g.KH * wspan;
+        if (smem <= 48 * 1024 && (int64_t)g.C * g.KH * wspan < 32768 && (int64_t)g.N * g.Ho < (1ll << 31)) {
+            im2col_nchw_rows_kernel<<<(unsigned)(g.N * g.Ho), 256, smem, s>>>(static_cast<const uint8_t*>(x), d, k_pad, pad_byte, wspan,
+                                                                          static_cast<uint8_t*>(a));
+            CHXQ_LAUNCH_CHECK();
+            return CHXQ_OK;
+        }
+    }
     im2col_kernel<<<grid_1d(total, 256, 32), 256, 0, s>>>(static_cast<const uint8_t*>(x), d, c_pitch, k_pad, pad_byte, static_cast<uint8_t*>(a));
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;

@@ -1,0 +1,513 @@
+// tcgen05 implicit-GEMM kernel for sm_100a (device code; see tc_igemm.cu for the host side): u8/s8 x u8/s8 -> s32 in
+// TMEM (kind::i8), operands staged in shared memory by TMA (no cluster multicast anywhere), zero-point terms,
+// per-channel requantize, bias, ReLU clamp and the residual tail applied in the epilogue straight out of TMEM.
+//
+// One persistent CTA per SM, 576 threads:
+//   warp 0      : TMA producer (one elected lane): A box {bk, Wb, Hb, Nb} of an NHWC map / matrix,
+//                 B box {bk, BN} of the packed weights, ring of kStages shared-memory stages.
+//   warp 1      : allocates TMEM, issues tcgen05.mma (one elected lane), M = 128, N = BN, K = 32 per
+//                 instruction; accumulators are double-buffered in TMEM (2 x BN columns) so the
+//                 epilogue of tile i overlaps the main loop of tile i + 1.
+//   warps 2..17 : epilogue; warp w may read TMEM lanes 32*(w % 4) .. +31 (one output position per thread), four
+//                 warps per lane quarter take every fourth 16-column chunk of the tile; per-channel parameters
+//                 come from a per-warp shared-memory cache, outputs leave as 128-bit stores.
+//
+// Every mbarrier wait is bounded: after ~2 s without progress the waiting thread raises the CTA's
+// abort flag and the device status word, every role leaves its loop, the CTA waits a bounded time
+// for copies in flight, frees its TMEM and returns.  Nothing traps.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.h"
+#include "kernels.h"
+#include "tc_launch.h"
+
+namespace chxq {
+namespace tc {
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+    return ok;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+// Bounded wait.  Returns false when the CTA is aborting (either this wait expired or another did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t it = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++it & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+            "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+            : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+            : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], kind::i8, issued by one thread.
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+            "}\n" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+}
+
+// Arrives on the mbarrier once every tcgen05 operation issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+              "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+              "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+              "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr)
+            : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are `bk` bytes long and
+// stored with the bk-byte swizzle (128B / 64B / 32B), 8-row groups packed back to back:
+//   bits  0-13 start address >> 4, 16-29 leading byte offset >> 4 (unused for swizzled K-major, 1),
+//   bits 32-45 stride byte offset >> 4 (distance between 8-row groups = 8 * bk),
+//   bits 46-47 descriptor version (1 on sm_100), bits 61-63 swizzle mode (2 = 128B, 4 = 64B, 6 = 32B).
+template <int BK>
+__device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {
+    constexpr uint64_t layout = BK == 128 ? 2ull : (BK == 64 ? 4ull : 6ull);
+    constexpr uint64_t sbo = (8ull * BK) >> 4;
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | (sbo << 32) | (1ull << 46) | (layout << 61);
+}
+
+
+template <int BN, int BK>
+struct TcConfig {
+    static constexpr int kStageA = 128 * BK;
+    static constexpr int kStageB = BN * BK;
+    static constexpr int kStageBytes = kStageA + kStageB;
+    static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+    // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+    static constexpr int kBarBytes = (2 * kStages + 4) * 8;
+    static constexpr int kParamOffset = ((kStages * kStageBytes + kBarBytes + 16 + 15) / 16) * 16;  // per-warp epilogue parameter caches
+    static constexpr int kParamBytes = 16 * (BN / 2) * 4;  // 16 warps x (BN/4 multipliers + BN/4 additive terms)
+    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kParamOffset + kParamBytes;
+};
+
+template <int BN, int BK, int EPI>
+__global__ void __launch_bounds__(576, 1)
+tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+    using Cfg = TcConfig<BN, BK>;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + kStages * Cfg::kStageA;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 16);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_ptr_smem), Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    const int pos_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
+    const int total_tiles = pos_tiles * p.col_tiles;
+    const int taps = p.KH * p.KW;
+    const int num_kb = taps * p.c_chunks;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int ct = tile % p.col_tiles;
+                int pt = tile / p.col_tiles;
+                const int tw = pt % p.tiles_w;
+                pt /= p.tiles_w;
+                const int th = pt % p.tiles_h;
+                const int tn = pt / p.tiles_h;
+                const int w0 = tw * p.Wb - p.pad_left, h0 = th * p.Hb - p.pad_top, n0 = tn * p.Nb;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
+                    const int kh = tap / p.KW, kw = tap - kh * p.KW;
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+                    tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA), &tmA, full_bar(stage), cc * BK, w0 + kw, h0 + kh, n0);
+                    tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), tap * p.c_pad + cc * BK, ct * BN);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kStageA);
+                    const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kStageB);
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k) {
+                        umma_i8(tmem_d, make_kmajor_desc<BK>(a_addr + k * 32), make_kmajor_desc<BK>(b_addr + k * 32), p.idesc,
+                                (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        // Sixteen warps: warp w may touch TMEM lanes 32*(w % 4) .. +31 only, so four warps share each lane quarter and
+        // take every fourth 16-column chunk of the tile.  Warps are independent of one another (no cross-warp barrier):
+        // a warp that sees the abort flag leaves on its own; within a warp the decision is made uniform with a vote
+        // because tcgen05.ld is warp-wide (.sync.aligned).
+        constexpr int kMine = BN / 64;              // 16-column chunks per warp per tile
+        const int e = warp - 2;                     // 0..15
+        const int quarter = warp & 3;
+        const int sub = e >> 2;                     // this warp owns the chunks with (chunk & 3) == sub
+        const int row = quarter * 32 + lane;
+        const int w_l = row % p.Wb, h_l = (row / p.Wb) % p.Hb, n_l = row / (p.Wb * p.Hb);
+        // Per-warp cache of the per-column parameters of this warp's chunks: multiplier and additive int32 term.
+        float* s_mult = reinterpret_cast<float*>(smem + Cfg::kParamOffset) + e * (BN / 2);  // [BN/4] floats then [BN/4] ints
+        uint32_t* s_add = reinterpret_cast<uint32_t*>(s_mult + BN / 4);
+        int cached_ct = -1;
+        const RequantParams rq = p.epi.rq;
+        const int hi_q = rq.clamp_hi_q >= 0 ? rq.clamp_hi_q : 255;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const int acc = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const int ct = tile % p.col_tiles;
+            int pt = tile / p.col_tiles;
+            const int tw = pt % p.tiles_w;
+            pt /= p.tiles_w;
+            const int th = pt % p.tiles_h;
+            const int tn = pt / p.tiles_h;
+            const int wo = tw * p.Wb + w_l, ho = th * p.Hb + h_l, no = tn * p.Nb + n_l;
+            const bool row_ok = wo < p.Wo && ho < p.Ho && no < p.No;
+            const int64_t pos = ((int64_t)no * p.Ho + ho) * p.Wo + wo;
+            const int col0 = ct * BN;
+
+            if (ct != cached_ct) {
+                __syncwarp();
+                for (int j = lane; j < BN / 4; j += 32) {
+                    const int c = col0 + ((j >> 4) * 4 + sub) * 16 + (j & 15);
+                    float m = 0.f;
+                    uint32_t bz = 0u;
+                    if (c < p.cols) {
+                        if (EPI != kEpiKInt32) {
+                            m = epi_mult(p.epi, c);
+                            if (EPI == kEpiKU8Fold || (EPI == kEpiKGeneric && rq.fold)) m = __fdiv_rn(m, rq.y_scale);  // folded: mult / y_scale
+                            if (p.epi.bias) bz = (uint32_t)p.epi.bias[c];
+                        }
+                        if (p.col_corr) bz -= (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];
+                    }
+                    s_mult[j] = m;
+                    s_add[j] = bz;
+                }
+                __syncwarp();
+                cached_ct = ct;
+            }
+
+            const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4);
+            if (!__all_sync(0xffffffffu, got)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int i = 0; i < kMine; ++i) {
+                uint32_t r[16];
+                const int ch = i * 4 + sub;
+                __syncwarp();
+                tmem_ld_32x32b_x16(taddr + (uint32_t)(ch * 16), r);
+                tmem_ld_wait();
+                const int cbase = col0 + ch * 16;
+                if (!(row_ok && cbase < p.cols)) continue;
+                const bool full_chunk = cbase + 16 <= p.cols;
+                const int64_t o = pos * p.ldc + cbase;
+                const float4* pm = reinterpret_cast<const float4*>(s_mult + i * 16);
+                const uint4* pa = reinterpret_cast<const uint4*>(s_add + i * 16);
+                // acc = raw + (bias - col_scale * col_corr[c])   (int32 wrap-around)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 a4 = pa[j];
+                    r[4 * j] += a4.x; r[4 * j + 1] += a4.y; r[4 * j + 2] += a4.z; r[4 * j + 3] += a4.w;
+                }
+                if (EPI == kEpiKInt32 || EPI == kEpiKGeneric) {
+                    if (p.col_mul) {  // weight zero-point term: - zw[c] * sum over the receptive field of (x - zx)
+                        const uint32_t rowc = p.row_corr ? (uint32_t)p.row_corr[pos] : 0u;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (full_chunk || cbase + j < p.cols) r[j] -= (uint32_t)__ldg(p.col_mul + cbase + j) * rowc;
+                    }
+                }
+                if (EPI == kEpiKInt32) {
+                    int32_t* yo = static_cast<int32_t*>(p.y) + o;
+                    if (full_chunk && p.vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            reinterpret_cast<uint4*>(yo)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (cbase + j < p.cols) yo[j] = (int32_t)r[j];
+                    }
+                } else {
+                    uint8_t* yo = static_cast<uint8_t*>(p.y) + o;
+                    const uint8_t* ro = p.epi.residual ? p.epi.residual + o : nullptr;
+                    const bool vec = full_chunk && p.vec_ok;
+                    uint32_t resw[4] = {0u, 0u, 0u, 0u};
+                    if (ro) {
+                        if (vec) {
+                            const uint4 r0 = *reinterpret_cast<const uint4*>(ro);
+                            resw[0] = r0.x; resw[1] = r0.y; resw[2] = r0.z; resw[3] = r0.w;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (cbase + j < p.cols) resw[j >> 2] |= (uint32_t)ro[j] << (8 * (j & 3));
+                        }
+                    }
+                    uint32_t outw[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 m4 = pm[j];
+                        const float mm[4] = {m4.x, m4.y, m4.z, m4.w};
+                        uint32_t o32 = 0u;
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            const int a = (int)r[4 * j + b];
+                            const int rb = (int)((resw[j] >> (8 * b)) & 0xffu);
+                            int q;
+                            if (EPI == kEpiKU8) {
+                                q = min(requant_u8_fast(a, mm[b], rq), hi_q);
+                                if (ro) q = residual_one(q, rb, rq);  // DequantizeLinear x2, Add, Relu, QuantizeLinear
+                            } else if (EPI == kEpiKU8Fold) {
+                                q = min(requant_u8_fold(a, mm[b], rq), hi_q);
+                                if (ro) q = residual_fold(q, rb, rq);
+                            } else if (rq.fold) {
+                                q = min(requant_u8_fold(a, mm[b], rq), hi_q);
+                                if (ro) q = residual_fold(q, rb, rq);
+                            } else {
+                                q = requant_one(a, mm[b], rq);
+                                if (ro) q = residual_one(q, rb, rq);
+                            }
+                            o32 |= ((uint32_t)q & 0xffu) << (8 * b);
+                        }
+                        outw[j] = o32;
+                    }
+                    if (vec) {
+                        *reinterpret_cast<uint4*>(yo) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (cbase + j < p.cols) yo[j] = (uint8_t)(outw[j >> 2] >> (8 * (j & 3)));
+                    }
+                }
+            }
+            // Hand the accumulator buffer back to the MMA warp.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // Bounded grace period for copies and MMAs still in flight before shared memory and TMEM go away.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// Launches the instantiation for (bn, BK, epi).  Called from the per-BK translation units.
+template <int BN, int BK, int EPI>
+int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s) {
+    using Cfg = TcConfig<BN, BK>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CHXQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm_kernel<BN, BK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    tc_igemm_kernel<BN, BK, EPI><<<grid, 576, Cfg::kSmemBytes, s>>>(tmA, tmB, p);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+template <int BK>
+int launch_bk(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s) {
+    if (epi == kEpiKGeneric) return launch_one<128, BK, kEpiKGeneric>(tmA, tmB, p, grid, s);  // rare path: one tile shape
+    switch (bn * 4 + epi) {
+        case 64 * 4 + kEpiKInt32: return launch_one<64, BK, kEpiKInt32>(tmA, tmB, p, grid, s);
+        case 128 * 4 + kEpiKInt32: return launch_one<128, BK, kEpiKInt32>(tmA, tmB, p, grid, s);
+        case 256 * 4 + kEpiKInt32: return launch_one<256, BK, kEpiKInt32>(tmA, tmB, p, grid, s);
+        case 64 * 4 + kEpiKU8: return launch_one<64, BK, kEpiKU8>(tmA, tmB, p, grid, s);
+        case 128 * 4 + kEpiKU8: return launch_one<128, BK, kEpiKU8>(tmA, tmB, p, grid, s);
+        case 256 * 4 + kEpiKU8: return launch_one<256, BK, kEpiKU8>(tmA, tmB, p, grid, s);
+        case 64 * 4 + kEpiKU8Fold: return launch_one<64, BK, kEpiKU8Fold>(tmA, tmB, p, grid, s);
+        case 128 * 4 + kEpiKU8Fold: return launch_one<128, BK, kEpiKU8Fold>(tmA, tmB, p, grid, s);
+        case 256 * 4 + kEpiKU8Fold: return launch_one<256, BK, kEpiKU8Fold>(tmA, tmB, p, grid, s);
+    }
+    return set_error(CHXQ_ERR_INVALID_ARGUMENT, "tensor-core kernel: no instantiation for bn %d, epilogue %d", bn, epi);
+}
+
+}  // namespace tc
+}  // namespace chxq

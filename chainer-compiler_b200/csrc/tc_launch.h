@@ -1,0 +1,45 @@
+// Interface between the host side of the tensor-core kernel (tc_igemm.cu) and its per-K-tile translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "epilogue.cuh"
+
+namespace chxq {
+namespace tc {
+
+struct TcParams {
+    int Wb, Hb, Nb;
+    int tiles_w, tiles_h, tiles_n;  // position tiles
+    int col_tiles;                   // ceil(cols / BN)
+    int Wo, Ho, No;
+    int KH, KW, pad_top, pad_left;
+    int c_chunks;  // c_pad / BK
+    int c_pad;
+    int cols;
+    int64_t ldc;
+    uint32_t idesc;
+    const int32_t* col_corr;
+    int col_scale;
+    const int32_t* col_mul;
+    const int32_t* row_corr;
+    EpiArgs epi;
+    void* y;
+    int* status;
+    int vec_ok;  // rows of y (and of the residual) start on 16-byte boundaries
+};
+
+// Epilogue families (template parameter EPI): dead paths are compiled out, which keeps the unrolled per-element
+// code of each kernel small enough for the instruction cache.
+constexpr int kEpiKInt32 = 0;    // store the int32 accumulator
+constexpr int kEpiKU8 = 1;       // requantize to uint8, optional residual tail
+constexpr int kEpiKGeneric = 2;  // int8 output and/or a weight zero-point term: general requantization
+constexpr int kEpiKU8Fold = 3;   // uint8 with one folded multiplier per channel (RequantParams::fold)
+
+int launch_tc_bk32(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s);
+int launch_tc_bk64(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s);
+int launch_tc_bk128(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s);
+
+}  // namespace tc
+}  // namespace chxq

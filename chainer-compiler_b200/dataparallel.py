@@ -73,8 +73,8 @@ class InferenceEngine:
     """One rank's share of a data-parallel inference job: a calibrated network captured in a CUDA graph, a pinned host
     staging buffer for inputs and one for the gathered logits."""
 
-    def __init__(self, net, world=1):
-        self.net, self.world = net, world
+    def __init__(self, net, world=1, fold=False):
+        self.net, self.world, self.fold = net, world, fold
         dev = net.device
         self.x_dev = torch.empty((net.batch, 3, net.image, net.image), dtype=torch.float32, device=dev)
         self.graph = None
@@ -85,7 +85,7 @@ class InferenceEngine:
     def prepare(self, calib_x):
         self.x_dev.copy_(calib_x)
         self.net.calibrate(self.x_dev)
-        self.graph, self.logits = self.net.capture(self.x_dev)
+        self.graph, self.logits = self.net.capture(self.x_dev, fold=self.fold)
         n, c = self.logits.shape
         self.all_logits = torch.empty((n * self.world, c), dtype=torch.float32, device=self.net.device)
         self.host_logits = torch.empty((n * self.world, c), dtype=torch.float32).pin_memory()

@@ -163,10 +163,10 @@ class ResNet50Int8:
             c.y_zp = int(np.clip(np.rint(-lo / float(c.y_scale)), 0, 255))
         return self._run_conv(c, x)
 
-    def _run_conv(self, c, x, residual=None, res_scale=1.0, res_zp=0, out_scale=1.0, out=None):
+    def _run_conv(self, c, x, residual=None, res_scale=1.0, res_zp=0, out_scale=1.0, out=None, fold=False):
         return ops.QLinearConvPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
                                      b=c.dev["bias"], residual=residual, res_scale=res_scale, res_zero_point=res_zp, res_relu=True,
-                                     out_scale=out_scale, out_zero_point=0, out=out)
+                                     out_scale=out_scale, out_zero_point=0, out=out, fold_scales=fold)
 
     def calibrate(self, x):
         """Uploads and packs the weights, then walks the network once over the fp32 NCHW batch x to fix every scale."""
@@ -205,25 +205,27 @@ class ResNet50Int8:
         torch.cuda.synchronize(self.device)
 
     # ---- inference ----------------------------------------------------------------------------------
-    def forward(self, x, fused=True, taps=None):
-        """fp32 NCHW batch -> fp32 logits [N, classes].  taps (a dict) receives intermediate uint8 maps when given."""
+    def forward(self, x, fused=True, taps=None, fold=False):
+        """fp32 NCHW batch -> fp32 logits [N, classes].  taps (a dict) receives intermediate uint8 maps when given.
+        fold=True requantizes every convolution with one multiplier per channel (QLinearConv's fold_scales)."""
         assert self.calibrated
+        assert fused or not fold, "the folded residual tail exists only inside the convolution epilogue"
         xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
-        h = self._run_conv(self.stem, xq)
+        h = self._run_conv(self.stem, xq, fold=fold)
         if taps is not None:
             taps["stem"] = h
         h = ops.MaxPoolU8(h, 3, 2, 0, cover_all=True)
         h_scale = self.stem.y_scale
         for i, b in enumerate(self.blocks):
-            h1 = self._run_conv(b["conv1"], h)
-            h2 = self._run_conv(b["conv2"], h1)
+            h1 = self._run_conv(b["conv1"], h, fold=fold)
+            h2 = self._run_conv(b["conv2"], h1, fold=fold)
             if b["proj"] is not None:
-                sc = self._run_conv(b["proj"], h)
+                sc = self._run_conv(b["proj"], h, fold=fold)
             else:
                 sc = h
             sc_scale, sc_zp = b["res"]
             if fused:
-                h = self._run_conv(b["conv3"], h2, residual=sc, res_scale=sc_scale, res_zp=sc_zp, out_scale=b["out_scale"])
+                h = self._run_conv(b["conv3"], h2, residual=sc, res_scale=sc_scale, res_zp=sc_zp, out_scale=b["out_scale"], fold=fold)
             else:
                 h3 = self._run_conv(b["conv3"], h2)
                 h = ops.QAddU8(h3, b["conv3"].y_scale, b["conv3"].y_zp, sc, sc_scale, sc_zp, b["out_scale"], 0, relu=True)
@@ -236,13 +238,13 @@ class ResNet50Int8:
             taps["pooled"] = pooled
         return logits
 
-    def capture(self, x_static):
+    def capture(self, x_static, fold=False):
         """Captures forward(x_static) into a CUDA graph; returns (graph, logits).  Replaying needs no host work per layer."""
-        self.forward(x_static)  # warm-up: JIT-free, but sizes the workspace and sets kernel attributes outside the capture
+        self.forward(x_static, fold=fold)  # warm-up: sizes the workspace and sets kernel attributes outside the capture
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            logits = self.forward(x_static)
+            logits = self.forward(x_static, fold=fold)
         return g, logits
 
     def export_numpy(self):

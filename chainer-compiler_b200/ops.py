@@ -222,8 +222,9 @@ def ConvInteger(x, w, x_zero_point=None, w_zero_point=None, strides=(), pads=(),
 
 
 def _qconv_params(x, w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, residual, res_scale,
-                  res_zero_point, res_relu, out_scale, out_zero_point, keep):
+                  res_zero_point, res_relu, out_scale, out_zero_point, keep, fold_scales=False):
     p = QConvParams()
+    p.fold_scales = int(bool(fold_scales))
     zx, _ = _zp_scalar(x_zero_point)
     zy, cy = _zp_scalar(y_zero_point)
     if not isinstance(w_scale, torch.Tensor):
@@ -262,18 +263,19 @@ def _qconv_params(x, w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y
 
 def QLinearConv(x, x_scale, x_zero_point, w, w_scale, w_zero_point, y_scale, y_zero_point, b=None, strides=(), pads=(), group=1,
                 auto_pad="", round_mode=ROUND_REF, path=PATH_AUTO, clamp_hi_q=None, residual=None, res_scale=1.0, res_zero_point=0,
-                res_relu=True, out_scale=1.0, out_zero_point=0):
+                res_relu=True, out_scale=1.0, out_zero_point=0, fold_scales=False):
     """runtime/chxvm_defs.py:457-461; body runtime/ops/quantize.cc:62-94.
 
     The keyword arguments after ``auto_pad`` have no counterpart in the reference: ``clamp_hi_q`` folds a
     ReLU6 into the output range, ``residual`` (+ scales) fuses the DequantizeLinear, DequantizeLinear, Add,
-    Relu, QuantizeLinear nodes that follow the convolution of a residual block into the epilogue.
+    Relu, QuantizeLinear nodes that follow the convolution of a residual block into the epilogue,
+    ``fold_scales`` requantizes with one multiplier per channel instead of a multiply and a divide.
     """
     _require_cuda(x, w)
     g = conv_geometry(x, w, strides, pads, group, auto_pad)
     keep = []
     p, cy = _qconv_params(x, w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, residual,
-                          res_scale, res_zero_point, res_relu, out_scale, out_zero_point, keep)
+                          res_scale, res_zero_point, res_relu, out_scale, out_zero_point, keep, fold_scales)
     x, y = _conv_io(x, g, torch.uint8 if cy == UINT8 else torch.int8)
     if residual is not None:
         if residual.shape != y.shape or residual.dtype != torch.uint8 or _is_channels_last(residual) != (g.y_layout == NHWC):
@@ -312,7 +314,7 @@ class PackedConv:
 
 def QLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b=None, round_mode=ROUND_REF,
                       clamp_hi_q=None, residual=None, res_scale=1.0, res_zero_point=0, res_relu=True, out_scale=1.0, out_zero_point=0,
-                      out=None):
+                      out=None, fold_scales=False):
     """QLinearConv with weights packed by PackedConv; x must be a channels_last map of the packed geometry."""
     _require_cuda(x)
     g = packed.g
@@ -321,7 +323,7 @@ def QLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y
         raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConvPacked: x does not match the packed geometry / layout")
     keep = []
     p, cy = _qconv_params(x, packed.w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, residual,
-                          res_scale, res_zero_point, res_relu, out_scale, out_zero_point, keep)
+                          res_scale, res_zero_point, res_relu, out_scale, out_zero_point, keep, fold_scales)
     y = out if out is not None else torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.uint8 if cy == UINT8 else torch.int8, device=x.device,
                                                  memory_format=torch.channels_last)
     if not packed.eligible:

@@ -166,6 +166,11 @@ typedef struct chxq_qconv_params {
     int32_t res_relu;
     float out_scale;
     int32_t out_zero_point;
+    int32_t fold_scales;      /* 0: multiply by x_scale*w_scale[m], then divide by y_scale (the reference's operation order).
+                                 1: one multiplier per channel, (x_scale*w_scale[m])/y_scale, and a residual tail on the
+                                 pre-divided scales y_scale/out_scale, res_scale/out_scale: fewer instructions per output
+                                 byte, at most one step from the other form where a rounding boundary is crossed.
+                                 uint8 outputs with zero weight zero points only. */
 } chxq_qconv_params;
 
 int chxq_qlinear_conv(const void* x, const void* w, const chxq_conv_geom* g, const chxq_qconv_params* p, void* y, void* workspace,

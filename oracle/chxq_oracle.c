@@ -326,14 +326,39 @@ void orc_qlinear_conv(
  * agrees with orc_qlinear_conv except where fp32 accumulation error crosses a rounding
  * boundary.  acc: [rows, M] (channel is the LAST axis) or, when chan_stride > 1, NCHW with
  * chan_stride = Ho*Wo: channel of element i = (i / chan_stride) % M. */
+/* fold != 0 is the library's optional single-multiplier form (uint8 outputs): m = (x_scale * w_scale[c]) / y_scale once per
+ * channel, t = float(acc) * m, then zero point, rounding and saturation as quantize_one.  It has no counterpart in the
+ * reference; it is restated here so that the kernels that implement it can be checked bit for bit. */
+static inline int quantize_prescaled_u8(float t, int zp, int round_mode) {
+    if (round_mode == ORC_ROUND_RNE) {
+        float r = nearbyintf(t) + (float)zp;
+        r = fminf(r, 255.f);
+        r = fmaxf(0.f, r);
+        return (int)r;
+    }
+    if (zp != 0) t = t + (float)zp;
+    t = t + 0.5f;
+    t = floorf(t);
+    t = fminf(t, 255.f);
+    t = fmaxf(0.f, t);
+    return (int)t;
+}
+
 void orc_requantize(
         const int32_t* acc, int64_t n, int64_t M, int64_t chan_stride, float x_scale, const float* w_scale, int64_t w_params_len,
-        const int32_t* bias, float y_scale, int y_zp, int y_signed, int round_mode, int clamp_hi_q, void* y) {
+        const int32_t* bias, float y_scale, int y_zp, int y_signed, int round_mode, int clamp_hi_q, int fold, void* y) {
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) {
         const int64_t m = (i / chan_stride) % M;
         const float mult = x_scale * (w_params_len == 1 ? w_scale[0] : w_scale[m]);
         const int32_t a = (int32_t)((uint32_t)acc[i] + (uint32_t)(bias ? bias[m] : 0));
+        if (fold) {
+            const float mm = mult / y_scale;
+            int q = quantize_prescaled_u8((float)a * mm, y_zp, round_mode);
+            if (clamp_hi_q >= 0 && q > clamp_hi_q) q = clamp_hi_q;
+            ((uint8_t*)y)[i] = (uint8_t)q;
+            continue;
+        }
         const float yf = (float)a * mult;
         int q = quantize_one(yf, y_scale, y_zp, y_signed, round_mode);
         if (clamp_hi_q >= 0 && q > clamp_hi_q) q = clamp_hi_q;
@@ -563,6 +588,25 @@ void orc_linear_f32(const float* x, const float* w, const float* b, int64_t N, i
             for (int64_t k = 0; k < K; ++k) acc = acc + x[n * K + k] * w[o * K + k];
             y[n * O + o] = acc + (b ? b[o] : 0.f);
         }
+}
+
+/* The library's folded residual tail (see orc_requantize, fold): v = (a - a_zp) * (a_scale / y_scale) fused-multiply-added
+ * with (b - b_zp) * (b_scale / y_scale), Relu, then zero point, rounding, saturation. */
+void orc_qadd_relu_fold(
+        const uint8_t* a, float a_scale, int a_zp, const uint8_t* b, float b_scale, int b_zp, int64_t n, float y_scale, int y_zp, int relu,
+        int round_mode, uint8_t* y) {
+    const float ka = a_scale / y_scale, kb = b_scale / y_scale;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        float u = (float)a[i];
+        if (a_zp != 0) u = u - (float)a_zp;
+        u = u * ka;
+        float w = (float)b[i];
+        if (b_zp != 0) w = w - (float)b_zp;
+        float v = fmaf(w, kb, u);
+        if (relu) v = v > 0.f ? v : 0.f;
+        y[i] = (uint8_t)quantize_prescaled_u8(v, y_zp, round_mode);
+    }
 }
 
 /* Residual join of two quantized maps as the reference graph runs it:

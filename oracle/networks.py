@@ -5,6 +5,7 @@ mode="emulate": every QLinearConv runs as the reference does (runtime/ops/quanti
 quantize) -- this is the reference's CPU path and what the bench times as the CPU baseline.
 mode="exact": every QLinearConv requantizes the exact int32 accumulator -- the arithmetic of the CUDA kernels, which the
 GPU results must match bit for bit.
+mode="fold": as "exact" with the library's optional single-multiplier requantization and folded residual tail.
 """
 import numpy as np
 
@@ -17,7 +18,7 @@ def _qconv(c, x, mode):
         return orc.qlinear_conv(x, c["x_scale"], 0, c["w"], c["w_scale"], wz, c["y_scale"], c["y_zp"], b=c["bias"],
                                 strides=(c["stride"], c["stride"]), pads=(c["pad"], c["pad"]))
     acc = orc.conv_integer(x, c["w"], 0, wz, strides=(c["stride"], c["stride"]), pads=(c["pad"], c["pad"]))
-    return orc.requantize(acc, c["x_scale"], c["w_scale"], c["y_scale"], c["y_zp"], bias=c["bias"], channel_axis=1)
+    return orc.requantize(acc, c["x_scale"], c["w_scale"], c["y_scale"], c["y_zp"], bias=c["bias"], channel_axis=1, fold=(mode == "fold"))
 
 
 def resnet50_forward(params, x, mode="exact", taps=None):
@@ -34,7 +35,7 @@ def resnet50_forward(params, x, mode="exact", taps=None):
         h3 = _qconv(b["conv3"], h2, mode)
         sc = _qconv(b["proj"], h, mode) if b["proj"] is not None else h
         sc_scale, sc_zp = b["res"]
-        h = orc.qadd_relu(h3, b["conv3"]["y_scale"], b["conv3"]["y_zp"], sc, sc_scale, sc_zp, b["out_scale"], 0, relu=True)
+        h = orc.qadd_relu(h3, b["conv3"]["y_scale"], b["conv3"]["y_zp"], sc, sc_scale, sc_zp, b["out_scale"], 0, relu=True, fold=(mode == "fold"))
         h_scale = b["out_scale"]
         if taps is not None:
             taps["block%d" % i] = h

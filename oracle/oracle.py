@@ -177,7 +177,7 @@ def qlinear_conv(x, x_scale, x_zero_point, w, w_scale, w_zero_point, y_scale, y_
 
 
 def requantize(acc, x_scale, w_scale, y_scale, y_zero_point, bias=None, channel_axis=-1, y_dtype=np.uint8, round_mode=ROUND_REF,
-               clamp_hi_q=-1):
+               clamp_hi_q=-1, fold=False):
     """Integer-domain requantization of an exact int32 accumulator (see orc_requantize)."""
     acc = _c(acc, np.int32)
     axis = channel_axis % acc.ndim
@@ -190,7 +190,7 @@ def requantize(acc, x_scale, w_scale, y_scale, y_zero_point, bias=None, channel_
     b = None if bias is None else _c(bias, np.int32)
     lib().orc_requantize(_p(acc), _i64(acc.size), _i64(M), _i64(chan_stride), _f(x_scale), _p(ws), _i64(ws.size),
                          None if b is None else _p(b), _f(y_scale), ctypes.c_int(int(y_zero_point)), ctypes.c_int(int(y_dtype == np.int8)),
-                         ctypes.c_int(round_mode), ctypes.c_int(int(clamp_hi_q)), _p(y))
+                         ctypes.c_int(round_mode), ctypes.c_int(int(clamp_hi_q)), ctypes.c_int(int(fold)), _p(y))
     return y
 
 
@@ -301,9 +301,10 @@ def linear_f32(x, w, b=None):
     return y
 
 
-def qadd_relu(a, a_scale, a_zp, b, b_scale, b_zp, y_scale, y_zp=0, relu=True, round_mode=ROUND_REF):
+def qadd_relu(a, a_scale, a_zp, b, b_scale, b_zp, y_scale, y_zp=0, relu=True, round_mode=ROUND_REF, fold=False):
     a, b = _c(a, np.uint8), _c(b, np.uint8)
     y = np.empty(a.shape, np.uint8)
-    lib().orc_qadd_relu(_p(a), _f(a_scale), ctypes.c_int(int(a_zp)), _p(b), _f(b_scale), ctypes.c_int(int(b_zp)), _i64(a.size), _f(y_scale),
+    fn = lib().orc_qadd_relu_fold if fold else lib().orc_qadd_relu
+    fn(_p(a), _f(a_scale), ctypes.c_int(int(a_zp)), _p(b), _f(b_scale), ctypes.c_int(int(b_zp)), _i64(a.size), _f(y_scale),
                         ctypes.c_int(int(y_zp)), ctypes.c_int(int(relu)), ctypes.c_int(round_mode), _p(y))
     return y

@@ -240,3 +240,38 @@ def test_conv_full_size_layer_properties(ops, dev):
     assert torch.equal(y1[:2], ref)
     xs = x[254:].contiguous(memory_format=torch.channels_last)
     assert torch.equal(y1[254:], ops.ConvInteger(xs, w1, None, None, (1, 1), (1, 1), path=SIMT))
+
+
+@pytest.mark.parametrize("path,cl", [(SIMT, False), (TENSOR, True)])
+@pytest.mark.parametrize("N,C,H,W,M,k,stride,pad", [TC_CASES[2], TC_CASES[6], TC_CASES[8]])
+def test_qlinear_conv_folded_scales(ops, orc, dev, path, cl, N, C, H, W, M, k, stride, pad):
+    """fold_scales: one multiplier per channel.  Bit-exact against the oracle's restatement of that arithmetic; at most one
+    step from both the reference-order kernel and the fp32-emulating chain, with the mismatch counts printed."""
+    rng = np.random.default_rng(M + 3 * k)
+    x = _rand(rng, (N, C, H, W), np.uint8)
+    w = _rand(rng, (M, C, k, k), np.int8, -127, 127)
+    ws = rng.uniform(0.0005, 0.002, M).astype(np.float32)
+    wz = np.zeros(M, np.int8)
+    bias = _rand(rng, M, np.int32, -3000, 3000)
+    r = _rand(rng, (N, M, (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1), np.uint8)
+    sx, sy = 0.02, 0.09
+    for zy, mode in ((0, 0), (17, 1), (131, 0)):
+        args = (_t(x, dev, cl), sx, np.uint8(0), _t(w, dev), _t(ws, dev), _t(wz, dev), sy, np.uint8(zy), _t(bias, dev), (stride, stride), (pad, pad))
+        y = ops.QLinearConv(*args, round_mode=mode, path=path, fold_scales=True).cpu().numpy()
+        y_ref_order = ops.QLinearConv(*args, round_mode=mode, path=path).cpu().numpy()
+        acc = orc.conv_integer(x, w, 0, wz, (stride, stride), (pad, pad))
+        want = orc.requantize(acc, sx, ws, sy, zy, bias=bias, channel_axis=1, round_mode=mode, fold=True)
+        assert np.array_equal(y, want)
+        emul = orc.qlinear_conv(x, sx, 0, w, ws, wz, sy, zy, b=bias, strides=(stride, stride), pads=(pad, pad), round_mode=mode)
+        m1, c1, tot = lsb_report(y, y_ref_order)
+        m2, c2, _ = lsb_report(y, emul)
+        print("folded vs reference-order kernel: %d of %d differ; vs fp32-emulating chain: %d differ" % (c1, tot, c2))
+        assert m1 <= 1 and m2 <= 1
+        # folded residual tail
+        yr = ops.QLinearConv(*args, round_mode=mode, path=path, fold_scales=True, residual=_t(r, dev, cl), res_scale=0.05, res_zero_point=9,
+                             out_scale=0.11, out_zero_point=0).cpu().numpy()
+        want_r = orc.qadd_relu(want, sy, zy, r, 0.05, 9, 0.11, 0, relu=True, round_mode=mode, fold=True)
+        assert np.array_equal(yr, want_r)
+        chain = orc.qadd_relu(emul, sy, zy, r, 0.05, 9, 0.11, 0, relu=True, round_mode=mode)
+        assert lsb_report(yr, chain)[0] <= 2  # one step from the convolution, one from the folded tail
+    ops.device_status()

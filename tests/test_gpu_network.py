@@ -67,6 +67,34 @@ def test_resnet_matches_oracle(small_resnet, orc, ops):
     assert np.abs(logits - emul).max() <= 0.05 * max(1.0, np.abs(emul).max())
 
 
+def test_resnet_folded_requantization(small_resnet, orc, ops):
+    """forward(fold=True) -- what the benchmark runs -- is bit-exact against the oracle chain restating the folded arithmetic,
+    and its logits stay close to the reference-order network's."""
+    import __graft_entry__ as entry
+    entry.load_oracle()
+    from oracle import networks
+    net, x, xt = small_resnet
+    taps = {}
+    logits = net.forward(xt, taps=taps, fold=True).cpu().numpy()
+    ops.device_status()
+    otaps = {}
+    want = networks.resnet50_forward(net.export_numpy(), x, mode="fold", taps=otaps)
+    for k, v in otaps.items():
+        assert np.array_equal(taps[k].cpu().numpy(), v), k
+    assert np.array_equal(logits, want)
+    exact = net.forward(xt).cpu().numpy()
+    ex_taps = {}
+    net.forward(xt, taps=ex_taps)
+    mx, cnt, tot = lsb_report(taps["stem"].cpu().numpy(), ex_taps["stem"].cpu().numpy())
+    print("stem, folded vs reference-order requantization: %d of %d bytes differ (max %d LSB)" % (cnt, tot, mx))
+    assert mx <= 1
+    assert np.abs(logits - exact).max() <= 0.05 * max(1.0, np.abs(exact).max())
+    graph, lg = net.capture(xt, fold=True)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(lg.cpu().numpy(), logits)
+
+
 def test_resnet_layer_outputs_within_one_step_of_reference_chain(small_resnet, orc, ops):
     """Each QLinearConv of the network, fed the SAME input bytes on both sides, is at most 1 LSB from the reference's
     dequantize -> fp32 conv -> quantize result; the mismatch count is reported."""
