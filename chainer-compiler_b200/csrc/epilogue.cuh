@@ -31,13 +31,12 @@ __device__ __forceinline__ float epi_mult(const EpiArgs& e, int ch) {
 // For kEpiRequant returns the quantized byte (as int); residual, when present, is the byte at the same
 // output position.
 __device__ __forceinline__ int epi_requant(const EpiArgs& e, int acc, float mult, int bias, int res_byte) {
-    const int a = (int)((unsigned)acc + (unsigned)bias);
     if (e.rq.fold) {  // uint8 only (checked on the host)
-        int q = requant_u8_fold(a, __fdiv_rn(mult, e.rq.y_scale), e.rq);
-        if (e.rq.clamp_hi_q >= 0 && q > e.rq.clamp_hi_q) q = e.rq.clamp_hi_q;
+        int q = requant_u8_fold(acc, bias, __fdiv_rn(mult, e.rq.y_scale), e.rq);
         if (e.residual != nullptr) q = residual_fold(q, res_byte, e.rq);
         return q;
     }
+    const int a = (int)((unsigned)acc + (unsigned)bias);
     int q = requant_one(a, mult, e.rq);
     if (e.residual != nullptr) q = residual_one(q, res_byte, e.rq);
     return q;

@@ -93,28 +93,55 @@ __device__ __forceinline__ int requant_u8_fast(int acc, float mult, const Requan
     return quantize_one<false>(__fmul_rn((float)acc, mult), p.y_scale, p.y_zp_f, p.y_has_zp != 0, p.round_mode);
 }
 
-// Folded requantization of a uint8 output: t = float(acc) * m with m = (x_scale * w_scale[c]) / y_scale computed once per
-// channel; then the zero point, the rounding and the saturation exactly as quantize_one does them.
-__device__ __forceinline__ int requant_u8_fold(int acc, float m, const RequantParams& p) {
-    float t = __fmul_rn((float)acc, m);
-    if (p.round_mode != 0) return cvt_rne_sat_u8(__fadd_rn(rintf(t), p.y_zp_f));
-    if (p.y_has_zp) t = __fadd_rn(t, p.y_zp_f);
-    return cvt_floor_sat_u8(__fadd_rn(t, 0.5f));
+// Folded requantization of a uint8 output (RequantParams::fold; no counterpart in the reference): one multiplier and one
+// additive term per channel,
+//     M = (x_scale * w_scale[c]) / y_scale,        B = fma(float(bias), M, y_zp + 0.5)        (round-half-up)
+//     y = min(max(floor(fma(float(acc), M, B)), 0), hi)
+// or, for round-half-to-even, B = fma(float(bias), M, y_zp) and y = clamp(rint(fma(float(acc), M, B)), 0, hi).
+// `acc` is the accumulator without the bias.
+__device__ __forceinline__ float fold_offset(int bias, float m, const RequantParams& p) {
+    return __fmaf_rn((float)bias, m, p.round_mode != 0 ? p.y_zp_f : __fadd_rn(p.y_zp_f, 0.5f));
 }
 
-// Folded residual tail: v = (q - y_zp) * (y_scale / out_scale) + (r - res_zp) * (res_scale / out_scale) with the second
-// product fused into the sum (one rounding), Relu, then zero point, rounding and saturation of the output.
+__device__ __forceinline__ int requant_u8_fold(int acc, int bias, float m, const RequantParams& p) {
+    const float t = __fmaf_rn((float)acc, m, fold_offset(bias, m, p));
+    int q = p.round_mode != 0 ? cvt_rne_sat_u8(rintf(t)) : cvt_floor_sat_u8(t);
+    if (p.clamp_hi_q >= 0 && q > p.clamp_hi_q) q = p.clamp_hi_q;
+    return q;
+}
+
+// Folded residual tail: v = fma(r - res_zp, res_scale / out_scale, (q - y_zp) * (y_scale / out_scale)), Relu, then
+// floor(v + (out_zp + 0.5)) (round-half-up) or rint(v) + out_zp (round-half-to-even), saturated to uint8.
 __device__ __forceinline__ int residual_fold(int q, int r, const RequantParams& p) {
-    float u = (float)q;
-    if (p.y_has_zp) u = __fsub_rn(u, p.y_zp_f);
-    u = __fmul_rn(u, p.y_over_out);
-    float w = (float)r;
-    if (p.res_has_zp) w = __fsub_rn(w, p.res_zp_f);
-    float v = __fmaf_rn(w, p.res_over_out, u);
-    if (p.res_relu) v = v > 0.f ? v : 0.f;
+    const float u = __fmul_rn(__fsub_rn((float)q, p.y_zp_f), p.y_over_out);
+    float v = __fmaf_rn(__fsub_rn((float)r, p.res_zp_f), p.res_over_out, u);
+    if (p.res_relu) v = fmaxf(v, 0.f);
     if (p.round_mode != 0) return cvt_rne_sat_u8(__fadd_rn(rintf(v), p.out_zp_f));
-    if (p.out_has_zp) v = __fadd_rn(v, p.out_zp_f);
-    return cvt_floor_sat_u8(__fadd_rn(v, 0.5f));
+    return cvt_floor_sat_u8(__fadd_rn(v, __fadd_rn(p.out_zp_f, 0.5f)));
+}
+
+// ---- conversion-free forms for the tensor-core epilogue -------------------------------------------------------------
+// Float <-> integer conversions issue on the quarter-rate pipe; the epilogue handles billions of bytes, so it rounds and
+// converts with ordinary adds instead.  For 0 <= x < 2^23, x + 2^23 rounded toward minus infinity is the float
+// 2^23 + floor(x), whose low mantissa bits are the integer; a byte b becomes the float 2^23 + b by placing it under the
+// exponent pattern 0x4B000000.  Every function below returns exactly what its cvt-based counterpart returns.
+constexpr float kMagic23 = 8388608.f;         // 2^23
+constexpr float kMagicRne = 12582912.f;       // 1.5 * 2^23: (x + c) - c == rint(x) for |x| <= 2^22
+
+// Round-half-up uint8 quantization of a value that already holds t + zp + 0.5: returns the float 2^23 + q with
+// q = min(max(floor(tp), 0), hi); hi_plus_half = hi + 0.5f.  floor(clamp(tp, 0, hi + 0.5)) is that value, and the add
+// that rounds toward minus infinity takes the floor.
+__device__ __forceinline__ float quant_u8_up_magic(float tp, float hi_plus_half) {
+    return __fadd_rd(fminf(fmaxf(tp, 0.f), hi_plus_half), kMagic23);
+}
+
+__device__ __forceinline__ uint32_t magic_byte(float f) {
+    return __float_as_uint(f) & 0xffu;
+}
+
+// The float 2^23 + byte `sel` (0..3) of word w.
+__device__ __forceinline__ float byte_to_magic(uint32_t w, int sel) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 | sel) );
 }
 
 // DequantizeLinear(y), DequantizeLinear(r), Add, Relu, QuantizeLinear on one element.

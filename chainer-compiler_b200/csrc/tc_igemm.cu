@@ -146,8 +146,8 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     // Epilogue family: the uint8 fast path covers everything except int8 outputs and weight zero-point terms.
     int epi_kind = tc::kEpiKInt32;
     if (q.epi.mode == kEpiRequant) {
-        if (q.epi.rq.y_signed || q.col_mul != nullptr) {
-            epi_kind = tc::kEpiKGeneric;
+        if (q.epi.rq.y_signed || q.col_mul != nullptr || q.epi.rq.round_mode != 0) {
+            epi_kind = tc::kEpiKGeneric;  // int8 outputs, weight zero-point terms and round-half-to-even
         } else {
             epi_kind = q.epi.rq.fold ? tc::kEpiKU8Fold : tc::kEpiKU8;
         }

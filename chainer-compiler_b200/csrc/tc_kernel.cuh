@@ -354,7 +354,13 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         if (p.col_corr) bz -= (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];
                     }
                     s_mult[j] = m;
-                    s_add[j] = bz;
+                    // additive term: int32 (bias and activation zero-point term) or, folded, the float offset B of the bias
+                    if (EPI == kEpiKU8Fold) {
+                        const int bias = (c < p.cols && p.epi.bias) ? p.epi.bias[c] : 0;
+                        s_add[j] = __float_as_uint(fold_offset(bias, m, rq));
+                    } else {
+                        s_add[j] = bz;
+                    }
                 }
                 __syncwarp();
                 cached_ct = ct;
@@ -377,11 +383,21 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int64_t o = pos * p.ldc + cbase;
                 const float4* pm = reinterpret_cast<const float4*>(s_mult + i * 16);
                 const uint4* pa = reinterpret_cast<const uint4*>(s_add + i * 16);
-                // acc = raw + (bias - col_scale * col_corr[c])   (int32 wrap-around)
+                uint32_t addw[16];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint4 a4 = pa[j];
-                    r[4 * j] += a4.x; r[4 * j + 1] += a4.y; r[4 * j + 2] += a4.z; r[4 * j + 3] += a4.w;
+                    addw[4 * j] = a4.x; addw[4 * j + 1] = a4.y; addw[4 * j + 2] = a4.z; addw[4 * j + 3] = a4.w;
+                }
+                if (EPI != kEpiKU8Fold) {
+                    // acc = raw + (bias - col_scale * col_corr[c])   (int32 wrap-around)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] += addw[j];
+                } else if (p.col_corr) {
+                    // folded: the bias lives in the float offset; only the activation zero-point term is an integer
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (full_chunk || cbase + j < p.cols) r[j] -= (uint32_t)p.col_scale * (uint32_t)__ldg(p.col_corr + cbase + j);
                 }
                 if (EPI == kEpiKInt32 || EPI == kEpiKGeneric) {
                     if (p.col_mul) {  // weight zero-point term: - zw[c] * sum over the receptive field of (x - zx)
@@ -418,32 +434,78 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         }
                     }
                     uint32_t outw[4];
+                    if (EPI == kEpiKGeneric) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float4 m4 = pm[j];
-                        const float mm[4] = {m4.x, m4.y, m4.z, m4.w};
-                        uint32_t o32 = 0u;
+                        for (int j = 0; j < 4; ++j) {
+                            const float4 m4 = pm[j];
+                            const float mm[4] = {m4.x, m4.y, m4.z, m4.w};
+                            uint32_t o32 = 0u;
 #pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            const int a = (int)r[4 * j + b];
-                            const int rb = (int)((resw[j] >> (8 * b)) & 0xffu);
-                            int q;
-                            if (EPI == kEpiKU8) {
-                                q = min(requant_u8_fast(a, mm[b], rq), hi_q);
-                                if (ro) q = residual_one(q, rb, rq);  // DequantizeLinear x2, Add, Relu, QuantizeLinear
-                            } else if (EPI == kEpiKU8Fold) {
-                                q = min(requant_u8_fold(a, mm[b], rq), hi_q);
-                                if (ro) q = residual_fold(q, rb, rq);
-                            } else if (rq.fold) {
-                                q = min(requant_u8_fold(a, mm[b], rq), hi_q);
-                                if (ro) q = residual_fold(q, rb, rq);
-                            } else {
-                                q = requant_one(a, mm[b], rq);
-                                if (ro) q = residual_one(q, rb, rq);
+                            for (int b = 0; b < 4; ++b) {
+                                const int a = (int)r[4 * j + b];
+                                const int rb = (int)((resw[j] >> (8 * b)) & 0xffu);
+                                int q;
+                                if (rq.fold) {
+                                    const int cc = cbase + 4 * j + b;
+                                    const int bpure = (p.epi.bias && cc < p.cols) ? __ldg(p.epi.bias + cc) : 0;
+                                    q = requant_u8_fold((int)(r[4 * j + b] - (uint32_t)bpure), bpure, mm[b], rq);
+                                    if (ro) q = residual_fold(q, rb, rq);
+                                } else {
+                                    q = requant_one(a, mm[b], rq);
+                                    if (ro) q = residual_one(q, rb, rq);
+                                }
+                                o32 |= ((uint32_t)q & 0xffu) << (8 * b);
                             }
-                            o32 |= ((uint32_t)q & 0xffu) << (8 * b);
+                            outw[j] = o32;
                         }
-                        outw[j] = o32;
+                    } else {
+                        // uint8, round-half-up (the other rounding mode takes the general kernel): one int->float conversion
+                        // per element, everything else on the add/multiply pipes (see qmath.cuh), no per-element branches
+                        // (adding a zero zero point is exact).  Results equal requant_one / residual_one (reference operation
+                        // order) or requant_u8_fold / residual_fold bit for bit.
+                        constexpr bool kFold = EPI == kEpiKU8Fold;
+                        const float hi_ph = (float)hi_q + 0.5f;
+                        const float cy = kMagic23 + rq.y_zp_f, cr = kMagic23 + rq.res_zp_f;
+                        const float relu_floor = rq.res_relu ? 0.f : -3.0e38f;
+                        const float out_half = __fadd_rn(rq.out_zp_f, 0.5f);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float4 m4 = pm[j];
+                            const float mm[4] = {m4.x, m4.y, m4.z, m4.w};
+                            uint32_t fb[4];
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const float a = (float)(int)r[4 * j + b];
+                                float tp;
+                                if (kFold) {
+                                    tp = __fmaf_rn(a, mm[b], __uint_as_float(addw[4 * j + b]));
+                                } else {
+                                    tp = __fdiv_rn(__fmul_rn(a, mm[b]), rq.y_scale);
+                                    tp = __fadd_rn(__fadd_rn(tp, rq.y_zp_f), 0.5f);
+                                }
+                                fb[b] = __float_as_uint(quant_u8_up_magic(tp, hi_ph));
+                            }
+                            if (ro) {
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) {
+                                    const float u = __fsub_rn(__uint_as_float(fb[b]), cy);           // q - y_zp, exact
+                                    const float w = __fsub_rn(byte_to_magic(resw[j], b), cr);          // r - res_zp, exact
+                                    float v;
+                                    if (kFold) {
+                                        v = __fmaf_rn(w, rq.res_over_out, __fmul_rn(u, rq.y_over_out));
+                                        v = fmaxf(v, relu_floor);
+                                    } else {
+                                        v = __fadd_rn(__fmul_rn(u, rq.y_scale), __fmul_rn(w, rq.res_scale));
+                                        v = fmaxf(v, relu_floor);
+                                        v = __fdiv_rn(v, rq.out_scale);
+                                    }
+                                    const float tp = kFold ? __fadd_rn(v, out_half) : __fadd_rn(__fadd_rn(v, rq.out_zp_f), 0.5f);
+                                    fb[b] = __float_as_uint(quant_u8_up_magic(tp, 255.5f));
+                                }
+                            }
+                            const uint32_t lo = __byte_perm(fb[0], fb[1], 0x0040), hi = __byte_perm(fb[2], fb[3], 0x0040);
+                            outw[j] = __byte_perm(lo, hi, 0x5410);
+                        }
                     }
                     if (vec) {
                         *reinterpret_cast<uint4*>(yo) = make_uint4(outw[0], outw[1], outw[2], outw[3]);

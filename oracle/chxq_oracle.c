@@ -326,19 +326,23 @@ void orc_qlinear_conv(
  * agrees with orc_qlinear_conv except where fp32 accumulation error crosses a rounding
  * boundary.  acc: [rows, M] (channel is the LAST axis) or, when chan_stride > 1, NCHW with
  * chan_stride = Ho*Wo: channel of element i = (i / chan_stride) % M. */
-/* fold != 0 is the library's optional single-multiplier form (uint8 outputs): m = (x_scale * w_scale[c]) / y_scale once per
- * channel, t = float(acc) * m, then zero point, rounding and saturation as quantize_one.  It has no counterpart in the
- * reference; it is restated here so that the kernels that implement it can be checked bit for bit. */
-static inline int quantize_prescaled_u8(float t, int zp, int round_mode) {
-    if (round_mode == ORC_ROUND_RNE) {
-        float r = nearbyintf(t) + (float)zp;
-        r = fminf(r, 255.f);
-        r = fmaxf(0.f, r);
-        return (int)r;
-    }
-    if (zp != 0) t = t + (float)zp;
-    t = t + 0.5f;
-    t = floorf(t);
+/* fold != 0 is the library's optional folded form for uint8 outputs (no counterpart in the reference; restated here so that
+ * the kernels implementing it can be checked bit for bit): per channel M = (x_scale * w_scale[c]) / y_scale and
+ * B = fma(float(bias), M, zp + 0.5) [round-half-up] or fma(float(bias), M, zp) [round-half-to-even];
+ * y = min(max(floor(fma(float(acc), M, B)), 0), hi)  or  clamp(rint(fma(float(acc), M, B)), 0, hi). */
+static inline int fold_quantize_u8(int32_t acc, int32_t bias, float M, int zp, int round_mode, int clamp_hi_q) {
+    const float B = fmaf((float)bias, M, round_mode == ORC_ROUND_RNE ? (float)zp : (float)zp + 0.5f);
+    float t = fmaf((float)acc, M, B);
+    t = round_mode == ORC_ROUND_RNE ? nearbyintf(t) : floorf(t);
+    t = fminf(t, 255.f);
+    t = fmaxf(0.f, t);
+    int q = (int)t;
+    if (clamp_hi_q >= 0 && q > clamp_hi_q) q = clamp_hi_q;
+    return q;
+}
+
+static inline int quantize_prescaled_u8(float v, int zp, int round_mode) {
+    float t = round_mode == ORC_ROUND_RNE ? nearbyintf(v) + (float)zp : floorf(v + ((float)zp + 0.5f));
     t = fminf(t, 255.f);
     t = fmaxf(0.f, t);
     return (int)t;
@@ -353,10 +357,7 @@ void orc_requantize(
         const float mult = x_scale * (w_params_len == 1 ? w_scale[0] : w_scale[m]);
         const int32_t a = (int32_t)((uint32_t)acc[i] + (uint32_t)(bias ? bias[m] : 0));
         if (fold) {
-            const float mm = mult / y_scale;
-            int q = quantize_prescaled_u8((float)a * mm, y_zp, round_mode);
-            if (clamp_hi_q >= 0 && q > clamp_hi_q) q = clamp_hi_q;
-            ((uint8_t*)y)[i] = (uint8_t)q;
+            ((uint8_t*)y)[i] = (uint8_t)fold_quantize_u8(acc[i], bias ? bias[m] : 0, mult / y_scale, y_zp, round_mode, clamp_hi_q);
             continue;
         }
         const float yf = (float)a * mult;
@@ -598,12 +599,8 @@ void orc_qadd_relu_fold(
     const float ka = a_scale / y_scale, kb = b_scale / y_scale;
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) {
-        float u = (float)a[i];
-        if (a_zp != 0) u = u - (float)a_zp;
-        u = u * ka;
-        float w = (float)b[i];
-        if (b_zp != 0) w = w - (float)b_zp;
-        float v = fmaf(w, kb, u);
+        const float u = ((float)a[i] - (float)a_zp) * ka;
+        float v = fmaf((float)b[i] - (float)b_zp, kb, u);
         if (relu) v = v > 0.f ? v : 0.f;
         y[i] = (uint8_t)quantize_prescaled_u8(v, y_zp, round_mode);
     }
