@@ -253,6 +253,50 @@ __global__ void __launch_bounds__(256) im2col_nchw_rows_kernel(
     }
 }
 
+// im2col of an NCHW map with at most 4 channels, channel pitch 4 (k = tap * 4 + c): each pixel becomes one 32-bit word, so
+// a matrix row is KH*KW words gathered with 32-bit shared-memory loads.  One block per (n, ho); the staged rows hold the
+// pixels of every needed input row as words (padding pixels = pad_byte in the real channels, 0 in the unused lanes).
+__global__ void __launch_bounds__(256) im2col_nchw_c4_kernel(
+        const uint8_t* __restrict__ x, ConvDesc d, int a_pitch, int pad_byte, int wspan, uint8_t* __restrict__ a) {
+    extern __shared__ __align__(16) uint32_t srow[];  // [KH][wspan] pixels
+    const int n = blockIdx.x / d.Ho, ho = blockIdx.x % d.Ho;
+    const int hi0 = ho * d.sh - d.pt;
+    const uint32_t lanes = d.C >= 4 ? 0x01010101u : ((1u << (8 * d.C)) - 1u) & 0x01010101u;  // only real channels carry the pad value
+    const uint32_t padw = (uint32_t)(pad_byte & 0xff) * lanes;
+    for (int i = threadIdx.x; i < d.KH * wspan; i += blockDim.x) {
+        const int col = i % wspan, kh = i / wspan;
+        const int hi = hi0 + kh, wi = col - d.pl;
+        uint32_t v = padw;
+        if (hi >= 0 && hi < d.H && wi >= 0 && wi < d.W) {
+            v = 0u;
+            for (int c = 0; c < d.C; ++c) v |= (uint32_t)x[(((int64_t)n * d.C + c) * d.H + hi) * d.W + wi] << (8 * c);
+        }
+        srow[i] = v;
+    }
+    __syncthreads();
+    const int cpr = a_pitch / 16;              // 16-byte chunks (4 taps) per matrix row
+    const int taps = d.KH * d.KW;
+    const int groups = blockDim.x / cpr;       // rows handled per sweep
+    const int j = threadIdx.x % cpr, g0 = threadIdx.x / cpr;
+    if (g0 >= groups) return;
+    int off[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const int t = j * 4 + b;
+        off[b] = t < taps ? (t / d.KW) * wspan + (t % d.KW) : -1;
+    }
+    uint8_t* out = a + ((int64_t)n * d.Ho + ho) * d.Wo * a_pitch;
+    for (int wo = g0; wo < d.Wo; wo += groups) {
+        const int base = wo * d.sw;
+        uint4 v;
+        v.x = off[0] >= 0 ? srow[off[0] + base] : 0u;
+        v.y = off[1] >= 0 ? srow[off[1] + base] : 0u;
+        v.z = off[2] >= 0 ? srow[off[2] + base] : 0u;
+        v.w = off[3] >= 0 ? srow[off[3] + base] : 0u;
+        *reinterpret_cast<uint4*>(out + ((int64_t)wo * cpr + j) * 16) = v;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Glue kernels (NHWC u8 maps, 16 channels = one 128-bit word per thread where channels allow).
 // ---------------------------------------------------------------------------------------------
@@ -328,37 +372,49 @@ __global__ void __launch_bounds__(256) global_avgpool_dq_kernel(
     y[idx] = __fmul_rn(__fdiv_rn((float)s, (float)HW), scale);
 }
 
-// fp32 Linear: y[n,o] = sum_k x[n,k] w[o,k] + b[o], k ascending with separate multiply and add
-// (the order the CPU restatement uses), 32x32 tiles through shared memory.
+// fp32 Linear: y[n,o] = fma chain over k ascending of x[n,k] * w[o,k], then + b[o].  32 x 64 output tile per block, each
+// thread a 2 x 4 patch, operands staged through shared memory in 32-wide K slices.  Every output is accumulated by one
+// thread in k order (no split-K), so the result does not depend on the tiling.
 __global__ void __launch_bounds__(256) linear_f32_kernel(
         const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, int N, int K, int O, float* __restrict__ y) {
-    __shared__ float Xs[32][33];
-    __shared__ float Ws[32][33];
-    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
-    const int n0 = blockIdx.y * 32, o0 = blockIdx.x * 32;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    __shared__ __align__(16) float Xs[32][34];   // [k][n]  (K slice major, so a thread reads its two rows as one 64-bit word)
+    __shared__ __align__(16) float Ws[32][68];   // [k][o]  (a thread reads its four columns as one 128-bit word)
+    const int tid = threadIdx.x;
+    const int tn = tid / 16, to = tid % 16;   // 16 x 16 threads: rows tn*2.., cols to*4..
+    const int n0 = blockIdx.y * 32, o0 = blockIdx.x * 64;
+    float acc[2][4] = {};
     for (int k0 = 0; k0 < K; k0 += 32) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = ty * 4 + i;
-            Xs[r][tx] = (n0 + r < N && k0 + tx < K) ? x[(int64_t)(n0 + r) * K + k0 + tx] : 0.f;
-            Ws[r][tx] = (o0 + r < O && k0 + tx < K) ? w[(int64_t)(o0 + r) * K + k0 + tx] : 0.f;
+        for (int i = tid; i < 32 * 32; i += 256) {
+            const int r = i / 32, c = i % 32;
+            Xs[c][r] = (n0 + r < N && k0 + c < K) ? x[(int64_t)(n0 + r) * K + k0 + c] : 0.f;
+        }
+        for (int i = tid; i < 64 * 32; i += 256) {
+            const int r = i / 32, c = i % 32;
+            Ws[c][r] = (o0 + r < O && k0 + c < K) ? w[(int64_t)(o0 + r) * K + k0 + c] : 0.f;
         }
         __syncthreads();
         const int kmax = min(32, K - k0);
         for (int kk = 0; kk < kmax; ++kk) {
-            const float wv = Ws[tx][kk];
+            const float2 xv = *reinterpret_cast<const float2*>(&Xs[kk][tn * 2]);
+            const float4 wv = *reinterpret_cast<const float4*>(&Ws[kk][to * 4]);
+            const float ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(Xs[ty * 4 + i][kk], wv));
+            for (int j = 0; j < 4; ++j) {
+                acc[0][j] = __fmaf_rn(xv.x, ww[j], acc[0][j]);
+                acc[1][j] = __fmaf_rn(xv.y, ww[j], acc[1][j]);
+            }
         }
         __syncthreads();
     }
-    const int o = o0 + tx;
-    if (o >= O) return;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int n = n0 + ty * 4 + i;
-        if (n < N) y[(int64_t)n * O + o] = __fadd_rn(acc[i], b ? b[o] : 0.f);
+    for (int i = 0; i < 2; ++i) {
+        const int n = n0 + tn * 2 + i;
+        if (n >= N) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int o = o0 + to * 4 + j;
+            if (o < O) y[(int64_t)n * O + o] = __fadd_rn(acc[i][j], b ? b[o] : 0.f);
+        }
     }
 }
 
@@ -453,6 +509,16 @@ int launch_im2col(const void* x, const chxq_conv_geom& g, int c_pitch, int k_pad
     ConvDesc d = make_desc(g, 0, 0, 0);
     const int64_t total = (int64_t)g.N * g.Ho * g.Wo * (k_pad / 16);
     if (total == 0) return CHXQ_OK;
+    if (!d.x_nhwc && c_pitch == 4 && g.C <= 4 && k_pad / 16 <= 256) {
+        const int wspan = (g.Wo - 1) * g.stride_w + g.KW;
+        const size_t smem = (size_t)g.KH * wspan * 4;
+        if (smem <= 48 * 1024 && (int64_t)g.N * g.Ho < (1ll << 31)) {
+            im2col_nchw_c4_kernel<<<(unsigned)(g.N * g.Ho), 256, smem, s>>>(static_cast<const uint8_t*>(x), d, k_pad, pad_byte, wspan,
+                                                                        static_cast<uint8_t*>(a));
+            CHXQ_LAUNCH_CHECK();
+            return CHXQ_OK;
+        }
+    }
     if (!d.x_nhwc && c_pitch == g.C && k_pad < 32768) {
         // NCHW input with dense K: stage whole input rows per (n, ho).
         const int wspan = (g.Wo - 1) * g.stride_w + g.KW;
@@ -499,8 +565,8 @@ extern "C" int chxq_global_avgpool_dq_nhwc(const uint8_t* x, int32_t N, int32_t 
 
 extern "C" int chxq_linear_f32(const float* x, const float* w, const float* b, int32_t N, int32_t K, int32_t O, float* y, void* stream) {
     CHXQ_CHECK_ARG(x && w && y && N > 0 && K > 0 && O > 0, "Linear: bad arguments");
-    dim3 grid((O + 31) / 32, (N + 31) / 32), block(32, 8);
-    linear_f32_kernel<<<grid, block, 0, as_stream(stream)>>>(x, w, b, N, K, O, y);
+    dim3 grid((O + 63) / 64, (N + 31) / 32);
+    linear_f32_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, w, b, N, K, O, y);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }

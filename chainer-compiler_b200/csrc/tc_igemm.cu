@@ -123,11 +123,13 @@ TcConvPlan plan_tc_conv(const chxq_conv_geom& g) {
         return pl;
     }
     // Everything else with one group: explicit im2col into workspace, then a plain GEMM.
-    const int K = taps * g.C;
+    // NCHW maps with up to 4 channels (a network stem) use one 32-bit word per pixel: channel pitch 4.
+    const int cp = (g.x_layout == CHXQ_NCHW && g.C < 4) ? 4 : g.C;
+    const int K = taps * cp;
     pl.path = kTcIm2col;
     // Large K tiles keep the TMA boxes wide; the part of the last tile beyond the matrix row is zero fill, not traffic.
     pl.bk = K > 64 ? 128 : (K > 32 ? 64 : 32);
-    pl.c_pitch = g.C;
+    pl.c_pitch = cp;
     pl.k_total = (K + pl.bk - 1) / pl.bk * pl.bk;
     pl.a_pitch = (K + 15) / 16 * 16;
     pl.Wb = 128; pl.Hb = 1; pl.Nb = 1;

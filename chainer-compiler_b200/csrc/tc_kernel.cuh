@@ -159,6 +159,16 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
             : "memory");
 }
 
+// Waits for this thread's outstanding TMEM loads.  The destination registers are passed through the statement as
+// read-write operands so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),
+                   "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -366,19 +376,26 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 cached_ct = ct;
             }
 
+            // Residual bytes of this warp's chunks are fetched before the accumulator is waited for, so that their latency
+            // overlaps the main loop of the tile (vector path only; ragged chunks load theirs bytewise).
+            const uint8_t* res_row = (EPI != kEpiKInt32 && p.epi.residual && row_ok) ? p.epi.residual + pos * p.ldc : nullptr;
+            auto res_load = [&](int i) -> uint4 {
+                const int cb = col0 + (i * 4 + sub) * 16;
+                if (EPI != kEpiKInt32 && res_row && p.vec_ok && i < kMine && cb + 16 <= p.cols)
+                    return __ldg(reinterpret_cast<const uint4*>(res_row + cb));
+                return make_uint4(0u, 0u, 0u, 0u);
+            };
+            uint4 res0 = res_load(0), res1 = res_load(1);
+
             const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4);
             if (!__all_sync(0xffffffffu, got)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-            for (int i = 0; i < kMine; ++i) {
-                uint32_t r[16];
+            // One 16-column chunk: registers of TMEM data in, 16 bytes (or 16 int32) out.
+            auto process = [&](uint32_t (&r)[16], const int i, const uint4 resv) {
                 const int ch = i * 4 + sub;
-                __syncwarp();
-                tmem_ld_32x32b_x16(taddr + (uint32_t)(ch * 16), r);
-                tmem_ld_wait();
                 const int cbase = col0 + ch * 16;
-                if (!(row_ok && cbase < p.cols)) continue;
+                if (!(row_ok && cbase < p.cols)) return;
                 const bool full_chunk = cbase + 16 <= p.cols;
                 const int64_t o = pos * p.ldc + cbase;
                 const float4* pm = reinterpret_cast<const float4*>(s_mult + i * 16);
@@ -425,8 +442,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     uint32_t resw[4] = {0u, 0u, 0u, 0u};
                     if (ro) {
                         if (vec) {
-                            const uint4 r0 = *reinterpret_cast<const uint4*>(ro);
-                            resw[0] = r0.x; resw[1] = r0.y; resw[2] = r0.z; resw[3] = r0.w;
+                            resw[0] = resv.x; resw[1] = resv.y; resw[2] = resv.z; resw[3] = resv.w;
                         } else {
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
@@ -515,6 +531,17 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             if (cbase + j < p.cols) yo[j] = (uint8_t)(outw[j >> 2] >> (8 * (j & 3)));
                     }
                 }
+            };
+            // Chunks are processed one after the other, fully unrolled (at most four per warp); the other warps of the
+            // scheduler cover the TMEM read latency.
+            uint4 resv[4] = {res0, res1, res_load(2), res_load(3)};
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) {
+                uint32_t ra[16];
+                __syncwarp();
+                tmem_ld_32x32b_x16(taddr + (uint32_t)((i * 4 + sub) * 16), ra);
+                tmem_ld_wait16(ra);
+                process(ra, i, resv[i]);
             }
             // Hand the accumulator buffer back to the MMA warp.
             tc_fence_before();

@@ -580,13 +580,14 @@ void orc_global_avgpool_dq(const uint8_t* x, int64_t N, int64_t C, int64_t HW, f
     }
 }
 
-/* Linear / Gemm: y[n, o] = sum_k x[n,k] * w[o,k] + b[o], fp32, k ascending. */
+/* Linear / Gemm: y[n, o] = sum_k x[n,k] * w[o,k] + b[o], fp32, k ascending, each step a fused multiply-add (the
+ * accumulation order inside ChainerX's Dot is not knowable from the reference checkout; this is the library's). */
 void orc_linear_f32(const float* x, const float* w, const float* b, int64_t N, int64_t K, int64_t O, float* y) {
 #pragma omp parallel for collapse(2) schedule(static)
     for (int64_t n = 0; n < N; ++n)
         for (int64_t o = 0; o < O; ++o) {
             float acc = 0.f;
-            for (int64_t k = 0; k < K; ++k) acc = acc + x[n * K + k] * w[o * K + k];
+            for (int64_t k = 0; k < K; ++k) acc = fmaf(x[n * K + k], w[o * K + k], acc);
             y[n * O + o] = acc + (b ? b[o] : 0.f);
         }
 }
