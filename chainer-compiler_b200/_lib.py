@@ -83,6 +83,7 @@ SIGNATURES = {
     "chxq_dequantize_linear": (_c.c_int, [_vp, _i32, _i64, _f32, _i32, _vp, _vp]),
     "chxq_matmul_integer_workspace": (_sz, [_i64, _i64, _i64, _i64]),
     "chxq_matmul_integer": (_c.c_int, [_vp, _i32, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _sz, _i32, _vp]),
+    "chxq_matmul_integer_noalloc": (_c.c_int, [_vp, _i32, _vp, _i32, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
     "chxq_qlinear_matmul": (_c.c_int, [_vp, _i32, _f32, _i32, _vp, _i32, _f32, _i32, _f32, _i32, _i32, _i64, _i64, _i64, _i32, _vp, _vp, _sz,
                                        _i32, _vp]),
     "chxq_conv_resolve_geometry": (_c.c_int, [_i32] * 8 + [_c.POINTER(_i64), _i32, _c.POINTER(_i64), _i32, _i32, _c.c_char_p,

@@ -494,6 +494,72 @@ extern "C" int chxq_matmul_integer(
                          workspace_bytes, path, s);
 }
 
+// ---------------------------------------------------------------------------------------------
+// MatMulInteger without any allocation: the scratch of the tensor-core path lives in a fixed device array.
+// ---------------------------------------------------------------------------------------------
+namespace chxq {
+namespace {
+
+// Scratch of chxq_matmul_integer_noalloc: transposed B, the two zero-point vectors and the row sums.  Every GPU that loads
+// this library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CHXQ_NOALLOC_SCRATCH_BYTES];
+
+// In host code the array's name is only a stand-in for the symbol, not a device address: the address a kernel can use
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+int noalloc_scratch_ptr(void** out) {
+    static void* cache[64] = {};
+    int dev = 0;
+    CHXQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return set_error(CHXQ_ERR_UNSUPPORTED, "MatMulInteger(noalloc): device ordinal %d out of range", dev);
+    if (cache[dev] == nullptr) {
+        void* ptr = nullptr;
+        CHXQ_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        if (ptr == nullptr) return set_error(CHXQ_ERR_CUDA, "MatMulInteger(noalloc): the scratch symbol has no device address");
+        cache[dev] = ptr;
+    }
+    *out = cache[dev];
+    return CHXQ_OK;
+}
+
+}  // namespace
+}  // namespace chxq
+
+extern "C" int chxq_matmul_integer_noalloc(
+        const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t M, int64_t N, int64_t K, const void* a_zero_point,
+        int64_t a_zp_len, const void* b_zero_point, int64_t b_zp_len, int32_t* y, void* stream) {
+    CHXQ_CHECK_ARG(is_q8(a_dtype) && is_q8(b_dtype), "MatMulInteger(noalloc): operands must be uint8 or int8 (got %d, %d)", a_dtype, b_dtype);
+    CHXQ_CHECK_ARG(M >= 0 && N >= 0 && K >= 0, "MatMulInteger(noalloc): negative extent");
+    int rc = check_zp_len("MatMulInteger(noalloc)", "a_zero_point", a_zero_point, a_zp_len, K);
+    if (rc != CHXQ_OK) return rc;
+    rc = check_zp_len("MatMulInteger(noalloc)", "b_zero_point", b_zero_point, b_zp_len, N);
+    if (rc != CHXQ_OK) return rc;
+    if (M * N == 0) return CHXQ_OK;
+    CHXQ_CHECK_ARG(y != nullptr && (K == 0 || (a && b)), "MatMulInteger(noalloc): null buffer");
+    cudaStream_t s = as_stream(stream);
+    if (K == 0) {
+        CHXQ_CUDA(cudaMemsetAsync(y, 0, (size_t)M * N * 4, s));
+        return CHXQ_OK;
+    }
+    EpiArgs epi{};
+    epi.mode = kEpiInt32;
+    const ZpSpec za{a_zero_point, a_zp_len, 0}, zb{b_zero_point, b_zp_len, 0};
+    if (!gemm_tc_eligible(a, M, N, K)) {
+        // shapes the tensor-core kernel does not take run on the CUDA-core kernel, which needs no scratch at all
+        return launch_gemm_simt(a, a_dtype == CHXQ_INT8, b, b_dtype == CHXQ_INT8, 1, M, N, K, za, zb, epi, y, s);
+    }
+    const size_t need = gemm_ws_layout(M, N, K).total;
+    if (need > (size_t)CHXQ_NOALLOC_SCRATCH_BYTES)
+        return set_error(CHXQ_ERR_WORKSPACE,
+                         "MatMulInteger(noalloc): M=%lld N=%lld K=%lld needs %zu bytes of scratch, the fixed array holds %d; use "
+                         "chxq_matmul_integer with a caller-provided workspace",
+                         (long long)M, (long long)N, (long long)K, need, (int)CHXQ_NOALLOC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    rc = noalloc_scratch_ptr(&scratch);
+    if (rc != CHXQ_OK) return rc;
+    return gemm_dispatch("MatMulInteger(noalloc)", a, a_dtype == CHXQ_INT8, b, b_dtype == CHXQ_INT8, 1, M, N, K, za, zb, epi, y, 4, scratch,
+                         (size_t)CHXQ_NOALLOC_SCRATCH_BYTES, CHXQ_PATH_TENSOR, s);
+}
+
 extern "C" int chxq_qlinear_matmul(
         const void* a, int32_t a_dtype, float a_scale, int32_t a_zero_point, const void* b, int32_t b_dtype, float b_scale, int32_t b_zero_point,
         float y_scale, int32_t y_zero_point, int32_t y_dtype, int64_t M, int64_t N, int64_t K, int32_t round_mode, void* y, void* workspace,

@@ -93,6 +93,27 @@ int chxq_matmul_integer(const void* a, int32_t a_dtype, const void* b, int32_t b
                         const void* a_zero_point, int64_t a_zp_len, const void* b_zero_point, int64_t b_zp_len, int32_t* y,
                         void* workspace, size_t workspace_bytes, int32_t path, void* stream);
 
+/* ---- MatMulInteger for callers that must not allocate.  It has no counterpart in the reference.
+ * Same result as chxq_matmul_integer on one matrix pair (no batch), but the scratch the tensor-core path needs
+ * (repacked B, zero-point vectors, row sums) sits in a fixed array inside the library image, so this entry calls no
+ * cudaMalloc / cudaFree and takes no workspace.  It is meant for callers such as an allocation hook of a memory pool,
+ * which runs while the pool's lock is held and cannot ask the pool (or the driver) for more memory, or a serving loop
+ * whose device memory was handed out completely at start-up and which must not take the device-wide synchronisation
+ * a driver allocation implies.
+ *  - Limit: the scratch needed, N * roundup(K, 32..128) + 8 * N + 4 * M bytes (each part rounded up to 256), must fit
+ *    CHXQ_NOALLOC_SCRATCH_BYTES; larger problems are refused with CHXQ_ERR_WORKSPACE.  Shapes the tensor-core kernel
+ *    does not take (K not a multiple of 16, unaligned A) run on the CUDA-core kernel, which uses no scratch.
+ *  - Every GPU that loads the library keeps the array until the process exits.
+ *  - The first call on a device looks the array's device address up (cudaGetSymbolAddress); make that first call
+ *    before any stream capture on that device.
+ *  - All calls share the array and it keeps the previous call's bytes.  Nothing in it needs clearing: every byte the
+ *    kernels read is written earlier in the same call.  Two calls whose kernels overlap on the GPU (different
+ *    streams) race on it; calls on one stream are ordered and safe. */
+#define CHXQ_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024)
+int chxq_matmul_integer_noalloc(const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t M, int64_t N, int64_t K,
+                                const void* a_zero_point, int64_t a_zp_len, const void* b_zero_point, int64_t b_zp_len, int32_t* y,
+                                void* stream);
+
 /* ---- QLinearMatMul: has no VM op in the reference; ReplaceQLinearMatMul
  * (compiler/simplifier.cc:675-694) expands it to DequantizeLinear x2, MatMul, QuantizeLinear
  * with scalar parameters.  This entry computes that chain's result from the exact int32
