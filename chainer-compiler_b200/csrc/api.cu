@@ -449,6 +449,7 @@ int fill_requant(const char* op, const chxq_qconv_params* p, const chxq_conv_geo
     e->rq.out_scale = p->out_scale;
     e->rq.out_zp_f = (float)p->out_zero_point;
     e->rq.out_has_zp = p->out_zero_point != 0;
+    finish_requant_params(&e->rq);
     if (p->fold_scales) {
         CHXQ_CHECK_ARG(p->y_dtype == CHXQ_UINT8, "%s: folded requantization needs a uint8 output", op);
         e->rq.fold = 1;
@@ -582,6 +583,7 @@ extern "C" int chxq_qlinear_matmul(
     epi.rq.y_signed = ys;
     epi.rq.round_mode = round_mode;
     epi.rq.clamp_hi_q = -1;
+    finish_requant_params(&epi.rq);
     const ZpSpec za{nullptr, a_zero_point != 0 ? 1 : 0, a_zero_point}, zb{nullptr, b_zero_point != 0 ? 1 : 0, b_zero_point};
     return gemm_dispatch("QLinearMatMul", a, a_dtype == CHXQ_INT8, b, b_dtype == CHXQ_INT8, 1, M, N, K, za, zb, epi, y, 1, workspace,
                          workspace_bytes, path, as_stream(stream));

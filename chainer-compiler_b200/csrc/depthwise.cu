@@ -3,8 +3,9 @@
 // halo tile is staged into shared memory with 128-bit loads (positions in the convolution's padding
 // are filled with the activation zero point, i.e. 0 after zero-point subtraction, which is where the
 // reference pads: runtime/ops/quantize.cc:65-72 dequantizes before chainerx::Conv zero-pads), the
-// per-channel taps are staged as (w - w_zp) in 16 bit, every thread accumulates 16 channels of one
-// position in registers and stores one 128-bit word of requantized output.
+// per-channel taps are staged as (w - w_zp) in the byte lane of their channel so that the multiply-accumulate is a
+// four-way dot product with no byte extraction, every thread accumulates 16 channels of one position in registers
+// and stores one 128-bit word of requantized output.
 //
 // The reference runs this as `group` separate fp32 convolutions plus a concatenate
 // (runtime/chainerx_util.cc:328-339): 960 launches for one MobileNetV2 layer.
@@ -26,13 +27,27 @@ struct DwDesc {
     int tiles_w;
 };
 
+// u8 (or s8) x s8 four-way dot product with accumulate.
+template <bool kXSigned>
+__device__ __forceinline__ int dp4a_xs(uint32_t x, uint32_t w, int acc) {
+    int d;
+    if (kXSigned)
+        asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    else
+        asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    return d;
+}
+
+template <bool kXSigned>
 __global__ void __launch_bounds__(256) depthwise_kernel(
         const uint8_t* __restrict__ x, const void* __restrict__ w, const void* __restrict__ w_zp, DwDesc d, EpiArgs epi, uint8_t* __restrict__ y) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int IH = (kTH - 1) * d.sh + d.KH, IW = (kTW - 1) * d.sw + d.KW;
     const int taps = d.KH * d.KW;
-    uint8_t* s_in = smem;                                                  // [IH][IW][64]
-    int16_t* s_w = reinterpret_cast<int16_t*>(smem + ((IH * IW * kCC + 15) & ~15));  // [taps][64]
+    uint8_t* s_in = smem;                                                               // [IH][IW][64] bytes
+    uint32_t* s_w = reinterpret_cast<uint32_t*>(smem + ((IH * IW * kCC + 15) & ~15));  // [taps][64] words: (w - w_zp) in byte (c & 3)
+    int* s_wsum = reinterpret_cast<int*>(s_w + taps * kCC);                            // [64] sum over taps of (w - w_zp)
+    __shared__ int s_wide;                                                              // some (w - w_zp) does not fit int8
 
     const int tile = blockIdx.x;
     const int th = tile / d.tiles_w, tw = tile % d.tiles_w;
@@ -41,8 +56,11 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
     const int ho0 = th * kTH, wo0 = tw * kTW;
     const int hi0 = ho0 * d.sh - d.pt, wi0 = wo0 * d.sw - d.pl;
     const int tid = threadIdx.x;
+    if (tid == 0) s_wide = 0;
+    __syncthreads();
 
-    // Stage the taps of this channel block: s_w[tap][c] = w[c0 + c, 0, tap] - w_zp[c0 + c].
+    // Stage the taps of this channel block.  The multiply runs as a four-way dot product whose weight word holds one
+    // non-zero byte -- the tap of channel c in byte (c & 3) -- so no byte of the activation word has to be extracted.
     for (int i = tid; i < taps * kCC; i += 256) {
         const int c = i % kCC, tap = i / kCC;
         int v = 0;
@@ -54,9 +72,10 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
                 v -= d.w_signed ? (int)static_cast<const int8_t*>(w_zp)[zi] : (int)static_cast<const uint8_t*>(w_zp)[zi];
             }
         }
-        s_w[tap * kCC + c] = (int16_t)v;
+        if (v < -128 || v > 127) s_wide = 1;
+        s_w[i] = ((uint32_t)v & 0xffu) << (8 * (c & 3));
     }
-    // Stage the input halo tile, 16 channels (one 128-bit word) per load.
+    // Stage the input halo tile, 16 channels (one 128-bit word) per load; padding holds the activation zero point.
     const uint32_t padw = (uint32_t)(d.x_zp & 0xff) * 0x01010101u;
     for (int i = tid; i < IH * IW * 4; i += 256) {
         const int cg = i & 3;
@@ -69,6 +88,13 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
         *reinterpret_cast<uint4*>(s_in + (size_t)p * kCC + cg * 16) = v;
     }
     __syncthreads();
+    if (tid < kCC) {
+        int sum = 0;
+        for (int t = 0; t < taps; ++t) sum += (int)(int8_t)(s_w[t * kCC + tid] >> (8 * (tid & 3)));
+        s_wsum[tid] = sum;
+    }
+    const bool wide = s_wide != 0;
+    __syncthreads();
 
     const int cg = tid & 3;
     const int p = tid >> 2;
@@ -79,20 +105,47 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
     int acc[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) acc[j] = 0;
-    for (int kh = 0; kh < d.KH; ++kh) {
-        for (int kw = 0; kw < d.KW; ++kw) {
-            const int ih = ph * d.sh + kh, iw = pw * d.sw + kw;
-            const uint4 xv = *reinterpret_cast<const uint4*>(s_in + (size_t)(ih * IW + iw) * kCC + cg * 16);
-            const uint4* wp = reinterpret_cast<const uint4*>(s_w + (kh * d.KW + kw) * kCC + cg * 16);
-            const uint4 w0 = wp[0], w1 = wp[1];
-            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-            const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    if (!wide) {
+        // acc = sum_taps x_q * (w - w_zp); the activation zero point comes off afterwards as x_zp * sum_taps (w - w_zp)
+        // (padding positions hold x_zp, so they cancel exactly).
+        for (int kh = 0; kh < d.KH; ++kh) {
+            for (int kw = 0; kw < d.KW; ++kw) {
+                const int ih = ph * d.sh + kh, iw = pw * d.sw + kw;
+                const uint4 xv = *reinterpret_cast<const uint4*>(s_in + (size_t)(ih * IW + iw) * kCC + cg * 16);
+                const uint4* wp = reinterpret_cast<const uint4*>(s_w + (kh * d.KW + kw) * kCC + cg * 16);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const uint32_t xb = (xw[j >> 2] >> (8 * (j & 3))) & 0xffu;
-                const int xq = (d.x_signed ? (int)(int8_t)xb : (int)xb) - d.x_zp;
-                const int wq = (int)(int16_t)((ww[j >> 1] >> (16 * (j & 1))) & 0xffffu);
-                acc[j] += xq * wq;
+                for (int g = 0; g < 4; ++g) {
+                    const uint4 w4 = wp[g];
+                    acc[4 * g + 0] = dp4a_xs<kXSigned>(xw[g], w4.x, acc[4 * g + 0]);
+                    acc[4 * g + 1] = dp4a_xs<kXSigned>(xw[g], w4.y, acc[4 * g + 1]);
+                    acc[4 * g + 2] = dp4a_xs<kXSigned>(xw[g], w4.z, acc[4 * g + 2]);
+                    acc[4 * g + 3] = dp4a_xs<kXSigned>(xw[g], w4.w, acc[4 * g + 3]);
+                }
+            }
+        }
+        if (d.x_zp != 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] -= d.x_zp * s_wsum[cg * 16 + j];
+        }
+    } else {
+        // (w - w_zp) needs nine bits (uint8 weights with a large zero point): scalar multiply per byte.
+        for (int kh = 0; kh < d.KH; ++kh) {
+            for (int kw = 0; kw < d.KW; ++kw) {
+                const int ih = ph * d.sh + kh, iw = pw * d.sw + kw;
+                const uint8_t* xp = s_in + (size_t)(ih * IW + iw) * kCC + cg * 16;
+                const int tap = kh * d.KW + kw;
+                for (int j = 0; j < 16; ++j) {
+                    const int c = c0 + cg * 16 + j;
+                    const int64_t wi = (int64_t)c * taps + tap;
+                    int wv = d.w_signed ? (int)static_cast<const int8_t*>(w)[wi] : (int)static_cast<const uint8_t*>(w)[wi];
+                    if (d.w_zp_len > 0) {
+                        const int64_t zi = d.w_zp_len == 1 ? 0 : c;
+                        wv -= d.w_signed ? (int)static_cast<const int8_t*>(w_zp)[zi] : (int)static_cast<const uint8_t*>(w_zp)[zi];
+                    }
+                    const int xq = (kXSigned ? (int)(int8_t)xp[j] : (int)xp[j]) - d.x_zp;
+                    acc[j] += xq * wv;
+                }
             }
         }
     }
@@ -102,6 +155,7 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
         const uint4 r = *reinterpret_cast<const uint4*>(epi.residual + o);
         resw[0] = r.x; resw[1] = r.y; resw[2] = r.z; resw[3] = r.w;
     }
+    const bool fast = !epi.rq.y_signed && epi.rq.round_mode == 0;
     uint32_t outw[4];
 #pragma unroll
     for (int wv = 0; wv < 4; ++wv) {
@@ -110,8 +164,13 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
         for (int b = 0; b < 4; ++b) {
             const int j = wv * 4 + b, c = c0 + cg * 16 + j;
             const int bias = epi.bias ? epi.bias[c] : 0;
-            const int q = epi_requant(epi, acc[j], epi_mult(epi, c), bias, (int)((resw[wv] >> (8 * b)) & 0xffu));
-            o32 |= ((uint32_t)q & 0xffu) << (8 * b);
+            const uint32_t rb = (resw[wv] >> (8 * b)) & 0xffu;
+            uint32_t q;
+            if (fast)
+                q = requant_u8_up_fast(acc[j], bias, epi_mult(epi, c), epi.residual != nullptr, rb, epi.rq);
+            else
+                q = (uint32_t)epi_requant(epi, acc[j], epi_mult(epi, c), bias, (int)rb) & 0xffu;
+            o32 |= q << (8 * b);
         }
         outw[wv] = o32;
     }
@@ -144,12 +203,15 @@ int launch_depthwise(
     d.tiles_w = (g.Wo + kTW - 1) / kTW;
     const int tiles_h = (g.Ho + kTH - 1) / kTH;
     const int IH = (kTH - 1) * d.sh + d.KH, IW = (kTW - 1) * d.sw + d.KW;
-    const size_t smem = ((size_t)(IH * IW * kCC + 15) & ~(size_t)15) + (size_t)g.KH * g.KW * kCC * 2;
-    if (smem > 48 * 1024) {
-        CHXQ_CUDA(cudaFuncSetAttribute(depthwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    }
+    const size_t smem = ((size_t)(IH * IW * kCC + 15) & ~(size_t)15) + (size_t)g.KH * g.KW * kCC * 4 + kCC * 4;
     dim3 grid((unsigned)(d.tiles_w * tiles_h), (unsigned)((g.C + kCC - 1) / kCC), (unsigned)g.N);
-    depthwise_kernel<<<grid, 256, smem, s>>>(static_cast<const uint8_t*>(x), w, w_zp, d, epi, static_cast<uint8_t*>(y));
+    if (d.x_signed) {
+        if (smem > 48 * 1024) CHXQ_CUDA(cudaFuncSetAttribute(depthwise_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        depthwise_kernel<true><<<grid, 256, smem, s>>>(static_cast<const uint8_t*>(x), w, w_zp, d, epi, static_cast<uint8_t*>(y));
+    } else {
+        if (smem > 48 * 1024) CHXQ_CUDA(cudaFuncSetAttribute(depthwise_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        depthwise_kernel<false><<<grid, 256, smem, s>>>(static_cast<const uint8_t*>(x), w, w_zp, d, epi, static_cast<uint8_t*>(y));
+    }
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }

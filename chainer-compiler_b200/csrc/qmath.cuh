@@ -5,6 +5,7 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 namespace chxq {
 
@@ -18,6 +19,58 @@ __device__ __forceinline__ int cvt_rne_sat_u8(float t) {
     uint32_t q;
     asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(t));
     return (int)q;
+}
+
+// Division by a scale that is constant for a whole kernel, without the per-element reciprocal of the general IEEE
+// sequence: q0 = x * r with r = RN(1/s) from the host, then two residual corrections q <- fma(fma(-q, s, x), r, q).
+// After the first correction the quotient is faithful; the second, from an exact residual, makes it the correctly
+// rounded x / s (Markstein's scheme; a scale whose significand is all ones is the known exception and is sent to the
+// general path by make_qdiv, as are scales outside a safe exponent range).  Quotients of magnitude >= 1e18 (and NaN) take
+// the general division; below 2^-60 the value returned may be inexact, which no quantization can observe.
+struct QDiv {
+    float s, r;
+    int fast;
+};
+
+inline QDiv make_qdiv(float s) {
+    QDiv d;
+    d.s = s;
+    d.r = 1.0f / s;
+    uint32_t bits;
+    memcpy(&bits, &s, 4);
+    const float a = s < 0 ? -s : s;
+    d.fast = (a > 1e-15f && a < 1e15f && (bits & 0x7fffffu) != 0x7fffffu) ? 1 : 0;
+    return d;
+}
+
+// The corrected quotient without the magnitude guard, and the guard on its own: a caller dividing many values can test
+// them together and redo the few that need the general division.
+__device__ __forceinline__ float qdiv_unguarded(float x, const QDiv& d, bool* needs_general) {
+    const float q0 = __fmul_rn(x, d.r);
+    float rem = __fmaf_rn(-q0, d.s, x);
+    float q = __fmaf_rn(rem, d.r, q0);
+    rem = __fmaf_rn(-q, d.s, x);
+    q = __fmaf_rn(rem, d.r, q);
+    *needs_general = *needs_general || !(fabsf(q0) < 1.0e18f);
+    return q;
+}
+
+__device__ __forceinline__ float qdiv(float x, const QDiv& d) {
+    if (!d.fast) return __fdiv_rn(x, d.s);
+    const float q0 = __fmul_rn(x, d.r);
+    float rem = __fmaf_rn(-q0, d.s, x);
+    float q = __fmaf_rn(rem, d.r, q0);
+    rem = __fmaf_rn(-q, d.s, x);
+    q = __fmaf_rn(rem, d.r, q);
+    if (!(fabsf(q0) < 1.0e18f)) q = __fdiv_rn(x, d.s);
+    return q;
+}
+
+// quantize_one for a uint8 output (round-half-up) on a pre-divided value, conversion-free: byte in the low bits of
+// the returned word.
+__device__ __forceinline__ uint32_t quantize_u8_up_bits(float t, float zp_f) {
+    t = __fadd_rn(__fadd_rn(t, zp_f), 0.5f);  // adding a zero zero point is exact
+    return __float_as_uint(__fadd_rd(fminf(fmaxf(t, 0.f), 255.5f), 8388608.f)) & 0xffu;
 }
 
 // One element of quantize_array (runtime/ops/quantize.cc:29-34): t = x / s; (+zp); min(hi);
@@ -78,7 +131,14 @@ struct RequantParams {
     int fold;
     float y_over_out;    // y_scale / out_scale
     float res_over_out;  // res_scale / out_scale
+    // constant-divisor forms of y_scale and out_scale (see QDiv)
+    QDiv y_div, out_div;
 };
+
+inline void finish_requant_params(RequantParams* p) {
+    p->y_div = make_qdiv(p->y_scale);
+    p->out_div = make_qdiv(p->out_scale != 0.f ? p->out_scale : 1.f);
+}
 
 // acc (exact int32, bias already added) -> quantized output value.
 __device__ __forceinline__ int requant_one(int acc, float mult, const RequantParams& p) {
@@ -142,6 +202,38 @@ __device__ __forceinline__ uint32_t magic_byte(float f) {
 // The float 2^23 + byte `sel` (0..3) of word w.
 __device__ __forceinline__ float byte_to_magic(uint32_t w, int sel) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 | sel) );
+}
+
+// uint8, round-half-up requantization of one accumulator (+ optional residual tail) without conversion instructions other
+// than the int -> float of the accumulator; equals requant_one / residual_one (reference operation order, fold == 0) or
+// requant_u8_fold / residual_fold (fold != 0) bit for bit.  Returns the output byte.
+__device__ __forceinline__ uint32_t requant_u8_up_fast(int acc, int bias, float mult, bool has_res, uint32_t res_byte, const RequantParams& p) {
+    const float hi_ph = (p.clamp_hi_q >= 0 ? (float)p.clamp_hi_q : 255.f) + 0.5f;
+    float tp;
+    if (p.fold) {
+        const float m = __fdiv_rn(mult, p.y_scale);
+        tp = __fmaf_rn((float)acc, m, __fmaf_rn((float)bias, m, __fadd_rn(p.y_zp_f, 0.5f)));
+    } else {
+        tp = qdiv(__fmul_rn((float)(int)((unsigned)acc + (unsigned)bias), mult), p.y_div);
+        tp = __fadd_rn(__fadd_rn(tp, p.y_zp_f), 0.5f);
+    }
+    float f = quant_u8_up_magic(tp, hi_ph);
+    if (has_res) {
+        const float u = __fsub_rn(f, __fadd_rn(kMagic23, p.y_zp_f));
+        const float w = __fsub_rn(__uint_as_float(0x4B000000u | (res_byte & 0xffu)), __fadd_rn(kMagic23, p.res_zp_f));
+        float v;
+        if (p.fold) {
+            v = __fmaf_rn(w, p.res_over_out, __fmul_rn(u, p.y_over_out));
+            if (p.res_relu) v = fmaxf(v, 0.f);
+            v = __fadd_rn(v, __fadd_rn(p.out_zp_f, 0.5f));
+        } else {
+            v = __fadd_rn(__fmul_rn(u, p.y_scale), __fmul_rn(w, p.res_scale));
+            if (p.res_relu) v = fmaxf(v, 0.f);
+            v = __fadd_rn(__fadd_rn(qdiv(v, p.out_div), p.out_zp_f), 0.5f);
+        }
+        f = quant_u8_up_magic(v, 255.5f);
+    }
+    return __float_as_uint(f) & 0xffu;
 }
 
 // DequantizeLinear(y), DequantizeLinear(r), Add, Relu, QuantizeLinear on one element.

@@ -47,24 +47,45 @@ namespace {
 
 constexpr int kThreads = 256;
 
-template <bool kSigned>
+// 16 elements per thread per step as four 128-bit loads and four 32-bit stores; lane i of a warp touches the i-th
+// 16 bytes (load) / 4 bytes (store) of a contiguous span, so every memory instruction is fully coalesced.
+// kMode: 0 = uint8 round-half-up through the constant-divisor division and add-based rounding (no conversion or
+// reciprocal instruction per element); 1 = general (int8 outputs, round-half-to-even, unusual scales).
+template <bool kSigned, int kMode>
 __global__ void __launch_bounds__(kThreads) quantize_vec16_kernel(
-        const float4* __restrict__ x, int64_t n16, float scale, float zp_f, int has_zp, int round_mode, uint4* __restrict__ y) {
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        const float4* __restrict__ x, int64_t n4, float scale, QDiv dv, float zp_f, int has_zp, int round_mode, uint32_t* __restrict__ y) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x * 4;
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x * 4 + threadIdx.x; base < n4; base += step) {
         float4 v[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = __ldcs(x + i * 4 + j);
-        uint32_t w[4];
+        for (int j = 0; j < 4; ++j) {
+            const int64_t g = base + (int64_t)j * blockDim.x;
+            v[j] = g < n4 ? __ldcs(x + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const uint32_t q0 = (uint32_t)quantize_one<kSigned>(v[j].x, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
-            const uint32_t q1 = (uint32_t)quantize_one<kSigned>(v[j].y, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
-            const uint32_t q2 = (uint32_t)quantize_one<kSigned>(v[j].z, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
-            const uint32_t q3 = (uint32_t)quantize_one<kSigned>(v[j].w, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
-            w[j] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+            const int64_t g = base + (int64_t)j * blockDim.x;
+            uint32_t q0, q1, q2, q3;
+            if (kMode == 0) {
+                bool general = false;  // one magnitude test for the four quotients; the rare group that fails is redone
+                q0 = quantize_u8_up_bits(qdiv_unguarded(v[j].x, dv, &general), zp_f);
+                q1 = quantize_u8_up_bits(qdiv_unguarded(v[j].y, dv, &general), zp_f);
+                q2 = quantize_u8_up_bits(qdiv_unguarded(v[j].z, dv, &general), zp_f);
+                q3 = quantize_u8_up_bits(qdiv_unguarded(v[j].w, dv, &general), zp_f);
+                if (general) {
+                    q0 = (uint32_t)quantize_one<false>(v[j].x, scale, zp_f, has_zp != 0, 0);
+                    q1 = (uint32_t)quantize_one<false>(v[j].y, scale, zp_f, has_zp != 0, 0);
+                    q2 = (uint32_t)quantize_one<false>(v[j].z, scale, zp_f, has_zp != 0, 0);
+                    q3 = (uint32_t)quantize_one<false>(v[j].w, scale, zp_f, has_zp != 0, 0);
+                }
+            } else {
+                q0 = (uint32_t)quantize_one<kSigned>(v[j].x, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
+                q1 = (uint32_t)quantize_one<kSigned>(v[j].y, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
+                q2 = (uint32_t)quantize_one<kSigned>(v[j].z, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
+                q3 = (uint32_t)quantize_one<kSigned>(v[j].w, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
+            }
+            if (g < n4) __stcs(y + g, q0 | (q1 << 8) | (q2 << 16) | (q3 << 24));
         }
-        y[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -77,25 +98,36 @@ __global__ void __launch_bounds__(kThreads) quantize_scalar_kernel(
     }
 }
 
+// 16 elements per thread per step as four 32-bit loads and four 128-bit stores, coalesced like the quantize kernel.
 template <bool kSigned>
 __global__ void __launch_bounds__(kThreads) dequantize_vec16_kernel(
-        const uint4* __restrict__ x, int64_t n16, float scale, float zp_f, int has_zp, float4* __restrict__ y) {
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
-        const uint4 q = __ldcs(x + i);
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        const uint32_t* __restrict__ x, int64_t n4, float scale, float zp_f, int has_zp, float4* __restrict__ y) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x * 4;
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x * 4 + threadIdx.x; base < n4; base += step) {
+        uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
+            const int64_t g = base + (int64_t)j * blockDim.x;
+            w[j] = g < n4 ? __ldcs(x + g) : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t g = base + (int64_t)j * blockDim.x;
             float4 o;
-            auto get = [&](int b) -> int {
-                const uint32_t u = (w[j] >> (8 * b)) & 0xffu;
-                return kSigned ? (int)(int8_t)u : (int)u;
-            };
-            o.x = dequantize_one(get(0), scale, zp_f, has_zp != 0);
-            o.y = dequantize_one(get(1), scale, zp_f, has_zp != 0);
-            o.z = dequantize_one(get(2), scale, zp_f, has_zp != 0);
-            o.w = dequantize_one(get(3), scale, zp_f, has_zp != 0);
-            __stcs(y + i * 4 + j, o);
+            if (kSigned) {
+                o.x = dequantize_one((int)(int8_t)(w[j] & 0xffu), scale, zp_f, has_zp != 0);
+                o.y = dequantize_one((int)(int8_t)((w[j] >> 8) & 0xffu), scale, zp_f, has_zp != 0);
+                o.z = dequantize_one((int)(int8_t)((w[j] >> 16) & 0xffu), scale, zp_f, has_zp != 0);
+                o.w = dequantize_one((int)(int8_t)(w[j] >> 24), scale, zp_f, has_zp != 0);
+            } else {
+                // byte -> float without a conversion instruction: 2^23 + b as a bit pattern, minus (2^23 + zp), exactly b - zp
+                const float c = __fadd_rn(8388608.f, zp_f);
+                o.x = __fmul_rn(__fsub_rn(byte_to_magic(w[j], 0), c), scale);
+                o.y = __fmul_rn(__fsub_rn(byte_to_magic(w[j], 1), c), scale);
+                o.z = __fmul_rn(__fsub_rn(byte_to_magic(w[j], 2), c), scale);
+                o.w = __fmul_rn(__fsub_rn(byte_to_magic(w[j], 3), c), scale);
+            }
+            if (g < n4) __stcs(y + g, o);
         }
     }
 }
@@ -241,17 +273,20 @@ extern "C" int chxq_quantize_linear(
     const float zp_f = (float)y_zero_point;
     const int has_zp = y_zero_point != 0;
     int64_t done = 0;
-    if (aligned16(x) && aligned16(y) && n >= 16) {
-        const int64_t n16 = n / 16;
-        const int grid = grid_for(n16, 8);
+    if (aligned16(x) && (reinterpret_cast<uintptr_t>(y) & 3u) == 0 && n >= 4) {
+        const int64_t n4 = n / 4;
+        const int grid = grid_for((n4 + 3) / 4, 8);
+        const QDiv dv = make_qdiv(y_scale);
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        uint32_t* y32 = reinterpret_cast<uint32_t*>(y);
         if (sgn)
-            quantize_vec16_kernel<true><<<grid, kThreads, 0, s>>>(reinterpret_cast<const float4*>(x), n16, y_scale, zp_f, has_zp, round_mode,
-                                                                  reinterpret_cast<uint4*>(y));
+            quantize_vec16_kernel<true, 1><<<grid, kThreads, 0, s>>>(x4, n4, y_scale, dv, zp_f, has_zp, round_mode, y32);
+        else if (round_mode == CHXQ_ROUND_REF_HALF_UP && dv.fast)
+            quantize_vec16_kernel<false, 0><<<grid, kThreads, 0, s>>>(x4, n4, y_scale, dv, zp_f, has_zp, round_mode, y32);
         else
-            quantize_vec16_kernel<false><<<grid, kThreads, 0, s>>>(reinterpret_cast<const float4*>(x), n16, y_scale, zp_f, has_zp,
-                                                                   round_mode, reinterpret_cast<uint4*>(y));
+            quantize_vec16_kernel<false, 1><<<grid, kThreads, 0, s>>>(x4, n4, y_scale, dv, zp_f, has_zp, round_mode, y32);
         CHXQ_LAUNCH_CHECK();
-        done = n16 * 16;
+        done = n4 * 4;
     }
     if (done < n) {
         const int grid = grid_for(n - done, 8);
@@ -275,17 +310,17 @@ extern "C" int chxq_dequantize_linear(
     const float zp_f = (float)x_zero_point;
     const int has_zp = x_zero_point != 0;
     int64_t done = 0;
-    if (aligned16(x) && aligned16(y) && n >= 16) {
-        const int64_t n16 = n / 16;
-        const int grid = grid_for(n16, 8);
+    if ((reinterpret_cast<uintptr_t>(x) & 3u) == 0 && aligned16(y) && n >= 4) {
+        const int64_t n4 = n / 4;
+        const int grid = grid_for((n4 + 3) / 4, 8);
         if (sgn)
-            dequantize_vec16_kernel<true><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint4*>(x), n16, x_scale, zp_f, has_zp,
+            dequantize_vec16_kernel<true><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint32_t*>(x), n4, x_scale, zp_f, has_zp,
                                                                     reinterpret_cast<float4*>(y));
         else
-            dequantize_vec16_kernel<false><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint4*>(x), n16, x_scale, zp_f, has_zp,
+            dequantize_vec16_kernel<false><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint32_t*>(x), n4, x_scale, zp_f, has_zp,
                                                                      reinterpret_cast<float4*>(y));
         CHXQ_LAUNCH_CHECK();
-        done = n16 * 16;
+        done = n4 * 4;
     }
     if (done < n) {
         const int grid = grid_for(n - done, 8);
@@ -316,6 +351,7 @@ extern "C" int chxq_qadd_u8(
     p.out_zp_f = (float)y_zp;
     p.out_has_zp = y_zp != 0;
     p.round_mode = round_mode;
+    finish_requant_params(&p);
     const int vec_ok = aligned16(a) && aligned16(b) && aligned16(y);
     qadd_u8_kernel<<<grid_for((n + 15) / 16, 8), kThreads, 0, as_stream(stream)>>>(a, b, n, p, y, vec_ok);
     CHXQ_LAUNCH_CHECK();

@@ -496,7 +496,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                 if (kFold) {
                                     tp = __fmaf_rn(a, mm[b], __uint_as_float(addw[4 * j + b]));
                                 } else {
-                                    tp = __fdiv_rn(__fmul_rn(a, mm[b]), rq.y_scale);
+                                    tp = qdiv(__fmul_rn(a, mm[b]), rq.y_div);
                                     tp = __fadd_rn(__fadd_rn(tp, rq.y_zp_f), 0.5f);
                                 }
                                 fb[b] = __float_as_uint(quant_u8_up_magic(tp, hi_ph));
@@ -513,7 +513,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                     } else {
                                         v = __fadd_rn(__fmul_rn(u, rq.y_scale), __fmul_rn(w, rq.res_scale));
                                         v = fmaxf(v, relu_floor);
-                                        v = __fdiv_rn(v, rq.out_scale);
+                                        v = qdiv(v, rq.out_div);
                                     }
                                     const float tp = kFold ? __fadd_rn(v, out_half) : __fadd_rn(__fadd_rn(v, rq.out_zp_f), 0.5f);
                                     fb[b] = __float_as_uint(quant_u8_up_magic(tp, 255.5f));

@@ -209,6 +209,27 @@ def test_depthwise_qlinear_conv(ops, orc, dev, C, H, W, k, stride, pad):
         assert lsb_report(exact, emul)[0] <= 1
 
 
+def test_depthwise_uint8_weights_with_zero_points(ops, orc, dev):
+    """uint8 depthwise weights: (w - w_zp) fits int8 for one channel set (dot-product path) and needs nine bits for another
+    (scalar path); int8 activations; folded scales; residual tail."""
+    rng = np.random.default_rng(31)
+    C = 64
+    for x_dtype, zx, wlo, whi, zlo, zhi in ((np.uint8, 3, 100, 160, 110, 150), (np.uint8, 0, 0, 255, 0, 255), (np.int8, -5, 90, 170, 120, 140)):
+        x = _rand(rng, (2, C, 11, 9), x_dtype)
+        w = _rand(rng, (C, 1, 3, 3), np.uint8, wlo, whi)
+        wz = _rand(rng, C, np.uint8, zlo, zhi)
+        ws = rng.uniform(0.001, 0.004, C).astype(np.float32)
+        r = _rand(rng, (2, C, 11, 9), np.uint8)
+        for fold in (False, True):
+            y = ops.QLinearConv(_t(x, dev, True), 0.02, x_dtype(zx), _t(w, dev), _t(ws, dev), _t(wz, dev), 0.03, np.uint8(20), None, (1, 1), (1, 1), C,
+                                fold_scales=fold, residual=_t(r, dev, True), res_scale=0.04, res_zero_point=3, out_scale=0.05, out_zero_point=0)
+            acc = orc.conv_integer(x, w, zx, wz, (1, 1), (1, 1), C)
+            y1 = orc.requantize(acc, 0.02, ws, 0.03, 20, channel_axis=1, fold=fold)
+            want = orc.qadd_relu(y1, 0.03, 20, r, 0.04, 3, 0.05, 0, relu=True, fold=fold)
+            assert np.array_equal(y.cpu().numpy(), want)
+    ops.device_status()
+
+
 def test_golden_conv(ops, dev):
     g = np.load(GOLDEN)
     x, w, zw = g["cv_x"], g["cv_w"], g["cv_zw"]

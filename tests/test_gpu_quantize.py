@@ -120,3 +120,31 @@ def test_glue_kernels(ops, orc, dev):
     assert torch.equal(ops.to_contiguous_nchw(ops.to_channels_last(nchw)), nchw)
     assert torch.equal(ops.to_channels_last(nchw), xt)
     ops.device_status()
+
+
+def test_quantize_division_is_correctly_rounded(ops, orc, dev):
+    """The uint8 round-half-up kernel divides by the (constant) scale with a reciprocal and two residual corrections instead
+    of an IEEE division per element.  Values sitting one or two ulps either side of every rounding boundary, over ordinary,
+    power-of-two, nearly-power-of-two, tiny and huge scales, must still quantize exactly as x / scale does."""
+    rng = np.random.default_rng(123)
+    scales = [1.0 / 255.0, 0.02, 0.25, 3.0, 1e-3, 0.0123456, np.float32(1.9999999), np.float32(1.0000001), 7e-9, 3.3e7, 1e-20, 1e20,
+              float(np.nextafter(np.float32(0.5), np.float32(0)))] + list(rng.uniform(1e-4, 10.0, 12).astype(np.float32))
+    k = np.arange(-4, 262, dtype=np.float64)
+    for s in scales:
+        s32 = np.float32(s)
+        base = ((k + 0.5) * np.float64(s32)).astype(np.float32)  # boundaries of the half-up rounding
+        xs = [base]
+        for ulps in (1, 2, 3):
+            up, dn = base.copy(), base.copy()
+            for _ in range(ulps):
+                up = np.nextafter(up, np.float32(np.inf))
+                dn = np.nextafter(dn, np.float32(-np.inf))
+            xs += [up, dn]
+        xs.append((rng.uniform(-5, 300, 200000) * np.float64(s32)).astype(np.float32))
+        xs.append(np.array([0.0, -0.0, np.inf, -np.inf, 1e38, -1e38, 1e-45, 1e-38], np.float32))
+        x = np.concatenate(xs).astype(np.float32)
+        x = np.concatenate([x, x[: (-len(x)) % 4]])
+        for zp in (0, 7):
+            got = ops.QuantizeLinear(torch.from_numpy(x).to(dev), float(s32), np.uint8(zp)).cpu().numpy()
+            want = orc.quantize_linear(x, s32, zp)
+            assert np.array_equal(got, want), "scale %r zero point %d: %d mismatches" % (s, zp, int((got != want).sum()))
