@@ -3,9 +3,8 @@
 // halo tile is staged into shared memory with 128-bit loads (positions in the convolution's padding
 // are filled with the activation zero point, i.e. 0 after zero-point subtraction, which is where the
 // reference pads: runtime/ops/quantize.cc:65-72 dequantizes before chainerx::Conv zero-pads), the
-// per-channel taps are staged as (w - w_zp) in the byte lane of their channel so that the multiply-accumulate is a
-// four-way dot product with no byte extraction, every thread accumulates 16 channels of one position in registers
-// and stores one 128-bit word of requantized output.
+// per-channel taps are staged as 32-bit (w - w_zp), every thread accumulates 16 channels of one position in registers
+// (one byte permute and one integer multiply-add per tap and channel) and stores one 128-bit word of requantized output.
 //
 // The reference runs this as `group` separate fp32 convolutions plus a concatenate
 // (runtime/chainerx_util.cc:328-339): 960 launches for one MobileNetV2 layer.
@@ -27,15 +26,15 @@ struct DwDesc {
     int tiles_w;
 };
 
-// u8 (or s8) x s8 four-way dot product with accumulate.
-template <bool kXSigned>
-__device__ __forceinline__ int dp4a_xs(uint32_t x, uint32_t w, int acc) {
-    int d;
-    if (kXSigned)
-        asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
-    else
-        asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
-    return d;
+// Byte `sel` of word w, zero- or sign-extended, in one permute: prmt's selector nibble n picks byte n of {w, 0}; with
+// bit 3 of the nibble set it replicates that byte's sign bit instead.
+template <bool kSigned>
+__device__ __forceinline__ int byte_of(uint32_t w, int sel) {
+    const uint32_t s8 = 8u | (uint32_t)sel;
+    const uint32_t selector = kSigned ? ((uint32_t)sel | (s8 << 4) | (s8 << 8) | (s8 << 12)) : (0x4440u | (uint32_t)sel);
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(0u), "r"(selector));
+    return (int)d;
 }
 
 template <bool kXSigned>
@@ -44,10 +43,9 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
     extern __shared__ __align__(16) uint8_t smem[];
     const int IH = (kTH - 1) * d.sh + d.KH, IW = (kTW - 1) * d.sw + d.KW;
     const int taps = d.KH * d.KW;
-    uint8_t* s_in = smem;                                                               // [IH][IW][64] bytes
-    uint32_t* s_w = reinterpret_cast<uint32_t*>(smem + ((IH * IW * kCC + 15) & ~15));  // [taps][64] words: (w - w_zp) in byte (c & 3)
-    int* s_wsum = reinterpret_cast<int*>(s_w + taps * kCC);                            // [64] sum over taps of (w - w_zp)
-    __shared__ int s_wide;                                                              // some (w - w_zp) does not fit int8
+    uint8_t* s_in = smem;                                                     // [IH][IW][64] bytes
+    int* s_w = reinterpret_cast<int*>(smem + ((IH * IW * kCC + 15) & ~15));  // [taps][64]: w - w_zp
+    int* s_wsum = s_w + taps * kCC;                                          // [64]: sum over taps of (w - w_zp)
 
     const int tile = blockIdx.x;
     const int th = tile / d.tiles_w, tw = tile % d.tiles_w;
@@ -56,11 +54,8 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
     const int ho0 = th * kTH, wo0 = tw * kTW;
     const int hi0 = ho0 * d.sh - d.pt, wi0 = wo0 * d.sw - d.pl;
     const int tid = threadIdx.x;
-    if (tid == 0) s_wide = 0;
-    __syncthreads();
 
-    // Stage the taps of this channel block.  The multiply runs as a four-way dot product whose weight word holds one
-    // non-zero byte -- the tap of channel c in byte (c & 3) -- so no byte of the activation word has to be extracted.
+    // Stage the taps of this channel block as 32-bit (w - w_zp).
     for (int i = tid; i < taps * kCC; i += 256) {
         const int c = i % kCC, tap = i / kCC;
         int v = 0;
@@ -72,8 +67,7 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
                 v -= d.w_signed ? (int)static_cast<const int8_t*>(w_zp)[zi] : (int)static_cast<const uint8_t*>(w_zp)[zi];
             }
         }
-        if (v < -128 || v > 127) s_wide = 1;
-        s_w[i] = ((uint32_t)v & 0xffu) << (8 * (c & 3));
+        s_w[i] = v;
     }
     // Stage the input halo tile, 16 channels (one 128-bit word) per load; padding holds the activation zero point.
     const uint32_t padw = (uint32_t)(d.x_zp & 0xff) * 0x01010101u;
@@ -90,10 +84,9 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
     __syncthreads();
     if (tid < kCC) {
         int sum = 0;
-        for (int t = 0; t < taps; ++t) sum += (int)(int8_t)(s_w[t * kCC + tid] >> (8 * (tid & 3)));
+        for (int t = 0; t < taps; ++t) sum += s_w[t * kCC + tid];
         s_wsum[tid] = sum;
     }
-    const bool wide = s_wide != 0;
     __syncthreads();
 
     const int cg = tid & 3;
@@ -102,52 +95,30 @@ __global__ void __launch_bounds__(256) depthwise_kernel(
     const int ho = ho0 + ph, wo = wo0 + pw;
     if (ho >= d.Ho || wo >= d.Wo || c0 + cg * 16 >= d.C) return;
 
+    // acc = sum_taps x_q * (w - w_zp); the activation zero point comes off afterwards as x_zp * sum_taps (w - w_zp)
+    // (padding positions hold x_zp, so they cancel exactly).
     int acc[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) acc[j] = 0;
-    if (!wide) {
-        // acc = sum_taps x_q * (w - w_zp); the activation zero point comes off afterwards as x_zp * sum_taps (w - w_zp)
-        // (padding positions hold x_zp, so they cancel exactly).
-        for (int kh = 0; kh < d.KH; ++kh) {
-            for (int kw = 0; kw < d.KW; ++kw) {
-                const int ih = ph * d.sh + kh, iw = pw * d.sw + kw;
-                const uint4 xv = *reinterpret_cast<const uint4*>(s_in + (size_t)(ih * IW + iw) * kCC + cg * 16);
-                const uint4* wp = reinterpret_cast<const uint4*>(s_w + (kh * d.KW + kw) * kCC + cg * 16);
-                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    for (int kh = 0; kh < d.KH; ++kh) {
+        for (int kw = 0; kw < d.KW; ++kw) {
+            const int ih = ph * d.sh + kh, iw = pw * d.sw + kw;
+            const uint4 xv = *reinterpret_cast<const uint4*>(s_in + (size_t)(ih * IW + iw) * kCC + cg * 16);
+            const int4* wp = reinterpret_cast<const int4*>(s_w + (kh * d.KW + kw) * kCC + cg * 16);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const uint4 w4 = wp[g];
-                    acc[4 * g + 0] = dp4a_xs<kXSigned>(xw[g], w4.x, acc[4 * g + 0]);
-                    acc[4 * g + 1] = dp4a_xs<kXSigned>(xw[g], w4.y, acc[4 * g + 1]);
-                    acc[4 * g + 2] = dp4a_xs<kXSigned>(xw[g], w4.z, acc[4 * g + 2]);
-                    acc[4 * g + 3] = dp4a_xs<kXSigned>(xw[g], w4.w, acc[4 * g + 3]);
-                }
+            for (int g = 0; g < 4; ++g) {
+                const int4 w4 = wp[g];
+                acc[4 * g + 0] += byte_of<kXSigned>(xw[g], 0) * w4.x;
+                acc[4 * g + 1] += byte_of<kXSigned>(xw[g], 1) * w4.y;
+                acc[4 * g + 2] += byte_of<kXSigned>(xw[g], 2) * w4.z;
+                acc[4 * g + 3] += byte_of<kXSigned>(xw[g], 3) * w4.w;
             }
         }
-        if (d.x_zp != 0) {
+    }
+    if (d.x_zp != 0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] -= d.x_zp * s_wsum[cg * 16 + j];
-        }
-    } else {
-        // (w - w_zp) needs nine bits (uint8 weights with a large zero point): scalar multiply per byte.
-        for (int kh = 0; kh < d.KH; ++kh) {
-            for (int kw = 0; kw < d.KW; ++kw) {
-                const int ih = ph * d.sh + kh, iw = pw * d.sw + kw;
-                const uint8_t* xp = s_in + (size_t)(ih * IW + iw) * kCC + cg * 16;
-                const int tap = kh * d.KW + kw;
-                for (int j = 0; j < 16; ++j) {
-                    const int c = c0 + cg * 16 + j;
-                    const int64_t wi = (int64_t)c * taps + tap;
-                    int wv = d.w_signed ? (int)static_cast<const int8_t*>(w)[wi] : (int)static_cast<const uint8_t*>(w)[wi];
-                    if (d.w_zp_len > 0) {
-                        const int64_t zi = d.w_zp_len == 1 ? 0 : c;
-                        wv -= d.w_signed ? (int)static_cast<const int8_t*>(w_zp)[zi] : (int)static_cast<const uint8_t*>(w_zp)[zi];
-                    }
-                    const int xq = (kXSigned ? (int)(int8_t)xp[j] : (int)xp[j]) - d.x_zp;
-                    acc[j] += xq * wv;
-                }
-            }
-        }
+        for (int j = 0; j < 16; ++j) acc[j] -= d.x_zp * s_wsum[cg * 16 + j];
     }
     const int64_t o = (((int64_t)n * d.Ho + ho) * d.Wo + wo) * d.y_cs + c0 + cg * 16;
     uint32_t resw[4] = {0u, 0u, 0u, 0u};

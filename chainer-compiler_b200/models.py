@@ -279,3 +279,258 @@ class QuantizedMLP:
         for l in self.layers:
             h = ops.QLinearMatMul(h, self.act_scale, np.uint8(0), l["dev"], l["w_scale"], np.int8(0), self.act_scale, np.uint8(0), path=path)
         return ops.DequantizeLinear(h, self.act_scale, np.uint8(0))
+
+
+# (expansion t, output channels c, repeats n, stride s) of MobileNetV2-1.0.
+MOBILENETV2_BLOCKS = [(1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)]
+
+
+def _pad16(c):
+    return (c + 15) // 16 * 16
+
+
+class _QLayer:
+    """One quantized convolution of MobileNetV2 (dense 1x1 / stem, or depthwise 3x3) with its calibration results."""
+
+    def __init__(self, name, cin, cout, k, stride, pad, group, rng, relu6, cin_real=None, cout_real=None):
+        self.name, self.cin, self.cout, self.k, self.stride, self.pad, self.group, self.relu6 = name, cin, cout, k, stride, pad, group, relu6
+        cin_real, cout_real = cin_real or cin, cout_real or cout
+        cg = cin // group
+        w = np.zeros((cout, cg, k, k), np.float32)
+        if group == 1:
+            w[:cout_real, :cin_real] = rng.standard_normal((cout_real, cin_real, k, k)).astype(np.float32) * np.float32(0.02) * np.float32(
+                np.sqrt(2.0 / (cin_real * k * k)) / 0.02)
+        else:
+            w[:cout_real] = rng.standard_normal((cout_real, 1, k, k)).astype(np.float32) * np.float32(np.sqrt(2.0 / (k * k)))
+        self.w_f = w
+        self.b_f = np.zeros(cout, np.float32)
+        self.b_f[:cout_real] = (rng.standard_normal(cout_real) * 0.1).astype(np.float32)
+        self.w_q, self.w_scale, wz = quantize_weights(w, per_channel=True, to_int8=True)
+        self.w_scale = np.where(self.w_scale > 0, self.w_scale, np.float32(1.0)).astype(np.float32)  # all-zero padded channels
+        self.w_zp = wz.astype(np.int8)
+        self.x_scale = self.y_scale = None
+        self.y_zp = 0
+        self.clamp = None
+        self.bias_q = None
+        self.packed = None
+        self.dev = {}
+
+
+class MobileNetV2Int8:
+    """MobileNetV2-1.0 (inverted residuals, expansion 6, depthwise 3x3, ReLU6), per-channel symmetric int8 weights, uint8
+    activations.  Channel counts that are not multiples of 16 (24) are zero-padded to the next multiple of 16 in storage, so
+    every NHWC row starts on a 16-byte boundary; the padded channels carry zero weights in and out.  Dense 1x1 layers run on
+    the tensor cores (packed weights), depthwise layers on the depthwise kernel, ReLU6 is the upper clamp of the
+    requantization, linear bottleneck outputs get an asymmetric zero point, residual joins run in the projecting
+    convolution's epilogue (DequantizeLinear x2, Add, QuantizeLinear; no Relu)."""
+
+    def __init__(self, batch, device, seed=0, image=224, num_classes=1000):
+        self.batch, self.device, self.image = int(batch), torch.device(device), int(image)
+        rng = np.random.default_rng(seed)
+        self.stem = _QLayer("stem", 3, 32, 3, 2, 1, 1, rng, True)
+        self.blocks = []
+        cin, cin_real = 32, 32
+        for bi, (t, c, n, s) in enumerate(MOBILENETV2_BLOCKS):
+            for i in range(n):
+                stride = s if i == 0 else 1
+                mid = cin_real * t
+                cout, cout_real = _pad16(c), c
+                nm = "b%d_%d" % (bi, i)
+                blk = {
+                    "expand": _QLayer(nm + "_expand", cin, mid, 1, 1, 0, 1, rng, True, cin_real=cin_real) if t != 1 else None,
+                    "dw": _QLayer(nm + "_dw", mid, mid, 3, stride, 1, mid, rng, True),
+                    "project": _QLayer(nm + "_project", mid, cout, 1, 1, 0, 1, rng, False, cout_real=cout_real),
+                    "residual": stride == 1 and cin_real == cout_real,
+                }
+                self.blocks.append(blk)
+                cin, cin_real = cout, cout_real
+        self.head = _QLayer("head", cin, 1280, 1, 1, 0, 1, rng, True, cin_real=cin_real)
+        self.fc_w = (rng.standard_normal((num_classes, 1280), dtype=np.float32) * np.float32(0.01))
+        self.fc_b = np.zeros(num_classes, np.float32)
+        self.in_scale = np.float32(1.0 / 255.0)
+        self.calibrated = False
+
+    def layers(self):
+        yield self.stem
+        for b in self.blocks:
+            for k in ("expand", "dw", "project"):
+                if b[k] is not None:
+                    yield b[k]
+        yield self.head
+
+    def macs_per_image(self):
+        """(dense multiply-accumulates, depthwise multiply-accumulates) of one image, counted on the real channel counts."""
+        dense = dw = 0
+        hw = self.image // 2
+        dense += 32 * 3 * 9 * hw * hw
+        cin = 32
+        for (t, c, n, s) in MOBILENETV2_BLOCKS:
+            for i in range(n):
+                stride = s if i == 0 else 1
+                mid = cin * t
+                if t != 1:
+                    dense += cin * mid * hw * hw
+                hw = (hw + 2 - 3) // stride + 1
+                dw += mid * 9 * hw * hw
+                dense += mid * c * hw * hw
+                cin = c
+        dense += cin * 1280 * hw * hw + 1280 * self.fc_w.shape[0]
+        return dense, dw
+
+    # ---- execution of one layer -----------------------------------------------------------------------------------------
+    def _upload(self, c, x_shape, x_nchw=False):
+        dev = self.device
+        c.dev["w"] = torch.from_numpy(c.w_q).to(dev)
+        c.dev["w_scale"] = torch.from_numpy(c.w_scale).to(dev)
+        c.dev["w_zp"] = torch.from_numpy(c.w_zp).to(dev)
+        if c.group == 1:
+            c.packed = ops.PackedConv(c.dev["w"], c.dev["w_zp"], x_shape, strides=(c.stride, c.stride), pads=(c.pad, c.pad),
+                                      x_layout=_lib.NCHW if x_nchw else _lib.NHWC)
+            if not c.packed.eligible:
+                raise _lib.ChxqError(_lib.ERR_UNSUPPORTED, "%s is not eligible for the tensor-core path" % c.name)
+
+    def _acc(self, c, x):
+        if c.group == 1:
+            g = c.packed.g
+            y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.int32, device=self.device, memory_format=torch.channels_last)
+            ws_bytes = lib().chxq_conv_packed_workspace(ctypes.byref(g), 0, c.packed.flags)
+            ws = ops.workspace(ws_bytes, self.device)
+            check(lib().chxq_conv_integer_packed(ops._ptr(x), ops._ptr(c.packed.blob), ctypes.byref(g), 1, 0, c.packed.flags, ops._ptr(y),
+                                                 ops._ptr(ws), ws_bytes, ops._stream()))
+            return y
+        return ops.ConvInteger(x, c.dev["w"], np.uint8(0), None, (c.stride, c.stride), (c.pad, c.pad), c.group, path=_lib.PATH_SIMT)
+
+    def _run(self, c, x, fold=False, residual=None, res_scale=1.0, res_zp=0, out_scale=1.0, out_zp=0):
+        kw = dict(b=c.dev["bias"], clamp_hi_q=c.clamp, residual=residual, res_scale=res_scale, res_zero_point=res_zp, res_relu=False,
+                  out_scale=out_scale, out_zero_point=out_zp, fold_scales=fold)
+        if c.group == 1:
+            return ops.QLinearConvPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp), **kw)
+        return ops.QLinearConv(x, c.x_scale, np.uint8(0), c.dev["w"], c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
+                               strides=(c.stride, c.stride), pads=(c.pad, c.pad), group=c.group, **kw)
+
+    def _calibrate(self, c, x, x_scale, x_nchw=False):
+        self._upload(c, tuple(x.shape), x_nchw)
+        c.x_scale = np.float32(x_scale)
+        mult = (np.float32(x_scale) * c.w_scale).astype(np.float32)
+        c.bias_q = np.rint(c.b_f.astype(np.float64) / mult.astype(np.float64)).clip(-2**31, 2**31 - 1).astype(np.int32)
+        c.dev["bias"] = torch.from_numpy(c.bias_q).to(self.device)
+        acc = self._acc(c, x)
+        yf = (acc + c.dev["bias"].view(1, -1, 1, 1)).float() * torch.from_numpy(mult).to(self.device).view(1, -1, 1, 1)
+        lo, hi = float(yf.amin().item()), float(yf.amax().item())
+        del yf, acc
+        if c.relu6:
+            c.y_scale, c.y_zp = np.float32(max(min(hi, 6.0), 1e-6) / 255.0), 0
+            c.clamp = int(min(255, np.rint(6.0 / float(c.y_scale))))
+        else:
+            lo, hi = min(lo, 0.0), max(hi, 0.0)
+            c.y_scale = np.float32(max(hi - lo, 1e-6) / 255.0)
+            c.y_zp = int(np.clip(np.rint(-lo / float(c.y_scale)), 0, 255))
+        return self._run(c, x)
+
+    def calibrate(self, x):
+        xq = ops.QuantizeLinear(x.contiguous(), self.in_scale, np.uint8(0))
+        h = self._calibrate(self.stem, xq, self.in_scale, x_nchw=True)
+        h_scale, h_zp = self.stem.y_scale, 0
+        for b in self.blocks:
+            inp, inp_scale, inp_zp = h, h_scale, h_zp
+            # every convolution here takes a zero activation zero point: block inputs with an asymmetric zero point (linear
+            # bottleneck outputs) are handled through x_zero_point of the consuming layer
+            if b["expand"] is not None:
+                b["expand"].x_zp = inp_zp
+                h = self._calibrate_zp(b["expand"], h, inp_scale, inp_zp)
+                e_scale = b["expand"].y_scale
+            else:
+                e_scale = inp_scale
+            b["dw"].x_zp = 0 if b["expand"] is not None else inp_zp
+            h = self._calibrate_zp(b["dw"], h, e_scale, b["dw"].x_zp)
+            b["project"].x_zp = 0
+            p = self._calibrate_zp(b["project"], h, b["dw"].y_scale, 0)
+            if b["residual"]:
+                sf = (p.float() - b["project"].y_zp) * float(b["project"].y_scale) + (inp.float() - inp_zp) * float(inp_scale)
+                lo, hi = min(float(sf.amin().item()), 0.0), max(float(sf.amax().item()), 0.0)
+                del sf
+                b["out_scale"] = np.float32(max(hi - lo, 1e-6) / 255.0)
+                b["out_zp"] = int(np.clip(np.rint(-lo / float(b["out_scale"])), 0, 255))
+                b["res"] = (inp_scale, inp_zp)
+                h = ops.QAddU8(p, b["project"].y_scale, b["project"].y_zp, inp, inp_scale, inp_zp, b["out_scale"], b["out_zp"], relu=False)
+                h_scale, h_zp = b["out_scale"], b["out_zp"]
+            else:
+                h, h_scale, h_zp = p, b["project"].y_scale, b["project"].y_zp
+        self.head.x_zp = h_zp
+        h = self._calibrate_zp(self.head, h, h_scale, h_zp)
+        self.dev_fc_w = torch.from_numpy(self.fc_w).to(self.device)
+        self.dev_fc_b = torch.from_numpy(self.fc_b).to(self.device)
+        self.calibrated = True
+        torch.cuda.synchronize(self.device)
+
+    def _calibrate_zp(self, c, x, x_scale, x_zp):
+        """_calibrate for a layer whose input has zero point x_zp (recorded in c.x_zp and used by _run_zp)."""
+        c.x_zp = int(x_zp)
+        if x_zp == 0:
+            return self._calibrate(c, x, x_scale)
+        self._upload(c, tuple(x.shape))
+        c.x_scale = np.float32(x_scale)
+        mult = (np.float32(x_scale) * c.w_scale).astype(np.float32)
+        c.bias_q = np.rint(c.b_f.astype(np.float64) / mult.astype(np.float64)).clip(-2**31, 2**31 - 1).astype(np.int32)
+        c.dev["bias"] = torch.from_numpy(c.bias_q).to(self.device)
+        acc = ops.ConvInteger(x, c.dev["w"], np.uint8(x_zp), None, (c.stride, c.stride), (c.pad, c.pad), c.group,
+                              path=_lib.PATH_TENSOR if c.group == 1 else _lib.PATH_SIMT)
+        yf = (acc + c.dev["bias"].view(1, -1, 1, 1)).float() * torch.from_numpy(mult).to(self.device).view(1, -1, 1, 1)
+        lo, hi = float(yf.amin().item()), float(yf.amax().item())
+        del yf, acc
+        if c.relu6:
+            c.y_scale, c.y_zp = np.float32(max(min(hi, 6.0), 1e-6) / 255.0), 0
+            c.clamp = int(min(255, np.rint(6.0 / float(c.y_scale))))
+        else:
+            lo, hi = min(lo, 0.0), max(hi, 0.0)
+            c.y_scale = np.float32(max(hi - lo, 1e-6) / 255.0)
+            c.y_zp = int(np.clip(np.rint(-lo / float(c.y_scale)), 0, 255))
+        return self._run_zp(c, x)
+
+    def _run_zp(self, c, x, fold=False, **kw):
+        if getattr(c, "x_zp", 0) == 0:
+            return self._run(c, x, fold=fold, **kw)
+        args = dict(b=c.dev["bias"], clamp_hi_q=c.clamp, fold_scales=fold, res_relu=False)
+        args.update({"residual": kw.get("residual"), "res_scale": kw.get("res_scale", 1.0), "res_zero_point": kw.get("res_zp", 0),
+                     "out_scale": kw.get("out_scale", 1.0), "out_zero_point": kw.get("out_zp", 0)})
+        if c.group == 1:
+            return ops.QLinearConvPacked(x, c.packed, c.x_scale, np.uint8(c.x_zp), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
+                                         **args)
+        return ops.QLinearConv(x, c.x_scale, np.uint8(c.x_zp), c.dev["w"], c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
+                               strides=(c.stride, c.stride), pads=(c.pad, c.pad), group=c.group, **args)
+
+    def forward(self, x, fused=True, fold=False, taps=None):
+        assert self.calibrated
+        xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
+        h = self._run(self.stem, xq, fold=fold)
+        if taps is not None:
+            taps["stem"] = h
+        for i, b in enumerate(self.blocks):
+            inp = h
+            if b["expand"] is not None:
+                h = self._run_zp(b["expand"], h, fold=fold)
+            h = self._run_zp(b["dw"], h, fold=fold)
+            if b["residual"] and fused:
+                h = self._run_zp(b["project"], h, fold=fold, residual=inp, res_scale=b["res"][0], res_zp=b["res"][1], out_scale=b["out_scale"],
+                                 out_zp=b["out_zp"])
+            else:
+                h = self._run_zp(b["project"], h, fold=fold)
+                if b["residual"]:
+                    h = ops.QAddU8(h, b["project"].y_scale, b["project"].y_zp, inp, b["res"][0], b["res"][1], b["out_scale"], b["out_zp"], relu=False)
+            if taps is not None:
+                taps["block%d" % i] = h
+        h = self._run_zp(self.head, h, fold=fold)
+        pooled = ops.GlobalAveragePoolDequant(h, self.head.y_scale, 0)
+        if taps is not None:
+            taps["pooled"] = pooled
+        return ops.Linear(pooled, self.dev_fc_w, self.dev_fc_b)
+
+    def export_numpy(self):
+        def lay(c):
+            return None if c is None else dict(name=c.name, w=c.w_q, w_scale=c.w_scale, w_zp=c.w_zp.astype(np.int32), bias=c.bias_q,
+                                               x_scale=c.x_scale, x_zp=getattr(c, "x_zp", 0), y_scale=c.y_scale, y_zp=c.y_zp, clamp=c.clamp,
+                                               stride=c.stride, pad=c.pad, group=c.group)
+        return dict(in_scale=self.in_scale, stem=lay(self.stem), head=lay(self.head),
+                    blocks=[dict(expand=lay(b["expand"]), dw=lay(b["dw"]), project=lay(b["project"]), residual=b["residual"],
+                                 res=b.get("res"), out_scale=b.get("out_scale"), out_zp=b.get("out_zp")) for b in self.blocks],
+                    fc_w=self.fc_w, fc_b=self.fc_b)

@@ -55,3 +55,39 @@ def mlp_forward(layers, act_scale, x, mode="emulate"):
             acc = orc.matmul_integer(h, l["w_q"])
             h = orc.requantize(acc, act_scale, np.array([l["w_scale"]], np.float32), act_scale, 0)
     return orc.dequantize_linear(h, act_scale, 0)
+
+
+def _mb_layer(c, x, mode):
+    wz = np.asarray(c["w_zp"], np.int32)
+    clamp = -1 if c["clamp"] is None else c["clamp"]
+    s, p, g = (c["stride"], c["stride"]), (c["pad"], c["pad"]), c["group"]
+    if mode == "emulate":
+        return orc.qlinear_conv(x, c["x_scale"], c["x_zp"], c["w"], c["w_scale"], wz, c["y_scale"], c["y_zp"], b=c["bias"], strides=s, pads=p,
+                                group=g, clamp_hi_q=clamp)
+    acc = orc.conv_integer(x, c["w"], c["x_zp"], wz, strides=s, pads=p, group=g)
+    return orc.requantize(acc, c["x_scale"], c["w_scale"], c["y_scale"], c["y_zp"], bias=c["bias"], channel_axis=1, clamp_hi_q=clamp,
+                          fold=(mode == "fold"))
+
+
+def mobilenetv2_forward(params, x, mode="exact", taps=None):
+    """params: ``models.MobileNetV2Int8.export_numpy()``; x: fp32 NCHW.  Modes as in resnet50_forward."""
+    xq = orc.quantize_linear(x, params["in_scale"], 0)
+    h = _mb_layer(params["stem"], xq, mode)
+    if taps is not None:
+        taps["stem"] = h
+    for i, b in enumerate(params["blocks"]):
+        inp = h
+        if b["expand"] is not None:
+            h = _mb_layer(b["expand"], h, mode)
+        h = _mb_layer(b["dw"], h, mode)
+        h = _mb_layer(b["project"], h, mode)
+        if b["residual"]:
+            h = orc.qadd_relu(h, b["project"]["y_scale"], b["project"]["y_zp"], inp, b["res"][0], b["res"][1], b["out_scale"], b["out_zp"],
+                              relu=False, fold=(mode == "fold"))
+        if taps is not None:
+            taps["block%d" % i] = h
+    h = _mb_layer(params["head"], h, mode)
+    pooled = orc.global_avgpool_dq(h, params["head"]["y_scale"], 0)
+    if taps is not None:
+        taps["pooled"] = pooled
+    return orc.linear_f32(pooled, params["fc_w"], params["fc_b"])

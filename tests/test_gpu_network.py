@@ -137,3 +137,53 @@ def test_mlp_matches_oracle(pkg, ops, orc, dev):
         assert y.shape == (64, 10) and np.array_equal(y, exact)
         assert np.abs(y - emul).max() <= 3 * float(mlp.act_scale)  # three requantizing layers, one step each at most... compounded
     ops.device_status()
+
+
+@pytest.fixture(scope="module")
+def small_mobilenet(pkg, dev):
+    from chainer_compiler_b200 import models
+    net = models.MobileNetV2Int8(batch=2, device=dev, seed=3, image=64, num_classes=24)
+    rng = np.random.default_rng(5)
+    x = rng.uniform(0, 1, (2, 3, 64, 64)).astype(np.float32)
+    xt = torch.from_numpy(x).to(dev)
+    net.calibrate(xt)
+    return net, x, xt
+
+
+def test_mobilenet_fused_unfused_agree(small_mobilenet, ops):
+    net, x, xt = small_mobilenet
+    tf, tu = {}, {}
+    lf = net.forward(xt, fused=True, taps=tf)
+    lu = net.forward(xt, fused=False, taps=tu)
+    ops.device_status()
+    for k in tf:
+        assert torch.equal(tf[k], tu[k]), k
+    assert torch.equal(lf, lu)
+
+
+@pytest.mark.parametrize("mode", ["exact", "fold"])
+def test_mobilenet_matches_oracle(small_mobilenet, orc, ops, mode):
+    """MobileNetV2 (1x1 tensor-core layers with asymmetric activation zero points, depthwise 3x3 stride 1 and 2, ReLU6 clamps,
+    residual joins without Relu) against the oracle's chain, every block output bit-exact."""
+    import __graft_entry__ as entry
+    entry.load_oracle()
+    from oracle import networks
+    net, x, xt = small_mobilenet
+    taps = {}
+    logits = net.forward(xt, taps=taps, fold=(mode == "fold")).cpu().numpy()
+    ops.device_status()
+    otaps = {}
+    want = networks.mobilenetv2_forward(net.export_numpy(), x, mode=mode, taps=otaps)
+    for k, v in otaps.items():
+        assert np.array_equal(taps[k].cpu().numpy(), v), "tap %s differs" % k
+    assert np.array_equal(logits, want)
+    if mode == "exact":
+        etaps = {}
+        emul = networks.mobilenetv2_forward(net.export_numpy(), x, mode="emulate", taps=etaps)
+        mx, cnt, tot = lsb_report(taps["stem"].cpu().numpy(), etaps["stem"])
+        print("mobilenet stem: %d of %d bytes differ from the fp32-emulating chain (max %d LSB)" % (cnt, tot, mx))
+        assert mx <= 1
+        # 52 quantized layers compound their 1-LSB differences: the whole-network bound is on the relative L2 distance
+        rel = float(np.linalg.norm(logits - emul) / np.linalg.norm(emul))
+        print("mobilenet logits: relative L2 distance to the fp32-emulating chain %.3g" % rel)
+        assert rel <= 0.1
