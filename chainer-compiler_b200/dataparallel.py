@@ -81,6 +81,7 @@ class InferenceEngine:
         self.logits = None
         self.all_logits = None
         self.host_logits = None
+        self.slots = None
 
     def prepare(self, calib_x):
         self.x_dev.copy_(calib_x)
@@ -105,3 +106,63 @@ class InferenceEngine:
         self.host_logits.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self.host_logits
+
+    # ---- pipelined end-to-end call ------------------------------------------------------------------------------------
+    def _make_slots(self):
+        """Two input slots, each with its own captured graph, logits and pinned result buffer, plus a copy-in and a
+        copy-out stream: batch i+1 crosses PCIe while batch i computes and batch i-1's logits go back."""
+        dev = self.net.device
+        self.h2d_stream, self.d2h_stream = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.slots = []
+        for k in range(2):
+            x = self.x_dev if k == 0 else torch.empty_like(self.x_dev)
+            if k == 0:
+                graph, logits = self.graph, self.logits
+            else:
+                x.copy_(self.x_dev)
+                graph, logits = self.net.capture(x, fold=self.fold)
+            n, c = logits.shape
+            self.slots.append({
+                "x": x, "graph": graph, "logits": logits,
+                "all": self.all_logits if k == 0 else torch.empty_like(self.all_logits),
+                "host": self.host_logits if k == 0 else torch.empty((n * self.world, c), dtype=torch.float32).pin_memory(),
+                "in_ready": torch.cuda.Event(), "in_free": torch.cuda.Event(), "out_ready": torch.cuda.Event(), "host_ready": torch.cuda.Event(),
+                "busy": False})
+
+    def run_stream(self, batches):
+        """Public streaming call: an iterable of pinned host fp32 NCHW batches in, one host logits array (all ranks' rows)
+        out per batch, in order.  The returned array of batch i is valid until batch i+2 is submitted."""
+        if self.slots is None:
+            self._make_slots()
+        compute = torch.cuda.current_stream()
+        pending = []
+        for i, xb in enumerate(batches):
+            s = self.slots[i % 2]
+            if s["busy"]:  # hand out this slot's previous result (its copy-out has then finished) before the slot is reused
+                yield self._finish(pending.pop(0))
+            with torch.cuda.stream(self.h2d_stream):
+                self.h2d_stream.wait_event(s["in_free"])
+                s["x"].copy_(xb, non_blocking=True)
+                s["in_ready"].record(self.h2d_stream)
+            compute.wait_event(s["in_ready"])
+            s["graph"].replay()
+            s["in_free"].record(compute)
+            out = s["logits"]
+            if self.world > 1:
+                gather_logits(s["logits"], self.world, s["all"])
+                out = s["all"]
+            s["out_ready"].record(compute)
+            with torch.cuda.stream(self.d2h_stream):
+                self.d2h_stream.wait_event(s["out_ready"])
+                s["host"].copy_(out, non_blocking=True)
+                s["host_ready"].record(self.d2h_stream)
+            s["busy"] = True
+            pending.append(s)
+        while pending:
+            yield self._finish(pending.pop(0))
+
+    @staticmethod
+    def _finish(s):
+        s["host_ready"].synchronize()
+        s["busy"] = False
+        return s["host"]

@@ -187,3 +187,21 @@ def test_mobilenet_matches_oracle(small_mobilenet, orc, ops, mode):
         rel = float(np.linalg.norm(logits - emul) / np.linalg.norm(emul))
         print("mobilenet logits: relative L2 distance to the fp32-emulating chain %.3g" % rel)
         assert rel <= 0.1
+
+
+def test_engine_stream_matches_single_calls(pkg, dev):
+    """InferenceEngine.run_stream (double-buffered copies around the captured graph) returns, batch by batch, what the
+    synchronous run_host returns."""
+    from chainer_compiler_b200 import models, dataparallel as dp
+    net = models.ResNet50Int8(batch=2, device=dev, seed=2, image=64, num_classes=16, width_mult=0.25)
+    eng = dp.InferenceEngine(net, 1, fold=True)
+    gen = torch.Generator().manual_seed(3)
+    eng.prepare(torch.rand((2, 3, 64, 64), generator=gen).to(dev))
+    batches = [torch.rand((2, 3, 64, 64), generator=gen).pin_memory() for _ in range(5)]
+    want = [eng.run_host(b).clone() for b in batches]
+    got = [h.clone() for h in eng.run_stream(batches)]
+    assert len(got) == 5
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    got2 = [h.clone() for h in eng.run_stream(batches[:1])]
+    assert torch.equal(got2[0], want[0])
