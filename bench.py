@@ -34,6 +34,8 @@ def parse():
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU")
     ap.add_argument("--cpu-sample", type=int, default=8, help="images of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tc-variant", type=int, default=0, choices=[0, 1, 2],
+                    help="tensor-core kernel choice (chxq_tc_variant): 0 by shape, 1 one tile per step, 2 grouped tiles")
     ap.add_argument("--exact-requant", action="store_true",
                     help="requantize in the reference's operation order (multiply by x_scale*w_scale, divide by y_scale) instead of one "
                          "folded multiplier per channel")
@@ -202,6 +204,7 @@ def run_chxq(args):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     L = pkg.lib()
+    pkg._lib.check(L.chxq_tc_variant(args.tc_variant))
 
     # Same seeded weights on every rank; every rank works on its own seeded images (weak scaling: 256 images per GPU).
     net = models.ResNet50Int8(batch=args.batch, device=dev, seed=0, image=IMAGE)

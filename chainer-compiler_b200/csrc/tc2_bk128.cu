@@ -1,0 +1,13 @@
+// Instantiations of the grouped-tile tcgen05 kernel for a 128-byte K tile.
+#include "tc_kernel2.cuh"
+
+namespace chxq {
+namespace tc {
+
+int launch_tc2_bk128(int bn, int epi, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
+                    const TcParams& p, int grid, cudaStream_t s) {
+    return launch_bk2<128>(bn, epi, res, tmA, tmB, tmY, tmR, p, grid, s);
+}
+
+}  // namespace tc
+}  // namespace chxq

@@ -56,6 +56,8 @@ bool g_prof_on = false;
 std::vector<ProfRec> g_prof;
 std::mutex g_prof_mu;
 
+int g_variant = 0;  // chxq_tc_variant: 0 = choose, 1 = one tile per step, 2 = grouped tiles where eligible
+
 int pick_bn(int cols, int64_t pos_tiles) {
     const int cand[3] = {256, 128, 64};
     const double base[3] = {1.0, 0.92, 0.78};
@@ -203,7 +205,47 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
                             swizzle_for(q.bk), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed with %d", (int)r);
     }
-    const int grid = total_tiles < num_sms() ? (int)total_tiles : num_sms();
+    int grid = total_tiles < num_sms() ? (int)total_tiles : num_sms();
+
+    // Grouped-tile kernel (tc_kernel2.cuh): uint8 epilogues whose outputs (and residual) can move through TMA.
+    bool grouped = false;
+    int bn2 = q.cols > 64 ? 128 : 64;
+    alignas(64) CUtensorMap tmY, tmR;
+    if ((epi_kind == tc::kEpiKU8 || epi_kind == tc::kEpiKU8Fold) && g_variant != 1 && p.vec_ok && q.ldc % 16 == 0 && (q.bk == 64 || q.bk == 128) &&
+        !(epi_kind == tc::kEpiKU8Fold && q.col_corr != nullptr) && !(q.epi.residual != nullptr && bn2 == 64) &&
+        // folded tail: the saturating add clamps at zero, which is the Relu only when the output zero point is zero
+        !(epi_kind == tc::kEpiKU8Fold && q.epi.residual != nullptr && q.epi.rq.res_relu && q.epi.rq.out_zp_f != 0.f)) {
+        const int r = 256 / bn2;
+        const int64_t groups = (pos_tiles + r - 1) / r * ((q.cols + bn2 - 1) / bn2);
+        // Chosen whenever there is at least one group per SM; smaller problems spread better as single tiles.
+        grouped = g_variant == 2 || groups >= (int64_t)num_sms();
+        if (grouped) {
+            const cuuint64_t dims[4] = {(cuuint64_t)q.cols, (cuuint64_t)q.Wo, (cuuint64_t)q.Ho, (cuuint64_t)q.No};
+            const cuuint64_t strides[3] = {(cuuint64_t)q.ldc, (cuuint64_t)q.ldc * q.Wo, (cuuint64_t)q.ldc * q.Wo * q.Ho};
+            const cuuint32_t box[4] = {(cuuint32_t)bn2, (cuuint32_t)q.Wb, (cuuint32_t)q.Hb, (cuuint32_t)q.Nb};
+            const cuuint32_t estr[4] = {1, 1, 1, 1};
+            const CUtensorMapSwizzle sw = bn2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+            CUresult r1 = encode(&tmY, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, q.y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                 CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r1 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(Y) failed with %d", (int)r1);
+            void* rbase = q.epi.residual ? const_cast<uint8_t*>(q.epi.residual) : q.y;
+            r1 = encode(&tmR, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, rbase, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r1 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(R) failed with %d", (int)r1);
+            // The weight box and the instruction shape follow the grouped kernel's channel block.
+            const int taps = q.KH * q.KW;
+            const cuuint64_t bdims[2] = {(cuuint64_t)taps * q.c_pad, (cuuint64_t)q.cols};
+            const cuuint64_t bstrides[1] = {(cuuint64_t)taps * q.c_pad};
+            const cuuint32_t bbox[2] = {(cuuint32_t)q.bk, (cuuint32_t)bn2};
+            const cuuint32_t bestr[2] = {1, 1};
+            r1 = encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(q.b), bdims, bstrides, bbox, bestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle_for(q.bk), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r1 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed with %d", (int)r1);
+            p.col_tiles = (q.cols + bn2 - 1) / bn2;
+            p.idesc = (p.idesc & ~(0x3fu << 17)) | ((uint32_t)(bn2 >> 3) << 17);
+            grid = groups < num_sms() ? (int)groups : num_sms();
+        }
+    }
     ProfRec rec{};
     if (g_prof_on) {
         CHXQ_CUDA(cudaEventCreate(&rec.e0));
@@ -212,6 +254,10 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
         CHXQ_CUDA(cudaEventRecord(rec.e0, s));
     }
     int rc;
+    if (grouped) {
+        rc = q.bk == 128 ? tc::launch_tc2_bk128(bn2, epi_kind, q.epi.residual != nullptr, tmA, tmB, tmY, tmR, p, grid, s)
+                         : tc::launch_tc2_bk64(bn2, epi_kind, q.epi.residual != nullptr, tmA, tmB, tmY, tmR, p, grid, s);
+    } else
     switch (q.bk) {
         case 128: rc = tc::launch_tc_bk128(bn, epi_kind, tmA, tmB, p, grid, s); break;
         case 64: rc = tc::launch_tc_bk64(bn, epi_kind, tmA, tmB, p, grid, s); break;
@@ -226,6 +272,14 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
 }
 
 }  // namespace chxq
+
+// Chooses between the two tensor-core kernels: 0 = by problem shape, 1 = always one tile per step, 2 = grouped tiles
+// whenever the problem is eligible.  Results are identical; the switch exists for measurements and tests.
+extern "C" int chxq_tc_variant(int32_t variant) {
+    if (variant < 0 || variant > 2) return chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, "chxq_tc_variant: variant must be 0, 1 or 2");
+    chxq::g_variant = variant;
+    return CHXQ_OK;
+}
 
 // Profiling of the tensor-core kernel: while enabled, every launch is bracketed by CUDA events on its stream.
 extern "C" int chxq_tc_profile(int32_t enable) {

@@ -65,22 +65,36 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is incomplete: a waiting
+// warp then issues (almost) nothing instead of spinning next to the warps that do the work.
+__device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(ns)
+            : "memory");
+    return ok;
+}
+
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr uint32_t kSuspendNs = 20000u;           // one suspended try: 20 us at most, then the abort flag and the clock are looked at
 
 // Bounded wait.  Returns false when the CTA is aborting (either this wait expired or another did).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
-    uint32_t it = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++it & 63u) == 0u) {
-            if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
-            }
+        if (mbar_try_wait_suspend(bar, parity, kSuspendNs)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, code);
+            return false;
         }
     }
 }
@@ -207,7 +221,8 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     using Cfg = TcConfig<BN, BK>;
     constexpr int kStages = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    // 1024-byte alignment by offset, so that the pointer stays a shared-memory pointer for the compiler (ld.shared / st.shared)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + kStages * Cfg::kStageA;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);

@@ -1,0 +1,504 @@
+// Grouped-tile variant of the tcgen05 implicit-GEMM kernel for the uint8 requantizing epilogues (device code; the host
+// side is in tc_igemm.cu).  Same roles and the same operand staging as tc_kernel.cuh; what changes is the unit of work and
+// how results leave the SM:
+//
+//   * A CTA works on a GROUP of R position tiles (R x 128 output positions) against one block of BN output channels:
+//     R = 2 with BN = 128, R = 4 with BN = 64.  One weight stage feeds R MMAs, and an epilogue thread keeps the
+//     per-channel multiplier and offset of a 16-channel chunk in registers while it requantizes that chunk of all R
+//     tiles, so the shared-memory reads of the per-channel parameters drop by R.
+//   * Outputs are written into a swizzled shared-memory staging tile (conflict-free 128-bit stores) and leave through a TMA
+//     store; the residual map of a fused residual tail arrives the same way through a TMA load issued by the producer
+//     warp.  A thread owns one output position (TMEM lane), so direct global accesses would touch 32 different lines per
+//     warp instruction; through shared memory every line is moved once, whole.
+//   * The TMA store clips rows and channels beyond the output, so ragged edges need no predicates.
+//
+//   * The folded requantization runs scaled by 2^-8 (exact), so that the saturating fma / add clamp at zero for free, and
+//     on pairs of floats (fma / add / mul .f32x2) wherever no clamp is involved.
+//
+// TMEM holds two groups (2 x R x BN = 512 columns): the epilogue of group i overlaps the main loop of group i + 1.  The
+// staging tiles are multi-buffered as well.  Every wait is bounded exactly as in tc_kernel.cuh.
+#pragma once
+
+#include "tc_kernel.cuh"
+
+namespace chxq {
+namespace tc {
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void tma_store_wait_all() {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- packed pairs of floats (one 64-bit register) and the saturating scalar forms -----------------------------------
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ float lo_of(uint64_t v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi_of(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
+__device__ __forceinline__ uint64_t add_rm_x2(uint64_t a, uint64_t b) {  // round toward minus infinity
+    uint64_t d;
+    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t sub_x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul_x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma_x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {  // clamp(fma(a, b, c), 0, 1)
+    float d;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float add_sat(float a, float b) {
+    float d;
+    asm("add.rn.sat.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+
+template <int BN, int BK, bool RES>
+struct Tc2Config {
+    static constexpr int kR = 256 / BN;                  // position tiles per group
+    static constexpr int kStageA = kR * 128 * BK;
+    static constexpr int kStageB = BN * BK;
+    static constexpr int kStageBytes = kStageA + kStageB;
+    static constexpr int kTileOut = 128 * BN;            // one staged output (or residual) tile
+    // Staging buffers of kR tiles each.  Without a residual: two, filled by the epilogue and drained by the TMA store.
+    // With one: three, each filled by the residual's TMA load, overwritten in place by the epilogue (a thread reads and
+    // writes the same 16 bytes) and drained by the store; three, so that the load for group i + 1 can run during the
+    // epilogue of group i while the store of group i - 1 is still reading its buffer.
+    static constexpr int kBufs = RES ? 3 : 2;
+    static constexpr int kOutBytes = kBufs * kR * kTileOut;
+    static constexpr int kFixed = kOutBytes;
+    static constexpr int kBudget = 222 * 1024;
+    static constexpr int kStagesRaw = (kBudget - kFixed) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kTmemCols = 512;
+    // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], res_full[3], res_empty[3], epilogue rendezvous
+    static constexpr int kBarBytes = (2 * kStages + 11) * 8;
+    static constexpr int kBarOffset = kStages * kStageBytes + kFixed;
+    static constexpr int kParamOffset = ((kBarOffset + kBarBytes + 16 + 15) / 16) * 16;
+    static constexpr int kParamBytes = 16 * (BN / 2) * 4;  // 16 warps x (BN/4 multipliers + BN/4 additive terms)
+    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kParamOffset + kParamBytes;
+    static constexpr bool kUsable = kStages >= 2;
+};
+
+// Byte offset of 16-byte unit `unit` of row `row` inside a staged [128][BN] tile laid out with the BN-byte TMA swizzle.
+template <int BN>
+__device__ __forceinline__ uint32_t staged_offset(int row, int unit) {
+    if (BN == 128) return (uint32_t)(row * 128 + ((unit ^ (row & 7)) << 4));
+    return (uint32_t)(row * 64 + ((unit ^ ((row >> 1) & 3)) << 4));
+}
+
+template <int BN, int BK, int EPI, bool RES>
+__global__ void __launch_bounds__(576, 1)
+tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
+                 const __grid_constant__ CUtensorMap tmR, const TcParams p) {
+    using Cfg = Tc2Config<BN, BK, RES>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kR = Cfg::kR;
+    constexpr bool kFold = EPI == kEpiKU8Fold;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // stays a shared-memory pointer
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + kStages * Cfg::kStageA;
+    uint8_t* smem_out = smem + kStages * Cfg::kStageBytes;  // [kBufs][kR][128][BN], 1024-byte aligned (all sizes are multiples of 1024)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOffset);
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 11);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+    auto rfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 4 + b); };
+    auto rempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 7 + b); };
+    const uint32_t esync_bar = bar_base + 8u * (2 * kStages + 10);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 16);  // one arrival per epilogue warp
+        }
+        for (int b = 0; b < 3; ++b) {
+            mbar_init(rfull_bar(b), 1);
+            mbar_init(rempty_bar(b), 1);  // the thread that issues the stores, once the store out of the buffer has read it
+        }
+        mbar_init(esync_bar, 16);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_ptr_smem), Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    const int pos_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
+    const int pos_groups = (pos_tiles + kR - 1) / kR;
+    const int total_groups = pos_groups * p.col_tiles;
+    const int taps = p.KH * p.KW;
+    const int num_kb = taps * p.c_chunks;
+
+    // Output coordinates of position tile `pt` (tiles past the end land beyond the last image: loads fill zero, stores
+    // are skipped).
+    auto tile_origin = [&](int pt, int& w0, int& h0, int& n0) {
+        const int tw = pt % p.tiles_w;
+        pt /= p.tiles_w;
+        const int th = pt % p.tiles_h;
+        const int tn = pt / p.tiles_h;
+        w0 = tw * p.Wb; h0 = th * p.Hb; n0 = tn * p.Nb;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int grp = blockIdx.x; grp < total_groups && ok; grp += gridDim.x, ++it) {
+                const int ct = grp % p.col_tiles;
+                const int pg = grp / p.col_tiles;
+                int w0[kR], h0[kR], n0[kR];
+#pragma unroll
+                for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
+                if (RES) {
+                    const int rb = it % 3;
+                    if (!mbar_wait(rempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5)) break;
+                    mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
+#pragma unroll
+                    for (int t = 0; t < kR; ++t)
+                        tma_load_4d(smem_u32(smem_out + (rb * kR + t) * Cfg::kTileOut), &tmR, rfull_bar(rb), ct * BN, w0[t], h0[t], n0[t]);
+                }
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
+                    const int kh = tap / p.KW, kw = tap - kh * p.KW;
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+#pragma unroll
+                    for (int t = 0; t < kR; ++t)
+                        tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA + t * 128 * BK), &tmA, full_bar(stage), cc * BK,
+                                    w0[t] - p.pad_left + kw, h0[t] - p.pad_top + kh, n0[t]);
+                    tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), tap * p.c_pad + cc * BK, ct * BN);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int grp = blockIdx.x; grp < total_groups && ok; grp += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * 256);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kStageA);
+                    const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kStageB);
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k) {
+                        const uint64_t db = make_kmajor_desc<BK>(b_addr + k * 32);
+#pragma unroll
+                        for (int t = 0; t < kR; ++t)
+                            umma_i8(tmem_d + (uint32_t)(t * BN), make_kmajor_desc<BK>(a_addr + t * 128 * BK + k * 32), db, p.idesc,
+                                    (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(tfull_bar(acc));  // all kR accumulators complete
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        // Warp w reads TMEM lanes 32*(w % 4) .. +31 (one output position per thread and tile); the four warps of a lane
+        // quarter take every fourth 16-channel chunk.  A unit of work is (chunk, tile): 16 accumulators in, 16 bytes out.
+        constexpr int kMine = BN / 64;  // chunks per warp
+        constexpr int kUnits = kMine * kR;
+        const int e = warp - 2;         // 0..15
+        const int quarter = warp & 3;
+        const int sub = e >> 2;
+        const int row = quarter * 32 + lane;
+        const bool issuer = e == 0 && lane == 0;
+        float* s_mult = reinterpret_cast<float*>(smem + Cfg::kParamOffset) + e * (BN / 2);
+        uint32_t* s_add = reinterpret_cast<uint32_t*>(s_mult + BN / 4);
+        int cached_ct = -1;
+        const RequantParams rq = p.epi.rq;
+        const float hi_ph = (float)(rq.clamp_hi_q >= 0 ? rq.clamp_hi_q : 255) + 0.5f;
+        const float cy = kMagic23 + rq.y_zp_f, cr = kMagic23 + rq.res_zp_f;
+        const float out_half = __fadd_rn(rq.out_zp_f, 0.5f);
+        // Relu before the final quantization equals raising the lower clamp bound to the output zero point.
+        const float res_lo = rq.res_relu ? out_half : 0.f;
+        // Folded epilogue, scaled by 2^-8 so that the saturating forms of fma / add clamp at 0 (and, never reached, at 256):
+        // every constant below is an exact power-of-two multiple of its unscaled counterpart, so each intermediate is the
+        // unscaled one times 2^-8 and the output bytes are the same.
+        constexpr float kS = 1.f / 256.f;
+        const float hi_s = hi_ph * kS;
+        const uint64_t magic15x2 = pack2(32768.f, 32768.f);                        // 2^15: ulp 2^-8, so rounding down floors t * 256
+        const uint64_t cy_s2 = pack2(32768.f + rq.y_zp_f * kS, 32768.f + rq.y_zp_f * kS);
+        const uint64_t cr2 = pack2(cr, cr);
+        const uint64_t yoo2 = pack2(rq.y_over_out, rq.y_over_out);
+        const uint64_t roo_s2 = pack2(rq.res_over_out * kS, rq.res_over_out * kS);
+        const float oh_s = out_half * kS;
+        // Rendezvous of the sixteen epilogue warps on an mbarrier (bounded like every other wait; bar.sync has no way out).
+        uint32_t esync_phase = 0;
+        auto epilogue_rendezvous = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(esync_bar);
+            const bool ok = mbar_wait(esync_bar, esync_phase, abort_flag, p.status, 7);
+            esync_phase ^= 1u;
+            return __all_sync(0xffffffffu, ok);
+        };
+        int it = 0;
+        for (int grp = blockIdx.x; grp < total_groups; grp += gridDim.x, ++it) {
+            const int acc = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const int ct = grp % p.col_tiles;
+            const int pg = grp / p.col_tiles;
+            const int col0 = ct * BN;
+            const int buf = it % Cfg::kBufs;
+
+            if (ct != cached_ct) {
+                __syncwarp();
+                for (int j = lane; j < BN / 4; j += 32) {
+                    const int c = col0 + ((j >> 4) * 4 + sub) * 16 + (j & 15);
+                    float m = 0.f;
+                    uint32_t add = 0u;
+                    if (c < p.cols) {
+                        m = epi_mult(p.epi, c);
+                        const int bias = p.epi.bias ? p.epi.bias[c] : 0;
+                        if (kFold) {
+                            m = __fdiv_rn(m, rq.y_scale);
+                            add = __float_as_uint(fold_offset(bias, m, rq) * kS);
+                            m *= kS;
+                        } else {
+                            add = (uint32_t)bias;
+                            if (p.col_corr) add -= (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];
+                        }
+                    }
+                    s_mult[j] = m;
+                    s_add[j] = add;
+                }
+                __syncwarp();
+                cached_ct = ct;
+            }
+
+            // Stores up to the one issued two groups ago have read their buffers: without a residual that frees this group's
+            // buffer for the epilogue; with one it frees the buffer the producer loads the NEXT group's residual into.
+            uint8_t* out_buf = smem_out + buf * (kR * Cfg::kTileOut);
+            if (issuer) {
+                tma_store_wait_read<1>();
+                if (RES && it >= 2) mbar_arrive(rempty_bar((it - 2) % 3));
+            }
+            bool got = epilogue_rendezvous();
+            if (got) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4);
+            if (RES && got) got = mbar_wait(rfull_bar(buf), (uint32_t)(it / 3) & 1u, abort_flag, p.status, 6);
+            if (!__all_sync(0xffffffffu, got)) break;
+            {
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 256);
+                uint32_t mmw[16], addw[16];  // multipliers (float bits) and additive terms of the current chunk
+#pragma unroll
+                for (int u = 0; u < kUnits; ++u) {
+                    const int i = u / kR, t = u % kR;
+                    const int ch = i * 4 + sub;
+                    if (col0 + ch * 16 >= p.cols) continue;  // warp-uniform; clipped by the store anyway
+                    if (t == 0) {
+                        const uint4* pm = reinterpret_cast<const uint4*>(s_mult + i * 16);
+                        const uint4* pa = reinterpret_cast<const uint4*>(s_add + i * 16);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint4 m4 = pm[j];
+                            const uint4 a4 = pa[j];
+                            mmw[4 * j] = m4.x; mmw[4 * j + 1] = m4.y; mmw[4 * j + 2] = m4.z; mmw[4 * j + 3] = m4.w;
+                            addw[4 * j] = a4.x; addw[4 * j + 1] = a4.y; addw[4 * j + 2] = a4.z; addw[4 * j + 3] = a4.w;
+                        }
+                    }
+                    uint32_t r[16];
+                    __syncwarp();
+                    tmem_ld_32x32b_x16(taddr + (uint32_t)(t * BN + ch * 16), r);
+                    uint8_t* cell = out_buf + t * Cfg::kTileOut + staged_offset<BN>(row, ch);
+                    uint4 resv = make_uint4(0u, 0u, 0u, 0u);
+                    if (RES) resv = *reinterpret_cast<const uint4*>(cell);
+                    tmem_ld_wait16(r);
+                    const uint32_t resw[4] = {resv.x, resv.y, resv.z, resv.w};
+                    uint32_t outw[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t fb[4];
+                        if (kFold) {
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const int e0 = 4 * j + 2 * h;
+                                float t0 = fma_sat((float)(int)r[e0], __uint_as_float(mmw[e0]), __uint_as_float(addw[e0]));
+                                float t1 = fma_sat((float)(int)r[e0 + 1], __uint_as_float(mmw[e0 + 1]), __uint_as_float(addw[e0 + 1]));
+                                uint64_t f2 = add_rm_x2(pack2(fminf(t0, hi_s), fminf(t1, hi_s)), magic15x2);  // 2^15 + q / 256
+                                if (RES) {
+                                    const uint64_t u2 = sub_x2(f2, cy_s2);                                   // (q - y_zp) / 256, exact
+                                    const uint64_t w2 = sub_x2(pack2(byte_to_magic(resw[j], 2 * h), byte_to_magic(resw[j], 2 * h + 1)), cr2);
+                                    const uint64_t v2 = fma_x2(w2, roo_s2, mul_x2(u2, yoo2));
+                                    t0 = add_sat(lo_of(v2), oh_s);
+                                    t1 = add_sat(hi_of(v2), oh_s);
+                                    f2 = add_rm_x2(pack2(fminf(t0, 255.5f * kS), fminf(t1, 255.5f * kS)), magic15x2);
+                                }
+                                fb[2 * h] = (uint32_t)f2;
+                                fb[2 * h + 1] = (uint32_t)(f2 >> 32);
+                            }
+                        } else {
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const float a = (float)(int)(r[4 * j + b] + addw[4 * j + b]);
+                                float tp = qdiv(__fmul_rn(a, __uint_as_float(mmw[4 * j + b])), rq.y_div);
+                                tp = __fadd_rn(__fadd_rn(tp, rq.y_zp_f), 0.5f);
+                                fb[b] = __float_as_uint(quant_u8_up_magic(tp, hi_ph));
+                            }
+                            if (RES) {
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) {
+                                    const float u8v = __fsub_rn(__uint_as_float(fb[b]), cy);   // q - y_zp, exact
+                                    const float w = __fsub_rn(byte_to_magic(resw[j], b), cr);   // r - res_zp, exact
+                                    const float v = __fadd_rn(__fmul_rn(u8v, rq.y_scale), __fmul_rn(w, rq.res_scale));
+                                    const float tp = __fadd_rn(__fadd_rn(qdiv(v, rq.out_div), rq.out_zp_f), 0.5f);
+                                    fb[b] = __float_as_uint(__fadd_rd(fminf(fmaxf(tp, res_lo), 255.5f), kMagic23));
+                                }
+                            }
+                        }
+                        const uint32_t lo = __byte_perm(fb[0], fb[1], 0x0040), hi = __byte_perm(fb[2], fb[3], 0x0040);
+                        outw[j] = __byte_perm(lo, hi, 0x5410);
+                    }
+                    *reinterpret_cast<uint4*>(cell) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+                }
+                // Hand the accumulators back.
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                fence_async_smem();  // staged bytes become visible to the TMA store
+            }
+            if (!epilogue_rendezvous()) break;
+            if (issuer) {
+#pragma unroll
+                for (int t = 0; t < kR; ++t) {
+                    const int pt = pg * kR + t;
+                    if (pt < pos_tiles) {
+                        int w0, h0, n0;
+                        tile_origin(pt, w0, h0, n0);
+                        tma_store_4d(&tmY, smem_u32(out_buf + t * Cfg::kTileOut), col0, w0, h0, n0);
+                    }
+                }
+                tma_store_commit();
+            }
+        }
+        if (issuer) tma_store_wait_all();
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+template <int BN, int BK, int EPI, bool RES>
+int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p, int grid,
+                cudaStream_t s) {
+    using Cfg = Tc2Config<BN, BK, RES>;
+    static_assert(Cfg::kUsable, "grouped kernel: not enough shared memory for two stages");
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CHXQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    tc_igemm2_kernel<BN, BK, EPI, RES><<<grid, 576, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+// Launches the grouped kernel for (bn, BK, epi, residual); CHXQ_ERR_UNSUPPORTED when the combination has no instantiation.
+template <int BK>
+int launch_bk2(int bn, int epi, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
+               const TcParams& p, int grid, cudaStream_t s) {
+    const int key = (bn == 128 ? 4 : 0) + (epi == kEpiKU8Fold ? 2 : 0) + (res ? 1 : 0);
+    switch (key) {
+        case 0: return launch_one2<64, BK, kEpiKU8, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 2: return launch_one2<64, BK, kEpiKU8Fold, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 4: return launch_one2<128, BK, kEpiKU8, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 5: return launch_one2<128, BK, kEpiKU8, true>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 6: return launch_one2<128, BK, kEpiKU8Fold, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 7: return launch_one2<128, BK, kEpiKU8Fold, true>(tmA, tmB, tmY, tmR, p, grid, s);
+    }
+    return CHXQ_ERR_UNSUPPORTED;
+}
+
+}  // namespace tc
+}  // namespace chxq

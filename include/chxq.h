@@ -72,6 +72,12 @@ int64_t chxq_launch_count(void);
 int chxq_tc_profile(int32_t enable);
 int chxq_tc_profile_read(double* total_ms, int64_t* launches, double* total_macs);
 
+/* The tensor-core path has two kernels with identical results: one output tile per step (every epilogue), and grouped
+ * tiles whose uint8 outputs leave through shared memory and a TMA store (uint8 requantizing epilogues with 16-byte
+ * aligned output rows).  0 = choose by problem shape (default), 1 = always the first, 2 = the second whenever
+ * eligible.  Process-wide; meant for measurements and tests.  No counterpart in the reference. */
+int chxq_tc_variant(int32_t variant);
+
 /* Reads (and clears) the device-side status word of the current device.  SYNCHRONISES `stream`.
  * Returns CHXQ_OK or CHXQ_ERR_DEVICE_TIMEOUT. */
 int chxq_device_status(void* stream);

@@ -296,3 +296,88 @@ def test_qlinear_conv_folded_scales(ops, orc, dev, path, cl, N, C, H, W, M, k, s
         chain = orc.qadd_relu(emul, sy, zy, r, 0.05, 9, 0.11, 0, relu=True, round_mode=mode)
         assert lsb_report(yr, chain)[0] <= 2  # one step from the convolution, one from the folded tail
     ops.device_status()
+
+
+@pytest.fixture
+def grouped_kernel(pkg):
+    """Forces the grouped-tile tensor-core kernel wherever a problem is eligible; restores the default choice afterwards."""
+    assert pkg.lib().chxq_tc_variant(2) == 0
+    yield
+    assert pkg.lib().chxq_tc_variant(0) == 0
+
+
+GROUPED_CASES = [
+    (2, 64, 8, 8, 64, 1, 1, 0),      # one position tile in a group of four, 64-channel block
+    (3, 128, 7, 7, 256, 1, 1, 0),    # ragged positions, two channel blocks
+    (9, 64, 8, 8, 64, 3, 1, 1),      # 3x3 boxes, groups of four with a ragged last group
+    (2, 48, 12, 12, 80, 3, 1, 1),    # ragged channel block (80 of 128), K tile 64 with TMA zero fill
+    (2, 256, 14, 14, 128, 3, 1, 1),  # K tile 128
+    (1, 64, 10, 10, 64, 5, 1, 2),    # 5x5
+    (4, 64, 16, 16, 128, 1, 2, 0),   # stride 2 -> explicit im2col in front of the same kernel
+    (2, 144, 6, 6, 32, 1, 1, 0),     # ragged last K chunk, 32 output channels
+]
+
+
+@pytest.mark.parametrize("N,C,H,W,M,k,stride,pad", GROUPED_CASES)
+def test_grouped_tensor_core_kernel(pkg, ops, orc, dev, grouped_kernel, N, C, H, W, M, k, stride, pad):
+    """The grouped-tile kernel (outputs staged in shared memory, TMA store, residual by TMA load) against the oracle and,
+    bit for bit, against the one-tile-per-step kernel: reference-order and folded requantization, activation zero point,
+    ReLU6 clamp, residual tails with and without Relu."""
+    rng = np.random.default_rng(N * 1000 + C + M + k)
+    x = _rand(rng, (N, C, H, W), np.uint8)
+    w = _rand(rng, (M, C, k, k), np.int8, -127, 127)
+    ws = rng.uniform(0.0005, 0.002, M).astype(np.float32)
+    wz = np.zeros(M, np.int8)
+    bias = _rand(rng, M, np.int32, -3000, 3000)
+    Ho, Wo = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
+    r = _rand(rng, (N, M, Ho, Wo), np.uint8)
+    sx, sy = 0.02, 0.09
+    xt, wt, wst, wzt, bt, rt = _t(x, dev, True), _t(w, dev), _t(ws, dev), _t(wz, dev), _t(bias, dev), _t(r, dev, True)
+
+    def run(variant, zx, zy, **kw):
+        assert pkg.lib().chxq_tc_variant(variant) == 0
+        y = ops.QLinearConv(xt, sx, np.uint8(zx), wt, wst, wzt, sy, np.uint8(zy), bt, (stride, stride), (pad, pad), path=TENSOR, **kw)
+        ops.device_status()
+        return y
+
+    cases = [
+        dict(zx=0, zy=0, kw={}),
+        dict(zx=5, zy=17, kw={}),
+        dict(zx=0, zy=131, kw=dict(fold_scales=True)),
+        dict(zx=0, zy=0, kw=dict(clamp_hi_q=77)),
+        dict(zx=0, zy=121, kw=dict(residual=rt, res_scale=0.05, res_zero_point=9, out_scale=0.11, out_zero_point=0)),
+        dict(zx=0, zy=121, kw=dict(residual=rt, res_scale=0.05, res_zero_point=9, out_scale=0.11, out_zero_point=0, fold_scales=True)),
+        dict(zx=0, zy=121, kw=dict(residual=rt, res_scale=0.05, res_zero_point=9, out_scale=0.11, out_zero_point=100, res_relu=False)),
+        dict(zx=0, zy=121, kw=dict(residual=rt, res_scale=0.05, res_zero_point=9, out_scale=0.11, out_zero_point=100, res_relu=False,
+                                   fold_scales=True)),
+    ]
+    for c in cases:
+        got = run(2, c["zx"], c["zy"], **c["kw"])
+        ref = run(1, c["zx"], c["zy"], **c["kw"])
+        assert torch.equal(got, ref), c
+    acc = orc.conv_integer(x, w, 0, wz, (stride, stride), (pad, pad))
+    want = orc.requantize(acc, sx, ws, sy, 131, bias=bias, channel_axis=1, fold=True)
+    assert np.array_equal(run(2, 0, 131, fold_scales=True).cpu().numpy(), want)
+    want = orc.requantize(acc, sx, ws, sy, 121, bias=bias, channel_axis=1)
+    want_r = orc.qadd_relu(want, sy, 121, r, 0.05, 9, 0.11, 100, relu=False)
+    got = run(2, 0, 121, residual=rt, res_scale=0.05, res_zero_point=9, out_scale=0.11, out_zero_point=100, res_relu=False)
+    assert np.array_equal(got.cpu().numpy(), want_r)
+
+
+def test_grouped_kernel_networks(pkg, ops, dev, grouped_kernel):
+    """ResNet-50 (reduced width) through the grouped kernel equals the same network through the one-tile kernel."""
+    from chainer_compiler_b200 import models
+    net = models.ResNet50Int8(batch=8, device=dev, seed=4, image=64, num_classes=32, width_mult=0.5)
+    xt = torch.rand((8, 3, 64, 64), generator=torch.Generator().manual_seed(1)).to(dev)
+    net.calibrate(xt)
+    for fold in (False, True):
+        assert pkg.lib().chxq_tc_variant(2) == 0
+        t2 = {}
+        l2 = net.forward(xt, fold=fold, taps=t2)
+        ops.device_status()
+        assert pkg.lib().chxq_tc_variant(1) == 0
+        t1 = {}
+        l1 = net.forward(xt, fold=fold, taps=t1)
+        for k in t1:
+            assert torch.equal(t1[k], t2[k]), (fold, k)
+        assert torch.equal(l1, l2)
