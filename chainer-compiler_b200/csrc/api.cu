@@ -365,6 +365,7 @@ int conv_tc_run(
             p.Wo = g.Wo; p.Ho = g.Ho; p.No = g.N;
         }
         p.c_pad = pl.c_pitch; p.KH = g.KH; p.KW = g.KW; p.pad_top = g.pad_top; p.pad_left = g.pad_left;
+        p.sw = g.stride_w; p.sh = g.stride_h;
         p.Wb = pl.Wb; p.Hb = pl.Hb; p.Nb = pl.Nb;
     }
     p.a_signed = x_signed;

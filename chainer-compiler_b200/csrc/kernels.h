@@ -55,6 +55,7 @@ struct TcProblem {
     int bk;           // 32 / 64 / 128
     // convolution taps (1,1,0,0 for a plain GEMM)
     int KH, KW, pad_top, pad_left;
+    int sw, sh;       // convolution strides, applied by the TMA box as element strides (0 reads as 1)
     // output extents (positions) and tile box
     int Wo, Ho, No;
     int Wb, Hb, Nb;

@@ -372,39 +372,74 @@ __global__ void __launch_bounds__(256) global_avgpool_dq_kernel(
     y[idx] = __fmul_rn(__fdiv_rn((float)s, (float)HW), scale);
 }
 
-// fp32 Linear: y[n,o] = fma chain over k ascending of x[n,k] * w[o,k], then + b[o].  32 x 64 output tile per block, each
-// thread a 2 x 4 patch, operands staged through shared memory in 32-wide K slices.  Every output is accumulated by one
-// thread in k order (no split-K), so the result does not depend on the tiling.
+// fp32 Linear: y[n,o] = fma chain over k ascending of x[n,k] * w[o,k], then + b[o].  Every output is accumulated by one
+// thread in k order (no split-K), so the result does not depend on the tiling.  32 x 64 output tile per block of 256
+// threads; a thread owns rows {2 tn, 2 tn + 1} and columns {to + 16 j}: with K-major tiles of pitch 36 floats in shared
+// memory its 128-bit reads along k are conflict-free (the eight lanes of a quarter warp read eight different rows whose
+// starts are 36 floats apart, or all the same row).  The next K slice is fetched into registers while the current one is
+// consumed, and shared memory is double-buffered, so there is one barrier per slice.
+constexpr int kLinKS = 32;     // K slice
+constexpr int kLinPitch = 36;  // floats
+
 __global__ void __launch_bounds__(256) linear_f32_kernel(
         const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, int N, int K, int O, float* __restrict__ y) {
-    __shared__ __align__(16) float Xs[32][34];   // [k][n]  (K slice major, so a thread reads its two rows as one 64-bit word)
-    __shared__ __align__(16) float Ws[32][68];   // [k][o]  (a thread reads its four columns as one 128-bit word)
+    __shared__ __align__(16) float Xs[2][32][kLinPitch];
+    __shared__ __align__(16) float Ws[2][64][kLinPitch];
     const int tid = threadIdx.x;
-    const int tn = tid / 16, to = tid % 16;   // 16 x 16 threads: rows tn*2.., cols to*4..
+    const int tn = tid / 16, to = tid % 16;
     const int n0 = blockIdx.y * 32, o0 = blockIdx.x * 64;
-    float acc[2][4] = {};
-    for (int k0 = 0; k0 < K; k0 += 32) {
-        for (int i = tid; i < 32 * 32; i += 256) {
-            const int r = i / 32, c = i % 32;
-            Xs[c][r] = (n0 + r < N && k0 + c < K) ? x[(int64_t)(n0 + r) * K + k0 + c] : 0.f;
-        }
-        for (int i = tid; i < 64 * 32; i += 256) {
-            const int r = i / 32, c = i % 32;
-            Ws[c][r] = (o0 + r < O && k0 + c < K) ? w[(int64_t)(o0 + r) * K + k0 + c] : 0.f;
-        }
-        __syncthreads();
-        const int kmax = min(32, K - k0);
-        for (int kk = 0; kk < kmax; ++kk) {
-            const float2 xv = *reinterpret_cast<const float2*>(&Xs[kk][tn * 2]);
-            const float4 wv = *reinterpret_cast<const float4*>(&Ws[kk][to * 4]);
-            const float ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                acc[0][j] = __fmaf_rn(xv.x, ww[j], acc[0][j]);
-                acc[1][j] = __fmaf_rn(xv.y, ww[j], acc[1][j]);
+    const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(w) & 15u) == 0);
+    // staging assignment: one float4 of X (row tid / 8, k offset 4 (tid % 8)) and two of W (rows tid / 8 and 32 + tid / 8)
+    const int sr = tid / 8, sk = (tid % 8) * 4;
+    auto fetch = [&](const float* base, int row, int rows, int k0) -> float4 {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < rows) {
+            const float* p = base + (int64_t)row * K + k0 + sk;
+            if (vec && k0 + sk + 4 <= K) {
+                v = *reinterpret_cast<const float4*>(p);
+            } else {
+                if (k0 + sk + 0 < K) v.x = p[0];
+                if (k0 + sk + 1 < K) v.y = p[1];
+                if (k0 + sk + 2 < K) v.z = p[2];
+                if (k0 + sk + 3 < K) v.w = p[3];
             }
         }
+        return v;
+    };
+    float acc[2][4] = {};
+    float4 px = fetch(x, n0 + sr, N, 0), pw0 = fetch(w, o0 + sr, O, 0), pw1 = fetch(w, o0 + 32 + sr, O, 0);
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += kLinKS, buf ^= 1) {
+        *reinterpret_cast<float4*>(&Xs[buf][sr][sk]) = px;
+        *reinterpret_cast<float4*>(&Ws[buf][sr][sk]) = pw0;
+        *reinterpret_cast<float4*>(&Ws[buf][32 + sr][sk]) = pw1;
         __syncthreads();
+        if (k0 + kLinKS < K) {
+            px = fetch(x, n0 + sr, N, k0 + kLinKS);
+            pw0 = fetch(w, o0 + sr, O, k0 + kLinKS);
+            pw1 = fetch(w, o0 + 32 + sr, O, k0 + kLinKS);
+        }
+        // Elements past K are zero in both operands; fma(0, 0, acc) leaves acc as it is, so the slice is always run in full.
+#pragma unroll
+        for (int k4 = 0; k4 < kLinKS; k4 += 4) {
+            float4 xv[2], wv[4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) xv[i] = *reinterpret_cast<const float4*>(&Xs[buf][tn * 2 + i][k4]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const float4*>(&Ws[buf][to + 16 * j][k4]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float a = acc[i][j];
+                    a = __fmaf_rn(xv[i].x, wv[j].x, a);
+                    a = __fmaf_rn(xv[i].y, wv[j].y, a);
+                    a = __fmaf_rn(xv[i].z, wv[j].z, a);
+                    a = __fmaf_rn(xv[i].w, wv[j].w, a);
+                    acc[i][j] = a;
+                }
+        }
+        // the buffer written next iteration is the other one; its readers finished before this iteration's barrier
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -412,7 +447,7 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(
         if (n >= N) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int o = o0 + to * 4 + j;
+            const int o = o0 + to + 16 * j;
             if (o < O) y[(int64_t)n * O + o] = __fadd_rn(acc[i][j], b ? b[o] : 0.f);
         }
     }

@@ -106,7 +106,8 @@ TcConvPlan plan_tc_conv(const chxq_conv_geom& g) {
     if (g.group != 1 || g.y_layout != CHXQ_NHWC) return pl;
     const int taps = g.KH * g.KW;
     const int64_t xcs = g.x_cstride > 0 ? g.x_cstride : g.C;
-    const bool direct = g.x_layout == CHXQ_NHWC && g.stride_h == 1 && g.stride_w == 1 && (xcs % 16 == 0) && g.pad_top >= 0 && g.pad_left >= 0 &&
+    const bool direct = g.x_layout == CHXQ_NHWC && g.stride_h >= 1 && g.stride_w >= 1 && g.stride_h <= 8 && g.stride_w <= 8 && (xcs % 16 == 0) &&
+                        g.pad_top >= 0 && g.pad_left >= 0 &&
                         g.pad_bottom >= 0 && g.pad_right >= 0 && g.pad_top < g.KH && g.pad_left < g.KW && g.C >= 16;
     if (direct) {
         pl.path = kTcDirect;
@@ -114,7 +115,8 @@ TcConvPlan plan_tc_conv(const chxq_conv_geom& g) {
         pl.c_pitch = (g.C + pl.bk - 1) / pl.bk * pl.bk;
         pl.k_total = taps * pl.c_pitch;
         pl.a_pitch = pl.k_total;
-        if (taps == 1 && g.pad_top == 0 && g.pad_left == 0 && g.pad_bottom == 0 && g.pad_right == 0 && (int64_t)g.N * g.H * g.W < (1ll << 31)) {
+        if (taps == 1 && g.stride_h == 1 && g.stride_w == 1 && g.pad_top == 0 && g.pad_left == 0 && g.pad_bottom == 0 && g.pad_right == 0 &&
+            (int64_t)g.N * g.H * g.W < (1ll << 31)) {
             // 1x1: the map is a plain [N*H*W, C] matrix.
             pl.Wb = 128; pl.Hb = 1; pl.Nb = 1;
         } else {
@@ -168,6 +170,9 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     if (total_tiles >= (1ll << 31)) return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: too many tiles");
     p.Wo = q.Wo; p.Ho = q.Ho; p.No = q.No;
     p.KH = q.KH; p.KW = q.KW; p.pad_top = q.pad_top; p.pad_left = q.pad_left;
+    p.sw = q.sw > 0 ? q.sw : 1; p.sh = q.sh > 0 ? q.sh : 1;
+    if (p.sw > 8 || p.sh > 8 || q.Wb * p.sw > 256 || q.Hb * p.sh > 256)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: stride %d x %d does not fit a TMA box", p.sh, p.sw);
     p.c_pad = q.c_pad;
     p.c_chunks = q.c_pad / q.bk;
     p.cols = q.cols;
@@ -184,13 +189,14 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     p.vec_ok = ((reinterpret_cast<uintptr_t>(q.y) & 15u) == 0) && ((q.ldc * elt) % 16 == 0) &&
                (q.epi.residual == nullptr || (reinterpret_cast<uintptr_t>(q.epi.residual) & 15u) == 0);
 
-    // A: {C, W, H, N} bytes, pitches {a_cs, W*a_cs, H*W*a_cs}; box {bk, Wb, Hb, Nb}; out-of-range reads fill 0.
+    // A: {C, W, H, N} bytes, pitches {a_cs, W*a_cs, H*W*a_cs}; box {bk, Wb, Hb, Nb} output positions, i.e. {bk, Wb*sw, Hb*sh, Nb}
+    // input elements traversed with element strides {1, sw, sh, 1}; out-of-range reads fill 0.
     alignas(64) CUtensorMap tmA, tmB;
     {
         const cuuint64_t dims[4] = {(cuuint64_t)q.C, (cuuint64_t)q.W, (cuuint64_t)q.H, (cuuint64_t)q.N};
         const cuuint64_t strides[3] = {(cuuint64_t)q.a_cs, (cuuint64_t)q.a_cs * q.W, (cuuint64_t)q.a_cs * q.W * q.H};
-        const cuuint32_t box[4] = {(cuuint32_t)q.bk, (cuuint32_t)q.Wb, (cuuint32_t)q.Hb, (cuuint32_t)q.Nb};
-        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        const cuuint32_t box[4] = {(cuuint32_t)q.bk, (cuuint32_t)(q.Wb * p.sw), (cuuint32_t)(q.Hb * p.sh), (cuuint32_t)q.Nb};
+        const cuuint32_t estr[4] = {1, (cuuint32_t)p.sw, (cuuint32_t)p.sh, 1};
         CUresult r = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             swizzle_for(q.bk), CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed with %d", (int)r);

@@ -278,7 +278,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 pt /= p.tiles_w;
                 const int th = pt % p.tiles_h;
                 const int tn = pt / p.tiles_h;
-                const int w0 = tw * p.Wb - p.pad_left, h0 = th * p.Hb - p.pad_top, n0 = tn * p.Nb;
+                const int w0 = tw * p.Wb * p.sw - p.pad_left, h0 = th * p.Hb * p.sh - p.pad_top, n0 = tn * p.Nb;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;

@@ -224,7 +224,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (int t = 0; t < kR; ++t)
                         tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA + t * 128 * BK), &tmA, full_bar(stage), cc * BK,
-                                    w0[t] - p.pad_left + kw, h0[t] - p.pad_top + kh, n0[t]);
+                                    w0[t] * p.sw - p.pad_left + kw, h0[t] * p.sh - p.pad_top + kh, n0[t]);
                     tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), tap * p.c_pad + cc * BK, ct * BN);
                     if (++stage == kStages) {
                         stage = 0;

@@ -15,6 +15,7 @@ struct TcParams {
     int col_tiles;                   // ceil(cols / BN)
     int Wo, Ho, No;
     int KH, KW, pad_top, pad_left;
+    int sw, sh;  // convolution strides: input coordinate = output coordinate * stride - pad + tap
     int c_chunks;  // c_pad / BK
     int c_pad;
     int cols;

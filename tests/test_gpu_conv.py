@@ -55,8 +55,8 @@ TC_CASES = [
     (2, 48, 12, 12, 80, 3, 1, 1),    # C = 48 -> bk 32 + zero-filled chunk? (48 = 32 + 16), box 4x4x8
     (2, 144, 6, 6, 32, 1, 1, 0),     # C = 144 -> ragged last K chunk filled by TMA
     (2, 256, 14, 14, 128, 3, 1, 1),  # box 2x2x32, bk 128
-    (4, 64, 16, 16, 128, 1, 2, 0),   # stride 2 1x1 -> im2col (gather)
-    (2, 16, 9, 9, 24, 3, 2, 1),      # stride 2 3x3 -> im2col, M = 24 (ragged column tile, scalar stores)
+    (4, 64, 16, 16, 128, 1, 2, 0),   # stride 2 1x1: TMA box with element strides
+    (2, 16, 9, 9, 24, 3, 2, 1),      # stride 2 3x3 with padding (strided box, shifted per tap), M = 24 (ragged column tile, scalar stores)
     (1, 64, 10, 10, 64, 5, 1, 2),    # 5x5
 ]
 
@@ -313,7 +313,7 @@ GROUPED_CASES = [
     (2, 48, 12, 12, 80, 3, 1, 1),    # ragged channel block (80 of 128), K tile 64 with TMA zero fill
     (2, 256, 14, 14, 128, 3, 1, 1),  # K tile 128
     (1, 64, 10, 10, 64, 5, 1, 2),    # 5x5
-    (4, 64, 16, 16, 128, 1, 2, 0),   # stride 2 -> explicit im2col in front of the same kernel
+    (4, 64, 16, 16, 128, 1, 2, 0),   # stride 2: TMA box with element strides
     (2, 144, 6, 6, 32, 1, 1, 0),     # ragged last K chunk, 32 output channels
 ]
 
