@@ -130,11 +130,11 @@ __global__ void __launch_bounds__(256) rowsum_matrix_kernel(const uint8_t* __res
     if (lane == 0) R[r] = s - sub;
 }
 
-// Receptive-field sums of an NHWC map for the direct path:
+// Receptive-field sums of a map addressed by element strides (es_n, es_c, es_h, es_w):
 // S[pos] = sum over taps inside the map and channels of (x - x_zp).  One thread per output position.
 __global__ void __launch_bounds__(256) conv_possum_kernel(
-        const uint8_t* __restrict__ x, int x_signed, int N, int H, int W, int C, int64_t cs, int KH, int KW, int sh, int sw, int pt, int pl, int Ho,
-        int Wo, int x_zp, int32_t* __restrict__ S) {
+        const uint8_t* __restrict__ x, int x_signed, int N, int H, int W, int C, int64_t es_n, int64_t es_c, int64_t es_h, int64_t es_w, int KH,
+        int KW, int sh, int sw, int pt, int pl, int Ho, int Wo, int x_zp, int32_t* __restrict__ S) {
     const int64_t total = (int64_t)N * Ho * Wo;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
@@ -149,11 +149,61 @@ __global__ void __launch_bounds__(256) conv_possum_kernel(
         for (int kw = 0; kw < KW; ++kw) {
             const int wi = wo * sw - pl + kw;
             if (wi < 0 || wi >= W) continue;
-            const uint8_t* p = x + (((int64_t)n * H + hi) * W + wi) * cs;
-            for (int c = 0; c < C; ++c) s += (x_signed ? (int)(int8_t)p[c] : (int)p[c]) - x_zp;
+            const uint8_t* p = x + (int64_t)n * es_n + (int64_t)hi * es_h + (int64_t)wi * es_w;
+            for (int c = 0; c < C; ++c) s += (x_signed ? (int)(int8_t)p[c * es_c] : (int)p[c * es_c]) - x_zp;
         }
     }
     S[idx] = s;
+}
+
+// Space-to-depth repack for the stride-2 small-channel path: block (n, r, b) of the output holds the 2x2 pixels
+// (2 (r + t0h) + dy, 2 (b + t0w) + dx), channel-minor, as 16 bytes [(dy*2+dx)*C + c]; pixels outside the map hold the
+// activation zero point, unused bytes hold zero (their weights are zero).  One thread per block.
+__global__ void __launch_bounds__(256) s2d_repack_kernel(
+        const uint8_t* __restrict__ x, int N, int C, int H, int W, int64_t es_n, int64_t es_c, int64_t es_h, int64_t es_w, int t0h, int t0w,
+        int rows2, int cols2, uint32_t pad_byte, uint4* __restrict__ out) {
+    const int64_t total = (int64_t)N * rows2 * cols2;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int b = (int)(idx % cols2);
+    const int64_t q = idx / cols2;
+    const int r = (int)(q % rows2);
+    const int n = (int)(q / rows2);
+    uint32_t word[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+        const int yy = 2 * (r + t0h) + (d >> 1), xx = 2 * (b + t0w) + (d & 1);
+        const bool inside = yy >= 0 && yy < H && xx >= 0 && xx < W;
+        const uint8_t* p = x + (int64_t)n * es_n + (int64_t)yy * es_h + (int64_t)xx * es_w;
+        for (int c = 0; c < C; ++c) {
+            const uint32_t v = inside ? (uint32_t)p[c * es_c] : pad_byte;
+            const int pos = d * C + c;
+            word[pos >> 2] |= v << (8 * (pos & 3));
+        }
+    }
+    out[idx] = make_uint4(word[0], word[1], word[2], word[3]);
+}
+
+// OIHW weights -> the K layout of the space-to-depth path: row m, K index t * bk + u * 16 + (dy*2+dx) * C + c holds
+// w[m][c][kh][kw] with kh = 2 (t + t0h) + dy + pad_top, kw = 2 (u + t0w) + dx + pad_left, zero where no such tap exists.
+__global__ void __launch_bounds__(256) pack_weights_s2d_kernel(
+        const uint8_t* __restrict__ w, int M, int C, int KH, int KW, int pt, int pl, int t0h, int t0w, int kw2, int bk, int k_total,
+        uint8_t* __restrict__ out) {
+    const int64_t total = (int64_t)M * k_total;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int k = (int)(i % k_total);
+        const int m = (int)(i / k_total);
+        const int t = k / bk, within = k % bk;
+        const int u = within / 16, e = within % 16;
+        uint8_t v = 0;
+        if (u < kw2 && e < 4 * C) {
+            const int d = e / C, c = e % C;
+            const int kh = 2 * (t + t0h) + (d >> 1) + pt, kw = 2 * (u + t0w) + (d & 1) + pl;
+            if (kh >= 0 && kh < KH && kw >= 0 && kw < KW) v = w[(((int64_t)m * C + c) * KH + kh) * KW + kw];
+        }
+        out[i] = v;
+    }
 }
 
 inline int blocks_for(int64_t threads_needed, int block = 256) {
@@ -292,13 +342,13 @@ ConvWs conv_ws_layout(const chxq_conv_geom& g, const TcConvPlan& pl) {
     w.flag_off = off; off += 256;
     w.pack_total = off;
     const size_t rows = (size_t)g.N * g.Ho * g.Wo;
-    w.im2col_bytes = align_up(rows * (size_t)pl.a_pitch, 1024);
+    w.im2col_bytes = pl.path == kTcS2d ? align_up((size_t)g.N * pl.rows2 * pl.cols2 * 16 + 256, 1024) : align_up(rows * (size_t)pl.a_pitch, 1024);
     w.rowsum_bytes = align_up(rows * 4, 256);
     return w;
 }
 
 bool needs_im2col(const chxq_conv_geom& g, const TcConvPlan& pl, int x_zp) {
-    if (pl.path == kTcIm2col) return true;
+    if (pl.path == kTcIm2col || pl.path == kTcS2d) return true;  // S2d: the repacked map lives in the same scratch
     const bool padded = g.pad_top || g.pad_left || g.pad_bottom || g.pad_right;
     return pl.path == kTcDirect && padded && x_zp != 0;
 }
@@ -308,8 +358,13 @@ int pack_weights(const void* w, const chxq_conv_geom& g, const TcConvPlan& pl, c
     const int taps = g.KH * g.KW;
     int32_t* flag = reinterpret_cast<int32_t*>(blob + L.flag_off);
     CHXQ_CUDA(cudaMemsetAsync(flag, 0, 4, s));
-    pack_weights_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, g.C, taps, pl.c_pitch, pl.k_total,
-                                                                              blob + L.pack_off);
+    if (pl.path == kTcS2d)
+        pack_weights_s2d_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, g.C, g.KH, g.KW, g.pad_top,
+                                                                                      g.pad_left, pl.t0h, pl.t0w, pl.kw2, pl.bk, pl.k_total,
+                                                                                      blob + L.pack_off);
+    else
+        pack_weights_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, g.C, taps, pl.c_pitch,
+                                                                                  pl.k_total, blob + L.pack_off);
     weight_terms_kernel<<<blocks_for((int64_t)g.M * 32), 256, 0, s>>>(w, g.w_dtype == CHXQ_INT8, g.M, g.C * taps, zw,
                                                                      reinterpret_cast<int32_t*>(blob + L.wsum_off),
                                                                      reinterpret_cast<int32_t*>(blob + L.zw_off), flag);
@@ -336,7 +391,28 @@ int conv_tc_run(
     const bool x_signed = g.x_dtype == CHXQ_INT8;
     TcProblem p{};
     int32_t* rowsum = nullptr;
-    if (im2col) {
+    // element strides of the input map
+    const bool nhwc = g.x_layout == CHXQ_NHWC;
+    const int64_t es_c = nhwc ? 1 : (int64_t)g.H * g.W, es_w = nhwc ? xcs : 1, es_h = nhwc ? xcs * g.W : g.W,
+                  es_n = nhwc ? xcs * g.W * g.H : (int64_t)g.C * g.H * g.W;
+    if (pl.path == kTcS2d) {
+        uint8_t* A = scratch;
+        s2d_repack_kernel<<<blocks_for((int64_t)g.N * pl.rows2 * pl.cols2), 256, 0, s>>>(static_cast<const uint8_t*>(x), g.N, g.C, g.H, g.W, es_n, es_c,
+                                                                                        es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2,
+                                                                                        (uint32_t)(x_zp & 0xff), reinterpret_cast<uint4*>(A));
+        CHXQ_LAUNCH_CHECK();
+        if (!zw_zero) {
+            rowsum = reinterpret_cast<int32_t*>(scratch + L.im2col_bytes);
+            conv_possum_kernel<<<blocks_for(rows), 256, 0, s>>>(static_cast<const uint8_t*>(x), x_signed, g.N, g.H, g.W, g.C, es_n, es_c, es_h, es_w,
+                                                              g.KH, g.KW, g.stride_h, g.stride_w, g.pad_top, g.pad_left, g.Ho, g.Wo, x_zp, rowsum);
+            CHXQ_LAUNCH_CHECK();
+        }
+        // Overlapping rows: output column wo reads the bk bytes that start 16 wo bytes into block row (ho + t).
+        p.a = A; p.C = pl.bk; p.a_cs = 16; p.W = g.Wo; p.H = pl.rows2; p.N = g.N;
+        p.c_pad = pl.bk; p.KH = pl.kh2; p.KW = 1; p.pad_top = 0; p.pad_left = 0; p.sw = 1; p.sh = 1;
+        p.a_row_bytes = (int64_t)pl.cols2 * 16;
+        p.Wo = g.Wo; p.Ho = g.Ho; p.No = g.N; p.Wb = pl.Wb; p.Hb = pl.Hb; p.Nb = pl.Nb;
+    } else if (im2col) {
         uint8_t* A = scratch;
         int rc = launch_im2col(x, g, pl.c_pitch, pl.a_pitch, x_zp & 0xff, A, s);
         if (rc != CHXQ_OK) return rc;
@@ -352,8 +428,8 @@ int conv_tc_run(
     } else {
         if (!zw_zero) {
             rowsum = reinterpret_cast<int32_t*>(scratch);
-            conv_possum_kernel<<<blocks_for(rows), 256, 0, s>>>(static_cast<const uint8_t*>(x), x_signed, g.N, g.H, g.W, g.C, xcs, g.KH, g.KW,
-                                                              g.stride_h, g.stride_w, g.pad_top, g.pad_left, g.Ho, g.Wo, x_zp, rowsum);
+            conv_possum_kernel<<<blocks_for(rows), 256, 0, s>>>(static_cast<const uint8_t*>(x), x_signed, g.N, g.H, g.W, g.C, es_n, es_c, es_h, es_w,
+                                                              g.KH, g.KW, g.stride_h, g.stride_w, g.pad_top, g.pad_left, g.Ho, g.Wo, x_zp, rowsum);
             CHXQ_LAUNCH_CHECK();
         }
         p.a = x; p.C = g.C; p.a_cs = xcs;
@@ -636,7 +712,7 @@ extern "C" size_t chxq_conv_workspace(const chxq_conv_geom* g) {
     const bool padded = g->pad_top || g->pad_left || g->pad_bottom || g->pad_right;
     // Worst case over zero points: an explicit im2col matrix when the direct path cannot express the
     // padding value, and per-position sums when the weight zero point is non-zero.
-    const size_t im2col = (pl.path == kTcIm2col || padded) ? L.im2col_bytes : 0;
+    const size_t im2col = (pl.path == kTcIm2col || pl.path == kTcS2d || padded) ? L.im2col_bytes : 0;
     return L.pack_total + im2col + L.rowsum_bytes;
 }
 

@@ -46,6 +46,7 @@ struct TcProblem {
     int a_signed;
     int C;            // channels (K extent per tap) present in memory
     int64_t a_cs;     // bytes between consecutive W positions
+    int64_t a_row_bytes;  // bytes between consecutive H rows; 0 = W * a_cs (a larger value lets rows of C bytes overlap: a_cs < C)
     int W, H, N;      // extents of the A map
     // B operand
     const void* b;    // [cols][taps * c_pad]
@@ -75,7 +76,7 @@ struct TcProblem {
 int launch_tc_igemm(const TcProblem& p, cudaStream_t s);
 
 // Tensor-core planning shared by pre-packing and execution.
-enum TcConvPath : int { kTcNone = 0, kTcDirect = 1, kTcIm2col = 2 };
+enum TcConvPath : int { kTcNone = 0, kTcDirect = 1, kTcIm2col = 2, kTcS2d = 3 };
 struct TcConvPlan {
     int path;
     int bk;
@@ -83,6 +84,10 @@ struct TcConvPlan {
     int k_total;   // packed weight row length (multiple of bk)
     int a_pitch;   // row length of the explicit im2col matrix (multiple of 16; the K tail up to k_total is TMA zero fill)
     int Wb, Hb, Nb;
+    // kTcS2d (stride 2, at most 4 channels): the map is repacked as 2x2 pixel blocks of 16 bytes; a K tile is one row of
+    // kw2 blocks, there are kh2 such rows per output; t0h / t0w are the (negative) block offsets of the first tap;
+    // rows2 x cols2 blocks per image including the halo.
+    int kh2, kw2, t0h, t0w, rows2, cols2;
 };
 TcConvPlan plan_tc_conv(const chxq_conv_geom& g);
 int choose_bk(int k);

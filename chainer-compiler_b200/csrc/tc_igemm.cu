@@ -106,6 +106,28 @@ TcConvPlan plan_tc_conv(const chxq_conv_geom& g) {
     if (g.group != 1 || g.y_layout != CHXQ_NHWC) return pl;
     const int taps = g.KH * g.KW;
     const int64_t xcs = g.x_cstride > 0 ? g.x_cstride : g.C;
+    // Stride-2 convolutions over at most 4 channels (network stems): space-to-depth.  A 2x2 pixel block becomes one
+    // 16-byte pixel (4 C <= 16 channels), the KH x KW stride-2 window becomes a kh2 x kw2 stride-1 window over blocks, and
+    // the kw2 blocks of one window row are contiguous in memory: 16 kw2 bytes, advancing by 16 bytes per output column.
+    if (g.stride_h == 2 && g.stride_w == 2 && g.C <= 4 && g.pad_top >= 0 && g.pad_left >= 0 && g.pad_bottom >= 0 && g.pad_right >= 0) {
+        auto floor_half = [](int a) { return a >= 0 ? a / 2 : -((-a + 1) / 2); };
+        const int t0h = floor_half(-g.pad_top), t0w = floor_half(-g.pad_left);
+        const int kh2 = floor_half(g.KH - 1 - g.pad_top) - t0h + 1, kw2 = floor_half(g.KW - 1 - g.pad_left) - t0w + 1;
+        if (kw2 * 16 <= 128 && kh2 <= 64) {
+            pl.path = kTcS2d;
+            pl.bk = kw2 * 16 <= 64 ? 64 : 128;
+            pl.c_pitch = pl.bk;
+            pl.k_total = kh2 * pl.bk;
+            pl.a_pitch = pl.bk;
+            pl.kh2 = kh2; pl.kw2 = kw2; pl.t0h = t0h; pl.t0w = t0w;
+            pl.rows2 = g.Ho + kh2 - 1;
+            pl.cols2 = g.Wo + pl.bk / 16 - 1;  // the last window of a row ends inside the row, zero weights beyond kw2 blocks
+            pl.Wb = largest_pow2_divisor(g.Wo, 16);
+            pl.Hb = largest_pow2_divisor(g.Ho, 128 / pl.Wb);
+            pl.Nb = 128 / (pl.Wb * pl.Hb);
+            return pl;
+        }
+    }
     const bool direct = g.x_layout == CHXQ_NHWC && g.stride_h >= 1 && g.stride_w >= 1 && g.stride_h <= 8 && g.stride_w <= 8 && (xcs % 16 == 0) &&
                         g.pad_top >= 0 && g.pad_left >= 0 &&
                         g.pad_bottom >= 0 && g.pad_right >= 0 && g.pad_top < g.KH && g.pad_left < g.KW && g.C >= 16;
@@ -194,7 +216,8 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     alignas(64) CUtensorMap tmA, tmB;
     {
         const cuuint64_t dims[4] = {(cuuint64_t)q.C, (cuuint64_t)q.W, (cuuint64_t)q.H, (cuuint64_t)q.N};
-        const cuuint64_t strides[3] = {(cuuint64_t)q.a_cs, (cuuint64_t)q.a_cs * q.W, (cuuint64_t)q.a_cs * q.W * q.H};
+        const cuuint64_t row_bytes = q.a_row_bytes > 0 ? (cuuint64_t)q.a_row_bytes : (cuuint64_t)q.a_cs * q.W;
+        const cuuint64_t strides[3] = {(cuuint64_t)q.a_cs, row_bytes, row_bytes * q.H};
         const cuuint32_t box[4] = {(cuuint32_t)q.bk, (cuuint32_t)(q.Wb * p.sw), (cuuint32_t)(q.Hb * p.sh), (cuuint32_t)q.Nb};
         const cuuint32_t estr[4] = {1, (cuuint32_t)p.sw, (cuuint32_t)p.sh, 1};
         CUresult r = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -88,23 +88,43 @@ def test_conv_integer_tensor_zero_points(ops, orc, dev, N, C, H, W, M, k, stride
     assert np.array_equal(y.cpu().numpy(), want)
 
 
-def test_conv_integer_stem_nchw_input_packed(ops, orc, dev, pkg):
-    """7x7 / 2 stem over a 3-channel NCHW map (im2col path) through the packed entry, NHWC output."""
+@pytest.mark.parametrize("shape,M,k,pad,nchw", [
+    ((3, 3, 30, 30), 64, 7, 3, True),    # ResNet stem: 4 x 4 blocks per window
+    ((2, 3, 17, 21), 32, 3, 1, True),    # MobileNet stem, odd map
+    ((2, 1, 16, 16), 16, 5, 2, True),    # one channel, 5x5
+    ((2, 4, 13, 12), 24, 4, 0, False),   # NHWC input with four channels, no padding, even window
+    ((1, 2, 9, 9), 8, 2, 0, True),       # 2x2 / 2: a single block per window
+])
+def test_conv_stride2_small_channel_space_to_depth(ops, orc, dev, pkg, shape, M, k, pad, nchw):
+    """Stride-2 convolutions over at most four channels (network stems) run as a stride-1 convolution over 2x2 pixel blocks
+    read through a TMA map with overlapping rows; packed entry, NHWC output.  Accumulators against the oracle with and
+    without zero points (the block map's halo holds the activation zero point), and the requantizing entry on top."""
     import ctypes
     from chainer_compiler_b200 import _lib
-    rng = np.random.default_rng(8)
-    x = _rand(rng, (3, 3, 30, 30), np.uint8)
-    w = _rand(rng, (64, 3, 7, 7), np.int8)
-    pk = ops.PackedConv(_t(w, dev), None, x.shape, (2, 2), (3, 3), x_layout=_lib.NCHW)
-    assert pk.eligible and (pk.flags & 2)
-    g = pk.g
-    y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.int32, device=dev, memory_format=torch.channels_last)
-    nb = pkg.lib().chxq_conv_packed_workspace(ctypes.byref(g), 0, pk.flags)
-    ws = ops.workspace(nb, dev)
-    _lib.check(pkg.lib().chxq_conv_integer_packed(ops._ptr(_t(x, dev)), ops._ptr(pk.blob), ctypes.byref(g), 1, 0, pk.flags, ops._ptr(y), ops._ptr(ws),
-                                                  nb, ops._stream()))
-    ops.device_status()
-    assert np.array_equal(y.cpu().numpy(), orc.conv_integer(x, w, 0, None, (2, 2), (3, 3)))
+    rng = np.random.default_rng(k * 10 + M)
+    x = _rand(rng, shape, np.uint8)
+    w = _rand(rng, (M, shape[1], k, k), np.int8)
+    xt = _t(x, dev) if nchw else _t(x, dev, True)
+    for zx, wz in ((0, None), (77, None), (5, _rand(rng, M, np.int8, -9, 9))):
+        pk = ops.PackedConv(_t(w, dev), _t(wz, dev), x.shape, (2, 2), (pad, pad), x_layout=_lib.NCHW if nchw else _lib.NHWC)
+        assert pk.eligible
+        g = pk.g
+        y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.int32, device=dev, memory_format=torch.channels_last)
+        nb = pkg.lib().chxq_conv_packed_workspace(ctypes.byref(g), zx, pk.flags)
+        ws = ops.workspace(nb, dev)
+        _lib.check(pkg.lib().chxq_conv_integer_packed(ops._ptr(xt), ops._ptr(pk.blob), ctypes.byref(g), 1, zx, pk.flags, ops._ptr(y), ops._ptr(ws),
+                                                      nb, ops._stream()))
+        ops.device_status()
+        assert np.array_equal(y.cpu().numpy(), orc.conv_integer(x, w, zx, wz, (2, 2), (pad, pad))), (zx, wz is not None)
+    pk = ops.PackedConv(_t(w, dev), None, x.shape, (2, 2), (pad, pad), x_layout=_lib.NCHW if nchw else _lib.NHWC)
+    ws_ = rng.uniform(0.0005, 0.002, M).astype(np.float32)
+    bias = _rand(rng, M, np.int32, -3000, 3000)
+    wz0 = np.zeros(M, np.int8)
+    for fold in (False, True):
+        yq = ops.QLinearConvPacked(xt, pk, 0.02, np.uint8(3), _t(ws_, dev), _t(wz0, dev), 0.05, np.uint8(20), b=_t(bias, dev), fold_scales=fold)
+        ops.device_status()
+        acc = orc.conv_integer(x, w, 3, wz0, (2, 2), (pad, pad))
+        assert np.array_equal(yq.cpu().numpy(), orc.requantize(acc, 0.02, ws_, 0.05, 20, bias=bias, channel_axis=1, fold=fold)), fold
 
 
 @pytest.mark.parametrize("path,cl", [(SIMT, False), (SIMT, True), (TENSOR, True)])
