@@ -65,36 +65,29 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
-// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is incomplete: a waiting
-// warp then issues (almost) nothing instead of spinning next to the warps that do the work.
-__device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t"
-            "}\n"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity), "r"(ns)
-            : "memory");
-    return ok;
-}
-
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
-constexpr uint32_t kSuspendNs = 20000u;           // one suspended try: 20 us at most, then the abort flag and the clock are looked at
 
-// Bounded wait.  Returns false when the CTA is aborting (either this wait expired or another did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+// Bounded wait.  Returns false when the CTA is aborting (either this wait expired or another did).  A waiting warp sleeps
+// between polls (doubling from sleep_ns up to 8 * sleep_ns): polling at full speed takes issue slots from the warps that
+// do the work.  The abort flag and the clock are looked at every 128 polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, uint32_t sleep_ns = 64) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    uint64_t t0 = 0;
+    uint32_t polls = 0, ns = sleep_ns;
+    const uint32_t ns_max = sleep_ns * 8u;
     while (true) {
-        if (mbar_try_wait_suspend(bar, parity, kSuspendNs)) return true;
-        if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
-            *abort_flag = 1;
-            atomicCAS(status, 0, code);
-            return false;
+        __nanosleep(ns);
+        if (mbar_try_wait(bar, parity)) return true;
+        if (ns < ns_max) ns <<= 1;
+        if ((++polls & 127u) == 0u) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
         }
     }
 }
@@ -282,7 +275,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 128)) {
                         ok = false;
                         break;
                     }
@@ -306,11 +299,11 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) break;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2, 128)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 16)) {
                         ok = false;
                         break;
                     }
@@ -402,7 +395,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             };
             uint4 res0 = res_load(0), res1 = res_load(1);
 
-            const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4);
+            const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4, 32);
             if (!__all_sync(0xffffffffu, got)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);

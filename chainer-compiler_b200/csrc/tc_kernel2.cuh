@@ -207,7 +207,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
                 if (RES) {
                     const int rb = it % 3;
-                    if (!mbar_wait(rempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5)) break;
+                    if (!mbar_wait(rempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5, 128)) break;
                     mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
 #pragma unroll
                     for (int t = 0; t < kR; ++t)
@@ -216,7 +216,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 128)) {
                         ok = false;
                         break;
                     }
@@ -243,11 +243,11 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int grp = blockIdx.x; grp < total_groups && ok; grp += gridDim.x, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) break;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2, 128)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * 256);
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 16)) {
                         ok = false;
                         break;
                     }
@@ -307,7 +307,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         auto epilogue_rendezvous = [&]() -> bool {
             __syncwarp();
             if (lane == 0) mbar_arrive(esync_bar);
-            const bool ok = mbar_wait(esync_bar, esync_phase, abort_flag, p.status, 7);
+            const bool ok = mbar_wait(esync_bar, esync_phase, abort_flag, p.status, 7, 32);
             esync_phase ^= 1u;
             return __all_sync(0xffffffffu, ok);
         };
@@ -353,47 +353,36 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (RES && it >= 2) mbar_arrive(rempty_bar((it - 2) % 3));
             }
             bool got = epilogue_rendezvous();
-            if (got) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4);
-            if (RES && got) got = mbar_wait(rfull_bar(buf), (uint32_t)(it / 3) & 1u, abort_flag, p.status, 6);
+            if (got) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4, 32);
+            if (RES && got) got = mbar_wait(rfull_bar(buf), (uint32_t)(it / 3) & 1u, abort_flag, p.status, 6, 32);
             if (!__all_sync(0xffffffffu, got)) break;
             {
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 256);
-                uint32_t mmw[16], addw[16];  // multipliers (float bits) and additive terms of the current chunk
-#pragma unroll
-                for (int u = 0; u < kUnits; ++u) {
+                // One unit: 16 accumulators of (chunk i, tile t) in registers -> 16 staged bytes.  The per-channel multiplier
+                // and additive term come from the per-warp cache four channels at a time.
+                auto process = [&](uint32_t (&r)[16], const int u) {
                     const int i = u / kR, t = u % kR;
                     const int ch = i * 4 + sub;
-                    if (col0 + ch * 16 >= p.cols) continue;  // warp-uniform; clipped by the store anyway
-                    if (t == 0) {
-                        const uint4* pm = reinterpret_cast<const uint4*>(s_mult + i * 16);
-                        const uint4* pa = reinterpret_cast<const uint4*>(s_add + i * 16);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint4 m4 = pm[j];
-                            const uint4 a4 = pa[j];
-                            mmw[4 * j] = m4.x; mmw[4 * j + 1] = m4.y; mmw[4 * j + 2] = m4.z; mmw[4 * j + 3] = m4.w;
-                            addw[4 * j] = a4.x; addw[4 * j + 1] = a4.y; addw[4 * j + 2] = a4.z; addw[4 * j + 3] = a4.w;
-                        }
-                    }
-                    uint32_t r[16];
-                    __syncwarp();
-                    tmem_ld_32x32b_x16(taddr + (uint32_t)(t * BN + ch * 16), r);
                     uint8_t* cell = out_buf + t * Cfg::kTileOut + staged_offset<BN>(row, ch);
                     uint4 resv = make_uint4(0u, 0u, 0u, 0u);
                     if (RES) resv = *reinterpret_cast<const uint4*>(cell);
-                    tmem_ld_wait16(r);
                     const uint32_t resw[4] = {resv.x, resv.y, resv.z, resv.w};
+                    const uint4* pm = reinterpret_cast<const uint4*>(s_mult + i * 16);
+                    const uint4* pa = reinterpret_cast<const uint4*>(s_add + i * 16);
                     uint32_t outw[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
+                        const uint4 m4 = pm[j], a4 = pa[j];
+                        const uint32_t mmw[4] = {m4.x, m4.y, m4.z, m4.w};
+                        const uint32_t addw[4] = {a4.x, a4.y, a4.z, a4.w};
                         uint32_t fb[4];
                         if (kFold) {
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
-                                const int e0 = 4 * j + 2 * h;
-                                float t0 = fma_sat((float)(int)r[e0], __uint_as_float(mmw[e0]), __uint_as_float(addw[e0]));
-                                float t1 = fma_sat((float)(int)r[e0 + 1], __uint_as_float(mmw[e0 + 1]), __uint_as_float(addw[e0 + 1]));
+                                const int e0 = 2 * h;
+                                float t0 = fma_sat((float)(int)r[4 * j + e0], __uint_as_float(mmw[e0]), __uint_as_float(addw[e0]));
+                                float t1 = fma_sat((float)(int)r[4 * j + e0 + 1], __uint_as_float(mmw[e0 + 1]), __uint_as_float(addw[e0 + 1]));
                                 uint64_t f2 = add_rm_x2(pack2(fminf(t0, hi_s), fminf(t1, hi_s)), magic15x2);  // 2^15 + q / 256
                                 if (RES) {
                                     const uint64_t u2 = sub_x2(f2, cy_s2);                                   // (q - y_zp) / 256, exact
@@ -409,8 +398,8 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         } else {
 #pragma unroll
                             for (int b = 0; b < 4; ++b) {
-                                const float a = (float)(int)(r[4 * j + b] + addw[4 * j + b]);
-                                float tp = qdiv(__fmul_rn(a, __uint_as_float(mmw[4 * j + b])), rq.y_div);
+                                const float a = (float)(int)(r[4 * j + b] + addw[b]);
+                                float tp = qdiv(__fmul_rn(a, __uint_as_float(mmw[b])), rq.y_div);
                                 tp = __fadd_rn(__fadd_rn(tp, rq.y_zp_f), 0.5f);
                                 fb[b] = __float_as_uint(quant_u8_up_magic(tp, hi_ph));
                             }
@@ -429,6 +418,25 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         outw[j] = __byte_perm(lo, hi, 0x5410);
                     }
                     *reinterpret_cast<uint4*>(cell) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+                };
+                auto unit_valid = [&](int u) { return col0 + ((u / kR) * 4 + sub) * 16 < p.cols; };  // warp-uniform; beyond: clipped by the store
+                auto unit_taddr = [&](int u) { return taddr + (uint32_t)((u % kR) * BN + ((u / kR) * 4 + sub) * 16); };
+                // The TMEM read of unit u + 1 is in flight while unit u is processed.
+                uint32_t ra[16], rb[16];
+                __syncwarp();
+                if (unit_valid(0)) tmem_ld_32x32b_x16(unit_taddr(0), ra);
+#pragma unroll
+                for (int u = 0; u < kUnits; ++u) {
+                    const bool valid = unit_valid(u);
+                    if (u & 1) {
+                        if (valid) tmem_ld_wait16(rb);
+                        if (u + 1 < kUnits && unit_valid(u + 1)) tmem_ld_32x32b_x16(unit_taddr(u + 1), ra);
+                        if (valid) process(rb, u);
+                    } else {
+                        if (valid) tmem_ld_wait16(ra);
+                        if (u + 1 < kUnits && unit_valid(u + 1)) tmem_ld_32x32b_x16(unit_taddr(u + 1), rb);
+                        if (valid) process(ra, u);
+                    }
                 }
                 // Hand the accumulators back.
                 tc_fence_before();
