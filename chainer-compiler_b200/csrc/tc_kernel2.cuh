@@ -15,6 +15,9 @@
 //   * The folded requantization runs scaled by 2^-8 (exact), so that the saturating fma / add clamp at zero for free, and
 //     on pairs of floats (fma / add / mul .f32x2) wherever no clamp is involved.
 //
+//   * A nineteenth warp issues the TMA stores: the epilogue warps only count themselves in on an mbarrier when their part
+//     of a group is staged, so they never wait for one another.
+//
 // TMEM holds two groups (2 x R x BN = 512 columns): the epilogue of group i overlaps the main loop of group i + 1.  The
 // staging tiles are multi-buffered as well.  Every wait is bounded exactly as in tc_kernel.cuh.
 #pragma once
@@ -104,8 +107,8 @@ struct Tc2Config {
     static constexpr int kStagesRaw = (kBudget - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kTmemCols = 512;
-    // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], res_full[3], res_empty[3], epilogue rendezvous
-    static constexpr int kBarBytes = (2 * kStages + 11) * 8;
+    // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], res_full[3], buf_empty[3], buf_full[3]
+    static constexpr int kBarBytes = (2 * kStages + 13) * 8;
     static constexpr int kBarOffset = kStages * kStageBytes + kFixed;
     static constexpr int kParamOffset = ((kBarOffset + kBarBytes + 16 + 15) / 16) * 16;
     static constexpr int kParamBytes = 16 * (BN / 2) * 4;  // 16 warps x (BN/4 multipliers + BN/4 additive terms)
@@ -121,7 +124,7 @@ __device__ __forceinline__ uint32_t staged_offset(int row, int unit) {
 }
 
 template <int BN, int BK, int EPI, bool RES>
-__global__ void __launch_bounds__(576, 1)
+__global__ void __launch_bounds__(608, 1)
 tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const TcParams p) {
     using Cfg = Tc2Config<BN, BK, RES>;
@@ -134,7 +137,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint8_t* smem_b = smem + kStages * Cfg::kStageA;
     uint8_t* smem_out = smem + kStages * Cfg::kStageBytes;  // [kBufs][kR][128][BN], 1024-byte aligned (all sizes are multiples of 1024)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOffset);
-    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 11);
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
     const uint32_t bar_base = smem_u32(bars);
@@ -143,8 +146,10 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
     auto rfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 4 + b); };
-    auto rempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 7 + b); };
-    const uint32_t esync_bar = bar_base + 8u * (2 * kStages + 10);
+    // buffer b of the staging ring: empty = the store out of it has read it (the residual load / the epilogue may write it),
+    // full = all sixteen epilogue warps have staged their part of it
+    auto bempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 7 + b); };
+    auto bfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 10 + b); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -160,9 +165,9 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         for (int b = 0; b < 3; ++b) {
             mbar_init(rfull_bar(b), 1);
-            mbar_init(rempty_bar(b), 1);  // the thread that issues the stores, once the store out of the buffer has read it
+            mbar_init(bempty_bar(b), 1);  // the store warp
+            mbar_init(bfull_bar(b), 16);  // one arrival per epilogue warp
         }
-        mbar_init(esync_bar, 16);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -207,7 +212,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
                 if (RES) {
                     const int rb = it % 3;
-                    if (!mbar_wait(rempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5, 128)) break;
+                    if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5, 128)) break;
                     mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
 #pragma unroll
                     for (int t = 0; t < kR; ++t)
@@ -271,7 +276,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (ok) umma_commit(tfull_bar(acc));  // all kR accumulators complete
             }
         }
-    } else {
+    } else if (warp < 18) {
         // ---------------- epilogue warps ----------------
         // Warp w reads TMEM lanes 32*(w % 4) .. +31 (one output position per thread and tile); the four warps of a lane
         // quarter take every fourth 16-channel chunk.  A unit of work is (chunk, tile): 16 accumulators in, 16 bytes out.
@@ -281,7 +286,6 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int quarter = warp & 3;
         const int sub = e >> 2;
         const int row = quarter * 32 + lane;
-        const bool issuer = e == 0 && lane == 0;
         float* s_mult = reinterpret_cast<float*>(smem + Cfg::kParamOffset) + e * (BN / 2);
         uint32_t* s_add = reinterpret_cast<uint32_t*>(s_mult + BN / 4);
         int cached_ct = -1;
@@ -302,15 +306,6 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint64_t yoo2 = pack2(rq.y_over_out, rq.y_over_out);
         const uint64_t roo_s2 = pack2(rq.res_over_out * kS, rq.res_over_out * kS);
         const float oh_s = out_half * kS;
-        // Rendezvous of the sixteen epilogue warps on an mbarrier (bounded like every other wait; bar.sync has no way out).
-        uint32_t esync_phase = 0;
-        auto epilogue_rendezvous = [&]() -> bool {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(esync_bar);
-            const bool ok = mbar_wait(esync_bar, esync_phase, abort_flag, p.status, 7, 32);
-            esync_phase ^= 1u;
-            return __all_sync(0xffffffffu, ok);
-        };
         int it = 0;
         for (int grp = blockIdx.x; grp < total_groups; grp += gridDim.x, ++it) {
             const int acc = it & 1;
@@ -345,16 +340,13 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 cached_ct = ct;
             }
 
-            // Stores up to the one issued two groups ago have read their buffers: without a residual that frees this group's
-            // buffer for the epilogue; with one it frees the buffer the producer loads the NEXT group's residual into.
+            // The buffer is ready when the store that last used it has read it (no residual) or when this group's residual
+            // has landed in it (which the producer starts only after that store).
             uint8_t* out_buf = smem_out + buf * (kR * Cfg::kTileOut);
-            if (issuer) {
-                tma_store_wait_read<1>();
-                if (RES && it >= 2) mbar_arrive(rempty_bar((it - 2) % 3));
-            }
-            bool got = epilogue_rendezvous();
+            const uint32_t use_phase = (uint32_t)(it / Cfg::kBufs) & 1u;
+            bool got = RES ? mbar_wait(rfull_bar(buf), use_phase, abort_flag, p.status, 6, 32)
+                           : mbar_wait(bempty_bar(buf), use_phase ^ 1u, abort_flag, p.status, 7, 32);
             if (got) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4, 32);
-            if (RES && got) got = mbar_wait(rfull_bar(buf), (uint32_t)(it / 3) & 1u, abort_flag, p.status, 6, 32);
             if (!__all_sync(0xffffffffu, got)) break;
             {
                 tc_fence_after();
@@ -438,27 +430,43 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         if (valid) process(ra, u);
                     }
                 }
-                // Hand the accumulators back.
+                // Hand the accumulators back and the staged tile over to the store warp.
                 tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar(acc));
                 fence_async_smem();  // staged bytes become visible to the TMA store
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(tempty_bar(acc));
+                    mbar_arrive(bfull_bar(buf));
+                }
             }
-            if (!epilogue_rendezvous()) break;
-            if (issuer) {
+        }
+    } else if (warp == 18) {
+        // ---------------- store warp ----------------
+        // One lane: waits until all sixteen epilogue warps have staged a group, issues its TMA stores, waits until they have
+        // read the buffer and hands the buffer back (to the epilogue, or to the producer for the next residual tile).
+        if (lane == 0) {
+            int it = 0;
+            for (int grp = blockIdx.x; grp < total_groups; grp += gridDim.x, ++it) {
+                const int ct = grp % p.col_tiles;
+                const int pg = grp / p.col_tiles;
+                const int buf = it % Cfg::kBufs;
+                if (!mbar_wait(bfull_bar(buf), (uint32_t)(it / Cfg::kBufs) & 1u, abort_flag, p.status, 8, 128)) break;
+                uint8_t* out_buf = smem_out + buf * (kR * Cfg::kTileOut);
 #pragma unroll
                 for (int t = 0; t < kR; ++t) {
                     const int pt = pg * kR + t;
                     if (pt < pos_tiles) {
                         int w0, h0, n0;
                         tile_origin(pt, w0, h0, n0);
-                        tma_store_4d(&tmY, smem_u32(out_buf + t * Cfg::kTileOut), col0, w0, h0, n0);
+                        tma_store_4d(&tmY, smem_u32(out_buf + t * Cfg::kTileOut), ct * BN, w0, h0, n0);
                     }
                 }
                 tma_store_commit();
+                tma_store_wait_read<0>();
+                mbar_arrive(bempty_bar(buf));
             }
+            tma_store_wait_all();
         }
-        if (issuer) tma_store_wait_all();
     }
 
     // ---------------- teardown ----------------
@@ -487,7 +495,7 @@ int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
         CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    tc_igemm2_kernel<BN, BK, EPI, RES><<<grid, 576, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
+    tc_igemm2_kernel<BN, BK, EPI, RES><<<grid, 608, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }
