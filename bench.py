@@ -158,8 +158,10 @@ def run_reference(args):
     import __graft_entry__ as entry
     orc = entry.load_oracle()
     from oracle import networks
+    # every host core this process may run on (torchrun exports OMP_NUM_THREADS=1, which is not what the reference arm is for)
+    orc.set_num_threads(len(os.sched_getaffinity(0)))
     cores = orc.num_threads()
-    n_img = 2
+    n_img = 8 if cores >= 8 else 2
     rng = np.random.default_rng(0)
     sample = rng.uniform(0, 1, (n_img, 3, IMAGE, IMAGE)).astype(np.float32)
     params = cpu_reference_params(orc, networks, 0, sample)
@@ -289,6 +291,7 @@ def run_chxq(args):
         if not args.no_cpu_baseline:
             orc = entry.load_oracle()
             from oracle import networks
+            orc.set_num_threads(len(os.sched_getaffinity(0)))
             sample = host_x[: args.cpu_sample].numpy()
             params = net.export_numpy()
             sec = time_cpu(orc, networks, params, sample)
