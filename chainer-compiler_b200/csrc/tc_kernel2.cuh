@@ -221,7 +221,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 128)) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 16)) {
                         ok = false;
                         break;
                     }
@@ -248,7 +248,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int grp = blockIdx.x; grp < total_groups && ok; grp += gridDim.x, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2, 128)) break;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2, 32)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * 256);
                 for (int kb = 0; kb < num_kb; ++kb) {
