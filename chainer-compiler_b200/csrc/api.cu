@@ -206,6 +206,20 @@ __global__ void __launch_bounds__(256) pack_weights_s2d_kernel(
     }
 }
 
+// Depthwise OIHW weights [M][1][taps] -> dense diagonal blocks: row m, K index tap * 64 + (m % 64) holds w[m][tap], the
+// other 63 entries of each tap are zero.
+__global__ void __launch_bounds__(256) pack_weights_diag_kernel(const uint8_t* __restrict__ w, int M, int taps, uint8_t* __restrict__ out) {
+    const int64_t total = (int64_t)M * taps * 64;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int j = (int)(i % 64);
+        const int64_t r = i / 64;
+        const int tap = (int)(r % taps);
+        const int m = (int)(r / taps);
+        out[i] = j == (m & 63) ? w[(int64_t)m * taps + tap] : (uint8_t)0;
+    }
+}
+
 inline int blocks_for(int64_t threads_needed, int block = 256) {
     int64_t b = (threads_needed + block - 1) / block;
     if (b < 1) b = 1;
@@ -358,14 +372,17 @@ int pack_weights(const void* w, const chxq_conv_geom& g, const TcConvPlan& pl, c
     const int taps = g.KH * g.KW;
     int32_t* flag = reinterpret_cast<int32_t*>(blob + L.flag_off);
     CHXQ_CUDA(cudaMemsetAsync(flag, 0, 4, s));
-    if (pl.path == kTcS2d)
+    const int cg = g.C / g.group;
+    if (pl.diag)
+        pack_weights_diag_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, taps, blob + L.pack_off);
+    else if (pl.path == kTcS2d)
         pack_weights_s2d_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, g.C, g.KH, g.KW, g.pad_top,
                                                                                       g.pad_left, pl.t0h, pl.t0w, pl.kw2, pl.bk, pl.k_total,
                                                                                       blob + L.pack_off);
     else
-        pack_weights_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, g.C, taps, pl.c_pitch,
+        pack_weights_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, cg, taps, pl.c_pitch,
                                                                                   pl.k_total, blob + L.pack_off);
-    weight_terms_kernel<<<blocks_for((int64_t)g.M * 32), 256, 0, s>>>(w, g.w_dtype == CHXQ_INT8, g.M, g.C * taps, zw,
+    weight_terms_kernel<<<blocks_for((int64_t)g.M * 32), 256, 0, s>>>(w, g.w_dtype == CHXQ_INT8, g.M, cg * taps, zw,
                                                                      reinterpret_cast<int32_t*>(blob + L.wsum_off),
                                                                      reinterpret_cast<int32_t*>(blob + L.zw_off), flag);
     count_launch(1);
@@ -382,6 +399,9 @@ int conv_tc_run(
     const int64_t rows = (int64_t)g.N * g.Ho * g.Wo;
     if (rows == 0) return CHXQ_OK;
     const bool im2col = needs_im2col(g, pl, x_zp);
+    if (g.group > 1 && (im2col || !zw_zero))
+        return set_error(CHXQ_ERR_UNSUPPORTED,
+                         "grouped convolution on the tensor-core path needs zero weight zero points and, with padding, a zero activation zero point");
     const size_t need = (im2col ? L.im2col_bytes : 0) + (zw_zero ? 0 : L.rowsum_bytes);
     if (need > 0 && (scratch == nullptr || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u)))
         return set_error(CHXQ_ERR_WORKSPACE, "convolution: tensor-core path needs %zu bytes of 256-byte aligned workspace (got %zu)", need,
@@ -442,6 +462,7 @@ int conv_tc_run(
         }
         p.c_pad = pl.c_pitch; p.KH = g.KH; p.KW = g.KW; p.pad_top = g.pad_top; p.pad_left = g.pad_left;
         p.sw = g.stride_w; p.sh = g.stride_h;
+        p.group_cols = pl.group_cols; p.group_cin = pl.group_cin;
         p.Wb = pl.Wb; p.Hb = pl.Hb; p.Nb = pl.Nb;
     }
     p.a_signed = x_signed;
@@ -452,7 +473,7 @@ int conv_tc_run(
     p.col_mul = zw_zero ? nullptr : reinterpret_cast<const int32_t*>(blob + L.zw_off);
     p.row_corr = zw_zero ? nullptr : rowsum;
     p.epi = epi;
-    p.alg_macs = (double)rows * g.M * g.C * taps;
+    p.alg_macs = (double)rows * g.M * (g.C / g.group) * taps;
     return launch_tc_igemm(p, s);
 }
 
@@ -470,6 +491,12 @@ int conv_dispatch(
     const TcConvPlan pl = plan_tc_conv(*g);
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     bool use_tc = path != CHXQ_PATH_SIMT && pl.path != kTcNone && aligned;
+    if (g->group > 1 && use_tc) {
+        // the grouped tensor-core path covers uint8 round-half-up epilogues (and raw accumulators) with absent weight zero points
+        const bool padded = g->pad_top || g->pad_left || g->pad_bottom || g->pad_right;
+        const bool epi_ok = epi.mode != kEpiRequant || (!epi.rq.y_signed && epi.rq.round_mode == 0);
+        if (zw.len != 0 || (padded && xz != 0) || !epi_ok) use_tc = false;
+    }
     if (path == CHXQ_PATH_TENSOR && !use_tc)
         return set_error(CHXQ_ERR_UNSUPPORTED, "%s: the tensor-core path needs group == 1, NHWC output and a 16-byte aligned input", op);
     if (use_tc) {

@@ -57,6 +57,9 @@ struct TcProblem {
     // convolution taps (1,1,0,0 for a plain GEMM)
     int KH, KW, pad_top, pad_left;
     int sw, sh;       // convolution strides, applied by the TMA box as element strides (0 reads as 1)
+    // grouped convolution: output columns [g * group_cols, (g + 1) * group_cols) read input channels starting at g * group_cin
+    // (0 = one group).  The column tile must not straddle groups: bn divides group_cols.
+    int group_cols, group_cin;
     // output extents (positions) and tile box
     int Wo, Ho, No;
     int Wb, Hb, Nb;
@@ -88,6 +91,9 @@ struct TcConvPlan {
     // kw2 blocks, there are kh2 such rows per output; t0h / t0w are the (negative) block offsets of the first tap;
     // rows2 x cols2 blocks per image including the halo.
     int kh2, kw2, t0h, t0w, rows2, cols2;
+    // grouped convolutions on the direct path (see TcProblem::group_cols); diag: depthwise weights expanded to dense
+    // 64 x 64 diagonal blocks
+    int group_cols, group_cin, diag;
 };
 TcConvPlan plan_tc_conv(const chxq_conv_geom& g);
 int choose_bk(int k);

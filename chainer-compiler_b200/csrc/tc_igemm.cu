@@ -103,9 +103,32 @@ static int largest_pow2_divisor(int v, int cap) {
 TcConvPlan plan_tc_conv(const chxq_conv_geom& g) {
     TcConvPlan pl{};
     pl.path = kTcNone;
-    if (g.group != 1 || g.y_layout != CHXQ_NHWC) return pl;
+    if (g.y_layout != CHXQ_NHWC) return pl;
     const int taps = g.KH * g.KW;
     const int64_t xcs = g.x_cstride > 0 ? g.x_cstride : g.C;
+    if (g.group != 1) {
+        // Grouped convolutions: a column tile of 64 output channels reads only its group's input channels.  Depthwise
+        // (one channel per group) runs as groups of 64 channels whose 64 x 64 weight blocks are diagonal: 64 times the
+        // multiply-accumulates of the definition, on a tensor pipe with that much to spare, against a memory-bound layer.
+        const int cg = g.C / g.group, mg = g.M / g.group;
+        const bool depthwise = cg == 1 && mg == 1;
+        const bool ok = g.x_layout == CHXQ_NHWC && (xcs % 16 == 0) && g.stride_h <= 8 && g.stride_w <= 8 && g.pad_top >= 0 && g.pad_left >= 0 &&
+                        g.pad_bottom >= 0 && g.pad_right >= 0 && g.pad_top < g.KH && g.pad_left < g.KW &&
+                        (depthwise ? g.C % 16 == 0 : (mg % 64 == 0 && cg % 16 == 0));
+        if (!ok) return pl;
+        pl.path = kTcDirect;
+        pl.diag = depthwise ? 1 : 0;
+        pl.group_cols = depthwise ? 64 : mg;
+        pl.group_cin = depthwise ? 64 : cg;
+        pl.bk = depthwise ? 64 : choose_bk(cg);
+        pl.c_pitch = depthwise ? 64 : (cg + pl.bk - 1) / pl.bk * pl.bk;
+        pl.k_total = taps * pl.c_pitch;
+        pl.a_pitch = pl.k_total;
+        pl.Wb = largest_pow2_divisor(g.Wo, 16);
+        pl.Hb = largest_pow2_divisor(g.Ho, 128 / pl.Wb);
+        pl.Nb = 128 / (pl.Wb * pl.Hb);
+        return pl;
+    }
     // Stride-2 convolutions over at most 4 channels (network stems): space-to-depth.  A 2x2 pixel block becomes one
     // 16-byte pixel (4 C <= 16 channels), the KH x KW stride-2 window becomes a kh2 x kw2 stride-1 window over blocks, and
     // the kw2 blocks of one window row are contiguous in memory: 16 kw2 bytes, advancing by 16 bytes per output column.
@@ -186,13 +209,16 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     p.tiles_h = (q.Ho + q.Hb - 1) / q.Hb;
     p.tiles_n = (q.No + q.Nb - 1) / q.Nb;
     const int64_t pos_tiles = (int64_t)p.tiles_w * p.tiles_h * p.tiles_n;
-    const int bn = epi_kind == tc::kEpiKGeneric ? 128 : (q.bn ? q.bn : pick_bn(q.cols, pos_tiles));
+    if (q.group_cols > 0 && q.group_cols % 64 != 0)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: grouped convolution needs a multiple of 64 output channels per group");
+    const int bn = q.group_cols > 0 ? 64 : (epi_kind == tc::kEpiKGeneric ? 128 : (q.bn ? q.bn : pick_bn(q.cols, pos_tiles)));
     p.col_tiles = (q.cols + bn - 1) / bn;
     const int64_t total_tiles = pos_tiles * p.col_tiles;
     if (total_tiles >= (1ll << 31)) return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: too many tiles");
     p.Wo = q.Wo; p.Ho = q.Ho; p.No = q.No;
     p.KH = q.KH; p.KW = q.KW; p.pad_top = q.pad_top; p.pad_left = q.pad_left;
     p.sw = q.sw > 0 ? q.sw : 1; p.sh = q.sh > 0 ? q.sh : 1;
+    p.group_cols = q.group_cols; p.group_cin = q.group_cin;
     if (p.sw > 8 || p.sh > 8 || q.Wb * p.sw > 256 || q.Hb * p.sh > 256)
         return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: stride %d x %d does not fit a TMA box", p.sh, p.sw);
     p.c_pad = q.c_pad;
@@ -238,7 +264,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
 
     // Grouped-tile kernel (tc_kernel2.cuh): uint8 epilogues whose outputs (and residual) can move through TMA.
     bool grouped = false;
-    int bn2 = q.cols > 64 ? 128 : 64;
+    int bn2 = (q.cols > 64 && q.group_cols == 0) ? 128 : 64;
     alignas(64) CUtensorMap tmY, tmR;
     if ((epi_kind == tc::kEpiKU8 || epi_kind == tc::kEpiKU8Fold) && g_variant != 1 && p.vec_ok && q.ldc % 16 == 0 && (q.bk == 64 || q.bk == 128) &&
         !(epi_kind == tc::kEpiKU8Fold && q.col_corr != nullptr) && !(q.epi.residual != nullptr && bn2 == 64) &&

@@ -272,6 +272,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int th = pt % p.tiles_h;
                 const int tn = pt / p.tiles_h;
                 const int w0 = tw * p.Wb * p.sw - p.pad_left, h0 = th * p.Hb * p.sh - p.pad_top, n0 = tn * p.Nb;
+                const int gbase = p.group_cols > 0 ? (ct * BN / p.group_cols) * p.group_cin : 0;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
@@ -280,7 +281,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         break;
                     }
                     mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
-                    tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA), &tmA, full_bar(stage), cc * BK, w0 + kw, h0 + kh, n0);
+                    tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA), &tmA, full_bar(stage), gbase + cc * BK, w0 + kw, h0 + kh, n0);
                     tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), tap * p.c_pad + cc * BK, ct * BN);
                     if (++stage == kStages) {
                         stage = 0;

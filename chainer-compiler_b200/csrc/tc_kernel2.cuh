@@ -210,6 +210,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 int w0[kR], h0[kR], n0[kR];
 #pragma unroll
                 for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
+                const int gbase = p.group_cols > 0 ? (ct * BN / p.group_cols) * p.group_cin : 0;
                 if (RES) {
                     const int rb = it % 3;
                     if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5, 128)) break;
@@ -228,7 +229,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
 #pragma unroll
                     for (int t = 0; t < kR; ++t)
-                        tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA + t * 128 * BK), &tmA, full_bar(stage), cc * BK,
+                        tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA + t * 128 * BK), &tmA, full_bar(stage), gbase + cc * BK,
                                     w0[t] * p.sw - p.pad_left + kw, h0[t] * p.sh - p.pad_top + kh, n0[t]);
                     tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), tap * p.c_pad + cc * BK, ct * BN);
                     if (++stage == kStages) {

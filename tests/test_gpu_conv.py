@@ -401,3 +401,47 @@ def test_grouped_kernel_networks(pkg, ops, dev, grouped_kernel):
         for k in t1:
             assert torch.equal(t1[k], t2[k]), (fold, k)
         assert torch.equal(l1, l2)
+
+
+@pytest.mark.parametrize("N,C,H,W,M,group,k,stride,pad", [
+    (2, 32, 14, 14, 32, 32, 3, 1, 1),     # depthwise, one ragged block of 64
+    (3, 96, 15, 13, 96, 96, 3, 2, 1),     # depthwise stride 2, odd map, two blocks (64 + 32)
+    (2, 144, 8, 8, 144, 144, 3, 1, 1),    # depthwise, 144 = 2 x 64 + 16
+    (2, 16, 9, 9, 16, 16, 5, 1, 2),       # depthwise 5x5
+    (2, 64, 8, 8, 128, 2, 3, 1, 1),       # two groups of 32 -> 64 channels
+    (1, 48, 10, 10, 192, 3, 1, 1, 0),     # three groups of 16 -> 64, 1x1
+])
+def test_grouped_conv_tensor_core_packed(pkg, ops, orc, dev, N, C, H, W, M, group, k, stride, pad):
+    """Grouped and depthwise convolutions on the tensor-core path (packed entry): a column tile reads its group's input
+    channels only; depthwise weights become diagonal 64 x 64 blocks.  Accumulators and requantized outputs against the
+    oracle, with and without an activation zero point where the geometry allows it."""
+    import ctypes
+    from chainer_compiler_b200 import _lib
+    rng = np.random.default_rng(C + M + k)
+    x = _rand(rng, (N, C, H, W), np.uint8)
+    w = _rand(rng, (M, C // group, k, k), np.int8)
+    xt = _t(x, dev, True)
+    pk = ops.PackedConv(_t(w, dev), None, x.shape, (stride, stride), (pad, pad), group=group)
+    assert pk.eligible and (pk.flags & 2)
+    g = pk.g
+    for zx in ((0,) if pad else (0, 9)):
+        y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.int32, device=dev, memory_format=torch.channels_last)
+        nb = pkg.lib().chxq_conv_packed_workspace(ctypes.byref(g), zx, pk.flags)
+        ws = ops.workspace(nb, dev)
+        _lib.check(pkg.lib().chxq_conv_integer_packed(ops._ptr(xt), ops._ptr(pk.blob), ctypes.byref(g), 1, zx, pk.flags, ops._ptr(y), ops._ptr(ws),
+                                                      nb, ops._stream()))
+        ops.device_status()
+        assert np.array_equal(y.cpu().numpy(), orc.conv_integer(x, w, zx, None, (stride, stride), (pad, pad), group)), zx
+    ws_ = rng.uniform(0.0005, 0.002, M).astype(np.float32)
+    bias = _rand(rng, M, np.int32, -3000, 3000)
+    wz0 = np.zeros(M, np.int8)
+    acc = orc.conv_integer(x, w, 0, wz0, (stride, stride), (pad, pad), group)
+    for fold in (False, True):
+        for variant in (1, 2):
+            assert pkg.lib().chxq_tc_variant(variant) == 0
+            yq = ops.QLinearConvPacked(xt, pk, 0.02, np.uint8(0), _t(ws_, dev), _t(wz0, dev), 0.05, np.uint8(20), b=_t(bias, dev), fold_scales=fold,
+                                       clamp_hi_q=200)
+            ops.device_status()
+            want = orc.requantize(acc, 0.02, ws_, 0.05, 20, bias=bias, channel_axis=1, fold=fold, clamp_hi_q=200)
+            assert np.array_equal(yq.cpu().numpy(), want), (fold, variant)
+    assert pkg.lib().chxq_tc_variant(0) == 0
