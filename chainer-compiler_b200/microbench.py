@@ -1,0 +1,134 @@
+"""Per-operator measurements on one B200 for the workloads next to the headline benchmark: the quantized MLP, the fused
+LSTM-cell elementwise group, the MatMulInteger / QLinearMatMul sweep, MobileNetV2, QuantizeLinear / DequantizeLinear and
+single depthwise layers.  One JSON line per measurement on stdout.
+
+    python chainer-compiler_b200/microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise]
+
+Timing: CUDA events on the launching stream, 3 warm-up calls, median of 10 (3 for the largest GEMMs), a 256 MB buffer
+rewritten between calls so that nothing is served from L2.  `gbs` is algorithmic bytes (every input read once, every
+output written once) per second; `frac_hbm` divides it by the measured copy bandwidth of MEASURED_PEAKS.json when that file
+is next to bench.py (else by the 6.65 TB/s fallback)."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+
+def hbm_peak_gbs():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def main():
+    pkg = entry.load_package()
+    from chainer_compiler_b200 import fusion, models, ops
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench.py needs a CUDA device: this package has no CPU path")
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise"}
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    peak, peak_src = hbm_peak_gbs()
+
+    def timeit(fn, iters=10, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return float(np.median(ts))
+
+    def emit(name, ms, **kw):
+        line = {"bench": name, "ms": ms}
+        line.update(kw)
+        if "gbs" in kw:
+            line["frac_hbm"] = kw["gbs"] / peak
+            line["hbm_peak"] = "%s %.0f GB/s" % (peak_src, peak)
+        print(json.dumps(line), flush=True)
+
+    if "quant" in which:
+        n = 256 * 3 * 224 * 224
+        x = torch.rand(n, device=dev)
+        ms = timeit(lambda: ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0)))
+        emit("QuantizeLinear f32->u8, 38.5 M elements, round half up (reference)", ms, gbs=n * 5 / ms / 1e6)
+        ms = timeit(lambda: ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0), round_mode=1))
+        emit("QuantizeLinear f32->u8, 38.5 M elements, round half to even", ms, gbs=n * 5 / ms / 1e6)
+        q = ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0))
+        ms = timeit(lambda: ops.DequantizeLinear(q, 1 / 255.0, np.uint8(0)))
+        emit("DequantizeLinear u8->f32, 38.5 M elements", ms, gbs=n * 5 / ms / 1e6)
+
+    if "eltwise" in which:
+        nodes = fusion.lstm_cell_group()
+        g = fusion.fuse_elementwise(nodes, {}, ["c_next", "h"])[0]
+        code = fusion.build_program(nodes, 1, g.inputs, g.outputs)
+        ins = [torch.randn((4096, 4096), device=dev) for _ in g.inputs]
+        ms = timeit(lambda: ops.ElementWiseNvrtc(ins, 2, code, 1))
+        emit("ElementWiseNvrtc LSTM cell, 5 inputs + 2 outputs of fp32 [4096,4096]", ms, gbs=7 * 4096 * 4096 * 4 / ms / 1e6)
+
+    if "gemm" in which:
+        for S in (1024, 4096, 8192, 16384):
+            a = torch.randint(0, 256, (S, S), dtype=torch.uint8, device=dev)
+            b = torch.randint(-127, 128, (S, S), dtype=torch.int8, device=dev)
+            za = torch.tensor([128], dtype=torch.uint8, device=dev)
+            it = 3 if S >= 8192 else 10
+            ms = timeit(lambda: ops.MatMulInteger(a, b, za, None, path=2), iters=it)
+            emit("MatMulInteger u8[%d,%d] (zp 128) x s8[%d,%d] -> s32" % (S, S, S, S), ms, tops=2 * S ** 3 / ms / 1e9)
+            ms = timeit(lambda: ops.QLinearMatMul(a, 0.01, np.uint8(128), b, 0.001, np.int8(0), 1e-3 * S, np.uint8(0), path=2), iters=it)
+            emit("QLinearMatMul u8[%d,%d] (zp 128) x s8[%d,%d] -> u8" % (S, S, S, S), ms, tops=2 * S ** 3 / ms / 1e9)
+
+    if "mlp" in which:
+        net = models.QuantizedMLP(dev, seed=0)
+        x = torch.rand((64, 784), generator=torch.Generator().manual_seed(0)).to(dev)
+        ms = timeit(lambda: net.forward(x))
+        emit("quantized MLP 784-1000-1000-10, batch 64, five ops per call", ms, samples_per_s=64 / ms * 1e3)
+
+    if "mobilenet" in which:
+        B = 512
+        x = torch.rand((B, 3, 224, 224), generator=torch.Generator().manual_seed(1)).to(dev)
+        for tc in (True, False):
+            net = models.MobileNetV2Int8(B, dev, seed=0, depthwise_on_tensor_cores=tc)
+            net.calibrate(x)
+            graph, logits = net.capture(x, fold=True)
+            ms = timeit(graph.replay)
+            dense, dw = net.macs_per_image()
+            emit("MobileNetV2-1.0 int8, batch 512, depthwise on %s, folded requantization" % ("tensor cores" if tc else "CUDA cores"), ms,
+                 img_per_s=B / ms * 1e3, gmac_per_image=(dense + dw) / 1e9)
+            del net, graph, logits
+            torch.cuda.empty_cache()
+
+    if "depthwise" in which:
+        N = 512
+        for C, H, s in ((96, 112, 2), (144, 56, 1), (384, 14, 1), (960, 7, 1)):
+            x = torch.randint(0, 256, (N, C, H, H), dtype=torch.uint8, device=dev).contiguous(memory_format=torch.channels_last)
+            w = torch.randint(-127, 128, (C, 1, 3, 3), dtype=torch.int8, device=dev)
+            ws = torch.full((C,), 1e-3, device=dev)
+            wz = torch.zeros(C, dtype=torch.int8, device=dev)
+            y = ops.QLinearConv(x, 0.02, np.uint8(0), w, ws, wz, 0.05, np.uint8(0), None, (s, s), (1, 1), C)
+            nbytes = x.numel() + y.numel()
+            ms = timeit(lambda: ops.QLinearConv(x, 0.02, np.uint8(0), w, ws, wz, 0.05, np.uint8(0), None, (s, s), (1, 1), C))
+            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, CUDA-core kernel" % (C, H, H, s, N), ms, gbs=nbytes / ms / 1e6)
+            pk = ops.PackedConv(w, wz, x.shape, (s, s), (1, 1), group=C)
+            ms = timeit(lambda: ops.QLinearConvPacked(x, pk, 0.02, np.uint8(0), ws, wz, 0.05, np.uint8(0), fold_scales=True))
+            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, tensor cores (diagonal blocks)" % (C, H, H, s, N), ms,
+                 gbs=nbytes / ms / 1e6)
+    ops.device_status()
+    del pkg
+
+
+if __name__ == "__main__":
+    main()

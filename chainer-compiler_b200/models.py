@@ -324,8 +324,9 @@ class MobileNetV2Int8:
     requantization, linear bottleneck outputs get an asymmetric zero point, residual joins run in the projecting
     convolution's epilogue (DequantizeLinear x2, Add, QuantizeLinear; no Relu)."""
 
-    def __init__(self, batch, device, seed=0, image=224, num_classes=1000):
+    def __init__(self, batch, device, seed=0, image=224, num_classes=1000, depthwise_on_tensor_cores=True):
         self.batch, self.device, self.image = int(batch), torch.device(device), int(image)
+        self.depthwise_on_tensor_cores = bool(depthwise_on_tensor_cores)
         rng = np.random.default_rng(seed)
         self.stem = _QLayer("stem", 3, 32, 3, 2, 1, 1, rng, True)
         self.blocks = []
@@ -383,14 +384,16 @@ class MobileNetV2Int8:
         c.dev["w"] = torch.from_numpy(c.w_q).to(dev)
         c.dev["w_scale"] = torch.from_numpy(c.w_scale).to(dev)
         c.dev["w_zp"] = torch.from_numpy(c.w_zp).to(dev)
-        if c.group == 1:
-            c.packed = ops.PackedConv(c.dev["w"], c.dev["w_zp"], x_shape, strides=(c.stride, c.stride), pads=(c.pad, c.pad),
+        if c.group == 1 or self.depthwise_on_tensor_cores:
+            c.packed = ops.PackedConv(c.dev["w"], c.dev["w_zp"], x_shape, strides=(c.stride, c.stride), pads=(c.pad, c.pad), group=c.group,
                                       x_layout=_lib.NCHW if x_nchw else _lib.NHWC)
             if not c.packed.eligible:
-                raise _lib.ChxqError(_lib.ERR_UNSUPPORTED, "%s is not eligible for the tensor-core path" % c.name)
+                if c.group == 1:
+                    raise _lib.ChxqError(_lib.ERR_UNSUPPORTED, "%s is not eligible for the tensor-core path" % c.name)
+                c.packed = None
 
     def _acc(self, c, x):
-        if c.group == 1:
+        if c.packed is not None:
             g = c.packed.g
             y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.int32, device=self.device, memory_format=torch.channels_last)
             ws_bytes = lib().chxq_conv_packed_workspace(ctypes.byref(g), 0, c.packed.flags)
@@ -403,7 +406,7 @@ class MobileNetV2Int8:
     def _run(self, c, x, fold=False, residual=None, res_scale=1.0, res_zp=0, out_scale=1.0, out_zp=0):
         kw = dict(b=c.dev["bias"], clamp_hi_q=c.clamp, residual=residual, res_scale=res_scale, res_zero_point=res_zp, res_relu=False,
                   out_scale=out_scale, out_zero_point=out_zp, fold_scales=fold)
-        if c.group == 1:
+        if c.packed is not None:
             return ops.QLinearConvPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp), **kw)
         return ops.QLinearConv(x, c.x_scale, np.uint8(0), c.dev["w"], c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
                                strides=(c.stride, c.stride), pads=(c.pad, c.pad), group=c.group, **kw)
@@ -493,7 +496,7 @@ class MobileNetV2Int8:
         args = dict(b=c.dev["bias"], clamp_hi_q=c.clamp, fold_scales=fold, res_relu=False)
         args.update({"residual": kw.get("residual"), "res_scale": kw.get("res_scale", 1.0), "res_zero_point": kw.get("res_zp", 0),
                      "out_scale": kw.get("out_scale", 1.0), "out_zero_point": kw.get("out_zp", 0)})
-        if c.group == 1:
+        if c.packed is not None and (c.group == 1 or c.pad == 0):  # grouped layers with padding need a zero activation zero point there
             return ops.QLinearConvPacked(x, c.packed, c.x_scale, np.uint8(c.x_zp), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
                                          **args)
         return ops.QLinearConv(x, c.x_scale, np.uint8(c.x_zp), c.dev["w"], c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
@@ -524,6 +527,15 @@ class MobileNetV2Int8:
         if taps is not None:
             taps["pooled"] = pooled
         return ops.Linear(pooled, self.dev_fc_w, self.dev_fc_b)
+
+    def capture(self, x_static, fold=False):
+        """Captures forward(x_static) into a CUDA graph; returns (graph, logits)."""
+        self.forward(x_static, fold=fold)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            logits = self.forward(x_static, fold=fold)
+        return g, logits
 
     def export_numpy(self):
         def lay(c):
