@@ -283,8 +283,12 @@ def run_chxq(args):
         pk = peaks()
         achieved = 2.0 * macs.value / (tms.value / 1000.0) / 1e12
         peak = 2.0 * pk["bf16_sustained"]
-        roof = {"bound": "tensor", "kernel": "tc_igemm_kernel (tcgen05 kind::i8 implicit GEMM, all convolutions)", "achieved": achieved,
-                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+        # DRAM traffic of the 53 tensor-core launches of one step at batch 256, one ncu pass per launch
+        # (dram__bytes_read.sum + dram__bytes_write.sum = 4679.0 MB per step; summary in profiles/tc_igemm2_resnet50_b256.txt)
+        traffic = 4679.0e6 / 53 if args.batch == 256 and fold else None
+        roof = {"bound": "tensor", "kernel": "tc_igemm2_kernel (tcgen05 kind::i8 implicit GEMM, grouped tiles, all 53 convolutions)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
+                "traffic_note": "bytes per launch, average over the 53 launches of a step (ncu, batch 256)" if traffic else "not captured for this configuration",
                 "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s; the file has no int8 entry; int8 ops counted as 2 per MAC)" % pk["source"],
                 "launches_per_step": int(n.value // prof_steps), "kernel_ms_per_step": tms.value / prof_steps,
                 "share_of_step": (tms.value / prof_steps) / ms_per_step, "algorithmic_gop_per_step": 2.0 * macs.value / prof_steps / 1e9}
