@@ -56,7 +56,8 @@ bool g_prof_on = false;
 std::vector<ProfRec> g_prof;
 std::mutex g_prof_mu;
 
-int g_variant = 0;  // chxq_tc_variant: 0 = choose, 1 = one tile per step, 2 = grouped tiles where eligible
+int g_variant = 0;  // chxq_tc_variant: 0 = choose, 1 = one tile per step, 2 = grouped tiles where eligible, 3 = grouped + halo tiles
+bool g_halo_auto = false;  // whether variant 0 may pick the halo form
 
 int pick_bn(int cols, int64_t pos_tiles) {
     const int cand[3] = {256, 128, 64};
@@ -263,7 +264,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     int grid = total_tiles < num_sms() ? (int)total_tiles : num_sms();
 
     // Grouped-tile kernel (tc_kernel2.cuh): uint8 epilogues whose outputs (and residual) can move through TMA.
-    bool grouped = false;
+    bool grouped = false, halo = false;
     int bn2 = (q.cols > 64 && q.group_cols == 0) ? 128 : 64;
     alignas(64) CUtensorMap tmY, tmR;
     if ((epi_kind == tc::kEpiKU8 || epi_kind == tc::kEpiKU8Fold) && g_variant != 1 && p.vec_ok && q.ldc % 16 == 0 && (q.bk == 64 || q.bk == 128) &&
@@ -271,13 +272,33 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
         // folded tail: the saturating add clamps at zero, which is the Relu only when the output zero point is zero
         !(epi_kind == tc::kEpiKU8Fold && q.epi.residual != nullptr && q.epi.rq.res_relu && q.epi.rq.out_zp_f != 0.f)) {
         const int r = 256 / bn2;
-        const int64_t groups = (pos_tiles + r - 1) / r * ((q.cols + bn2 - 1) / bn2);
+        // Halo form: a KH x KW (<= 3 x 3) stride-1 convolution over the NHWC map with a 64-byte K tile; tiles are 8 x 16 positions
+        // of one image.
+        halo = (g_variant == 3 || (g_variant == 0 && g_halo_auto)) && q.KH * q.KW > 1 && q.KH <= 3 && q.KW <= 3 && p.sw == 1 && p.sh == 1 &&
+               q.bk == 64 && q.a_row_bytes == 0 && q.Wo >= 8 && q.Ho >= 8;
+        int64_t pos_tiles2 = pos_tiles;
+        if (halo) {
+            p.Wb = 8; p.Hb = 16; p.Nb = 1;
+            p.tiles_w = (q.Wo + 7) / 8; p.tiles_h = (q.Ho + 15) / 16; p.tiles_n = q.No;
+            pos_tiles2 = (int64_t)p.tiles_w * p.tiles_h * p.tiles_n;
+            if (pos_tiles2 * ((q.cols + bn2 - 1) / bn2) >= (1ll << 31)) return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: too many tiles");
+        }
+        const int64_t groups = (pos_tiles2 + r - 1) / r * ((q.cols + bn2 - 1) / bn2);
         // Chosen whenever there is at least one group per SM; smaller problems spread better as single tiles.
-        grouped = g_variant == 2 || groups >= (int64_t)num_sms();
+        grouped = halo || g_variant >= 2 || groups >= (int64_t)num_sms();
+        if (halo) {
+            const cuuint64_t dims[4] = {(cuuint64_t)q.C, (cuuint64_t)q.W, (cuuint64_t)q.H, (cuuint64_t)q.N};
+            const cuuint64_t strides[3] = {(cuuint64_t)q.a_cs, (cuuint64_t)q.a_cs * q.W, (cuuint64_t)q.a_cs * q.W * q.H};
+            const cuuint32_t box[4] = {16u, (cuuint32_t)(8 + q.KW - 1), (cuuint32_t)(16 + q.KH - 1), 1u};
+            const cuuint32_t estr[4] = {1, 1, 1, 1};
+            CUresult r0 = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r0 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A halo) failed with %d", (int)r0);
+        }
         if (grouped) {
             const cuuint64_t dims[4] = {(cuuint64_t)q.cols, (cuuint64_t)q.Wo, (cuuint64_t)q.Ho, (cuuint64_t)q.No};
             const cuuint64_t strides[3] = {(cuuint64_t)q.ldc, (cuuint64_t)q.ldc * q.Wo, (cuuint64_t)q.ldc * q.Wo * q.Ho};
-            const cuuint32_t box[4] = {(cuuint32_t)bn2, (cuuint32_t)q.Wb, (cuuint32_t)q.Hb, (cuuint32_t)q.Nb};
+            const cuuint32_t box[4] = {(cuuint32_t)bn2, (cuuint32_t)p.Wb, (cuuint32_t)p.Hb, (cuuint32_t)p.Nb};
             const cuuint32_t estr[4] = {1, 1, 1, 1};
             const CUtensorMapSwizzle sw = bn2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
             CUresult r1 = encode(&tmY, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, q.y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
@@ -310,8 +331,8 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     }
     int rc;
     if (grouped) {
-        rc = q.bk == 128 ? tc::launch_tc2_bk128(bn2, epi_kind, q.epi.residual != nullptr, tmA, tmB, tmY, tmR, p, grid, s)
-                         : tc::launch_tc2_bk64(bn2, epi_kind, q.epi.residual != nullptr, tmA, tmB, tmY, tmR, p, grid, s);
+        rc = q.bk == 128 ? tc::launch_tc2_bk128(bn2, epi_kind, q.epi.residual != nullptr, halo, tmA, tmB, tmY, tmR, p, grid, s)
+                         : tc::launch_tc2_bk64(bn2, epi_kind, q.epi.residual != nullptr, halo, tmA, tmB, tmY, tmR, p, grid, s);
     } else
     switch (q.bk) {
         case 128: rc = tc::launch_tc_bk128(bn, epi_kind, tmA, tmB, p, grid, s); break;
@@ -331,7 +352,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
 // Chooses between the two tensor-core kernels: 0 = by problem shape, 1 = always one tile per step, 2 = grouped tiles
 // whenever the problem is eligible.  Results are identical; the switch exists for measurements and tests.
 extern "C" int chxq_tc_variant(int32_t variant) {
-    if (variant < 0 || variant > 2) return chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, "chxq_tc_variant: variant must be 0, 1 or 2");
+    if (variant < 0 || variant > 3) return chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, "chxq_tc_variant: variant must be 0, 1, 2 or 3");
     chxq::g_variant = variant;
     return CHXQ_OK;
 }

@@ -67,27 +67,33 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
-// Bounded wait.  Returns false when the CTA is aborting (either this wait expired or another did).  A waiting warp sleeps
-// between polls (doubling from sleep_ns up to 8 * sleep_ns): polling at full speed takes issue slots from the warps that
-// do the work.  The abort flag and the clock are looked at every 128 polls.
+// Bounded wait.  Returns false when the CTA is aborting (either this wait expired or another did).
+// sleep_ns == 0: a tight poll loop (try_wait itself blocks in hardware for a short while, so the loop issues a few
+// instructions per ~100 ns) -- for the single-lane producer / MMA / store roles, whose wake-up latency is on the
+// critical path of load-bound layers.  sleep_ns > 0: sleep between polls, doubling up to 8 * sleep_ns -- for the sixteen
+// epilogue warps, whose polling would otherwise take issue slots from the warps that do the work.
+// The abort flag and the clock are looked at every 256 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, uint32_t sleep_ns = 64) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
-    uint32_t polls = 0, ns = sleep_ns;
+    uint32_t ns = sleep_ns;
     const uint32_t ns_max = sleep_ns * 8u;
     while (true) {
-        __nanosleep(ns);
-        if (mbar_try_wait(bar, parity)) return true;
-        if (ns < ns_max) ns <<= 1;
-        if ((++polls & 127u) == 0u) {
-            if (*abort_flag) return false;
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            if (now - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i) {
+            if (sleep_ns != 0) {
+                __nanosleep(ns);
+                if (ns < ns_max) ns <<= 1;
             }
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (*abort_flag) return false;
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, code);
+            return false;
         }
     }
 }
@@ -276,7 +282,7 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 16)) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 0)) {
                         ok = false;
                         break;
                     }
@@ -300,11 +306,11 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2, 32)) break;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2, 0)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 16)) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 0)) {
                         ok = false;
                         break;
                     }

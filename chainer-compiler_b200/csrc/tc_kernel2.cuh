@@ -89,12 +89,23 @@ __device__ __forceinline__ float add_sat(float a, float b) {
     return d;
 }
 
-template <int BN, int BK, bool RES>
+// HALO: the A operand of a KH x KW (<= 3 x 3), stride-1 convolution is staged once per tile and channel chunk as the halo
+// tile of an 8 x 16 block of output positions of one image -- (16 + KH - 1) x (8 + KW - 1) pixels -- instead of once per
+// tap: each tap is a shifted view of the same bytes.  The halo tile is stored WITHOUT swizzle as BK / 16 planes of
+// [pixel][16 bytes]: in the canonical K-major layout a core matrix is 8 rows of 16 bytes, 16 bytes apart, so eight
+// consecutive pixels of an image row are one core matrix wherever the view starts; the stride between 8-row groups (SBO)
+// is one halo row, the stride between the two K halves of an MMA (LBO) is one plane.  Weight stages keep their own ring.
+constexpr int kHaloPlane = 3072;   // bytes reserved per plane: 18 x 10 pixels x 16 bytes = 2880, rounded up to 128
+constexpr int kHaloWb = 8, kHaloHb = 16;
+
+template <int BN, int BK, bool RES, bool HALO = false>
 struct Tc2Config {
     static constexpr int kR = 256 / BN;                  // position tiles per group
-    static constexpr int kStageA = kR * 128 * BK;
+    static constexpr int kTileA = HALO ? (BK / 16) * kHaloPlane : 128 * BK;
+    static constexpr int kStageA = kR * kTileA;
+    static constexpr int kAStages = 2;                   // HALO only: ring of halo-tile stages
     static constexpr int kStageB = BN * BK;
-    static constexpr int kStageBytes = kStageA + kStageB;
+    static constexpr int kStageBytes = HALO ? kStageB : kStageA + kStageB;  // bytes of one stage of the main ring
     static constexpr int kTileOut = 128 * BN;            // one staged output (or residual) tile
     // Staging buffers of kR tiles each.  Without a residual: two, filled by the epilogue and drained by the TMA store.
     // With one: three, each filled by the residual's TMA load, overwritten in place by the epilogue (a thread reads and
@@ -102,13 +113,14 @@ struct Tc2Config {
     // epilogue of group i while the store of group i - 1 is still reading its buffer.
     static constexpr int kBufs = RES ? 3 : 2;
     static constexpr int kOutBytes = kBufs * kR * kTileOut;
-    static constexpr int kFixed = kOutBytes;
+    static constexpr int kFixed = kOutBytes + (HALO ? kAStages * kStageA : 0);
     static constexpr int kBudget = 222 * 1024;
     static constexpr int kStagesRaw = (kBudget - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kTmemCols = 512;
-    // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], res_full[3], buf_empty[3], buf_full[3]
-    static constexpr int kBarBytes = (2 * kStages + 13) * 8;
+    // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], res_full[3], buf_empty[3], buf_full[3],
+    // halo_full[2], halo_empty[2]
+    static constexpr int kBarBytes = (2 * kStages + 17) * 8;
     static constexpr int kBarOffset = kStages * kStageBytes + kFixed;
     static constexpr int kParamOffset = ((kBarOffset + kBarBytes + 16 + 15) / 16) * 16;
     static constexpr int kParamBytes = 16 * (BN / 2) * 4;  // 16 warps x (BN/4 multipliers + BN/4 additive terms)
@@ -123,21 +135,26 @@ __device__ __forceinline__ uint32_t staged_offset(int row, int unit) {
     return (uint32_t)(row * 64 + ((unit ^ ((row >> 1) & 3)) << 4));
 }
 
-template <int BN, int BK, int EPI, bool RES>
+// K-major descriptor of a shifted view into a halo tile (no swizzle): LBO = one plane, SBO = one halo row.
+__device__ __forceinline__ uint64_t make_halo_desc(uint32_t smem_addr, uint32_t row_bytes) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(kHaloPlane >> 4) << 16) | ((uint64_t)(row_bytes >> 4) << 32) | (1ull << 46);
+}
+
+template <int BN, int BK, int EPI, bool RES, bool HALO>
 __global__ void __launch_bounds__(608, 1)
 tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const TcParams p) {
-    using Cfg = Tc2Config<BN, BK, RES>;
+    using Cfg = Tc2Config<BN, BK, RES, HALO>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kR = Cfg::kR;
     constexpr bool kFold = EPI == kEpiKU8Fold;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // stays a shared-memory pointer
     uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem + kStages * Cfg::kStageA;
-    uint8_t* smem_out = smem + kStages * Cfg::kStageBytes;  // [kBufs][kR][128][BN], 1024-byte aligned (all sizes are multiples of 1024)
+    uint8_t* smem_b = smem + (HALO ? Cfg::kAStages : kStages) * Cfg::kStageA;
+    uint8_t* smem_out = smem_b + kStages * Cfg::kStageB;  // [kBufs][kR][128][BN], 1024-byte aligned (all sizes are multiples of 1024)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOffset);
-    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 13);
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 17);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
     const uint32_t bar_base = smem_u32(bars);
@@ -150,6 +167,8 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // full = all sixteen epilogue warps have staged their part of it
     auto bempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 7 + b); };
     auto bfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 10 + b); };
+    auto hfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 13 + a); };
+    auto hempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 15 + a); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -162,6 +181,10 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
             mbar_init(tempty_bar(a), 16);  // one arrival per epilogue warp
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(hfull_bar(a), 1);
+            mbar_init(hempty_bar(a), 1);
         }
         for (int b = 0; b < 3; ++b) {
             mbar_init(rfull_bar(b), 1);
@@ -200,8 +223,8 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, hstage = 0;
+            uint32_t phase = 0, hphase = 0;
             bool ok = true;
             int it = 0;
             for (int grp = blockIdx.x; grp < total_groups && ok; grp += gridDim.x, ++it) {
@@ -213,16 +236,49 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int gbase = p.group_cols > 0 ? (ct * BN / p.group_cols) * p.group_cin : 0;
                 if (RES) {
                     const int rb = it % 3;
-                    if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5, 128)) break;
+                    if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5, 0)) break;
                     mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
 #pragma unroll
                     for (int t = 0; t < kR; ++t)
                         tma_load_4d(smem_u32(smem_out + (rb * kR + t) * Cfg::kTileOut), &tmR, rfull_bar(rb), ct * BN, w0[t], h0[t], n0[t]);
                 }
+                if (HALO) {
+                    // one halo tile per position tile and channel chunk, then one weight stage per tap
+                    const uint32_t halo_bytes = (uint32_t)((kHaloWb + p.KW - 1) * (kHaloHb + p.KH - 1) * 16);
+                    for (int cc = 0; cc < p.c_chunks && ok; ++cc) {
+                        if (!mbar_wait(hempty_bar(hstage), hphase ^ 1u, abort_flag, p.status, 9, 0)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_expect_tx(hfull_bar(hstage), (uint32_t)(kR * (BK / 16)) * halo_bytes);
+#pragma unroll
+                        for (int t = 0; t < kR; ++t)
+#pragma unroll
+                            for (int j = 0; j < BK / 16; ++j)
+                                tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA + j * kHaloPlane), &tmA, hfull_bar(hstage),
+                                            gbase + cc * BK + j * 16, w0[t] - p.pad_left, h0[t] - p.pad_top, n0[t]);
+                        if (++hstage == Cfg::kAStages) {
+                            hstage = 0;
+                            hphase ^= 1u;
+                        }
+                        for (int tap = 0; tap < taps; ++tap) {
+                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 0)) {
+                                ok = false;
+                                break;
+                            }
+                            mbar_expect_tx(full_bar(stage), Cfg::kStageB);
+                            tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), tap * p.c_pad + cc * BK, ct * BN);
+                            if (++stage == kStages) {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                    }
+                } else
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 16)) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 0)) {
                         ok = false;
                         break;
                     }
@@ -242,18 +298,58 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, hstage = 0;
+            uint32_t phase = 0, hphase = 0;
             int it = 0;
             bool ok = true;
             for (int grp = blockIdx.x; grp < total_groups && ok; grp += gridDim.x, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2, 32)) break;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2, 0)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * 256);
+                if (HALO) {
+                    const int halo_w = kHaloWb + p.KW - 1;
+                    for (int cc = 0; cc < p.c_chunks && ok; ++cc) {
+                        if (!mbar_wait(hfull_bar(hstage), hphase, abort_flag, p.status, 10, 0)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t a_addr = smem_u32(smem_a + hstage * Cfg::kStageA);
+                        for (int tap = 0; tap < taps; ++tap) {
+                            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+                            if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 0)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+                            const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kStageB);
+                            const uint32_t shift = (uint32_t)((kh * halo_w + kw) * 16);
+#pragma unroll
+                            for (int k = 0; k < BK / 32; ++k) {
+                                const uint64_t db = make_kmajor_desc<BK>(b_addr + k * 32);
+#pragma unroll
+                                for (int t = 0; t < kR; ++t)
+                                    umma_i8(tmem_d + (uint32_t)(t * BN),
+                                            make_halo_desc(a_addr + t * Cfg::kTileA + 2 * k * kHaloPlane + shift, (uint32_t)(halo_w * 16)), db, p.idesc,
+                                            (cc > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                            }
+                            umma_commit(empty_bar(stage));
+                            if (++stage == kStages) {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                        if (ok) umma_commit(hempty_bar(hstage));  // the halo tiles are free once the MMAs of all taps have read them
+                        if (++hstage == Cfg::kAStages) {
+                            hstage = 0;
+                            hphase ^= 1u;
+                        }
+                    }
+                } else
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 16)) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 0)) {
                         ok = false;
                         break;
                     }
@@ -451,7 +547,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int ct = grp % p.col_tiles;
                 const int pg = grp / p.col_tiles;
                 const int buf = it % Cfg::kBufs;
-                if (!mbar_wait(bfull_bar(buf), (uint32_t)(it / Cfg::kBufs) & 1u, abort_flag, p.status, 8, 128)) break;
+                if (!mbar_wait(bfull_bar(buf), (uint32_t)(it / Cfg::kBufs) & 1u, abort_flag, p.status, 8, 0)) break;
                 uint8_t* out_buf = smem_out + buf * (kR * Cfg::kTileOut);
 #pragma unroll
                 for (int t = 0; t < kR; ++t) {
@@ -484,35 +580,49 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
-template <int BN, int BK, int EPI, bool RES>
+template <int BN, int BK, int EPI, bool RES, bool HALO>
 int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p, int grid,
                 cudaStream_t s) {
-    using Cfg = Tc2Config<BN, BK, RES>;
+    using Cfg = Tc2Config<BN, BK, RES, HALO>;
     static_assert(Cfg::kUsable, "grouped kernel: not enough shared memory for two stages");
     static bool attr_set[64] = {};
     int dev = 0;
     CHXQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES, HALO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    tc_igemm2_kernel<BN, BK, EPI, RES><<<grid, 608, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
+    tc_igemm2_kernel<BN, BK, EPI, RES, HALO><<<grid, 608, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }
 
-// Launches the grouped kernel for (bn, BK, epi, residual); CHXQ_ERR_UNSUPPORTED when the combination has no instantiation.
+// Launches the grouped kernel for (bn, BK, epi, residual, halo); CHXQ_ERR_UNSUPPORTED when the combination has no
+// instantiation.  The halo form exists for the 64-byte K tile only.
 template <int BK>
-int launch_bk2(int bn, int epi, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
-               const TcParams& p, int grid, cudaStream_t s) {
+int launch_bk2(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
+               const CUtensorMap& tmR, const TcParams& p, int grid, cudaStream_t s) {
     const int key = (bn == 128 ? 4 : 0) + (epi == kEpiKU8Fold ? 2 : 0) + (res ? 1 : 0);
+    if (halo) {
+        if constexpr (BK == 64) {
+            switch (key) {
+                case 0: return launch_one2<64, BK, kEpiKU8, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
+                case 2: return launch_one2<64, BK, kEpiKU8Fold, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
+                case 4: return launch_one2<128, BK, kEpiKU8, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
+                case 5: return launch_one2<128, BK, kEpiKU8, true, true>(tmA, tmB, tmY, tmR, p, grid, s);
+                case 6: return launch_one2<128, BK, kEpiKU8Fold, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
+                case 7: return launch_one2<128, BK, kEpiKU8Fold, true, true>(tmA, tmB, tmY, tmR, p, grid, s);
+            }
+        }
+        return CHXQ_ERR_UNSUPPORTED;
+    }
     switch (key) {
-        case 0: return launch_one2<64, BK, kEpiKU8, false>(tmA, tmB, tmY, tmR, p, grid, s);
-        case 2: return launch_one2<64, BK, kEpiKU8Fold, false>(tmA, tmB, tmY, tmR, p, grid, s);
-        case 4: return launch_one2<128, BK, kEpiKU8, false>(tmA, tmB, tmY, tmR, p, grid, s);
-        case 5: return launch_one2<128, BK, kEpiKU8, true>(tmA, tmB, tmY, tmR, p, grid, s);
-        case 6: return launch_one2<128, BK, kEpiKU8Fold, false>(tmA, tmB, tmY, tmR, p, grid, s);
-        case 7: return launch_one2<128, BK, kEpiKU8Fold, true>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 0: return launch_one2<64, BK, kEpiKU8, false, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 2: return launch_one2<64, BK, kEpiKU8Fold, false, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 4: return launch_one2<128, BK, kEpiKU8, false, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 5: return launch_one2<128, BK, kEpiKU8, true, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 6: return launch_one2<128, BK, kEpiKU8Fold, false, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 7: return launch_one2<128, BK, kEpiKU8Fold, true, false>(tmA, tmB, tmY, tmR, p, grid, s);
     }
     return CHXQ_ERR_UNSUPPORTED;
 }

@@ -43,9 +43,9 @@ int launch_tc_bk32(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& t
 int launch_tc_bk64(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s);
 int launch_tc_bk128(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s);
 // Grouped-tile kernel (tc_kernel2.cuh); bn is 64 or 128, epi is kEpiKU8 or kEpiKU8Fold.
-int launch_tc2_bk64(int bn, int epi, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
+int launch_tc2_bk64(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
                     const TcParams& p, int grid, cudaStream_t s);
-int launch_tc2_bk128(int bn, int epi, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
+int launch_tc2_bk128(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
                      const TcParams& p, int grid, cudaStream_t s);
 
 }  // namespace tc

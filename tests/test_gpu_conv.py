@@ -335,6 +335,9 @@ GROUPED_CASES = [
     (1, 64, 10, 10, 64, 5, 1, 2),    # 5x5
     (4, 64, 16, 16, 128, 1, 2, 0),   # stride 2: TMA box with element strides
     (2, 144, 6, 6, 32, 1, 1, 0),     # ragged last K chunk, 32 output channels
+    (3, 64, 20, 13, 64, 3, 1, 1),    # halo tiles: ragged in both directions (13 = 8 + 5 columns, 20 = 16 + 4 rows)
+    (2, 128, 16, 16, 192, 3, 1, 1),  # halo tiles, two channel chunks of 64, 128-channel blocks with a ragged last block
+    (2, 64, 9, 12, 64, 2, 1, 0),     # halo tiles, 2 x 2 window without padding
 ]
 
 
@@ -372,9 +375,10 @@ def test_grouped_tensor_core_kernel(pkg, ops, orc, dev, grouped_kernel, N, C, H,
                                    fold_scales=True)),
     ]
     for c in cases:
-        got = run(2, c["zx"], c["zy"], **c["kw"])
         ref = run(1, c["zx"], c["zy"], **c["kw"])
-        assert torch.equal(got, ref), c
+        for variant in (2, 3):  # 3: halo tiles where the geometry allows them (3x3 and smaller, stride 1, 64-byte K tile)
+            got = run(variant, c["zx"], c["zy"], **c["kw"])
+            assert torch.equal(got, ref), (variant, c)
     acc = orc.conv_integer(x, w, 0, wz, (stride, stride), (pad, pad))
     want = orc.requantize(acc, sx, ws, sy, 131, bias=bias, channel_axis=1, fold=True)
     assert np.array_equal(run(2, 0, 131, fold_scales=True).cpu().numpy(), want)
@@ -437,7 +441,7 @@ def test_grouped_conv_tensor_core_packed(pkg, ops, orc, dev, N, C, H, W, M, grou
     wz0 = np.zeros(M, np.int8)
     acc = orc.conv_integer(x, w, 0, wz0, (stride, stride), (pad, pad), group)
     for fold in (False, True):
-        for variant in (1, 2):
+        for variant in (1, 2, 3):
             assert pkg.lib().chxq_tc_variant(variant) == 0
             yq = ops.QLinearConvPacked(xt, pk, 0.02, np.uint8(0), _t(ws_, dev), _t(wz0, dev), 0.05, np.uint8(20), b=_t(bias, dev), fold_scales=fold,
                                        clamp_hi_q=200)
