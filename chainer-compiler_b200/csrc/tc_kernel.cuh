@@ -198,6 +198,34 @@ __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | (sbo << 32) | (1ull << 46) | (layout << 61);
 }
 
+// The same descriptor as two 32-bit halves.  The MMA warp issues from one thread, whose instructions are dependent and
+// several cycles apart: rebuilding a 64-bit descriptor per instruction (shifts, masks, ors) costs more cycles than a
+// 128 x 64 x 32 MMA takes.  The high word is a constant of the layout; the low word is (address >> 4) plus constant bits,
+// so stepping along K or to the next tile of a stage is one 32-bit add of a compile-time constant (shared memory is
+// smaller than 256 KB, so the 14-bit address field never carries).
+template <int BK>
+__device__ __forceinline__ uint32_t kmajor_desc_hi() {
+    constexpr uint32_t layout = BK == 128 ? 2u : (BK == 64 ? 4u : 6u);
+    return (uint32_t)((8 * BK) >> 4) | (1u << 14) | (layout << 29);
+}
+__device__ __forceinline__ uint32_t kmajor_desc_lo(uint32_t smem_addr) {
+    return (smem_addr >> 4) | (1u << 16);
+}
+
+__device__ __forceinline__ void umma_i8_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            ".reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %2};\n\t"
+            "mov.b64 db, {%3, %4};\n\t"
+            "setp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t"
+            "}\n" ::"r"(tmem_d),
+            "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+            : "memory");
+}
 
 template <int BN, int BK>
 struct TcConfig {
@@ -303,6 +331,8 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t phase = 0;
             int it = 0;
             bool ok = true;
+            const uint32_t desc_hi = kmajor_desc_hi<BK>();
+            const uint32_t a_lo0 = kmajor_desc_lo(smem_u32(smem_a)), b_lo0 = kmajor_desc_lo(smem_u32(smem_b));
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -315,13 +345,11 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kStageA);
-                    const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kStageB);
+                    const uint32_t a_lo = a_lo0 + (uint32_t)(stage * (Cfg::kStageA >> 4));
+                    const uint32_t b_lo = b_lo0 + (uint32_t)(stage * (Cfg::kStageB >> 4));
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k) {
-                        umma_i8(tmem_d, make_kmajor_desc<BK>(a_addr + k * 32), make_kmajor_desc<BK>(b_addr + k * 32), p.idesc,
-                                (kb > 0 || k > 0) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < BK / 32; ++k)
+                        umma_i8_lohi(tmem_d, a_lo + k * 2, desc_hi, b_lo + k * 2, desc_hi, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
                     if (++stage == kStages) {
                         stage = 0;

@@ -302,6 +302,12 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t phase = 0, hphase = 0;
             int it = 0;
             bool ok = true;
+            // descriptor halves (see kmajor_desc_hi): stepping is one 32-bit add of a compile-time constant
+            const uint32_t desc_hi = kmajor_desc_hi<BK>();
+            const uint32_t a_lo0 = kmajor_desc_lo(smem_u32(smem_a)), b_lo0 = kmajor_desc_lo(smem_u32(smem_b));
+            const int halo_w = kHaloWb + p.KW - 1;
+            const uint32_t halo_hi = (uint32_t)halo_w | (1u << 14);                                          // SBO = one halo row, no swizzle
+            const uint32_t halo_lo0 = (smem_u32(smem_a) >> 4) | ((uint32_t)(kHaloPlane >> 4) << 16);      // LBO = one plane
             for (int grp = blockIdx.x; grp < total_groups && ok; grp += gridDim.x, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -309,14 +315,13 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * 256);
                 if (HALO) {
-                    const int halo_w = kHaloWb + p.KW - 1;
                     for (int cc = 0; cc < p.c_chunks && ok; ++cc) {
                         if (!mbar_wait(hfull_bar(hstage), hphase, abort_flag, p.status, 10, 0)) {
                             ok = false;
                             break;
                         }
                         tc_fence_after();
-                        const uint32_t a_addr = smem_u32(smem_a + hstage * Cfg::kStageA);
+                        const uint32_t ha_lo = halo_lo0 + (uint32_t)(hstage * (Cfg::kStageA >> 4));
                         for (int tap = 0; tap < taps; ++tap) {
                             const int kh = tap / p.KW, kw = tap - kh * p.KW;
                             if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 0)) {
@@ -324,17 +329,15 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 break;
                             }
                             tc_fence_after();
-                            const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kStageB);
-                            const uint32_t shift = (uint32_t)((kh * halo_w + kw) * 16);
+                            const uint32_t b_lo = b_lo0 + (uint32_t)(stage * (Cfg::kStageB >> 4));
+                            const uint32_t a_lo = ha_lo + (uint32_t)(kh * halo_w + kw);  // the tap's view starts (kh, kw) pixels of 16 bytes in
+                            const uint32_t accum = (cc > 0 || tap > 0) ? 1u : 0u;
 #pragma unroll
-                            for (int k = 0; k < BK / 32; ++k) {
-                                const uint64_t db = make_kmajor_desc<BK>(b_addr + k * 32);
+                            for (int k = 0; k < BK / 32; ++k)
 #pragma unroll
                                 for (int t = 0; t < kR; ++t)
-                                    umma_i8(tmem_d + (uint32_t)(t * BN),
-                                            make_halo_desc(a_addr + t * Cfg::kTileA + 2 * k * kHaloPlane + shift, (uint32_t)(halo_w * 16)), db, p.idesc,
-                                            (cc > 0 || tap > 0 || k > 0) ? 1u : 0u);
-                            }
+                                    umma_i8_lohi(tmem_d + (uint32_t)(t * BN), a_lo + (uint32_t)((t * Cfg::kTileA + 2 * k * kHaloPlane) >> 4), halo_hi,
+                                                 b_lo + k * 2, desc_hi, p.idesc, k > 0 ? 1u : accum);
                             umma_commit(empty_bar(stage));
                             if (++stage == kStages) {
                                 stage = 0;
@@ -354,16 +357,15 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kStageA);
-                    const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kStageB);
+                    const uint32_t a_lo = a_lo0 + (uint32_t)(stage * (Cfg::kStageA >> 4));
+                    const uint32_t b_lo = b_lo0 + (uint32_t)(stage * (Cfg::kStageB >> 4));
+                    const uint32_t accum = kb > 0 ? 1u : 0u;
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k) {
-                        const uint64_t db = make_kmajor_desc<BK>(b_addr + k * 32);
+                    for (int k = 0; k < BK / 32; ++k)
 #pragma unroll
                         for (int t = 0; t < kR; ++t)
-                            umma_i8(tmem_d + (uint32_t)(t * BN), make_kmajor_desc<BK>(a_addr + t * 128 * BK + k * 32), db, p.idesc,
-                                    (kb > 0 || k > 0) ? 1u : 0u);
-                    }
+                            umma_i8_lohi(tmem_d + (uint32_t)(t * BN), a_lo + (uint32_t)((t * 128 * BK + k * 32) >> 4), desc_hi, b_lo + k * 2, desc_hi,
+                                         p.idesc, k > 0 ? 1u : accum);
                     umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
                     if (++stage == kStages) {
                         stage = 0;
