@@ -275,7 +275,7 @@ extern "C" int chxq_quantize_linear(
     int64_t done = 0;
     if (aligned16(x) && (reinterpret_cast<uintptr_t>(y) & 3u) == 0 && n >= 4) {
         const int64_t n4 = n / 4;
-        const int grid = grid_for((n4 + 3) / 4, 8);
+        const int grid = grid_for((n4 + 3) / 4, 32);
         const QDiv dv = make_qdiv(y_scale);
         const float4* x4 = reinterpret_cast<const float4*>(x);
         uint32_t* y32 = reinterpret_cast<uint32_t*>(y);
@@ -312,7 +312,7 @@ extern "C" int chxq_dequantize_linear(
     int64_t done = 0;
     if ((reinterpret_cast<uintptr_t>(x) & 3u) == 0 && aligned16(y) && n >= 4) {
         const int64_t n4 = n / 4;
-        const int grid = grid_for((n4 + 3) / 4, 8);
+        const int grid = grid_for((n4 + 3) / 4, 1 << 20);
         if (sgn)
             dequantize_vec16_kernel<true><<<grid, kThreads, 0, s>>>(reinterpret_cast<const uint32_t*>(x), n4, x_scale, zp_f, has_zp,
                                                                     reinterpret_cast<float4*>(y));

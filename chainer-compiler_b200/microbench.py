@@ -62,15 +62,17 @@ def main():
         print(json.dumps(line), flush=True)
 
     if "quant" in which:
-        n = 256 * 3 * 224 * 224
-        x = torch.rand(n, device=dev)
-        ms = timeit(lambda: ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0)))
-        emit("QuantizeLinear f32->u8, 38.5 M elements, round half up (reference)", ms, gbs=n * 5 / ms / 1e6)
-        ms = timeit(lambda: ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0), round_mode=1))
-        emit("QuantizeLinear f32->u8, 38.5 M elements, round half to even", ms, gbs=n * 5 / ms / 1e6)
-        q = ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0))
-        ms = timeit(lambda: ops.DequantizeLinear(q, 1 / 255.0, np.uint8(0)))
-        emit("DequantizeLinear u8->f32, 38.5 M elements", ms, gbs=n * 5 / ms / 1e6)
+        # the ResNet-50 input batch (a 40 us kernel: launch ramp and tail are ~10 % of it) and a 1.3 GB stream
+        for n, label in ((256 * 3 * 224 * 224, "38.5 M"), (1 << 28, "268 M")):
+            x = torch.rand(n, device=dev)
+            ms = timeit(lambda: ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0)))
+            emit("QuantizeLinear f32->u8, %s elements, round half up (reference)" % label, ms, gbs=n * 5 / ms / 1e6)
+            ms = timeit(lambda: ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0), round_mode=1))
+            emit("QuantizeLinear f32->u8, %s elements, round half to even" % label, ms, gbs=n * 5 / ms / 1e6)
+            q = ops.QuantizeLinear(x, 1 / 255.0, np.uint8(0))
+            ms = timeit(lambda: ops.DequantizeLinear(q, 1 / 255.0, np.uint8(0)))
+            emit("DequantizeLinear u8->f32, %s elements" % label, ms, gbs=n * 5 / ms / 1e6)
+            del x, q
 
     if "eltwise" in which:
         nodes = fusion.lstm_cell_group()
