@@ -405,7 +405,7 @@ extern "C" int chxq_eltwise_run(
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t work = aligned ? (n + vec - 1) / vec : n;
     int64_t blocks = (work + 255) / 256;
-    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+    if (blocks > (int64_t)sms * 32) blocks = (int64_t)sms * 32;
     if (blocks < 1) blocks = 1;
     CUresult cr = driver().LaunchKernel(aligned ? fn.vec : fn.scalar, (unsigned)blocks, 1, 1, 256, 1, 1, 0, reinterpret_cast<CUstream>(stream),
                                         args.data(), nullptr);

@@ -73,6 +73,15 @@ __device__ __forceinline__ uint32_t quantize_u8_up_bits(float t, float zp_f) {
     return __float_as_uint(__fadd_rd(fminf(fmaxf(t, 0.f), 255.5f), 8388608.f)) & 0xffu;
 }
 
+// uint8, round-half-to-even on a pre-divided value, conversion-free: saturate(rint(t) + zp).  (t + 1.5 * 2^23) - 1.5 * 2^23
+// is rint(t) for |t| <= 2^22; beyond +-4e6 the result saturates whatever the zero point, so t is clamped there first.
+__device__ __forceinline__ uint32_t quantize_u8_rne_bits(float t, float zp_f) {
+    const float tc = fminf(fmaxf(t, -4.0e6f), 4.0e6f);
+    const float r = __fsub_rn(__fadd_rn(tc, 12582912.f), 12582912.f);
+    const float u = __fadd_rn(r, zp_f);
+    return __float_as_uint(__fadd_rn(fminf(fmaxf(u, 0.f), 255.f), 8388608.f)) & 0xffu;
+}
+
 // One element of quantize_array (runtime/ops/quantize.cc:29-34): t = x / s; (+zp); min(hi);
 // max(lo); + 0.5f; truncate.  ROUND_RNE instead gives saturate(rint(x / s) + zp).
 template <bool kSigned>

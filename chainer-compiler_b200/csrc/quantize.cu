@@ -50,7 +50,7 @@ constexpr int kThreads = 256;
 // 16 elements per thread per step as four 128-bit loads and four 32-bit stores; lane i of a warp touches the i-th
 // 16 bytes (load) / 4 bytes (store) of a contiguous span, so every memory instruction is fully coalesced.
 // kMode: 0 = uint8 round-half-up through the constant-divisor division and add-based rounding (no conversion or
-// reciprocal instruction per element); 1 = general (int8 outputs, round-half-to-even, unusual scales).
+// reciprocal instruction per element); 2 = the same for round-half-to-even; 1 = general (int8 outputs, unusual scales).
 template <bool kSigned, int kMode>
 __global__ void __launch_bounds__(kThreads) quantize_vec16_kernel(
         const float4* __restrict__ x, int64_t n4, float scale, QDiv dv, float zp_f, int has_zp, int round_mode, uint32_t* __restrict__ y) {
@@ -66,17 +66,22 @@ __global__ void __launch_bounds__(kThreads) quantize_vec16_kernel(
         for (int j = 0; j < 4; ++j) {
             const int64_t g = base + (int64_t)j * blockDim.x;
             uint32_t q0, q1, q2, q3;
-            if (kMode == 0) {
+            if (kMode == 0 || kMode == 2) {
                 bool general = false;  // one magnitude test for the four quotients; the rare group that fails is redone
-                q0 = quantize_u8_up_bits(qdiv_unguarded(v[j].x, dv, &general), zp_f);
-                q1 = quantize_u8_up_bits(qdiv_unguarded(v[j].y, dv, &general), zp_f);
-                q2 = quantize_u8_up_bits(qdiv_unguarded(v[j].z, dv, &general), zp_f);
-                q3 = quantize_u8_up_bits(qdiv_unguarded(v[j].w, dv, &general), zp_f);
+                const float t0 = qdiv_unguarded(v[j].x, dv, &general), t1 = qdiv_unguarded(v[j].y, dv, &general);
+                const float t2 = qdiv_unguarded(v[j].z, dv, &general), t3 = qdiv_unguarded(v[j].w, dv, &general);
+                if (kMode == 0) {
+                    q0 = quantize_u8_up_bits(t0, zp_f); q1 = quantize_u8_up_bits(t1, zp_f);
+                    q2 = quantize_u8_up_bits(t2, zp_f); q3 = quantize_u8_up_bits(t3, zp_f);
+                } else {
+                    q0 = quantize_u8_rne_bits(t0, zp_f); q1 = quantize_u8_rne_bits(t1, zp_f);
+                    q2 = quantize_u8_rne_bits(t2, zp_f); q3 = quantize_u8_rne_bits(t3, zp_f);
+                }
                 if (general) {
-                    q0 = (uint32_t)quantize_one<false>(v[j].x, scale, zp_f, has_zp != 0, 0);
-                    q1 = (uint32_t)quantize_one<false>(v[j].y, scale, zp_f, has_zp != 0, 0);
-                    q2 = (uint32_t)quantize_one<false>(v[j].z, scale, zp_f, has_zp != 0, 0);
-                    q3 = (uint32_t)quantize_one<false>(v[j].w, scale, zp_f, has_zp != 0, 0);
+                    q0 = (uint32_t)quantize_one<false>(v[j].x, scale, zp_f, has_zp != 0, round_mode);
+                    q1 = (uint32_t)quantize_one<false>(v[j].y, scale, zp_f, has_zp != 0, round_mode);
+                    q2 = (uint32_t)quantize_one<false>(v[j].z, scale, zp_f, has_zp != 0, round_mode);
+                    q3 = (uint32_t)quantize_one<false>(v[j].w, scale, zp_f, has_zp != 0, round_mode);
                 }
             } else {
                 q0 = (uint32_t)quantize_one<kSigned>(v[j].x, scale, zp_f, has_zp != 0, round_mode) & 0xffu;
@@ -283,6 +288,8 @@ extern "C" int chxq_quantize_linear(
             quantize_vec16_kernel<true, 1><<<grid, kThreads, 0, s>>>(x4, n4, y_scale, dv, zp_f, has_zp, round_mode, y32);
         else if (round_mode == CHXQ_ROUND_REF_HALF_UP && dv.fast)
             quantize_vec16_kernel<false, 0><<<grid, kThreads, 0, s>>>(x4, n4, y_scale, dv, zp_f, has_zp, round_mode, y32);
+        else if (dv.fast)
+            quantize_vec16_kernel<false, 2><<<grid, kThreads, 0, s>>>(x4, n4, y_scale, dv, zp_f, has_zp, round_mode, y32);
         else
             quantize_vec16_kernel<false, 1><<<grid, kThreads, 0, s>>>(x4, n4, y_scale, dv, zp_f, has_zp, round_mode, y32);
         CHXQ_LAUNCH_CHECK();
