@@ -91,3 +91,58 @@ def mobilenetv2_forward(params, x, mode="exact", taps=None):
     if taps is not None:
         taps["pooled"] = pooled
     return orc.linear_f32(pooled, params["fc_w"], params["fc_b"])
+
+
+def run_program(program, inputs, trace=None):
+    """CPU evaluation of a `run_onnx` program (the instruction list `chainer-compiler_b200/run_onnx.py::compile_model`
+    produces) with the oracle's ops: the checker for the quantized graph the reference's `--quantize` pass builds
+    (compiler/quantize.cc:142-281).  program: an object with .insts (op, inputs, outputs, attrs), .constants (numpy),
+    .outputs.  Glue ops are numpy expressions."""
+    env = dict(program.constants)
+    env.update({k: np.asarray(v) for k, v in inputs.items()})
+    for inst in program.insts:
+        a, x, op = inst.attrs, [env[i] for i in inst.inputs], inst.op
+        if op == "ReduceMinMax":
+            out = [np.float32(x[0].min()), np.float32(x[0].max())]
+        elif op == "DynamicQuantParamsU8":
+            rmin, rmax = np.float32(x[0]), np.float32(x[1])
+            scale = np.float32((rmax - rmin) / np.float32(255.0)) if rmax != rmin else np.float32(1.0)
+            out = [scale, np.uint8(int(np.clip(np.floor(np.float32((np.float32(0.0) - rmin) / scale)), 0, 255)))]
+        elif op == "QuantizeLinear":
+            out = [orc.quantize_linear(x[0], x[1], int(x[2]), out_dtype=np.asarray(x[2]).dtype)]
+        elif op == "ConvInteger":
+            auto_pad = a.get("auto_pad", "NOTSET")
+            pads = list(a.get("pads", []))
+            out = [orc.conv_integer(x[0], x[1], int(x[2]), np.asarray(x[3]).astype(np.int32), tuple(a.get("strides", [])), tuple(pads[:len(pads) // 2]),
+                                    a.get("group", 1), "" if auto_pad == "NOTSET" else auto_pad)]
+        elif op == "MatMulInteger":
+            out = [orc.matmul_integer(x[0], x[1], np.asarray(x[2]).reshape(-1), np.asarray(x[3]).reshape(-1))]
+        elif op == "ScaleProduct":
+            m = (np.asarray(x[0], np.float32) * np.asarray(x[1], np.float32)).astype(np.float32)
+            out = [m.reshape(a["shape"]) if a.get("shape") else m]
+        elif op == "Cast":
+            out = [x[0].astype(np.float32)]
+        elif op in ("Add", "Sub", "Mul", "Div"):
+            f = {"Add": np.add, "Sub": np.subtract, "Mul": np.multiply, "Div": np.divide}[op]
+            out = [f(x[0], x[1]).astype(np.float32)]
+        elif op == "Relu":
+            out = [np.maximum(x[0], np.float32(0))]
+        elif op == "Reshape":
+            shape = [x[0].shape[i] if d == 0 else int(d) for i, d in enumerate(x[1])]
+            out = [x[0].reshape(shape)]
+        elif op == "MaxPool":
+            k, s = a["kernel_shape"], a.get("strides", [1, 1])
+            N, C, H, W = x[0].shape
+            Ho, Wo = (H - k[0]) // s[0] + 1, (W - k[1]) // s[1] + 1
+            y = np.full((N, C, Ho, Wo), -np.inf, np.float32)
+            for i in range(k[0]):
+                for j in range(k[1]):
+                    y = np.maximum(y, x[0][:, :, i:i + s[0] * Ho:s[0], j:j + s[1] * Wo:s[1]])
+            out = [y]
+        else:
+            raise NotImplementedError(op)
+        for name, v in zip(inst.outputs, out):
+            env[name] = v
+            if trace is not None:
+                trace[name] = v
+    return [(o, env[o]) for o in program.outputs]
