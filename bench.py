@@ -61,7 +61,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "200"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -246,7 +246,18 @@ def run_chxq(args):
     e1.record()
     barrier()
     ms_total = dp.max_over_ranks(e0.elapsed_time(e1), dev, world)
+    if ms_total < 600.0:
+        # a short timed region gives nvidia-smi no time for samples: keep the same loop running (untimed) until the sampler
+        # has seen ~0.6 s of this load
+        t_end = time.perf_counter() + (600.0 - ms_total) / 1000.0
+        while time.perf_counter() < t_end:
+            for _ in range(10):
+                eng.step_device()
+            torch.cuda.synchronize(dev)
+        barrier()
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None and ms_total < 600.0:
+        clocks["note"] = "timed region of %.0f ms extended by an untimed continuation of the same loop for the samples" % ms_total
     ops.device_status()
     ms_per_step = ms_total / args.steps
     value = args.batch * world / (ms_per_step / 1000.0)
@@ -280,6 +291,17 @@ def run_chxq(args):
         tms, n, macs = ctypes.c_double(), ctypes.c_int64(), ctypes.c_double()
         L.chxq_tc_profile_read(ctypes.byref(tms), ctypes.byref(n), ctypes.byref(macs))
         L.chxq_tc_profile(0)
+        # an event pair around nothing still measures a few microseconds: take that off every launch
+        gaps = []
+        for _ in range(50):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            b.record()
+            gaps.append((a, b))
+        torch.cuda.synchronize(dev)
+        pair_ms = float(np.median([a.elapsed_time(b) for a, b in gaps]))
+        raw_ms = tms.value
+        tms.value = max(raw_ms - pair_ms * n.value, 0.5 * raw_ms)
         pk = peaks()
         achieved = 2.0 * macs.value / (tms.value / 1000.0) / 1e12
         peak = 2.0 * pk["bf16_sustained"]
@@ -291,6 +313,7 @@ def run_chxq(args):
                 "traffic_note": "bytes per launch, average over the 53 launches of a step (ncu, batch 256)" if traffic else "not captured for this configuration",
                 "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s; the file has no int8 entry; int8 ops counted as 2 per MAC)" % pk["source"],
                 "launches_per_step": int(n.value // prof_steps), "kernel_ms_per_step": tms.value / prof_steps,
+                "event_pair_overhead_us": pair_ms * 1000.0, "kernel_ms_per_step_uncorrected": raw_ms / prof_steps,
                 "share_of_step": (tms.value / prof_steps) / ms_per_step, "algorithmic_gop_per_step": 2.0 * macs.value / prof_steps / 1e9}
         if not args.no_cpu_baseline:
             orc = entry.load_oracle()

@@ -83,16 +83,10 @@ int pick_bn(int cols, int64_t pos_tiles) {
 }  // namespace
 
 int choose_bk(int k) {
-    const int cand[3] = {128, 64, 32};
-    int best = 32, best_cost = 1 << 30;
-    for (int i = 0; i < 3; ++i) {
-        const int cost = (k + cand[i] - 1) / cand[i] * cand[i];
-        if (cost < best_cost) {
-            best_cost = cost;
-            best = cand[i];
-        }
-    }
-    return best;
+    // 64- or 128-byte K tiles, whichever pads K less (128 on a tie): the part of a tile beyond the operand is TMA zero fill, not
+    // traffic, and only these two tile sizes have the grouped kernel.
+    const int pad128 = (k + 127) / 128 * 128, pad64 = (k + 63) / 64 * 64;
+    return pad128 <= pad64 ? 128 : 64;
 }
 
 static int largest_pow2_divisor(int v, int cap) {
