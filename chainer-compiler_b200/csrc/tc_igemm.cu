@@ -262,7 +262,6 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     int bn2 = (q.cols > 64 && q.group_cols == 0) ? 128 : 64;
     alignas(64) CUtensorMap tmY, tmR;
     if ((epi_kind == tc::kEpiKU8 || epi_kind == tc::kEpiKU8Fold) && g_variant != 1 && p.vec_ok && q.ldc % 16 == 0 && (q.bk == 64 || q.bk == 128) &&
-        !(epi_kind == tc::kEpiKU8Fold && q.col_corr != nullptr) && !(q.epi.residual != nullptr && bn2 == 64) &&
         // folded tail: the saturating add clamps at zero, which is the Relu only when the output zero point is zero
         !(epi_kind == tc::kEpiKU8Fold && q.epi.residual != nullptr && q.epi.rq.res_relu && q.epi.rq.out_zp_f != 0.f)) {
         const int r = 256 / bn2;

@@ -111,7 +111,7 @@ struct Tc2Config {
     // With one: three, each filled by the residual's TMA load, overwritten in place by the epilogue (a thread reads and
     // writes the same 16 bytes) and drained by the store; three, so that the load for group i + 1 can run during the
     // epilogue of group i while the store of group i - 1 is still reading its buffer.
-    static constexpr int kBufs = RES ? 3 : 2;
+    static constexpr int kBufs = RES ? ((BN == 64 && BK == 128 && !HALO) ? 2 : 3) : 2;  // 64-channel blocks with 128-byte K tiles: two, for room
     static constexpr int kOutBytes = kBufs * kR * kTileOut;
     static constexpr int kFixed = kOutBytes + (HALO ? kAStages * kStageA : 0);
     static constexpr int kBudget = 222 * 1024;
@@ -123,7 +123,7 @@ struct Tc2Config {
     static constexpr int kBarBytes = (2 * kStages + 17) * 8;
     static constexpr int kBarOffset = kStages * kStageBytes + kFixed;
     static constexpr int kParamOffset = ((kBarOffset + kBarBytes + 16 + 15) / 16) * 16;
-    static constexpr int kParamBytes = 16 * (BN / 2) * 4;  // 16 warps x (BN/4 multipliers + BN/4 additive terms)
+    static constexpr int kParamBytes = 16 * (3 * BN / 4) * 4;  // 16 warps x (BN/4 multipliers + BN/4 additive terms + BN/4 zero-point terms)
     static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kParamOffset + kParamBytes;
     static constexpr bool kUsable = kStages >= 2;
 };
@@ -235,8 +235,8 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
                 const int gbase = p.group_cols > 0 ? (ct * BN / p.group_cols) * p.group_cin : 0;
                 if (RES) {
-                    const int rb = it % 3;
-                    if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / 3) & 1u) ^ 1u, abort_flag, p.status, 5, 0)) break;
+                    const int rb = it % Cfg::kBufs;
+                    if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / Cfg::kBufs) & 1u) ^ 1u, abort_flag, p.status, 5, 0)) break;
                     mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
 #pragma unroll
                     for (int t = 0; t < kR; ++t)
@@ -385,8 +385,10 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int quarter = warp & 3;
         const int sub = e >> 2;
         const int row = quarter * 32 + lane;
-        float* s_mult = reinterpret_cast<float*>(smem + Cfg::kParamOffset) + e * (BN / 2);
+        float* s_mult = reinterpret_cast<float*>(smem + Cfg::kParamOffset) + e * (3 * BN / 4);
         uint32_t* s_add = reinterpret_cast<uint32_t*>(s_mult + BN / 4);
+        uint32_t* s_corr = s_add + BN / 4;  // folded epilogue only: activation zero point x sum of the channel's weights
+        const bool has_corr = kFold && p.col_corr != nullptr;
         int cached_ct = -1;
         const RequantParams rq = p.epi.rq;
         const float hi_ph = (float)(rq.clamp_hi_q >= 0 ? rq.clamp_hi_q : 255) + 0.5f;
@@ -419,7 +421,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int j = lane; j < BN / 4; j += 32) {
                     const int c = col0 + ((j >> 4) * 4 + sub) * 16 + (j & 15);
                     float m = 0.f;
-                    uint32_t add = 0u;
+                    uint32_t add = 0u, corr = 0u;
                     if (c < p.cols) {
                         m = epi_mult(p.epi, c);
                         const int bias = p.epi.bias ? p.epi.bias[c] : 0;
@@ -427,6 +429,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             m = __fdiv_rn(m, rq.y_scale);
                             add = __float_as_uint(fold_offset(bias, m, rq) * kS);
                             m *= kS;
+                            if (p.col_corr) corr = (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];
                         } else {
                             add = (uint32_t)bias;
                             if (p.col_corr) add -= (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];
@@ -434,6 +437,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                     s_mult[j] = m;
                     s_add[j] = add;
+                    s_corr[j] = corr;
                 }
                 __syncwarp();
                 cached_ct = ct;
@@ -461,6 +465,14 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const uint32_t resw[4] = {resv.x, resv.y, resv.z, resv.w};
                     const uint4* pm = reinterpret_cast<const uint4*>(s_mult + i * 16);
                     const uint4* pa = reinterpret_cast<const uint4*>(s_add + i * 16);
+                    if (has_corr) {  // folded: the bias lives in the float offset, the activation zero-point term stays an integer
+                        const uint4* pc = reinterpret_cast<const uint4*>(s_corr + i * 16);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint4 c4 = pc[j];
+                            r[4 * j] -= c4.x; r[4 * j + 1] -= c4.y; r[4 * j + 2] -= c4.z; r[4 * j + 3] -= c4.w;
+                        }
+                    }
                     uint32_t outw[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -609,7 +621,9 @@ int launch_bk2(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, con
         if constexpr (BK == 64) {
             switch (key) {
                 case 0: return launch_one2<64, BK, kEpiKU8, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
+                case 1: return launch_one2<64, BK, kEpiKU8, true, true>(tmA, tmB, tmY, tmR, p, grid, s);
                 case 2: return launch_one2<64, BK, kEpiKU8Fold, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
+                case 3: return launch_one2<64, BK, kEpiKU8Fold, true, true>(tmA, tmB, tmY, tmR, p, grid, s);
                 case 4: return launch_one2<128, BK, kEpiKU8, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
                 case 5: return launch_one2<128, BK, kEpiKU8, true, true>(tmA, tmB, tmY, tmR, p, grid, s);
                 case 6: return launch_one2<128, BK, kEpiKU8Fold, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
@@ -620,7 +634,9 @@ int launch_bk2(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, con
     }
     switch (key) {
         case 0: return launch_one2<64, BK, kEpiKU8, false, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 1: return launch_one2<64, BK, kEpiKU8, true, false>(tmA, tmB, tmY, tmR, p, grid, s);
         case 2: return launch_one2<64, BK, kEpiKU8Fold, false, false>(tmA, tmB, tmY, tmR, p, grid, s);
+        case 3: return launch_one2<64, BK, kEpiKU8Fold, true, false>(tmA, tmB, tmY, tmR, p, grid, s);
         case 4: return launch_one2<128, BK, kEpiKU8, false, false>(tmA, tmB, tmY, tmR, p, grid, s);
         case 5: return launch_one2<128, BK, kEpiKU8, true, false>(tmA, tmB, tmY, tmR, p, grid, s);
         case 6: return launch_one2<128, BK, kEpiKU8Fold, false, false>(tmA, tmB, tmY, tmR, p, grid, s);

@@ -367,6 +367,7 @@ def test_grouped_tensor_core_kernel(pkg, ops, orc, dev, grouped_kernel, N, C, H,
         dict(zx=0, zy=0, kw={}),
         dict(zx=5, zy=17, kw={}),
         dict(zx=0, zy=131, kw=dict(fold_scales=True)),
+        dict(zx=7, zy=131, kw=dict(fold_scales=True)),  # folded epilogue with the activation zero-point term
         dict(zx=0, zy=0, kw=dict(clamp_hi_q=77)),
         dict(zx=0, zy=121, kw=dict(residual=rt, res_scale=0.05, res_zero_point=9, out_scale=0.11, out_zero_point=0)),
         dict(zx=0, zy=121, kw=dict(residual=rt, res_scale=0.05, res_zero_point=9, out_scale=0.11, out_zero_point=0, fold_scales=True)),
@@ -382,6 +383,9 @@ def test_grouped_tensor_core_kernel(pkg, ops, orc, dev, grouped_kernel, N, C, H,
     acc = orc.conv_integer(x, w, 0, wz, (stride, stride), (pad, pad))
     want = orc.requantize(acc, sx, ws, sy, 131, bias=bias, channel_axis=1, fold=True)
     assert np.array_equal(run(2, 0, 131, fold_scales=True).cpu().numpy(), want)
+    acc7 = orc.conv_integer(x, w, 7, wz, (stride, stride), (pad, pad))
+    want7 = orc.requantize(acc7, sx, ws, sy, 131, bias=bias, channel_axis=1, fold=True)
+    assert np.array_equal(run(2, 7, 131, fold_scales=True).cpu().numpy(), want7)
     want = orc.requantize(acc, sx, ws, sy, 121, bias=bias, channel_axis=1)
     want_r = orc.qadd_relu(want, sy, 121, r, 0.05, 9, 0.11, 100, relu=False)
     got = run(2, 0, 121, residual=rt, res_scale=0.05, res_zero_point=9, out_scale=0.11, out_zero_point=100, res_relu=False)
