@@ -34,7 +34,7 @@ def parse():
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU")
     ap.add_argument("--cpu-sample", type=int, default=8, help="images of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tc-variant", type=int, default=0, choices=[0, 1, 2, 3],
+    ap.add_argument("--tc-variant", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
                     help="tensor-core kernel choice (chxq_tc_variant): 0 by shape, 1 one tile per step, 2 grouped tiles")
     ap.add_argument("--exact-requant", action="store_true",
                     help="requantize in the reference's operation order (multiply by x_scale*w_scale, divide by y_scale) instead of one "

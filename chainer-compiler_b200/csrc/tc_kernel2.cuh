@@ -251,12 +251,19 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             break;
                         }
                         mbar_expect_tx(hfull_bar(hstage), (uint32_t)(kR * (BK / 16)) * halo_bytes);
+                        if (p.halo_swz) {
 #pragma unroll
-                        for (int t = 0; t < kR; ++t)
+                            for (int t = 0; t < kR; ++t)
+                                tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA), &tmA, hfull_bar(hstage), gbase + cc * BK,
+                                            w0[t] - p.pad_left, h0[t] - p.pad_top, n0[t]);
+                        } else {
 #pragma unroll
-                            for (int j = 0; j < BK / 16; ++j)
-                                tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA + j * kHaloPlane), &tmA, hfull_bar(hstage),
-                                            gbase + cc * BK + j * 16, w0[t] - p.pad_left, h0[t] - p.pad_top, n0[t]);
+                            for (int t = 0; t < kR; ++t)
+#pragma unroll
+                                for (int j = 0; j < BK / 16; ++j)
+                                    tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA + j * kHaloPlane), &tmA, hfull_bar(hstage),
+                                                gbase + cc * BK + j * 16, w0[t] - p.pad_left, h0[t] - p.pad_top, n0[t]);
+                        }
                         if (++hstage == Cfg::kAStages) {
                             hstage = 0;
                             hphase ^= 1u;
@@ -330,14 +337,27 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             }
                             tc_fence_after();
                             const uint32_t b_lo = b_lo0 + (uint32_t)(stage * (Cfg::kStageB >> 4));
-                            const uint32_t a_lo = ha_lo + (uint32_t)(kh * halo_w + kw);  // the tap's view starts (kh, kw) pixels of 16 bytes in
                             const uint32_t accum = (cc > 0 || tap > 0) ? 1u : 0u;
+                            if (p.halo_swz) {
+                                // one swizzled tile of BK-byte pixels: the view starts (kh, kw) pixels in; 8-row groups are one halo row apart
+                                const uint32_t a_lo = a_lo0 + (uint32_t)(hstage * (Cfg::kStageA >> 4)) + (uint32_t)((kh * halo_w + kw) * (BK >> 4));
+                                uint32_t a_hi = (uint32_t)((halo_w * BK) >> 4) | (1u << 14) | ((BK == 128 ? 2u : 4u) << 29);
+                                if (p.halo_swz == 2) a_hi |= ((a_lo >> 3) & 7u) << 17;  // base offset: (start address >> 7) & 7
 #pragma unroll
-                            for (int k = 0; k < BK / 32; ++k)
+                                for (int k = 0; k < BK / 32; ++k)
 #pragma unroll
-                                for (int t = 0; t < kR; ++t)
-                                    umma_i8_lohi(tmem_d + (uint32_t)(t * BN), a_lo + (uint32_t)((t * Cfg::kTileA + 2 * k * kHaloPlane) >> 4), halo_hi,
-                                                 b_lo + k * 2, desc_hi, p.idesc, k > 0 ? 1u : accum);
+                                    for (int t = 0; t < kR; ++t)
+                                        umma_i8_lohi(tmem_d + (uint32_t)(t * BN), a_lo + (uint32_t)((t * Cfg::kTileA + k * 32) >> 4), a_hi, b_lo + k * 2,
+                                                     desc_hi, p.idesc, k > 0 ? 1u : accum);
+                            } else {
+                                const uint32_t a_lo = ha_lo + (uint32_t)(kh * halo_w + kw);  // the tap's view starts (kh, kw) pixels of 16 bytes in
+#pragma unroll
+                                for (int k = 0; k < BK / 32; ++k)
+#pragma unroll
+                                    for (int t = 0; t < kR; ++t)
+                                        umma_i8_lohi(tmem_d + (uint32_t)(t * BN), a_lo + (uint32_t)((t * Cfg::kTileA + 2 * k * kHaloPlane) >> 4), halo_hi,
+                                                     b_lo + k * 2, desc_hi, p.idesc, k > 0 ? 1u : accum);
+                            }
                             umma_commit(empty_bar(stage));
                             if (++stage == kStages) {
                                 stage = 0;

@@ -16,6 +16,7 @@ struct TcParams {
     int Wo, Ho, No;
     int KH, KW, pad_top, pad_left;
     int sw, sh;  // convolution strides: input coordinate = output coordinate * stride - pad + tap
+    int halo_swz;  // halo form: 0 = planes of 16-byte rows without swizzle, 1 = one swizzled tile of BK-byte rows, 2 = same with the descriptor's base offset
     int group_cols, group_cin;  // grouped convolution (0 = one group): first input channel of a column tile = (col0 / group_cols) * group_cin
     int c_chunks;  // c_pad / BK
     int c_pad;
