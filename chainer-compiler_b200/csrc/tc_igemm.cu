@@ -269,7 +269,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
         // by default for grouped / depthwise layers (measured: MobileNetV2 -7 %), on request (variant 3) for dense ones (ResNet-50's 3x3
         // layers are faster without: the halo planes are 16-byte TMA rows, and TMA moves about one row per clock)
         halo = (g_variant >= 3 || (g_variant == 0 && q.group_cols > 0)) && q.KH * q.KW > 1 && q.KH <= 3 && q.KW <= 3 && p.sw == 1 && p.sh == 1 &&
-               q.bk == 64 && q.a_row_bytes == 0 && q.Wo >= 8 && q.Ho >= 8;
+               (q.bk == 64 || (q.bk == 128 && bn2 == 128 && q.epi.residual == nullptr)) && q.a_row_bytes == 0 && q.Wo >= 8 && q.Ho >= 8;
         int64_t pos_tiles2 = pos_tiles;
         if (halo) {
             p.Wb = 8; p.Hb = 16; p.Nb = 1;
@@ -283,11 +283,11 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
         if (halo) {
             const cuuint64_t dims[4] = {(cuuint64_t)q.C, (cuuint64_t)q.W, (cuuint64_t)q.H, (cuuint64_t)q.N};
             const cuuint64_t strides[3] = {(cuuint64_t)q.a_cs, (cuuint64_t)q.a_cs * q.W, (cuuint64_t)q.a_cs * q.W * q.H};
-            p.halo_swz = g_variant == 4 ? 1 : (g_variant == 5 ? 2 : 0);
-            const cuuint32_t box[4] = {p.halo_swz ? 64u : 16u, (cuuint32_t)(8 + q.KW - 1), (cuuint32_t)(16 + q.KH - 1), 1u};
+            p.halo_swz = g_variant == 5 ? 2 : ((g_variant == 4 || q.bk == 128) ? 1 : 0);  // 128-byte pixels: the swizzled form only
+            const cuuint32_t box[4] = {p.halo_swz ? (cuuint32_t)q.bk : 16u, (cuuint32_t)(8 + q.KW - 1), (cuuint32_t)(16 + q.KH - 1), 1u};
             const cuuint32_t estr[4] = {1, 1, 1, 1};
             CUresult r0 = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                 p.halo_swz ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 p.halo_swz ? swizzle_for(q.bk) : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r0 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A halo) failed with %d", (int)r0);
         }

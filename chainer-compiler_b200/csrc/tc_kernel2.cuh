@@ -632,12 +632,19 @@ int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
 }
 
 // Launches the grouped kernel for (bn, BK, epi, residual, halo); CHXQ_ERR_UNSUPPORTED when the combination has no
-// instantiation.  The halo form exists for the 64-byte K tile only.
+// instantiation.
 template <int BK>
 int launch_bk2(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
                const CUtensorMap& tmR, const TcParams& p, int grid, cudaStream_t s) {
     const int key = (bn == 128 ? 4 : 0) + (epi == kEpiKU8Fold ? 2 : 0) + (res ? 1 : 0);
     if (halo) {
+        if constexpr (BK == 128) {
+            // 128-byte K tiles: one swizzled halo tile per position tile; 128-channel blocks without a residual only (shared memory)
+            switch (key) {
+                case 4: return launch_one2<128, BK, kEpiKU8, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
+                case 6: return launch_one2<128, BK, kEpiKU8Fold, false, true>(tmA, tmB, tmY, tmR, p, grid, s);
+            }
+        }
         if constexpr (BK == 64) {
             switch (key) {
                 case 0: return launch_one2<64, BK, kEpiKU8, false, true>(tmA, tmB, tmY, tmR, p, grid, s);

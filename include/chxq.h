@@ -74,9 +74,10 @@ int chxq_tc_profile_read(double* total_ms, int64_t* launches, double* total_macs
 
 /* The tensor-core path has two kernels with identical results: one output tile per step (every epilogue), and grouped
  * tiles whose uint8 outputs leave through shared memory and a TMA store (uint8 requantizing epilogues with 16-byte
- * aligned output rows); the second also has a form for stride-1 convolutions up to 3 x 3 that stages the input halo tile
+ * aligned output rows); the second also has forms for stride-1 convolutions up to 3 x 3 that stage the input halo tile
  * once per tile instead of once per tap.  0 = choose by problem shape (default), 1 = always the first, 2 = the second
- * whenever eligible, 3 = the second with halo tiles whenever eligible.  Process-wide; meant for measurements and tests.
+ * whenever eligible, 3 = the second with halo tiles (planes of 16-byte rows) whenever eligible, 4 = halo tiles stored
+ * swizzled, 5 = as 4 with the descriptor's base-offset field set.  Process-wide; meant for measurements and tests.
  * No counterpart in the reference. */
 int chxq_tc_variant(int32_t variant);
 

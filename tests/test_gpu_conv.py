@@ -377,7 +377,7 @@ def test_grouped_tensor_core_kernel(pkg, ops, orc, dev, grouped_kernel, N, C, H,
     ]
     for c in cases:
         ref = run(1, c["zx"], c["zy"], **c["kw"])
-        for variant in (2, 3):  # 3: halo tiles where the geometry allows them (3x3 and smaller, stride 1, 64-byte K tile)
+        for variant in (2, 3, 4, 5):  # 3..5: halo tiles where the geometry allows them (3x3 and smaller, stride 1): planes, swizzled, swizzled + base offset
             got = run(variant, c["zx"], c["zy"], **c["kw"])
             assert torch.equal(got, ref), (variant, c)
     acc = orc.conv_integer(x, w, 0, wz, (stride, stride), (pad, pad))
@@ -445,7 +445,7 @@ def test_grouped_conv_tensor_core_packed(pkg, ops, orc, dev, N, C, H, W, M, grou
     wz0 = np.zeros(M, np.int8)
     acc = orc.conv_integer(x, w, 0, wz0, (stride, stride), (pad, pad), group)
     for fold in (False, True):
-        for variant in (1, 2, 3):
+        for variant in (1, 2, 3, 4):
             assert pkg.lib().chxq_tc_variant(variant) == 0
             yq = ops.QLinearConvPacked(xt, pk, 0.02, np.uint8(0), _t(ws_, dev), _t(wz0, dev), 0.05, np.uint8(20), b=_t(bias, dev), fold_scales=fold,
                                        clamp_hi_q=200)
