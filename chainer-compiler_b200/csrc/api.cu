@@ -158,30 +158,71 @@ __global__ void __launch_bounds__(256) conv_possum_kernel(
 
 // Space-to-depth repack for the stride-2 small-channel path: block (n, r, b) of the output holds the 2x2 pixels
 // (2 (r + t0h) + dy, 2 (b + t0w) + dx), channel-minor, as 16 bytes [(dy*2+dx)*C + c]; pixels outside the map hold the
-// activation zero point, unused bytes hold zero (their weights are zero).  One thread per block.
+// activation zero point, unused bytes hold zero (their weights are zero).
+// kQuant: the input is the fp32 tensor in front of a QuantizeLinear (scale qs, zero point qzp, reference rounding) that is
+// applied on the fly, with the arithmetic of quantize_one, so that the uint8 map never exists in memory.
+struct S2dQuant {
+    float scale, zp_f;
+    int has_zp, round_mode;
+};
+template <bool kQuant>
 __global__ void __launch_bounds__(256) s2d_repack_kernel(
-        const uint8_t* __restrict__ x, int N, int C, int H, int W, int64_t es_n, int64_t es_c, int64_t es_h, int64_t es_w, int t0h, int t0w,
-        int rows2, int cols2, uint32_t pad_byte, uint4* __restrict__ out) {
-    const int64_t total = (int64_t)N * rows2 * cols2;
+        const void* __restrict__ xv, int N, int C, int H, int W, int64_t es_n, int64_t es_c, int64_t es_h, int64_t es_w, int t0h, int t0w,
+        int rows2, int cols2, uint32_t pad_byte, S2dQuant qz, uint4* __restrict__ out) {
+    // One thread per PAIR of horizontally adjacent blocks: their four input pixels per (row, channel) are contiguous in a
+    // W-contiguous map and come in as one 32-bit (uint8) or 128-bit (fp32) load away from the borders.
+    const uint8_t* x = static_cast<const uint8_t*>(xv);
+    const float* xf = static_cast<const float*>(xv);
+    const int pairs = (cols2 + 1) / 2;
+    const int64_t total = (int64_t)N * rows2 * pairs;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
-    const int b = (int)(idx % cols2);
-    const int64_t q = idx / cols2;
+    const int b0 = 2 * (int)(idx % pairs);
+    const int64_t q = idx / pairs;
     const int r = (int)(q % rows2);
     const int n = (int)(q / rows2);
-    uint32_t word[4] = {0u, 0u, 0u, 0u};
+    const bool base_ok = (reinterpret_cast<uintptr_t>(xv) & 15u) == 0;
+    uint32_t word[2][4] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};
+    const int xx0 = 2 * (b0 + t0w);
 #pragma unroll
-    for (int d = 0; d < 4; ++d) {
-        const int yy = 2 * (r + t0h) + (d >> 1), xx = 2 * (b + t0w) + (d & 1);
-        const bool inside = yy >= 0 && yy < H && xx >= 0 && xx < W;
-        const uint8_t* p = x + (int64_t)n * es_n + (int64_t)yy * es_h + (int64_t)xx * es_w;
+    for (int dy = 0; dy < 2; ++dy) {
+        const int yy = 2 * (r + t0h) + dy;
+        const bool row_in = yy >= 0 && yy < H;
         for (int c = 0; c < C; ++c) {
-            const uint32_t v = inside ? (uint32_t)p[c * es_c] : pad_byte;
-            const int pos = d * C + c;
-            word[pos >> 2] |= v << (8 * (pos & 3));
+            uint32_t px[4] = {pad_byte, pad_byte, pad_byte, pad_byte};
+            if (row_in) {
+                const int64_t off = (int64_t)n * es_n + (int64_t)yy * es_h + (int64_t)c * es_c + (int64_t)xx0 * es_w;
+                if (es_w == 1 && xx0 >= 0 && xx0 + 3 < W && (off & 3) == 0 && base_ok) {
+                    if (kQuant) {
+                        const float4 f = *reinterpret_cast<const float4*>(xf + off);
+                        px[0] = (uint32_t)quantize_one<false>(f.x, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                        px[1] = (uint32_t)quantize_one<false>(f.y, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                        px[2] = (uint32_t)quantize_one<false>(f.z, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                        px[3] = (uint32_t)quantize_one<false>(f.w, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                    } else {
+                        const uint32_t w4 = *reinterpret_cast<const uint32_t*>(x + off);
+                        px[0] = w4 & 0xffu; px[1] = (w4 >> 8) & 0xffu; px[2] = (w4 >> 16) & 0xffu; px[3] = w4 >> 24;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int xx = xx0 + i;
+                        if (xx >= 0 && xx < W)
+                            px[i] = kQuant ? (uint32_t)quantize_one<false>(xf[off + i * es_w], qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode)
+                                           : (uint32_t)x[off + i * es_w];
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int pos = (dy * 2 + (i & 1)) * C + c;
+                word[i >> 1][pos >> 2] |= px[i] << (8 * (pos & 3));
+            }
         }
     }
-    out[idx] = make_uint4(word[0], word[1], word[2], word[3]);
+    const int64_t o = ((int64_t)n * rows2 + r) * cols2 + b0;
+    out[o] = make_uint4(word[0][0], word[0][1], word[0][2], word[0][3]);
+    if (b0 + 1 < cols2) out[o + 1] = make_uint4(word[1][0], word[1][1], word[1][2], word[1][3]);
 }
 
 // OIHW weights -> the K layout of the space-to-depth path: row m, K index t * bk + u * 16 + (dy*2+dx) * C + c holds
@@ -393,7 +434,7 @@ int pack_weights(const void* w, const chxq_conv_geom& g, const TcConvPlan& pl, c
 // Runs a planned convolution on the tensor-core kernel from a packed weight blob.
 int conv_tc_run(
         const void* x, const uint8_t* blob, const chxq_conv_geom& g, const TcConvPlan& pl, int x_zp, bool zw_zero, const EpiArgs& epi, void* y,
-        uint8_t* scratch, size_t scratch_bytes, cudaStream_t s) {
+        uint8_t* scratch, size_t scratch_bytes, cudaStream_t s, const S2dQuant* quant_in = nullptr) {
     const ConvWs L = conv_ws_layout(g, pl);
     const int taps = g.KH * g.KW;
     const int64_t rows = (int64_t)g.N * g.Ho * g.Wo;
@@ -417,10 +458,15 @@ int conv_tc_run(
                   es_n = nhwc ? xcs * g.W * g.H : (int64_t)g.C * g.H * g.W;
     if (pl.path == kTcS2d) {
         uint8_t* A = scratch;
-        s2d_repack_kernel<<<blocks_for((int64_t)g.N * pl.rows2 * pl.cols2), 256, 0, s>>>(static_cast<const uint8_t*>(x), g.N, g.C, g.H, g.W, es_n, es_c,
-                                                                                        es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2,
-                                                                                        (uint32_t)(x_zp & 0xff), reinterpret_cast<uint4*>(A));
+        if (quant_in)
+            s2d_repack_kernel<true><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
+                    x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), *quant_in,
+                    reinterpret_cast<uint4*>(A));
+        else
+            s2d_repack_kernel<false><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
+                    x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), S2dQuant{}, reinterpret_cast<uint4*>(A));
         CHXQ_LAUNCH_CHECK();
+        if (quant_in && !zw_zero) return set_error(CHXQ_ERR_UNSUPPORTED, "fused QuantizeLinear + QLinearConv needs zero weight zero points");
         if (!zw_zero) {
             rowsum = reinterpret_cast<int32_t*>(scratch + L.im2col_bytes);
             conv_possum_kernel<<<blocks_for(rows), 256, 0, s>>>(static_cast<const uint8_t*>(x), x_signed, g.N, g.H, g.W, g.C, es_n, es_c, es_h, es_w,
@@ -832,6 +878,28 @@ extern "C" int chxq_qlinear_conv_packed(
     if (rc != CHXQ_OK) return rc;
     return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, p->x_zero_point, (packed_flags & 2) != 0, epi, y,
                        static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream));
+}
+
+// QuantizeLinear(x; p->x_scale, p->x_zero_point, uint8, reference rounding or round-half-to-even) fused into the packed
+// QLinearConv that consumes it: for stride-2 stems (the space-to-depth path), whose repack pass quantizes on the fly.
+extern "C" int chxq_quantize_qlinear_conv_packed(
+        const float* x, int32_t quant_round_mode, const void* packed, const chxq_conv_geom* g, const chxq_qconv_params* p, int32_t packed_flags, void* y,
+        void* workspace, size_t workspace_bytes, void* stream) {
+    TcConvPlan pl;
+    int rc = packed_common("QuantizeLinear+QLinearConv(packed)", x, packed, g, packed_flags, &pl);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(y != nullptr, "QuantizeLinear+QLinearConv(packed): null output");
+    CHXQ_CHECK_ARG(g->x_dtype == CHXQ_UINT8, "QuantizeLinear+QLinearConv(packed): the quantized activation type must be uint8");
+    CHXQ_CHECK_ARG(quant_round_mode == CHXQ_ROUND_REF_HALF_UP || quant_round_mode == CHXQ_ROUND_RNE, "QuantizeLinear+QLinearConv(packed): bad rounding mode");
+    if (pl.path != kTcS2d)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "QuantizeLinear+QLinearConv(packed): only stride-2 convolutions over at most 4 channels fuse their QuantizeLinear");
+    EpiArgs epi;
+    rc = fill_requant("QuantizeLinear+QLinearConv(packed)", p, g, &epi);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(p->x_zero_point >= 0 && p->x_zero_point <= 255 && p->x_scale > 0.f, "QuantizeLinear+QLinearConv(packed): bad activation scale / zero point");
+    const S2dQuant qz{p->x_scale, (float)p->x_zero_point, p->x_zero_point != 0, quant_round_mode};
+    return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, p->x_zero_point, (packed_flags & 2) != 0, epi, y,
+                       static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream), &qz);
 }
 
 extern "C" int chxq_conv_integer_packed(

@@ -210,8 +210,13 @@ class ResNet50Int8:
         fold=True requantizes every convolution with one multiplier per channel (QLinearConv's fold_scales)."""
         assert self.calibrated
         assert fused or not fold, "the folded residual tail exists only inside the convolution epilogue"
-        xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
-        h = self._run_conv(self.stem, xq, fold=fold)
+        c = self.stem
+        if fused:  # the input's QuantizeLinear runs inside the stem convolution's repack pass
+            h = ops.QuantizeLinearConvPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
+                                             b=c.dev["bias"], fold_scales=fold)
+        else:
+            xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
+            h = self._run_conv(c, xq, fold=fold)
         if taps is not None:
             taps["stem"] = h
         h = ops.MaxPoolU8(h, 3, 2, 0, cover_all=True)
@@ -504,8 +509,13 @@ class MobileNetV2Int8:
 
     def forward(self, x, fused=True, fold=False, taps=None):
         assert self.calibrated
-        xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
-        h = self._run(self.stem, xq, fold=fold)
+        c = self.stem
+        if fused:  # the input's QuantizeLinear runs inside the stem convolution's repack pass
+            h = ops.QuantizeLinearConvPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
+                                             b=c.dev["bias"], clamp_hi_q=c.clamp, fold_scales=fold)
+        else:
+            xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
+            h = self._run(c, xq, fold=fold)
         if taps is not None:
             taps["stem"] = h
         for i, b in enumerate(self.blocks):

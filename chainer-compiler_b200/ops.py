@@ -335,6 +335,31 @@ def QLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y
     return y
 
 
+def QuantizeLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b=None, round_mode=ROUND_REF,
+                             quant_round_mode=ROUND_REF, clamp_hi_q=None, out=None, fold_scales=False):
+    """QuantizeLinear(x, x_scale, x_zero_point) fused into the packed QLinearConv that consumes it: x is the fp32 tensor (same
+    layout as the packed geometry expects of the quantized map).  Only for stride-2 convolutions over at most 4 channels
+    (network stems); bit-identical to the two ops run one after the other."""
+    _require_cuda(x)
+    g = packed.g
+    layout_ok = _is_channels_last(x) if g.x_layout == NHWC else x.is_contiguous()
+    if tuple(x.shape) != (g.N, g.C, g.H, g.W) or not layout_ok or x.dtype != torch.float32:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QuantizeLinearConvPacked: x must be the fp32 tensor of the packed geometry / layout")
+    keep = []
+    xq_like = torch.empty(0, dtype=torch.uint8, device=x.device)
+    p, cy = _qconv_params(xq_like, packed.w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, None, 1.0, 0,
+                          True, 1.0, 0, keep, fold_scales)
+    y = out if out is not None else torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.uint8 if cy == UINT8 else torch.int8, device=x.device,
+                                                 memory_format=torch.channels_last)
+    if not packed.eligible:
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "QuantizeLinearConvPacked: this geometry is not eligible for the packed tensor-core path")
+    ws_bytes = lib().chxq_conv_packed_workspace(ctypes.byref(g), p.x_zero_point, packed.flags)
+    ws = workspace(ws_bytes, x.device)
+    check(lib().chxq_quantize_qlinear_conv_packed(_ptr(x), quant_round_mode, _ptr(packed.blob), ctypes.byref(g), ctypes.byref(p), packed.flags, _ptr(y),
+                                                  _ptr(ws), ws_bytes, _stream()))
+    return y
+
+
 def ElementWiseNvrtc(inputs, num_outputs, code, fusion_id):
     """runtime/chxvm_defs.py:431-434; body runtime/ops/nvrtc.cc:90-161: broadcast every input to the common
     shape, make it contiguous, allocate num_outputs arrays of that shape and dtype, run the generated kernel."""

@@ -223,6 +223,14 @@ int chxq_conv_prepack(const void* w, const chxq_conv_geom* g, const void* w_zero
                       size_t packed_bytes, int32_t* flags, void* stream);
 int chxq_qlinear_conv_packed(const void* x, const void* packed, const chxq_conv_geom* g, const chxq_qconv_params* p, int32_t packed_flags,
                              void* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* QuantizeLinear(x; p->x_scale, p->x_zero_point -> uint8, quant_round_mode) fused into the packed QLinearConv that consumes
+ * it: x is the fp32 tensor (layout g->x_layout), the uint8 map never exists in memory.  Only for geometries on the
+ * space-to-depth path (stride 2, at most 4 channels: network stems), CHXQ_ERR_UNSUPPORTED otherwise.  Bit-identical to
+ * chxq_quantize_linear followed by chxq_qlinear_conv_packed.  The reference runs the two ops separately
+ * (runtime/ops/quantize.cc:48-53, 62-94). */
+int chxq_quantize_qlinear_conv_packed(const float* x, int32_t quant_round_mode, const void* packed, const chxq_conv_geom* g,
+                                      const chxq_qconv_params* p, int32_t packed_flags, void* y, void* workspace, size_t workspace_bytes, void* stream);
 int chxq_conv_integer_packed(const void* x, const void* packed, const chxq_conv_geom* g, int32_t has_x_zp, int32_t x_zero_point,
                              int32_t packed_flags, int32_t* y, void* workspace, size_t workspace_bytes, void* stream);
 
