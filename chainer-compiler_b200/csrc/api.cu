@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(256) conv_possum_kernel(
 struct S2dQuant {
     float scale, zp_f;
     int has_zp, round_mode;
+    QDiv dv;  // constant-divisor form of scale (fast path of the QuantizeLinear kernels)
 };
 template <bool kQuant>
 __global__ void __launch_bounds__(256) s2d_repack_kernel(
@@ -194,11 +195,25 @@ __global__ void __launch_bounds__(256) s2d_repack_kernel(
                 const int64_t off = (int64_t)n * es_n + (int64_t)yy * es_h + (int64_t)c * es_c + (int64_t)xx0 * es_w;
                 if (es_w == 1 && xx0 >= 0 && xx0 + 3 < W && (off & 3) == 0 && base_ok) {
                     if (kQuant) {
-                        const float4 f = *reinterpret_cast<const float4*>(xf + off);
-                        px[0] = (uint32_t)quantize_one<false>(f.x, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
-                        px[1] = (uint32_t)quantize_one<false>(f.y, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
-                        px[2] = (uint32_t)quantize_one<false>(f.z, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
-                        px[3] = (uint32_t)quantize_one<false>(f.w, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                        const float4 f = __ldcs(reinterpret_cast<const float4*>(xf + off));
+                        bool general = !qz.dv.fast;  // same arithmetic as quantize_vec16_kernel: division by a constant, add-based rounding
+                        if (!general) {
+                            const float t0 = qdiv_unguarded(f.x, qz.dv, &general), t1 = qdiv_unguarded(f.y, qz.dv, &general);
+                            const float t2 = qdiv_unguarded(f.z, qz.dv, &general), t3 = qdiv_unguarded(f.w, qz.dv, &general);
+                            if (qz.round_mode == 0) {
+                                px[0] = quantize_u8_up_bits(t0, qz.zp_f); px[1] = quantize_u8_up_bits(t1, qz.zp_f);
+                                px[2] = quantize_u8_up_bits(t2, qz.zp_f); px[3] = quantize_u8_up_bits(t3, qz.zp_f);
+                            } else {
+                                px[0] = quantize_u8_rne_bits(t0, qz.zp_f); px[1] = quantize_u8_rne_bits(t1, qz.zp_f);
+                                px[2] = quantize_u8_rne_bits(t2, qz.zp_f); px[3] = quantize_u8_rne_bits(t3, qz.zp_f);
+                            }
+                        }
+                        if (general) {
+                            px[0] = (uint32_t)quantize_one<false>(f.x, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                            px[1] = (uint32_t)quantize_one<false>(f.y, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                            px[2] = (uint32_t)quantize_one<false>(f.z, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                            px[3] = (uint32_t)quantize_one<false>(f.w, qz.scale, qz.zp_f, qz.has_zp != 0, qz.round_mode);
+                        }
                     } else {
                         const uint32_t w4 = *reinterpret_cast<const uint32_t*>(x + off);
                         px[0] = w4 & 0xffu; px[1] = (w4 >> 8) & 0xffu; px[2] = (w4 >> 16) & 0xffu; px[3] = w4 >> 24;
@@ -897,7 +912,7 @@ extern "C" int chxq_quantize_qlinear_conv_packed(
     rc = fill_requant("QuantizeLinear+QLinearConv(packed)", p, g, &epi);
     if (rc != CHXQ_OK) return rc;
     CHXQ_CHECK_ARG(p->x_zero_point >= 0 && p->x_zero_point <= 255 && p->x_scale > 0.f, "QuantizeLinear+QLinearConv(packed): bad activation scale / zero point");
-    const S2dQuant qz{p->x_scale, (float)p->x_zero_point, p->x_zero_point != 0, quant_round_mode};
+    const S2dQuant qz{p->x_scale, (float)p->x_zero_point, p->x_zero_point != 0, quant_round_mode, make_qdiv(p->x_scale)};
     return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, p->x_zero_point, (packed_flags & 2) != 0, epi, y,
                        static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream), &qz);
 }
