@@ -178,10 +178,18 @@ __global__ void __launch_bounds__(256) s2d_repack_kernel(
     const int64_t total = (int64_t)N * rows2 * pairs;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
-    const int b0 = 2 * (int)(idx % pairs);
-    const int64_t q = idx / pairs;
-    const int r = (int)(q % rows2);
-    const int n = (int)(q / rows2);
+    int b0, r, n;
+    if (total < (1ll << 31)) {  // 32-bit index arithmetic where it fits: 64-bit divisions are an order of magnitude dearer
+        unsigned q = (unsigned)idx;
+        b0 = 2 * (int)(q % (unsigned)pairs); q /= (unsigned)pairs;
+        r = (int)(q % (unsigned)rows2);
+        n = (int)(q / (unsigned)rows2);
+    } else {
+        b0 = 2 * (int)(idx % pairs);
+        const int64_t q = idx / pairs;
+        r = (int)(q % rows2);
+        n = (int)(q / rows2);
+    }
     const bool base_ok = (reinterpret_cast<uintptr_t>(xv) & 15u) == 0;
     uint32_t word[2][4] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};
     const int xx0 = 2 * (b0 + t0w);

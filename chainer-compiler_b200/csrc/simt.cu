@@ -304,18 +304,40 @@ __device__ __forceinline__ uint32_t vmax_u8x4(uint32_t a, uint32_t b) {
     return __vmaxu4(a, b);
 }
 
+// Running maximum of packed bytes kept as two words of 16-bit lanes (even bytes, odd bytes): the byte-wise maximum has no
+// native instruction, the 16-bit-pair maximum has.
+struct MaxU8x4 {
+    uint32_t even, odd;
+    __device__ __forceinline__ void init() { even = odd = 0u; }
+    __device__ __forceinline__ void update(uint32_t w) {
+        even = __vmaxu2(even, w & 0x00ff00ffu);
+        odd = __vmaxu2(odd, (w >> 8) & 0x00ff00ffu);
+    }
+    __device__ __forceinline__ uint32_t value() const { return even | (odd << 8); }
+};
+
 __global__ void __launch_bounds__(256) maxpool_u8_nhwc_kernel(
         const uint8_t* __restrict__ x, int N, int H, int W, int C, int k, int s, int p, int Ho, int Wo, uint8_t* __restrict__ y) {
     const int cv = C / 16;
     const int64_t total = (int64_t)N * Ho * Wo * cv;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-        const int c16 = (int)(idx % cv);
-        int64_t r = idx / cv;
-        const int wo = (int)(r % Wo); r /= Wo;
-        const int ho = (int)(r % Ho);
-        const int n = (int)(r / Ho);
-        uint4 best = make_uint4(0u, 0u, 0u, 0u);
+        int c16, wo, ho, n;
+        if (total < (1ll << 31)) {  // 32-bit index arithmetic: a 64-bit division costs an order of magnitude more instructions
+            unsigned r = (unsigned)idx;
+            c16 = (int)(r % (unsigned)cv); r /= (unsigned)cv;
+            wo = (int)(r % (unsigned)Wo); r /= (unsigned)Wo;
+            ho = (int)(r % (unsigned)Ho);
+            n = (int)(r / (unsigned)Ho);
+        } else {
+            c16 = (int)(idx % cv);
+            int64_t r = idx / cv;
+            wo = (int)(r % Wo); r /= Wo;
+            ho = (int)(r % Ho);
+            n = (int)(r / Ho);
+        }
+        MaxU8x4 b0, b1, b2, b3;
+        b0.init(); b1.init(); b2.init(); b3.init();
         for (int kh = 0; kh < k; ++kh) {
             const int hi = ho * s - p + kh;
             if (hi < 0 || hi >= H) continue;
@@ -323,13 +345,10 @@ __global__ void __launch_bounds__(256) maxpool_u8_nhwc_kernel(
                 const int wi = wo * s - p + kw;
                 if (wi < 0 || wi >= W) continue;
                 const uint4 v = *reinterpret_cast<const uint4*>(x + (((int64_t)n * H + hi) * W + wi) * C + c16 * 16);
-                best.x = vmax_u8x4(best.x, v.x);
-                best.y = vmax_u8x4(best.y, v.y);
-                best.z = vmax_u8x4(best.z, v.z);
-                best.w = vmax_u8x4(best.w, v.w);
+                b0.update(v.x); b1.update(v.y); b2.update(v.z); b3.update(v.w);
             }
         }
-        *reinterpret_cast<uint4*>(y + (((int64_t)n * Ho + ho) * Wo + wo) * C + c16 * 16) = best;
+        *reinterpret_cast<uint4*>(y + (((int64_t)n * Ho + ho) * Wo + wo) * C + c16 * 16) = make_uint4(b0.value(), b1.value(), b2.value(), b3.value());
     }
 }
 
