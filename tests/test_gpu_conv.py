@@ -453,3 +453,31 @@ def test_grouped_conv_tensor_core_packed(pkg, ops, orc, dev, N, C, H, W, M, grou
             want = orc.requantize(acc, 0.02, ws_, 0.05, 20, bias=bias, channel_axis=1, fold=fold, clamp_hi_q=200)
             assert np.array_equal(yq.cpu().numpy(), want), (fold, variant)
     assert pkg.lib().chxq_tc_variant(0) == 0
+
+
+def test_quantize_fused_into_stem_conv(pkg, ops, orc, dev):
+    """QuantizeLinear fused into the stem convolution's repack pass equals the two ops in sequence, in both rounding modes and
+    with a zero point; geometries that are not on the space-to-depth path are refused."""
+    from chainer_compiler_b200 import _lib
+    rng = np.random.default_rng(21)
+    xf = rng.uniform(-0.2, 1.2, (3, 3, 30, 26)).astype(np.float32)
+    xf[0, 0, 0, :4] = [0.5 / 255, 1.5 / 255, 2.5 / 255, -1.0]  # exact ties and a negative
+    w = _rand(rng, (32, 3, 7, 7), np.int8)
+    ws = rng.uniform(0.0005, 0.002, 32).astype(np.float32)
+    wz = np.zeros(32, np.int8)
+    bias = _rand(rng, 32, np.int32, -3000, 3000)
+    pk = ops.PackedConv(_t(w, dev), _t(wz, dev), xf.shape, (2, 2), (3, 3), x_layout=_lib.NCHW)
+    xt = _t(xf, dev)
+    for zx, qmode in ((0, 0), (9, 0), (0, 1), (9, 1)):
+        xq = ops.QuantizeLinear(xt, 1 / 255.0, np.uint8(zx), round_mode=qmode)
+        assert np.array_equal(xq.cpu().numpy(), orc.quantize_linear(xf, 1 / 255.0, zx, round_mode=qmode))
+        two = ops.QLinearConvPacked(xq, pk, 1 / 255.0, np.uint8(zx), _t(ws, dev), _t(wz, dev), 0.05, np.uint8(3), b=_t(bias, dev), fold_scales=True)
+        one = ops.QuantizeLinearConvPacked(xt, pk, 1 / 255.0, np.uint8(zx), _t(ws, dev), _t(wz, dev), 0.05, np.uint8(3), b=_t(bias, dev), fold_scales=True,
+                                           quant_round_mode=qmode)
+        ops.device_status()
+        assert torch.equal(one, two), (zx, qmode)
+    w1 = _rand(rng, (32, 16, 1, 1), np.int8)
+    pk1 = ops.PackedConv(_t(w1, dev), _t(wz, dev), (2, 16, 8, 8))
+    with pytest.raises(_lib.ChxqError):
+        ops.QuantizeLinearConvPacked(torch.zeros((2, 16, 8, 8), device=dev).contiguous(memory_format=torch.channels_last), pk1, 0.1, np.uint8(0),
+                                     _t(ws, dev), _t(wz, dev), 0.05, np.uint8(3))
