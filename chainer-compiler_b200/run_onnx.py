@@ -4,17 +4,30 @@ it on the VM ops of this package (reference entry point: tools/run_onnx.cc:289-3
 
     python chainer-compiler_b200/run_onnx.py --test DIR [--quantize] [-d cuda:0] [-I 3] [--rtol 1e-4] [--atol 1e-6]
 
-What runs where: with `--quantize` every Conv (without bias input) and MatMul becomes the dynamic IntegerOps sequence of
-compiler/quantize.cc:142-281 -- ReduceMin / ReduceMax -> scale, zero point -> QuantizeLinear -> ConvInteger / MatMulInteger
--> Cast -> Mul -- and those ops run on this package's kernels (ops.MinMax, ops.QuantizeLinear, ops.ConvInteger,
-ops.MatMulInteger).  The float glue between them (Add, Relu, MaxPool, Reshape, Cast, Mul, ...) is outside the quantized hot
-path and runs as torch tensor expressions on the same device.  Without `--quantize` a float Conv / MatMul has no kernel here
-and is refused, unless `--float_ops_via_torch` asks for the torch expression (useful to check a test directory's expected
-outputs; not a code path of the product).
+What runs where.  QuantizeLinear, DequantizeLinear, QLinearConv, QLinearMatMul, ConvInteger and MatMulInteger nodes of the
+file run on this package's kernels; their scale / zero-point operands may be initializers or graph inputs (one element each,
+read on the host once per call as the reference's GetScalar does, runtime/chxvm_var.cc:70-76).  With `--quantize` every Conv
+without a bias input and every MatMul first becomes the dynamic IntegerOps sequence of compiler/quantize.cc:142-281 --
+ReduceMin / ReduceMax -> scale, zero point -> QuantizeLinear -> ConvInteger / MatMulInteger -> Cast -> Mul.  With
+`--fuse_operations --use_nvrtc` the float Add / Sub / Mul / Tanh / Sigmoid / Exp glue is grouped as the reference groups it
+(compiler/fusion_elementwise.cc:10-40) and every group runs as one generated kernel (ElementWiseNvrtc).  The remaining float
+glue (Relu, MaxPool, Reshape, Cast, BatchNormalization, ...) is outside the quantized hot path and runs as torch tensor
+expressions on the same device.  A float Conv / MatMul / Gemm has no kernel here and is refused, unless
+`--float_ops_via_torch` asks for the torch expression (useful to check a test directory's expected outputs; not a code path of
+the product).
+
+Compile passes, in the reference's order (compiler/passes.cc:121-128): constant folding of Reshape over initializers,
+Quantize, then MergeConvBN (compiler/merge.cc:142-215) over the Conv nodes that are still float.  `--fold_bn_first` swaps the
+last two, so that a Conv + BatchNormalization pair is quantized as one convolution; the bias the merge creates is then added
+in fp32 after the scale-back Mul (the reference leaves a Conv with bias unquantized, compiler/quantize.cc:366-369).
 
 Flags kept from the reference: positional or --test DIR / --onnx FILE, -d/--device, -I/--iterations, --rtol, --atol,
---equal_nan, --no_check_values, --always_show_diff, --check_nans, --check_infs, --dump_outputs_dir, --report_json,
---verbose/-v, --quiet/-q, --quantize, --disable_per_channel_quantize, --compile_only, --dump_chxvm (prints the program)."""
+--equal_nan, --no_check_values, --always_show_diff, --check_nans, --check_infs, --dump_outputs_dir (one
+`<instruction id, 5 digits>_<value name>.npy` per instruction output, runtime/chxvm.cc:70-92), --chrome_tracing FILE (one
+complete event per instruction, runtime/chrome_tracing.cc:39-67), --report_json, --trace/-t, --verbose/-v, --quiet/-q,
+--quantize, --disable_per_channel_quantize, --fuse_operations, --use_nvrtc, --compile_only, --skip_inference, --dump_chxvm,
+--dump_onnx, --out_onnx FILE, --backend (only `chxvm`), --skip_runtime_type_check and --use_cuda (accepted, no effect: there is
+one backend and one device kind)."""
 import argparse
 import json
 import os
@@ -32,7 +45,7 @@ class Inst:
         self.op, self.inputs, self.outputs, self.attrs = op, list(inputs), list(outputs), attrs
 
     def __repr__(self):
-        a = ", ".join("%s=%r" % kv for kv in self.attrs.items() if not isinstance(kv[1], np.ndarray))
+        a = ", ".join("%s=%r" % kv for kv in self.attrs.items() if not isinstance(kv[1], (np.ndarray, list)) or kv[0] in ("strides", "pads", "kernel_shape"))
         return "%s(%s%s) -> (%s)" % (self.op, ", ".join("$" + i for i in self.inputs), (", " + a) if a else "", ", ".join("$" + o for o in self.outputs))
 
 
@@ -41,17 +54,19 @@ class Program:
         self.insts, self.constants, self.inputs, self.outputs = insts, constants, inputs, outputs
 
     def dump(self):
-        return "\n".join(repr(i) for i in self.insts)
+        return "\n".join("%5d: %r" % (pc, i) for pc, i in enumerate(self.insts))
 
 
 def _fold_constants(model):
-    """Reshape / Cast of initializers become initializers (the reference's constant propagation does the same before the
-    weights reach the quantizer)."""
+    """Reshape of initializers becomes an initializer, Constant nodes become initializers (the reference's constant
+    propagation does the same before the weights reach the quantizer)."""
     consts = dict(model.initializers)
     nodes = []
     for n in model.nodes:
         if n.op_type == "Reshape" and all(i in consts for i in n.inputs):
             consts[n.outputs[0]] = consts[n.inputs[0]].reshape([int(d) for d in consts[n.inputs[1]]])
+        elif n.op_type == "Constant" and isinstance(n.attrs.get("value"), np.ndarray):
+            consts[n.outputs[0]] = n.attrs["value"]
         else:
             nodes.append(n)
     return nodes, consts
@@ -64,10 +79,65 @@ def quantize_weight(w, per_channel, to_int8):
     return q, scale.astype(np.float32), zp.astype(q.dtype)
 
 
-def compile_model(model, quantize=False, per_channel=True, asymmetric_input_types=False):
+def merge_conv_bn(nodes, consts, graph_outputs=(), only=None):
+    """MergeConvBN (compiler/merge.cc:142-215): a Conv whose only user is a one-output BatchNormalization with constant
+    scale, bias, mean and variance, and whose own weight (and bias, if any) is constant, becomes one Conv:
+        s = scale / sqrt(var + eps);  W'[m] = W[m] * s[m];  b' = (b - mean) * s + bn_bias      (all fp32)
+    Returns the new node list; the new parameters are added to `consts`.  only: a predicate that selects the Conv nodes the
+    pass may touch."""
+    from chainer_compiler_b200.onnx_io import Node
+    users = {}
+    for n in nodes:
+        for i in n.inputs:
+            users.setdefault(i, []).append(n)
+    out, dropped = [], set()
+    for n in nodes:
+        if id(n) in dropped:
+            continue
+        if n.op_type != "Conv" or n.outputs[0] in graph_outputs or len(users.get(n.outputs[0], [])) != 1 or (only and not only(n)):
+            out.append(n)
+            continue
+        bn = users[n.outputs[0]][0]
+        ok = bn.op_type == "BatchNormalization" and bn.inputs[0] == n.outputs[0] and len(bn.outputs) == 1 and len(bn.inputs) == 5
+        ok = ok and all(v in consts for v in bn.inputs[1:5]) and n.inputs[1] in consts and (len(n.inputs) < 3 or n.inputs[2] in consts)
+        if not ok:
+            out.append(n)
+            continue
+        f32 = np.float32
+        scale, bn_bias, mean, var = (np.asarray(consts[v], f32) for v in bn.inputs[1:5])
+        w = np.asarray(consts[n.inputs[1]], f32)
+        bc = np.asarray(consts[n.inputs[2]], f32) if len(n.inputs) == 3 else np.zeros(scale.shape[0], f32)
+        eps = f32(bn.attrs.get("epsilon", 1e-5))
+        s = (scale / np.sqrt(var + eps)).astype(f32)
+        if w.shape[0] != s.shape[0]:
+            raise ValueError("MergeConvBN: %d output channels but %d batch-norm scales" % (w.shape[0], s.shape[0]))
+        new_w = (w * s.reshape((-1,) + (1,) * (w.ndim - 1))).astype(f32)
+        new_b = ((bc - mean) * s + bn_bias).astype(f32)
+        wn, bname = n.inputs[1] + "@bn", (n.inputs[2] if len(n.inputs) == 3 else bn.inputs[2]) + "@bn"
+        consts[wn], consts[bname] = new_w, new_b
+        out.append(Node("Conv", [n.inputs[0], wn, bname], list(bn.outputs), dict(n.attrs), n.name))
+        dropped.add(id(bn))
+    return [n for n in out if id(n) not in dropped]
+
+
+def compile_model(model, quantize=False, per_channel=True, asymmetric_input_types=False, fold_bn_first=False, fuse=False):
     """ONNX graph -> Program.  quantize: the reference's `--quantize` (dynamic, IntegerOps; weights uint8 unless
-    asymmetric_input_types, which makes them int8: compiler/quantize.cc:392-400)."""
+    asymmetric_input_types, which makes them int8: compiler/quantize.cc:392-400).  fuse: group elementwise float nodes into
+    ElementWiseNvrtc instructions (`--fuse_operations --use_nvrtc`)."""
     nodes, consts = _fold_constants(model)
+
+    def quantizable(n):
+        if n.op_type != "Conv" or n.inputs[1] not in consts:
+            return False
+        # compiler/quantize.cc:366-369 skips a Conv with bias; after --fold_bn_first the merged bias is handled below
+        return len(n.inputs) == 2 or (fold_bn_first and n.inputs[2] in consts)
+
+    if fold_bn_first:
+        nodes = merge_conv_bn(nodes, consts, model.outputs)
+    else:
+        # Quantize runs before MergeConvBN (compiler/passes.cc:121-128): a Conv the quantizer rewrites is no longer a Conv when
+        # the merge pass looks, so only the convolutions that stay float are merged with their BatchNormalization.
+        nodes = merge_conv_bn(nodes, consts, model.outputs, only=lambda n: not (quantize and quantizable(n)))
     insts, tmp = [], [0]
 
     def fresh(base):
@@ -83,7 +153,7 @@ def compile_model(model, quantize=False, per_channel=True, asymmetric_input_type
         return xq, scale, zp
 
     for n in nodes:
-        if quantize and n.op_type == "Conv" and len(n.inputs) == 2 and n.inputs[1] in consts:
+        if quantize and quantizable(n):
             w = consts[n.inputs[1]]
             wq, ws, wz = quantize_weight(w, per_channel, asymmetric_input_types)
             wname, wsn, wzn = fresh("wq"), fresh("wscale"), fresh("wzp")
@@ -94,7 +164,13 @@ def compile_model(model, quantize=False, per_channel=True, asymmetric_input_type
                               group=n.attrs.get("group", 1), auto_pad=n.attrs.get("auto_pad", "NOTSET"), dilations=n.attrs.get("dilations", [])))
             insts.append(Inst("Cast", [acc], [accf], to="float32"))
             insts.append(Inst("ScaleProduct", [xs, wsn], [mul], shape=[-1] + [1] * (w.ndim - 2) if ws.size > 1 else []))
-            insts.append(Inst("Mul", [accf, mul], [n.outputs[0]]))
+            if len(n.inputs) == 3:
+                scaled, bname = fresh("scaled"), fresh("bias")
+                consts[bname] = np.asarray(consts[n.inputs[2]], np.float32).reshape([1, -1] + [1] * (w.ndim - 2))
+                insts.append(Inst("Mul", [accf, mul], [scaled]))
+                insts.append(Inst("Add", [scaled, bname], [n.outputs[0]]))
+            else:
+                insts.append(Inst("Mul", [accf, mul], [n.outputs[0]]))
         elif quantize and n.op_type == "MatMul":
             a, b = n.inputs
             if b in consts:
@@ -116,7 +192,140 @@ def compile_model(model, quantize=False, per_channel=True, asymmetric_input_type
             insts.append(Inst("Mul", [accf, mul], [n.outputs[0]]))
         else:
             insts.append(Inst(n.op_type, n.inputs, n.outputs, **n.attrs))
-    return Program(insts, consts, list(model.inputs), list(model.outputs))
+    program = Program(insts, consts, list(model.inputs), list(model.outputs))
+    if fuse:
+        program = fuse_elementwise(program)
+    return program
+
+
+# ---- elementwise fusion over a program -----------------------------------------------------------------------------------
+_NP_NAME = {np.dtype(np.float32): "float32", np.dtype(np.float64): "float64", np.dtype(np.float16): "float16", np.dtype(np.int8): "int8",
+            np.dtype(np.uint8): "uint8", np.dtype(np.int32): "int32", np.dtype(np.int64): "int64", np.dtype(np.bool_): "bool", np.dtype(np.int16): "int16"}
+_ONNX_TO_NAME = {1: "float32", 2: "uint8", 3: "int8", 5: "int16", 6: "int32", 7: "int64", 9: "bool", 10: "float16", 11: "float64"}
+
+
+def infer_dtypes(program):
+    """Value name -> dtype name, by the ops' typing rules (inputs of unknown dtype are taken as float32)."""
+    dt = {k: _NP_NAME.get(np.asarray(v).dtype) for k, v in program.constants.items()}
+    for k in program.inputs:
+        dt.setdefault(k, "float32")
+    for inst in program.insts:
+        first = dt.get(inst.inputs[0], "float32") if inst.inputs else "float32"
+        if inst.op == "QuantizeLinear":
+            o = [dt.get(inst.inputs[2], "uint8") if len(inst.inputs) > 2 else "uint8"]
+        elif inst.op in ("ConvInteger", "MatMulInteger"):
+            o = ["int32"]
+        elif inst.op in ("QLinearConv", "QLinearMatMul"):
+            o = [dt.get(inst.inputs[7], "uint8")]
+        elif inst.op == "DequantizeLinear":
+            o = ["float32"]
+        elif inst.op == "Cast":
+            to = inst.attrs.get("to", 1)
+            o = [to if isinstance(to, str) else _ONNX_TO_NAME.get(int(to), "float32")]
+        elif inst.op == "DynamicQuantParamsU8":
+            o = ["float32", "uint8"]
+        elif inst.op == "Shape":
+            o = ["int64"]
+        else:
+            o = [first] * len(inst.outputs)
+        for name, d in zip(inst.outputs, o):
+            dt[name] = d
+    return dt
+
+
+def fuse_elementwise(program):
+    """`--fuse_operations --use_nvrtc`: the reference's grouping (compiler/fusion_elementwise.cc:10-40 over
+    compiler/fusion.cc:165-214, here chxq_fuse_elementwise) decides the groups; each becomes one ElementWiseNvrtc instruction
+    whose `code` attribute is the generated kernel source (compiler/nvrtc_builder.cc:91-206, here chxq_eltwise_codegen).  The
+    member nodes stay in the `members` attribute (a CPU evaluation runs them one by one, as the reference's CPU path does:
+    compiler/chxvm/emitter.cc:702-726)."""
+    from chainer_compiler_b200 import fusion
+    dt = infer_dtypes(program)
+    nodes = [fusion.Node(i.op, list(i.inputs), list(i.outputs)) for i in program.insts]
+    groups = fusion.fuse_elementwise(nodes, dt, program.outputs)
+    if not groups:
+        return program
+    member_of = {}
+    for g in groups:
+        for idx in g.node_indices:
+            member_of[idx] = g
+    insts, emitted = [], set()
+    for idx, inst in enumerate(program.insts):
+        g = member_of.get(idx)
+        if g is None:
+            insts.append(inst)
+        elif g.fusion_id not in emitted and idx == max(g.node_indices):
+            emitted.add(g.fusion_id)
+            members = [nodes[k] for k in g.node_indices]
+            code = fusion.build_program(members, g.fusion_id, g.inputs, g.outputs, dt.get(g.outputs[0]) or "float32")
+            insts.append(Inst("ElementWiseNvrtc", g.inputs, g.outputs, num_outputs=len(g.outputs), code=code, fusion_id=g.fusion_id,
+                              members=[(m.op_type, list(m.inputs), list(m.outputs)) for m in members]))
+    return Program(_topological(insts, set(program.constants) | set(program.inputs)), program.constants, program.inputs, program.outputs)
+
+
+def _topological(insts, available):
+    """Stable topological order: a fused group sits where its last member was, which can be after a reader of one of its
+    earlier outputs."""
+    done, out, rest = set(available), [], list(insts)
+    while rest:
+        progressed = False
+        for k, inst in enumerate(rest):
+            if all(i in done or i == "" for i in inst.inputs):
+                out.append(inst)
+                done.update(inst.outputs)
+                del rest[k]
+                progressed = True
+                break
+        if not progressed:
+            raise ValueError("program has a cycle or reads an undefined value: %r" % rest[0])
+    return out
+
+
+# ---- ONNX export of a program ----------------------------------------------------------------------------------------------
+def program_to_onnx(program, name="graph"):
+    """The program as an ONNX graph of standard nodes (`--out_onnx`): the dynamic-quantization helper instructions are written
+    out as the node sequences compiler/quantize.cc:172-207,232-244 emits (ReduceMin, ReduceMax, Sub, Div, Floor, Cast, Mul,
+    Reshape); fused groups are written as their member nodes."""
+    from chainer_compiler_b200 import onnx_io
+    consts = dict(program.constants)
+    nodes = []
+    N = onnx_io.Node
+    code_of = {"float32": onnx_io.FLOAT, "uint8": onnx_io.UINT8, "int8": onnx_io.INT8, "int32": onnx_io.INT32, "int64": onnx_io.INT64,
+               "float16": onnx_io.FLOAT16, "float64": onnx_io.DOUBLE, "bool": onnx_io.BOOL, "int16": onnx_io.INT16}
+    for pc, i in enumerate(program.insts):
+        t = lambda s: "%s@x%d" % (s, pc)  # noqa: E731
+        if i.op == "ReduceMinMax":
+            nodes.append(N("ReduceMin", i.inputs, [i.outputs[0]], {"keepdims": 0}))
+            nodes.append(N("ReduceMax", i.inputs, [i.outputs[1]], {"keepdims": 0}))
+        elif i.op == "DynamicQuantParamsU8":
+            consts[t("qrange")], consts[t("zero")] = np.float32(255.0).reshape(()), np.float32(0.0).reshape(())
+            nodes.append(N("Sub", [i.inputs[1], i.inputs[0]], [t("span")], {}))
+            nodes.append(N("Div", [t("span"), t("qrange")], [i.outputs[0]], {}))
+            nodes.append(N("Sub", [t("zero"), i.inputs[0]], [t("zsub")], {}))
+            nodes.append(N("Div", [t("zsub"), i.outputs[0]], [t("zdiv")], {}))
+            nodes.append(N("Floor", [t("zdiv")], [t("zfloor")], {}))
+            nodes.append(N("Cast", [t("zfloor")], [i.outputs[1]], {"to": onnx_io.UINT8}))
+        elif i.op == "ScaleProduct":
+            if i.attrs.get("shape"):
+                consts[t("shape")] = np.asarray(i.attrs["shape"], np.int64)
+                nodes.append(N("Mul", i.inputs, [t("prod")], {}))
+                nodes.append(N("Reshape", [t("prod"), t("shape")], i.outputs, {}))
+            else:
+                nodes.append(N("Mul", i.inputs, i.outputs, {}))
+        elif i.op == "ElementWiseNvrtc":
+            for op, ins, outs in i.attrs["members"]:
+                nodes.append(N(op, ins, outs, {}))
+        elif i.op == "Cast":
+            to = i.attrs.get("to", 1)
+            nodes.append(N("Cast", i.inputs, i.outputs, {"to": code_of[to] if isinstance(to, str) else int(to)}))
+        else:
+            attrs = {k: v for k, v in i.attrs.items() if v is not None and not (isinstance(v, (list, tuple)) and len(v) == 0)}
+            if attrs.get("auto_pad") == "NOTSET":
+                del attrs["auto_pad"]
+            nodes.append(N(i.op, i.inputs, i.outputs, attrs))
+    used = {v for n in nodes for v in n.inputs}
+    inits = {k: np.asarray(v) for k, v in consts.items() if k in used}
+    return onnx_io.Model(nodes, inits, list(program.inputs), list(program.outputs), name=name)
 
 
 # ---- execution -------------------------------------------------------------------------------------------------------
@@ -135,6 +344,29 @@ def _pool_pads(attrs, ndim):
     return pads
 
 
+def _contiguous(v):
+    v = np.asarray(v)
+    return np.ascontiguousarray(v).reshape(v.shape)  # ascontiguousarray alone turns a 0-d array into a 1-d one
+
+
+class ChromeTracing:
+    """One complete ("ph":"X") event per executed instruction with category, name, start and duration in microseconds and the
+    program counter, in the layout runtime/chrome_tracing.cc:39-67 writes.  The executor synchronizes the device after each
+    traced instruction, so a duration covers the kernels the instruction launched."""
+
+    def __init__(self):
+        self.base = time.perf_counter()
+        self.events = []
+
+    def add(self, category, name, pc, start, end):
+        self.events.append({"cat": category, "name": name, "ts": int((start - self.base) * 1e6), "dur": int((end - start) * 1e6), "tid": 1, "pid": 1,
+                            "args": {"pc": pc}, "ph": "X"})
+
+    def emit(self, path):
+        with open(path, "w") as f:
+            f.write("[\n" + ",\n".join(json.dumps(e, separators=(",", ":")) for e in self.events) + "]\n")
+
+
 class Executor:
     """Runs a Program on one CUDA device.  Quantized ops go through chainer_compiler_b200.ops; glue ops are torch expressions."""
 
@@ -151,91 +383,150 @@ class Executor:
         self.device = torch.device(device if ":" in str(device) else "cuda:0")
         self.consts = {}
         for k, v in program.constants.items():
-            self.consts[k] = torch.from_numpy(np.ascontiguousarray(v)).to(self.device)
+            self.consts[k] = torch.from_numpy(_contiguous(v)).to(self.device)
         self.host_consts = program.constants
 
-    def run(self, inputs, trace=None):
+    def _scalar(self, name, env, host):
+        """A Scalar operand on the host, keeping its dtype (the zero point's dtype selects the output dtype)."""
+        if name in host:
+            return host[name]
+        if name in self.host_consts:
+            v = np.asarray(self.host_consts[name])
+        else:
+            v = env[name].cpu().numpy()  # the device-to-host read of runtime/chxvm_var.cc:70-76
+        if v.size != 1:
+            raise ValueError("run_onnx: %s must have one element, has shape %s" % (name, v.shape))
+        return v.reshape(())[()]
+
+    def run(self, inputs, trace=None, tracer=None, log=None):
+        """trace: a dict that receives every instruction output; tracer: a ChromeTracing; log: a file the instructions are
+        printed to as they run (`--trace`)."""
         t, ops = self.torch, self.ops
         env = dict(self.consts)
         host = {}  # host-side scalars (dynamic quantization parameters)
         for k, v in inputs.items():
-            env[k] = t.from_numpy(np.ascontiguousarray(v)).to(self.device)
-        for inst in self.program.insts:
-            a = inst.attrs
-            x = [env.get(i) if i in env else host.get(i) for i in inst.inputs]
-            op = inst.op
-            if op == "ReduceMinMax":
-                mm = ops.MinMax(x[0].contiguous()).cpu().numpy()  # the device-to-host read the reference does per scalar argument
-                host[inst.outputs[0]], host[inst.outputs[1]] = np.float32(mm[0]), np.float32(mm[1])
-            elif op == "DynamicQuantParamsU8":
-                host[inst.outputs[0]], host[inst.outputs[1]] = dynamic_params_u8(host[inst.inputs[0]], host[inst.inputs[1]])
-            elif op == "QuantizeLinear":
-                env[inst.outputs[0]] = ops.QuantizeLinear(x[0].contiguous(), host[inst.inputs[1]], host[inst.inputs[2]])
-            elif op == "ConvInteger":
-                if any(d != 1 for d in a.get("dilations", [])):
-                    raise NotImplementedError("ConvInteger: dilation must be 1 (compiler/chxvm/simple_node_emitter.cc:655)")
-                zx = host[inst.inputs[2]]
-                auto_pad = a.get("auto_pad", "NOTSET")
-                env[inst.outputs[0]] = ops.ConvInteger(x[0], x[1], zx, x[3], tuple(a.get("strides", [])), self._sym_pads(a.get("pads", [])), a.get("group", 1),
-                                                       "" if auto_pad == "NOTSET" else auto_pad)
-            elif op == "MatMulInteger":
-                za = x[2] if inst.inputs[2] in env else t.tensor([int(host[inst.inputs[2]])], dtype=t.uint8, device=self.device)
-                zb = x[3] if inst.inputs[3] in env else t.tensor([int(host[inst.inputs[3]])], dtype=t.uint8, device=self.device)
-                env[inst.outputs[0]] = ops.MatMulInteger(x[0].contiguous(), x[1].contiguous(), za, zb)
-            elif op == "ScaleProduct":
-                s0 = x[0] if inst.inputs[0] in env else t.tensor(float(host[inst.inputs[0]]), dtype=t.float32, device=self.device)
-                s1 = x[1] if inst.inputs[1] in env else t.tensor(float(host[inst.inputs[1]]), dtype=t.float32, device=self.device)
-                m = s0 * s1
-                env[inst.outputs[0]] = m.reshape(a["shape"]) if a.get("shape") else m
-            elif op == "Cast":
-                env[inst.outputs[0]] = x[0].to(getattr(t, a["to"]) if isinstance(a["to"], str) else t.float32)
-            elif op in ("Add", "Sub", "Mul", "Div"):
-                f = {"Add": t.add, "Sub": t.sub, "Mul": t.mul, "Div": t.div}[op]
-                env[inst.outputs[0]] = f(x[0], x[1])
-            elif op == "Relu":
-                env[inst.outputs[0]] = t.relu(x[0])
-            elif op == "Reshape":
-                shape = [int(d) for d in self.host_consts[inst.inputs[1]]] if inst.inputs[1] in self.host_consts else [int(d) for d in x[1].cpu()]
-                shape = [x[0].shape[i] if d == 0 else d for i, d in enumerate(shape)]
-                env[inst.outputs[0]] = x[0].reshape(shape)
-            elif op == "MaxPool":
-                k, s = a["kernel_shape"], a.get("strides", [1] * len(a["kernel_shape"]))
-                p = _pool_pads(a, len(k))
-                if any(p[i] != p[i + len(k)] for i in range(len(k))):
-                    raise NotImplementedError("MaxPool: asymmetric pads")
-                env[inst.outputs[0]] = t.nn.functional.max_pool2d(x[0], k, s, p[:len(k)])
-            elif op == "Flatten":
-                ax = a.get("axis", 1)
-                env[inst.outputs[0]] = x[0].reshape(int(np.prod(x[0].shape[:ax])), -1)
-            elif op in ("Conv", "MatMul", "Gemm"):
-                if not self.float_ok:
-                    raise SystemExit("run_onnx: float %s has no kernel in this package; run with --quantize (or --float_ops_via_torch to "
-                                     "evaluate it as a torch expression outside the product path)" % op)
-                if op == "Conv":
-                    auto_pad = a.get("auto_pad", "NOTSET")
-                    pads = self._sym_pads(a.get("pads", []))
-                    xin = x[0]
-                    if auto_pad == "SAME_UPPER":
-                        from chainer_compiler_b200.ops import conv_geometry_from_shapes  # the library's geometry rule
-                        g = conv_geometry_from_shapes(tuple(xin.shape), 6, tuple(x[1].shape), 2, tuple(a.get("strides", [])), (), a.get("group", 1), "SAME_UPPER")
-                        xin = t.nn.functional.pad(xin, (g.pad_left, g.pad_right, g.pad_top, g.pad_bottom))
-                        pads = (0, 0)
-                    env[inst.outputs[0]] = t.nn.functional.conv2d(xin, x[1], x[2] if len(x) > 2 else None, tuple(a.get("strides", [1, 1])), pads or 0, 1,
-                                                                  a.get("group", 1))
-                elif op == "MatMul":
-                    env[inst.outputs[0]] = x[0] @ x[1]
-                else:
-                    A = x[0].t() if a.get("transA", 0) else x[0]
-                    B = x[1].t() if a.get("transB", 0) else x[1]
-                    y = a.get("alpha", 1.0) * (A @ B)
-                    env[inst.outputs[0]] = y + a.get("beta", 1.0) * x[2] if len(x) > 2 else y
-            else:
-                raise NotImplementedError("run_onnx: op %s" % op)
+            env[k] = t.from_numpy(_contiguous(v)).to(self.device)
+        for pc, inst in enumerate(self.program.insts):
+            if log is not None:
+                log.write("%5d: %r\n" % (pc, inst))
+            if tracer is not None:
+                t.cuda.synchronize(self.device)
+                t0 = time.perf_counter()
+            self._step(inst, env, host)
+            if tracer is not None:
+                t.cuda.synchronize(self.device)
+                tracer.add("ChxVM", inst.op, pc, t0, time.perf_counter())
             if trace is not None:
                 for o in inst.outputs:
                     trace[o] = env[o] if o in env else host[o]
         ops.device_status()
         return [(o, env[o]) for o in self.program.outputs]
+
+    def _step(self, inst, env, host):
+        t, ops = self.torch, self.ops
+        a, op = inst.attrs, inst.op
+        x = [env.get(i) if i in env else host.get(i) for i in inst.inputs]
+        sc = lambda k: self._scalar(inst.inputs[k], env, host)  # noqa: E731
+        has = lambda k: len(inst.inputs) > k and inst.inputs[k] != ""  # noqa: E731
+        out = inst.outputs[0]
+        auto_pad = a.get("auto_pad", "NOTSET")
+        auto_pad = "" if auto_pad == "NOTSET" else auto_pad
+        if op == "ReduceMinMax":
+            mm = ops.MinMax(x[0].contiguous()).cpu().numpy()  # the device-to-host read the reference does per scalar argument
+            host[inst.outputs[0]], host[inst.outputs[1]] = np.float32(mm[0]), np.float32(mm[1])
+        elif op == "DynamicQuantParamsU8":
+            host[inst.outputs[0]], host[inst.outputs[1]] = dynamic_params_u8(host[inst.inputs[0]], host[inst.inputs[1]])
+        elif op == "QuantizeLinear":
+            env[out] = ops.QuantizeLinear(x[0].contiguous(), sc(1), sc(2) if has(2) else None)
+        elif op == "DequantizeLinear":
+            env[out] = ops.DequantizeLinear(x[0].contiguous(), sc(1), sc(2) if has(2) else None)
+        elif op in ("ConvInteger", "QLinearConv"):
+            if any(d != 1 for d in a.get("dilations", [])):
+                raise NotImplementedError("%s: dilation must be 1 (compiler/chxvm/simple_node_emitter.cc:655)" % op)
+            strides, pads, group = tuple(a.get("strides", [])), self._sym_pads(a.get("pads", [])), a.get("group", 1)
+            if op == "ConvInteger":
+                env[out] = ops.ConvInteger(x[0], x[1], sc(2) if has(2) else None, x[3] if has(3) else None, strides, pads, group, auto_pad)
+            else:
+                env[out] = ops.QLinearConv(x[0], sc(1), sc(2), x[3], x[4], x[5], sc(6), sc(7), x[8] if has(8) else None, strides, pads, group, auto_pad)
+        elif op == "MatMulInteger":
+            def zp_arr(k, like):
+                if not has(k):
+                    return None
+                if inst.inputs[k] in env:
+                    return env[inst.inputs[k]]
+                return t.tensor([int(host[inst.inputs[k]])], dtype=like.dtype, device=self.device)
+            env[out] = ops.MatMulInteger(x[0].contiguous(), x[1].contiguous(), zp_arr(2, x[0]), zp_arr(3, x[1]))
+        elif op == "QLinearMatMul":
+            env[out] = ops.QLinearMatMul(x[0].contiguous(), sc(1), sc(2), x[3].contiguous(), sc(4), sc(5), sc(6), sc(7))
+        elif op == "ElementWiseNvrtc":
+            outs = ops.ElementWiseNvrtc(x, a["num_outputs"], a["code"], a["fusion_id"])
+            for name, y in zip(inst.outputs, outs):
+                env[name] = y
+        elif op == "ScaleProduct":
+            s0 = x[0] if inst.inputs[0] in env else t.tensor(float(host[inst.inputs[0]]), dtype=t.float32, device=self.device)
+            s1 = x[1] if inst.inputs[1] in env else t.tensor(float(host[inst.inputs[1]]), dtype=t.float32, device=self.device)
+            m = s0 * s1
+            env[out] = m.reshape(a["shape"]) if a.get("shape") else m
+        elif op == "Cast":
+            to = a.get("to", 1)
+            env[out] = x[0].to(getattr(t, to if isinstance(to, str) else _ONNX_TO_NAME[int(to)]))
+        elif op in ("Add", "Sub", "Mul", "Div", "Max", "Min"):
+            f = {"Add": t.add, "Sub": t.sub, "Mul": t.mul, "Div": t.div, "Max": t.maximum, "Min": t.minimum}[op]
+            env[out] = f(x[0], x[1])
+        elif op in ("Relu", "Tanh", "Sigmoid", "Exp", "Floor", "Abs", "Identity"):
+            f = {"Relu": t.relu, "Tanh": t.tanh, "Sigmoid": t.sigmoid, "Exp": t.exp, "Floor": t.floor, "Abs": t.abs, "Identity": lambda v: v}[op]
+            env[out] = f(x[0])
+        elif op in ("ReduceMin", "ReduceMax"):
+            if a.get("axes"):
+                raise NotImplementedError("%s over chosen axes" % op)
+            mm = ops.MinMax(x[0].contiguous())
+            y = mm[0] if op == "ReduceMin" else mm[1]
+            env[out] = y.reshape(()) if not a.get("keepdims", 1) else y.reshape([1] * x[0].dim())
+        elif op == "Clip":
+            lo = a.get("min", float(sc(1)) if has(1) else None)
+            hi = a.get("max", float(sc(2)) if has(2) else None)
+            env[out] = t.clamp(x[0], lo, hi)
+        elif op == "BatchNormalization":
+            shape = [1, -1] + [1] * (x[0].dim() - 2)
+            eps = np.float32(a.get("epsilon", 1e-5))
+            env[out] = (x[0] - x[3].reshape(shape)) / t.sqrt(x[4].reshape(shape) + float(eps)) * x[1].reshape(shape) + x[2].reshape(shape)
+        elif op == "Reshape":
+            shape = [int(d) for d in self.host_consts[inst.inputs[1]]] if inst.inputs[1] in self.host_consts else [int(d) for d in x[1].cpu()]
+            shape = [x[0].shape[i] if d == 0 else d for i, d in enumerate(shape)]
+            env[out] = x[0].reshape(shape)
+        elif op == "MaxPool":
+            k, s = a["kernel_shape"], a.get("strides", [1] * len(a["kernel_shape"]))
+            p = _pool_pads(a, len(k))
+            if any(p[i] != p[i + len(k)] for i in range(len(k))):
+                raise NotImplementedError("MaxPool: asymmetric pads")
+            env[out] = t.nn.functional.max_pool2d(x[0], k, s, p[:len(k)])
+        elif op == "GlobalAveragePool":
+            env[out] = x[0].mean(dim=tuple(range(2, x[0].dim())), keepdim=True)
+        elif op == "Flatten":
+            ax = a.get("axis", 1)
+            env[out] = x[0].reshape(int(np.prod(x[0].shape[:ax])), -1)
+        elif op in ("Conv", "MatMul", "Gemm"):
+            if not self.float_ok:
+                raise SystemExit("run_onnx: float %s has no kernel in this package; run with --quantize (or --float_ops_via_torch to "
+                                 "evaluate it as a torch expression outside the product path)" % op)
+            if op == "Conv":
+                pads = self._sym_pads(a.get("pads", []))
+                xin = x[0]
+                if auto_pad == "SAME_UPPER":
+                    from chainer_compiler_b200.ops import conv_geometry_from_shapes  # the library's geometry rule
+                    g = conv_geometry_from_shapes(tuple(xin.shape), 6, tuple(x[1].shape), 2, tuple(a.get("strides", [])), (), a.get("group", 1), "SAME_UPPER")
+                    xin = t.nn.functional.pad(xin, (g.pad_left, g.pad_right, g.pad_top, g.pad_bottom))
+                    pads = (0, 0)
+                env[out] = t.nn.functional.conv2d(xin, x[1], x[2] if len(x) > 2 else None, tuple(a.get("strides", [1, 1])), pads or 0, 1, a.get("group", 1))
+            elif op == "MatMul":
+                env[out] = x[0] @ x[1]
+            else:
+                A = x[0].t() if a.get("transA", 0) else x[0]
+                B = x[1].t() if a.get("transB", 0) else x[1]
+                y = a.get("alpha", 1.0) * (A @ B)
+                env[out] = y + a.get("beta", 1.0) * x[2] if len(x) > 2 else y
+        else:
+            raise NotImplementedError("run_onnx: op %s" % op)
 
     @staticmethod
     def _sym_pads(pads):
@@ -264,15 +555,30 @@ def parse_args(argv):
     ap.add_argument("--check_nans", action="store_true")
     ap.add_argument("--check_infs", action="store_true")
     ap.add_argument("--dump_outputs_dir")
+    ap.add_argument("--chrome_tracing")
     ap.add_argument("--report_json")
     ap.add_argument("--compile_only", action="store_true")
+    ap.add_argument("--skip_inference", action="store_true")
     ap.add_argument("--dump_chxvm", action="store_true")
+    ap.add_argument("--dump_onnx", action="store_true")
+    ap.add_argument("--out_onnx")
     ap.add_argument("--quantize", action="store_true")
     ap.add_argument("--disable_per_channel_quantize", action="store_true")
+    ap.add_argument("--fold_bn_first", action="store_true")
+    ap.add_argument("--fuse_operations", action="store_true")
+    ap.add_argument("--use_nvrtc", action="store_true")
+    ap.add_argument("--use_cuda", action="store_true")
+    ap.add_argument("--skip_runtime_type_check", action="store_true")
+    ap.add_argument("--backend", default="chxvm")
     ap.add_argument("--float_ops_via_torch", action="store_true")
+    ap.add_argument("-t", "--trace", action="store_true")
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("-q", "--quiet", action="store_true")
     return ap.parse_args(argv)
+
+
+def _file_name(value_name):
+    return value_name.replace("/", "_").replace(os.sep, "_")
 
 
 def run_onnx(argv):
@@ -282,6 +588,8 @@ def run_onnx(argv):
     entry.load_package()
     from chainer_compiler_b200 import onnx_io
     args = parse_args(argv)
+    if args.backend != "chxvm":
+        raise SystemExit("run_onnx: unknown backend %r (this package has the chxvm backend only)" % args.backend)
     target = args.test or args.onnx or args.positional
     if not target:
         raise SystemExit("run_onnx: give a test directory or an .onnx file")
@@ -289,28 +597,41 @@ def run_onnx(argv):
         model, cases = onnx_io.load_test_dir(target)
     else:
         model, cases = onnx_io.load_model(target), []
-    program = compile_model(model, quantize=args.quantize, per_channel=not args.disable_per_channel_quantize)
+    unfused = compile_model(model, quantize=args.quantize, per_channel=not args.disable_per_channel_quantize, fold_bn_first=args.fold_bn_first)
+    # the reference fuses for NVRTC only when both flags are given (compiler/passes.cc: fusion needs a code generator)
+    program = fuse_elementwise(unfused) if (args.fuse_operations and args.use_nvrtc) else unfused
+    if args.dump_onnx or args.out_onnx:
+        exported = program_to_onnx(unfused, model.name)
+        if args.dump_onnx:
+            sys.stderr.write("=== vvv after simplification vvv ===\n%s\n=== ^^^ after simplification ^^^ ===\n" % "\n".join(repr(n) for n in exported.nodes))
+        if args.out_onnx:
+            with open(args.out_onnx, "wb") as f:
+                f.write(onnx_io.serialize_model(exported))
     if args.dump_chxvm:
         print(program.dump())
-    if args.compile_only:
+    if args.compile_only or args.skip_inference:
         return 0
     import torch
     ex = Executor(program, args.device, args.float_ops_via_torch)
+    tracer = ChromeTracing() if args.chrome_tracing else None
     failures, elapsed, report = 0, [], []
     for ci, (ins, expected) in enumerate(cases):
-        outs = None
+        outs, values = None, ({} if args.dump_outputs_dir else None)
         for it in range(max(1, args.iterations)):
             torch.cuda.synchronize(ex.device)
             t0 = time.perf_counter()
-            outs = ex.run(ins)
+            outs = ex.run(ins, trace=values, tracer=tracer, log=sys.stderr if args.trace else None)
             torch.cuda.synchronize(ex.device)
             if it > 0 or args.iterations == 1:  # the first iteration is discarded when there are several (tools/run_onnx.cc:468-469)
                 elapsed.append(time.perf_counter() - t0)
         got = {k: v.detach().cpu().numpy() for k, v in outs}
         if args.dump_outputs_dir:
             os.makedirs(args.dump_outputs_dir, exist_ok=True)
-            for k, v in got.items():
-                np.save(os.path.join(args.dump_outputs_dir, "%d_%s.npy" % (ci, k.replace("/", "_"))), v)
+            for pc, inst in enumerate(program.insts):
+                for o in inst.outputs:
+                    v = values.get(o)
+                    if v is not None and o:
+                        np.save(os.path.join(args.dump_outputs_dir, "%05d_%s.npy" % (pc, _file_name(o))), v.detach().cpu().numpy() if hasattr(v, "detach") else np.asarray(v))
         for name, want in expected:
             y = got.get(name)
             ok = y is not None and y.shape == want.shape
@@ -322,12 +643,14 @@ def run_onnx(argv):
                 ok = bool(np.allclose(y, want, rtol=args.rtol, atol=args.atol, equal_nan=args.equal_nan))
             if (not ok or args.always_show_diff) and not args.quiet and y is not None and y.shape == want.shape:
                 d = np.abs(y.astype(np.float64) - want.astype(np.float64))
-                print("case %d output %s: max abs diff %.6g, max rel diff %.6g" % (ci, name, d.max(), (d / np.maximum(np.abs(want), 1e-30)).max()))
+                print("case %d output %s: max abs diff %.6g, max rel diff %.6g" % (ci, name, d.max(), (d / np.maximum(np.abs(want.astype(np.float64)), 1e-30)).max()))
             if not ok:
                 failures += 1
             report.append({"case": ci, "output": name, "ok": bool(ok)})
         if args.verbose and not args.quiet:
             print("case %d: %s" % (ci, {k: v.shape for k, v in got.items()}))
+    if tracer is not None:
+        tracer.emit(args.chrome_tracing)
     if not cases and not args.quiet:
         print("run_onnx: model compiled (%d instructions); no test data to run" % len(program.insts))
     avg_ms = 1000.0 * float(np.mean(elapsed)) if elapsed else 0.0

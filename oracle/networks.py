@@ -93,6 +93,21 @@ def mobilenetv2_forward(params, x, mode="exact", taps=None):
     return orc.linear_f32(pooled, params["fc_w"], params["fc_b"])
 
 
+def _f32(v):
+    return np.float32(np.asarray(v).reshape(()))
+
+
+def _sigmoid(v):
+    # 1 / (1 + exp(-x)); the reference's generated kernel writes tanh(x / 2) / 2 + 1 / 2 (compiler/nvrtc_builder.cc:133-136), the
+    # same function within 1e-5 relative
+    one = np.float32(1.0)
+    return one / (one + np.exp(-v))
+
+
+_ONNX_DTYPE = {1: np.float32, 2: np.uint8, 3: np.int8, 5: np.int16, 6: np.int32, 7: np.int64, 9: np.bool_, 10: np.float16, 11: np.float64}
+_EW = {"Add": np.add, "Sub": np.subtract, "Mul": np.multiply, "Tanh": np.tanh, "Sigmoid": _sigmoid, "Exp": np.exp, "Identity": lambda v: v}
+
+
 def run_program(program, inputs, trace=None):
     """CPU evaluation of a `run_onnx` program (the instruction list `chainer-compiler_b200/run_onnx.py::compile_model`
     produces) with the oracle's ops: the checker for the quantized graph the reference's `--quantize` pass builds
@@ -109,19 +124,53 @@ def run_program(program, inputs, trace=None):
             scale = np.float32((rmax - rmin) / np.float32(255.0)) if rmax != rmin else np.float32(1.0)
             out = [scale, np.uint8(int(np.clip(np.floor(np.float32((np.float32(0.0) - rmin) / scale)), 0, 255)))]
         elif op == "QuantizeLinear":
-            out = [orc.quantize_linear(x[0], x[1], int(x[2]), out_dtype=np.asarray(x[2]).dtype)]
-        elif op == "ConvInteger":
+            zp = np.asarray(x[2]).reshape(()) if len(x) > 2 else np.uint8(0)
+            out = [orc.quantize_linear(x[0], _f32(x[1]), int(zp), out_dtype=zp.dtype)]
+        elif op == "DequantizeLinear":
+            out = [orc.dequantize_linear(x[0], _f32(x[1]), int(np.asarray(x[2]).reshape(())) if len(x) > 2 else 0)]
+        elif op in ("ConvInteger", "QLinearConv"):
             auto_pad = a.get("auto_pad", "NOTSET")
+            auto_pad = "" if auto_pad == "NOTSET" else auto_pad
             pads = list(a.get("pads", []))
-            out = [orc.conv_integer(x[0], x[1], int(x[2]), np.asarray(x[3]).astype(np.int32), tuple(a.get("strides", [])), tuple(pads[:len(pads) // 2]),
-                                    a.get("group", 1), "" if auto_pad == "NOTSET" else auto_pad)]
+            strides, pads, group = tuple(a.get("strides", [])), tuple(pads[:len(pads) // 2]), a.get("group", 1)
+            if op == "ConvInteger":
+                zx = int(np.asarray(x[2]).reshape(())) if len(x) > 2 else None
+                zw = np.asarray(x[3]).astype(np.int32) if len(x) > 3 else None
+                out = [orc.conv_integer(x[0], x[1], zx, zw, strides, pads, group, auto_pad)]
+            else:
+                zy = np.asarray(x[7]).reshape(())
+                out = [orc.qlinear_conv(x[0], _f32(x[1]), int(np.asarray(x[2]).reshape(())), x[3], np.asarray(x[4], np.float32), np.asarray(x[5]),
+                                        _f32(x[6]), zy[()], x[8] if len(x) > 8 else None, strides, pads, group, auto_pad)]
         elif op == "MatMulInteger":
-            out = [orc.matmul_integer(x[0], x[1], np.asarray(x[2]).reshape(-1), np.asarray(x[3]).reshape(-1))]
+            out = [orc.matmul_integer(x[0], x[1], np.asarray(x[2]).reshape(-1) if len(x) > 2 else None,
+                                      np.asarray(x[3]).reshape(-1) if len(x) > 3 else None)]
+        elif op == "QLinearMatMul":
+            zy = np.asarray(x[7]).reshape(())
+            out = [orc.qlinear_matmul(x[0], _f32(x[1]), int(np.asarray(x[2]).reshape(())), x[3], _f32(x[4]), int(np.asarray(x[5]).reshape(())),
+                                      _f32(x[6]), int(zy), y_dtype=zy.dtype.type)]
+        elif op == "ElementWiseNvrtc":
+            # the group's member nodes one by one, as the reference's CPU path runs a fusion group (compiler/chxvm/emitter.cc:702-726)
+            local = {}
+            get = lambda k: local[k] if k in local else env[k]  # noqa: E731
+            for mop, mins, mouts in a["members"]:
+                v = [np.asarray(get(k), np.float32) for k in mins]
+                local[mouts[0]] = _EW[mop](*v).astype(np.float32)
+            out = [np.broadcast_to(local[o], np.broadcast_shapes(*[np.shape(env[k]) for k in inst.inputs])).copy() for o in inst.outputs]
+        elif op == "BatchNormalization":
+            shape = [1, -1] + [1] * (x[0].ndim - 2)
+            f = np.float32
+            out = [((x[0] - x[3].reshape(shape)) / np.sqrt(x[4].reshape(shape) + f(a.get("epsilon", 1e-5))) * x[1].reshape(shape) + x[2].reshape(shape)).astype(f)]
         elif op == "ScaleProduct":
             m = (np.asarray(x[0], np.float32) * np.asarray(x[1], np.float32)).astype(np.float32)
             out = [m.reshape(a["shape"]) if a.get("shape") else m]
         elif op == "Cast":
-            out = [x[0].astype(np.float32)]
+            to = a.get("to", "float32")
+            out = [np.asarray(x[0]).astype(to if isinstance(to, str) else _ONNX_DTYPE[int(to)])]
+        elif op in ("ReduceMin", "ReduceMax"):
+            v = np.float32(x[0].min() if op == "ReduceMin" else x[0].max())
+            out = [v.reshape([1] * x[0].ndim) if a.get("keepdims", 1) else v.reshape(())]
+        elif op == "Floor":
+            out = [np.floor(x[0])]
         elif op in ("Add", "Sub", "Mul", "Div"):
             f = {"Add": np.add, "Sub": np.subtract, "Mul": np.multiply, "Div": np.divide}[op]
             out = [f(x[0], x[1]).astype(np.float32)]

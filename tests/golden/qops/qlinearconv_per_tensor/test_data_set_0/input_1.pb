@@ -1,0 +1,2 @@
+"
+ף<Bx_scale

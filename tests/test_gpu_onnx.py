@@ -49,3 +49,77 @@ def test_run_onnx_command_line(pkg, tmp_path):
         run_onnx.run_onnx([GOLDEN, "-q"])  # float Conv / MatMul: no kernel in this package
     # the float graph as torch expressions reproduces the shipped outputs (library convolutions may use TF32: loose tolerance)
     assert run_onnx.run_onnx([GOLDEN, "--float_ops_via_torch", "--rtol", "1e-2", "--atol", "1", "-q"]) == 0
+
+
+QOPS = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "qops")
+
+
+@pytest.mark.parametrize("name", sorted(os.listdir(QOPS)))
+def test_operator_directories_run_exactly(pkg, name):
+    """One quantized operator per directory, scalars as graph inputs (tests/golden/make_qop_dirs.py): integer outputs are
+    compared with zero tolerance, float outputs (DequantizeLinear) at one fp32 rounding."""
+    from chainer_compiler_b200 import run_onnx
+    assert run_onnx.run_onnx(["--test", os.path.join(QOPS, name), "--rtol", "1e-7", "--atol", "0", "-q"]) == 0
+
+
+def test_fused_groups_tracing_and_dumps(pkg, tmp_path):
+    from chainer_compiler_b200 import onnx_io, run_onnx
+    model, cases = onnx_io.load_test_dir(GOLDEN)
+    plain = run_onnx.Executor(run_onnx.compile_model(model, quantize=True), "cuda:0")
+    fused_prog = run_onnx.compile_model(model, quantize=True, fuse=True)
+    assert sum(i.op == "ElementWiseNvrtc" for i in fused_prog.insts) == 3
+    fused = run_onnx.Executor(fused_prog, "cuda:0")
+    for ins, _ in cases:
+        (_, a), = plain.run(ins)
+        (_, b), = fused.run(ins)
+        # the generated kernel may contract the Mul and the Add into one fused multiply-add
+        assert np.allclose(a.cpu().numpy(), b.cpu().numpy(), rtol=1e-5, atol=1e-4)
+    trace, dumps = str(tmp_path / "trace.json"), str(tmp_path / "dumps")
+    rc = run_onnx.run_onnx(["--test", GOLDEN, "--quantize", "--fuse_operations", "--use_nvrtc", "--chrome_tracing", trace, "--dump_outputs_dir", dumps,
+                            "--no_check_values", "-q"])
+    assert rc == 0
+    events = json.load(open(trace))
+    assert len(events) == 3 * len(fused_prog.insts)
+    assert all(e["ph"] == "X" and e["cat"] == "ChxVM" and e["pid"] == 1 and e["tid"] == 1 and e["dur"] >= 0 for e in events)
+    assert [e["name"] for e in events[:len(fused_prog.insts)]] == [i.op for i in fused_prog.insts]
+    assert [e["args"]["pc"] for e in events[:4]] == [0, 1, 2, 3] and all(events[k]["ts"] <= events[k + 1]["ts"] for k in range(len(events) - 1))
+    files = sorted(os.listdir(dumps))
+    assert files[0].startswith("00000_") and all(f[:5].isdigit() and f[5] == "_" and f.endswith(".npy") for f in files)
+    last = fused_prog.insts[-1]
+    y = np.load(os.path.join(dumps, "%05d_%s.npy" % (len(fused_prog.insts) - 1, last.outputs[0])))
+    assert y.shape == (1, 10)
+
+
+def test_exported_graph_and_bn_folding_on_the_device(pkg, tmp_path):
+    import torch
+    from chainer_compiler_b200 import onnx_io, run_onnx
+    model, cases = onnx_io.load_test_dir(GOLDEN)
+    out = str(tmp_path / "quantized.onnx")
+    assert run_onnx.run_onnx(["--test", GOLDEN, "--quantize", "--out_onnx", out, "--skip_inference", "-q"]) == 0
+    prog = run_onnx.compile_model(model, quantize=True)
+    again = run_onnx.compile_model(onnx_io.load_model(out))
+    assert any(i.op == "ReduceMin" for i in again.insts) and any(i.op == "ConvInteger" for i in again.insts)
+    e1, e2 = run_onnx.Executor(prog, "cuda:0"), run_onnx.Executor(again, "cuda:0")
+    for ins, _ in cases:
+        (_, a), = e1.run(ins)
+        (_, b), = e2.run(ins)
+        assert torch.equal(a, b)
+    # Conv + BatchNormalization: merged first and quantized as one convolution, against the float pair
+    rng = np.random.default_rng(8)
+    N, f32 = onnx_io.Node, np.float32
+    inits = {"w": (rng.standard_normal((16, 8, 3, 3)) * 0.2).astype(f32), "gamma": rng.uniform(0.5, 1.5, 16).astype(f32),
+             "beta": (rng.standard_normal(16) * 0.1).astype(f32), "mean": (rng.standard_normal(16) * 0.1).astype(f32), "var": rng.uniform(0.5, 1.5, 16).astype(f32)}
+    nodes = [N("Conv", ["x", "w"], ["c"], {"kernel_shape": [3, 3], "pads": [1, 1, 1, 1]}),
+             N("BatchNormalization", ["c", "gamma", "beta", "mean", "var"], ["y"], {"epsilon": 2e-5})]
+    m = onnx_io.Model(nodes, inits, ["x"], ["y"], ir_version=5, opset=10)
+    x = rng.standard_normal((2, 8, 12, 12)).astype(f32)
+    t = lambda k: torch.from_numpy(inits[k])  # noqa: E731
+    sh = (1, -1, 1, 1)
+    want = (torch.nn.functional.conv2d(torch.from_numpy(x), t("w"), None, 1, 1) - t("mean").reshape(sh)) / torch.sqrt(t("var").reshape(sh) + 2e-5) \
+        * t("gamma").reshape(sh) + t("beta").reshape(sh)
+    for first in (False, True):
+        p = run_onnx.compile_model(m, quantize=True, fold_bn_first=first)
+        assert ("BatchNormalization" in [i.op for i in p.insts]) == (not first)
+        (_, y), = run_onnx.Executor(p, "cuda:0").run({"x": x})
+        err = (y.cpu() - want).abs().max().item()
+        assert err < 0.05 * want.abs().max().item(), (first, err)

@@ -82,3 +82,136 @@ def test_oracle_runs_the_quantized_mnist_graph_close_to_the_shipped_outputs(mods
         rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
         print("quantized MNIST vs shipped float output: relative L2 distance %.4f" % rel)
         assert rel < 0.05
+
+
+QOPS = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "qops")
+
+
+@pytest.mark.parametrize("name", sorted(os.listdir(QOPS)))
+def test_operator_directories_load_and_match_the_oracle(mods, name):
+    """tests/golden/qops (written by tests/golden/make_qop_dirs.py): one quantized operator per directory, every operand a
+    graph input; the oracle's evaluation of the loaded program reproduces the stored outputs bit for bit."""
+    onnx_io, run_onnx = mods
+    entry.load_oracle()
+    from oracle import networks
+    model, cases = onnx_io.load_test_dir(os.path.join(QOPS, name))
+    prog = run_onnx.compile_model(model)
+    assert len(cases) == 1
+    for ins, expected in cases:
+        got = dict(networks.run_program(prog, ins))
+        for oname, want in expected:
+            assert got[oname].dtype == want.dtype and np.array_equal(got[oname], want), name
+
+
+def _conv_bn_model(onnx_io, rng, with_bias):
+    N = onnx_io.Node
+    f32 = np.float32
+    inits = {"w": (rng.standard_normal((6, 3, 3, 3)) * 0.2).astype(f32), "gamma": rng.uniform(0.5, 1.5, 6).astype(f32),
+             "beta": (rng.standard_normal(6) * 0.1).astype(f32), "mean": (rng.standard_normal(6) * 0.1).astype(f32), "var": rng.uniform(0.5, 1.5, 6).astype(f32)}
+    conv_in = ["x", "w"]
+    if with_bias:
+        inits["b"] = (rng.standard_normal(6) * 0.1).astype(f32)
+        conv_in.append("b")
+    nodes = [N("Conv", conv_in, ["c"], {"kernel_shape": [3, 3], "pads": [1, 1, 1, 1]}),
+             N("BatchNormalization", ["c", "gamma", "beta", "mean", "var"], ["bn"], {"epsilon": 2e-5}),
+             N("Relu", ["bn"], ["y"], {})]
+    return onnx_io.Model(nodes, inits, ["x"], ["y"], ir_version=5, opset=10)
+
+
+def test_merge_conv_bn_pass_and_its_order_against_quantize(mods):
+    """compiler/merge.cc:142-215 and the pass order of compiler/passes.cc:121-128."""
+    import torch
+    onnx_io, run_onnx = mods
+    rng = np.random.default_rng(5)
+    for with_bias in (False, True):
+        model = _conv_bn_model(onnx_io, rng, with_bias)
+        prog = run_onnx.compile_model(model)
+        assert [i.op for i in prog.insts] == ["Conv", "Relu"] and len(prog.insts[0].inputs) == 3
+        w2, b2 = prog.constants[prog.insts[0].inputs[1]], prog.constants[prog.insts[0].inputs[2]]
+        i = model.initializers
+        x = torch.from_numpy(rng.standard_normal((2, 3, 8, 8)).astype(np.float32))
+        c = torch.nn.functional.conv2d(x, torch.from_numpy(i["w"]), torch.from_numpy(i["b"]) if with_bias else None, 1, 1)
+        sh = (1, -1, 1, 1)
+        bn = (c - torch.from_numpy(i["mean"]).reshape(sh)) / torch.sqrt(torch.from_numpy(i["var"]).reshape(sh) + 2e-5) * torch.from_numpy(i["gamma"]).reshape(sh) \
+            + torch.from_numpy(i["beta"]).reshape(sh)
+        merged = torch.nn.functional.conv2d(x, torch.from_numpy(w2), torch.from_numpy(b2), 1, 1)
+        assert torch.allclose(bn, merged, rtol=1e-4, atol=1e-5)
+        assert w2.dtype == np.float32 and b2.dtype == np.float32
+        # reference order: the quantizer takes the bias-free Conv first, the BatchNormalization stays a float node; a Conv with
+        # bias is not quantized (compiler/quantize.cc:366-369) and is merged
+        ops = [k.op for k in run_onnx.compile_model(model, quantize=True).insts]
+        if with_bias:
+            assert ops == ["Conv", "Relu"]
+        else:
+            assert ops == ["ReduceMinMax", "DynamicQuantParamsU8", "QuantizeLinear", "ConvInteger", "Cast", "ScaleProduct", "Mul", "BatchNormalization", "Relu"]
+        # merge first: one quantized convolution, the merged bias added after the scale-back
+        ops = [k.op for k in run_onnx.compile_model(model, quantize=True, fold_bn_first=True).insts]
+        assert ops == ["ReduceMinMax", "DynamicQuantParamsU8", "QuantizeLinear", "ConvInteger", "Cast", "ScaleProduct", "Mul", "Add", "Relu"]
+    # a Conv with a second user, or one that is a graph output, is left alone
+    model = _conv_bn_model(onnx_io, rng, False)
+    model.outputs = ["y", "c"]
+    assert [k.op for k in run_onnx.compile_model(model).insts] == ["Conv", "BatchNormalization", "Relu"]
+
+
+def test_fused_program_equals_the_unfused_one_on_the_oracle(mods):
+    onnx_io, run_onnx = mods
+    entry.load_oracle()
+    from oracle import networks
+    model, cases = onnx_io.load_test_dir(GOLDEN)
+    plain = run_onnx.compile_model(model, quantize=True)
+    fused = run_onnx.compile_model(model, quantize=True, fuse=True)
+    groups = [i for i in fused.insts if i.op == "ElementWiseNvrtc"]
+    # Mul (scale-back) + Add (bias) after each of the two convolutions and after the MatMul; Relu is not in the reference's
+    # fusable set (compiler/fusion_elementwise.cc:12-24)
+    assert len(groups) == 3 and all([m[0] for m in g.attrs["members"]] == ["Mul", "Add"] for g in groups)
+    assert all("fusion%d" % g.attrs["fusion_id"] in g.attrs["code"] for g in groups)
+    assert len(fused.insts) == len(plain.insts) - 3
+    for ins, _ in cases[:2]:
+        (_, a), = networks.run_program(plain, ins)
+        (_, b), = networks.run_program(fused, ins)
+        assert np.array_equal(a, b)
+
+
+def test_exported_onnx_graph_round_trips(mods, tmp_path):
+    """--out_onnx: the quantized program written as standard ONNX nodes, read back and evaluated, gives the same bits."""
+    onnx_io, run_onnx = mods
+    entry.load_oracle()
+    from oracle import networks
+    model, cases = onnx_io.load_test_dir(GOLDEN)
+    prog = run_onnx.compile_model(model, quantize=True)
+    exported = run_onnx.program_to_onnx(prog)
+    kinds = [n.op_type for n in exported.nodes]
+    assert kinds[:12] == ["ReduceMin", "ReduceMax", "Sub", "Div", "Sub", "Div", "Floor", "Cast", "QuantizeLinear", "ConvInteger", "Cast", "Mul"]
+    assert not any(k in kinds for k in ("ReduceMinMax", "DynamicQuantParamsU8", "ScaleProduct"))
+    path = tmp_path / "q.onnx"
+    path.write_bytes(onnx_io.serialize_model(exported))
+    again = run_onnx.compile_model(onnx_io.load_model(str(path)))
+    for ins, _ in cases[:2]:
+        (_, a), = networks.run_program(prog, ins)
+        (_, b), = networks.run_program(again, ins)
+        assert np.array_equal(a, b)
+    assert run_onnx.run_onnx([str(path), "--compile_only", "--quiet"]) == 0
+    args = run_onnx.parse_args(["--test", "d", "--chrome_tracing", "t.json", "-t", "--backend", "chxvm", "--fuse_operations", "--use_nvrtc", "--skip_inference"])
+    assert args.chrome_tracing == "t.json" and args.trace and args.fuse_operations and args.use_nvrtc and args.skip_inference
+
+
+def test_compare_dump_dirs(mods, tmp_path):
+    import io
+    entry.load_package()
+    from chainer_compiler_b200 import compare_dump_dirs
+    a, b = tmp_path / "a", tmp_path / "b"
+    a.mkdir()
+    b.mkdir()
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+    np.save(a / "00000_x.npy", x)
+    np.save(a / "00001_y.npy", x.astype(np.uint8))
+    np.save(a / "00002_only_here.npy", x)
+    np.save(b / "00000_y.npy", x.astype(np.uint8))       # numbered differently: matched by name
+    y = x.copy()
+    y[1, 2] += 0.5
+    np.save(b / "00005_x.npy", y)
+    log = io.StringIO()
+    assert compare_dump_dirs.compare(str(a), str(b), out=log) == 1
+    text = log.getvalue()
+    assert "y: OK" in text and "x: 1 of 12 elements differ" in text and "only_here" not in text
+    assert compare_dump_dirs.compare(str(a), str(b), atol=1.0, out=io.StringIO()) == 0
