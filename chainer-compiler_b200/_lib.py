@@ -103,6 +103,8 @@ SIGNATURES = {
     "chxq_eltwise_run": (_c.c_int, [_c.c_char_p, _i32, _c.POINTER(_vp), _i32, _c.POINTER(_vp), _i32, _i64, _i32, _vp]),
     "chxq_fuse_elementwise": (_c.c_int, [_c.POINTER(GraphNode), _i32, _c.POINTER(GraphValue), _i32, _c.POINTER(_i32), _c.POINTER(_i32)]),
     "chxq_quantize_weights_host": (_c.c_int, [_vp, _i64, _i64, _i32, _i32, _vp, _vp, _vp]),
+    "chxq_prepare_weights_workspace": (_sz, [_i64]),
+    "chxq_prepare_weights": (_c.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _f32, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "chxq_maxpool_u8_nhwc": (_c.c_int, [_vp] + [_i32] * 9 + [_vp, _vp]),
     "chxq_global_avgpool_dq_nhwc": (_c.c_int, [_vp, _i32, _i32, _i32, _f32, _i32, _vp, _vp]),
     "chxq_linear_f32": (_c.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),

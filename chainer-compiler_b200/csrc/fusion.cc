@@ -146,7 +146,7 @@ static void quantize_block(const float* w, int64_t n, bool to_int8, void* q, flo
         const float scale = max_range * 2 / 254.f;
         int8_t* out = static_cast<int8_t*>(q);
         // SlowRound (runtime/chainerx_util.cc:397-410): fp32 quotient, rint in double, back to fp32, then AsType.
-        for (int64_t i = 0; i < n; ++i) out[i] = static_cast<int8_t>(static_cast<float>(rint(static_cast<double>(w[i] / scale))));
+        for (int64_t i = 0; i < n; ++i) out[i] = static_cast<int8_t>(static_cast<int32_t>(static_cast<float>(rint(static_cast<double>(w[i] / scale)))));
         *scale_out = scale;
         *zp_out = 0;
     } else {
@@ -155,7 +155,7 @@ static void quantize_block(const float* w, int64_t n, bool to_int8, void* q, flo
         uint8_t* out = static_cast<uint8_t*>(q);
         for (int64_t i = 0; i < n; ++i) {
             const float v = static_cast<float>(rint(static_cast<double>(w[i] / scale))) + static_cast<float>(zp);
-            out[i] = static_cast<uint8_t>(v);
+            out[i] = static_cast<uint8_t>(static_cast<int32_t>(v));  // low eight bits of the truncated integer
         }
         *scale_out = scale;
         *zp_out = static_cast<int32_t>(zp);

@@ -2,7 +2,7 @@
 LSTM-cell elementwise group, the MatMulInteger / QLinearMatMul sweep, MobileNetV2, QuantizeLinear / DequantizeLinear and
 single depthwise layers.  One JSON line per measurement on stdout.
 
-    python chainer-compiler_b200/microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise]
+    python chainer-compiler_b200/microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [prepare]
 
 Timing: CUDA events on the launching stream, 3 warm-up calls, median of 10 (3 for the largest GEMMs), a 256 MB buffer
 rewritten between calls so that nothing is served from L2.  `gbs` is algorithmic bytes (every input read once, every
@@ -34,7 +34,7 @@ def main():
         raise SystemExit("microbench.py needs a CUDA device: this package has no CPU path")
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise"}
+    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare"}
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     peak, peak_src = hbm_peak_gbs()
 
@@ -128,6 +128,36 @@ def main():
             ms = timeit(lambda: ops.QLinearConvPacked(x, pk, 0.02, np.uint8(0), ws, wz, 0.05, np.uint8(0), fold_scales=True))
             emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, tensor cores (diagonal blocks)" % (C, H, H, s, N), ms,
                  gbs=nbytes / ms / 1e6)
+    if "prepare" in which:
+        # model preparation: batch-norm folding + per-channel int8 weight quantization of every ResNet-50 convolution
+        import time
+        net_shapes = [(64, 3, 7, 7)]
+        cin = 64
+        for width, blocks in ((64, 3), (128, 4), (256, 6), (512, 3)):
+            for b in range(blocks):
+                net_shapes += [(width, cin, 1, 1), (width, width, 3, 3), (width * 4, width, 1, 1)]
+                if b == 0:
+                    net_shapes.append((width * 4, cin, 1, 1))
+                cin = width * 4
+        rng = np.random.default_rng(0)
+        host = [(rng.standard_normal(s, dtype=np.float32) * 0.05) for s in net_shapes]
+        bns = [tuple(rng.uniform(0.5, 1.5, s[0]).astype(np.float32) for _ in range(4)) for s in net_shapes]
+        devw = [torch.from_numpy(w).to(dev) for w in host]
+        devbn = [tuple(torch.from_numpy(v).to(dev) for v in bn) for bn in bns]
+        nw = sum(w.size for w in host)
+
+        def on_device():
+            for w, bn in zip(devw, devbn):
+                ops.PrepareWeights(w, bn, None, 2e-5, True, True)
+        ms = timeit(on_device)
+        emit("batch-norm folding + int8 per-channel weight quantization, %d convolutions of ResNet-50 (%.1f M weights), device" % (len(host), nw / 1e6),
+             ms, weights_per_s=nw / ms * 1e3, launches=2 * len(host))
+        t0 = time.perf_counter()
+        for w, bn in zip(host, bns):
+            g, be, mu, var = bn
+            s = (g / np.sqrt(var + np.float32(2e-5))).astype(np.float32)
+            models.quantize_weights((w * s.reshape(-1, 1, 1, 1)).astype(np.float32), per_channel=True, to_int8=True)
+        emit("the same on one host core (NumPy merge + the library's host quantizer)", (time.perf_counter() - t0) * 1e3)
     ops.device_status()
     del pkg
 

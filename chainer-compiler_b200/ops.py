@@ -457,6 +457,36 @@ def to_contiguous_nchw(x):
     return y
 
 
+def PrepareWeights(w, bn=None, conv_bias=None, epsilon=1e-5, to_int8=True, per_channel=True, return_folded=False):
+    """Model preparation on the device: the Conv + BatchNormalization merge (compiler/merge.cc:142-215) followed by the weight
+    quantizer (compiler/quantize.cc:70-129).  w: fp32 [M, ...]; bn: None or (scale, bias, mean, var), fp32 [M] each.
+    Returns (q, scales, zero_points, folded_bias or None[, folded_w]); zero_points are int32."""
+    _require_cuda(w)
+    if w.dtype != torch.float32:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "PrepareWeights: w must be float32")
+    w = w.contiguous()
+    M = w.shape[0]
+    inner = w.numel() // M
+    vec = lambda t: None if t is None else t.to(device=w.device, dtype=torch.float32).contiguous()  # noqa: E731
+    gamma, beta, mean, var = (vec(t) for t in bn) if bn is not None else (None, None, None, None)
+    conv_bias = vec(conv_bias)
+    for t in (gamma, beta, mean, var, conv_bias):
+        if t is not None and t.numel() != M:
+            raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "PrepareWeights: per-channel vectors need one entry per output channel")
+    n = M if per_channel else 1
+    q = torch.empty(w.shape, dtype=torch.int8 if to_int8 else torch.uint8, device=w.device)
+    scales = torch.empty(n, dtype=torch.float32, device=w.device)
+    zps = torch.empty(n, dtype=torch.int32, device=w.device)
+    folded_bias = torch.empty(M, dtype=torch.float32, device=w.device) if bn is not None else None
+    folded_w = torch.empty_like(w) if return_folded else None
+    ws_bytes = lib().chxq_prepare_weights_workspace(M)
+    ws = workspace(ws_bytes, w.device)
+    p = lambda t: None if t is None else _ptr(t)  # noqa: E731
+    check(lib().chxq_prepare_weights(_ptr(w), M, inner, p(gamma), p(beta), p(mean), p(var), float(epsilon), p(conv_bias), int(to_int8), int(per_channel),
+                                     _ptr(q), _ptr(scales), _ptr(zps), p(folded_w), p(folded_bias), _ptr(ws), ws_bytes, _stream()))
+    return (q, scales, zps, folded_bias, folded_w) if return_folded else (q, scales, zps, folded_bias)
+
+
 def MinMax(x):
     """ReduceMin and ReduceMax of an fp32 tensor in one pass -> device tensor [min, max]."""
     _require_cuda(x)

@@ -299,6 +299,20 @@ int chxq_fuse_elementwise(const chxq_graph_node* nodes, int32_t n_nodes, const c
 int chxq_quantize_weights_host(const float* w, int64_t M, int64_t inner, int32_t to_int8, int32_t per_channel, void* q, float* scales,
                                int32_t* zero_points);
 
+/* The same quantizer on the DEVICE, with the Conv + BatchNormalization merge (compiler/merge.cc:142-215) in front of it, for
+ * preparing a model without a host pass over the weights.  Device pointers; never synchronizes.
+ *   w [M, inner] fp32.  bn_scale / bn_bias / bn_mean / bn_var [M] fp32: all four or none (none = quantize w as it is);
+ *   conv_bias [M] fp32 or NULL (only with batch normalization).  With batch normalization
+ *       s = bn_scale / sqrt(bn_var + epsilon);  w'[m] = w[m] * s[m];  folded_bias = (conv_bias - bn_mean) * s + bn_bias
+ *   and w' is what gets quantized.  q [M, inner] int8 / uint8; scales, zero_points: [M] (per_channel != 0) or [1].
+ *   folded_w [M, inner] fp32 or NULL: receives w'.  folded_bias [M] fp32: required with batch normalization.
+ *   workspace: chxq_prepare_weights_workspace(M) bytes.
+ * Results are bit-identical to chxq_quantize_weights_host applied to a single-rounded fp32 evaluation of the merge. */
+size_t chxq_prepare_weights_workspace(int64_t M);
+int chxq_prepare_weights(const float* w, int64_t M, int64_t inner, const float* bn_scale, const float* bn_bias, const float* bn_mean,
+                         const float* bn_var, float epsilon, const float* conv_bias, int32_t to_int8, int32_t per_channel, void* q, float* scales,
+                         int32_t* zero_points, float* folded_w, float* folded_bias, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- Glue ops a quantized CNN graph runs between the int8 ops (reference bodies are one-line
  * ChainerX calls; kernels here work on NHWC u8 maps). */
 /* MaxPool (runtime/ops/pooling.cc:47-60) on u8 NHWC; cover_all as Chainer's max_pooling_2d. */

@@ -227,6 +227,18 @@ def quantize_weight_per_channel(w, to_int8=True):
     return q, s, z
 
 
+def merge_conv_bn(w, bn_scale, bn_bias, bn_mean, bn_var, epsilon, conv_bias=None):
+    """MergeConvBN, compiler/merge.cc:166-189, every step a single-rounded fp32 array operation as ChainerX evaluates it:
+    s = scale / sqrt(var + eps); w'[m] = w[m] * s[m]; b' = (b - mean) * s + bn_bias.  Returns (w', b')."""
+    f = np.float32
+    w, bn_scale, bn_bias, bn_mean, bn_var = (np.asarray(v, f) for v in (w, bn_scale, bn_bias, bn_mean, bn_var))
+    bc = np.zeros(bn_scale.shape[0], f) if conv_bias is None else np.asarray(conv_bias, f)
+    s = (bn_scale / np.sqrt(bn_var + f(epsilon))).astype(f)
+    new_w = (w * s.reshape((-1,) + (1,) * (w.ndim - 1))).astype(f)
+    t = ((bc - bn_mean).astype(f) * s).astype(f)
+    return new_w, (t + bn_bias).astype(f)
+
+
 def dynamic_params_u8(x):
     x = _c(x, np.float32)
     s = ctypes.c_float()

@@ -148,3 +148,47 @@ def test_quantize_division_is_correctly_rounded(ops, orc, dev):
             got = ops.QuantizeLinear(torch.from_numpy(x).to(dev), float(s32), np.uint8(zp)).cpu().numpy()
             want = orc.quantize_linear(x, s32, zp)
             assert np.array_equal(got, want), "scale %r zero point %d: %d mismatches" % (s, zp, int((got != want).sum()))
+
+
+@pytest.mark.parametrize("to_int8", [True, False])
+@pytest.mark.parametrize("per_channel", [True, False])
+def test_prepare_weights_matches_host_quantizer_and_merge(pkg, ops, orc, dev, to_int8, per_channel):
+    """Device model preparation (Conv + BatchNormalization merge, then the weight quantizer) against the oracle's merge
+    (compiler/merge.cc:166-189) followed by its quantizer (compiler/quantize.cc:70-129): every output bit for bit."""
+    rng = np.random.default_rng(31 + 2 * int(to_int8) + int(per_channel))
+    for shape in ((64, 16, 3, 3), (10, 1000), (7, 3, 1, 1), (300, 5, 5, 5)):
+        w = (rng.standard_normal(shape) * 0.1).astype(np.float32)
+        w[0].reshape(-1)[:3] = [0.0, 0.05, -0.05]
+        if shape[0] > 8:
+            w[3] = np.abs(w[3])       # a channel with no negative weight (range widened to include zero)
+            w[5] = 0.0                # an all-zero channel: uint8 scale 1; int8 scale 0 is left out below
+        M = shape[0]
+        gamma, beta = rng.uniform(0.5, 1.5, M).astype(np.float32), (rng.standard_normal(M) * 0.1).astype(np.float32)
+        mean, var = (rng.standard_normal(M) * 0.1).astype(np.float32), rng.uniform(0.5, 1.5, M).astype(np.float32)
+        bias = (rng.standard_normal(M) * 0.1).astype(np.float32)
+        if to_int8 and per_channel and shape[0] > 8:
+            w[5].reshape(-1)[0] = 0.01    # int8 with scale 0 divides 0 by 0 in the reference: not a defined case
+        for bn, cb in ((None, None), ((gamma, beta, mean, var), None), ((gamma, beta, mean, var), bias)):
+            if bn is None:
+                wf, bf = w, None
+            else:
+                wf, bf = orc.merge_conv_bn(w, gamma, beta, mean, var, 2e-5, cb)
+            if per_channel:
+                qo, so, zo = orc.quantize_weight_per_channel(wf, to_int8)
+            else:
+                qo, so, zo = orc.quantize_data(wf, to_int8)
+                so, zo = np.array([so], np.float32), np.array([zo], np.int32)
+            tb = None if bn is None else tuple(torch.from_numpy(v).to(dev) for v in bn)
+            q, s, z, fb, fw = ops.PrepareWeights(torch.from_numpy(w).to(dev), tb, None if cb is None else torch.from_numpy(cb).to(dev), 2e-5,
+                                                 to_int8, per_channel, return_folded=True)
+            ops.device_status()
+            assert np.array_equal(fw.cpu().numpy(), wf), (shape, "folded weights")
+            assert np.array_equal(s.cpu().numpy(), so) and np.array_equal(z.cpu().numpy(), zo), (shape, "scales / zero points")
+            assert np.array_equal(q.cpu().numpy(), qo), (shape, "quantized weights")
+            if bn is not None:
+                assert np.array_equal(fb.cpu().numpy(), bf), (shape, "folded bias")
+            else:
+                assert fb is None
+    from chainer_compiler_b200 import _lib
+    with pytest.raises(_lib.ChxqError):
+        ops.PrepareWeights(torch.zeros((4, 3), device=dev), (torch.ones(3, device=dev),) * 4)
