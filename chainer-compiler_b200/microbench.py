@@ -2,7 +2,7 @@
 LSTM-cell elementwise group, the MatMulInteger / QLinearMatMul sweep, MobileNetV2, QuantizeLinear / DequantizeLinear and
 single depthwise layers.  One JSON line per measurement on stdout.
 
-    python chainer-compiler_b200/microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [prepare]
+    python chainer-compiler_b200/microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [prepare] [onnx]
 
 Timing: CUDA events on the launching stream, 3 warm-up calls, median of 10 (3 for the largest GEMMs), a 256 MB buffer
 rewritten between calls so that nothing is served from L2.  `gbs` is algorithmic bytes (every input read once, every
@@ -34,7 +34,7 @@ def main():
         raise SystemExit("microbench.py needs a CUDA device: this package has no CPU path")
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare"}
+    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare", "onnx"}
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     peak, peak_src = hbm_peak_gbs()
 
@@ -158,6 +158,27 @@ def main():
             s = (g / np.sqrt(var + np.float32(2e-5))).astype(np.float32)
             models.quantize_weights((w * s.reshape(-1, 1, 1, 1)).astype(np.float32), per_channel=True, to_int8=True)
         emit("the same on one host core (NumPy merge + the library's host quantizer)", (time.perf_counter() - t0) * 1e3)
+    if "onnx" in which:
+        # the run_onnx entry point on a statically quantized ResNet-50 file (written from the calibrated hand-built network):
+        # Elapsed as the reference's tool reports it, inputs staged on the device before the clock starts
+        import tempfile
+        from chainer_compiler_b200 import onnx_io, run_onnx
+        B = 256
+        net = models.ResNet50Int8(B, dev, seed=0)
+        x = torch.rand((B, 3, 224, 224), generator=torch.Generator().manual_seed(1))
+        net.calibrate(x.to(dev))
+        want = net.forward(x.to(dev), fused=True, fold=True).cpu().numpy()
+        with tempfile.TemporaryDirectory() as d:
+            onnx_io.write_test_dir(d, net.to_onnx(), [({"x": x.numpy()}, [("logits", want)])])
+            del net
+            torch.cuda.empty_cache()
+            for extra in ([], ["--fold_scales"], ["--fold_scales", "--cuda_graph"]):
+                rep = os.path.join(d, "report.json")
+                rc = run_onnx.run_onnx(["--test", d, "-I", "20", "--rtol", "1e-2", "--atol", "%g" % (1e-2 * float(np.abs(want).max())), "--report_json", rep, "-q"]
+                                       + extra)
+                r = json.load(open(rep))
+                emit("run_onnx --test <int8 ResNet-50 directory, batch 256> -I 20 %s" % " ".join(extra), r["best_ms"], avg_ms=r["elapsed_ms"],
+                     img_per_s=B / r["best_ms"] * 1e3, outputs_within_tolerance=(rc == 0))
     ops.device_status()
     del pkg
 

@@ -252,6 +252,58 @@ class ResNet50Int8:
             logits = self.forward(x_static, fold=fold)
         return g, logits
 
+    def to_onnx(self):
+        """The calibrated network as a statically quantized ONNX graph (an onnx_io.Model) of standard nodes: QuantizeLinear,
+        QLinearConv with int32 bias (a zero output zero point makes the uint8 saturation the ReLU), MaxPool on uint8 with
+        ceil_mode (Chainer's cover_all), per residual join DequantizeLinear x2, Add, Relu, QuantizeLinear, then
+        DequantizeLinear, GlobalAveragePool, Flatten and an fp32 Gemm.  `run_onnx` executes this file on the same kernels the
+        hand-built forward() uses."""
+        from . import onnx_io
+        assert self.calibrated
+        N, f32, u8 = onnx_io.Node, np.float32, np.uint8
+        inits, nodes = {"zero_u8": u8(0).reshape(())}, []
+
+        def scalar(name, v, dt=f32):
+            inits[name] = np.asarray(v, dt).reshape(())
+            return name
+
+        def conv(c, x, x_scale_name, out):
+            n = c.name
+            inits[n + "_w"], inits[n + "_ws"], inits[n + "_wz"], inits[n + "_b"] = c.w_q, c.w_scale, c.w_zp, c.bias_q
+            ys, zy = scalar(n + "_ys", c.y_scale), scalar(n + "_zy", c.y_zp, u8)
+            attrs = {"kernel_shape": [c.k, c.k], "strides": [c.stride, c.stride], "pads": [c.pad] * 4}
+            nodes.append(N("QLinearConv", [x, x_scale_name, "zero_u8", n + "_w", n + "_ws", n + "_wz", ys, zy, n + "_b"], [out], attrs, n))
+            return ys, zy
+
+        in_s = scalar("in_scale", self.in_scale)
+        nodes.append(N("QuantizeLinear", ["x", in_s, "zero_u8"], ["xq"], {}))
+        h_s, _ = conv(self.stem, "xq", in_s, "stem")
+        nodes.append(N("MaxPool", ["stem"], ["pool"], {"kernel_shape": [3, 3], "strides": [2, 2], "ceil_mode": 1}))
+        h = "pool"
+        for i, b in enumerate(self.blocks):
+            p = "b%d_" % i
+            s1, _ = conv(b["conv1"], h, h_s, p + "h1")
+            s2, _ = conv(b["conv2"], p + "h1", s1, p + "h2")
+            s3, z3 = conv(b["conv3"], p + "h2", s2, p + "h3")
+            if b["proj"] is not None:
+                ss, zs = conv(b["proj"], h, h_s, p + "sc")
+                sc = p + "sc"
+            else:
+                sc, ss, zs = h, h_s, "zero_u8"
+            out_s = scalar(p + "out_scale", b["out_scale"])
+            nodes.append(N("DequantizeLinear", [p + "h3", s3, z3], [p + "f3"], {}))
+            nodes.append(N("DequantizeLinear", [sc, ss, zs], [p + "fs"], {}))
+            nodes.append(N("Add", [p + "f3", p + "fs"], [p + "sum"], {}))
+            nodes.append(N("Relu", [p + "sum"], [p + "relu"], {}))
+            nodes.append(N("QuantizeLinear", [p + "relu", out_s, "zero_u8"], [p + "out"], {}))
+            h, h_s = p + "out", out_s
+        inits["fc_w"], inits["fc_b"] = self.fc_w, self.fc_b
+        nodes.append(N("DequantizeLinear", [h, h_s, "zero_u8"], ["feat"], {}))
+        nodes.append(N("GlobalAveragePool", ["feat"], ["gap"], {}))
+        nodes.append(N("Flatten", ["gap"], ["flat"], {"axis": 1}))
+        nodes.append(N("Gemm", ["flat", "fc_w", "fc_b"], ["logits"], {"transB": 1}))
+        return onnx_io.Model(nodes, inits, ["x"], ["logits"], ir_version=5, opset=12, name="resnet50_int8")
+
     def export_numpy(self):
         """Everything the CPU oracle needs to run the same network."""
         def conv(c):

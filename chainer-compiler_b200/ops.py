@@ -335,6 +335,24 @@ def QLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y
     return y
 
 
+def ConvIntegerPacked(x, packed, x_zero_point=None):
+    """ConvInteger with weights packed by PackedConv; x must be a channels_last map of the packed geometry."""
+    _require_cuda(x)
+    g = packed.g
+    layout_ok = _is_channels_last(x) if g.x_layout == NHWC else x.is_contiguous()
+    if tuple(x.shape) != (g.N, g.C, g.H, g.W) or not layout_ok:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "ConvIntegerPacked: x does not match the packed geometry / layout")
+    if not packed.eligible:
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "ConvIntegerPacked: this geometry is not eligible for the packed tensor-core path")
+    zx, _ = _zp_scalar(x_zero_point)
+    y = torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.int32, device=x.device, memory_format=torch.channels_last)
+    ws_bytes = lib().chxq_conv_packed_workspace(ctypes.byref(g), zx, packed.flags)
+    ws = workspace(ws_bytes, x.device)
+    check(lib().chxq_conv_integer_packed(_ptr(x), _ptr(packed.blob), ctypes.byref(g), int(x_zero_point is not None), zx, packed.flags, _ptr(y),
+                                         _ptr(ws), ws_bytes, _stream()))
+    return y
+
+
 def QuantizeLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b=None, round_mode=ROUND_REF,
                              quant_round_mode=ROUND_REF, clamp_hi_q=None, out=None, fold_scales=False):
     """QuantizeLinear(x, x_scale, x_zero_point) fused into the packed QLinearConv that consumes it: x is the fp32 tensor (same

@@ -21,6 +21,13 @@ Quantize, then MergeConvBN (compiler/merge.cc:142-215) over the Conv nodes that 
 last two, so that a Conv + BatchNormalization pair is quantized as one convolution; the bias the merge creates is then added
 in fp32 after the scale-back Mul (the reference leaves a Conv with bias unquantized, compiler/quantize.cc:366-369).
 
+On a statically quantized graph two peepholes run unless `--no_peephole` is given: DequantizeLinear x2 + Add + [Relu] +
+QuantizeLinear (a residual join) becomes one uint8 kernel, and a QLinearConv whose only reader is such a join takes it into its
+epilogue; both keep every output bit.  Convolutions with constant weights are packed once and run on the tensor-core kernels
+over channels_last activations.  Options of this build beyond the reference's: `--fold_scales` (one fp32 multiplier per output
+channel in the requantization instead of a multiply and a divide; up to one output step of difference) and `--cuda_graph`
+(with -I > 1 a program without device-to-host reads is captured after the first iteration and replayed).
+
 Flags kept from the reference: positional or --test DIR / --onnx FILE, -d/--device, -I/--iterations, --rtol, --atol,
 --equal_nan, --no_check_values, --always_show_diff, --check_nans, --check_infs, --dump_outputs_dir (one
 `<instruction id, 5 digits>_<value name>.npy` per instruction output, runtime/chxvm.cc:70-92), --chrome_tracing FILE (one
@@ -120,10 +127,11 @@ def merge_conv_bn(nodes, consts, graph_outputs=(), only=None):
     return [n for n in out if id(n) not in dropped]
 
 
-def compile_model(model, quantize=False, per_channel=True, asymmetric_input_types=False, fold_bn_first=False, fuse=False):
+def compile_model(model, quantize=False, per_channel=True, asymmetric_input_types=False, fold_bn_first=False, fuse=False, peephole=True):
     """ONNX graph -> Program.  quantize: the reference's `--quantize` (dynamic, IntegerOps; weights uint8 unless
     asymmetric_input_types, which makes them int8: compiler/quantize.cc:392-400).  fuse: group elementwise float nodes into
-    ElementWiseNvrtc instructions (`--fuse_operations --use_nvrtc`)."""
+    ElementWiseNvrtc instructions (`--fuse_operations --use_nvrtc`).  peephole: True = fuse_quantized_add, then fuse_conv_residual;
+    "join" = the first only; False = neither."""
     nodes, consts = _fold_constants(model)
 
     def quantizable(n):
@@ -193,9 +201,105 @@ def compile_model(model, quantize=False, per_channel=True, asymmetric_input_type
         else:
             insts.append(Inst(n.op_type, n.inputs, n.outputs, **n.attrs))
     program = Program(insts, consts, list(model.inputs), list(model.outputs))
+    if peephole:
+        program = fuse_quantized_add(program)
+        if peephole != "join":
+            program = fuse_conv_residual(program)
     if fuse:
         program = fuse_elementwise(program)
     return program
+
+
+def fuse_quantized_add(program):
+    """Peephole over a statically quantized graph: DequantizeLinear(a), DequantizeLinear(b), Add, [Relu], QuantizeLinear with
+    single-use intermediates and constant scalar parameters -- the join of a residual block -- becomes one QAddU8
+    instruction (five full-tensor passes, three of them over fp32 data, become one uint8 pass).  The kernel evaluates the
+    same fp32 chain per element, so the result is bit-identical to the five nodes."""
+    insts = program.insts
+    users, producer = {}, {}
+    for k, i in enumerate(insts):
+        for v in i.inputs:
+            users.setdefault(v, []).append(k)
+        for v in i.outputs:
+            producer[v] = k
+    consts = program.constants
+
+    def scalar_const(name):
+        return name in consts and np.asarray(consts[name]).size == 1
+
+    def single_use(v):
+        return len(users.get(v, [])) == 1 and v not in program.outputs
+
+    replaced, drop = {}, set()
+    for k, q in enumerate(insts):
+        if q.op != "QuantizeLinear" or len(q.inputs) != 3 or not (scalar_const(q.inputs[1]) and scalar_const(q.inputs[2])):
+            continue
+        if np.asarray(consts[q.inputs[2]]).dtype != np.uint8:
+            continue
+        chain, v, relu = [], q.inputs[0], False
+        pk = producer.get(v)
+        if pk is not None and insts[pk].op == "Relu" and single_use(v):
+            relu, v = True, insts[pk].inputs[0]
+            chain.append(pk)
+            pk = producer.get(v)
+        if pk is None or insts[pk].op != "Add" or not single_use(v):
+            continue
+        add = insts[pk]
+        chain.append(pk)
+        dqs = [producer.get(t) for t in add.inputs]
+        if any(d is None or insts[d].op != "DequantizeLinear" or len(insts[d].inputs) != 3 or not single_use(t) for d, t in zip(dqs, add.inputs)):
+            continue
+        if dqs[0] == dqs[1]:
+            continue
+        if not all(scalar_const(insts[d].inputs[1]) and scalar_const(insts[d].inputs[2]) and np.asarray(consts[insts[d].inputs[2]]).dtype == np.uint8
+                   for d in dqs):
+            continue
+        a, b = insts[dqs[0]], insts[dqs[1]]
+        replaced[k] = Inst("QAddU8", [a.inputs[0], a.inputs[1], a.inputs[2], b.inputs[0], b.inputs[1], b.inputs[2], q.inputs[1], q.inputs[2]],
+                           q.outputs, relu=int(relu))
+        drop.update(chain + dqs)
+    if not replaced:
+        return program
+    new = [replaced.get(k, i) for k, i in enumerate(insts) if k not in drop]
+    return Program(new, program.constants, program.inputs, program.outputs)
+
+
+def fuse_conv_residual(program):
+    """Second peephole: a QLinearConv with constant weights whose only reader is a QAddU8 takes the join into its epilogue
+    (the residual map is read once, the convolution output never reaches memory).  The fused instruction sits where the
+    QAddU8 was, so the other operand is always computed before it.  Inputs 0-8 are QLinearConv's, 9-13 are the residual map,
+    its scale and zero point, and the join's output scale and zero point."""
+    insts = program.insts
+    users, producer = {}, {}
+    for k, i in enumerate(insts):
+        for v in i.inputs:
+            users.setdefault(v, []).append(k)
+        for v in i.outputs:
+            producer[v] = k
+    consts = program.constants
+    replaced, drop = {}, set()
+    for k, q in enumerate(insts):
+        if q.op != "QAddU8":
+            continue
+        for side in (0, 3):
+            v = q.inputs[side]
+            pk = producer.get(v)
+            if pk is None or pk in drop or insts[pk].op != "QLinearConv" or len(users.get(v, [])) != 1 or v in program.outputs:
+                continue
+            conv = insts[pk]
+            if conv.inputs[3] not in consts or conv.attrs.get("residual"):
+                continue
+            if [conv.inputs[6], conv.inputs[7]] != q.inputs[side + 1:side + 3]:  # the join must dequantize with the convolution's output parameters
+                continue
+            other = 3 - side
+            ins = list(conv.inputs) + [""] * (9 - len(conv.inputs)) + [q.inputs[other], q.inputs[other + 1], q.inputs[other + 2], q.inputs[6], q.inputs[7]]
+            replaced[k] = Inst("QLinearConv", ins, q.outputs, **dict(conv.attrs, residual=1, res_relu=int(q.attrs.get("relu", 0)), conv_output=v))
+            drop.add(pk)
+            break
+    if not replaced:
+        return program
+    new = [replaced.get(k, i) for k, i in enumerate(insts) if k not in drop]
+    return Program(new, program.constants, program.inputs, program.outputs)
 
 
 # ---- elementwise fusion over a program -----------------------------------------------------------------------------------
@@ -315,6 +419,27 @@ def program_to_onnx(program, name="graph"):
         elif i.op == "ElementWiseNvrtc":
             for op, ins, outs in i.attrs["members"]:
                 nodes.append(N(op, ins, outs, {}))
+        elif i.op == "QLinearConv" and i.attrs.get("residual"):
+            attrs = {k: v for k, v in i.attrs.items() if k not in ("residual", "res_relu", "conv_output") and v is not None
+                     and not (isinstance(v, (list, tuple)) and len(v) == 0)}
+            cin = [v for v in i.inputs[:9]]
+            while cin and cin[-1] == "":
+                cin.pop()
+            h = i.attrs["conv_output"]
+            nodes.append(N("QLinearConv", cin, [h], attrs))
+            nodes.append(N("DequantizeLinear", [h, i.inputs[6], i.inputs[7]], [t("fa")], {}))
+            nodes.append(N("DequantizeLinear", i.inputs[9:12], [t("fb")], {}))
+            nodes.append(N("Add", [t("fa"), t("fb")], [t("sum")], {}))
+            if i.attrs.get("res_relu"):
+                nodes.append(N("Relu", [t("sum")], [t("relu")], {}))
+            nodes.append(N("QuantizeLinear", [t("relu") if i.attrs.get("res_relu") else t("sum"), i.inputs[12], i.inputs[13]], i.outputs, {}))
+        elif i.op == "QAddU8":
+            nodes.append(N("DequantizeLinear", i.inputs[0:3], [t("fa")], {}))
+            nodes.append(N("DequantizeLinear", i.inputs[3:6], [t("fb")], {}))
+            nodes.append(N("Add", [t("fa"), t("fb")], [t("sum")], {}))
+            if i.attrs.get("relu"):
+                nodes.append(N("Relu", [t("sum")], [t("relu")], {}))
+            nodes.append(N("QuantizeLinear", [t("relu") if i.attrs.get("relu") else t("sum"), i.inputs[6], i.inputs[7]], i.outputs, {}))
         elif i.op == "Cast":
             to = i.attrs.get("to", 1)
             nodes.append(N("Cast", i.inputs, i.outputs, {"to": code_of[to] if isinstance(to, str) else int(to)}))
@@ -370,13 +495,16 @@ class ChromeTracing:
 class Executor:
     """Runs a Program on one CUDA device.  Quantized ops go through chainer_compiler_b200.ops; glue ops are torch expressions."""
 
-    def __init__(self, program, device="cuda:0", float_ops_via_torch=False):
+    def __init__(self, program, device="cuda:0", float_ops_via_torch=False, fold_scales=False):
+        """fold_scales: requantize every QLinearConv with one fp32 multiplier per output channel (x_scale * w_scale / y_scale
+        folded on the host) instead of the reference's multiply and divide; outputs can differ from the default by one step
+        on exact ties of the intermediate rounding."""
         import torch
         sys.path.insert(0, ROOT)
         import __graft_entry__ as entry
         entry.load_package()
-        from chainer_compiler_b200 import ops
-        self.torch, self.ops = torch, ops
+        from chainer_compiler_b200 import _lib, ops
+        self.torch, self.ops, self.NCHW = torch, ops, _lib.NCHW
         self.program, self.float_ok = program, float_ops_via_torch
         if not str(device).startswith("cuda"):
             raise SystemExit("run_onnx: device %r is not supported, this package runs on CUDA devices only" % (device,))
@@ -385,6 +513,9 @@ class Executor:
         for k, v in program.constants.items():
             self.consts[k] = torch.from_numpy(_contiguous(v)).to(self.device)
         self.host_consts = program.constants
+        self.packed = {}
+        self.fold_scales = bool(fold_scales)
+        self._graph = None
 
     def _scalar(self, name, env, host):
         """A Scalar operand on the host, keeping its dtype (the zero point's dtype selects the output dtype)."""
@@ -398,6 +529,55 @@ class Executor:
             raise ValueError("run_onnx: %s must have one element, has shape %s" % (name, v.shape))
         return v.reshape(())[()]
 
+    _SCALAR_OPERANDS = {"QuantizeLinear": (1, 2), "DequantizeLinear": (1, 2), "QLinearConv": (1, 2, 6, 7, 10, 11, 12, 13), "QLinearMatMul": (1, 2, 4, 5, 6, 7),
+                        "ConvInteger": (2,), "QAddU8": (1, 2, 4, 5, 6, 7), "Clip": (1, 2), "Reshape": (1,)}
+
+    def stage(self, v):
+        """An input array on the device (the reference stages the inputs before it starts the clock, tools/run_onnx.cc:421-427)."""
+        t = self.torch
+        return v.to(self.device) if isinstance(v, t.Tensor) else t.from_numpy(_contiguous(v)).to(self.device)
+
+    def is_static(self):
+        """True when running the program needs no device-to-host read: every scalar operand is an initializer and there is no
+        dynamic-quantization instruction.  Such a program can be captured in a CUDA graph."""
+        for inst in self.program.insts:
+            if inst.op in ("ReduceMinMax", "DynamicQuantParamsU8", "ReduceMin", "ReduceMax"):
+                return False
+            for k in self._SCALAR_OPERANDS.get(inst.op, ()):
+                if k < len(inst.inputs) and inst.inputs[k] != "" and inst.inputs[k] not in self.host_consts:
+                    return False
+        return True
+
+    def capture(self, inputs):
+        """Captures one run over device copies of `inputs` in a CUDA graph (static programs only).  Afterwards replay(inputs)
+        copies new input values into the captured buffers, replays, and returns the (captured) output tensors.  The library's
+        scratch buffer must not grow after the capture: run every other workload of the process first."""
+        t = self.torch
+        if not self.is_static():
+            raise ValueError("run_onnx: the program reads scalars back from the device and cannot be captured")
+        self._static_in = {k: self.stage(v).clone() for k, v in inputs.items()}
+        host = {}
+        for _ in range(2):  # warm-up: packs the weights, sizes the scratch buffer, compiles generated kernels
+            env = dict(self.consts, **self._static_in)
+            for inst in self.program.insts:
+                self._step(inst, env, host)
+        t.cuda.synchronize(self.device)
+        self._graph = t.cuda.CUDAGraph()
+        with t.cuda.graph(self._graph):
+            env = dict(self.consts, **self._static_in)
+            for inst in self.program.insts:
+                self._step(inst, env, host)
+            self._static_out = [(o, env[o]) for o in self.program.outputs]
+        return self
+
+    def replay(self, inputs):
+        t = self.torch
+        for k, v in inputs.items():
+            self._static_in[k].copy_(v if isinstance(v, t.Tensor) else t.from_numpy(_contiguous(v)), non_blocking=True)
+        self._graph.replay()
+        self.ops.device_status()
+        return self._static_out
+
     def run(self, inputs, trace=None, tracer=None, log=None):
         """trace: a dict that receives every instruction output; tracer: a ChromeTracing; log: a file the instructions are
         printed to as they run (`--trace`)."""
@@ -405,7 +585,7 @@ class Executor:
         env = dict(self.consts)
         host = {}  # host-side scalars (dynamic quantization parameters)
         for k, v in inputs.items():
-            env[k] = t.from_numpy(_contiguous(v)).to(self.device)
+            env[k] = self.stage(v)
         for pc, inst in enumerate(self.program.insts):
             if log is not None:
                 log.write("%5d: %r\n" % (pc, inst))
@@ -444,10 +624,51 @@ class Executor:
             if any(d != 1 for d in a.get("dilations", [])):
                 raise NotImplementedError("%s: dilation must be 1 (compiler/chxvm/simple_node_emitter.cc:655)" % op)
             strides, pads, group = tuple(a.get("strides", [])), self._sym_pads(a.get("pads", [])), a.get("group", 1)
+            wk, zk = (1, 3) if op == "ConvInteger" else (3, 5)
+            xin, packed = x[0], None
+            if xin.dim() == 4 and xin.dtype == t.uint8 and inst.inputs[wk] in self.host_consts and (not has(zk) or inst.inputs[zk] in self.host_consts):
+                # constant weights: pack them once per input shape and keep the activations channels_last, which is the layout
+                # the tensor-core kernels read (the first convolution of a graph pays one layout pass)
+                # (a network stem with at most four input channels is read as NCHW by the packed entry itself)
+                wz = x[zk] if has(zk) else None
+                key = (id(inst), tuple(xin.shape))
+                packed = self.packed.get(key)
+                if packed is None:
+                    if xin.shape[1] <= 4 and xin.is_contiguous():
+                        packed = ops.PackedConv(x[wk], wz, tuple(xin.shape), strides, pads, group, auto_pad, x_layout=self.NCHW)
+                    if packed is None or not packed.eligible:
+                        packed = ops.PackedConv(x[wk], wz, tuple(xin.shape), strides, pads, group, auto_pad)
+                    self.packed[key] = packed
+                if packed.g.x_layout != self.NCHW:
+                    xin = ops.to_channels_last(xin)
+                if not packed.eligible:
+                    packed = None
             if op == "ConvInteger":
-                env[out] = ops.ConvInteger(x[0], x[1], sc(2) if has(2) else None, x[3] if has(3) else None, strides, pads, group, auto_pad)
+                if packed is not None:
+                    env[out] = ops.ConvIntegerPacked(xin, packed, sc(2) if has(2) else None)
+                else:
+                    env[out] = ops.ConvInteger(xin, x[1], sc(2) if has(2) else None, x[3] if has(3) else None, strides, pads, group, auto_pad)
             else:
-                env[out] = ops.QLinearConv(x[0], sc(1), sc(2), x[3], x[4], x[5], sc(6), sc(7), x[8] if has(8) else None, strides, pads, group, auto_pad)
+                res = {}
+                if a.get("residual"):
+                    r = ops.to_channels_last(x[9]) if x[9].dim() == 4 else x[9]
+                    if int(sc(13)) != 0:
+                        raise NotImplementedError("QLinearConv with a fused join: the join's output zero point must be 0")
+                    res = dict(residual=r, res_scale=sc(10), res_zero_point=int(sc(11)), res_relu=bool(a.get("res_relu", 0)), out_scale=sc(12),
+                               out_zero_point=0)
+                    if xin.dim() == 4 and packed is None:
+                        xin = ops.to_channels_last(xin)  # the residual map and the output share the NHWC layout
+                if packed is not None:
+                    env[out] = ops.QLinearConvPacked(xin, packed, sc(1), sc(2), x[4], x[5], sc(6), sc(7), b=x[8] if has(8) else None,
+                                                     fold_scales=self.fold_scales, **res)
+                else:
+                    env[out] = ops.QLinearConv(xin, sc(1), sc(2), x[3], x[4], x[5], sc(6), sc(7), x[8] if has(8) else None, strides, pads, group,
+                                               auto_pad, fold_scales=self.fold_scales, **res)
+        elif op == "QAddU8":
+            qa, qb = x[0], x[3]
+            if qa.stride() != qb.stride():  # one operand came from a kernel of the other layout
+                qa, qb = (ops.to_channels_last(qa), ops.to_channels_last(qb)) if qa.dim() == 4 else (qa.contiguous(), qb.contiguous())
+            env[out] = ops.QAddU8(qa, sc(1), sc(2), qb, sc(4), sc(5), sc(6), sc(7), relu=bool(a.get("relu", 0)))
         elif op == "MatMulInteger":
             def zp_arr(k, like):
                 if not has(k):
@@ -499,12 +720,21 @@ class Executor:
             p = _pool_pads(a, len(k))
             if any(p[i] != p[i + len(k)] for i in range(len(k))):
                 raise NotImplementedError("MaxPool: asymmetric pads")
-            env[out] = t.nn.functional.max_pool2d(x[0], k, s, p[:len(k)])
+            ceil = bool(a.get("ceil_mode", 0))
+            if x[0].dtype == t.uint8:
+                if len(k) != 2 or k[0] != k[1] or s[0] != s[1] or len(set(p)) != 1:
+                    raise NotImplementedError("uint8 MaxPool with a non-square window")
+                env[out] = ops.MaxPoolU8(ops.to_channels_last(x[0]), k[0], s[0], p[0], cover_all=ceil)
+            else:
+                env[out] = t.nn.functional.max_pool2d(x[0], k, s, p[:len(k)], ceil_mode=ceil)
         elif op == "GlobalAveragePool":
             env[out] = x[0].mean(dim=tuple(range(2, x[0].dim())), keepdim=True)
         elif op == "Flatten":
             ax = a.get("axis", 1)
             env[out] = x[0].reshape(int(np.prod(x[0].shape[:ax])), -1)
+        elif op == "Gemm" and a.get("transB", 0) and not a.get("transA", 0) and a.get("alpha", 1.0) == 1.0 and a.get("beta", 1.0) == 1.0 \
+                and x[0].dtype == t.float32 and x[0].dim() == 2:
+            env[out] = ops.Linear(x[0].contiguous(), x[1].contiguous(), x[2] if has(2) else None)  # the classifier of a quantized CNN
         elif op in ("Conv", "MatMul", "Gemm"):
             if not self.float_ok:
                 raise SystemExit("run_onnx: float %s has no kernel in this package; run with --quantize (or --float_ops_via_torch to "
@@ -565,6 +795,9 @@ def parse_args(argv):
     ap.add_argument("--quantize", action="store_true")
     ap.add_argument("--disable_per_channel_quantize", action="store_true")
     ap.add_argument("--fold_bn_first", action="store_true")
+    ap.add_argument("--fold_scales", action="store_true")
+    ap.add_argument("--cuda_graph", action="store_true")
+    ap.add_argument("--no_peephole", action="store_true")
     ap.add_argument("--fuse_operations", action="store_true")
     ap.add_argument("--use_nvrtc", action="store_true")
     ap.add_argument("--use_cuda", action="store_true")
@@ -597,7 +830,8 @@ def run_onnx(argv):
         model, cases = onnx_io.load_test_dir(target)
     else:
         model, cases = onnx_io.load_model(target), []
-    unfused = compile_model(model, quantize=args.quantize, per_channel=not args.disable_per_channel_quantize, fold_bn_first=args.fold_bn_first)
+    unfused = compile_model(model, quantize=args.quantize, per_channel=not args.disable_per_channel_quantize, fold_bn_first=args.fold_bn_first,
+                            peephole=not args.no_peephole)
     # the reference fuses for NVRTC only when both flags are given (compiler/passes.cc: fusion needs a code generator)
     program = fuse_elementwise(unfused) if (args.fuse_operations and args.use_nvrtc) else unfused
     if args.dump_onnx or args.out_onnx:
@@ -612,15 +846,25 @@ def run_onnx(argv):
     if args.compile_only or args.skip_inference:
         return 0
     import torch
-    ex = Executor(program, args.device, args.float_ops_via_torch)
+    ex = Executor(program, args.device, args.float_ops_via_torch, fold_scales=args.fold_scales)
     tracer = ChromeTracing() if args.chrome_tracing else None
+    # --cuda_graph: after the first (discarded) iteration of a case the remaining ones replay a captured graph
+    use_graph = args.cuda_graph and args.iterations > 1 and ex.is_static() and not (args.chrome_tracing or args.dump_outputs_dir or args.trace)
     failures, elapsed, report = 0, [], []
     for ci, (ins, expected) in enumerate(cases):
         outs, values = None, ({} if args.dump_outputs_dir else None)
+        ins = {k: ex.stage(v) for k, v in ins.items()}
         for it in range(max(1, args.iterations)):
             torch.cuda.synchronize(ex.device)
             t0 = time.perf_counter()
-            outs = ex.run(ins, trace=values, tracer=tracer, log=sys.stderr if args.trace else None)
+            if use_graph and it == 1:
+                ex.capture(ins)
+                torch.cuda.synchronize(ex.device)
+                t0 = time.perf_counter()
+            if use_graph and it >= 1:
+                outs = ex.replay(ins)
+            else:
+                outs = ex.run(ins, trace=values, tracer=tracer, log=sys.stderr if args.trace else None)
             torch.cuda.synchronize(ex.device)
             if it > 0 or args.iterations == 1:  # the first iteration is discarded when there are several (tools/run_onnx.cc:468-469)
                 elapsed.append(time.perf_counter() - t0)
@@ -656,10 +900,12 @@ def run_onnx(argv):
     avg_ms = 1000.0 * float(np.mean(elapsed)) if elapsed else 0.0
     if not args.quiet:
         print("Elapsed: %.3f msec" % avg_ms)
+        if len(elapsed) > 1:
+            sys.stderr.write("Average elapsed: %.3f msec\nBest elapsed: %.3f msec\n" % (avg_ms, 1000.0 * min(elapsed)))
         print("OK!" if failures == 0 else "FAILED: %d output(s) out of tolerance" % failures)
     if args.report_json:
         with open(args.report_json, "w") as f:
-            json.dump({"elapsed_ms": avg_ms, "failures": failures, "outputs": report, "quantize": bool(args.quantize)}, f)
+            json.dump({"elapsed_ms": avg_ms, "best_ms": 1000.0 * min(elapsed) if elapsed else 0.0, "cuda_graph": bool(use_graph), "failures": failures, "outputs": report, "quantize": bool(args.quantize)}, f)
     return 0 if failures == 0 else 1
 
 

@@ -108,15 +108,17 @@ _ONNX_DTYPE = {1: np.float32, 2: np.uint8, 3: np.int8, 5: np.int16, 6: np.int32,
 _EW = {"Add": np.add, "Sub": np.subtract, "Mul": np.multiply, "Tanh": np.tanh, "Sigmoid": _sigmoid, "Exp": np.exp, "Identity": lambda v: v}
 
 
-def run_program(program, inputs, trace=None):
+def run_program(program, inputs, trace=None, conv_mode="emulate"):
     """CPU evaluation of a `run_onnx` program (the instruction list `chainer-compiler_b200/run_onnx.py::compile_model`
     produces) with the oracle's ops: the checker for the quantized graph the reference's `--quantize` pass builds
     (compiler/quantize.cc:142-281).  program: an object with .insts (op, inputs, outputs, attrs), .constants (numpy),
-    .outputs.  Glue ops are numpy expressions."""
+    .outputs.  Glue ops are numpy expressions.  conv_mode: how a QLinearConv node is evaluated -- "emulate" as the reference
+    does (dequantize, fp32 convolution, quantize), "exact" by requantizing the exact int32 accumulator (the arithmetic of the
+    CUDA kernels; the two agree within one step of the output scale)."""
     env = dict(program.constants)
     env.update({k: np.asarray(v) for k, v in inputs.items()})
     for inst in program.insts:
-        a, x, op = inst.attrs, [env[i] for i in inst.inputs], inst.op
+        a, x, op = inst.attrs, [env[i] if i != "" else None for i in inst.inputs], inst.op
         if op == "ReduceMinMax":
             out = [np.float32(x[0].min()), np.float32(x[0].max())]
         elif op == "DynamicQuantParamsU8":
@@ -139,8 +141,17 @@ def run_program(program, inputs, trace=None):
                 out = [orc.conv_integer(x[0], x[1], zx, zw, strides, pads, group, auto_pad)]
             else:
                 zy = np.asarray(x[7]).reshape(())
-                out = [orc.qlinear_conv(x[0], _f32(x[1]), int(np.asarray(x[2]).reshape(())), x[3], np.asarray(x[4], np.float32), np.asarray(x[5]),
-                                        _f32(x[6]), zy[()], x[8] if len(x) > 8 else None, strides, pads, group, auto_pad)]
+                bias = x[8] if len(x) > 8 and inst.inputs[8] != "" else None
+                if conv_mode == "exact":
+                    acc = orc.conv_integer(x[0], x[3], int(np.asarray(x[2]).reshape(())), np.asarray(x[5]).astype(np.int32).reshape(-1), strides, pads, group, auto_pad)
+                    out = [orc.requantize(acc, _f32(x[1]), np.asarray(x[4], np.float32), _f32(x[6]), int(zy), bias=bias, channel_axis=1, y_dtype=zy.dtype.type)]
+                else:
+                    out = [orc.qlinear_conv(x[0], _f32(x[1]), int(np.asarray(x[2]).reshape(())), x[3], np.asarray(x[4], np.float32), np.asarray(x[5]),
+                                            _f32(x[6]), zy[()], bias, strides, pads, group, auto_pad)]
+                if a.get("residual"):
+                    # the join run_onnx's second peephole moved into the convolution: DequantizeLinear x2, Add, [Relu], QuantizeLinear
+                    out = [orc.qadd_relu(out[0], _f32(x[6]), int(zy), x[9], _f32(x[10]), int(np.asarray(x[11]).reshape(())), _f32(x[12]),
+                                         int(np.asarray(x[13]).reshape(())), relu=bool(a.get("res_relu", 0)))]
         elif op == "MatMulInteger":
             out = [orc.matmul_integer(x[0], x[1], np.asarray(x[2]).reshape(-1) if len(x) > 2 else None,
                                       np.asarray(x[3]).reshape(-1) if len(x) > 3 else None)]
@@ -179,6 +190,25 @@ def run_program(program, inputs, trace=None):
         elif op == "Reshape":
             shape = [x[0].shape[i] if d == 0 else int(d) for i, d in enumerate(x[1])]
             out = [x[0].reshape(shape)]
+        elif op == "QAddU8":
+            # DequantizeLinear, DequantizeLinear, Add, [Relu], QuantizeLinear as run_onnx's peephole groups them
+            out = [orc.qadd_relu(x[0], _f32(x[1]), int(np.asarray(x[2]).reshape(())), x[3], _f32(x[4]), int(np.asarray(x[5]).reshape(())), _f32(x[6]),
+                                 int(np.asarray(x[7]).reshape(())), relu=bool(a.get("relu", 0)))]
+        elif op == "GlobalAveragePool":
+            out = [x[0].astype(np.float32).mean(axis=tuple(range(2, x[0].ndim)), keepdims=True, dtype=np.float32)]
+        elif op == "Flatten":
+            ax = a.get("axis", 1)
+            out = [x[0].reshape(int(np.prod(x[0].shape[:ax])), -1)]
+        elif op == "Gemm":
+            if a.get("transA", 0) or not a.get("transB", 0) or a.get("alpha", 1.0) != 1.0 or a.get("beta", 1.0) != 1.0:
+                raise NotImplementedError("Gemm other than x . w^T + b")
+            out = [orc.linear_f32(x[0], x[1], x[2] if len(x) > 2 else None)]
+        elif op == "MaxPool" and x[0].dtype == np.uint8:
+            k, s = a["kernel_shape"], a.get("strides", [1, 1])
+            p = list(a.get("pads", [0, 0, 0, 0]))
+            if k[0] != k[1] or s[0] != s[1] or len(set(p)) != 1:
+                raise NotImplementedError("uint8 MaxPool with a non-square window")
+            out = [orc.maxpool_u8(x[0], k[0], s[0], p[0], cover_all=bool(a.get("ceil_mode", 0)))]
         elif op == "MaxPool":
             k, s = a["kernel_shape"], a.get("strides", [1, 1])
             N, C, H, W = x[0].shape

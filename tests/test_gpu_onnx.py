@@ -123,3 +123,64 @@ def test_exported_graph_and_bn_folding_on_the_device(pkg, tmp_path):
         (_, y), = run_onnx.Executor(p, "cuda:0").run({"x": x})
         err = (y.cpu() - want).abs().max().item()
         assert err < 0.05 * want.abs().max().item(), (first, err)
+
+
+def test_statically_quantized_resnet_file_runs_on_the_tensor_core_kernels(pkg, ops, orc, tmp_path):
+    """models.ResNet50Int8.to_onnx(): the calibrated network as a standard ONNX file, executed by run_onnx (packed weights,
+    channels_last activations, residual joins as one kernel) against the oracle's evaluation of the same file."""
+    import torch
+    from chainer_compiler_b200 import models, onnx_io, run_onnx
+    from oracle import networks
+    dev = torch.device("cuda:0")
+    net = models.ResNet50Int8(2, dev, seed=3, image=64, width_mult=0.25)
+    x = torch.rand((2, 3, 64, 64), generator=torch.Generator().manual_seed(4))
+    net.calibrate(x.to(dev))
+    want = net.forward(x.to(dev), fused=False).cpu().numpy()
+    model = net.to_onnx()
+    d = str(tmp_path / "resnet")
+    onnx_io.write_test_dir(d, model, [({"x": x.numpy()}, [("logits", want)])])
+    # the hand-built forward() pools the uint8 map and dequantizes the mean; the file dequantizes, then pools: fp32 rounding only
+    atol = "%g" % (1e-5 * float(np.abs(want).max()))
+    assert run_onnx.run_onnx(["--test", d, "--rtol", "1e-4", "--atol", atol, "-q"]) == 0
+    launches = pkg._lib.lib().chxq_launch_count()
+    model2, cases = onnx_io.load_test_dir(d)
+    prog = run_onnx.compile_model(model2)
+    # all 16 residual joins moved into the epilogue of the block's last convolution
+    assert sum(i.op == "QAddU8" for i in prog.insts) == 0 and sum(i.op == "QLinearConv" for i in prog.insts) == 53
+    assert sum(bool(i.attrs.get("residual")) for i in prog.insts) == 16
+    assert sum(i.op == "QAddU8" for i in run_onnx.compile_model(model2, peephole="join").insts) == 16
+    ex = run_onnx.Executor(prog, "cuda:0")
+    gt, ot = {}, {}
+    (_, got), = ex.run(cases[0][0], trace=gt)
+    assert all(p.eligible for p in ex.packed.values()) and len(ex.packed) == 53     # every convolution ran from packed weights
+    assert pkg._lib.lib().chxq_launch_count() > launches
+    (_, ref), = networks.run_program(prog, cases[0][0], trace=ot, conv_mode="exact")
+    for inst in prog.insts:
+        o = inst.outputs[0]
+        g = gt[o].cpu().numpy()
+        if g.dtype == np.uint8:
+            assert np.array_equal(g, ot[o]), (inst.op, o)
+        else:
+            assert np.allclose(g, ot[o], rtol=1e-5, atol=1e-5 * float(np.abs(ot[o]).max())), (inst.op, o)
+    assert np.allclose(got.cpu().numpy(), ref, rtol=1e-5, atol=1e-5 * float(np.abs(ref).max()))
+    # without the peepholes (five-node joins), and with the join as its own kernel, the same bits
+    for level in (False, "join"):
+        ex2 = run_onnx.Executor(run_onnx.compile_model(model2, peephole=level), "cuda:0")
+        (_, got2), = ex2.run(cases[0][0])
+        assert torch.equal(got, got2), level
+    # a captured graph replays to the same bits, also on new input values
+    assert ex.is_static()
+    ex.capture(cases[0][0])
+    (_, got3), = ex.replay(cases[0][0])
+    assert torch.equal(got, got3)
+    x2 = torch.rand((2, 3, 64, 64), generator=torch.Generator().manual_seed(5)).numpy()
+    (_, eager), = run_onnx.Executor(prog, "cuda:0").run({"x": x2})
+    (_, replayed), = ex.replay({"x": x2})
+    assert torch.equal(eager, replayed)
+    assert run_onnx.run_onnx(["--test", d, "--rtol", "1e-4", "--atol", atol, "-q", "-I", "3", "--cuda_graph"]) == 0
+    # single-multiplier requantization: the quantized maps of the hand-built folded forward, bit for bit
+    taps, gt = {}, {}
+    net.forward(x.to(dev), fused=True, fold=True, taps=taps)
+    run_onnx.Executor(prog, "cuda:0", fold_scales=True).run(cases[0][0], trace=gt)
+    assert torch.equal(gt["stem"], taps["stem"]) and all(torch.equal(gt["b%d_out" % i], taps["block%d" % i]) for i in range(16))
+    assert not run_onnx.Executor(run_onnx.compile_model(onnx_io.load_test_dir(GOLDEN)[0], quantize=True), "cuda:0").is_static()

@@ -215,3 +215,53 @@ def test_compare_dump_dirs(mods, tmp_path):
     text = log.getvalue()
     assert "y: OK" in text and "x: 1 of 12 elements differ" in text and "only_here" not in text
     assert compare_dump_dirs.compare(str(a), str(b), atol=1.0, out=io.StringIO()) == 0
+
+
+def _residual_join_model(onnx_io, rng):
+    N, f32, u8, i8 = onnx_io.Node, np.float32, np.uint8, np.int8
+    inits = {"s_in": f32(1 / 64.0).reshape(()), "z0": u8(0).reshape(()), "z9": u8(9).reshape(()),
+             "w1": rng.integers(-127, 128, (16, 16, 3, 3), dtype=i8), "ws1": rng.uniform(0.001, 0.003, 16).astype(f32), "wz1": np.zeros(16, i8),
+             "w2": rng.integers(-127, 128, (16, 16, 1, 1), dtype=i8), "ws2": rng.uniform(0.001, 0.003, 16).astype(f32), "wz2": np.zeros(16, i8),
+             "b2": rng.integers(-500, 500, 16).astype(np.int32),
+             "s1": f32(0.02).reshape(()), "s2": f32(0.03).reshape(()), "s_out": f32(0.05).reshape(())}
+    nodes = [N("QuantizeLinear", ["x", "s_in", "z0"], ["xq"], {}),
+             N("QLinearConv", ["xq", "s_in", "z0", "w1", "ws1", "wz1", "s1", "z0"], ["h1"], {"kernel_shape": [3, 3], "pads": [1, 1, 1, 1]}),
+             N("QLinearConv", ["h1", "s1", "z0", "w2", "ws2", "wz2", "s2", "z9", "b2"], ["h2"], {"kernel_shape": [1, 1]}),
+             N("DequantizeLinear", ["h2", "s2", "z9"], ["f2"], {}),
+             N("DequantizeLinear", ["xq", "s_in", "z0"], ["fx"], {}),
+             N("Add", ["f2", "fx"], ["sum"], {}),
+             N("Relu", ["sum"], ["r"], {}),
+             N("QuantizeLinear", ["r", "s_out", "z0"], ["yq"], {}),
+             N("DequantizeLinear", ["yq", "s_out", "z0"], ["y"], {})]
+    return onnx_io.Model(nodes, inits, ["x"], ["y"], ir_version=5, opset=10)
+
+
+def test_residual_join_peephole_keeps_every_bit(mods):
+    onnx_io, run_onnx = mods
+    entry.load_oracle()
+    from oracle import networks
+    rng = np.random.default_rng(12)
+    model = _residual_join_model(onnx_io, rng)
+    plain = run_onnx.compile_model(model, peephole=False)
+    fused = run_onnx.compile_model(model, peephole="join")
+    both = run_onnx.compile_model(model)
+    assert [i.op for i in fused.insts] == ["QuantizeLinear", "QLinearConv", "QLinearConv", "QAddU8", "DequantizeLinear"]
+    assert fused.insts[3].attrs["relu"] == 1 and fused.insts[3].inputs[0] == "h2" and fused.insts[3].inputs[3] == "xq"
+    # the convolution whose only reader is the join takes it into its epilogue
+    assert [i.op for i in both.insts] == ["QuantizeLinear", "QLinearConv", "QLinearConv", "DequantizeLinear"]
+    assert both.insts[2].attrs["residual"] == 1 and both.insts[2].inputs[9:] == ["xq", "s_in", "z0", "s_out", "z0"] and both.insts[2].outputs == ["yq"]
+    x = rng.uniform(0, 3.9, (2, 16, 9, 9)).astype(np.float32)
+    for mode in ("emulate", "exact"):
+        ta, tb, tc = {}, {}, {}
+        (_, a), = networks.run_program(plain, {"x": x}, trace=ta, conv_mode=mode)
+        (_, b), = networks.run_program(fused, {"x": x}, trace=tb, conv_mode=mode)
+        (_, c), = networks.run_program(both, {"x": x}, trace=tc, conv_mode=mode)
+        assert np.array_equal(ta["yq"], tb["yq"]) and np.array_equal(a, b) and ta["yq"].max() > 0
+        assert np.array_equal(ta["yq"], tc["yq"]) and np.array_equal(a, c)
+    # the export writes the join back as the five standard nodes
+    for prog in (fused, both):
+        kinds = [n.op_type for n in run_onnx.program_to_onnx(prog).nodes]
+        assert kinds == [n.op_type for n in model.nodes]
+    # a second reader of an intermediate value, or a non-constant scale, blocks the rewrite
+    model.outputs = ["y", "sum"]
+    assert "QAddU8" not in [i.op for i in run_onnx.compile_model(model).insts]
