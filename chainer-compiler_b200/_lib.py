@@ -97,6 +97,8 @@ SIGNATURES = {
     "chxq_conv_prepack": (_c.c_int, [_vp, _c.POINTER(ConvGeom), _vp, _i64, _vp, _sz, _c.POINTER(_i32), _vp]),
     "chxq_qlinear_conv_packed": (_c.c_int, [_vp, _vp, _c.POINTER(ConvGeom), _c.POINTER(QConvParams), _i32, _vp, _vp, _sz, _vp]),
     "chxq_quantize_qlinear_conv_packed": (_c.c_int, [_vp, _i32, _vp, _c.POINTER(ConvGeom), _c.POINTER(QConvParams), _i32, _vp, _vp, _sz, _vp]),
+    "chxq_qlinear_conv_maxpool_packed": (_c.c_int, [_vp, _i32, _i32, _vp, _c.POINTER(ConvGeom), _c.POINTER(QConvParams), _i32, _i32, _i32, _i32, _i32, _vp,
+                                                   _vp, _sz, _vp]),
     "chxq_conv_integer_packed": (_c.c_int, [_vp, _vp, _c.POINTER(ConvGeom), _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "chxq_eltwise_codegen": (_c.c_int, [_c.POINTER(EwNode), _i32, _c.POINTER(_i32), _i32, _c.POINTER(_i32), _i32, _c.POINTER(_c.c_char_p), _i32,
                                         _i32, _i32, _c.c_char_p, _sz, _c.POINTER(_sz)]),

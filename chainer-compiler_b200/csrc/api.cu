@@ -161,6 +161,10 @@ __global__ void __launch_bounds__(256) conv_possum_kernel(
 // activation zero point, unused bytes hold zero (their weights are zero).
 // kQuant: the input is the fp32 tensor in front of a QuantizeLinear (scale qs, zero point qzp, reference rounding) that is
 // applied on the fly, with the arithmetic of quantize_one, so that the uint8 map never exists in memory.
+// Fused max pooling (kernel 3, stride 2, no padding) of a convolution's uint8 output: extents of the pooled map.
+struct PoolSpec {
+    int ho, wo;
+};
 struct S2dQuant {
     float scale, zp_f;
     int has_zp, round_mode;
@@ -457,7 +461,7 @@ int pack_weights(const void* w, const chxq_conv_geom& g, const TcConvPlan& pl, c
 // Runs a planned convolution on the tensor-core kernel from a packed weight blob.
 int conv_tc_run(
         const void* x, const uint8_t* blob, const chxq_conv_geom& g, const TcConvPlan& pl, int x_zp, bool zw_zero, const EpiArgs& epi, void* y,
-        uint8_t* scratch, size_t scratch_bytes, cudaStream_t s, const S2dQuant* quant_in = nullptr) {
+        uint8_t* scratch, size_t scratch_bytes, cudaStream_t s, const S2dQuant* quant_in = nullptr, const PoolSpec* pool = nullptr) {
     const ConvWs L = conv_ws_layout(g, pl);
     const int taps = g.KH * g.KW;
     const int64_t rows = (int64_t)g.N * g.Ho * g.Wo;
@@ -522,7 +526,7 @@ int conv_tc_run(
             CHXQ_LAUNCH_CHECK();
         }
         p.a = x; p.C = g.C; p.a_cs = xcs;
-        if (pl.Wb == 128 && taps == 1) {
+        if (pl.Wb == 128 && taps == 1 && !pool) {  // a 1x1 convolution over the flattened map (the pooling form needs the image structure)
             p.W = (int)((int64_t)g.N * g.H * g.W); p.H = 1; p.N = 1;
             p.Wo = (int)rows; p.Ho = 1; p.No = 1;
         } else {
@@ -543,6 +547,12 @@ int conv_tc_run(
     p.row_corr = zw_zero ? nullptr : rowsum;
     p.epi = epi;
     p.alg_macs = (double)rows * g.M * (g.C / g.group) * taps;
+    if (pool) {
+        if (!(pl.path == kTcS2d || (pl.path == kTcDirect && !im2col)) || p.No != g.N || epi.mode != kEpiRequant)
+            return set_error(CHXQ_ERR_UNSUPPORTED, "fused max pooling: the convolution must run on the direct or space-to-depth tensor-core path");
+        p.Wb = 16; p.Hb = 8; p.Nb = 1;  // the pooling form's tiles, whatever the output extents (edges are masked)
+        p.pool_ho = pool->ho; p.pool_wo = pool->wo;
+    }
     return launch_tc_igemm(p, s);
 }
 
@@ -923,6 +933,39 @@ extern "C" int chxq_quantize_qlinear_conv_packed(
     const S2dQuant qz{p->x_scale, (float)p->x_zero_point, p->x_zero_point != 0, quant_round_mode, make_qdiv(p->x_scale)};
     return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, p->x_zero_point, (packed_flags & 2) != 0, epi, y,
                        static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream), &qz);
+}
+
+// QLinearConv (with its QuantizeLinear in front when x_is_f32) followed by MaxPool(kernel 3, stride 2, pad 0) as one kernel.
+extern "C" int chxq_qlinear_conv_maxpool_packed(
+        const void* x, int32_t x_is_f32, int32_t quant_round_mode, const void* packed, const chxq_conv_geom* g, const chxq_qconv_params* p,
+        int32_t packed_flags, int32_t pool_kernel, int32_t pool_stride, int32_t pool_pad, int32_t cover_all, void* y, void* workspace,
+        size_t workspace_bytes, void* stream) {
+    const char* op = "QLinearConv+MaxPool(packed)";
+    TcConvPlan pl;
+    int rc = packed_common(op, x, packed, g, packed_flags, &pl);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(y != nullptr, "%s: null output", op);
+    if (pool_kernel != 3 || pool_stride != 2 || pool_pad != 0)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "%s: only kernel 3, stride 2, pad 0 pooling is fused", op);
+    EpiArgs epi;
+    rc = fill_requant(op, p, g, &epi);
+    if (rc != CHXQ_OK) return rc;
+    if (epi.residual != nullptr || epi.rq.y_signed) return set_error(CHXQ_ERR_UNSUPPORTED, "%s: uint8 output without a residual only", op);
+    const int extra = cover_all ? 1 : 0;
+    if (g->Ho < 3 || g->Wo < 3) return set_error(CHXQ_ERR_UNSUPPORTED, "%s: the convolution's output is smaller than the pooling window", op);
+    const PoolSpec pool{(g->Ho - 3 + extra) / 2 + 1, (g->Wo - 3 + extra) / 2 + 1};
+    if (x_is_f32) {
+        CHXQ_CHECK_ARG(g->x_dtype == CHXQ_UINT8, "%s: the quantized activation type must be uint8", op);
+        CHXQ_CHECK_ARG(quant_round_mode == CHXQ_ROUND_REF_HALF_UP || quant_round_mode == CHXQ_ROUND_RNE, "%s: bad rounding mode", op);
+        if (pl.path != kTcS2d)
+            return set_error(CHXQ_ERR_UNSUPPORTED, "%s: only stride-2 convolutions over at most 4 channels fuse their QuantizeLinear", op);
+        CHXQ_CHECK_ARG(p->x_zero_point >= 0 && p->x_zero_point <= 255 && p->x_scale > 0.f, "%s: bad activation scale / zero point", op);
+        const S2dQuant qz{p->x_scale, (float)p->x_zero_point, p->x_zero_point != 0, quant_round_mode, make_qdiv(p->x_scale)};
+        return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, p->x_zero_point, (packed_flags & 2) != 0, epi, y,
+                           static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream), &qz, &pool);
+    }
+    return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, p->x_zero_point, (packed_flags & 2) != 0, epi, y,
+                       static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream), nullptr, &pool);
 }
 
 extern "C" int chxq_conv_integer_packed(

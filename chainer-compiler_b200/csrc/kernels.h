@@ -74,6 +74,9 @@ struct TcProblem {
     const int32_t* row_corr;
     EpiArgs epi;
     double alg_macs;  // multiply-accumulates of the problem as the op defines it (no padding), for profiling
+    // Fused 3x3 / stride-2 / pad-0 max pooling of the uint8 output: y is then the pooled map [No, pool_ho, pool_wo] x ldc and the
+    // convolution's own output is never written.  Needs a 64-byte K tile, the box 16 x 8 x 1 and no residual.  0 = no pooling.
+    int pool_ho, pool_wo;
 };
 
 int launch_tc_igemm(const TcProblem& p, cudaStream_t s);

@@ -392,15 +392,19 @@ __global__ void __launch_bounds__(256) global_avgpool_dq_kernel(
 }
 
 // fp32 Linear: y[n,o] = fma chain over k ascending of x[n,k] * w[o,k], then + b[o].  Every output is accumulated by one
-// thread in k order (no split-K), so the result does not depend on the tiling.  32 x 64 output tile per block of 256
-// threads; a thread owns rows {2 tn, 2 tn + 1} and columns {to + 16 j}: with K-major tiles of pitch 36 floats in shared
-// memory its 128-bit reads along k are conflict-free (the eight lanes of a quarter warp read eight different rows whose
-// starts are 36 floats apart, or all the same row).  The next K slice is fetched into registers while the current one is
-// consumed, and shared memory is double-buffered, so there is one barrier per slice.
+// thread in k order (no split-K), so the result does not depend on the tiling.  32 x 64 output tile per block of 128
+// threads; a thread owns rows {4 tn .. 4 tn + 3} and columns {to + 16 j}.  A 128-bit shared-memory load costs four cycles
+// of the SM's load unit whatever it broadcasts; the 4 x 4 register tile needs eight of them per 64 fused multiply-adds.  The
+// price of the sequential chains is parallelism: 256 x 1000 outputs are 3.5 warps per SM, about one per scheduler (measured:
+// 63 us for [256, 2048] x [1000, 2048]^T, a quarter of the fp32 rate).  With K-major tiles of pitch 36 floats the loads along k are
+// conflict-free (the eight lanes of a quarter warp read eight different rows whose starts are 36 floats apart, or all the
+// same row).  The next K slice is fetched into registers while the current one is consumed, and shared memory is
+// double-buffered, so there is one barrier per slice.
 constexpr int kLinKS = 32;     // K slice
 constexpr int kLinPitch = 36;  // floats
+constexpr int kLinThreads = 128;
 
-__global__ void __launch_bounds__(256) linear_f32_kernel(
+__global__ void __launch_bounds__(kLinThreads) linear_f32_kernel(
         const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, int N, int K, int O, float* __restrict__ y) {
     __shared__ __align__(16) float Xs[2][32][kLinPitch];
     __shared__ __align__(16) float Ws[2][64][kLinPitch];
@@ -408,7 +412,7 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(
     const int tn = tid / 16, to = tid % 16;
     const int n0 = blockIdx.y * 32, o0 = blockIdx.x * 64;
     const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(w) & 15u) == 0);
-    // staging assignment: one float4 of X (row tid / 8, k offset 4 (tid % 8)) and two of W (rows tid / 8 and 32 + tid / 8)
+    // staging assignment: float4 number f = tid + 128 i of a tile covers row f / 8, k offset 4 (f % 8): two of X, four of W
     const int sr = tid / 8, sk = (tid % 8) * 4;
     auto fetch = [&](const float* base, int row, int rows, int k0) -> float4 {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -425,44 +429,51 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(
         }
         return v;
     };
-    float acc[2][4] = {};
-    float4 px = fetch(x, n0 + sr, N, 0), pw0 = fetch(w, o0 + sr, O, 0), pw1 = fetch(w, o0 + 32 + sr, O, 0);
+    float acc[4][4] = {};
+    float4 px[2], pw[4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) px[i] = fetch(x, n0 + sr + 16 * i, N, 0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pw[i] = fetch(w, o0 + sr + 16 * i, O, 0);
     int buf = 0;
     for (int k0 = 0; k0 < K; k0 += kLinKS, buf ^= 1) {
-        *reinterpret_cast<float4*>(&Xs[buf][sr][sk]) = px;
-        *reinterpret_cast<float4*>(&Ws[buf][sr][sk]) = pw0;
-        *reinterpret_cast<float4*>(&Ws[buf][32 + sr][sk]) = pw1;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) *reinterpret_cast<float4*>(&Xs[buf][sr + 16 * i][sk]) = px[i];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(&Ws[buf][sr + 16 * i][sk]) = pw[i];
         __syncthreads();
         if (k0 + kLinKS < K) {
-            px = fetch(x, n0 + sr, N, k0 + kLinKS);
-            pw0 = fetch(w, o0 + sr, O, k0 + kLinKS);
-            pw1 = fetch(w, o0 + 32 + sr, O, k0 + kLinKS);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) px[i] = fetch(x, n0 + sr + 16 * i, N, k0 + kLinKS);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pw[i] = fetch(w, o0 + sr + 16 * i, O, k0 + kLinKS);
         }
         // Elements past K are zero in both operands; fma(0, 0, acc) leaves acc as it is, so the slice is always run in full.
 #pragma unroll
         for (int k4 = 0; k4 < kLinKS; k4 += 4) {
-            float4 xv[2], wv[4];
+            float4 xv[4], wv[4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) xv[i] = *reinterpret_cast<const float4*>(&Xs[buf][tn * 2 + i][k4]);
+            for (int i = 0; i < 4; ++i) xv[i] = *reinterpret_cast<const float4*>(&Xs[buf][tn * 4 + i][k4]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const float4*>(&Ws[buf][to + 16 * j][k4]);
+            // k ascending per accumulator; the sixteen accumulators advance together, so that a fused multiply-add never waits
+            // for the one before it (there is only one warp per scheduler to hide that latency)
+            const float xa[4][4] = {{xv[0].x, xv[0].y, xv[0].z, xv[0].w}, {xv[1].x, xv[1].y, xv[1].z, xv[1].w},
+                                    {xv[2].x, xv[2].y, xv[2].z, xv[2].w}, {xv[3].x, xv[3].y, xv[3].z, xv[3].w}};
+            const float wa[4][4] = {{wv[0].x, wv[0].y, wv[0].z, wv[0].w}, {wv[1].x, wv[1].y, wv[1].z, wv[1].w},
+                                    {wv[2].x, wv[2].y, wv[2].z, wv[2].w}, {wv[3].x, wv[3].y, wv[3].z, wv[3].w}};
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int kk = 0; kk < 4; ++kk)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float a = acc[i][j];
-                    a = __fmaf_rn(xv[i].x, wv[j].x, a);
-                    a = __fmaf_rn(xv[i].y, wv[j].y, a);
-                    a = __fmaf_rn(xv[i].z, wv[j].z, a);
-                    a = __fmaf_rn(xv[i].w, wv[j].w, a);
-                    acc[i][j] = a;
-                }
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(xa[i][kk], wa[j][kk], acc[i][j]);
         }
         // the buffer written next iteration is the other one; its readers finished before this iteration's barrier
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int n = n0 + tn * 2 + i;
+    for (int i = 0; i < 4; ++i) {
+        const int n = n0 + tn * 4 + i;
         if (n >= N) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -620,7 +631,7 @@ extern "C" int chxq_global_avgpool_dq_nhwc(const uint8_t* x, int32_t N, int32_t 
 extern "C" int chxq_linear_f32(const float* x, const float* w, const float* b, int32_t N, int32_t K, int32_t O, float* y, void* stream) {
     CHXQ_CHECK_ARG(x && w && y && N > 0 && K > 0 && O > 0, "Linear: bad arguments");
     dim3 grid((O + 63) / 64, (N + 31) / 32);
-    linear_f32_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, w, b, N, K, O, y);
+    linear_f32_kernel<<<grid, kLinThreads, 0, as_stream(stream)>>>(x, w, b, N, K, O, y);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }

@@ -258,9 +258,12 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
 
     // Grouped-tile kernel (tc_kernel2.cuh): uint8 epilogues whose outputs (and residual) can move through TMA.
     bool grouped = false, halo = false;
-    int bn2 = (q.cols > 64 && q.group_cols == 0) ? 128 : 64;
+    const bool pool = q.pool_ho > 0;
+    if (pool && (q.bk != 64 || q.Wb != 16 || q.Hb != 8 || q.Nb != 1 || q.epi.residual != nullptr || q.group_cols != 0 || q.pool_wo <= 0))
+        return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: fused max pooling needs a 64-byte K tile, 16 x 8 position tiles and no residual");
+    int bn2 = (q.cols > 64 && q.group_cols == 0 && !pool) ? 128 : 64;
     alignas(64) CUtensorMap tmY, tmR;
-    if ((epi_kind == tc::kEpiKU8 || epi_kind == tc::kEpiKU8Fold) && g_variant != 1 && p.vec_ok && q.ldc % 16 == 0 && (q.bk == 64 || q.bk == 128) &&
+    if ((epi_kind == tc::kEpiKU8 || epi_kind == tc::kEpiKU8Fold) && (pool || g_variant != 1) && p.vec_ok && q.ldc % 16 == 0 && (q.bk == 64 || q.bk == 128) &&
         // folded tail: the saturating add clamps at zero, which is the Relu only when the output zero point is zero
         !(epi_kind == tc::kEpiKU8Fold && q.epi.residual != nullptr && q.epi.rq.res_relu && q.epi.rq.out_zp_f != 0.f)) {
         const int r = 256 / bn2;
@@ -268,8 +271,19 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
         // of one image.
         // by default for grouped / depthwise layers (measured: MobileNetV2 -7 %), on request (variant 3) for dense ones (ResNet-50's 3x3
         // layers are faster without: the halo planes are 16-byte TMA rows, and TMA moves about one row per clock)
-        halo = (g_variant >= 3 || (g_variant == 0 && q.group_cols > 0)) && q.KH * q.KW > 1 && q.KH <= 3 && q.KW <= 3 && p.sw == 1 && p.sh == 1 &&
+        halo = !pool && (g_variant >= 3 || (g_variant == 0 && q.group_cols > 0)) && q.KH * q.KW > 1 && q.KH <= 3 && q.KW <= 3 && p.sw == 1 && p.sh == 1 &&
                (q.bk == 64 || (q.bk == 128 && bn2 == 128 && q.epi.residual == nullptr)) && q.a_row_bytes == 0 && q.Wo >= 8 && q.Ho >= 8;
+        // Space-to-depth stems: the A map is rows of 16-byte blocks read through overlapping 64-byte windows (a_cs 16 < C 64), i.e. a
+        // KH x 4 stride-1 convolution over a 16-byte-pixel map.  As a halo tile every block is fetched once per tile instead of once per
+        // window that covers it (up to 16 times), and the four blocks of a window are consecutive pixels of the halo row.
+        const bool s2d_halo = g_variant != 1 && g_variant != 2 && q.a_row_bytes > 0 && q.a_cs == 16 && q.C == 64 && q.bk == 64 && q.KW == 1 &&
+                              q.KH <= 4 && p.sw == 1 && p.sh == 1 && q.group_cols == 0 && q.Wo >= 8 && q.Ho >= 8;
+        halo = halo || s2d_halo;
+        p.halo_w = 8 + (s2d_halo ? 4 : q.KW) - 1;
+        p.halo_h = 16 + q.KH - 1;
+        p.halo_planes = s2d_halo ? 1 : q.bk / 16;
+        p.halo_lbo = s2d_halo ? 1 : (tc::kHaloPlaneBytes >> 4);
+        p.halo_kstep = s2d_halo ? 2 : 2 * (tc::kHaloPlaneBytes >> 4);
         int64_t pos_tiles2 = pos_tiles;
         if (halo) {
             p.Wb = 8; p.Hb = 16; p.Nb = 1;
@@ -277,21 +291,35 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
             pos_tiles2 = (int64_t)p.tiles_w * p.tiles_h * p.tiles_n;
             if (pos_tiles2 * ((q.cols + bn2 - 1) / bn2) >= (1ll << 31)) return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: too many tiles");
         }
-        const int64_t groups = (pos_tiles2 + r - 1) / r * ((q.cols + bn2 - 1) / bn2);
+        int64_t groups = (pos_tiles2 + r - 1) / r * ((q.cols + bn2 - 1) / bn2);
+        if (pool) {
+            // a group of 2 x 2 tiles owns 15 x 7 pooled positions (see tc_kernel2.cuh)
+            p.pool_wo = q.pool_wo; p.pool_ho = q.pool_ho;
+            const int own_w = halo ? 7 : 15, own_h = halo ? 15 : 7;
+            p.pool_groups_w = (q.pool_wo + own_w - 1) / own_w; p.pool_groups_h = (q.pool_ho + own_h - 1) / own_h;
+            groups = (int64_t)p.pool_groups_w * p.pool_groups_h * q.No * ((q.cols + bn2 - 1) / bn2);
+            if (groups >= (1ll << 31)) return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: too many tiles");
+        }
         // Chosen whenever there is at least one group per SM; smaller problems spread better as single tiles.
-        grouped = halo || g_variant >= 2 || groups >= (int64_t)num_sms();
+        grouped = pool || halo || g_variant >= 2 || groups >= (int64_t)num_sms();
         if (halo) {
-            const cuuint64_t dims[4] = {(cuuint64_t)q.C, (cuuint64_t)q.W, (cuuint64_t)q.H, (cuuint64_t)q.N};
-            const cuuint64_t strides[3] = {(cuuint64_t)q.a_cs, (cuuint64_t)q.a_cs * q.W, (cuuint64_t)q.a_cs * q.W * q.H};
-            p.halo_swz = g_variant == 5 ? 2 : ((g_variant == 4 || q.bk == 128) ? 1 : 0);  // 128-byte pixels: the swizzled form only
-            const cuuint32_t box[4] = {p.halo_swz ? (cuuint32_t)q.bk : 16u, (cuuint32_t)(8 + q.KW - 1), (cuuint32_t)(16 + q.KH - 1), 1u};
+            // space-to-depth: the block map itself, [N][rows][a_row_bytes / 16 blocks][16 bytes]
+            const cuuint64_t dims[4] = {s2d_halo ? 16u : (cuuint64_t)q.C, s2d_halo ? (cuuint64_t)(q.a_row_bytes / 16) : (cuuint64_t)q.W, (cuuint64_t)q.H,
+                                        (cuuint64_t)q.N};
+            const cuuint64_t row_bytes = s2d_halo ? (cuuint64_t)q.a_row_bytes : (cuuint64_t)q.a_cs * q.W;
+            const cuuint64_t strides[3] = {(cuuint64_t)q.a_cs, row_bytes, row_bytes * q.H};
+            p.halo_swz = s2d_halo ? 0 : (g_variant == 5 ? 2 : ((g_variant == 4 || q.bk == 128) ? 1 : 0));  // 128-byte pixels: the swizzled form only
+            const cuuint32_t box[4] = {p.halo_swz ? (cuuint32_t)q.bk : 16u, (cuuint32_t)p.halo_w, (cuuint32_t)p.halo_h, 1u};
             const cuuint32_t estr[4] = {1, 1, 1, 1};
             CUresult r0 = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                  p.halo_swz ? swizzle_for(q.bk) : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r0 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A halo) failed with %d", (int)r0);
         }
-        if (grouped) {
+        if (grouped && pool) {
+            tmY = tmA;  // the pooling form writes the pooled map with plain stores and reads no residual: the maps are placeholders
+            tmR = tmA;
+        } else if (grouped) {
             const cuuint64_t dims[4] = {(cuuint64_t)q.cols, (cuuint64_t)q.Wo, (cuuint64_t)q.Ho, (cuuint64_t)q.No};
             const cuuint64_t strides[3] = {(cuuint64_t)q.ldc, (cuuint64_t)q.ldc * q.Wo, (cuuint64_t)q.ldc * q.Wo * q.Ho};
             const cuuint32_t box[4] = {(cuuint32_t)bn2, (cuuint32_t)p.Wb, (cuuint32_t)p.Hb, (cuuint32_t)p.Nb};
@@ -304,8 +332,11 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
             r1 = encode(&tmR, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, rbase, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r1 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(R) failed with %d", (int)r1);
+        }
+        if (grouped) {
             // The weight box and the instruction shape follow the grouped kernel's channel block.
             const int taps = q.KH * q.KW;
+            CUresult r1;
             const cuuint64_t bdims[2] = {(cuuint64_t)taps * q.c_pad, (cuuint64_t)q.cols};
             const cuuint64_t bstrides[1] = {(cuuint64_t)taps * q.c_pad};
             const cuuint32_t bbox[2] = {(cuuint32_t)q.bk, (cuuint32_t)bn2};
@@ -325,8 +356,12 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
         rec.macs = q.alg_macs;
         CHXQ_CUDA(cudaEventRecord(rec.e0, s));
     }
+    if (pool && !grouped)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: fused max pooling needs a uint8 epilogue and 16-byte aligned output rows");
     int rc;
-    if (grouped) {
+    if (pool) {
+        rc = tc::launch_tc2_bk64_pool(epi_kind, halo, tmA, tmB, tmY, tmR, p, grid, s);
+    } else if (grouped) {
         rc = q.bk == 128 ? tc::launch_tc2_bk128(bn2, epi_kind, q.epi.residual != nullptr, halo, tmA, tmB, tmY, tmR, p, grid, s)
                          : tc::launch_tc2_bk64(bn2, epi_kind, q.epi.residual != nullptr, halo, tmA, tmB, tmY, tmR, p, grid, s);
     } else

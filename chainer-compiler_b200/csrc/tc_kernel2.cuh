@@ -95,7 +95,7 @@ __device__ __forceinline__ float add_sat(float a, float b) {
 // [pixel][16 bytes]: in the canonical K-major layout a core matrix is 8 rows of 16 bytes, 16 bytes apart, so eight
 // consecutive pixels of an image row are one core matrix wherever the view starts; the stride between 8-row groups (SBO)
 // is one halo row, the stride between the two K halves of an MMA (LBO) is one plane.  Weight stages keep their own ring.
-constexpr int kHaloPlane = 3072;   // bytes reserved per plane: 18 x 10 pixels x 16 bytes = 2880, rounded up to 128
+constexpr int kHaloPlane = kHaloPlaneBytes;  // a space-to-depth stem uses one plane of 19 x 11 pixels (3344 bytes) at the start of a tile's planes
 constexpr int kHaloWb = 8, kHaloHb = 16;
 
 template <int BN, int BK, bool RES, bool HALO = false>
@@ -140,7 +140,17 @@ __device__ __forceinline__ uint64_t make_halo_desc(uint32_t smem_addr, uint32_t 
     return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(kHaloPlane >> 4) << 16) | ((uint64_t)(row_bytes >> 4) << 32) | (1ull << 46);
 }
 
-template <int BN, int BK, int EPI, bool RES, bool HALO>
+// POOL: the 3x3 / stride-2 max pooling that follows the convolution runs on the staged tiles, and only the pooled map is
+// written.  A group is then 2 x 2 tiles of 16 x 8 output positions (8 x 16 with halo tiles) whose origin advances by 30
+// columns and 14 rows per group (14 and 30), so that every pooling window of the 15 x 7 (7 x 15) pooled positions a group
+// owns lies inside it (neighbouring groups recompute the two overlapping columns and rows: 512 positions computed for 420
+// kept).  BN = 64 only.
+template <bool HALO>
+struct PoolGeom {
+    static constexpr int kTileW = HALO ? 8 : 16, kTileH = HALO ? 16 : 8;  // positions of one tile
+    static constexpr int kW = kTileW - 1, kH = kTileH - 1;                 // pooled positions a group owns
+};
+template <int BN, int BK, int EPI, bool RES, bool HALO, bool POOL = false>
 __global__ void __launch_bounds__(608, 1)
 tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const TcParams p) {
@@ -188,7 +198,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         for (int b = 0; b < 3; ++b) {
             mbar_init(rfull_bar(b), 1);
-            mbar_init(bempty_bar(b), 1);  // the store warp
+            mbar_init(bempty_bar(b), POOL ? 16 : 1);  // the store warp; pooling form: the sixteen epilogue warps
             mbar_init(bfull_bar(b), 16);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
@@ -204,8 +214,10 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
+    static_assert(!POOL || (BN == 64 && !RES), "fused pooling: 64-channel blocks without a residual");
+    using PG = PoolGeom<HALO>;
     const int pos_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
-    const int pos_groups = (pos_tiles + kR - 1) / kR;
+    const int pos_groups = POOL ? p.pool_groups_w * p.pool_groups_h * p.No : (pos_tiles + kR - 1) / kR;
     const int total_groups = pos_groups * p.col_tiles;
     const int taps = p.KH * p.KW;
     const int num_kb = taps * p.c_chunks;
@@ -219,6 +231,15 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int tn = pt / p.tiles_h;
         w0 = tw * p.Wb; h0 = th * p.Hb; n0 = tn * p.Nb;
     };
+    // POOL: origin of group pg in output coordinates; tile t of the group sits one tile to the right for t & 1, one down for t >> 1.
+    auto pool_group_origin = [&](int pg, int& gw0, int& gh0, int& n) {
+        const int gw = pg % p.pool_groups_w;
+        pg /= p.pool_groups_w;
+        const int gh = pg % p.pool_groups_h;
+        n = pg / p.pool_groups_h;
+        gw0 = gw * (2 * PG::kW);
+        gh0 = gh * (2 * PG::kH);
+    };
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -231,8 +252,19 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int ct = grp % p.col_tiles;
                 const int pg = grp / p.col_tiles;
                 int w0[kR], h0[kR], n0[kR];
+                if (POOL) {
+                    int gw0, gh0, gn;
+                    pool_group_origin(pg, gw0, gh0, gn);
 #pragma unroll
-                for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
+                    for (int t = 0; t < kR; ++t) {
+                        w0[t] = gw0 + PG::kTileW * (t & 1);
+                        h0[t] = gh0 + PG::kTileH * (t >> 1);
+                        n0[t] = gn;
+                    }
+                } else {
+#pragma unroll
+                    for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
+                }
                 const int gbase = p.group_cols > 0 ? (ct * BN / p.group_cols) * p.group_cin : 0;
                 if (RES) {
                     const int rb = it % Cfg::kBufs;
@@ -244,13 +276,13 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
                 if (HALO) {
                     // one halo tile per position tile and channel chunk, then one weight stage per tap
-                    const uint32_t halo_bytes = (uint32_t)((kHaloWb + p.KW - 1) * (kHaloHb + p.KH - 1) * 16);
+                    const uint32_t halo_bytes = (uint32_t)(p.halo_w * p.halo_h * 16);
                     for (int cc = 0; cc < p.c_chunks && ok; ++cc) {
                         if (!mbar_wait(hempty_bar(hstage), hphase ^ 1u, abort_flag, p.status, 9, 0)) {
                             ok = false;
                             break;
                         }
-                        mbar_expect_tx(hfull_bar(hstage), (uint32_t)(kR * (BK / 16)) * halo_bytes);
+                        mbar_expect_tx(hfull_bar(hstage), (uint32_t)(kR * (p.halo_swz ? BK / 16 : p.halo_planes)) * halo_bytes);
                         if (p.halo_swz) {
 #pragma unroll
                             for (int t = 0; t < kR; ++t)
@@ -259,8 +291,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         } else {
 #pragma unroll
                             for (int t = 0; t < kR; ++t)
-#pragma unroll
-                                for (int j = 0; j < BK / 16; ++j)
+                                for (int j = 0; j < p.halo_planes; ++j)
                                     tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA + j * kHaloPlane), &tmA, hfull_bar(hstage),
                                                 gbase + cc * BK + j * 16, w0[t] - p.pad_left, h0[t] - p.pad_top, n0[t]);
                         }
@@ -312,9 +343,9 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // descriptor halves (see kmajor_desc_hi): stepping is one 32-bit add of a compile-time constant
             const uint32_t desc_hi = kmajor_desc_hi<BK>();
             const uint32_t a_lo0 = kmajor_desc_lo(smem_u32(smem_a)), b_lo0 = kmajor_desc_lo(smem_u32(smem_b));
-            const int halo_w = kHaloWb + p.KW - 1;
+            const int halo_w = p.halo_w;
             const uint32_t halo_hi = (uint32_t)halo_w | (1u << 14);                                          // SBO = one halo row, no swizzle
-            const uint32_t halo_lo0 = (smem_u32(smem_a) >> 4) | ((uint32_t)(kHaloPlane >> 4) << 16);      // LBO = one plane
+            const uint32_t halo_lo0 = (smem_u32(smem_a) >> 4) | ((uint32_t)p.halo_lbo << 16);             // LBO = one plane, or one pixel
             for (int grp = blockIdx.x; grp < total_groups && ok; grp += gridDim.x, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -355,7 +386,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 for (int k = 0; k < BK / 32; ++k)
 #pragma unroll
                                     for (int t = 0; t < kR; ++t)
-                                        umma_i8_lohi(tmem_d + (uint32_t)(t * BN), a_lo + (uint32_t)((t * Cfg::kTileA + 2 * k * kHaloPlane) >> 4), halo_hi,
+                                        umma_i8_lohi(tmem_d + (uint32_t)(t * BN), a_lo + (uint32_t)((t * Cfg::kTileA) >> 4) + (uint32_t)(k * p.halo_kstep), halo_hi,
                                                      b_lo + k * 2, desc_hi, p.idesc, k > 0 ? 1u : accum);
                             }
                             umma_commit(empty_bar(stage));
@@ -570,12 +601,52 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     mbar_arrive(bfull_bar(buf));
                 }
             }
+            if (POOL) {
+                // Once all sixteen warps have staged the group, each of the 16 x 32 lanes takes one (pooled position, 16 channels)
+                // item of the 105 x 4 the group owns: nine 16-byte reads of the staged tiles, one 16-byte store.  Byte maxima are
+                // kept as two words of 16-bit lanes (even bytes, odd bytes), the widest unsigned SIMD maximum the hardware has.
+                // Positions outside the convolution's output do not take part (uint8: the maximum with 0).  (One dedicated warp
+                // walking the group with a sliding window was three times slower than the whole kernel is now.)
+                const bool staged = mbar_wait(bfull_bar(buf), use_phase, abort_flag, p.status, 8, 32);
+                if (!__all_sync(0xffffffffu, staged)) break;
+                const int q = e * 32 + lane;
+                int gw0, gh0, gn;
+                pool_group_origin(pg, gw0, gh0, gn);
+                const int unit = q & 3, pos = q >> 2;
+                const int pi = pos / PG::kW, pj = pos - pi * PG::kW;
+                const int ph = (gh0 >> 1) + pi, pw = (gw0 >> 1) + pj;
+                if (pos < PG::kW * PG::kH && ph < p.pool_ho && pw < p.pool_wo && col0 + unit * 16 < p.cols) {
+                    uint32_t ev[4] = {0u, 0u, 0u, 0u}, od[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (int dr = 0; dr < 3; ++dr) {
+                        const int lr = 2 * pi + dr;  // row inside the group
+                        if (gh0 + lr >= p.Ho) continue;
+#pragma unroll
+                        for (int dc = 0; dc < 3; ++dc) {
+                            const int lc = 2 * pj + dc;  // column inside the group
+                            if (gw0 + lc >= p.Wo) continue;
+                            const uint8_t* tile = out_buf + ((lr / PG::kTileH) * 2 + lc / PG::kTileW) * Cfg::kTileOut;
+                            const uint4 v = *reinterpret_cast<const uint4*>(tile + staged_offset<BN>((lr % PG::kTileH) * PG::kTileW + lc % PG::kTileW, unit));
+                            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                ev[k] = __vmaxu2(ev[k], w4[k] & 0x00ff00ffu);
+                                od[k] = __vmaxu2(od[k], (w4[k] >> 8) & 0x00ff00ffu);
+                            }
+                        }
+                    }
+                    uint8_t* dst = static_cast<uint8_t*>(p.y) + (((int64_t)gn * p.pool_ho + ph) * p.pool_wo + pw) * p.ldc + col0 + unit * 16;
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(ev[0] | (od[0] << 8), ev[1] | (od[1] << 8), ev[2] | (od[2] << 8), ev[3] | (od[3] << 8));
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bempty_bar(buf));  // this warp has read what it needs of the buffer
+            }
         }
     } else if (warp == 18) {
         // ---------------- store warp ----------------
         // One lane: waits until all sixteen epilogue warps have staged a group, issues its TMA stores, waits until they have
         // read the buffer and hands the buffer back (to the epilogue, or to the producer for the next residual tile).
-        if (lane == 0) {
+        if (!POOL && lane == 0) {  // the pooling form stores nothing by TMA: the epilogue warps pool and write
             int it = 0;
             for (int grp = blockIdx.x; grp < total_groups; grp += gridDim.x, ++it) {
                 const int ct = grp % p.col_tiles;
@@ -614,7 +685,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
-template <int BN, int BK, int EPI, bool RES, bool HALO>
+template <int BN, int BK, int EPI, bool RES, bool HALO, bool POOL = false>
 int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p, int grid,
                 cudaStream_t s) {
     using Cfg = Tc2Config<BN, BK, RES, HALO>;
@@ -623,10 +694,10 @@ int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
     int dev = 0;
     CHXQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES, HALO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    tc_igemm2_kernel<BN, BK, EPI, RES, HALO><<<grid, 608, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
+    tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL><<<grid, 608, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }

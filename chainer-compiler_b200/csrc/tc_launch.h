@@ -9,6 +9,8 @@
 namespace chxq {
 namespace tc {
 
+constexpr int kHaloPlaneBytes = 3072;  // bytes reserved per plane of a halo tile: 18 x 10 pixels x 16 bytes = 2880, rounded up to 128
+
 struct TcParams {
     int Wb, Hb, Nb;
     int tiles_w, tiles_h, tiles_n;  // position tiles
@@ -17,6 +19,10 @@ struct TcParams {
     int KH, KW, pad_top, pad_left;
     int sw, sh;  // convolution strides: input coordinate = output coordinate * stride - pad + tap
     int halo_swz;  // halo form: 0 = planes of 16-byte rows without swizzle, 1 = one swizzled tile of BK-byte rows, 2 = same with the descriptor's base offset
+    // halo form: halo tile of halo_w x halo_h pixels in halo_planes planes of [pixel][16 bytes]; the two 16-byte K halves of an MMA are
+    // halo_lbo 16-byte units apart (one plane for channel chunks; one pixel for the space-to-depth stem, whose K runs along the row),
+    // consecutive MMAs of a tap halo_kstep units
+    int halo_w, halo_h, halo_planes, halo_lbo, halo_kstep;
     int group_cols, group_cin;  // grouped convolution (0 = one group): first input channel of a column tile = (col0 / group_cols) * group_cin
     int c_chunks;  // c_pad / BK
     int c_pad;
@@ -31,6 +37,10 @@ struct TcParams {
     void* y;
     int* status;
     int vec_ok;  // rows of y (and of the residual) start on 16-byte boundaries
+    // Fused 3x3 / stride-2 max pooling (grouped kernel, 64-channel blocks): y is the POOLED map [No, pool_ho, pool_wo, ldc]; a
+    // group is 2 x 2 tiles of 16 x 8 positions and owns 15 x 7 pooled positions (8 x 16 and 7 x 15 with halo tiles).
+    // pool_groups_w == 0: no pooling.
+    int pool_groups_w, pool_groups_h, pool_wo, pool_ho;
 };
 
 // Epilogue families (template parameter EPI): dead paths are compiled out, which keeps the unrolled per-element
@@ -44,6 +54,9 @@ int launch_tc_bk32(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& t
 int launch_tc_bk64(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s);
 int launch_tc_bk128(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s);
 // Grouped-tile kernel (tc_kernel2.cuh); bn is 64 or 128, epi is kEpiKU8 or kEpiKU8Fold.
+// pool: the fused max-pooling form (bn 64, no residual; 64-byte K tiles only), with or without halo tiles.
+int launch_tc2_bk64_pool(int epi, bool halo, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p,
+                         int grid, cudaStream_t s);
 int launch_tc2_bk64(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
                     const TcParams& p, int grid, cudaStream_t s);
 int launch_tc2_bk128(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,

@@ -211,15 +211,21 @@ class ResNet50Int8:
         assert self.calibrated
         assert fused or not fold, "the folded residual tail exists only inside the convolution epilogue"
         c = self.stem
-        if fused:  # the input's QuantizeLinear runs inside the stem convolution's repack pass
-            h = ops.QuantizeLinearConvPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
-                                             b=c.dev["bias"], fold_scales=fold)
+        if fused and taps is None:
+            # the input's QuantizeLinear runs inside the stem convolution's repack pass and the max pooling on its output tiles:
+            # neither the uint8 image nor the full-resolution stem output reaches memory
+            h = ops.QLinearConvMaxPoolPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
+                                             b=c.dev["bias"], cover_all=True, fold_scales=fold)
         else:
-            xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
-            h = self._run_conv(c, xq, fold=fold)
-        if taps is not None:
-            taps["stem"] = h
-        h = ops.MaxPoolU8(h, 3, 2, 0, cover_all=True)
+            if fused:
+                h = ops.QuantizeLinearConvPacked(x, c.packed, c.x_scale, np.uint8(0), c.dev["w_scale"], c.dev["w_zp"], c.y_scale, np.uint8(c.y_zp),
+                                                 b=c.dev["bias"], fold_scales=fold)
+            else:
+                xq = ops.QuantizeLinear(x, self.in_scale, np.uint8(0))
+                h = self._run_conv(c, xq, fold=fold)
+            if taps is not None:
+                taps["stem"] = h
+            h = ops.MaxPoolU8(h, 3, 2, 0, cover_all=True)
         h_scale = self.stem.y_scale
         for i, b in enumerate(self.blocks):
             h1 = self._run_conv(b["conv1"], h, fold=fold)

@@ -335,6 +335,36 @@ def QLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y
     return y
 
 
+def QLinearConvMaxPoolPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b=None, pool_kernel=3, pool_stride=2,
+                             pool_pad=0, cover_all=False, round_mode=ROUND_REF, quant_round_mode=ROUND_REF, clamp_hi_q=None, out=None,
+                             fold_scales=False):
+    """QLinearConvPacked followed by MaxPoolU8(pool_kernel, pool_stride, pool_pad, cover_all) as one kernel; bit-identical to the
+    two ops.  x: the uint8 map, or the fp32 tensor in front of a QuantizeLinear(x_scale, x_zero_point) (as
+    QuantizeLinearConvPacked).  Only kernel 3 / stride 2 / pad 0 pooling behind a convolution whose packed K tile is 64 bytes
+    (network stems); raises ChxqError(ERR_UNSUPPORTED) otherwise."""
+    _require_cuda(x)
+    g = packed.g
+    layout_ok = _is_channels_last(x) if g.x_layout == NHWC else x.is_contiguous()
+    if tuple(x.shape) != (g.N, g.C, g.H, g.W) or not layout_ok or x.dtype not in (torch.float32, torch.uint8):
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConvMaxPoolPacked: x does not match the packed geometry / layout")
+    if not packed.eligible:
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "QLinearConvMaxPoolPacked: this geometry is not eligible for the packed tensor-core path")
+    keep = []
+    p, cy = _qconv_params(x, packed.w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, None, 1.0, 0,
+                          True, 1.0, 0, keep, fold_scales)
+    if cy != UINT8:
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "QLinearConvMaxPoolPacked: the output must be uint8")
+    extra = pool_stride - 1 if cover_all else 0
+    Hp, Wp = (g.Ho + 2 * pool_pad - pool_kernel + extra) // pool_stride + 1, (g.Wo + 2 * pool_pad - pool_kernel + extra) // pool_stride + 1
+    y = out if out is not None else torch.empty((g.N, g.M, Hp, Wp), dtype=torch.uint8, device=x.device, memory_format=torch.channels_last)
+    ws_bytes = lib().chxq_conv_packed_workspace(ctypes.byref(g), p.x_zero_point, packed.flags)
+    ws = workspace(ws_bytes, x.device)
+    check(lib().chxq_qlinear_conv_maxpool_packed(_ptr(x), int(x.dtype == torch.float32), quant_round_mode, _ptr(packed.blob), ctypes.byref(g),
+                                                 ctypes.byref(p), packed.flags, pool_kernel, pool_stride, pool_pad, int(bool(cover_all)), _ptr(y), _ptr(ws),
+                                                 ws_bytes, _stream()))
+    return y
+
+
 def ConvIntegerPacked(x, packed, x_zero_point=None):
     """ConvInteger with weights packed by PackedConv; x must be a channels_last map of the packed geometry."""
     _require_cuda(x)

@@ -204,7 +204,7 @@ def compile_model(model, quantize=False, per_channel=True, asymmetric_input_type
     if peephole:
         program = fuse_quantized_add(program)
         if peephole != "join":
-            program = fuse_conv_residual(program)
+            program = fuse_stem(fuse_conv_residual(program))
     if fuse:
         program = fuse_elementwise(program)
     return program
@@ -300,6 +300,54 @@ def fuse_conv_residual(program):
         return program
     new = [replaced.get(k, i) for k, i in enumerate(insts) if k not in drop]
     return Program(new, program.constants, program.inputs, program.outputs)
+
+
+def fuse_stem(program):
+    """Third peephole, for network stems: a QLinearConv with constant weights takes (a) the QuantizeLinear in front of it when
+    that node quantizes a float value with the convolution's own input scale and zero point and has no other reader
+    (attribute quantize_input: input 0 is then the float value), and (b) the uint8 MaxPool(kernel 3, stride 2, no padding)
+    behind it when that is its only reader (attribute pool = ceil_mode of the MaxPool; the instruction's output is the pooled
+    map).  Whether the fused kernels apply depends on the geometry, which is known at run time: the executor falls back to
+    the separate kernels when the library refuses, with the same results."""
+    insts = program.insts
+    users, producer = {}, {}
+    for k, i in enumerate(insts):
+        for v in i.inputs:
+            users.setdefault(v, []).append(k)
+        for v in i.outputs:
+            producer[v] = k
+    consts = program.constants
+    replaced, drop = {}, set()
+    for k, conv in enumerate(insts):
+        if conv.op != "QLinearConv" or conv.inputs[3] not in consts or conv.attrs.get("residual"):
+            continue
+        ins, attrs, outs = list(conv.inputs), dict(conv.attrs), list(conv.outputs)
+        qk = producer.get(ins[0])
+        if qk is not None and insts[qk].op == "QuantizeLinear" and len(users.get(ins[0], [])) == 1 and ins[0] not in program.outputs \
+                and len(insts[qk].inputs) == 3 and insts[qk].inputs[1:3] == ins[1:3] and all(v in consts for v in ins[1:3]) \
+                and np.asarray(consts[ins[2]]).dtype == np.uint8:
+            attrs["quantize_input"] = 1
+            attrs["quantized_name"] = ins[0]
+            ins[0] = insts[qk].inputs[0]
+            drop.add(qk)
+        u = users.get(outs[0], [])
+        if len(u) == 1 and outs[0] not in program.outputs and insts[u[0]].op == "MaxPool":
+            mp = insts[u[0]]
+            a = mp.attrs
+            pads = list(a.get("pads", [])) or [0, 0, 0, 0]
+            if list(a.get("kernel_shape", [])) == [3, 3] and list(a.get("strides", [1, 1])) == [2, 2] and not any(pads) \
+                    and not any(d != 1 for d in a.get("dilations", [])) and len(mp.outputs) == 1 \
+                    and np.asarray(consts.get(ins[7], np.int8(0))).dtype == np.uint8:
+                attrs["pool"] = 1 + int(bool(a.get("ceil_mode", 0)))  # 1 = floor, 2 = ceil_mode
+                attrs["conv_output"] = outs[0]
+                outs = list(mp.outputs)
+                drop.add(u[0])
+        if attrs != conv.attrs:
+            replaced[k] = Inst("QLinearConv", ins, outs, **attrs)
+    if not replaced:
+        return program
+    new = [replaced.get(k, i) for k, i in enumerate(insts) if k not in drop]
+    return Program(_topological(new, set(program.constants) | set(program.inputs)), program.constants, program.inputs, program.outputs)
 
 
 # ---- elementwise fusion over a program -----------------------------------------------------------------------------------
@@ -419,6 +467,23 @@ def program_to_onnx(program, name="graph"):
         elif i.op == "ElementWiseNvrtc":
             for op, ins, outs in i.attrs["members"]:
                 nodes.append(N(op, ins, outs, {}))
+        elif i.op == "QLinearConv" and (i.attrs.get("quantize_input") or i.attrs.get("pool")):
+            skip = ("quantize_input", "quantized_name", "pool", "conv_output")
+            attrs = {k: v for k, v in i.attrs.items() if k not in skip and v is not None and not (isinstance(v, (list, tuple)) and len(v) == 0)}
+            cin = list(i.inputs)
+            if i.attrs.get("quantize_input"):
+                nodes.append(N("QuantizeLinear", [cin[0], cin[1], cin[2]], [i.attrs["quantized_name"]], {}))
+                cin[0] = i.attrs["quantized_name"]
+            while cin and cin[-1] == "":
+                cin.pop()
+            if i.attrs.get("pool"):
+                nodes.append(N("QLinearConv", cin, [i.attrs["conv_output"]], attrs))
+                pattrs = {"kernel_shape": [3, 3], "strides": [2, 2]}
+                if i.attrs["pool"] == 2:
+                    pattrs["ceil_mode"] = 1
+                nodes.append(N("MaxPool", [i.attrs["conv_output"]], i.outputs, pattrs))
+            else:
+                nodes.append(N("QLinearConv", cin, i.outputs, attrs))
         elif i.op == "QLinearConv" and i.attrs.get("residual"):
             attrs = {k: v for k, v in i.attrs.items() if k not in ("residual", "res_relu", "conv_output") and v is not None
                      and not (isinstance(v, (list, tuple)) and len(v) == 0)}
@@ -626,6 +691,14 @@ class Executor:
             strides, pads, group = tuple(a.get("strides", [])), self._sym_pads(a.get("pads", [])), a.get("group", 1)
             wk, zk = (1, 3) if op == "ConvInteger" else (3, 5)
             xin, packed = x[0], None
+            fq, fpool = bool(a.get("quantize_input")), int(a.get("pool", 0))
+            if fq or fpool:
+                y = self._stem(inst, x, sc, has, strides, pads, group, auto_pad, fq, fpool)
+                if y is not None:
+                    env[out] = y
+                    return
+                if fq:  # the library refused the fused form: the separate kernels, same results
+                    xin = ops.QuantizeLinear(xin.contiguous(), sc(1), sc(2))
             if xin.dim() == 4 and xin.dtype == t.uint8 and inst.inputs[wk] in self.host_consts and (not has(zk) or inst.inputs[zk] in self.host_consts):
                 # constant weights: pack them once per input shape and keep the activations channels_last, which is the layout
                 # the tensor-core kernels read (the first convolution of a graph pays one layout pass)
@@ -659,11 +732,14 @@ class Executor:
                     if xin.dim() == 4 and packed is None:
                         xin = ops.to_channels_last(xin)  # the residual map and the output share the NHWC layout
                 if packed is not None:
-                    env[out] = ops.QLinearConvPacked(xin, packed, sc(1), sc(2), x[4], x[5], sc(6), sc(7), b=x[8] if has(8) else None,
-                                                     fold_scales=self.fold_scales, **res)
+                    y = ops.QLinearConvPacked(xin, packed, sc(1), sc(2), x[4], x[5], sc(6), sc(7), b=x[8] if has(8) else None,
+                                              fold_scales=self.fold_scales, **res)
                 else:
-                    env[out] = ops.QLinearConv(xin, sc(1), sc(2), x[3], x[4], x[5], sc(6), sc(7), x[8] if has(8) else None, strides, pads, group,
-                                               auto_pad, fold_scales=self.fold_scales, **res)
+                    y = ops.QLinearConv(xin, sc(1), sc(2), x[3], x[4], x[5], sc(6), sc(7), x[8] if has(8) else None, strides, pads, group,
+                                        auto_pad, fold_scales=self.fold_scales, **res)
+                if fpool:
+                    y = ops.MaxPoolU8(ops.to_channels_last(y), 3, 2, 0, cover_all=(fpool == 2))
+                env[out] = y
         elif op == "QAddU8":
             qa, qb = x[0], x[3]
             if qa.stride() != qb.stride():  # one operand came from a kernel of the other layout
@@ -757,6 +833,50 @@ class Executor:
                 env[out] = y + a.get("beta", 1.0) * x[2] if len(x) > 2 else y
         else:
             raise NotImplementedError("run_onnx: op %s" % op)
+
+    def _stem(self, inst, x, sc, has, strides, pads, group, auto_pad, fq, fpool):
+        """The fused forms of a stem convolution (QuantizeLinear in front and / or MaxPool behind); None when the library has no
+        fused kernel for the geometry."""
+        t, ops = self.torch, self.ops
+        from chainer_compiler_b200 import _lib
+        xin = x[0]
+        if xin.dim() != 4 or not (xin.dtype == t.float32 if fq else xin.dtype == t.uint8):
+            return None
+        wz = x[5] if has(5) else None
+        key = (id(inst), tuple(xin.shape), "stem")
+        entry = self.packed.get(key)
+        if entry is None:
+            entry = False
+            layouts = (self.NCHW,) if (xin.shape[1] <= 4 and xin.is_contiguous()) else ()
+            for layout in layouts + (None,):
+                pk = ops.PackedConv(x[3], wz, tuple(xin.shape), strides, pads, group, auto_pad) if layout is None else \
+                    ops.PackedConv(x[3], wz, tuple(xin.shape), strides, pads, group, auto_pad, x_layout=layout)
+                if pk.eligible:
+                    entry = pk
+                    break
+            self.packed[key] = entry
+        if entry is False:
+            return None
+        if entry.g.x_layout != self.NCHW:
+            xin = ops.to_channels_last(xin)
+        args = (xin, entry, sc(1), sc(2), x[4], x[5], sc(6), sc(7))
+        kw = dict(b=x[8] if has(8) else None, fold_scales=self.fold_scales)
+        try:
+            if fpool:
+                return ops.QLinearConvMaxPoolPacked(*args, cover_all=(fpool == 2), **kw)
+            return ops.QuantizeLinearConvPacked(*args, **kw)
+        except _lib.ChxqError as e:
+            if e.code != _lib.ERR_UNSUPPORTED:
+                raise
+        if fq and fpool:  # the pooling may be what was refused: the fused quantization alone
+            try:
+                y = ops.QuantizeLinearConvPacked(*args, **kw)
+                return ops.MaxPoolU8(y, 3, 2, 0, cover_all=(fpool == 2))
+            except _lib.ChxqError as e:
+                if e.code != _lib.ERR_UNSUPPORTED:
+                    raise
+        self.packed[key] = False  # do not try again
+        return None
 
     @staticmethod
     def _sym_pads(pads):

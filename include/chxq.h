@@ -231,6 +231,16 @@ int chxq_qlinear_conv_packed(const void* x, const void* packed, const chxq_conv_
  * (runtime/ops/quantize.cc:48-53, 62-94). */
 int chxq_quantize_qlinear_conv_packed(const float* x, int32_t quant_round_mode, const void* packed, const chxq_conv_geom* g,
                                       const chxq_qconv_params* p, int32_t packed_flags, void* y, void* workspace, size_t workspace_bytes, void* stream);
+/* QLinearConv followed by MaxPool(kernel 3, stride 2, pad 0; cover_all as Chainer's max_pooling_2d, i.e. ONNX ceil_mode) as ONE
+ * kernel: the pooling runs on the convolution's output tiles while they are in shared memory and only the pooled map
+ * y [N, Hp, Wp, M] (NHWC uint8, Hp = (Ho - 3 + cover_all) / 2 + 1) is written.  The reference runs QLinearConv
+ * (runtime/ops/quantize.cc:62-94) and MaxPool (runtime/ops/pooling.cc:47-60) as two ops with the full-resolution map in
+ * between; results are bit-identical to that sequence.  x_is_f32 != 0: x is the fp32 tensor in front of a QuantizeLinear
+ * (as chxq_quantize_qlinear_conv_packed).  Needs packed weights of a geometry whose K tile is 64 bytes (network stems);
+ * CHXQ_ERR_UNSUPPORTED otherwise -- run the two ops then.  Workspace: chxq_conv_packed_workspace. */
+int chxq_qlinear_conv_maxpool_packed(const void* x, int32_t x_is_f32, int32_t quant_round_mode, const void* packed, const chxq_conv_geom* g,
+                                     const chxq_qconv_params* p, int32_t packed_flags, int32_t pool_kernel, int32_t pool_stride, int32_t pool_pad,
+                                     int32_t cover_all, void* y, void* workspace, size_t workspace_bytes, void* stream);
 int chxq_conv_integer_packed(const void* x, const void* packed, const chxq_conv_geom* g, int32_t has_x_zp, int32_t x_zero_point,
                              int32_t packed_flags, int32_t* y, void* workspace, size_t workspace_bytes, void* stream);
 

@@ -142,6 +142,8 @@ def run_program(program, inputs, trace=None, conv_mode="emulate"):
             else:
                 zy = np.asarray(x[7]).reshape(())
                 bias = x[8] if len(x) > 8 and inst.inputs[8] != "" else None
+                if a.get("quantize_input"):  # run_onnx's stem peephole: the QuantizeLinear in front of the convolution
+                    x[0] = orc.quantize_linear(x[0], _f32(x[1]), int(np.asarray(x[2]).reshape(())))
                 if conv_mode == "exact":
                     acc = orc.conv_integer(x[0], x[3], int(np.asarray(x[2]).reshape(())), np.asarray(x[5]).astype(np.int32).reshape(-1), strides, pads, group, auto_pad)
                     out = [orc.requantize(acc, _f32(x[1]), np.asarray(x[4], np.float32), _f32(x[6]), int(zy), bias=bias, channel_axis=1, y_dtype=zy.dtype.type)]
@@ -152,6 +154,8 @@ def run_program(program, inputs, trace=None, conv_mode="emulate"):
                     # the join run_onnx's second peephole moved into the convolution: DequantizeLinear x2, Add, [Relu], QuantizeLinear
                     out = [orc.qadd_relu(out[0], _f32(x[6]), int(zy), x[9], _f32(x[10]), int(np.asarray(x[11]).reshape(())), _f32(x[12]),
                                          int(np.asarray(x[13]).reshape(())), relu=bool(a.get("res_relu", 0)))]
+                if a.get("pool"):  # ... and the MaxPool(3, 2, 0) behind it (2 = ceil_mode)
+                    out = [orc.maxpool_u8(out[0], 3, 2, 0, cover_all=(a["pool"] == 2))]
         elif op == "MatMulInteger":
             out = [orc.matmul_integer(x[0], x[1], np.asarray(x[2]).reshape(-1) if len(x) > 2 else None,
                                       np.asarray(x[3]).reshape(-1) if len(x) > 3 else None)]

@@ -481,3 +481,56 @@ def test_quantize_fused_into_stem_conv(pkg, ops, orc, dev):
     with pytest.raises(_lib.ChxqError):
         ops.QuantizeLinearConvPacked(torch.zeros((2, 16, 8, 8), device=dev).contiguous(memory_format=torch.channels_last), pk1, 0.1, np.uint8(0),
                                      _t(ws, dev), _t(wz, dev), 0.05, np.uint8(3))
+
+
+@pytest.mark.parametrize("case", ["stem64", "stem_odd", "stem224", "c64_1x1", "c64_3x3_m128", "c64_m32"])
+def test_conv_with_fused_max_pooling(pkg, ops, orc, dev, case):
+    """QLinearConv + MaxPool(3, 2, 0) as one kernel (pooling on the staged output tiles, overlapping tile groups) against the
+    two ops run one after the other, and against the oracle's convolution and pooling."""
+    from chainer_compiler_b200 import _lib
+    rng = np.random.default_rng(sum(map(ord, case)))
+    if case.startswith("stem"):
+        N, H, W = {"stem64": (2, 64, 64), "stem_odd": (3, 62, 90), "stem224": (8, 224, 224)}[case]
+        M = 64
+        xf = rng.uniform(-0.1, 1.1, (N, 3, H, W)).astype(np.float32)
+        w = _rand(rng, (M, 3, 7, 7), np.int8)
+        geom = dict(strides=(2, 2), pads=(3, 3), x_layout=_lib.NCHW)
+        xt, x_scale = _t(xf, dev), 1 / 255.0
+        xq_np = orc.quantize_linear(xf, x_scale, 0)
+    else:
+        N, C, H, W, M, k = {"c64_1x1": (2, 64, 20, 36, 64, 1), "c64_3x3_m128": (2, 64, 21, 19, 128, 3), "c64_m32": (1, 64, 9, 40, 32, 1)}[case]
+        xq_np = _rand(rng, (N, C, H, W), np.uint8)
+        w = _rand(rng, (M, C, k, k), np.int8)
+        geom = dict(strides=(1, 1), pads=(k // 2, k // 2))
+        xt, x_scale = _t(xq_np, dev, True), 0.02
+    ws = rng.uniform(0.0005, 0.002, M).astype(np.float32) / (1 if case.startswith("stem") else 8)
+    wz = np.zeros(M, np.int8)
+    bias = _rand(rng, M, np.int32, -3000, 3000)
+    pk = ops.PackedConv(_t(w, dev), _t(wz, dev), xt.shape, **geom)
+    assert pk.eligible
+    args = (pk, x_scale, np.uint8(0), _t(ws, dev), _t(wz, dev), 0.05, np.uint8(2))
+    for fold in (False, True):
+        for cover_all in (True, False):
+            if xt.dtype == torch.float32:
+                conv = ops.QuantizeLinearConvPacked(xt, *args, b=_t(bias, dev), fold_scales=fold)
+            else:
+                conv = ops.QLinearConvPacked(xt, *args, b=_t(bias, dev), fold_scales=fold)
+            two = ops.MaxPoolU8(conv, 3, 2, 0, cover_all=cover_all)
+            one = ops.QLinearConvMaxPoolPacked(xt, *args, b=_t(bias, dev), cover_all=cover_all, fold_scales=fold)
+            ops.device_status()
+            assert one.shape == two.shape and torch.equal(one, two), (case, fold, cover_all)
+            assert int(one.max()) > 2
+    if case != "stem224":
+        acc = orc.conv_integer(xq_np, w, 0, wz.astype(np.int32), strides=geom["strides"], pads=geom["pads"])
+        want = orc.maxpool_u8(orc.requantize(acc, x_scale, ws, 0.05, 2, bias=bias, channel_axis=1), 3, 2, 0, cover_all=True)
+        got = ops.QLinearConvMaxPoolPacked(xt, *args, b=_t(bias, dev), cover_all=True)
+        assert np.array_equal(got.cpu().numpy(), want)
+    # refused: other pooling windows; convolutions whose K tile is 128 bytes
+    with pytest.raises(_lib.ChxqError):
+        ops.QLinearConvMaxPoolPacked(xt, *args, b=_t(bias, dev), pool_kernel=2)
+    w128 = _rand(rng, (64, 128, 1, 1), np.int8)
+    x128 = _t(_rand(rng, (1, 128, 16, 16), np.uint8), dev, True)
+    wz64, ws64 = np.zeros(64, np.int8), np.full(64, 1e-4, np.float32)
+    pk128 = ops.PackedConv(_t(w128, dev), _t(wz64, dev), x128.shape)
+    with pytest.raises(_lib.ChxqError):
+        ops.QLinearConvMaxPoolPacked(x128, pk128, 0.02, np.uint8(0), _t(ws64, dev), _t(wz64, dev), 0.05, np.uint8(2))

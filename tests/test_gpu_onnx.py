@@ -182,5 +182,6 @@ def test_statically_quantized_resnet_file_runs_on_the_tensor_core_kernels(pkg, o
     taps, gt = {}, {}
     net.forward(x.to(dev), fused=True, fold=True, taps=taps)
     run_onnx.Executor(prog, "cuda:0", fold_scales=True).run(cases[0][0], trace=gt)
-    assert torch.equal(gt["stem"], taps["stem"]) and all(torch.equal(gt["b%d_out" % i], taps["block%d" % i]) for i in range(16))
+    assert prog.insts[0].attrs.get("quantize_input") and prog.insts[0].attrs.get("pool") == 2 and prog.insts[0].outputs == ["pool"]
+    assert torch.equal(gt["pool"], ops.MaxPoolU8(taps["stem"], 3, 2, 0, cover_all=True)) and all(torch.equal(gt["b%d_out" % i], taps["block%d" % i]) for i in range(16))
     assert not run_onnx.Executor(run_onnx.compile_model(onnx_io.load_test_dir(GOLDEN)[0], quantize=True), "cuda:0").is_static()

@@ -265,3 +265,34 @@ def test_residual_join_peephole_keeps_every_bit(mods):
     # a second reader of an intermediate value, or a non-constant scale, blocks the rewrite
     model.outputs = ["y", "sum"]
     assert "QAddU8" not in [i.op for i in run_onnx.compile_model(model).insts]
+
+
+def test_stem_peephole(mods):
+    """QuantizeLinear -> QLinearConv -> MaxPool(3, 2) at the head of a network becomes one instruction; the oracle's evaluation
+    and the exported graph are unchanged."""
+    onnx_io, run_onnx = mods
+    entry.load_oracle()
+    from oracle import networks
+    N, f32, u8, i8 = onnx_io.Node, np.float32, np.uint8, np.int8
+    rng = np.random.default_rng(17)
+    inits = {"s_in": f32(1 / 255.0).reshape(()), "z0": u8(0).reshape(()), "w": rng.integers(-127, 128, (16, 3, 7, 7), dtype=i8),
+             "ws": rng.uniform(0.0005, 0.002, 16).astype(f32), "wz": np.zeros(16, i8), "b": rng.integers(-500, 500, 16).astype(np.int32),
+             "s1": f32(0.05).reshape(())}
+    nodes = [N("QuantizeLinear", ["x", "s_in", "z0"], ["xq"], {}),
+             N("QLinearConv", ["xq", "s_in", "z0", "w", "ws", "wz", "s1", "z0", "b"], ["c"], {"kernel_shape": [7, 7], "strides": [2, 2], "pads": [3, 3, 3, 3]}),
+             N("MaxPool", ["c"], ["p"], {"kernel_shape": [3, 3], "strides": [2, 2], "ceil_mode": 1}),
+             N("DequantizeLinear", ["p", "s1", "z0"], ["y"], {})]
+    model = onnx_io.Model(nodes, inits, ["x"], ["y"], ir_version=5, opset=12)
+    plain, fused = run_onnx.compile_model(model, peephole=False), run_onnx.compile_model(model)
+    assert [i.op for i in fused.insts] == ["QLinearConv", "DequantizeLinear"]
+    st = fused.insts[0]
+    assert st.inputs[0] == "x" and st.outputs == ["p"] and st.attrs["quantize_input"] == 1 and st.attrs["pool"] == 2
+    x = rng.uniform(0, 1, (1, 3, 30, 34)).astype(f32)
+    (_, a), = networks.run_program(plain, {"x": x})
+    (_, b), = networks.run_program(fused, {"x": x})
+    assert a.shape == (1, 16, 7, 8) and np.array_equal(a, b)
+    assert [n.op_type for n in run_onnx.program_to_onnx(fused).nodes] == [n.op_type for n in nodes]
+    # a second reader of the quantized image or of the convolution's output keeps the nodes apart
+    model.outputs = ["y", "c"]
+    st = run_onnx.compile_model(model).insts[0]
+    assert st.op == "QLinearConv" and st.attrs.get("quantize_input") == 1 and not st.attrs.get("pool")
