@@ -306,8 +306,8 @@ def run_chxq(args):
         achieved = 2.0 * macs.value / (tms.value / 1000.0) / 1e12
         peak = 2.0 * pk["bf16_sustained"]
         # DRAM traffic of the 53 tensor-core launches of one step at batch 256, one ncu pass per launch
-        # (dram__bytes_read.sum + dram__bytes_write.sum = 4690.0 MB per step; summary in profiles/tc_igemm2_resnet50_b256.txt)
-        traffic = 4690.0e6 / 53 if args.batch == 256 and fold else None
+        # (dram__bytes_read.sum + dram__bytes_write.sum = 4537.9 MB per step; summary in profiles/tc_igemm2_resnet50_b256.txt)
+        traffic = 4537.9e6 / 53 if args.batch == 256 and fold else None
         roof = {"bound": "tensor", "kernel": "tc_igemm2_kernel (tcgen05 kind::i8 implicit GEMM, grouped tiles, all 53 convolutions)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
                 "traffic_note": "bytes per launch, average over the 53 launches of a step (ncu, batch 256)" if traffic else "not captured for this configuration",

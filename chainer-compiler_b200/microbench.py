@@ -2,7 +2,7 @@
 LSTM-cell elementwise group, the MatMulInteger / QLinearMatMul sweep, MobileNetV2, QuantizeLinear / DequantizeLinear and
 single depthwise layers.  One JSON line per measurement on stdout.
 
-    python chainer-compiler_b200/microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [prepare] [onnx]
+    python chainer-compiler_b200/microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [prepare] [onnx] [stem[=BATCH]]
 
 Timing: CUDA events on the launching stream, 3 warm-up calls, median of 10 (3 for the largest GEMMs), a 256 MB buffer
 rewritten between calls so that nothing is served from L2.  `gbs` is algorithmic bytes (every input read once, every
@@ -34,7 +34,7 @@ def main():
         raise SystemExit("microbench.py needs a CUDA device: this package has no CPU path")
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare", "onnx"}
+    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare", "onnx", "stem"}
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     peak, peak_src = hbm_peak_gbs()
 
@@ -158,6 +158,30 @@ def main():
             s = (g / np.sqrt(var + np.float32(2e-5))).astype(np.float32)
             models.quantize_weights((w * s.reshape(-1, 1, 1, 1)).astype(np.float32), per_channel=True, to_int8=True)
         emit("the same on one host core (NumPy merge + the library's host quantizer)", (time.perf_counter() - t0) * 1e3)
+    for token in sorted(which):
+        if token != "stem" and not token.startswith("stem="):
+            continue
+        # the head of ResNet-50 on a uint8 image batch: 7x7 / 2 stem convolution (64 channels) and 3x3 / 2 max pooling, as two
+        # calls and as one
+        from chainer_compiler_b200 import _lib as L
+        B = int(token.split("=")[1]) if "=" in token else 256
+        rng = np.random.default_rng(0)
+        xq = torch.randint(0, 256, (B, 3, 224, 224), dtype=torch.uint8, device=dev)
+        w = torch.from_numpy(rng.integers(-127, 128, (64, 3, 7, 7)).astype(np.int8)).to(dev)
+        wz = torch.zeros(64, dtype=torch.int8, device=dev)
+        ws = torch.full((64,), 1e-3, device=dev)
+        bias = torch.zeros(64, dtype=torch.int32, device=dev)
+        pk = ops.PackedConv(w, wz, xq.shape, (2, 2), (3, 3), x_layout=L.NCHW)
+        args = (pk, 1 / 255.0, np.uint8(0), ws, wz, 0.05, np.uint8(0))
+        ms = timeit(lambda: ops.QLinearConvPacked(xq, *args, b=bias, fold_scales=True))
+        emit("stem 7x7/2 QLinearConv, batch %d: space-to-depth repack + tensor-core kernel (halo tiles)" % B, ms)
+        y = ops.QLinearConvPacked(xq, *args, b=bias, fold_scales=True)
+        ms = timeit(lambda: ops.MaxPoolU8(y, 3, 2, 0, cover_all=True))
+        emit("3x3/2 MaxPool of the stem output, batch %d" % B, ms, gbs=(y.numel() * 1.25) / ms / 1e6)
+        ms = timeit(lambda: ops.QLinearConvMaxPoolPacked(xq, *args, b=bias, cover_all=True, fold_scales=True))
+        emit("stem QLinearConv + MaxPool as one call, batch %d" % B, ms)
+        del xq, y
+
     if "onnx" in which:
         # the run_onnx entry point on a statically quantized ResNet-50 file (written from the calibrated hand-built network):
         # Elapsed as the reference's tool reports it, inputs staged on the device before the clock starts
