@@ -327,6 +327,30 @@ def run_chxq(args):
                              "QLinearConv), one timed pass after a discarded first run" % (args.cpu_sample, args.batch)}
     if world > 1:
         dist.barrier()
+    # ---- the same step with the reference's operation order in every requantization (multiply, divide), for comparison ------
+    ref_order = None
+    if rank == 0 and world == 1 and fold:
+        logits_fold = net.forward(eng.x_dev, fold=True).clone()
+        g_exact, logits_exact = net.capture(eng.x_dev, fold=False)
+        for _ in range(3):
+            g_exact.replay()
+        torch.cuda.synchronize(dev)
+        n_exact = max(3, args.steps // 4)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_exact):
+            g_exact.replay()
+        b.record()
+        torch.cuda.synchronize(dev)
+        ms_exact = a.elapsed_time(b) / n_exact
+        ref_order = {"ms_per_step": ms_exact, "value": args.batch / (ms_exact / 1000.0), "unit": "img/s", "steps": n_exact,
+                     "top1_agreement_with_folded": float((logits_fold.argmax(1) == logits_exact.argmax(1)).float().mean().item()),
+                     "max_abs_logit_difference": float((logits_fold - logits_exact).abs().max().item()),
+                     "max_abs_logit": float(logits_exact.abs().max().item()),
+                     "note": "fold_scales off: every QLinearConv requantizes with the reference's multiply and divide (runtime/ops/quantize.cc:16-35); "
+                             "the headline runs the single-multiplier form, at most one output step apart per layer"}
+        del g_exact
+        ops.device_status()
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -344,6 +368,7 @@ def run_chxq(args):
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roof,
             "cpu_baseline": cpu,
+            "reference_order_requantization": ref_order,
             "tops": 2.0 * net.macs_per_image() * args.batch * world / (ms_per_step / 1000.0) / 1e12,
         }
         print(json.dumps(line), flush=True)
