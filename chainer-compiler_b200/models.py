@@ -343,6 +343,30 @@ class QuantizedMLP:
             h = ops.QLinearMatMul(h, self.act_scale, np.uint8(0), l["dev"], l["w_scale"], np.int8(0), self.act_scale, np.uint8(0), path=path)
         return ops.DequantizeLinear(h, self.act_scale, np.uint8(0))
 
+    def forward_packed(self, x):
+        """The same five ops with the constant weights packed once: each QLinearMatMul runs as a packed 1x1 QLinearConv over the
+        batch seen as an [N, K, 1, 1] map (no per-call repacking of B).  Same results as forward().  Layers whose inner
+        dimension is not a multiple of 16 keep the QLinearMatMul entry."""
+        h = ops.QuantizeLinear(x, self.act_scale, np.uint8(0))
+        n = h.shape[0]
+        for l in self.layers:
+            k, m = l["w_q"].shape
+            if k % 16 or m % 16:
+                h = ops.QLinearMatMul(h, self.act_scale, np.uint8(0), l["dev"], l["w_scale"], np.int8(0), self.act_scale, np.uint8(0))
+                continue
+            key = ("packed", n)
+            if key not in l:
+                w = l["dev"].t().contiguous().reshape(m, k, 1, 1)
+                zw = torch.zeros((), dtype=torch.int8, device=self.device)
+                l[key] = (ops.PackedConv(w, zw, (n, k, 1, 1)), torch.tensor(float(l["w_scale"]), device=self.device), zw)
+            pk, ws, zw = l[key]
+            hm = h.reshape(n, k, 1, 1).contiguous(memory_format=torch.channels_last)
+            if pk.eligible:
+                h = ops.QLinearConvPacked(hm, pk, self.act_scale, np.uint8(0), ws, zw, self.act_scale, np.uint8(0)).reshape(n, m)
+            else:
+                h = ops.QLinearMatMul(h, self.act_scale, np.uint8(0), l["dev"], l["w_scale"], np.int8(0), self.act_scale, np.uint8(0))
+        return ops.DequantizeLinear(h, self.act_scale, np.uint8(0))
+
 
 # (expansion t, output channels c, repeats n, stride s) of MobileNetV2-1.0.
 MOBILENETV2_BLOCKS = [(1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)]

@@ -136,6 +136,8 @@ def test_mlp_matches_oracle(pkg, ops, orc, dev):
         y = mlp.forward(torch.from_numpy(x).to(dev), path=path).cpu().numpy()
         assert y.shape == (64, 10) and np.array_equal(y, exact)
         assert np.abs(y - emul).max() <= 3 * float(mlp.act_scale)  # three requantizing layers, one step each at most... compounded
+    # constant weights packed once (each MatMul as a packed 1x1 convolution): the same bits
+    assert np.array_equal(mlp.forward_packed(torch.from_numpy(x).to(dev)).cpu().numpy(), exact)
     ops.device_status()
 
 
