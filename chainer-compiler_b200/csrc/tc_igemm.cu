@@ -311,10 +311,22 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
             p.halo_swz = s2d_halo ? 0 : (g_variant == 5 ? 2 : ((g_variant == 4 || q.bk == 128) ? 1 : 0));  // 128-byte pixels: the swizzled form only
             const cuuint32_t box[4] = {p.halo_swz ? (cuuint32_t)q.bk : 16u, (cuuint32_t)p.halo_w, (cuuint32_t)p.halo_h, 1u};
             const cuuint32_t estr[4] = {1, 1, 1, 1};
-            CUresult r0 = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                 p.halo_swz ? swizzle_for(q.bk) : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r0 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A halo) failed with %d", (int)r0);
+            p.halo_row_map = s2d_halo ? 1 : 0;
+            if (s2d_halo) {
+                // rows of blocks are contiguous: {row bytes, rows, images, 1} with a box of halo_h rows of halo_w * 16 bytes moves the same
+                // bytes to the same places in 19 long rows instead of 209 16-byte ones
+                const cuuint64_t rdims[4] = {(cuuint64_t)q.a_row_bytes, (cuuint64_t)q.H, (cuuint64_t)q.N, 1};
+                const cuuint64_t rstrides[3] = {(cuuint64_t)q.a_row_bytes, (cuuint64_t)q.a_row_bytes * q.H, (cuuint64_t)q.a_row_bytes * q.H * q.N};
+                const cuuint32_t rbox[4] = {(cuuint32_t)(p.halo_w * 16), (cuuint32_t)p.halo_h, 1u, 1u};
+                CUresult r0 = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q.a), rdims, rstrides, rbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (r0 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A halo rows) failed with %d", (int)r0);
+            } else {
+                CUresult r0 = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     p.halo_swz ? swizzle_for(q.bk) : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (r0 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A halo) failed with %d", (int)r0);
+            }
         }
         if (grouped && pool) {
             tmY = tmA;  // the pooling form writes the pooled map with plain stores and reads no residual: the maps are placeholders

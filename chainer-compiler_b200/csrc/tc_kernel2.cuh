@@ -289,11 +289,19 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA), &tmA, hfull_bar(hstage), gbase + cc * BK,
                                             w0[t] - p.pad_left, h0[t] - p.pad_top, n0[t]);
                         } else {
+                            if (p.halo_row_map) {
+                                // 16-byte pixels: a halo row is contiguous in memory, so the tile is halo_h long rows, not halo_w x halo_h short ones
 #pragma unroll
-                            for (int t = 0; t < kR; ++t)
-                                for (int j = 0; j < p.halo_planes; ++j)
-                                    tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA + j * kHaloPlane), &tmA, hfull_bar(hstage),
-                                                gbase + cc * BK + j * 16, w0[t] - p.pad_left, h0[t] - p.pad_top, n0[t]);
+                                for (int t = 0; t < kR; ++t)
+                                    tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA), &tmA, hfull_bar(hstage),
+                                                16 * (w0[t] - p.pad_left), h0[t] - p.pad_top, n0[t], 0);
+                            } else {
+#pragma unroll
+                                for (int t = 0; t < kR; ++t)
+                                    for (int j = 0; j < p.halo_planes; ++j)
+                                        tma_load_4d(smem_u32(smem_a + hstage * Cfg::kStageA + t * Cfg::kTileA + j * kHaloPlane), &tmA, hfull_bar(hstage),
+                                                    gbase + cc * BK + j * 16, w0[t] - p.pad_left, h0[t] - p.pad_top, n0[t]);
+                            }
                         }
                         if (++hstage == Cfg::kAStages) {
                             hstage = 0;

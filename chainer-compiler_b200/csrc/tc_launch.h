@@ -23,6 +23,7 @@ struct TcParams {
     // halo_lbo 16-byte units apart (one plane for channel chunks; one pixel for the space-to-depth stem, whose K runs along the row),
     // consecutive MMAs of a tap halo_kstep units
     int halo_w, halo_h, halo_planes, halo_lbo, halo_kstep;
+    int halo_row_map;  // the A map is {bytes of a row, rows, images}: a halo tile is halo_h rows of halo_w * 16 contiguous bytes (16-byte pixels only)
     int group_cols, group_cin;  // grouped convolution (0 = one group): first input channel of a column tile = (col0 / group_cols) * group_cin
     int c_chunks;  // c_pad / BK
     int c_pad;
