@@ -33,7 +33,9 @@ def parse():
     ap.add_argument("--impl", default="chxq", choices=["chxq", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU")
     ap.add_argument("--cpu-sample", type=int, default=8, help="images of the CPU-baseline sample")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline and the parity check that shares its sample")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the measurements of the workloads beside the headline")
+    ap.add_argument("--sustain-s", type=float, default=2.0, help="seconds of the sustained loop that follows the timed region")
     ap.add_argument("--tc-variant", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
                     help="tensor-core kernel choice (chxq_tc_variant): 0 by shape, 1 one tile per step, 2 grouped tiles")
     ap.add_argument("--exact-requant", action="store_true",
@@ -138,18 +140,6 @@ def cpu_reference_params(orc, networks, seed, sample):
     return net.export_numpy()
 
 
-def time_cpu(orc, networks, params, sample, repeats=1):
-    """Seconds per forward of the reference-algorithm chain (first run discarded, as tools/run_onnx.cc:468-469 of the reference does)."""
-    networks.resnet50_forward(params, sample[:1], mode="emulate")
-    best = None
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        networks.resnet50_forward(params, sample, mode="emulate")
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return best
-
-
 def run_reference(args):
     """CPU arm: rank 0 alone works; other ranks exit 0 without work."""
     rank = int(os.environ.get("RANK", "0"))
@@ -184,12 +174,90 @@ def run_reference(args):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "ResNet-50 v1 int8 inference, 3x224x224 (configs[4]); CPU sample of %d images per step" % n_img,
                    "batch_per_gpu": args.batch, "note": "the reference binary cannot be built here (ChainerX/ONNX/protobuf submodules empty); "
-                   "this is the oracle restatement of its algorithm on the host cores"},
+                   "this is the oracle restatement of its algorithm on the host cores.  The oracle's fp32 convolution is a direct loop "
+                   "(OpenMP over output channels), not the im2col + GEMM a tuned native backend would run, so this is a pessimistic CPU figure.  "
+                   "The arm imports this repository's models module to generate the seeded weights only (that loads libchxq.so for the host-side "
+                   "weight quantizer); the timed region runs nothing but the oracle"},
         "cpu_baseline": {"value": value, "unit": "img/s", "cores": cores, "kind": "port", "sample": sample_txt},
         "e2e": {"value": value, "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def csrc_digest():
+    """SHA-256 over the kernel sources: ties a recorded DRAM-traffic figure to the code it was captured on."""
+    import glob
+    import hashlib
+    h = hashlib.sha256()
+    for path in sorted(glob.glob(os.path.join(ROOT, "chainer-compiler_b200", "csrc", "*.cu*")) + glob.glob(os.path.join(ROOT, "chainer-compiler_b200", "csrc", "*.h"))):
+        h.update(os.path.basename(path).encode())
+        h.update(open(path, "rb").read())
+    return h.hexdigest()
+
+
+def recorded_traffic(batch, fold):
+    """DRAM bytes per tensor-core launch from profiles/tc_dram_traffic.json (one ncu pass of dram__bytes_read.sum +
+    dram__bytes_write.sum over the convolutions of one step), or (None, why) when the record is for other kernel sources."""
+    path = os.path.join(ROOT, "profiles", "tc_dram_traffic.json")
+    if not os.path.exists(path):
+        return None, "no record in profiles/"
+    rec = json.load(open(path))
+    if rec.get("csrc_sha256") != csrc_digest():
+        return None, "the record in profiles/tc_dram_traffic.json was captured on other kernel sources"
+    if not fold or not rec.get("fold", True):
+        return None, "the record is for the folded requantization only"
+    per_launch = rec["bytes_per_step"] / rec["launches_per_step"] * (batch / float(rec["batch"]))
+    note = "ncu capture at batch %d" % rec["batch"]
+    if rec["batch"] != batch:
+        note += ", scaled to batch %d by the images per step (activation traffic grows with the batch; the 23.5 MB of weights do not)" % batch
+    return per_launch, note
+
+
+def int8_probe(dev):
+    """Dense int8 GEMM throughput of this GPU through the vendor library (torch._int_mm, 8192^3), best of 10: a MEASUREMENT of
+    the tensor pipe's int8 peak beside the bf16 figures of MEASURED_PEAKS.json, never a product path."""
+    import torch
+    try:
+        n = 8192
+        a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize(dev)
+        best = None
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            t = e0.elapsed_time(e1)
+            best = t if best is None else min(best, t)
+        return 2.0 * n ** 3 / (best / 1000.0) / 1e12, None
+    except Exception as exc:  # the probe is optional: say why there is no number
+        return None, "%s: %s" % (type(exc).__name__, str(exc)[:120])
+
+
+def h2d_ceiling(host_x, dev, world, dp, repeats=8):
+    """Aggregate GB/s of plain pinned-memory host-to-device copies of one step's input, every rank copying at once and nothing
+    else running: the platform's ceiling for the end-to-end number."""
+    import torch
+    import torch.distributed as dist
+    dst = torch.empty_like(host_x, device=dev)
+    dst.copy_(host_x, non_blocking=True)
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(repeats):
+        dst.copy_(host_x, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = dp.max_over_ranks(e0.elapsed_time(e1), dev, world) / repeats
+    del dst
+    return host_x.numel() * 4 * world / (ms / 1000.0) / 1e9
 
 
 def run_chxq(args):
@@ -211,13 +279,15 @@ def run_chxq(args):
     # Same seeded weights on every rank; every rank works on its own seeded images (weak scaling: 256 images per GPU).
     net = models.ResNet50Int8(batch=args.batch, device=dev, seed=0, image=IMAGE)
     fold = not args.exact_requant
-    eng = dp.InferenceEngine(net, world, fold=fold)
+    gop_per_image = 2.0 * net.macs_per_image() / 1e9
+    eng = dp.InferenceEngine(net, world, fold=fold, rank=rank)
     gen = torch.Generator(device="cpu").manual_seed(1234)
     calib = torch.rand((args.batch, 3, IMAGE, IMAGE), generator=gen, dtype=torch.float32)
     eng.prepare(calib.to(dev))
     gen_r = torch.Generator(device="cpu").manual_seed(99 + rank)
-    host_x = torch.rand((args.batch, 3, IMAGE, IMAGE), generator=gen_r, dtype=torch.float32).pin_memory()
-    eng.x_dev.copy_(host_x)
+    host_x = dp.pinned_like((args.batch, 3, IMAGE, IMAGE), torch.float32, local_rank)
+    host_x.copy_(torch.rand((args.batch, 3, IMAGE, IMAGE), generator=gen_r, dtype=torch.float32))
+    eng.set_resident_input(host_x)
     ops.device_status()
 
     def barrier():
@@ -231,6 +301,17 @@ def run_chxq(args):
     torch.cuda.synchronize(dev)
     launches_per_step = int(L.chxq_launch_count() - c0)
 
+    def timed(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            eng.step_device()
+        eng.drain()  # the last steps' logits all-gathers belong to the region
+        e1.record()
+        barrier()
+        return dp.max_over_ranks(e0.elapsed_time(e1), dev, world)
+
     # ---- device-resident timed region -----------------------------------------------------------------
     for _ in range(max(3, args.warmup)):
         eng.step_device()
@@ -238,29 +319,29 @@ def run_chxq(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        eng.step_device()
-    e1.record()
-    barrier()
-    ms_total = dp.max_over_ranks(e0.elapsed_time(e1), dev, world)
-    if ms_total < 600.0:
-        # a short timed region gives nvidia-smi no time for samples: keep the same loop running (untimed) until the sampler
-        # has seen ~0.6 s of this load
-        t_end = time.perf_counter() + (600.0 - ms_total) / 1000.0
-        while time.perf_counter() < t_end:
-            for _ in range(10):
-                eng.step_device()
-            torch.cuda.synchronize(dev)
-        barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None and ms_total < 600.0:
-        clocks["note"] = "timed region of %.0f ms extended by an untimed continuation of the same loop for the samples" % ms_total
-    ops.device_status()
+    ms_total = timed(args.steps)
+    clocks_burst = sampler.stop() if rank == 0 else None
     ms_per_step = ms_total / args.steps
     value = args.batch * world / (ms_per_step / 1000.0)
+
+    # ---- the same loop for >= 2 s: what the GPU sustains once it sits at its power limit ----------------------
+    sustained_steps = max(args.steps, int(args.sustain_s * 1000.0 / ms_per_step) + 1)
+    sampler2 = ClockSampler(local_rank)
+    if rank == 0:
+        sampler2.start()
+    ms_sus = timed(sustained_steps)
+    clocks = sampler2.stop() if rank == 0 else None
+    ops.device_status()
+    sus_ms_per_step = ms_sus / sustained_steps
+    sustained = None
+    if rank == 0:
+        mhz = clocks.get("sm_mhz") if clocks else None
+        sustained = {"img_s": args.batch * world / (sus_ms_per_step / 1000.0), "ms_per_step": sus_ms_per_step, "steps": sustained_steps,
+                     "seconds": ms_sus / 1000.0, "sm_mhz_median": mhz, "time_x_mhz": sus_ms_per_step * mhz if mhz else None,
+                     "reasons": clocks.get("reasons") if clocks else None}
+        if clocks is not None:
+            clocks["note"] = "sampled over the %.1f s sustained loop that follows the timed region; burst-region samples: %s" % (
+                ms_sus / 1000.0, json.dumps(clocks_burst))
 
     # ---- end to end through the public host-buffer call ---------------------------------------------------
     # run_stream double-buffers: batch i+1 crosses PCIe while batch i computes; every step still copies its own input from
@@ -268,6 +349,7 @@ def run_chxq(args):
     for _ in eng.run_stream([host_x] * 3):
         pass
     barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
     for _ in eng.run_stream([host_x] * args.steps):
@@ -278,10 +360,13 @@ def run_chxq(args):
     e2e_wall_ms = 1000.0 * (time.perf_counter() - t0) / args.steps
     e2e_value = args.batch * world / (e2e_ms / 1000.0)
     h2d = host_x.numel() * 4
-    d2h = eng.host_logits.numel() * 4
+    d2h = eng.slots[0]["host"].numel() * 4  # rank 0: the gathered logits of the whole job; other ranks copy their own rows only
+    ceiling_gbs = h2d_ceiling(host_x, dev, world, dp)
+    e2e_h2d_gbs = h2d * world / (e2e_ms / 1000.0) / 1e9
 
     # ---- roofline of the dominant kernel (tcgen05 implicit GEMM), timed with CUDA events per launch ---------
-    roof = cpu = None
+    roof = cpu = parity = None
+    emulate_logits = None
     if rank == 0:
         L.chxq_tc_profile(1)
         prof_steps = 3
@@ -304,34 +389,58 @@ def run_chxq(args):
         tms.value = max(raw_ms - pair_ms * n.value, 0.5 * raw_ms)
         pk = peaks()
         achieved = 2.0 * macs.value / (tms.value / 1000.0) / 1e12
-        peak = 2.0 * pk["bf16_sustained"]
-        # DRAM traffic of the 53 tensor-core launches of one step at batch 256, one ncu pass per launch
-        # (dram__bytes_read.sum + dram__bytes_write.sum = 4537.9 MB per step; summary in profiles/tc_igemm2_resnet50_b256.txt)
-        traffic = 4537.9e6 / 53 if args.batch == 256 and fold else None
+        peak = 2.0 * pk["bf16_burst"]  # the per-launch events above time a short burst at full clocks
+        traffic, traffic_note = recorded_traffic(args.batch, fold)
+        probe_tops, probe_err = int8_probe(dev)
+        share = (tms.value / prof_steps) / ms_per_step
+        sus_tops = achieved * (ms_per_step / sus_ms_per_step)  # same kernels, same share of the step, at the sustained clocks
         roof = {"bound": "tensor", "kernel": "tc_igemm2_kernel (tcgen05 kind::i8 implicit GEMM, grouped tiles, all 53 convolutions)",
-                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
-                "traffic_note": "bytes per launch, average over the 53 launches of a step (ncu, batch 256)" if traffic else "not captured for this configuration",
-                "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s; the file has no int8 entry; int8 ops counted as 2 per MAC)" % pk["source"],
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic, "traffic_note": traffic_note,
+                "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s; the file has no int8 entry; int8 ops counted as 2 per MAC); of %s"
+                               % (pk["source"], "measured" if pk["source"] == "measured" else "fallback"),
+                "int8_probe_tops": probe_tops, "int8_probe_note": probe_err or "torch._int_mm 8192^3 on this GPU, best of 10 (vendor library; measurement only)",
+                "frac_of_int8_probe": achieved / probe_tops if probe_tops else None,
+                "frac_of_nominal_4500_tops": achieved / 4500.0,
+                "sustained": {"achieved": sus_tops, "peak": 2.0 * pk["bf16_sustained"], "frac": sus_tops / (2.0 * pk["bf16_sustained"]),
+                              "peak_source": "2 x bf16_tflops_sustained"},
                 "launches_per_step": int(n.value // prof_steps), "kernel_ms_per_step": tms.value / prof_steps,
                 "event_pair_overhead_us": pair_ms * 1000.0, "kernel_ms_per_step_uncorrected": raw_ms / prof_steps,
-                "share_of_step": (tms.value / prof_steps) / ms_per_step, "algorithmic_gop_per_step": 2.0 * macs.value / prof_steps / 1e9}
+                "share_of_step": share, "algorithmic_gop_per_step": 2.0 * macs.value / prof_steps / 1e9}
         if not args.no_cpu_baseline:
             orc = entry.load_oracle()
             from oracle import networks
             orc.set_num_threads(len(os.sched_getaffinity(0)))
             sample = host_x[: args.cpu_sample].numpy()
             params = net.export_numpy()
-            sec = time_cpu(orc, networks, params, sample)
+            networks.resnet50_forward(params, sample[:1], mode="emulate")  # first run discarded (tools/run_onnx.cc:468-469 of the reference)
+            t0 = time.perf_counter()
+            emulate_logits = networks.resnet50_forward(params, sample, mode="emulate")
+            sec = time.perf_counter() - t0
             cpu = {"value": args.cpu_sample / sec, "unit": "img/s", "cores": orc.num_threads(), "kind": "port",
                    "sample": "%d of the %d images of one step through the oracle's reference-algorithm chain (dequantize, fp32 conv, quantize per "
-                             "QLinearConv), one timed pass after a discarded first run" % (args.cpu_sample, args.batch)}
+                             "QLinearConv; the convolution is a direct loop, not im2col + GEMM), one timed pass after a discarded first run"
+                             % (args.cpu_sample, args.batch)}
+            # ---- parity on this very configuration: the images of the CPU sample through the GPU network, tapped per operator ----
+            taps = {}
+            gl = net.forward(eng.x_dev, fold=fold, taps=taps, detail=True)
+            k = args.cpu_sample
+            to_np = lambda t: t[:k].contiguous().cpu().numpy()  # noqa: E731  (logically NCHW; .contiguous() undoes channels_last)
+            np_taps = {name: to_np(t) for name, t in taps.items()}
+            graph_logits = eng.slots[0]["logits"]
+            eng.slots[0]["graph"].replay()
+            torch.cuda.synchronize(dev)
+            parity = networks.resnet50_parity(params, sample, np_taps, gl[:k].cpu().numpy(), fold=fold, emulate_logits=emulate_logits)
+            parity["config"] = "ResNet-50 v1 224x224 full width, the first %d images of rank 0's batch of %d" % (k, args.batch)
+            parity["captured_graph_logits_equal_tapped_run"] = bool(torch.equal(graph_logits, gl))
+            parity["ok"] = bool(parity["ok"] and parity["captured_graph_logits_equal_tapped_run"])
+            del taps, np_taps
     if world > 1:
         dist.barrier()
     # ---- the same step with the reference's operation order in every requantization (multiply, divide), for comparison ------
     ref_order = None
     if rank == 0 and world == 1 and fold:
         logits_fold = net.forward(eng.x_dev, fold=True).clone()
-        g_exact, logits_exact = net.capture(eng.x_dev, fold=False)
+        g_exact, logits_exact = net.capture(eng.slots[0]["x"], fold=False)
         for _ in range(3):
             g_exact.replay()
         torch.cuda.synchronize(dev)
@@ -348,9 +457,26 @@ def run_chxq(args):
                      "max_abs_logit_difference": float((logits_fold - logits_exact).abs().max().item()),
                      "max_abs_logit": float(logits_exact.abs().max().item()),
                      "note": "fold_scales off: every QLinearConv requantizes with the reference's multiply and divide (runtime/ops/quantize.cc:16-35); "
-                             "the headline runs the single-multiplier form, at most one output step apart per layer"}
+                             "the headline runs the single-multiplier form, at most one output step apart per operator (see parity)"}
         del g_exact
         ops.device_status()
+    # ---- the workloads beside the headline (rank 0, after every timed region) --------------------------------------------
+    secondary = None
+    if rank == 0 and not args.no_secondary:
+        del eng, net
+        torch.cuda.empty_cache()
+        import microbench
+        t0 = time.perf_counter()
+        try:
+            secondary = {"results": microbench.secondary(dev), "seconds": None,
+                         "note": "per-operator measurements of microbench.py: CUDA events, 3 warm-ups, median of 10 (3 for the largest GEMMs), a 256 MB "
+                                 "buffer rewritten between calls; GB/s are algorithmic bytes, fractions against the measured copy bandwidth and "
+                                 "against the nominal 8 TB/s; TOPS against the nominal 4.5 POPS"}
+        except Exception as exc:
+            secondary = {"error": "%s: %s" % (type(exc).__name__, str(exc)[:200])}
+        secondary["seconds"] = time.perf_counter() - t0
+    if world > 1:
+        dist.barrier()
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -360,20 +486,33 @@ def run_chxq(args):
                                    % args.batch,
                        "batch_per_gpu": args.batch, "global_batch": args.batch * world, "parallelism": "dp%d" % world,
                        "l2": "inputs (154 MB fp32 per step) and activations are larger than the 126 MB L2; no explicit flush",
-                       "gop_per_image": 2.0 * net.macs_per_image() / 1e9, "cuda_graph": True,
-                       "requantization": "one folded multiplier per channel (fold_scales)" if fold else "reference operation order"},
+                       "gop_per_image": gop_per_image, "cuda_graph": True,
+                       "requantization": "one folded multiplier per channel (fold_scales)" if fold else "reference operation order",
+                       "parity_class": ("folded requantization: bit-exact against the oracle's restatement of that arithmetic, at most one output step "
+                                        "from the reference's operation order per operator (see parity); --exact-requant runs the reference's order")
+                       if fold else "reference operation order: bit-exact against the integer-domain oracle",
+                       "vs_baseline_note": "null: the reference publishes no number for this metric; cpu_baseline is measured in this run"},
             "clocks": clocks,
+            "sustained": sustained,
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "wall_ms_per_step": e2e_wall_ms},
+                    "wall_ms_per_step": e2e_wall_ms, "h2d_gbs": e2e_h2d_gbs, "h2d_ceiling_gbs": ceiling_gbs,
+                    "frac_of_h2d_ceiling": e2e_h2d_gbs / ceiling_gbs if ceiling_gbs else None,
+                    "note": "h2d_ceiling_gbs: every rank copying the same pinned input at once with nothing else running (aggregate over ranks); "
+                            "d2h bytes are rank 0's (the whole job's logits), other ranks copy their own rows"},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roof,
             "cpu_baseline": cpu,
+            "parity": parity,
             "reference_order_requantization": ref_order,
-            "tops": 2.0 * net.macs_per_image() * args.batch * world / (ms_per_step / 1000.0) / 1e12,
+            "secondary": secondary,
+            "tops": gop_per_image * args.batch * world / (ms_per_step / 1000.0) / 1e3,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.stderr.write("bench.py: parity check failed: %s\n" % json.dumps(parity))
+        sys.exit(1)
 
 
 def main():

@@ -3,6 +3,8 @@
 // pre-pass kernels that feed the tensor-core kernel (operand repacking and zero-point terms).
 #include <string.h>
 
+#include <atomic>
+
 #include "common.h"
 #include "kernels.h"
 
@@ -485,6 +487,7 @@ int conv_tc_run(
                   es_n = nhwc ? xcs * g.W * g.H : (int64_t)g.C * g.H * g.W;
     if (pl.path == kTcS2d) {
         uint8_t* A = scratch;
+        if (quant_in && !zw_zero) return set_error(CHXQ_ERR_UNSUPPORTED, "fused QuantizeLinear + QLinearConv needs zero weight zero points");
         if (quant_in)
             s2d_repack_kernel<true><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
                     x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), *quant_in,
@@ -493,7 +496,6 @@ int conv_tc_run(
             s2d_repack_kernel<false><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
                     x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), S2dQuant{}, reinterpret_cast<uint4*>(A));
         CHXQ_LAUNCH_CHECK();
-        if (quant_in && !zw_zero) return set_error(CHXQ_ERR_UNSUPPORTED, "fused QuantizeLinear + QLinearConv needs zero weight zero points");
         if (!zw_zero) {
             rowsum = reinterpret_cast<int32_t*>(scratch + L.im2col_bytes);
             conv_possum_kernel<<<blocks_for(rows), 256, 0, s>>>(static_cast<const uint8_t*>(x), x_signed, g.N, g.H, g.W, g.C, es_n, es_c, es_h, es_w,
@@ -638,6 +640,7 @@ int fill_requant(const char* op, const chxq_qconv_params* p, const chxq_conv_geo
         e->rq.fold = 1;
         e->rq.y_over_out = p->residual ? p->y_scale / p->out_scale : 0.f;
         e->rq.res_over_out = p->residual ? p->res_scale / p->out_scale : 0.f;
+        finish_fold_params(&e->rq);
     }
     return CHXQ_OK;
 }
@@ -690,18 +693,25 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[CHXQ_NOALLOC_SC
 
 // In host code the array's name is only a stand-in for the symbol, not a device address: the address a kernel can use
 // comes from cudaGetSymbolAddress, asked once per device with that device current.
-int noalloc_scratch_ptr(void** out) {
-    static void* cache[64] = {};
+int noalloc_scratch_ptr(void** out, cudaStream_t s) {
+    static std::atomic<void*> cache[64] = {};  // two host threads may make the first call together: both store the same address
     int dev = 0;
     CHXQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return set_error(CHXQ_ERR_UNSUPPORTED, "MatMulInteger(noalloc): device ordinal %d out of range", dev);
-    if (cache[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = cache[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
+        // The lookup is not a stream operation and fails with an opaque error inside a capture: say what to do instead.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return set_error(CHXQ_ERR_UNSUPPORTED,
+                             "MatMulInteger(noalloc): the first call on a device looks up the scratch array's address and cannot run "
+                             "inside a stream capture; make one call on this device before capturing");
+        cudaGetLastError();
         CHXQ_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
         if (ptr == nullptr) return set_error(CHXQ_ERR_CUDA, "MatMulInteger(noalloc): the scratch symbol has no device address");
-        cache[dev] = ptr;
+        cache[dev].store(ptr, std::memory_order_release);
     }
-    *out = cache[dev];
+    *out = ptr;
     return CHXQ_OK;
 }
 
@@ -738,7 +748,7 @@ extern "C" int chxq_matmul_integer_noalloc(
                          "chxq_matmul_integer with a caller-provided workspace",
                          (long long)M, (long long)N, (long long)K, need, (int)CHXQ_NOALLOC_SCRATCH_BYTES);
     void* scratch = nullptr;
-    rc = noalloc_scratch_ptr(&scratch);
+    rc = noalloc_scratch_ptr(&scratch, s);
     if (rc != CHXQ_OK) return rc;
     return gemm_dispatch("MatMulInteger(noalloc)", a, a_dtype == CHXQ_INT8, b, b_dtype == CHXQ_INT8, 1, M, N, K, za, zb, epi, y, 4, scratch,
                          (size_t)CHXQ_NOALLOC_SCRATCH_BYTES, CHXQ_PATH_TENSOR, s);

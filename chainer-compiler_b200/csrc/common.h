@@ -8,6 +8,7 @@
 #include <string>
 
 #include "../../include/chxq.h"
+#include "../../include/chxq_testing.h"
 
 namespace chxq {
 

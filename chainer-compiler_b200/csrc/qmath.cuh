@@ -140,6 +140,7 @@ struct RequantParams {
     int fold;
     float y_over_out;    // y_scale / out_scale
     float res_over_out;  // res_scale / out_scale
+    float fold_a, fold_r, fold_c;  // round-half-up residual tail in units of the output range (see residual_fold)
     // constant-divisor forms of y_scale and out_scale (see QDiv)
     QDiv y_div, out_div;
 };
@@ -147,6 +148,14 @@ struct RequantParams {
 inline void finish_requant_params(RequantParams* p) {
     p->y_div = make_qdiv(p->y_scale);
     p->out_div = make_qdiv(p->out_scale != 0.f ? p->out_scale : 1.f);
+}
+
+// Constants of the folded residual tail; call once y_over_out / res_over_out and the zero points are set.  The additive term
+// is evaluated in double and rounded once, so that every implementation of it (this one, the CPU oracle's) gives the same float.
+inline void finish_fold_params(RequantParams* p) {
+    p->fold_a = p->y_over_out / 255.5f;
+    p->fold_r = p->res_over_out / 255.5f;
+    p->fold_c = (float)((((double)p->out_zp_f + 0.5) - (double)p->y_zp_f * (double)p->y_over_out - (double)p->res_zp_f * (double)p->res_over_out) / 255.5);
 }
 
 // acc (exact int32, bias already added) -> quantized output value.
@@ -162,31 +171,74 @@ __device__ __forceinline__ int requant_u8_fast(int acc, float mult, const Requan
     return quantize_one<false>(__fmul_rn((float)acc, mult), p.y_scale, p.y_zp_f, p.y_has_zp != 0, p.round_mode);
 }
 
-// Folded requantization of a uint8 output (RequantParams::fold; no counterpart in the reference): one multiplier and one
-// additive term per channel,
-//     M = (x_scale * w_scale[c]) / y_scale,        B = fma(float(bias), M, y_zp + 0.5)        (round-half-up)
-//     y = min(max(floor(fma(float(acc), M, B)), 0), hi)
-// or, for round-half-to-even, B = fma(float(bias), M, y_zp) and y = clamp(rint(fma(float(acc), M, B)), 0, hi).
+// Folded requantization of a uint8 output (RequantParams::fold; no counterpart in the reference).
+//
+// Round-half-up (the reference's rounding).  Per channel, with hp = hi + 0.5 (hi = 255 or the optional upper clamp):
+//     M  = (x_scale * w_scale[c]) / y_scale        B  = fma(float(bias), M, y_zp + 0.5)
+//     Ms = M / hp                                  Bs = B / hp
+// per element, with sat(v) = min(max(v, 0), 1):
+//     t = sat(fma(float(acc), Ms, Bs))             y = floor(t * hp)        (the product is exact, one floor)
+// i.e. the value is computed in units of the output range, where the saturation of one fused multiply-add is both clamps
+// (a zero lower bound is the ReLU when y_zp == 0) and one more multiply-add with a round-down places the integer.
+// Round-half-to-even keeps the plain form: B = fma(float(bias), M, y_zp), y = clamp(rint(fma(float(acc), M, B)), 0, hi).
 // `acc` is the accumulator without the bias.
-__device__ __forceinline__ float fold_offset(int bias, float m, const RequantParams& p) {
-    return __fmaf_rn((float)bias, m, p.round_mode != 0 ? p.y_zp_f : __fadd_rn(p.y_zp_f, 0.5f));
+struct FoldCh {
+    float ms, bs;
+};
+
+__device__ __forceinline__ float fold_hi_ph(const RequantParams& p) {
+    return (p.clamp_hi_q >= 0 ? (float)p.clamp_hi_q : 255.f) + 0.5f;
+}
+
+// m = (x_scale * w_scale[c]) / y_scale
+__device__ __forceinline__ FoldCh fold_channel(int bias, float m, const RequantParams& p) {
+    FoldCh c;
+    if (p.round_mode != 0) {
+        c.ms = m;
+        c.bs = __fmaf_rn((float)bias, m, p.y_zp_f);
+        return c;
+    }
+    const float hp = fold_hi_ph(p);
+    c.ms = __fdiv_rn(m, hp);
+    c.bs = __fdiv_rn(__fmaf_rn((float)bias, m, __fadd_rn(p.y_zp_f, 0.5f)), hp);
+    return c;
+}
+
+// floor(t * hp) for t in [0, 1], hp < 256: the fused multiply-add onto 2^23 rounded toward minus infinity leaves the
+// integer in the low mantissa bits.
+__device__ __forceinline__ int fold_place(float t, float hp) {
+    return (int)(__float_as_uint(__fmaf_rd(t, hp, 8388608.f)) & 0x1ffu);
 }
 
 __device__ __forceinline__ int requant_u8_fold(int acc, int bias, float m, const RequantParams& p) {
-    const float t = __fmaf_rn((float)acc, m, fold_offset(bias, m, p));
-    int q = p.round_mode != 0 ? cvt_rne_sat_u8(rintf(t)) : cvt_floor_sat_u8(t);
-    if (p.clamp_hi_q >= 0 && q > p.clamp_hi_q) q = p.clamp_hi_q;
-    return q;
+    const FoldCh c = fold_channel(bias, m, p);
+    const float t = __fmaf_rn((float)acc, c.ms, c.bs);
+    if (p.round_mode != 0) {
+        int q = cvt_rne_sat_u8(rintf(t));
+        if (p.clamp_hi_q >= 0 && q > p.clamp_hi_q) q = p.clamp_hi_q;
+        return q;
+    }
+    return fold_place(__saturatef(t), fold_hi_ph(p));
 }
 
-// Folded residual tail: v = fma(r - res_zp, res_scale / out_scale, (q - y_zp) * (y_scale / out_scale)), Relu, then
-// floor(v + (out_zp + 0.5)) (round-half-up) or rint(v) + out_zp (round-half-to-even), saturated to uint8.
+// Folded residual tail.  Round-half-up: with the host-side constants (finish_fold_params)
+//     A = (y_scale / out_scale) / 255.5        R = (res_scale / out_scale) / 255.5
+//     C = (out_zp + 0.5 - y_zp * (y_scale / out_scale) - res_zp * (res_scale / out_scale)) / 255.5
+//     t = sat(fma(float(q), A, fma(float(r), R, C)))        out = floor(t * 255.5),
+// and, when a Relu sits in front of the final QuantizeLinear, out = max(out, out_zp) (the Relu of the sum is the clamp of the
+// quantized value at the zero point).  Round-half-to-even: v = fma(r - res_zp, res_scale / out_scale, (q - y_zp) * (y_scale /
+// out_scale)), Relu, rint(v) + out_zp, saturated.
 __device__ __forceinline__ int residual_fold(int q, int r, const RequantParams& p) {
-    const float u = __fmul_rn(__fsub_rn((float)q, p.y_zp_f), p.y_over_out);
-    float v = __fmaf_rn(__fsub_rn((float)r, p.res_zp_f), p.res_over_out, u);
-    if (p.res_relu) v = fmaxf(v, 0.f);
-    if (p.round_mode != 0) return cvt_rne_sat_u8(__fadd_rn(rintf(v), p.out_zp_f));
-    return cvt_floor_sat_u8(__fadd_rn(v, __fadd_rn(p.out_zp_f, 0.5f)));
+    if (p.round_mode != 0) {
+        const float u = __fmul_rn(__fsub_rn((float)q, p.y_zp_f), p.y_over_out);
+        float v = __fmaf_rn(__fsub_rn((float)r, p.res_zp_f), p.res_over_out, u);
+        if (p.res_relu) v = fmaxf(v, 0.f);
+        return cvt_rne_sat_u8(__fadd_rn(rintf(v), p.out_zp_f));
+    }
+    const float t = __saturatef(__fmaf_rn((float)q, p.fold_a, __fmaf_rn((float)r, p.fold_r, p.fold_c)));
+    int o = fold_place(t, 255.5f);
+    if (p.res_relu) o = max(o, (int)p.out_zp_f);
+    return o;
 }
 
 // ---- conversion-free forms for the tensor-core epilogue -------------------------------------------------------------
@@ -214,32 +266,24 @@ __device__ __forceinline__ float byte_to_magic(uint32_t w, int sel) {
 }
 
 // uint8, round-half-up requantization of one accumulator (+ optional residual tail) without conversion instructions other
-// than the int -> float of the accumulator; equals requant_one / residual_one (reference operation order, fold == 0) or
-// requant_u8_fold / residual_fold (fold != 0) bit for bit.  Returns the output byte.
+// than the int -> float of the accumulator; equals requant_one / residual_one (reference operation order, fold == 0) bit for
+// bit; fold != 0 is requant_u8_fold / residual_fold.  Returns the output byte.
 __device__ __forceinline__ uint32_t requant_u8_up_fast(int acc, int bias, float mult, bool has_res, uint32_t res_byte, const RequantParams& p) {
     const float hi_ph = (p.clamp_hi_q >= 0 ? (float)p.clamp_hi_q : 255.f) + 0.5f;
-    float tp;
     if (p.fold) {
-        const float m = __fdiv_rn(mult, p.y_scale);
-        tp = __fmaf_rn((float)acc, m, __fmaf_rn((float)bias, m, __fadd_rn(p.y_zp_f, 0.5f)));
-    } else {
-        tp = qdiv(__fmul_rn((float)(int)((unsigned)acc + (unsigned)bias), mult), p.y_div);
-        tp = __fadd_rn(__fadd_rn(tp, p.y_zp_f), 0.5f);
+        int q = requant_u8_fold(acc, bias, __fdiv_rn(mult, p.y_scale), p);
+        if (has_res) q = residual_fold(q, (int)(res_byte & 0xffu), p);
+        return (uint32_t)q;
     }
+    float tp = qdiv(__fmul_rn((float)(int)((unsigned)acc + (unsigned)bias), mult), p.y_div);
+    tp = __fadd_rn(__fadd_rn(tp, p.y_zp_f), 0.5f);
     float f = quant_u8_up_magic(tp, hi_ph);
     if (has_res) {
         const float u = __fsub_rn(f, __fadd_rn(kMagic23, p.y_zp_f));
         const float w = __fsub_rn(__uint_as_float(0x4B000000u | (res_byte & 0xffu)), __fadd_rn(kMagic23, p.res_zp_f));
-        float v;
-        if (p.fold) {
-            v = __fmaf_rn(w, p.res_over_out, __fmul_rn(u, p.y_over_out));
-            if (p.res_relu) v = fmaxf(v, 0.f);
-            v = __fadd_rn(v, __fadd_rn(p.out_zp_f, 0.5f));
-        } else {
-            v = __fadd_rn(__fmul_rn(u, p.y_scale), __fmul_rn(w, p.res_scale));
-            if (p.res_relu) v = fmaxf(v, 0.f);
-            v = __fadd_rn(__fadd_rn(qdiv(v, p.out_div), p.out_zp_f), 0.5f);
-        }
+        float v = __fadd_rn(__fmul_rn(u, p.y_scale), __fmul_rn(w, p.res_scale));
+        if (p.res_relu) v = fmaxf(v, 0.f);
+        v = __fadd_rn(__fadd_rn(qdiv(v, p.out_div), p.out_zp_f), 0.5f);
         f = quant_u8_up_magic(v, 255.5f);
     }
     return __float_as_uint(f) & 0xffu;

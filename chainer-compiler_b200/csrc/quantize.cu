@@ -32,15 +32,16 @@ void count_launch(int n) {
 
 int* device_status_ptr() {
     // Resolved once per device (symbol lookup is not something to repeat inside a stream capture).
-    static int* cache[64] = {};
+    // Host threads driving different GPUs may get here at the same time: the slots are atomics (every writer stores the same value).
+    static std::atomic<int*> cache[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (cache[dev] == nullptr) {
-        int* p = nullptr;
+    int* p = cache[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
-        cache[dev] = p;
+        cache[dev].store(p, std::memory_order_release);
     }
-    return cache[dev];
+    return p;
 }
 
 namespace {

@@ -2,6 +2,7 @@
 // tc_bk32.cu / tc_bk64.cu / tc_bk128.cu): planning of tile shapes, tensor maps, dispatch and optional per-launch timing.
 #include <cuda.h>
 
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -36,13 +37,15 @@ CUtensorMapSwizzle swizzle_for(int bk) {
     return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
+// SM count of the current device (grid size and kernel choice depend on it), looked up once per device ordinal.
 int num_sms() {
-    static int sms = 0;
+    static std::atomic<int> cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+    int sms = (dev >= 0 && dev < 64) ? cache[dev].load(std::memory_order_relaxed) : 0;
     if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
+        if (dev < 0 || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        if (dev >= 0 && dev < 64) cache[dev].store(sms, std::memory_order_relaxed);
     }
     return sms;
 }
@@ -56,7 +59,7 @@ bool g_prof_on = false;
 std::vector<ProfRec> g_prof;
 std::mutex g_prof_mu;
 
-int g_variant = 0;  // chxq_tc_variant: 0 = choose, 1 = one tile per step, 2 = grouped tiles where eligible, 3 = grouped + halo tiles
+std::atomic<int> g_variant{0};  // chxq_tc_variant: 0 = choose, 1 = one tile per step, 2 = grouped tiles where eligible, 3 = grouped + halo tiles
 
 int pick_bn(int cols, int64_t pos_tiles) {
     const int cand[3] = {256, 128, 64};
@@ -259,6 +262,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     // Grouped-tile kernel (tc_kernel2.cuh): uint8 epilogues whose outputs (and residual) can move through TMA.
     bool grouped = false, halo = false;
     const bool pool = q.pool_ho > 0;
+    const int g_variant = chxq::g_variant.load(std::memory_order_relaxed);  // one consistent value for this launch
     if (pool && (q.bk != 64 || q.Wb != 16 || q.Hb != 8 || q.Nb != 1 || q.epi.residual != nullptr || q.group_cols != 0 || q.pool_wo <= 0))
         return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: fused max pooling needs a 64-byte K tile, 16 x 8 position tiles and no residual");
     int bn2 = (q.cols > 64 && q.group_cols == 0 && !pool) ? 128 : 64;
@@ -396,7 +400,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
 // whenever the problem is eligible.  Results are identical; the switch exists for measurements and tests.
 extern "C" int chxq_tc_variant(int32_t variant) {
     if (variant < 0 || variant > 5) return chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, "chxq_tc_variant: variant must be 0 .. 5");
-    chxq::g_variant = variant;
+    chxq::g_variant.store(variant, std::memory_order_relaxed);
     return CHXQ_OK;
 }
 

@@ -19,6 +19,8 @@
 
 #include <cuda.h>
 
+#include <atomic>
+
 #include "common.h"
 #include "kernels.h"
 #include "tc_launch.h"
@@ -406,12 +408,15 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         }
                         if (p.col_corr) bz -= (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];
                     }
-                    s_mult[j] = m;
-                    // additive term: int32 (bias and activation zero-point term) or, folded, the float offset B of the bias
+                    // additive term: int32 (bias and activation zero-point term) or, folded, the float offset of the bias; the folded
+                    // round-half-up form keeps both in units of the output range (fold_channel)
                     if (EPI == kEpiKU8Fold) {
                         const int bias = (c < p.cols && p.epi.bias) ? p.epi.bias[c] : 0;
-                        s_add[j] = __float_as_uint(fold_offset(bias, m, rq));
+                        const FoldCh fc = fold_channel(bias, m, rq);
+                        s_mult[j] = fc.ms;
+                        s_add[j] = __float_as_uint(fc.bs);
                     } else {
+                        s_mult[j] = m;
                         s_add[j] = bz;
                     }
                 }
@@ -521,12 +526,13 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         // uint8, round-half-up (the other rounding mode takes the general kernel): one int->float conversion
                         // per element, everything else on the add/multiply pipes (see qmath.cuh), no per-element branches
                         // (adding a zero zero point is exact).  Results equal requant_one / residual_one (reference operation
-                        // order) or requant_u8_fold / residual_fold bit for bit.
+                        // order) or requant_u8_fold / residual_fold (folded: saturating multiply-adds in units of the output
+                        // range) bit for bit.
                         constexpr bool kFold = EPI == kEpiKU8Fold;
                         const float hi_ph = (float)hi_q + 0.5f;
                         const float cy = kMagic23 + rq.y_zp_f, cr = kMagic23 + rq.res_zp_f;
                         const float relu_floor = rq.res_relu ? 0.f : -3.0e38f;
-                        const float out_half = __fadd_rn(rq.out_zp_f, 0.5f);
+                        const float relu_q = rq.res_relu ? kMagic23 + rq.out_zp_f : 0.f;  // folded tail: Relu = clamp at the output zero point
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const float4 m4 = pm[j];
@@ -535,30 +541,31 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                             for (int b = 0; b < 4; ++b) {
                                 const float a = (float)(int)r[4 * j + b];
-                                float tp;
                                 if (kFold) {
-                                    tp = __fmaf_rn(a, mm[b], __uint_as_float(addw[4 * j + b]));
+                                    const float t = __saturatef(__fmaf_rn(a, mm[b], __uint_as_float(addw[4 * j + b])));
+                                    fb[b] = __float_as_uint(__fmaf_rd(t, hi_ph, kMagic23));
                                 } else {
-                                    tp = qdiv(__fmul_rn(a, mm[b]), rq.y_div);
+                                    float tp = qdiv(__fmul_rn(a, mm[b]), rq.y_div);
                                     tp = __fadd_rn(__fadd_rn(tp, rq.y_zp_f), 0.5f);
+                                    fb[b] = __float_as_uint(quant_u8_up_magic(tp, hi_ph));
                                 }
-                                fb[b] = __float_as_uint(quant_u8_up_magic(tp, hi_ph));
                             }
                             if (ro) {
 #pragma unroll
                                 for (int b = 0; b < 4; ++b) {
+                                    if (kFold) {
+                                        const float qf = __fsub_rn(__uint_as_float(fb[b]), kMagic23);     // q, exact
+                                        const float rf = __fsub_rn(byte_to_magic(resw[j], b), kMagic23);   // r, exact
+                                        const float t = __saturatef(__fmaf_rn(qf, rq.fold_a, __fmaf_rn(rf, rq.fold_r, rq.fold_c)));
+                                        fb[b] = __float_as_uint(fmaxf(__fmaf_rd(t, 255.5f, kMagic23), relu_q));
+                                        continue;
+                                    }
                                     const float u = __fsub_rn(__uint_as_float(fb[b]), cy);           // q - y_zp, exact
                                     const float w = __fsub_rn(byte_to_magic(resw[j], b), cr);          // r - res_zp, exact
-                                    float v;
-                                    if (kFold) {
-                                        v = __fmaf_rn(w, rq.res_over_out, __fmul_rn(u, rq.y_over_out));
-                                        v = fmaxf(v, relu_floor);
-                                    } else {
-                                        v = __fadd_rn(__fmul_rn(u, rq.y_scale), __fmul_rn(w, rq.res_scale));
-                                        v = fmaxf(v, relu_floor);
-                                        v = qdiv(v, rq.out_div);
-                                    }
-                                    const float tp = kFold ? __fadd_rn(v, out_half) : __fadd_rn(__fadd_rn(v, rq.out_zp_f), 0.5f);
+                                    float v = __fadd_rn(__fmul_rn(u, rq.y_scale), __fmul_rn(w, rq.res_scale));
+                                    v = fmaxf(v, relu_floor);
+                                    v = qdiv(v, rq.out_div);
+                                    const float tp = __fadd_rn(__fadd_rn(v, rq.out_zp_f), 0.5f);
                                     fb[b] = __float_as_uint(quant_u8_up_magic(tp, 255.5f));
                                 }
                             }
@@ -612,12 +619,12 @@ tc_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 template <int BN, int BK, int EPI>
 int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, int grid, cudaStream_t s) {
     using Cfg = TcConfig<BN, BK>;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};  // per device; host threads may race here, every writer stores true
     int dev = 0;
     CHXQ_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm_kernel<BN, BK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     tc_igemm_kernel<BN, BK, EPI><<<grid, 576, Cfg::kSmemBytes, s>>>(tmA, tmB, p);
     CHXQ_LAUNCH_CHECK();

@@ -12,8 +12,8 @@
 //     warp instruction; through shared memory every line is moved once, whole.
 //   * The TMA store clips rows and channels beyond the output, so ragged edges need no predicates.
 //
-//   * The folded requantization runs scaled by 2^-8 (exact), so that the saturating fma / add clamp at zero for free, and
-//     on pairs of floats (fma / add / mul .f32x2) wherever no clamp is involved.
+//   * The folded requantization runs in units of the output range, so that the saturating fma is both clamps, and on pairs of
+//     floats (fma / sub .f32x2) wherever no clamp is involved.
 //
 //   * A nineteenth warp issues the TMA stores: the epilogue warps only count themselves in on an mbarrier when their part
 //     of a group is staged, so they never wait for one another.
@@ -76,6 +76,11 @@ __device__ __forceinline__ uint64_t mul_x2(uint64_t a, uint64_t b) {
 __device__ __forceinline__ uint64_t fma_x2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma_rm_x2(uint64_t a, uint64_t b, uint64_t c) {  // round toward minus infinity
+    uint64_t d;
+    asm("fma.rm.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
 __device__ __forceinline__ float fma_sat(float a, float b, float c) {  // clamp(fma(a, b, c), 0, 1)
@@ -455,17 +460,14 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const float out_half = __fadd_rn(rq.out_zp_f, 0.5f);
         // Relu before the final quantization equals raising the lower clamp bound to the output zero point.
         const float res_lo = rq.res_relu ? out_half : 0.f;
-        // Folded epilogue, scaled by 2^-8 so that the saturating forms of fma / add clamp at 0 (and, never reached, at 256):
-        // every constant below is an exact power-of-two multiple of its unscaled counterpart, so each intermediate is the
-        // unscaled one times 2^-8 and the output bytes are the same.
-        constexpr float kS = 1.f / 256.f;
-        const float hi_s = hi_ph * kS;
-        const uint64_t magic15x2 = pack2(32768.f, 32768.f);                        // 2^15: ulp 2^-8, so rounding down floors t * 256
-        const uint64_t cy_s2 = pack2(32768.f + rq.y_zp_f * kS, 32768.f + rq.y_zp_f * kS);
-        const uint64_t cr2 = pack2(cr, cr);
-        const uint64_t yoo2 = pack2(rq.y_over_out, rq.y_over_out);
-        const uint64_t roo_s2 = pack2(rq.res_over_out * kS, rq.res_over_out * kS);
-        const float oh_s = out_half * kS;
+        // Folded epilogue (fold_channel / residual_fold in qmath.cuh): values run in units of the output range, so the saturation of
+        // one fused multiply-add is both clamps, and a second one, rounded toward minus infinity onto 2^23, leaves the integer in the
+        // low mantissa bits.  No minimum / maximum and no conversion instruction besides the int -> float of the accumulator.
+        const uint64_t magic23x2 = pack2(kMagic23, kMagic23);
+        const uint64_t hp2 = pack2(hi_ph, hi_ph);
+        const uint64_t c255x2 = pack2(255.5f, 255.5f);
+        const uint64_t fr2 = pack2(rq.fold_r, rq.fold_r), fc2 = pack2(rq.fold_c, rq.fold_c);
+        const float fa = rq.fold_a;
         int it = 0;
         for (int grp = blockIdx.x; grp < total_groups; grp += gridDim.x, ++it) {
             const int acc = it & 1;
@@ -485,9 +487,9 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         m = epi_mult(p.epi, c);
                         const int bias = p.epi.bias ? p.epi.bias[c] : 0;
                         if (kFold) {
-                            m = __fdiv_rn(m, rq.y_scale);
-                            add = __float_as_uint(fold_offset(bias, m, rq) * kS);
-                            m *= kS;
+                            const FoldCh fc = fold_channel(bias, __fdiv_rn(m, rq.y_scale), rq);
+                            m = fc.ms;
+                            add = __float_as_uint(fc.bs);
                             if (p.col_corr) corr = (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];
                         } else {
                             add = (uint32_t)bias;
@@ -545,14 +547,14 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 const int e0 = 2 * h;
                                 float t0 = fma_sat((float)(int)r[4 * j + e0], __uint_as_float(mmw[e0]), __uint_as_float(addw[e0]));
                                 float t1 = fma_sat((float)(int)r[4 * j + e0 + 1], __uint_as_float(mmw[e0 + 1]), __uint_as_float(addw[e0 + 1]));
-                                uint64_t f2 = add_rm_x2(pack2(fminf(t0, hi_s), fminf(t1, hi_s)), magic15x2);  // 2^15 + q / 256
+                                uint64_t f2 = fma_rm_x2(pack2(t0, t1), hp2, magic23x2);                  // 2^23 + q
                                 if (RES) {
-                                    const uint64_t u2 = sub_x2(f2, cy_s2);                                   // (q - y_zp) / 256, exact
-                                    const uint64_t w2 = sub_x2(pack2(byte_to_magic(resw[j], 2 * h), byte_to_magic(resw[j], 2 * h + 1)), cr2);
-                                    const uint64_t v2 = fma_x2(w2, roo_s2, mul_x2(u2, yoo2));
-                                    t0 = add_sat(lo_of(v2), oh_s);
-                                    t1 = add_sat(hi_of(v2), oh_s);
-                                    f2 = add_rm_x2(pack2(fminf(t0, 255.5f * kS), fminf(t1, 255.5f * kS)), magic15x2);
+                                    const uint64_t q2 = sub_x2(f2, magic23x2);                               // q, exact
+                                    const uint64_t r2 = sub_x2(pack2(byte_to_magic(resw[j], 2 * h), byte_to_magic(resw[j], 2 * h + 1)), magic23x2);
+                                    const uint64_t in2 = fma_x2(r2, fr2, fc2);
+                                    t0 = fma_sat(lo_of(q2), fa, lo_of(in2));
+                                    t1 = fma_sat(hi_of(q2), fa, hi_of(in2));
+                                    f2 = fma_rm_x2(pack2(t0, t1), c255x2, magic23x2);
                                 }
                                 fb[2 * h] = (uint32_t)f2;
                                 fb[2 * h + 1] = (uint32_t)(f2 >> 32);
@@ -698,12 +700,12 @@ int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
                 cudaStream_t s) {
     using Cfg = Tc2Config<BN, BK, RES, HALO>;
     static_assert(Cfg::kUsable, "grouped kernel: not enough shared memory for two stages");
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};  // per device; host threads may race here, every writer stores true
     int dev = 0;
     CHXQ_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL><<<grid, 608, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
     CHXQ_LAUNCH_CHECK();

@@ -69,12 +69,54 @@ def max_over_ranks(value, device, world):
     return float(t.item())
 
 
-class InferenceEngine:
-    """One rank's share of a data-parallel inference job: a calibrated network captured in a CUDA graph, a pinned host
-    staging buffer for inputs and one for the gathered logits."""
+def gpu_numa_cpus(device_index):
+    """CPUs of the NUMA node the GPU hangs off (from sysfs), or None when the machine has one node or the answer is unknown."""
+    try:
+        bus = torch.cuda.get_device_properties(device_index).pci_bus_id
+        dom = torch.cuda.get_device_properties(device_index).pci_domain_id
+        dev = torch.cuda.get_device_properties(device_index).pci_device_id
+        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/numa_node" % (dom, bus, dev)
+        node = int(open(path).read().strip())
+        if node < 0 or not os.path.isdir("/sys/devices/system/node/node1"):
+            return None
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        return cpus or None
+    except Exception:
+        return None
 
-    def __init__(self, net, world=1, fold=False):
-        self.net, self.world, self.fold = net, world, fold
+
+def pinned_like(shape, dtype, device_index):
+    """Pinned host buffer whose pages are first touched from a CPU of the GPU's NUMA node (first-touch placement), so that the
+    copies do not cross the socket interconnect on a two-socket host.  On a one-node host this is a plain pinned allocation."""
+    cpus = gpu_numa_cpus(device_index) if torch.cuda.is_available() else None
+    old = None
+    if cpus:
+        try:
+            old = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, cpus & old or old)
+        except OSError:
+            old = None
+    try:
+        t = torch.zeros(shape, dtype=dtype).pin_memory()
+    finally:
+        if old is not None:
+            os.sched_setaffinity(0, old)
+    return t
+
+
+class InferenceEngine:
+    """One rank's share of a data-parallel inference job: a calibrated network captured in two CUDA graphs (two input slots,
+    two logits buffers) used alternately, a communication stream on which the logits all-gather of step i runs while step
+    i + 1 computes, and pinned host buffers for the results.
+
+    Results: every rank holds the logits of the whole job on the device after a step (all-gather).  The host copy is
+    what the rank needs: rank 0 receives the whole job's logits, the other ranks their own rows."""
+
+    def __init__(self, net, world=1, fold=False, rank=0):
+        self.net, self.world, self.fold, self.rank = net, world, fold, rank
         dev = net.device
         self.x_dev = torch.empty((net.batch, 3, net.image, net.image), dtype=torch.float32, device=dev)
         self.graph = None
@@ -82,58 +124,90 @@ class InferenceEngine:
         self.all_logits = None
         self.host_logits = None
         self.slots = None
+        self._flip = 0
 
     def prepare(self, calib_x):
+        """Calibrates on calib_x and captures the two graphs.  The device-resident input of step_device is self.x_dev (call
+        set_resident_input after changing it)."""
         self.x_dev.copy_(calib_x)
         self.net.calibrate(self.x_dev)
-        self.graph, self.logits = self.net.capture(self.x_dev, fold=self.fold)
-        n, c = self.logits.shape
-        self.all_logits = torch.empty((n * self.world, c), dtype=torch.float32, device=self.net.device)
-        self.host_logits = torch.empty((n * self.world, c), dtype=torch.float32).pin_memory()
-
-    def step_device(self):
-        """One pass over the batch already resident in self.x_dev; logits of every rank end up in self.all_logits."""
-        self.graph.replay()
-        if self.world > 1:
-            gather_logits(self.logits, self.world, self.all_logits)
-            return self.all_logits
-        return self.logits
-
-    def run_host(self, x_host_pinned):
-        """Public end-to-end call: pinned host fp32 NCHW batch in, host logits of the whole job out."""
-        self.x_dev.copy_(x_host_pinned, non_blocking=True)
-        out = self.step_device()
-        self.host_logits.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.host_logits
-
-    # ---- pipelined end-to-end call ------------------------------------------------------------------------------------
-    def _make_slots(self):
-        """Two input slots, each with its own captured graph, logits and pinned result buffer, plus a copy-in and a
-        copy-out stream: batch i+1 crosses PCIe while batch i computes and batch i-1's logits go back."""
         dev = self.net.device
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.comm_stream = torch.cuda.Stream(dev)
         self.h2d_stream, self.d2h_stream = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         self.slots = []
         for k in range(2):
             x = self.x_dev if k == 0 else torch.empty_like(self.x_dev)
-            if k == 0:
-                graph, logits = self.graph, self.logits
-            else:
+            if k:
                 x.copy_(self.x_dev)
-                graph, logits = self.net.capture(x, fold=self.fold)
+            graph, logits = self.net.capture(x, fold=self.fold)
             n, c = logits.shape
+            rows = n * self.world if (self.world > 1 and self.rank == 0) else n
             self.slots.append({
                 "x": x, "graph": graph, "logits": logits,
-                "all": self.all_logits if k == 0 else torch.empty_like(self.all_logits),
-                "host": self.host_logits if k == 0 else torch.empty((n * self.world, c), dtype=torch.float32).pin_memory(),
-                "in_ready": torch.cuda.Event(), "in_free": torch.cuda.Event(), "out_ready": torch.cuda.Event(), "host_ready": torch.cuda.Event(),
-                "busy": False})
+                "all": torch.empty((n * self.world, c), dtype=torch.float32, device=dev) if self.world > 1 else logits,
+                "host": pinned_like((rows, c), torch.float32, idx),
+                "in_ready": torch.cuda.Event(), "in_free": torch.cuda.Event(), "out_ready": torch.cuda.Event(),
+                "gathered": torch.cuda.Event(), "host_ready": torch.cuda.Event(), "busy": False})
+        s0 = self.slots[0]
+        self.graph, self.logits, self.all_logits, self.host_logits = s0["graph"], s0["logits"], s0["all"], s0["host"]
 
+    def set_resident_input(self, x):
+        """Makes x (device or pinned host, fp32 NCHW) the input of both slots for step_device."""
+        for s in self.slots:
+            s["x"].copy_(x)
+
+    def _gather_async(self, s, compute):
+        """All-gather of slot s's logits on the communication stream, ordered after the slot's graph on `compute`."""
+        s["out_ready"].record(compute)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(s["out_ready"])
+            gather_logits(s["logits"], self.world, s["all"])
+            s["gathered"].record(self.comm_stream)
+
+    def step_device(self):
+        """One pass over the resident batch; returns the device tensor that will hold the whole job's logits once the
+        communication stream has caught up (drain() orders the current stream after that).  The two slots alternate, so the
+        all-gather of one step overlaps the next step's kernels instead of sitting between two graph replays."""
+        compute = torch.cuda.current_stream()
+        s = self.slots[self._flip]
+        self._flip ^= 1
+        if self.world > 1:
+            compute.wait_event(s["gathered"])  # the gather that read this slot's logits two steps ago
+        s["graph"].replay()
+        if self.world > 1:
+            self._gather_async(s, compute)
+        return s["all"]
+
+    def drain(self):
+        """Orders the current stream after every all-gather issued so far (call before recording the end of a timed region)."""
+        if self.world > 1:
+            compute = torch.cuda.current_stream()
+            for s in self.slots:
+                compute.wait_event(s["gathered"])
+
+    def _result_view(self, s):
+        """What this rank copies to the host: rank 0 the whole job's logits, the others their own rows."""
+        return s["all"] if (self.world > 1 and self.rank == 0) else s["logits"]
+
+    def run_host(self, x_host_pinned):
+        """Public end-to-end call: pinned host fp32 NCHW batch in, host logits out (rank 0: the whole job's; others: own rows)."""
+        s = self.slots[0]
+        compute = torch.cuda.current_stream()
+        s["x"].copy_(x_host_pinned, non_blocking=True)
+        s["graph"].replay()
+        if self.world > 1:
+            self._gather_async(s, compute)
+            compute.wait_event(s["gathered"])
+        s["host"].copy_(self._result_view(s), non_blocking=True)
+        compute.synchronize()
+        return s["host"]
+
+    # ---- pipelined end-to-end call ------------------------------------------------------------------------------------
     def run_stream(self, batches):
-        """Public streaming call: an iterable of pinned host fp32 NCHW batches in, one host logits array (all ranks' rows)
-        out per batch, in order.  The returned array of batch i is valid until batch i+2 is submitted."""
-        if self.slots is None:
-            self._make_slots()
+        """Public streaming call: an iterable of pinned host fp32 NCHW batches in, one host logits array out per batch, in
+        order (rank 0: the whole job's rows; other ranks: their own).  Batch i+1 crosses PCIe while batch i computes and batch
+        i-1's logits are gathered and copied back.  The returned array of batch i is valid until batch i+2 is submitted."""
         compute = torch.cuda.current_stream()
         pending = []
         for i, xb in enumerate(batches):
@@ -147,14 +221,15 @@ class InferenceEngine:
             compute.wait_event(s["in_ready"])
             s["graph"].replay()
             s["in_free"].record(compute)
-            out = s["logits"]
             if self.world > 1:
-                gather_logits(s["logits"], self.world, s["all"])
-                out = s["all"]
-            s["out_ready"].record(compute)
+                self._gather_async(s, compute)
+                last = s["gathered"]
+            else:
+                s["out_ready"].record(compute)
+                last = s["out_ready"]
             with torch.cuda.stream(self.d2h_stream):
-                self.d2h_stream.wait_event(s["out_ready"])
-                s["host"].copy_(out, non_blocking=True)
+                self.d2h_stream.wait_event(last)
+                s["host"].copy_(self._result_view(s), non_blocking=True)
                 s["host_ready"].record(self.d2h_stream)
             s["busy"] = True
             pending.append(s)

@@ -205,8 +205,11 @@ class ResNet50Int8:
         torch.cuda.synchronize(self.device)
 
     # ---- inference ----------------------------------------------------------------------------------
-    def forward(self, x, fused=True, taps=None, fold=False):
-        """fp32 NCHW batch -> fp32 logits [N, classes].  taps (a dict) receives intermediate uint8 maps when given.
+    def forward(self, x, fused=True, taps=None, fold=False, detail=False):
+        """fp32 NCHW batch -> fp32 logits [N, classes].  taps (a dict) receives intermediate uint8 maps when given: 'stem',
+        'block<i>' and 'pooled'; with detail=True also the input and output of every operator ('pool', 'b<i>_h1', 'b<i>_h2',
+        'b<i>_h3' = the last convolution's own output before the residual join, 'b<i>_sc' = the shortcut), so that each operator
+        can be checked on its own against the reference's arithmetic fed the same bytes.
         fold=True requantizes every convolution with one multiplier per channel (QLinearConv's fold_scales)."""
         assert self.calibrated
         assert fused or not fold, "the folded residual tail exists only inside the convolution epilogue"
@@ -226,6 +229,8 @@ class ResNet50Int8:
             if taps is not None:
                 taps["stem"] = h
             h = ops.MaxPoolU8(h, 3, 2, 0, cover_all=True)
+            if taps is not None and detail:
+                taps["pool"] = h
         h_scale = self.stem.y_scale
         for i, b in enumerate(self.blocks):
             h1 = self._run_conv(b["conv1"], h, fold=fold)
@@ -235,6 +240,9 @@ class ResNet50Int8:
             else:
                 sc = h
             sc_scale, sc_zp = b["res"]
+            if taps is not None and detail:
+                taps["b%d_h1" % i], taps["b%d_h2" % i], taps["b%d_sc" % i] = h1, h2, sc
+                taps["b%d_h3" % i] = self._run_conv(b["conv3"], h2, fold=fold)
             if fused:
                 h = self._run_conv(b["conv3"], h2, residual=sc, res_scale=sc_scale, res_zp=sc_zp, out_scale=b["out_scale"], fold=fold)
             else:

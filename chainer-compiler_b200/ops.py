@@ -26,6 +26,7 @@ from ._lib import (FLOAT16, FLOAT32, FLOAT64, INT8, NCHW, NHWC, PATH_AUTO, PATH_
 _TORCH_Q = {torch.uint8: UINT8, torch.int8: INT8}
 _TORCH_F = {torch.float16: FLOAT16, torch.float32: FLOAT32, torch.float64: FLOAT64}
 _workspaces = {}
+_retired_workspaces = []  # superseded scratch buffers: kept alive because captured CUDA graphs hold their raw addresses
 
 
 def _stream():
@@ -49,15 +50,35 @@ def _qcode(t, what):
 
 
 def workspace(nbytes, device):
-    """Grow-only scratch buffer per device, 256-byte aligned (the op body owns scratch, as it owns outputs)."""
+    """Grow-only scratch buffer per device, 256-byte aligned (the op body owns scratch, as it owns outputs).
+
+    A CUDA graph captured around these ops bakes the buffer's address into its kernel nodes.  When a later call needs more
+    scratch a larger buffer is allocated, and the superseded one is never handed back to the allocator: a graph captured
+    earlier keeps writing its im2col data and row sums into memory that still belongs to this module, not into a block the
+    allocator may have given to a live tensor.  Growth is geometric (at least 1.5x), so the retained buffers sum to less than
+    three times the largest request."""
     if nbytes == 0:
         return None
     key = (device.index if device.index is not None else torch.cuda.current_device())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired_workspaces.append(ws)
+            nbytes = max(int(nbytes), ws.numel() + ws.numel() // 2)
         ws = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def _check_residual(op, residual, y_shape, channels_last):
+    """A fused residual is read with the output's indexing: it must be a uint8 map of the output's shape and layout, and the
+    tensor-core kernels read it 16 bytes at a time."""
+    if residual is None:
+        return
+    if tuple(residual.shape) != tuple(y_shape) or residual.dtype != torch.uint8 or _is_channels_last(residual) != bool(channels_last):
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "%s: residual must be a uint8 map with the output's shape and layout" % op)
+    if channels_last and residual.data_ptr() % 16:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "%s: residual must start on a 16-byte boundary" % op)
 
 
 def _zp_scalar(zp, default_dtype=np.uint8):
@@ -322,8 +343,11 @@ def QLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y
     if tuple(x.shape) != (g.N, g.C, g.H, g.W) or not layout_ok:
         raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConvPacked: x does not match the packed geometry / layout")
     keep = []
+    _check_residual("QLinearConvPacked", residual, (g.N, g.M, g.Ho, g.Wo), True)
     p, cy = _qconv_params(x, packed.w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, round_mode, clamp_hi_q, residual,
                           res_scale, res_zero_point, res_relu, out_scale, out_zero_point, keep, fold_scales)
+    if out is not None and (tuple(out.shape) != (g.N, g.M, g.Ho, g.Wo) or not _is_channels_last(out) or out.dtype != (torch.uint8 if cy == UINT8 else torch.int8)):
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConvPacked: out must be a channels_last map of the output's shape and dtype")
     y = out if out is not None else torch.empty((g.N, g.M, g.Ho, g.Wo), dtype=torch.uint8 if cy == UINT8 else torch.int8, device=x.device,
                                                  memory_format=torch.channels_last)
     if not packed.eligible:

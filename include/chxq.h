@@ -72,15 +72,6 @@ int64_t chxq_launch_count(void);
 int chxq_tc_profile(int32_t enable);
 int chxq_tc_profile_read(double* total_ms, int64_t* launches, double* total_macs);
 
-/* The tensor-core path has two kernels with identical results: one output tile per step (every epilogue), and grouped
- * tiles whose uint8 outputs leave through shared memory and a TMA store (uint8 requantizing epilogues with 16-byte
- * aligned output rows); the second also has forms for stride-1 convolutions up to 3 x 3 that stage the input halo tile
- * once per tile instead of once per tap.  0 = choose by problem shape (default), 1 = always the first, 2 = the second
- * whenever eligible, 3 = the second with halo tiles (planes of 16-byte rows) whenever eligible, 4 = halo tiles stored
- * swizzled, 5 = as 4 with the descriptor's base-offset field set.  Process-wide; meant for measurements and tests.
- * No counterpart in the reference. */
-int chxq_tc_variant(int32_t variant);
-
 /* Reads (and clears) the device-side status word of the current device.  SYNCHRONISES `stream`.
  * Returns CHXQ_OK or CHXQ_ERR_DEVICE_TIMEOUT. */
 int chxq_device_status(void* stream);
@@ -109,12 +100,13 @@ int chxq_matmul_integer(const void* a, int32_t a_dtype, const void* b, int32_t b
  * which runs while the pool's lock is held and cannot ask the pool (or the driver) for more memory, or a serving loop
  * whose device memory was handed out completely at start-up and which must not take the device-wide synchronisation
  * a driver allocation implies.
- *  - Limit: the scratch needed, N * roundup(K, 32..128) + 8 * N + 4 * M bytes (each part rounded up to 256), must fit
+ *  - Limit: the scratch needed, N * roundup(K, 64 or 128) + 8 * N + 4 * M bytes (each part rounded up to 256; the K tile is
+ *    whichever of 64 and 128 pads K less), must fit
  *    CHXQ_NOALLOC_SCRATCH_BYTES; larger problems are refused with CHXQ_ERR_WORKSPACE.  Shapes the tensor-core kernel
  *    does not take (K not a multiple of 16, unaligned A) run on the CUDA-core kernel, which uses no scratch.
  *  - Every GPU that loads the library keeps the array until the process exits.
  *  - The first call on a device looks the array's device address up (cudaGetSymbolAddress); make that first call
- *    before any stream capture on that device.
+ *    before any stream capture on that device (a first call inside a capture is refused with CHXQ_ERR_UNSUPPORTED).
  *  - All calls share the array and it keeps the previous call's bytes.  Nothing in it needs clearing: every byte the
  *    kernels read is written earlier in the same call.  Two calls whose kernels overlap on the GPU (different
  *    streams) race on it; calls on one stream are ordered and safe. */

@@ -1,0 +1,27 @@
+/*
+ * chxq_testing.h - entry points of libchxq.so that exist for measurements and tests only.  Nothing here has a counterpart in
+ * the reference, and no product code path depends on any of it: the switches are process-wide and default to "off".
+ */
+#ifndef CHXQ_TESTING_H_
+#define CHXQ_TESTING_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The tensor-core path has two kernels with identical results: one output tile per step (every epilogue), and grouped
+ * tiles whose uint8 outputs leave through shared memory and a TMA store (uint8 requantizing epilogues with 16-byte
+ * aligned output rows); the second also has forms for stride-1 convolutions up to 3 x 3 that stage the input halo tile
+ * once per tile instead of once per tap.  0 = choose by problem shape (default), 1 = always the first, 2 = the second
+ * whenever eligible, 3 = the second with halo tiles (planes of 16-byte rows) whenever eligible, 4 = halo tiles stored
+ * swizzled, 5 = as 4 with the descriptor's base-offset field set.  Process-wide; meant for measurements and tests.
+ */
+int chxq_tc_variant(int32_t variant);
+
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHXQ_TESTING_H_ */

@@ -2,7 +2,9 @@
 LSTM-cell elementwise group, the MatMulInteger / QLinearMatMul sweep, MobileNetV2, QuantizeLinear / DequantizeLinear and
 single depthwise layers.  One JSON line per measurement on stdout.
 
-    python chainer-compiler_b200/microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [prepare] [onnx] [stem[=BATCH]]
+    python microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [prepare] [onnx] [stem[=BATCH]]
+
+`bench.py` imports `secondary()` from here for the `secondary` block of its JSON line.
 
 Timing: CUDA events on the launching stream, 3 warm-up calls, median of 10 (3 for the largest GEMMs), a 256 MB buffer
 rewritten between calls so that nothing is served from L2.  `gbs` is algorithmic bytes (every input read once, every
@@ -15,7 +17,7 @@ import sys
 import numpy as np
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
@@ -27,16 +29,17 @@ def hbm_peak_gbs():
         return 6650.0, "fallback"
 
 
-def main():
+NOMINAL_HBM_GBS = 8000.0    # the figure the benchmark specification quotes for B200
+NOMINAL_INT8_TOPS = 4500.0  # NVIDIA's dense int8 figure for B200
+
+
+def run(which, dev, emit_line=None, gemm_sizes=(1024, 4096, 8192, 16384), mobilenet_cuda_cores=True):
+    """Runs the measurements named in `which` on `dev`; returns the list of result dicts (and passes each to emit_line)."""
     pkg = entry.load_package()
     from chainer_compiler_b200 import fusion, models, ops
-    if not torch.cuda.is_available():
-        raise SystemExit("microbench.py needs a CUDA device: this package has no CPU path")
-    dev = torch.device("cuda:0")
-    torch.cuda.set_device(dev)
-    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare", "onnx", "stem"}
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     peak, peak_src = hbm_peak_gbs()
+    results = []
 
     def timeit(fn, iters=10, warm=3):
         for _ in range(warm):
@@ -59,7 +62,12 @@ def main():
         if "gbs" in kw:
             line["frac_hbm"] = kw["gbs"] / peak
             line["hbm_peak"] = "%s %.0f GB/s" % (peak_src, peak)
-        print(json.dumps(line), flush=True)
+            line["frac_hbm_nominal_8tbs"] = kw["gbs"] / NOMINAL_HBM_GBS
+        if "tops" in kw:
+            line["frac_nominal_int8_4500"] = kw["tops"] / NOMINAL_INT8_TOPS
+        results.append(line)
+        if emit_line is not None:
+            emit_line(line)
 
     if "quant" in which:
         # the ResNet-50 input batch (a 40 us kernel: launch ramp and tail are ~10 % of it) and a 1.3 GB stream
@@ -83,7 +91,7 @@ def main():
         emit("ElementWiseNvrtc LSTM cell, 5 inputs + 2 outputs of fp32 [4096,4096]", ms, gbs=7 * 4096 * 4096 * 4 / ms / 1e6)
 
     if "gemm" in which:
-        for S in (1024, 4096, 8192, 16384):
+        for S in gemm_sizes:
             a = torch.randint(0, 256, (S, S), dtype=torch.uint8, device=dev)
             b = torch.randint(-127, 128, (S, S), dtype=torch.int8, device=dev)
             za = torch.tensor([128], dtype=torch.uint8, device=dev)
@@ -119,7 +127,7 @@ def main():
     if "mobilenet" in which:
         B = 512
         x = torch.rand((B, 3, 224, 224), generator=torch.Generator().manual_seed(1)).to(dev)
-        for tc in (True, False):
+        for tc in ((True, False) if mobilenet_cuda_cores else (True,)):
             net = models.MobileNetV2Int8(B, dev, seed=0, depthwise_on_tensor_cores=tc)
             net.calibrate(x)
             graph, logits = net.capture(x, fold=True)
@@ -221,7 +229,25 @@ def main():
                 emit("run_onnx --test <int8 ResNet-50 directory, batch 256> -I 20 %s" % " ".join(extra), r["best_ms"], avg_ms=r["elapsed_ms"],
                      img_per_s=B / r["best_ms"] * 1e3, outputs_within_tolerance=(rc == 0))
     ops.device_status()
-    del pkg
+    del pkg, flush
+    torch.cuda.empty_cache()
+    return results
+
+
+def secondary(dev):
+    """The workloads beside the headline benchmark, for the `secondary` block of bench.py's JSON line: QuantizeLinear /
+    DequantizeLinear and the fused LSTM-cell group in GB/s (against the measured copy bandwidth and against the nominal
+    8 TB/s), the MatMulInteger / QLinearMatMul sweep in TOPS, MobileNetV2 batch 512 in img/s and depthwise layers in GB/s."""
+    return run({"quant", "eltwise", "gemm", "mobilenet", "depthwise", "mlp"}, dev, mobilenet_cuda_cores=False)
+
+
+def main():
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench.py needs a CUDA device: this package has no CPU path")
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare", "onnx", "stem"}
+    run(which, dev, emit_line=lambda line: print(json.dumps(line), flush=True))
 
 
 if __name__ == "__main__":

@@ -327,18 +327,31 @@ void orc_qlinear_conv(
  * boundary.  acc: [rows, M] (channel is the LAST axis) or, when chan_stride > 1, NCHW with
  * chan_stride = Ho*Wo: channel of element i = (i / chan_stride) % M. */
 /* fold != 0 is the library's optional folded form for uint8 outputs (no counterpart in the reference; restated here so that
- * the kernels implementing it can be checked bit for bit): per channel M = (x_scale * w_scale[c]) / y_scale and
- * B = fma(float(bias), M, zp + 0.5) [round-half-up] or fma(float(bias), M, zp) [round-half-to-even];
- * y = min(max(floor(fma(float(acc), M, B)), 0), hi)  or  clamp(rint(fma(float(acc), M, B)), 0, hi). */
+ * the kernels implementing it can be checked bit for bit).  Per channel M = (x_scale * w_scale[c]) / y_scale.
+ * Round-half-up: values run in units of the output range hp = hi + 0.5 (hi = 255 or the upper clamp):
+ *   B = fma(float(bias), M, zp + 0.5);  Ms = M / hp;  Bs = B / hp;
+ *   t = min(max(fma(float(acc), Ms, Bs), 0), 1);  y = floor(t * hp)   (exact product, one floor).
+ * Round-half-to-even: B = fma(float(bias), M, zp); y = clamp(rint(fma(float(acc), M, B)), 0, hi). */
+static inline int fold_place(float t, float hp) {
+    if (!(t > 0.f)) t = 0.f; /* also NaN */
+    if (t > 1.f) t = 1.f;
+    return (int)floor((double)t * (double)hp); /* 24 x 24 bits: exact in double */
+}
+
 static inline int fold_quantize_u8(int32_t acc, int32_t bias, float M, int zp, int round_mode, int clamp_hi_q) {
-    const float B = fmaf((float)bias, M, round_mode == ORC_ROUND_RNE ? (float)zp : (float)zp + 0.5f);
-    float t = fmaf((float)acc, M, B);
-    t = round_mode == ORC_ROUND_RNE ? nearbyintf(t) : floorf(t);
-    t = fminf(t, 255.f);
-    t = fmaxf(0.f, t);
-    int q = (int)t;
-    if (clamp_hi_q >= 0 && q > clamp_hi_q) q = clamp_hi_q;
-    return q;
+    if (round_mode == ORC_ROUND_RNE) {
+        const float B = fmaf((float)bias, M, (float)zp);
+        float t = nearbyintf(fmaf((float)acc, M, B));
+        t = fminf(t, 255.f);
+        t = fmaxf(0.f, t);
+        int q = (int)t;
+        if (clamp_hi_q >= 0 && q > clamp_hi_q) q = clamp_hi_q;
+        return q;
+    }
+    const float hp = (clamp_hi_q >= 0 ? (float)clamp_hi_q : 255.f) + 0.5f;
+    const float B = fmaf((float)bias, M, (float)zp + 0.5f);
+    const float Ms = M / hp, Bs = B / hp;
+    return fold_place(fmaf((float)acc, Ms, Bs), hp);
 }
 
 static inline int quantize_prescaled_u8(float v, int zp, int round_mode) {
@@ -592,18 +605,29 @@ void orc_linear_f32(const float* x, const float* w, const float* b, int64_t N, i
         }
 }
 
-/* The library's folded residual tail (see orc_requantize, fold): v = (a - a_zp) * (a_scale / y_scale) fused-multiply-added
- * with (b - b_zp) * (b_scale / y_scale), Relu, then zero point, rounding, saturation. */
+/* The library's folded residual tail (see orc_requantize, fold), a = the convolution's own output, b = the residual.
+ * Round-half-up, in units of the output range: ka = a_scale / y_scale, kb = b_scale / y_scale (fp32),
+ *   A = ka / 255.5;  R = kb / 255.5;  C = float((y_zp + 0.5 - a_zp * ka - b_zp * kb) / 255.5) evaluated in double;
+ *   t = min(max(fma(float(a), A, fma(float(b), R, C)), 0), 1);  y = floor(t * 255.5);  Relu: y = max(y, y_zp).
+ * Round-half-to-even: v = fma(b - b_zp, kb, (a - a_zp) * ka), Relu, rint(v) + y_zp, saturated. */
 void orc_qadd_relu_fold(
         const uint8_t* a, float a_scale, int a_zp, const uint8_t* b, float b_scale, int b_zp, int64_t n, float y_scale, int y_zp, int relu,
         int round_mode, uint8_t* y) {
     const float ka = a_scale / y_scale, kb = b_scale / y_scale;
+    const float A = ka / 255.5f, R = kb / 255.5f;
+    const float C = (float)((((double)y_zp + 0.5) - (double)a_zp * (double)ka - (double)b_zp * (double)kb) / 255.5);
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) {
-        const float u = ((float)a[i] - (float)a_zp) * ka;
-        float v = fmaf((float)b[i] - (float)b_zp, kb, u);
-        if (relu) v = v > 0.f ? v : 0.f;
-        y[i] = (uint8_t)quantize_prescaled_u8(v, y_zp, round_mode);
+        if (round_mode == ORC_ROUND_RNE) {
+            const float u = ((float)a[i] - (float)a_zp) * ka;
+            float v = fmaf((float)b[i] - (float)b_zp, kb, u);
+            if (relu) v = v > 0.f ? v : 0.f;
+            y[i] = (uint8_t)quantize_prescaled_u8(v, y_zp, round_mode);
+            continue;
+        }
+        int q = fold_place(fmaf((float)a[i], A, fmaf((float)b[i], R, C)), 255.5f);
+        if (relu && q < y_zp) q = y_zp;
+        y[i] = (uint8_t)q;
     }
 }
 

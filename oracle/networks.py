@@ -45,6 +45,71 @@ def resnet50_forward(params, x, mode="exact", taps=None):
     return orc.linear_f32(pooled, params["fc_w"], params["fc_b"])
 
 
+def _lsb(a, b):
+    d = np.abs(np.asarray(a).astype(np.int32) - np.asarray(b).astype(np.int32))
+    return int(d.max()) if d.size else 0, int(np.count_nonzero(d)), int(d.size)
+
+
+def resnet50_parity(params, x, gpu_taps, gpu_logits, fold=True, emulate_logits=None):
+    """Checks a run of the library's ResNet-50 against the oracle on the same images.
+
+    x: fp32 NCHW images; gpu_taps: the detailed taps of the library's forward pass over the same images as numpy NCHW arrays
+    (``models.ResNet50Int8.forward(..., taps=, detail=True)``); gpu_logits: its logits.
+
+    (1) whole network, bit for bit: the chain restated in the library's arithmetic (mode "fold" or "exact"), fed its own
+        outputs from the input image on, must reproduce every tapped map.
+    (2) every operator on its own against the REFERENCE's arithmetic (runtime/ops/quantize.cc:62-94: dequantize, fp32
+        convolution, quantize; joins: DequantizeLinear x2, Add, Relu, QuantizeLinear), fed the very bytes the library's
+        operator was fed: at most one output step apart.
+    Returns a dict of counts; 'ok' says whether both bounds hold."""
+    mode = "fold" if fold else "exact"
+    ot = {}
+    o_logits = resnet50_forward(params, x, mode=mode, taps=ot)
+    mism = total = 0
+    first_bad = None
+    for k, v in ot.items():
+        if k not in gpu_taps:
+            continue
+        g = np.asarray(gpu_taps[k])
+        bad = int(np.count_nonzero(g != v))
+        mism += bad
+        total += int(v.size)
+        if bad and first_bad is None:
+            first_bad = k
+    exact = {"mismatches": mism, "total": total, "first_differing_tap": first_bad,
+             "logits_max_abs_difference": float(np.abs(o_logits - gpu_logits).max())}
+
+    worst = {"max_lsb": 0, "mismatches": 0, "total": 0, "worst_layer": None, "layers": 0}
+
+    def check(name, ref, got):
+        mx, cnt, tot = _lsb(ref, got)
+        worst["mismatches"] += cnt
+        worst["total"] += tot
+        worst["layers"] += 1
+        if mx > worst["max_lsb"]:
+            worst["max_lsb"], worst["worst_layer"] = mx, name
+    xq = orc.quantize_linear(x, params["in_scale"], 0)
+    check("stem", _qconv(params["stem"], xq, "emulate"), gpu_taps["stem"])
+    h = gpu_taps["pool"]
+    for i, b in enumerate(params["blocks"]):
+        t = lambda k: gpu_taps["b%d_%s" % (i, k)]  # noqa: E731
+        check(b["conv1"]["name"], _qconv(b["conv1"], h, "emulate"), t("h1"))
+        check(b["conv2"]["name"], _qconv(b["conv2"], t("h1"), "emulate"), t("h2"))
+        check(b["conv3"]["name"], _qconv(b["conv3"], t("h2"), "emulate"), t("h3"))
+        if b["proj"] is not None:
+            check(b["proj"]["name"], _qconv(b["proj"], h, "emulate"), t("sc"))
+        sc_scale, sc_zp = b["res"]
+        join = orc.qadd_relu(t("h3"), b["conv3"]["y_scale"], b["conv3"]["y_zp"], t("sc"), sc_scale, sc_zp, b["out_scale"], 0, relu=True)
+        check("block%d_join" % i, join, gpu_taps["block%d" % i])
+        h = gpu_taps["block%d" % i]
+    out = {"images": int(x.shape[0]), "arithmetic": mode, "whole_network_vs_arithmetic_mirror": exact,
+           "each_operator_vs_reference_chain_same_input": worst}
+    if emulate_logits is not None:
+        out["logits_top1_agreement_with_reference_chain"] = float(np.mean(np.argmax(emulate_logits, 1) == np.argmax(gpu_logits, 1)))
+    out["ok"] = bool(mism == 0 and worst["max_lsb"] <= 1)
+    return out
+
+
 def mlp_forward(layers, act_scale, x, mode="emulate"):
     """QuantizeLinear -> QLinearMatMul x n -> DequantizeLinear; layers: list of dict(w_q [K,N] int8, w_scale)."""
     h = orc.quantize_linear(x, act_scale, 0)

@@ -12,7 +12,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_header_symbols_exported(pkg):
     from chainer_compiler_b200 import _lib
-    text = open(os.path.join(ROOT, "include", "chxq.h")).read()
+    import glob
+    headers = sorted(glob.glob(os.path.join(ROOT, "include", "*.h")))
+    assert len(headers) >= 2
+    text = "".join(open(h).read() for h in headers)
     declared = set(re.findall(r"\b(chxq_[a-z0-9_]+)\s*\(", text))
     declared -= {"chxq_conv_geom", "chxq_qconv_params", "chxq_ew_node", "chxq_graph_node", "chxq_graph_value"}
     assert len(declared) >= 25

@@ -207,3 +207,10 @@ def test_engine_stream_matches_single_calls(pkg, dev):
         assert torch.equal(g, w)
     got2 = [h.clone() for h in eng.run_stream(batches[:1])]
     assert torch.equal(got2[0], want[0])
+    # the device-resident step alternates between the two captured graphs: both give the same logits
+    eng.set_resident_input(batches[0])
+    for _ in range(3):
+        out = eng.step_device()
+        eng.drain()
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), want[0])

@@ -72,3 +72,30 @@ def test_noalloc_rejects_oversize_and_takes_unaligned_k(pkg, ops, orc, dev):
     b2 = rng.integers(-128, 128, (50, 24)).astype(np.int8)
     y_new, y_old = _both(pkg, ops, torch.from_numpy(a2).to(dev), torch.from_numpy(b2).to(dev), None, None)
     assert torch.equal(y_new, y_old) and np.array_equal(y_new.cpu().numpy(), orc.matmul_integer(a2, b2))
+
+
+def test_noalloc_int8_a_and_unaligned_a(pkg, ops, orc, dev):
+    """A signed left operand on the tensor-core path, and a left operand that starts one byte off a 16-byte boundary (the
+    tensor-core kernel cannot read it, so the CUDA-core kernel answers -- still without scratch)."""
+    rng = np.random.default_rng(2)
+    a = rng.integers(-128, 128, (200, 320)).astype(np.int8)
+    b = rng.integers(0, 256, (320, 96), dtype=np.uint8)
+    za = rng.integers(-128, 128, 320).astype(np.int8)
+    zb = rng.integers(0, 256, 96, dtype=np.uint8)
+    y_new, y_old = _both(pkg, ops, torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev), torch.from_numpy(za).to(dev), torch.from_numpy(zb).to(dev))
+    assert torch.equal(y_new, y_old) and np.array_equal(y_new.cpu().numpy(), orc.matmul_integer(a, b, za, zb))
+    from chainer_compiler_b200 import _lib
+    L = pkg.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    a2 = rng.integers(0, 256, (64, 128), dtype=np.uint8)
+    b2 = rng.integers(-128, 128, (128, 48)).astype(np.int8)
+    buf = torch.zeros(64 * 128 + 16, dtype=torch.uint8, device=dev)
+    off = (16 - buf.data_ptr() % 16) % 16 + 1
+    a_dev = buf[off:off + 64 * 128].view(64, 128)
+    a_dev.copy_(torch.from_numpy(a2))
+    assert a_dev.data_ptr() % 16 == 1
+    b_dev = torch.from_numpy(b2).to(dev)
+    y = torch.full((64, 48), -7, dtype=torch.int32, device=dev)
+    _lib.check(L.chxq_matmul_integer_noalloc(_ptr(a_dev), _lib.UINT8, _ptr(b_dev), _lib.INT8, 64, 48, 128, None, 0, None, 0, _ptr(y), stream))
+    ops.device_status()
+    assert np.array_equal(y.cpu().numpy(), orc.matmul_integer(a2, b2))
