@@ -36,7 +36,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline and the parity check that shares its sample")
     ap.add_argument("--no-secondary", action="store_true", help="skip the measurements of the workloads beside the headline")
     ap.add_argument("--sustain-s", type=float, default=2.0, help="seconds of the sustained loop that follows the timed region")
-    ap.add_argument("--tc-variant", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
+    ap.add_argument("--tc-variant", type=int, default=0, choices=[0, 1, 2, 3, 4, 5, 6, 7],
                     help="tensor-core kernel choice (chxq_tc_variant): 0 by shape, 1 one tile per step, 2 grouped tiles")
     ap.add_argument("--exact-requant", action="store_true",
                     help="requantize in the reference's operation order (multiply by x_scale*w_scale, divide by y_scale) instead of one "

@@ -59,6 +59,9 @@ bool g_prof_on = false;
 std::vector<ProfRec> g_prof;
 std::mutex g_prof_mu;
 
+#ifdef CHXQ_TL
+long long* g_tl_buf = nullptr;
+#endif
 std::atomic<int> g_variant{0};  // chxq_tc_variant: 0 = choose, 1 = one tile per step, 2 = grouped tiles where eligible, 3 = grouped + halo tiles
 
 int pick_bn(int cols, int64_t pos_tiles) {
@@ -228,6 +231,11 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     p.col_corr = q.col_corr; p.col_scale = q.col_scale; p.col_mul = q.col_mul; p.row_corr = q.row_corr;
     p.epi = q.epi;
     p.y = q.y;
+#ifdef CHXQ_TL
+    if (!g_tl_buf) cudaMalloc(&g_tl_buf, 3 * 2048 * sizeof(long long));
+    cudaMemsetAsync(g_tl_buf, 0, 3 * 2048 * sizeof(long long), s);
+    p.tl = g_tl_buf;
+#endif
     p.status = device_status_ptr();
     if (!p.status) return set_error(CHXQ_ERR_CUDA, "device status word is unavailable");
     const int elt = q.epi.mode == kEpiInt32 ? 4 : 1;
@@ -266,6 +274,8 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     if (pool && (q.bk != 64 || q.Wb != 16 || q.Hb != 8 || q.Nb != 1 || q.epi.residual != nullptr || q.group_cols != 0 || q.pool_wo <= 0))
         return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: fused max pooling needs a 64-byte K tile, 16 x 8 position tiles and no residual");
     int bn2 = (q.cols > 64 && q.group_cols == 0 && !pool) ? 128 : 64;
+    bool pair = false;  // the CTA-pair kernel (tc_kernel3.cuh)
+    int64_t pair_items = 0;
     alignas(64) CUtensorMap tmY, tmR;
     if ((epi_kind == tc::kEpiKU8 || epi_kind == tc::kEpiKU8Fold) && (pool || g_variant != 1) && p.vec_ok && q.ldc % 16 == 0 && (q.bk == 64 || q.bk == 128) &&
         // folded tail: the saturating add clamps at zero, which is the Relu only when the output zero point is zero
@@ -304,8 +314,14 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
             groups = (int64_t)p.pool_groups_w * p.pool_groups_h * q.No * ((q.cols + bn2 - 1) / bn2);
             if (groups >= (1ll << 31)) return set_error(CHXQ_ERR_UNSUPPORTED, "tensor-core kernel: too many tiles");
         }
+        // CTA pairs (cta_group::2): dense layers with at least 256 output channels and a 128-byte K tile.  A pair works on two position
+        // tiles against a 256-channel block; chosen when there is at least one such item for every second pair of SMs.
+        pair_items = (pos_tiles + 1) / 2 * ((q.cols + 255) / 256);
+        pair = !pool && !halo && g_variant != 1 && g_variant != 6 && q.bk == 128 && q.group_cols == 0 && q.cols >= 256 && q.a_row_bytes == 0 &&
+               pair_items < (1ll << 31) && (g_variant == 7 || ((g_variant == 0 || g_variant == 2) && pair_items >= (int64_t)num_sms() / 4));
+        if (pair) bn2 = 128;  // the maps below are those of 128-channel blocks: one CTA's half of the weights, halves of the staged output
         // Chosen whenever there is at least one group per SM; smaller problems spread better as single tiles.
-        grouped = pool || halo || g_variant >= 2 || groups >= (int64_t)num_sms();
+        grouped = pair || pool || halo || g_variant >= 2 || groups >= (int64_t)num_sms();
         if (halo) {
             // space-to-depth: the block map itself, [N][rows][a_row_bytes / 16 blocks][16 bytes]
             const cuuint64_t dims[4] = {s2d_halo ? 16u : (cuuint64_t)q.C, s2d_halo ? (cuuint64_t)(q.a_row_bytes / 16) : (cuuint64_t)q.W, (cuuint64_t)q.H,
@@ -363,6 +379,11 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
             p.col_tiles = (q.cols + bn2 - 1) / bn2;
             p.idesc = (p.idesc & ~(0x3fu << 17)) | ((uint32_t)(bn2 >> 3) << 17);
             grid = groups < num_sms() ? (int)groups : num_sms();
+            if (pair) {
+                // one instruction covers the pair: M = 256 (128 rows per CTA), N = 256
+                p.col_tiles = (q.cols + 255) / 256;
+                p.idesc = (p.idesc & ~((0x3fu << 17) | (0x1fu << 24))) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            }
         }
     }
     ProfRec rec{};
@@ -377,6 +398,8 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     int rc;
     if (pool) {
         rc = tc::launch_tc2_bk64_pool(epi_kind, halo, tmA, tmB, tmY, tmR, p, grid, s);
+    } else if (pair) {
+        rc = tc::launch_tc3_bk128(epi_kind, q.epi.residual != nullptr, tmA, tmB, tmY, tmR, p, (int)pair_items, s);
     } else if (grouped) {
         rc = q.bk == 128 ? tc::launch_tc2_bk128(bn2, epi_kind, q.epi.residual != nullptr, halo, tmA, tmB, tmY, tmR, p, grid, s)
                          : tc::launch_tc2_bk64(bn2, epi_kind, q.epi.residual != nullptr, halo, tmA, tmB, tmY, tmR, p, grid, s);
@@ -399,9 +422,25 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
 // Chooses between the two tensor-core kernels: 0 = by problem shape, 1 = always one tile per step, 2 = grouped tiles
 // whenever the problem is eligible.  Results are identical; the switch exists for measurements and tests.
 extern "C" int chxq_tc_variant(int32_t variant) {
-    if (variant < 0 || variant > 5) return chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, "chxq_tc_variant: variant must be 0 .. 5");
+    if (variant < 0 || variant > 7) return chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, "chxq_tc_variant: variant must be 0 .. 7");
     chxq::g_variant.store(variant, std::memory_order_relaxed);
     return CHXQ_OK;
+}
+
+#ifdef CHXQ_TL
+extern "C" int chxq_tl_read(long long* host) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpy(host, chxq::g_tl_buf, 3 * 2048 * sizeof(long long), cudaMemcpyDeviceToHost);
+}
+#endif
+
+// Number of CTA pairs of the paired tensor-core kernel that the current device keeps resident at once.
+extern "C" int chxq_tc_pair_slots(int32_t* slots) {
+    if (!slots) return chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, "chxq_tc_pair_slots: null pointer");
+    int n = 0;
+    const int rc = chxq::tc::tc3_pair_slots(&n);
+    *slots = n;
+    return rc;
 }
 
 // Profiling of the tensor-core kernel: while enabled, every launch is bracketed by CUDA events on its stream.

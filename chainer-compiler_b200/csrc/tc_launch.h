@@ -42,6 +42,9 @@ struct TcParams {
     // group is 2 x 2 tiles of 16 x 8 positions and owns 15 x 7 pooled positions (8 x 16 and 7 x 15 with halo tiles).
     // pool_groups_w == 0: no pooling.
     int pool_groups_w, pool_groups_h, pool_wo, pool_ho;
+#ifdef CHXQ_TL
+    long long* tl;  // timeline build: [2 roles][512 K blocks][4] clock stamps of CTA 0
+#endif
 };
 
 // Epilogue families (template parameter EPI): dead paths are compiled out, which keeps the unrolled per-element
@@ -62,6 +65,13 @@ int launch_tc2_bk64(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA
                     const TcParams& p, int grid, cudaStream_t s);
 int launch_tc2_bk128(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
                      const TcParams& p, int grid, cudaStream_t s);
+
+// CTA-pair kernel (tc_kernel3.cuh): 256-channel blocks, 128-byte K tiles, uint8 epilogues; tmB's box is one CTA's half of the
+// weight block (128 rows), tmY / tmR boxes are 128 channels wide; items = position-tile pairs x 256-channel blocks.
+int launch_tc3_bk128(int epi, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p,
+                     int items, cudaStream_t s);
+
+int tc3_pair_slots(int* out);  // CTA pairs the current device keeps resident at once
 
 }  // namespace tc
 }  // namespace chxq

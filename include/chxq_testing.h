@@ -16,9 +16,15 @@ extern "C" {
  * aligned output rows); the second also has forms for stride-1 convolutions up to 3 x 3 that stage the input halo tile
  * once per tile instead of once per tap.  0 = choose by problem shape (default), 1 = always the first, 2 = the second
  * whenever eligible, 3 = the second with halo tiles (planes of 16-byte rows) whenever eligible, 4 = halo tiles stored
- * swizzled, 5 = as 4 with the descriptor's base-offset field set.  Process-wide; meant for measurements and tests.
- */
+ * swizzled, 5 = as 4 with the descriptor's base-offset field set.  A third kernel runs dense layers with at least 256 output
+ * channels and a 128-byte K tile on CTA pairs (tcgen05.mma.cta_group::2, a 256 x 256 block per pair): 6 = as 0 but never
+ * that kernel, 7 = that kernel whenever the problem is eligible, however small.  Process-wide; meant for measurements and
+ * tests. */
 int chxq_tc_variant(int32_t variant);
+
+/* Number of CTA pairs (clusters of two) of the paired tensor-core kernel that the current device keeps resident at once
+ * (cudaOccupancyMaxActiveClusters): the kernel's grid is twice this, or smaller for small problems. */
+int chxq_tc_pair_slots(int32_t* slots);
 
 
 #ifdef __cplusplus

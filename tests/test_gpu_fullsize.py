@@ -221,3 +221,53 @@ def test_packed_conv_rejects_bad_residual(ops, dev):
             ops.QLinearConvPacked(x, pk, 0.1, np.uint8(0), ws, wz, 0.1, np.uint8(0), residual=bad, res_scale=0.1, out_scale=0.1)
         assert e.value.code == 1  # CHXQ_ERR_INVALID_ARGUMENT
     ops.device_status()
+
+
+# (N, cin, cout, H, k, stride, pad, residual, x_zp): dense layers the CTA-pair kernel (tcgen05.mma.cta_group::2) takes
+PAIR_CASES = [
+    (8, 256, 256, 14, 3, 1, 1, False, 0),     # res4 conv2: 13 position tiles (odd: the last pair has one real tile)
+    (8, 256, 1024, 14, 1, 1, 0, True, 0),     # res4 conv3 + join: four 256-channel blocks
+    (8, 1024, 512, 14, 1, 2, 0, False, 0),    # res5 conv1: stride 2, K = 8 x 128
+    (8, 512, 512, 7, 3, 1, 1, False, 5),      # res5 conv2 on 7 x 7 maps (tiles of 128 images) with an activation zero point... no padding value issue: see below
+    (3, 128, 320, 28, 1, 1, 0, True, 0),      # ragged channel block (256 + 64), K = one 128-byte tile
+    (2, 384, 256, 10, 1, 1, 0, False, 9),     # 200 positions: ragged position tile; activation zero point term
+]
+
+
+@pytest.mark.parametrize("N,cin,cout,H,k,stride,pad,res,zx", PAIR_CASES)
+def test_cta_pair_kernel(pkg, ops, orc, dev, N, cin, cout, H, k, stride, pad, res, zx):
+    """The CTA-pair kernel, forced on (it is chosen by itself only for problems that fill the GPU), against the integer-domain
+    oracle bit for bit and against the grouped-tile kernel."""
+    from chainer_compiler_b200 import _lib
+    if pad and zx:
+        zx = 0  # padding with a non-zero activation zero point takes the explicit im2col path, not this kernel
+    rng = np.random.default_rng(cin + cout + H)
+    x = rng.integers(0, 256, (N, cin, H, H), dtype=np.uint8)
+    w, ws, bias = _layer(rng, cin, cout, k)
+    wz = np.zeros(cout, np.int8)
+    sx, sy, zy = np.float32(0.02), np.float32(0.05), (117 if res else 3)
+    pk = ops.PackedConv(_t(w, dev), _t(wz, dev), x.shape, strides=(stride, stride), pads=(pad, pad))
+    Ho = (H + 2 * pad - k) // stride + 1
+    kw = {}
+    r = None
+    if res:
+        r = rng.integers(0, 256, (N, cout, Ho, Ho), dtype=np.uint8)
+        kw = dict(residual=_t(r, dev, True), res_scale=0.04, res_zero_point=7, res_relu=True, out_scale=0.06, out_zero_point=0)
+    acc = orc.conv_integer(x, w, zx, None, strides=(stride, stride), pads=(pad, pad))
+    L = pkg.lib()
+    try:
+        for fold in (False, True):
+            want = orc.requantize(acc, sx, ws, sy, zy, bias=bias, channel_axis=1, fold=fold)
+            if res:
+                want = orc.qadd_relu(want, sy, zy, r, 0.04, 7, 0.06, 0, relu=True, fold=fold)
+            got = {}
+            for variant in (7, 6):
+                _lib.check(L.chxq_tc_variant(variant))
+                got[variant] = ops.QLinearConvPacked(_t(x, dev, True), pk, sx, np.uint8(zx), _t(ws, dev), _t(wz, dev), sy, np.uint8(zy), b=_t(bias, dev),
+                                                     fold_scales=fold, **kw).cpu().numpy()
+                ops.device_status()
+            assert np.array_equal(got[7], want), "CTA-pair kernel: %d of %d bytes differ from the oracle (fold=%s)" % (
+                int((got[7] != want).sum()), want.size, fold)
+            assert np.array_equal(got[6], want)
+    finally:
+        _lib.check(L.chxq_tc_variant(0))
