@@ -115,6 +115,9 @@ SIGNATURES = {
     "chxq_nchw_to_nhwc": (_c.c_int, [_vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "chxq_nhwc_to_nchw": (_c.c_int, [_vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "chxq_minmax_f32": (_c.c_int, [_vp, _i64, _vp, _vp]),
+    "chxq_dynamic_quant_params_u8": (_c.c_int, [_vp, _vp, _vp, _vp, _vp]),
+    "chxq_quantize_linear_dev": (_c.c_int, [_vp, _i64, _vp, _vp, _i32, _i32, _vp, _vp]),
+    "chxq_conv_integer_dev": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
 }
 
 _lib = None

@@ -558,6 +558,44 @@ int conv_tc_run(
     return launch_tc_igemm(p, s);
 }
 
+// The reference's own signature is NCHW in, NCHW out (runtime/chxvm_defs.py:457-461, 466-469).  The tensor-core kernels read and
+// write NHWC, so an NCHW call is run as: transpose x into scratch (skipped for maps of at most four channels, which the stem
+// paths read as NCHW themselves), the NHWC convolution into scratch, transpose y back.  The two transposes move every activation
+// byte once more; a caller that keeps its maps NHWC (chxq_conv_geom layouts) avoids them.
+struct NchwPlan {
+    chxq_conv_geom g2;   // the NHWC problem that actually runs
+    bool x_transposed;
+    size_t x_bytes, y_bytes, y_elem;
+};
+
+bool nchw_plan(const chxq_conv_geom& g, size_t y_elem, NchwPlan* out) {
+    if (g.x_layout != CHXQ_NCHW || g.y_layout != CHXQ_NCHW || g.N > 65535) return false;
+    NchwPlan pl{};
+    pl.g2 = g;
+    pl.y_elem = y_elem;
+    pl.x_transposed = g.C > 4;
+    if (pl.x_transposed) {
+        pl.g2.x_layout = CHXQ_NHWC;
+        pl.g2.x_cstride = (g.C + 15) / 16 * 16;
+        pl.x_bytes = align_up((size_t)g.N * g.H * g.W * pl.g2.x_cstride, 1024);
+    }
+    pl.g2.y_layout = CHXQ_NHWC;
+    pl.g2.y_cstride = (g.M + 15) / 16 * 16;
+    pl.y_bytes = align_up((size_t)g.N * g.Ho * g.Wo * pl.g2.y_cstride * y_elem, 1024);
+    if (plan_tc_conv(pl.g2).path == kTcNone) return false;
+    *out = pl;
+    return true;
+}
+
+size_t inner_conv_workspace(const chxq_conv_geom& g2) {
+    const TcConvPlan pl = plan_tc_conv(g2);
+    if (pl.path == kTcNone) return 0;
+    const ConvWs L = conv_ws_layout(g2, pl);
+    const bool padded = g2.pad_top || g2.pad_left || g2.pad_bottom || g2.pad_right;
+    const size_t im2col = (pl.path == kTcIm2col || pl.path == kTcS2d || padded) ? L.im2col_bytes : 0;
+    return L.pack_total + im2col + L.rowsum_bytes;
+}
+
 int conv_dispatch(
         const char* op, const void* x, const void* w, const chxq_conv_geom* g, int has_x_zp, int x_zp, const ZpSpec& zw, const EpiArgs& epi,
         void* y, void* workspace, size_t workspace_bytes, int path, cudaStream_t s) {
@@ -569,6 +607,31 @@ int conv_dispatch(
     const int xz = has_x_zp ? x_zp : 0;
     if (path == CHXQ_PATH_AUTO && g->group > 1 && epi.mode == kEpiRequant && depthwise_eligible(*g, x, y, epi.residual))
         return launch_depthwise(x, w, *g, xz, zw.ptr, zw.len, epi, y, s);
+    // NCHW in, NCHW out (the reference's signature): NHWC inside, transposes around it, when the caller's workspace has room.
+    NchwPlan np;
+    if (path != CHXQ_PATH_SIMT && epi.residual == nullptr && nchw_plan(*g, epi.mode == kEpiInt32 ? 4 : 1, &np)) {
+        const size_t need = np.x_bytes + np.y_bytes + inner_conv_workspace(np.g2);
+        const bool aligned_io = (reinterpret_cast<uintptr_t>(x) & 3u) == 0 && (reinterpret_cast<uintptr_t>(y) & 3u) == 0;
+        if (workspace != nullptr && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && aligned_io) {
+            uint8_t* wsp = static_cast<uint8_t*>(workspace);
+            const void* x2 = x;
+            if (np.x_transposed) {
+                rc = chxq_nchw_to_nhwc(x, 1, g->N, g->C, g->H, g->W, np.g2.x_cstride, wsp, s);
+                if (rc != CHXQ_OK) return rc;
+                x2 = wsp;
+            }
+            void* y2 = wsp + np.x_bytes;
+            rc = conv_dispatch(op, x2, w, &np.g2, has_x_zp, x_zp, zw, epi, y2, wsp + np.x_bytes + np.y_bytes, workspace_bytes - np.x_bytes - np.y_bytes,
+                               CHXQ_PATH_TENSOR, s);
+            if (rc == CHXQ_OK) return chxq_nhwc_to_nchw(y2, (int)np.y_elem, g->N, g->M, g->Ho, g->Wo, np.g2.y_cstride, y, s);
+            if (!(rc == CHXQ_ERR_UNSUPPORTED && path == CHXQ_PATH_AUTO)) return rc;
+            // zero points or an epilogue the tensor-core kernels do not take: the general kernel reads NCHW directly
+            return launch_conv_simt(x, w, *g, has_x_zp, x_zp, zw.ptr, zw.len, epi, y, s);
+        }
+        if (path == CHXQ_PATH_TENSOR)
+            return set_error(CHXQ_ERR_WORKSPACE, "%s: the tensor-core path behind NCHW tensors needs %zu bytes of 256-byte aligned workspace (got %zu)", op,
+                             need, workspace_bytes);
+    }
     const TcConvPlan pl = plan_tc_conv(*g);
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     bool use_tc = path != CHXQ_PATH_SIMT && pl.path != kTcNone && aligned;
@@ -611,7 +674,7 @@ int fill_requant(const char* op, const chxq_qconv_params* p, const chxq_conv_geo
     // runtime/ops/quantize.cc:76-88: per-channel needs one scale and zero point per output channel, else both are 0-d.
     CHXQ_CHECK_ARG(p->w_params_len == 1 || p->w_params_len == g->M, "%s: w_scale / w_zero_point must have 1 or M=%d elements (got %lld)", op,
                    g->M, (long long)p->w_params_len);
-    CHXQ_CHECK_ARG(p->w_scale != nullptr && p->w_zero_point != nullptr, "%s: null weight scale or zero point", op);
+    CHXQ_CHECK_ARG(p->w_scale != nullptr, "%s: null weight scale", op);  // a null w_zero_point says "every zero point is zero"
     CHXQ_CHECK_ARG(p->round_mode == CHXQ_ROUND_REF_HALF_UP || p->round_mode == CHXQ_ROUND_RNE, "%s: bad round_mode", op);
     CHXQ_CHECK_ARG(p->residual == nullptr || p->y_dtype == CHXQ_UINT8, "%s: the residual tail needs a uint8 output", op);
     memset(e, 0, sizeof(*e));
@@ -822,6 +885,8 @@ extern "C" int chxq_conv_resolve_geometry(
 
 extern "C" size_t chxq_conv_workspace(const chxq_conv_geom* g) {
     if (!g || validate_geom("conv workspace", g) != CHXQ_OK) return 0;
+    NchwPlan np;
+    if (nchw_plan(*g, 4, &np)) return np.x_bytes + np.y_bytes + inner_conv_workspace(np.g2);  // sized for int32 outputs (ConvInteger), the larger case
     const TcConvPlan pl = plan_tc_conv(*g);
     if (pl.path == kTcNone) return 0;
     const ConvWs L = conv_ws_layout(*g, pl);
@@ -853,6 +918,20 @@ extern "C" int chxq_conv_integer(
     return conv_dispatch("ConvInteger", x, w, g, has_x_zp, x_zero_point, zw, epi, y, workspace, workspace_bytes, path, as_stream(stream));
 }
 
+extern "C" int chxq_conv_integer_dev(
+        const void* x, const void* w, const chxq_conv_geom* g, const void* x_zero_point, const void* w_zero_point, int64_t w_zp_len, int32_t* y,
+        void* stream) {
+    int rc = validate_geom("ConvInteger", g);
+    if (rc != CHXQ_OK) return rc;
+    rc = check_zp_len("ConvInteger", "w_zero_point", w_zero_point, w_zp_len, g->M);
+    if (rc != CHXQ_OK) return rc;
+    if ((int64_t)g->N * g->M * g->Ho * g->Wo == 0) return CHXQ_OK;
+    CHXQ_CHECK_ARG(x && w && y && x_zero_point, "ConvInteger: null buffer");
+    EpiArgs epi{};
+    epi.mode = kEpiInt32;
+    return launch_conv_simt(x, w, *g, 1, 0, w_zero_point, w_zp_len, epi, y, as_stream(stream), x_zero_point);
+}
+
 extern "C" int chxq_qlinear_conv(
         const void* x, const void* w, const chxq_conv_geom* g, const chxq_qconv_params* p, void* y, void* workspace, size_t workspace_bytes,
         int32_t path, void* stream) {
@@ -861,7 +940,7 @@ extern "C" int chxq_qlinear_conv(
     EpiArgs epi;
     rc = fill_requant("QLinearConv", p, g, &epi);
     if (rc != CHXQ_OK) return rc;
-    const ZpSpec zw{p->w_zero_point, p->w_params_len, 0};
+    const ZpSpec zw{p->w_zero_point, p->w_zero_point ? p->w_params_len : 0, 0};
     return conv_dispatch("QLinearConv", x, w, g, 1, p->x_zero_point, zw, epi, y, workspace, workspace_bytes, path, as_stream(stream));
 }
 

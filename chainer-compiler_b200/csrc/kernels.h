@@ -23,7 +23,7 @@ int launch_gemm_simt(
         const ZpSpec& zb, const EpiArgs& epi, void* y, cudaStream_t s);
 int launch_conv_simt(
         const void* x, const void* w, const chxq_conv_geom& g, int has_x_zp, int x_zp, const void* w_zp, int64_t w_zp_len, const EpiArgs& epi,
-        void* y, cudaStream_t s);
+        void* y, cudaStream_t s, const void* x_zp_dev = nullptr);  // x_zp_dev: the activation zero point as a device scalar of x's dtype
 // A[row, k], row = (n, ho, wo), k = tap * c_pitch + c, row length k_pad (multiple of 16); padding
 // positions hold pad_byte, columns with c >= C or tap >= KH*KW hold 0.
 int launch_im2col(const void* x, const chxq_conv_geom& g, int c_pitch, int k_pad, int pad_byte, void* a, cudaStream_t s);

@@ -366,6 +366,72 @@ extern "C" int chxq_qadd_u8(
     return CHXQ_OK;
 }
 
+namespace chxq {
+namespace {
+
+// scale = (rmax - rmin) / 255 (1 when the range is empty); zero point = uint8(floor((0 - rmin) / scale)), in the fp32 operations
+// of the Sub / Div / Floor / Cast nodes the quantizer emits (compiler/quantize.cc:196-207).  The range is not widened to
+// include zero, as in the reference, so an all-positive input gives floor(-rmin / scale) < 0; the Cast of a negative float to
+// uint8 is undefined in C++, here it saturates to 0 (and to 255 above), which is what the host-side helper of run_onnx does.
+__global__ void dynamic_params_u8_kernel(const float* __restrict__ rmin, const float* __restrict__ rmax, float* __restrict__ scale, uint8_t* __restrict__ zp) {
+    const float lo = *rmin, hi = *rmax;
+    const float sc = hi != lo ? __fdiv_rn(__fsub_rn(hi, lo), 255.0f) : 1.0f;
+    float z = floorf(__fdiv_rn(__fsub_rn(0.0f, lo), sc));
+    z = fminf(fmaxf(z, 0.0f), 255.0f);
+    *scale = sc;
+    *zp = (uint8_t)(z != z ? 0.f : z);
+}
+
+// QuantizeLinear whose scale and zero point are device scalars: same element arithmetic as quantize_one (true division).
+template <bool kSigned>
+__global__ void __launch_bounds__(kThreads) quantize_dev_kernel(
+        const float* __restrict__ x, int64_t n, const float* __restrict__ scale_p, const void* __restrict__ zp_p, int round_mode, uint8_t* __restrict__ y,
+        int vec_ok) {
+    const float scale = *scale_p;
+    const int zp = zp_p == nullptr ? 0 : (kSigned ? (int)*static_cast<const int8_t*>(zp_p) : (int)*static_cast<const uint8_t*>(zp_p));
+    const float zp_f = (float)zp;
+    const bool has_zp = zp != 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t n4 = vec_ok ? n / 4 : 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(x) + i);
+        const uint32_t q0 = (uint32_t)quantize_one<kSigned>(v.x, scale, zp_f, has_zp, round_mode) & 0xffu;
+        const uint32_t q1 = (uint32_t)quantize_one<kSigned>(v.y, scale, zp_f, has_zp, round_mode) & 0xffu;
+        const uint32_t q2 = (uint32_t)quantize_one<kSigned>(v.z, scale, zp_f, has_zp, round_mode) & 0xffu;
+        const uint32_t q3 = (uint32_t)quantize_one<kSigned>(v.w, scale, zp_f, has_zp, round_mode) & 0xffu;
+        reinterpret_cast<uint32_t*>(y)[i] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+    }
+    for (int64_t i = n4 * 4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        y[i] = (uint8_t)quantize_one<kSigned>(x[i], scale, zp_f, has_zp, round_mode);
+}
+
+}  // namespace
+}  // namespace chxq
+
+extern "C" int chxq_dynamic_quant_params_u8(const float* rmin, const float* rmax, float* scale, uint8_t* zero_point, void* stream) {
+    CHXQ_CHECK_ARG(rmin && rmax && scale && zero_point, "dynamic quantization parameters: null pointer");
+    dynamic_params_u8_kernel<<<1, 1, 0, as_stream(stream)>>>(rmin, rmax, scale, zero_point);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
+extern "C" int chxq_quantize_linear_dev(
+        const float* x, int64_t n, const float* y_scale, const void* y_zero_point, int32_t y_dtype, int32_t round_mode, void* y, void* stream) {
+    CHXQ_CHECK_ARG(n >= 0, "QuantizeLinear: negative element count");
+    CHXQ_CHECK_ARG(is_q8(y_dtype), "QuantizeLinear: y_zero_point dtype must be uint8 or int8 (got %d)", y_dtype);
+    CHXQ_CHECK_ARG(round_mode == CHXQ_ROUND_REF_HALF_UP || round_mode == CHXQ_ROUND_RNE, "QuantizeLinear: bad round_mode");
+    if (n == 0) return CHXQ_OK;
+    CHXQ_CHECK_ARG(x && y && y_scale, "QuantizeLinear: null buffer");
+    const int vec_ok = aligned16(x) && (reinterpret_cast<uintptr_t>(y) & 3u) == 0;
+    const int grid = grid_for((n + 3) / 4, 16);
+    if (y_dtype == CHXQ_INT8)
+        quantize_dev_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(x, n, y_scale, y_zero_point, round_mode, static_cast<uint8_t*>(y), vec_ok);
+    else
+        quantize_dev_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(x, n, y_scale, y_zero_point, round_mode, static_cast<uint8_t*>(y), vec_ok);
+    CHXQ_LAUNCH_CHECK();
+    return CHXQ_OK;
+}
+
 extern "C" int chxq_minmax_f32(const float* x, int64_t n, float* out2, void* stream) {
     CHXQ_CHECK_ARG(n > 0 && x && out2, "minmax: empty input or null buffer");
     cudaStream_t s = as_stream(stream);

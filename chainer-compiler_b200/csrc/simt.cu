@@ -94,8 +94,15 @@ struct ConvDesc {
     int64_t w_zp_len;
 };
 
+// x_zp_dev != nullptr: the activation zero point is a device scalar of x's dtype (a zero point that was computed on the
+// device, e.g. by the dynamic-quantization parameter kernel), read here instead of on the host.
 __global__ void __launch_bounds__(256) conv_simt_kernel(
-        const void* __restrict__ x, const void* __restrict__ w, const void* __restrict__ w_zp, ConvDesc d, EpiArgs epi, void* __restrict__ y) {
+        const void* __restrict__ x, const void* __restrict__ w, const void* __restrict__ w_zp, ConvDesc d, EpiArgs epi, void* __restrict__ y,
+        const void* __restrict__ x_zp_dev) {
+    if (x_zp_dev != nullptr) {
+        d.has_x_zp = 1;
+        d.x_zp = ldq_rt(x_zp_dev, 0, d.x_signed);
+    }
     const int64_t total = (int64_t)d.N * d.M * d.Ho * d.Wo;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int Cg = d.C / d.group, Mg = d.M / d.group;
@@ -509,6 +516,97 @@ __global__ void __launch_bounds__(256) transpose_chw_kernel(const T* __restrict_
     }
 }
 
+// NCHW <-> NHWC transposes of 1-byte maps, 64 channels x 64 positions per block of 256 threads.  The NCHW side moves as 32-bit
+// words (four positions of one channel), the NHWC side as 128-bit words (sixteen channels of one position); in between, every
+// thread transposes a 4 x 4 block of bytes in registers (eight byte permutes) and the tile crosses shared memory as words
+// [position][channel / 4] with a pitch of 17 words, which keeps the word accesses of both phases (nearly) conflict-free.
+// Channels beyond C up to the NHWC pitch are written as zeros (to_nhwc) or ignored.
+constexpr int kTrC = 64, kTrP = 64, kTrPitchW = 17;
+
+__device__ __forceinline__ void transpose4x4_bytes(uint32_t (&r)[4]) {
+    const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[0], r[1], 0x7362);
+    const uint32_t t2 = __byte_perm(r[2], r[3], 0x5140), t3 = __byte_perm(r[2], r[3], 0x7362);
+    r[0] = __byte_perm(t0, t2, 0x5410);
+    r[1] = __byte_perm(t0, t2, 0x7632);
+    r[2] = __byte_perm(t1, t3, 0x5410);
+    r[3] = __byte_perm(t1, t3, 0x7632);
+}
+
+template <bool kToNhwc>
+__global__ void __launch_bounds__(256) transpose_u8_tile_kernel(const uint8_t* __restrict__ x, int C, int HW, int ld, uint8_t* __restrict__ y) {
+    __shared__ uint32_t tw[kTrP][kTrPitchW];
+    const int n = blockIdx.z, c0 = blockIdx.y * kTrC, p0 = blockIdx.x * kTrP, tid = threadIdx.x;
+    const uint8_t* nchw_in = x + (int64_t)n * C * HW;
+    uint8_t* nchw_out = y + (int64_t)n * C * HW;
+    const uint8_t* nhwc_in = x + (int64_t)n * HW * ld;
+    uint8_t* nhwc_out = y + (int64_t)n * HW * ld;
+    const bool words_ok = (HW % 4 == 0) && ((reinterpret_cast<uintptr_t>(kToNhwc ? x : y) & 3u) == 0);
+    const bool quads_ok = (ld % 16 == 0) && ((reinterpret_cast<uintptr_t>(kToNhwc ? y : x) & 15u) == 0);
+    const int a = tid / 16, b = tid % 16;   // NCHW side: channels 4a .. 4a+3, positions 4b .. 4b+3
+    const int pos = tid / 4, q = tid % 4;   // NHWC side: position pos, channels 16q .. 16q+15
+    if (kToNhwc) {
+        uint32_t r[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = c0 + 4 * a + i, p = p0 + 4 * b;
+            uint32_t v = 0u;
+            if (c < C && p < HW) {
+                const uint8_t* src = nchw_in + (int64_t)c * HW + p;
+                if (words_ok && p + 4 <= HW) {
+                    v = *reinterpret_cast<const uint32_t*>(src);
+                } else {
+                    for (int j = 0; j < 4 && p + j < HW; ++j) v |= (uint32_t)src[j] << (8 * j);
+                }
+            }
+            r[i] = v;
+        }
+        transpose4x4_bytes(r);  // r[j] = channels 4a .. 4a+3 of position 4b + j
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tw[4 * b + j][a] = r[j];
+        __syncthreads();
+        const int p = p0 + pos, c = c0 + 16 * q;
+        if (p < HW && c < ld) {
+            const uint32_t w4[4] = {tw[pos][4 * q], tw[pos][4 * q + 1], tw[pos][4 * q + 2], tw[pos][4 * q + 3]};
+            uint8_t* dst = nhwc_out + (int64_t)p * ld + c;
+            if (quads_ok && c + 16 <= ld) {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            } else {
+                for (int j = 0; j < 16 && c + j < ld; ++j) dst[j] = (uint8_t)(w4[j >> 2] >> (8 * (j & 3)));
+            }
+        }
+    } else {
+        const int p = p0 + pos, c = c0 + 16 * q;
+        uint32_t w4[4] = {0u, 0u, 0u, 0u};
+        if (p < HW && c < C) {
+            const uint8_t* src = nhwc_in + (int64_t)p * ld + c;
+            if (quads_ok && c + 16 <= ld) {
+                const uint4 v = *reinterpret_cast<const uint4*>(src);
+                w4[0] = v.x; w4[1] = v.y; w4[2] = v.z; w4[3] = v.w;
+            } else {
+                for (int j = 0; j < 16 && c + j < C; ++j) w4[j >> 2] |= (uint32_t)src[j] << (8 * (j & 3));
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tw[pos][4 * q + k] = w4[k];
+        __syncthreads();
+        uint32_t r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r[j] = tw[4 * b + j][a];  // channels 4a .. 4a+3 of position 4b + j
+        transpose4x4_bytes(r);                                // r[i] = positions 4b .. 4b+3 of channel 4a + i
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int cc = c0 + 4 * a + i, pp = p0 + 4 * b;
+            if (cc >= C || pp >= HW) continue;
+            uint8_t* dst = nchw_out + (int64_t)cc * HW + pp;
+            if (words_ok && pp + 4 <= HW) {
+                *reinterpret_cast<uint32_t*>(dst) = r[i];
+            } else {
+                for (int j = 0; j < 4 && pp + j < HW; ++j) dst[j] = (uint8_t)(r[i] >> (8 * j));
+            }
+        }
+    }
+}
+
 inline int grid_1d(int64_t total, int threads = 256, int per_sm = 16) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -561,11 +659,11 @@ static ConvDesc make_desc(const chxq_conv_geom& g, int has_x_zp, int x_zp, int64
 
 int launch_conv_simt(
         const void* x, const void* w, const chxq_conv_geom& g, int has_x_zp, int x_zp, const void* w_zp, int64_t w_zp_len, const EpiArgs& epi,
-        void* y, cudaStream_t s) {
+        void* y, cudaStream_t s, const void* x_zp_dev) {
     const int64_t total = (int64_t)g.N * g.M * g.Ho * g.Wo;
     if (total == 0) return CHXQ_OK;
     ConvDesc d = make_desc(g, has_x_zp, x_zp, w_zp_len);
-    conv_simt_kernel<<<grid_1d(total, 256, 32), 256, 0, s>>>(x, w, w_zp, d, epi, y);
+    conv_simt_kernel<<<grid_1d(total, 256, 32), 256, 0, s>>>(x, w, w_zp, d, epi, y, x_zp_dev);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }
@@ -647,9 +745,15 @@ static int transpose_dispatch(const void* x, int elem_bytes, int N, int C, int H
     dim3 grid((cols + 31) / 32, (rows + 31) / 32, N), block(32, 8);
     CHXQ_CHECK_ARG(grid.y <= 65535, "layout transform: map too large for the grid");
     cudaStream_t s = as_stream(stream);
-    if (elem_bytes == 1)
-        transpose_chw_kernel<uint8_t><<<grid, block, 0, s>>>(static_cast<const uint8_t*>(x), C, HW, ld, ld, to_nhwc, static_cast<uint8_t*>(y));
-    else
+    if (elem_bytes == 1) {
+        // 1-byte maps: the tiled kernel (32-bit words on the NCHW side, 128-bit words on the NHWC side)
+        dim3 tgrid((HW + kTrP - 1) / kTrP, ((to_nhwc ? ld : C) + kTrC - 1) / kTrC, N);
+        CHXQ_CHECK_ARG(tgrid.y <= 65535, "layout transform: too many channels for the grid");
+        if (to_nhwc)
+            transpose_u8_tile_kernel<true><<<tgrid, 256, 0, s>>>(static_cast<const uint8_t*>(x), C, HW, ld, static_cast<uint8_t*>(y));
+        else
+            transpose_u8_tile_kernel<false><<<tgrid, 256, 0, s>>>(static_cast<const uint8_t*>(x), C, HW, ld, static_cast<uint8_t*>(y));
+    } else
         transpose_chw_kernel<uint32_t><<<grid, block, 0, s>>>(static_cast<const uint32_t*>(x), C, HW, ld, ld, to_nhwc, static_cast<uint32_t*>(y));
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;

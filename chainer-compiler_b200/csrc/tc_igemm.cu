@@ -318,7 +318,12 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
         // tiles against a 256-channel block; chosen when there is at least one such item for every second pair of SMs.
         pair_items = (pos_tiles + 1) / 2 * ((q.cols + 255) / 256);
         pair = !pool && !halo && g_variant != 1 && g_variant != 6 && q.bk == 128 && q.group_cols == 0 && q.cols >= 256 && q.a_row_bytes == 0 &&
-               pair_items < (1ll << 31) && (g_variant == 7 || ((g_variant == 0 || g_variant == 2) && pair_items >= (int64_t)num_sms() / 4));
+               pair_items < (1ll << 31) &&
+               (g_variant == 7 ||
+                // by default where it measures faster: enough items to fill the pairs, and not the short-K layers with a residual tail
+                // (fewer than four K tiles per item), which are bound by their epilogue and run slightly faster as grouped tiles
+                ((g_variant == 0 || g_variant == 2) && pair_items >= (int64_t)num_sms() / 4 &&
+                 !(q.epi.residual != nullptr && q.KH * q.KW * (q.c_pad / q.bk) < 4)));
         if (pair) bn2 = 128;  // the maps below are those of 128-channel blocks: one CTA's half of the weights, halves of the staged output
         // Chosen whenever there is at least one group per SM; smaller problems spread better as single tiles.
         grouped = pair || pool || halo || g_variant >= 2 || groups >= (int64_t)num_sms();
@@ -328,7 +333,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
                                         (cuuint64_t)q.N};
             const cuuint64_t row_bytes = s2d_halo ? (cuuint64_t)q.a_row_bytes : (cuuint64_t)q.a_cs * q.W;
             const cuuint64_t strides[3] = {(cuuint64_t)q.a_cs, row_bytes, row_bytes * q.H};
-            p.halo_swz = s2d_halo ? 0 : (g_variant == 5 ? 2 : ((g_variant == 4 || q.bk == 128) ? 1 : 0));  // 128-byte pixels: the swizzled form only
+            p.halo_swz = s2d_halo ? 0 : ((g_variant == 4 || g_variant == 5 || q.bk == 128) ? 1 : 0);  // 128-byte pixels: the swizzled form only
             const cuuint32_t box[4] = {p.halo_swz ? (cuuint32_t)q.bk : 16u, (cuuint32_t)p.halo_w, (cuuint32_t)p.halo_h, 1u};
             const cuuint32_t estr[4] = {1, 1, 1, 1};
             p.halo_row_map = s2d_halo ? 1 : 0;

@@ -16,7 +16,7 @@
 //     floats (fma / sub .f32x2) wherever no clamp is involved.
 //
 //   * A nineteenth warp issues the TMA stores: the epilogue warps only count themselves in on an mbarrier when their part
-//     of a group is staged, so they never wait for one another.
+//     of a group is staged, so they never wait for one another.  A twentieth warp is the weights' TMA producer.
 //
 // TMEM holds two groups (2 x R x BN = 512 columns): the epilogue of group i overlaps the main loop of group i + 1.  The
 // staging tiles are multi-buffered as well.  Every wait is bounded exactly as in tc_kernel.cuh.
@@ -156,7 +156,7 @@ struct PoolGeom {
     static constexpr int kW = kTileW - 1, kH = kTileH - 1;                 // pooled positions a group owns
 };
 template <int BN, int BK, int EPI, bool RES, bool HALO, bool POOL = false>
-__global__ void __launch_bounds__(608, 1)
+__global__ void __launch_bounds__(640, 1)
 tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const TcParams p) {
     using Cfg = Tc2Config<BN, BK, RES, HALO>;
@@ -246,9 +246,13 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         gh0 = gh * (2 * PG::kH);
     };
 
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
+    if (warp == 0 || (warp == 19 && !HALO)) {
+        // ---------------- TMA producers ----------------
+        // Warp 0 loads the positions (and the residual tiles); without halo tiles warp 19 loads the weights.  One thread per
+        // operand: a thread that issues a tensor copy is held until the copy engine takes it, and with one thread for both operands
+        // the engine idles while that thread waits for the next free stage.  (Halo form: warp 0 loads both.)
         if (lane == 0) {
+            const bool is_a = warp == 0;
             int stage = 0, hstage = 0;
             uint32_t phase = 0, hphase = 0;
             bool ok = true;
@@ -271,7 +275,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
                 }
                 const int gbase = p.group_cols > 0 ? (ct * BN / p.group_cols) * p.group_cin : 0;
-                if (RES) {
+                if (RES && is_a) {
                     const int rb = it % Cfg::kBufs;
                     if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / Cfg::kBufs) & 1u) ^ 1u, abort_flag, p.status, 5, 0)) break;
                     mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
@@ -325,24 +329,29 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             }
                         }
                     }
-                } else
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    const int tap = kb / p.c_chunks, cc = kb - tap * p.c_chunks;
-                    const int kh = tap / p.KW, kw = tap - kh * p.KW;
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 0)) {
-                        ok = false;
-                        break;
-                    }
-                    mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+                } else {
+                    int bcol = 0;  // K offset in the packed weights: tap * c_pad + channel chunk
+                    for (int kh = 0; kh < p.KH && ok; ++kh)
+                        for (int kw = 0; kw < p.KW && ok; ++kw)
+                            for (int cc = 0; cc < p.c_chunks; ++cc, bcol += BK) {
+                                if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 0)) {
+                                    ok = false;
+                                    break;
+                                }
+                                if (is_a) {
+                                    mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);  // both operands' bytes
 #pragma unroll
-                    for (int t = 0; t < kR; ++t)
-                        tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA + t * 128 * BK), &tmA, full_bar(stage), gbase + cc * BK,
-                                    w0[t] * p.sw - p.pad_left + kw, h0[t] * p.sh - p.pad_top + kh, n0[t]);
-                    tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), tap * p.c_pad + cc * BK, ct * BN);
-                    if (++stage == kStages) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                                    for (int t = 0; t < kR; ++t)
+                                        tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA + t * 128 * BK), &tmA, full_bar(stage), gbase + cc * BK,
+                                                    w0[t] * p.sw - p.pad_left + kw, h0[t] * p.sh - p.pad_top + kh, n0[t]);
+                                } else {
+                                    tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), bcol, ct * BN);
+                                }
+                                if (++stage == kStages) {
+                                    stage = 0;
+                                    phase ^= 1u;
+                                }
+                            }
                 }
             }
         }
@@ -385,8 +394,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             if (p.halo_swz) {
                                 // one swizzled tile of BK-byte pixels: the view starts (kh, kw) pixels in; 8-row groups are one halo row apart
                                 const uint32_t a_lo = a_lo0 + (uint32_t)(hstage * (Cfg::kStageA >> 4)) + (uint32_t)((kh * halo_w + kw) * (BK >> 4));
-                                uint32_t a_hi = (uint32_t)((halo_w * BK) >> 4) | (1u << 14) | ((BK == 128 ? 2u : 4u) << 29);
-                                if (p.halo_swz == 2) a_hi |= ((a_lo >> 3) & 7u) << 17;  // base offset: (start address >> 7) & 7
+                                const uint32_t a_hi = (uint32_t)((halo_w * BK) >> 4) | (1u << 14) | ((BK == 128 ? 2u : 4u) << 29);
 #pragma unroll
                                 for (int k = 0; k < BK / 32; ++k)
 #pragma unroll
@@ -707,7 +715,7 @@ int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
         CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
-    tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL><<<grid, 608, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
+    tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL><<<grid, 640, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
 }

@@ -18,7 +18,7 @@ struct TcParams {
     int Wo, Ho, No;
     int KH, KW, pad_top, pad_left;
     int sw, sh;  // convolution strides: input coordinate = output coordinate * stride - pad + tap
-    int halo_swz;  // halo form: 0 = planes of 16-byte rows without swizzle, 1 = one swizzled tile of BK-byte rows, 2 = same with the descriptor's base offset
+    int halo_swz;  // halo form: 0 = planes of 16-byte rows without swizzle, 1 = one swizzled tile of BK-byte rows
     // halo form: halo tile of halo_w x halo_h pixels in halo_planes planes of [pixel][16 bytes]; the two 16-byte K halves of an MMA are
     // halo_lbo 16-byte units apart (one plane for channel chunks; one pixel for the space-to-depth stem, whose K runs along the row),
     // consecutive MMAs of a tap halo_kstep units

@@ -26,6 +26,7 @@ from ._lib import (FLOAT16, FLOAT32, FLOAT64, INT8, NCHW, NHWC, PATH_AUTO, PATH_
 _TORCH_Q = {torch.uint8: UINT8, torch.int8: INT8}
 _TORCH_F = {torch.float16: FLOAT16, torch.float32: FLOAT32, torch.float64: FLOAT64}
 _workspaces = {}
+_zero_zp_cache = {}  # (data_ptr, numel, dtype) -> (version, all zero?) of weight zero-point tensors seen by QLinearConv
 _retired_workspaces = []  # superseded scratch buffers: kept alive because captured CUDA graphs hold their raw addresses
 
 
@@ -70,6 +71,24 @@ def workspace(nbytes, device):
     return ws
 
 
+def _weight_zero_points_are_zero(wz):
+    """Whether a weight zero-point tensor holds only zeros, learned by ONE device-to-host read per tensor (and again only after
+    an in-place change, which bumps the tensor's version): weight zero points are graph constants, and symmetric int8 weights,
+    the common case, have none.  The C ABI treats a zero point that is present as non-zero, because it never reads device
+    memory back; this op body is the place that may know better, as the reference's VM knows its constants at Init."""
+    if torch.cuda.is_current_stream_capturing():
+        return False  # no synchronization during a capture: the general form
+    key = (wz.data_ptr(), wz.numel(), wz.dtype)
+    hit = _zero_zp_cache.get(key)
+    if hit is not None and hit[0] == wz._version:
+        return hit[1]
+    zero = not bool(torch.any(wz != 0).item())
+    if len(_zero_zp_cache) > 4096:
+        _zero_zp_cache.clear()
+    _zero_zp_cache[key] = (wz._version, zero)
+    return zero
+
+
 def _check_residual(op, residual, y_shape, channels_last):
     """A fused residual is read with the output's indexing: it must be a uint8 map of the output's shape and layout, and the
     tensor-core kernels read it 16 bytes at a time."""
@@ -105,11 +124,30 @@ def _is_channels_last(t):
     return t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last) and not (t.is_contiguous() and t.shape[1] != 1)
 
 
+def _is_device_scalar(v):
+    return isinstance(v, torch.Tensor) and v.is_cuda and v.numel() == 1
+
+
 def QuantizeLinear(x, y_scale, y_zero_point=None, round_mode=ROUND_REF):
-    """runtime/chxvm_defs.py:451-453; body runtime/ops/quantize.cc:16-35,48-53."""
+    """runtime/chxvm_defs.py:451-453; body runtime/ops/quantize.cc:16-35,48-53.
+
+    y_scale (and y_zero_point) may be one-element CUDA tensors: the scalars are then read by the kernel on the device, without
+    the device-to-host read the reference's VM does per Scalar argument (runtime/chxvm_var.cc:70-76)."""
     _require_cuda(x)
     if x.dtype != torch.float32:
         raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QuantizeLinear: x must be float32, got %s" % x.dtype)
+    if _is_device_scalar(y_scale):
+        if y_scale.dtype != torch.float32:
+            raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QuantizeLinear: a device y_scale must be float32")
+        if y_zero_point is not None and not _is_device_scalar(y_zero_point):
+            zp_h, code_h = _zp_scalar(y_zero_point)
+            y_zero_point = torch.tensor([zp_h], dtype=torch.uint8 if code_h == UINT8 else torch.int8, device=x.device)
+        code = UINT8 if y_zero_point is None else _qcode(y_zero_point, "QuantizeLinear: y_zero_point")
+        if not (x.is_contiguous() or _is_channels_last(x)):
+            x = x.contiguous()
+        y = torch.empty_like(x, dtype=torch.uint8 if code == UINT8 else torch.int8)
+        check(lib().chxq_quantize_linear_dev(_ptr(x), x.numel(), _ptr(y_scale), _ptr(y_zero_point), code, round_mode, _ptr(y), _stream()))
+        return y
     zp, code = _zp_scalar(y_zero_point)
     if not (x.is_contiguous() or _is_channels_last(x)):
         x = x.contiguous()
@@ -228,11 +266,20 @@ def _conv_io(x, g, out_dtype):
 
 
 def ConvInteger(x, w, x_zero_point=None, w_zero_point=None, strides=(), pads=(), group=1, auto_pad="", path=PATH_AUTO):
-    """runtime/chxvm_defs.py:466-469; body runtime/ops/quantize.cc:116-146."""
+    """runtime/chxvm_defs.py:466-469; body runtime/ops/quantize.cc:116-146.
+
+    x_zero_point may be a one-element CUDA tensor of x's dtype (a zero point computed on the device): it is then read by the
+    kernel, not by the host (general CUDA-core kernel)."""
     _require_cuda(x, w)
     g = conv_geometry(x, w, strides, pads, group, auto_pad)
     x, y = _conv_io(x, g, torch.int32)
     w = w.contiguous()
+    if _is_device_scalar(x_zero_point):
+        if x_zero_point.dtype != x.dtype:
+            raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "ConvInteger: a device x_zero_point must have x's dtype")
+        zw, zw_len = _zp_array(w_zero_point, w, "w_zero_point")
+        check(lib().chxq_conv_integer_dev(_ptr(x), _ptr(w), ctypes.byref(g), _ptr(x_zero_point), _ptr(zw), zw_len, _ptr(y), _stream()))
+        return y
     zx, _ = _zp_scalar(x_zero_point)
     zw, zw_len = _zp_array(w_zero_point, w, "w_zero_point")
     ws_bytes = lib().chxq_conv_workspace(ctypes.byref(g)) if path != PATH_SIMT else 0
@@ -264,6 +311,8 @@ def _qconv_params(x, w, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y
     keep.extend([w_scale, w_zero_point])
     p.x_scale, p.x_zero_point = float(x_scale), zx
     p.w_scale, p.w_zero_point, p.w_params_len = w_scale.data_ptr(), w_zero_point.data_ptr(), w_scale.numel()
+    if _weight_zero_points_are_zero(w_zero_point):
+        p.w_zero_point = None  # symmetric weights: the kernels skip the weight zero-point term (and its input sums)
     p.y_scale, p.y_zero_point, p.y_dtype = float(y_scale), zy, cy
     if b is not None:
         _require_cuda(b)
@@ -557,6 +606,18 @@ def PrepareWeights(w, bn=None, conv_bias=None, epsilon=1e-5, to_int8=True, per_c
     check(lib().chxq_prepare_weights(_ptr(w), M, inner, p(gamma), p(beta), p(mean), p(var), float(epsilon), p(conv_bias), int(to_int8), int(per_channel),
                                      _ptr(q), _ptr(scales), _ptr(zps), p(folded_w), p(folded_bias), _ptr(ws), ws_bytes, _stream()))
     return (q, scales, zps, folded_bias, folded_w) if return_folded else (q, scales, zps, folded_bias)
+
+
+def DynamicQuantParamsU8(rmin, rmax):
+    """scale, zero point of the dynamic uint8 quantization of an activation from its ReduceMin / ReduceMax, as the Sub, Div,
+    Floor, Cast nodes of compiler/quantize.cc:196-207 compute them, on the device: returns (float32[1], uint8[1]) CUDA tensors."""
+    _require_cuda(rmin, rmax)
+    if rmin.dtype != torch.float32 or rmax.dtype != torch.float32 or rmin.numel() != 1 or rmax.numel() != 1:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "DynamicQuantParamsU8: rmin and rmax must be one-element float32 tensors")
+    scale = torch.empty(1, dtype=torch.float32, device=rmin.device)
+    zp = torch.empty(1, dtype=torch.uint8, device=rmin.device)
+    check(lib().chxq_dynamic_quant_params_u8(_ptr(rmin), _ptr(rmax), _ptr(scale), _ptr(zp), _stream()))
+    return scale, zp
 
 
 def MinMax(x):

@@ -560,10 +560,13 @@ class ChromeTracing:
 class Executor:
     """Runs a Program on one CUDA device.  Quantized ops go through chainer_compiler_b200.ops; glue ops are torch expressions."""
 
-    def __init__(self, program, device="cuda:0", float_ops_via_torch=False, fold_scales=False):
+    def __init__(self, program, device="cuda:0", float_ops_via_torch=False, fold_scales=False, device_scalars=True):
         """fold_scales: requantize every QLinearConv with one fp32 multiplier per output channel (x_scale * w_scale / y_scale
         folded on the host) instead of the reference's multiply and divide; outputs can differ from the default by one step
-        on exact ties of the intermediate rounding."""
+        on exact ties of the intermediate rounding.
+        device_scalars: the scale and zero point of a dynamically quantized activation (the ReduceMin / ReduceMax -> Sub, Div,
+        Floor, Cast sub-graph of `--quantize`) stay on the device and are read by the kernels that consume them; False reads
+        them back to the host per operator, as the reference's VM does (runtime/chxvm_var.cc:70-76).  Same results."""
         import torch
         sys.path.insert(0, ROOT)
         import __graft_entry__ as entry
@@ -580,6 +583,7 @@ class Executor:
         self.host_consts = program.constants
         self.packed = {}
         self.fold_scales = bool(fold_scales)
+        self.device_scalars = bool(device_scalars)
         self._graph = None
 
     def _scalar(self, name, env, host):
@@ -605,11 +609,19 @@ class Executor:
     def is_static(self):
         """True when running the program needs no device-to-host read: every scalar operand is an initializer and there is no
         dynamic-quantization instruction.  Such a program can be captured in a CUDA graph."""
+        dev_scalars = set()  # values the device-scalar path keeps on the device
         for inst in self.program.insts:
-            if inst.op in ("ReduceMinMax", "DynamicQuantParamsU8", "ReduceMin", "ReduceMax"):
+            if inst.op in ("ReduceMinMax", "DynamicQuantParamsU8"):
+                if not self.device_scalars:
+                    return False
+                dev_scalars.update(inst.outputs)
+                continue
+            if inst.op in ("ReduceMin", "ReduceMax"):
                 return False
             for k in self._SCALAR_OPERANDS.get(inst.op, ()):
                 if k < len(inst.inputs) and inst.inputs[k] != "" and inst.inputs[k] not in self.host_consts:
+                    if inst.inputs[k] in dev_scalars and inst.op in ("QuantizeLinear", "ConvInteger"):
+                        continue  # these two read a device scalar themselves
                     return False
         return True
 
@@ -676,11 +688,22 @@ class Executor:
         out = inst.outputs[0]
         auto_pad = a.get("auto_pad", "NOTSET")
         auto_pad = "" if auto_pad == "NOTSET" else auto_pad
+        dev_scalar = lambda k: has(k) and inst.inputs[k] in env and inst.inputs[k] not in self.host_consts and self.device_scalars \
+            and env[inst.inputs[k]].numel() == 1  # noqa: E731
         if op == "ReduceMinMax":
-            mm = ops.MinMax(x[0].contiguous()).cpu().numpy()  # the device-to-host read the reference does per scalar argument
-            host[inst.outputs[0]], host[inst.outputs[1]] = np.float32(mm[0]), np.float32(mm[1])
+            mm = ops.MinMax(x[0].contiguous())
+            if self.device_scalars:
+                env[inst.outputs[0]], env[inst.outputs[1]] = mm[0:1], mm[1:2]  # stay on the device
+            else:
+                mm = mm.cpu().numpy()  # the device-to-host read the reference does per scalar argument
+                host[inst.outputs[0]], host[inst.outputs[1]] = np.float32(mm[0]), np.float32(mm[1])
         elif op == "DynamicQuantParamsU8":
-            host[inst.outputs[0]], host[inst.outputs[1]] = dynamic_params_u8(host[inst.inputs[0]], host[inst.inputs[1]])
+            if inst.inputs[0] in env:
+                env[inst.outputs[0]], env[inst.outputs[1]] = ops.DynamicQuantParamsU8(x[0], x[1])
+            else:
+                host[inst.outputs[0]], host[inst.outputs[1]] = dynamic_params_u8(host[inst.inputs[0]], host[inst.inputs[1]])
+        elif op == "QuantizeLinear" and dev_scalar(1):
+            env[out] = ops.QuantizeLinear(x[0].contiguous(), x[1], x[2] if has(2) else None)
         elif op == "QuantizeLinear":
             env[out] = ops.QuantizeLinear(x[0].contiguous(), sc(1), sc(2) if has(2) else None)
         elif op == "DequantizeLinear":
@@ -716,7 +739,10 @@ class Executor:
                     xin = ops.to_channels_last(xin)
                 if not packed.eligible:
                     packed = None
-            if op == "ConvInteger":
+            if op == "ConvInteger" and dev_scalar(2):
+                # the zero point was computed on the device: the general kernel reads it there (no host round trip)
+                env[out] = ops.ConvInteger(x[0], x[1], x[2], x[3] if has(3) else None, strides, pads, group, auto_pad)
+            elif op == "ConvInteger":
                 if packed is not None:
                     env[out] = ops.ConvIntegerPacked(xin, packed, sc(2) if has(2) else None)
                 else:
@@ -917,6 +943,9 @@ def parse_args(argv):
     ap.add_argument("--fold_bn_first", action="store_true")
     ap.add_argument("--fold_scales", action="store_true")
     ap.add_argument("--cuda_graph", action="store_true")
+    ap.add_argument("--host_scalars", action="store_true",
+                    help="read dynamic-quantization scales and zero points back to the host per operator, as the reference's VM does; "
+                         "default: they stay on the device (same results, no synchronization, the program can be captured in a CUDA graph)")
     ap.add_argument("--no_peephole", action="store_true")
     ap.add_argument("--fuse_operations", action="store_true")
     ap.add_argument("--use_nvrtc", action="store_true")
@@ -966,7 +995,7 @@ def run_onnx(argv):
     if args.compile_only or args.skip_inference:
         return 0
     import torch
-    ex = Executor(program, args.device, args.float_ops_via_torch, fold_scales=args.fold_scales)
+    ex = Executor(program, args.device, args.float_ops_via_torch, fold_scales=args.fold_scales, device_scalars=not args.host_scalars)
     tracer = ChromeTracing() if args.chrome_tracing else None
     # --cuda_graph: after the first (discarded) iteration of a case the remaining ones replay a captured graph
     use_graph = args.cuda_graph and args.iterations > 1 and ex.is_static() and not (args.chrome_tracing or args.dump_outputs_dir or args.trace)

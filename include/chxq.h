@@ -174,7 +174,9 @@ typedef struct chxq_qconv_params {
     float x_scale;
     int32_t x_zero_point;
     const float* w_scale;     /* device, length w_params_len */
-    const void* w_zero_point; /* device, dtype of w, length w_params_len */
+    const void* w_zero_point; /* device, dtype of w, length w_params_len; NULL = the caller knows every zero point is zero
+                                 (symmetric weights): the weight zero-point term and its per-position input sums are then skipped.
+                                 A pointer is never read back by the host, so zero points that are present are treated as non-zero. */
     int64_t w_params_len;     /* 1 (per tensor) or M (per output channel) */
     float y_scale;
     int32_t y_zero_point;
@@ -333,6 +335,26 @@ int chxq_nhwc_to_nchw(const void* x, int32_t elem_bytes, int32_t N, int32_t C, i
 /* ReduceMin + ReduceMax of an fp32 tensor in one pass (the dynamic-quantization parameter
  * sub-graph of compiler/quantize.cc:172-202); out[0] = min, out[1] = max, both on the device. */
 int chxq_minmax_f32(const float* x, int64_t n, float* out2, void* stream);
+
+/* ---- Dynamic quantization without a host round trip.  The reference's --quantize pass feeds every quantized operator from
+ * a sub-graph ReduceMin / ReduceMax -> Sub, Div, Floor, Cast -> QuantizeLinear (compiler/quantize.cc:172-207) whose scale and
+ * zero point are 0-d device arrays; its VM reads each of them back to the host per op call (runtime/chxvm_var.cc:70-76), which
+ * synchronizes the stream and keeps the program out of a CUDA graph.  The three entries below take those scalars where they
+ * are: on the device.
+ *   chxq_dynamic_quant_params_u8: scale = (rmax - rmin) / 255 (1 when rmax == rmin), zero point = uint8(floor((0 - rmin) /
+ *     scale)) in the fp32 operations of the emitted nodes; the range is NOT widened to include zero (as in the reference); the
+ *     Cast saturates.  rmin / rmax: the two floats chxq_minmax_f32 writes.
+ *   chxq_quantize_linear_dev: chxq_quantize_linear with y_scale and y_zero_point (dtype y_dtype, may be NULL = 0) read from
+ *     device memory; same element arithmetic (runtime/ops/quantize.cc:16-35).
+ *   chxq_conv_integer_dev: chxq_conv_integer (runtime/ops/quantize.cc:116-146) with the activation zero point read from a device
+ *     scalar of x's dtype; runs on the general CUDA-core kernel (the tensor-core path folds a host-known zero point into its
+ *     padding value and correction terms).
+ * MatMulInteger already takes its zero points as device arrays. */
+int chxq_dynamic_quant_params_u8(const float* rmin, const float* rmax, float* scale, uint8_t* zero_point, void* stream);
+int chxq_quantize_linear_dev(const float* x, int64_t n, const float* y_scale, const void* y_zero_point, int32_t y_dtype, int32_t round_mode,
+                             void* y, void* stream);
+int chxq_conv_integer_dev(const void* x, const void* w, const chxq_conv_geom* g, const void* x_zero_point, const void* w_zero_point,
+                          int64_t w_zp_len, int32_t* y, void* stream);
 
 #ifdef __cplusplus
 }

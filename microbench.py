@@ -2,7 +2,7 @@
 LSTM-cell elementwise group, the MatMulInteger / QLinearMatMul sweep, MobileNetV2, QuantizeLinear / DequantizeLinear and
 single depthwise layers.  One JSON line per measurement on stdout.
 
-    python microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [prepare] [onnx] [stem[=BATCH]]
+    python microbench.py [mlp] [eltwise] [gemm] [mobilenet] [quant] [depthwise] [nchw] [prepare] [onnx] [stem[=BATCH]]
 
 `bench.py` imports `secondary()` from here for the `secondary` block of its JSON line.
 
@@ -153,6 +153,23 @@ def run(which, dev, emit_line=None, gemm_sizes=(1024, 4096, 8192, 16384), mobile
             ms = timeit(lambda: ops.QLinearConvPacked(x, pk, 0.02, np.uint8(0), ws, wz, 0.05, np.uint8(0), fold_scales=True))
             emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, tensor cores (diagonal blocks)" % (C, H, H, s, N), ms,
                  gbs=nbytes / ms / 1e6)
+    if "nchw" in which:
+        # the literal drop-in call of the reference's op (NCHW in, NCHW out, unpacked weights) on a res3 3x3 layer, beside the
+        # packed NHWC entry the benchmark network uses
+        N, C, H = 256, 128, 28
+        x = torch.randint(0, 256, (N, C, H, H), dtype=torch.uint8, device=dev)
+        w = torch.randint(-127, 128, (C, C, 3, 3), dtype=torch.int8, device=dev)
+        ws = torch.full((C,), 1e-3, device=dev)
+        wz = torch.zeros(C, dtype=torch.int8, device=dev)
+        ms = timeit(lambda: ops.QLinearConv(x, 0.02, np.uint8(0), w, ws, wz, 0.05, np.uint8(0), None, (1, 1), (1, 1)))
+        emit("QLinearConv 3x3 C128 28x28 batch 256, NCHW in / NCHW out through the op signature (transposes + tensor cores)", ms,
+             tops=2 * N * H * H * C * C * 9 / ms / 1e9)
+        ms = timeit(lambda: ops.QLinearConv(x, 0.02, np.uint8(0), w, ws, wz, 0.05, np.uint8(0), None, (1, 1), (1, 1), path=1))
+        emit("the same call on the general CUDA-core kernel", ms, tops=2 * N * H * H * C * C * 9 / ms / 1e9)
+        xl = x.contiguous(memory_format=torch.channels_last)
+        pk = ops.PackedConv(w, wz, x.shape, (1, 1), (1, 1))
+        ms = timeit(lambda: ops.QLinearConvPacked(xl, pk, 0.02, np.uint8(0), ws, wz, 0.05, np.uint8(0)))
+        emit("the same layer through the packed NHWC entry", ms, tops=2 * N * H * H * C * C * 9 / ms / 1e9)
     if "prepare" in which:
         # model preparation: batch-norm folding + per-channel int8 weight quantization of every ResNet-50 convolution
         import time
@@ -238,7 +255,7 @@ def secondary(dev):
     """The workloads beside the headline benchmark, for the `secondary` block of bench.py's JSON line: QuantizeLinear /
     DequantizeLinear and the fused LSTM-cell group in GB/s (against the measured copy bandwidth and against the nominal
     8 TB/s), the MatMulInteger / QLinearMatMul sweep in TOPS, MobileNetV2 batch 512 in img/s and depthwise layers in GB/s."""
-    return run({"quant", "eltwise", "gemm", "mobilenet", "depthwise", "mlp"}, dev, mobilenet_cuda_cores=False)
+    return run({"quant", "eltwise", "gemm", "mobilenet", "depthwise", "mlp", "nchw"}, dev, mobilenet_cuda_cores=False)
 
 
 def main():
@@ -246,7 +263,7 @@ def main():
         raise SystemExit("microbench.py needs a CUDA device: this package has no CPU path")
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare", "onnx", "stem"}
+    which = set(sys.argv[1:]) or {"mlp", "eltwise", "gemm", "mobilenet", "quant", "depthwise", "prepare", "onnx", "stem", "nchw"}
     run(which, dev, emit_line=lambda line: print(json.dumps(line), flush=True))
 
 

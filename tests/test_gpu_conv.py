@@ -71,6 +71,10 @@ def test_conv_integer_tensor(ops, orc, dev, N, C, H, W, M, k, stride, pad):
     assert y.is_contiguous(memory_format=torch.channels_last)
     want = orc.conv_integer(x, w, None, None, (stride, stride), (pad, pad))
     assert np.array_equal(y.cpu().numpy(), want)
+    # the reference's own signature, NCHW in and NCHW out, on the tensor-core kernels (transposes through the workspace)
+    y2 = ops.ConvInteger(_t(x, dev, False), _t(w, dev), None, None, (stride, stride), (pad, pad), path=TENSOR)
+    ops.device_status()
+    assert y2.is_contiguous() and np.array_equal(y2.cpu().numpy(), want)
 
 
 @pytest.mark.parametrize("N,C,H,W,M,k,stride,pad", [TC_CASES[2], TC_CASES[4], TC_CASES[8], TC_CASES[0]])
@@ -127,7 +131,7 @@ def test_conv_stride2_small_channel_space_to_depth(ops, orc, dev, pkg, shape, M,
         assert np.array_equal(yq.cpu().numpy(), orc.requantize(acc, 0.02, ws_, 0.05, 20, bias=bias, channel_axis=1, fold=fold)), fold
 
 
-@pytest.mark.parametrize("path,cl", [(SIMT, False), (SIMT, True), (TENSOR, True)])
+@pytest.mark.parametrize("path,cl", [(SIMT, False), (SIMT, True), (TENSOR, True), (TENSOR, False)])  # (TENSOR, False): NCHW in and out, as the reference's op
 @pytest.mark.parametrize("N,C,H,W,M,k,stride,pad", [TC_CASES[2], TC_CASES[3], TC_CASES[8], TC_CASES[1]])
 def test_qlinear_conv(ops, orc, dev, path, cl, N, C, H, W, M, k, stride, pad):
     rng = np.random.default_rng(M * 7 + k)
@@ -377,7 +381,7 @@ def test_grouped_tensor_core_kernel(pkg, ops, orc, dev, grouped_kernel, N, C, H,
     ]
     for c in cases:
         ref = run(1, c["zx"], c["zy"], **c["kw"])
-        for variant in (2, 3, 4, 5):  # 3..5: halo tiles where the geometry allows them (3x3 and smaller, stride 1): planes, swizzled, swizzled + base offset
+        for variant in (2, 3, 4, 7):  # 3, 4: halo tiles where the geometry allows them (3x3 and smaller, stride 1): planes, swizzled; 7: CTA pairs where eligible
             got = run(variant, c["zx"], c["zy"], **c["kw"])
             assert torch.equal(got, ref), (variant, c)
     acc = orc.conv_integer(x, w, 0, wz, (stride, stride), (pad, pad))
