@@ -79,6 +79,7 @@ SIGNATURES = {
     "chxq_launch_count": (_i64, []),
     "chxq_tc_variant": (_c.c_int, [_i32]),
     "chxq_tc_pair_slots": (_c.c_int, [_c.POINTER(_c.c_int32)]),
+    "chxq_tc_test_hooks": (_c.c_int, [_i64, _i32]),
     "chxq_tc_profile": (_c.c_int, [_i32]),
     "chxq_tc_profile_read": (_c.c_int, [_c.POINTER(_c.c_double), _c.POINTER(_i64), _c.POINTER(_c.c_double)]),
     "chxq_quantize_linear": (_c.c_int, [_vp, _i64, _f32, _i32, _i32, _i32, _vp, _vp]),

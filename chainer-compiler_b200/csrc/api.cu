@@ -28,36 +28,79 @@ __device__ __forceinline__ int zp_at(const ZpSpec& z, int64_t i, int is_signed) 
     return ldq_rt(z.ptr, z.len == 1 ? 0 : i, is_signed);
 }
 
-// B[K, N] (row-major) -> Bt[N, k_pad] (K-major rows, zero padded), through a 32x32 shared tile.
-__global__ void __launch_bounds__(256) transpose_b_kernel(const uint8_t* __restrict__ b, int64_t K, int64_t N, int64_t k_pad, uint8_t* __restrict__ bt) {
-    __shared__ uint8_t tile[32][33];
-    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
-    const int64_t k0 = (int64_t)blockIdx.y * 32, n0 = (int64_t)blockIdx.x * 32;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int64_t k = k0 + ty * 4 + i, n = n0 + tx;
-        tile[ty * 4 + i][tx] = (k < K && n < N) ? b[k * N + n] : (uint8_t)0;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int64_t n = n0 + ty * 4 + i, k = k0 + tx;
-        if (n < N && k < k_pad) bt[n * k_pad + k] = tile[tx][ty * 4 + i];
-    }
+// B[K, N] (row-major) -> Bt[N, k_pad] (K-major rows, zero padded) and, in the same pass, the column terms of the activation zero
+// point, T[n] += sum_k za[k] * b[k, n] (T zeroed beforehand; integer atomics, so the sum is exact whatever the order).
+// 64 x 64 bytes per block of 256 threads: 32-bit loads along N, a 4 x 4 byte transpose in registers, the tile through shared
+// memory as words with a pitch of 17 (conflict-free), 128-bit stores along K.
+__device__ __forceinline__ void transpose4x4(uint32_t (&r)[4]) {
+    const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[0], r[1], 0x7362);
+    const uint32_t t2 = __byte_perm(r[2], r[3], 0x5140), t3 = __byte_perm(r[2], r[3], 0x7362);
+    r[0] = __byte_perm(t0, t2, 0x5410);
+    r[1] = __byte_perm(t0, t2, 0x7632);
+    r[2] = __byte_perm(t1, t3, 0x5410);
+    r[3] = __byte_perm(t1, t3, 0x7632);
 }
 
-// T[n] = sum_k za[k] * b[k, n]; zbn[n] = zb[n] widened.  One thread per column.
-__global__ void __launch_bounds__(256) gemm_col_terms_kernel(
-        const void* __restrict__ b, int b_signed, int a_signed, int64_t K, int64_t N, ZpSpec za, ZpSpec zb, int32_t* __restrict__ T,
-        int32_t* __restrict__ zbn) {
-    const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (n >= N) return;
-    unsigned t = 0u;
-    if (za.len > 0) {
-        for (int64_t k = 0; k < K; ++k) t += (unsigned)zp_at(za, k, a_signed) * (unsigned)ldq_rt(b, k * N + n, b_signed);
+__global__ void __launch_bounds__(256) transpose_b_terms_kernel(
+        const uint8_t* __restrict__ b, int64_t K, int64_t N, int64_t k_pad, uint8_t* __restrict__ bt, ZpSpec za, int a_signed, int b_signed,
+        int32_t* __restrict__ T) {
+    __shared__ uint32_t tw[64][17];
+    __shared__ int colsum[64];
+    const int tid = threadIdx.x;
+    const int64_t k0 = (int64_t)blockIdx.y * 64, n0 = (int64_t)blockIdx.x * 64;
+    const int a = tid / 16, bq = tid % 16;  // load side: rows k0 + 4a .. +3, columns n0 + 4bq .. +3
+    const bool words_ok = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(b) & 3u) == 0);
+    if (tid < 64) colsum[tid] = 0;
+    uint32_t r[4];
+    int part[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t k = k0 + 4 * a + i, n = n0 + 4 * bq;
+        uint32_t v = 0u;
+        if (k < K && n < N) {
+            const uint8_t* src = b + k * N + n;
+            if (words_ok && n + 4 <= N) {
+                v = *reinterpret_cast<const uint32_t*>(src);
+            } else {
+                for (int j = 0; j < 4 && n + j < N; ++j) v |= (uint32_t)src[j] << (8 * j);
+            }
+            if (T != nullptr) {
+                const int z = zp_at(za, k, a_signed);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t byte = (v >> (8 * j)) & 0xffu;
+                    part[j] += z * (b_signed ? (int)(int8_t)byte : (int)byte);
+                }
+            }
+        }
+        r[i] = v;
     }
-    T[n] = (int32_t)t;
-    zbn[n] = zp_at(zb, n, b_signed);
+    transpose4x4(r);  // r[j] = rows 4a .. 4a+3 of column 4bq + j
+    __syncthreads();   // colsum is zero
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        tw[4 * bq + j][a] = r[j];
+        if (T != nullptr && part[j] != 0) atomicAdd(&colsum[4 * bq + j], part[j]);
+    }
+    __syncthreads();
+    const int col = tid / 4, q = tid % 4;  // store side: column n0 + col, rows k0 + 16q .. +15
+    const int64_t n = n0 + col, k = k0 + 16 * q;
+    if (n < N && k < k_pad) {
+        const uint32_t w4[4] = {tw[col][4 * q], tw[col][4 * q + 1], tw[col][4 * q + 2], tw[col][4 * q + 3]};
+        uint8_t* dst = bt + n * k_pad + k;
+        if (k + 16 <= k_pad && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        } else {
+            for (int j = 0; j < 16 && k + j < k_pad; ++j) dst[j] = (uint8_t)(w4[j >> 2] >> (8 * (j & 3)));
+        }
+    }
+    if (T != nullptr && tid < 64 && n0 + tid < N && colsum[tid] != 0) atomicAdd(&T[n0 + tid], colsum[tid]);
+}
+
+// zbn[n] = zb[n] widened.  One thread per column.
+__global__ void __launch_bounds__(256) gemm_zb_kernel(int b_signed, int64_t N, ZpSpec zb, int32_t* __restrict__ zbn) {
+    const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n < N) zbn[n] = zp_at(zb, n, b_signed);
 }
 
 // R[m] = sum_k (a[m, k] - za[k]).  One warp per row.
@@ -354,13 +397,16 @@ int gemm_dispatch(
     for (int64_t bi = 0; bi < batch; ++bi) {
         const uint8_t* ab = static_cast<const uint8_t*>(a) + bi * M * K;
         const uint8_t* bb = static_cast<const uint8_t*>(b) + bi * K * N;
-        dim3 tgrid((unsigned)((N + 31) / 32), (unsigned)((ws.k_pad + 31) / 32)), tblock(32, 8);
+        dim3 tgrid((unsigned)((N + 63) / 64), (unsigned)((ws.k_pad + 63) / 64));
         if (tgrid.y > 65535) return set_error(CHXQ_ERR_UNSUPPORTED, "%s: K too large for the repacking grid", op);
-        transpose_b_kernel<<<tgrid, tblock, 0, s>>>(bb, K, N, ws.k_pad, bt);
-        const bool need_cols = za.len > 0 || zb.len > 0;
-        if (need_cols) gemm_col_terms_kernel<<<blocks_for(N), 256, 0, s>>>(bb, b_signed, a_signed, K, N, za, zb, T, zbn);
-        if (zb.len > 0) gemm_row_terms_kernel<<<blocks_for(M * 32), 256, 0, s>>>(ab, a_signed, M, K, za, R);
-        count_launch((need_cols ? 1 : 0) + (zb.len > 0 ? 1 : 0));
+        // one pass over B: the K-major copy and, when a has a zero point, its column terms
+        if (za.len > 0) CHXQ_CUDA(cudaMemsetAsync(T, 0, (size_t)N * 4, s));
+        transpose_b_terms_kernel<<<tgrid, 256, 0, s>>>(bb, K, N, ws.k_pad, bt, za, a_signed ? 1 : 0, b_signed ? 1 : 0, za.len > 0 ? T : nullptr);
+        if (zb.len > 0) {
+            gemm_zb_kernel<<<blocks_for(N), 256, 0, s>>>(b_signed ? 1 : 0, N, zb, zbn);
+            gemm_row_terms_kernel<<<blocks_for(M * 32), 256, 0, s>>>(ab, a_signed, M, K, za, R);
+            count_launch(2);
+        }
         CHXQ_LAUNCH_CHECK();
         TcProblem p{};
         p.a = ab; p.a_signed = a_signed; p.C = (int)K; p.a_cs = K; p.W = (int)M; p.H = 1; p.N = 1;

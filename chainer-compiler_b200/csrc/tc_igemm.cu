@@ -62,6 +62,8 @@ std::mutex g_prof_mu;
 #ifdef CHXQ_TL
 long long* g_tl_buf = nullptr;
 #endif
+std::atomic<long long> g_wait_limit_ns{2000000000ll};  // chxq_tc_test_hooks
+std::atomic<int> g_test_skip_kb{-1};
 std::atomic<int> g_variant{0};  // chxq_tc_variant: 0 = choose, 1 = one tile per step, 2 = grouped tiles where eligible, 3 = grouped + halo tiles
 
 int pick_bn(int cols, int64_t pos_tiles) {
@@ -236,6 +238,8 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     cudaMemsetAsync(g_tl_buf, 0, 3 * 2048 * sizeof(long long), s);
     p.tl = g_tl_buf;
 #endif
+    p.wait_limit_ns = (unsigned long long)g_wait_limit_ns.load(std::memory_order_relaxed);
+    p.test_skip_kb = g_test_skip_kb.load(std::memory_order_relaxed);
     p.status = device_status_ptr();
     if (!p.status) return set_error(CHXQ_ERR_CUDA, "device status word is unavailable");
     const int elt = q.epi.mode == kEpiInt32 ? 4 : 1;
@@ -391,6 +395,26 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
             }
         }
     }
+    // MatMulInteger / ConvInteger on CTA pairs: int32 accumulators written straight from registers (no staging, no output map).
+    if (epi_kind == tc::kEpiKInt32 && !pool && g_variant != 1 && g_variant != 6 && q.bk == 128 && q.group_cols == 0 && q.cols >= 256 &&
+        q.a_row_bytes == 0) {
+        pair_items = (pos_tiles + 1) / 2 * ((q.cols + 255) / 256);
+        pair = pair_items < (1ll << 31) && (g_variant == 7 || pair_items >= (int64_t)num_sms() / 4);
+        if (pair) {
+            const int taps = q.KH * q.KW;
+            const cuuint64_t bdims[2] = {(cuuint64_t)taps * q.c_pad, (cuuint64_t)q.cols};
+            const cuuint64_t bstrides[1] = {(cuuint64_t)taps * q.c_pad};
+            const cuuint32_t bbox[2] = {(cuuint32_t)q.bk, 128u};  // one CTA's half of a 256-column block
+            const cuuint32_t bestr[2] = {1, 1};
+            CUresult r1 = encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(q.b), bdims, bstrides, bbox, bestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 swizzle_for(q.bk), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r1 != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed with %d", (int)r1);
+            tmY = tmA;  // placeholders: the int32 form stores from registers and reads no residual
+            tmR = tmA;
+            p.col_tiles = (q.cols + 255) / 256;
+            p.idesc = (p.idesc & ~((0x3fu << 17) | (0x1fu << 24))) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+        }
+    }
     ProfRec rec{};
     if (g_prof_on) {
         CHXQ_CUDA(cudaEventCreate(&rec.e0));
@@ -404,7 +428,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     if (pool) {
         rc = tc::launch_tc2_bk64_pool(epi_kind, halo, tmA, tmB, tmY, tmR, p, grid, s);
     } else if (pair) {
-        rc = tc::launch_tc3_bk128(epi_kind, q.epi.residual != nullptr, tmA, tmB, tmY, tmR, p, (int)pair_items, s);
+        rc = tc::launch_tc3_bk128(epi_kind, epi_kind != tc::kEpiKInt32 && q.epi.residual != nullptr, tmA, tmB, tmY, tmR, p, (int)pair_items, s);
     } else if (grouped) {
         rc = q.bk == 128 ? tc::launch_tc2_bk128(bn2, epi_kind, q.epi.residual != nullptr, halo, tmA, tmB, tmY, tmR, p, grid, s)
                          : tc::launch_tc2_bk64(bn2, epi_kind, q.epi.residual != nullptr, halo, tmA, tmB, tmY, tmR, p, grid, s);
@@ -438,6 +462,16 @@ extern "C" int chxq_tl_read(long long* host) {
     return (int)cudaMemcpy(host, chxq::g_tl_buf, 3 * 2048 * sizeof(long long), cudaMemcpyDeviceToHost);
 }
 #endif
+
+// Test hooks of the bounded device-side waits (one-tile kernel): the time without progress after which a wait gives up, and the
+// K block whose weight load the producer leaves out (-1: none), so that a test can make a wait run out without faulting anything.
+extern "C" int chxq_tc_test_hooks(int64_t wait_limit_ns, int32_t skip_weight_load_kb) {
+    if (wait_limit_ns < 1000000 || wait_limit_ns > 10000000000ll)
+        return chxq::set_error(CHXQ_ERR_INVALID_ARGUMENT, "chxq_tc_test_hooks: the wait limit must lie between 1 ms and 10 s");
+    chxq::g_wait_limit_ns.store(wait_limit_ns, std::memory_order_relaxed);
+    chxq::g_test_skip_kb.store(skip_weight_load_kb, std::memory_order_relaxed);
+    return CHXQ_OK;
+}
 
 // Number of CTA pairs of the paired tensor-core kernel that the current device keeps resident at once.
 extern "C" int chxq_tc_pair_slots(int32_t* slots) {

@@ -101,14 +101,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
 
 constexpr int kPairBN = 256;  // channels of a pair's block
 
-template <int BK, bool RES>
+template <int BK, bool RES, bool I32 = false>
 struct Tc3Config {
     static constexpr int kTileA = 128 * BK;              // this CTA's 128 positions
     static constexpr int kHalfB = 128 * BK;              // this CTA's half of the 256 weight rows
     static constexpr int kStageBytes = kTileA + kHalfB;
     static constexpr int kHalfOut = 128 * 128;           // one swizzled [128 positions][128 channels] half of the staged output
     static constexpr int kTileOut = 2 * kHalfOut;
-    static constexpr int kBufs = RES ? 3 : 2;            // as in tc_kernel2.cuh
+    static constexpr int kBufs = I32 ? 0 : (RES ? 3 : 2);  // as in tc_kernel2.cuh; int32 accumulators leave straight from registers
     static constexpr int kOutBytes = kBufs * kTileOut;
     static constexpr int kBudget = 208 * 1024;
     static constexpr int kStagesRaw = (kBudget - kOutBytes) / kStageBytes;
@@ -128,10 +128,13 @@ template <int BK, int EPI, bool RES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(640, 1)
 tc_igemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const TcParams p) {
-    using Cfg = Tc3Config<BK, RES>;
+    constexpr bool kInt32 = EPI == kEpiKInt32;  // MatMulInteger / ConvInteger: the exact accumulator (minus the zero-point terms)
+    using Cfg = Tc3Config<BK, RES, kInt32>;
     constexpr int kStages = Cfg::kStages;
     constexpr int BN = kPairBN;
     constexpr bool kFold = EPI == kEpiKU8Fold;
+    static_assert(!(kInt32 && RES), "int32 outputs have no residual tail");
+    constexpr int kBufsDiv = Cfg::kBufs > 0 ? Cfg::kBufs : 1;  // divisor that stays valid where the staging ring does not exist
     extern __shared__ uint8_t smem_raw[];
     // The dynamic shared-memory window starts at the same address in both CTAs of a pair (same kernel, same static usage), so
     // the aligned offsets below are the same in both: descriptors and barrier offsets of the first CTA are valid in the second.
@@ -223,8 +226,8 @@ tc_igemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 int w0, h0, n0;
                 tile_origin(pt, w0, h0, n0);
                 if (RES && is_a) {
-                    const int rb = it % Cfg::kBufs;
-                    if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / Cfg::kBufs) & 1u) ^ 1u, abort_flag, p.status, 5, 0)) break;
+                    const int rb = it % kBufsDiv;
+                    if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / kBufsDiv) & 1u) ^ 1u, abort_flag, p.status, 5, 0)) break;
                     mbar_expect_tx(rfull_bar(rb), Cfg::kTileOut);
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf)
@@ -351,7 +354,7 @@ tc_igemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             const int ct = item % p.col_tiles;
             const int col0 = ct * BN;
-            const int buf = it % Cfg::kBufs;
+            const int buf = it % kBufsDiv;
 
             if (ct != cached_ct) {
                 __syncwarp();
@@ -359,7 +362,10 @@ tc_igemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const int c = col0 + ((j >> 4) * 4 + sub) * 16 + (j & 15);
                     float m = 0.f;
                     uint32_t add = 0u, corr = 0u;
-                    if (c < p.cols) {
+                    if (c < p.cols && kInt32) {
+                        if (p.col_corr) add = 0u - (uint32_t)p.col_scale * (uint32_t)p.col_corr[c];  // activation zero point x sum of the column's weights
+                        if (p.col_mul) corr = (uint32_t)p.col_mul[c];                                   // the column's weight zero point
+                    } else if (c < p.cols) {
                         m = epi_mult(p.epi, c);
                         const int bias = p.epi.bias ? p.epi.bias[c] : 0;
                         if (kFold) {
@@ -380,14 +386,60 @@ tc_igemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 cached_ct = ct;
             }
 
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+            if constexpr (kInt32) {
+                // int32 outputs: every thread owns one output position (row) and writes its sixteen accumulators of a chunk as 64
+                // contiguous bytes, straight from registers.
+                const int pt = (item / p.col_tiles) * 2 + (int)rank;
+                int w0, h0, n0;
+                tile_origin(pt, w0, h0, n0);
+                const int w_l = row % p.Wb, h_l = (row / p.Wb) % p.Hb, n_l = row / (p.Wb * p.Hb);
+                const int wo = w0 + w_l, ho = h0 + h_l, no = n0 + n_l;
+                const bool row_ok = pt < pos_tiles && wo < p.Wo && ho < p.Ho && no < p.No;
+                const int64_t pos = ((int64_t)no * p.Ho + ho) * p.Wo + wo;
+                const uint32_t rowc = (p.row_corr && row_ok) ? (uint32_t)p.row_corr[pos] : 0u;  // sum over the row of (a - za), for the weight zero points
+                const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4, 32);
+                if (!__all_sync(0xffffffffu, got)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int i = 0; i < BN / 64; ++i) {
+                    const int cbase = col0 + (i * 4 + sub) * 16;
+                    if (cbase >= p.cols) continue;  // warp-uniform
+                    uint32_t r[16];
+                    __syncwarp();
+                    tmem_ld_32x32b_x16(taddr + (uint32_t)((i * 4 + sub) * 16), r);
+                    tmem_ld_wait16(r);
+                    const uint4* pa = reinterpret_cast<const uint4*>(s_add + i * 16);
+                    const uint4* pc = reinterpret_cast<const uint4*>(s_corr + i * 16);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 a4 = pa[j], c4 = pc[j];
+                        r[4 * j] += a4.x - c4.x * rowc; r[4 * j + 1] += a4.y - c4.y * rowc;
+                        r[4 * j + 2] += a4.z - c4.z * rowc; r[4 * j + 3] += a4.w - c4.w * rowc;
+                    }
+                    if (!row_ok) continue;
+                    int32_t* yo = static_cast<int32_t*>(p.y) + pos * p.ldc + cbase;
+                    if (p.vec_ok && cbase + 16 <= p.cols) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(yo)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (cbase + j < p.cols) yo[j] = (int32_t)r[j];
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
+                continue;
+            }
             uint8_t* out_buf = smem_out + buf * Cfg::kTileOut;
-            const uint32_t use_phase = (uint32_t)(it / Cfg::kBufs) & 1u;
+            const uint32_t use_phase = (uint32_t)(it / kBufsDiv) & 1u;
             bool got = RES ? mbar_wait(rfull_bar(buf), use_phase, abort_flag, p.status, 6, 32)
                            : mbar_wait(bempty_bar(buf), use_phase ^ 1u, abort_flag, p.status, 7, 32);
             if (got) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4, 32);
             if (!__all_sync(0xffffffffu, got)) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             // One unit: 16 accumulators of chunk ch in registers -> 16 staged bytes (half ch / 8 of the staged tile, 16-byte unit ch % 8).
             auto process = [&](uint32_t (&r)[16], const int i) {
                 const int ch = i * 4 + sub;
@@ -482,14 +534,14 @@ tc_igemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
         }
     } else if (warp == 18) {
-        // ---------------- store warp (both CTAs) ----------------
-        if (lane == 0) {
+        // ---------------- store warp (both CTAs; idle for int32 outputs) ----------------
+        if (lane == 0 && !kInt32) {
             int it = 0;
             for (int item = first_item; item < total_items; item += num_pairs_launched, ++it) {
                 const int ct = item % p.col_tiles;
                 const int pt = (item / p.col_tiles) * 2 + (int)rank;
-                const int buf = it % Cfg::kBufs;
-                if (!mbar_wait(bfull_bar(buf), (uint32_t)(it / Cfg::kBufs) & 1u, abort_flag, p.status, 8, 0)) break;
+                const int buf = it % kBufsDiv;
+                if (!mbar_wait(bfull_bar(buf), (uint32_t)(it / kBufsDiv) & 1u, abort_flag, p.status, 8, 0)) break;
                 uint8_t* out_buf = smem_out + buf * Cfg::kTileOut;
                 if (pt < pos_tiles) {
                     int w0, h0, n0;
@@ -525,7 +577,7 @@ tc_igemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // shared-memory attribute); asked once per device.
 template <int BK, int EPI, bool RES>
 int pair_slots(int* out) {
-    using Cfg = Tc3Config<BK, RES>;
+    using Cfg = Tc3Config<BK, RES, EPI == kEpiKInt32>;
     static std::atomic<int> max_pairs[64] = {};
     int dev = 0;
     CHXQ_CUDA(cudaGetDevice(&dev));
@@ -559,7 +611,7 @@ int pair_slots(int* out) {
 template <int BK, int EPI, bool RES>
 int launch_one3(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p, int items,
                 cudaStream_t s) {
-    using Cfg = Tc3Config<BK, RES>;
+    using Cfg = Tc3Config<BK, RES, EPI == kEpiKInt32>;
     int pairs = 0;
     const int rc = pair_slots<BK, EPI, RES>(&pairs);
     if (rc != CHXQ_OK) return rc;
@@ -574,6 +626,7 @@ int launch_one3(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
 template <int BK>
 int launch_bk3(int epi, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p,
                int items, cudaStream_t s) {
+    if (epi == kEpiKInt32) return res ? CHXQ_ERR_UNSUPPORTED : launch_one3<BK, kEpiKInt32, false>(tmA, tmB, tmY, tmR, p, items, s);
     const int key = (epi == kEpiKU8Fold ? 2 : 0) + (res ? 1 : 0);
     switch (key) {
         case 0: return launch_one3<BK, kEpiKU8, false>(tmA, tmB, tmY, tmR, p, items, s);

@@ -42,6 +42,10 @@ struct TcParams {
     // group is 2 x 2 tiles of 16 x 8 positions and owns 15 x 7 pooled positions (8 x 16 and 7 x 15 with halo tiles).
     // pool_groups_w == 0: no pooling.
     int pool_groups_w, pool_groups_h, pool_wo, pool_ho;
+    // Bounded waits: nanoseconds without progress after which a wait gives up (2 s unless a test shortens it), and, for the test of
+    // that path only, the K block whose weight load the one-tile kernel's producer leaves out (-1: none).
+    unsigned long long wait_limit_ns;
+    int test_skip_kb;
 #ifdef CHXQ_TL
     long long* tl;  // timeline build: [2 roles][512 K blocks][4] clock stamps of CTA 0
 #endif

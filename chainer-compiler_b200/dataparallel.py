@@ -69,6 +69,26 @@ def max_over_ranks(value, device, world):
     return float(t.item())
 
 
+def sharded_matmul_integer(a_local, b, a_zero_point=None, b_zero_point=None, total_rows=None, world=1, rank=0, gather=True, matmul=None):
+    """MatMulInteger (runtime/ops/quantize.cc:96-114) with the rows of A sharded over the ranks and B replicated: every output row
+    depends on one row of A only, so each rank computes Y[begin:end] = (A[begin:end] - za) . (B - zb) for its slice
+    shard_bounds(total_rows, world, rank) with no exchange, and the optional all-gather of the int32 rows is the only traffic.
+    a_local: this rank's rows; total_rows: rows of the whole A (default: a_local's, i.e. one rank).  matmul: the single-GPU op
+    (default ops.MatMulInteger; the CPU-rank tests pass a stand-in).  Returns the whole Y on every rank (gather=True) or this
+    rank's rows."""
+    if matmul is None:
+        from . import ops
+        matmul = ops.MatMulInteger
+    total_rows = a_local.shape[0] if total_rows is None else int(total_rows)
+    begin, end = shard_bounds(total_rows, world, rank)
+    if a_local.shape[0] != end - begin:
+        raise ValueError("rank %d holds %d rows of A, its shard of %d rows over %d ranks is [%d, %d)" % (rank, a_local.shape[0], total_rows, world, begin, end))
+    y_local = matmul(a_local, b, a_zero_point, b_zero_point)
+    if not gather or world == 1:
+        return y_local
+    return gather_ragged(y_local, total_rows, world, rank)
+
+
 def gpu_numa_cpus(device_index):
     """CPUs of the NUMA node the GPU hangs off (from sysfs), or None when the machine has one node or the answer is unknown."""
     try:

@@ -22,6 +22,12 @@ extern "C" {
  * tests. */
 int chxq_tc_variant(int32_t variant);
 
+/* The bounded device-side waits of the tensor-core kernels give up after wait_limit_ns without progress (default 2 s; 1 ms ..
+ * 10 s here), set the device status word (chxq_device_status -> CHXQ_ERR_DEVICE_TIMEOUT), and the CTA tears down in order:
+ * nothing traps or spins on.  skip_weight_load_kb >= 0 makes the one-tile kernel's producer leave out the weight load of that K
+ * block, so that its stage never fills: the way a test makes a wait run out.  (-1: off, the default.)  Process-wide. */
+int chxq_tc_test_hooks(int64_t wait_limit_ns, int32_t skip_weight_load_kb);
+
 /* Number of CTA pairs (clusters of two) of the paired tensor-core kernel that the current device keeps resident at once
  * (cudaOccupancyMaxActiveClusters): the kernel's grid is twice this, or smaller for small problems. */
 int chxq_tc_pair_slots(int32_t* slots);

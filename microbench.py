@@ -258,7 +258,52 @@ def secondary(dev):
     return run({"quant", "eltwise", "gemm", "mobilenet", "depthwise", "mlp", "nchw"}, dev, mobilenet_cuda_cores=False)
 
 
+def gemm_sharded():
+    """The MatMulInteger sweep with the rows of A sharded over the ranks of a torchrun job (B replicated, no gather inside the
+    timed region: the product stays sharded, as a following row-wise operator would consume it); rank 0 prints one line per
+    size with the aggregate TOPS (max over ranks of the CUDA-event time).  Run as
+        python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 microbench.py gemm_sharded"""
+    import torch.distributed as dist
+    entry.load_package()
+    from chainer_compiler_b200 import dataparallel as dp, ops
+    rank, local_rank, world = dp.init()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for S in (4096, 8192, 16384):
+        b0, e0 = dp.shard_bounds(S, world, rank)
+        gen = torch.Generator(device=dev).manual_seed(S)  # the same B on every rank
+        b = torch.randint(-127, 128, (S, S), dtype=torch.int8, device=dev, generator=gen)
+        a = torch.randint(0, 256, (e0 - b0, S), dtype=torch.uint8, device=dev)
+        za = torch.tensor([128], dtype=torch.uint8, device=dev)
+        fn = lambda: dp.sharded_matmul_integer(a, b, za, None, total_rows=S, world=world, rank=rank, gather=False)  # noqa: E731
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(5):
+            flush.zero_()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+            e_a, e_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e_a.record()
+            fn()
+            e_b.record()
+            torch.cuda.synchronize(dev)
+            ts.append(dp.max_over_ranks(e_a.elapsed_time(e_b), dev, world))
+        ms = float(np.median(ts))
+        if rank == 0:
+            print(json.dumps({"bench": "MatMulInteger %d^3, rows of A sharded over %d GPU(s), B replicated" % (S, world), "ms": ms,
+                              "tops": 2 * S ** 3 / ms / 1e9, "n_gpus": world}), flush=True)
+        del a, b
+    ops.device_status()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
+    if "gemm_sharded" in sys.argv[1:]:
+        return gemm_sharded()
     if not torch.cuda.is_available():
         raise SystemExit("microbench.py needs a CUDA device: this package has no CPU path")
     dev = torch.device("cuda:0")

@@ -45,6 +45,22 @@ WORKER = textwrap.dedent("""
     full = torch.arange(7 * classes, dtype=torch.float32).reshape(7, classes)
     b, e = dp.shard_bounds(7, world, rank)
     assert torch.equal(dp.gather_ragged(full[b:e].clone(), 7, world, rank), full)
+    # MatMulInteger with the rows of A sharded (B replicated, int32 rows gathered): ragged 7 rows over 2 ranks
+    g = torch.Generator().manual_seed(0)
+    A = torch.randint(0, 256, (7, 12), generator=g, dtype=torch.int32)
+    B = torch.randint(-127, 128, (12, 5), generator=g, dtype=torch.int32)
+    za = torch.tensor([128], dtype=torch.int32)
+    cpu_mm = lambda a, b, za_, zb_: ((a - za_) @ b).to(torch.int32)   # stand-in for the GPU op: the host logic is what runs here
+    b7, e7 = dp.shard_bounds(7, world, rank)
+    Y = dp.sharded_matmul_integer(A[b7:e7], B, za, None, total_rows=7, world=world, rank=rank, gather=True, matmul=cpu_mm)
+    assert torch.equal(Y, ((A - 128) @ B).to(torch.int32))
+    Yl = dp.sharded_matmul_integer(A[b7:e7], B, za, None, total_rows=7, world=world, rank=rank, gather=False, matmul=cpu_mm)
+    assert torch.equal(Yl, Y[b7:e7])
+    try:
+        dp.sharded_matmul_integer(A, B, za, None, total_rows=7, world=world, rank=rank, matmul=cpu_mm)
+        raise SystemExit("a shard of the wrong size was accepted")
+    except ValueError:
+        pass
     # timing rule: the slowest rank's time is what every rank reports
     assert dp.max_over_ranks(1.0 + rank, torch.device("cpu"), world) == 2.0
     dist.barrier()

@@ -271,3 +271,51 @@ def test_cta_pair_kernel(pkg, ops, orc, dev, N, cin, cout, H, k, stride, pad, re
             assert np.array_equal(got[6], want)
     finally:
         _lib.check(L.chxq_tc_variant(0))
+
+
+@pytest.mark.parametrize("M,N,K,a_dt,b_dt,za_mode,zb_mode", [
+    (300, 512, 384, np.uint8, np.int8, "scalar", None),     # ragged rows (3 position tiles: the last pair has one real tile)
+    (256, 320, 128, np.uint8, np.int8, "vec", "vec"),       # ragged 256-column block, vector zero points on both sides, one K tile
+    (1024, 256, 1024, np.int8, np.uint8, None, "scalar"),   # signed left operand, unsigned right operand with a zero point
+    (130, 1000, 256, np.uint8, np.uint8, "vec", None),      # N not a multiple of 16: scalar stores
+])
+def test_matmul_integer_on_cta_pairs(pkg, ops, orc, dev, M, N, K, a_dt, b_dt, za_mode, zb_mode):
+    """MatMulInteger on the CTA-pair kernel (int32 accumulators stored from registers), forced on, bit-exact against the oracle
+    and equal to the one-tile kernel."""
+    from chainer_compiler_b200 import _lib
+    rng = np.random.default_rng(M + N + K)
+    ia, ib = np.iinfo(a_dt), np.iinfo(b_dt)
+    a = rng.integers(ia.min, ia.max + 1, (M, K)).astype(a_dt)
+    b = rng.integers(ib.min, ib.max + 1, (K, N)).astype(b_dt)
+    za = None if za_mode is None else (rng.integers(ia.min, ia.max + 1, K).astype(a_dt) if za_mode == "vec" else np.array([ia.min + 128], a_dt))
+    zb = None if zb_mode is None else (rng.integers(ib.min, ib.max + 1, N).astype(b_dt) if zb_mode == "vec" else np.array([ib.min + 100], b_dt))
+    want = orc.matmul_integer(a, b, za, zb)
+    L = pkg.lib()
+    tt = lambda v: None if v is None else torch.from_numpy(v).to(dev)  # noqa: E731
+    try:
+        for variant in (7, 6):
+            _lib.check(L.chxq_tc_variant(variant))
+            y = ops.MatMulInteger(tt(a), tt(b), tt(za), tt(zb), path=ops.PATH_TENSOR)
+            ops.device_status()
+            assert np.array_equal(y.cpu().numpy(), want), variant
+    finally:
+        _lib.check(L.chxq_tc_variant(0))
+
+
+def test_conv_integer_on_cta_pairs(pkg, ops, orc, dev):
+    """ConvInteger with packed weights on the CTA-pair kernel: 3 x 3 with padding and an activation zero point of zero, and a
+    1 x 1 with an activation zero point (the column-correction term)."""
+    from chainer_compiler_b200 import _lib
+    rng = np.random.default_rng(8)
+    L = pkg.lib()
+    try:
+        _lib.check(L.chxq_tc_variant(7))
+        for (N, C, H, M, k, pad, zx) in ((4, 128, 14, 256, 3, 1, 0), (3, 256, 10, 512, 1, 0, 131)):
+            x = rng.integers(0, 256, (N, C, H, H), dtype=np.uint8)
+            w = rng.integers(-127, 128, (M, C, k, k)).astype(np.int8)
+            pk = ops.PackedConv(_t(w, dev), None, x.shape, strides=(1, 1), pads=(pad, pad))
+            y = ops.ConvIntegerPacked(_t(x, dev, True), pk, np.uint8(zx))
+            ops.device_status()
+            assert np.array_equal(y.cpu().numpy(), orc.conv_integer(x, w, zx, None, (1, 1), (pad, pad)))
+    finally:
+        _lib.check(L.chxq_tc_variant(0))
