@@ -289,7 +289,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
         // of one image.
         // by default for grouped / depthwise layers (measured: MobileNetV2 -7 %), on request (variant 3) for dense ones (ResNet-50's 3x3
         // layers are faster without: the halo planes are 16-byte TMA rows, and TMA moves about one row per clock)
-        halo = !pool && (g_variant >= 3 || (g_variant == 0 && q.group_cols > 0)) && q.KH * q.KW > 1 && q.KH <= 3 && q.KW <= 3 && p.sw == 1 && p.sh == 1 &&
+        halo = !pool && ((g_variant >= 3 && g_variant <= 5) || (g_variant == 0 && q.group_cols > 0)) && q.KH * q.KW > 1 && q.KH <= 3 && q.KW <= 3 && p.sw == 1 && p.sh == 1 &&
                (q.bk == 64 || (q.bk == 128 && bn2 == 128 && q.epi.residual == nullptr)) && q.a_row_bytes == 0 && q.Wo >= 8 && q.Ho >= 8;
         // Space-to-depth stems: the A map is rows of 16-byte blocks read through overlapping 64-byte windows (a_cs 16 < C 64), i.e. a
         // KH x 4 stride-1 convolution over a 16-byte-pixel map.  As a halo tile every block is fetched once per tile instead of once per
@@ -330,7 +330,7 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
                  !(q.epi.residual != nullptr && q.KH * q.KW * (q.c_pad / q.bk) < 4)));
         if (pair) bn2 = 128;  // the maps below are those of 128-channel blocks: one CTA's half of the weights, halves of the staged output
         // Chosen whenever there is at least one group per SM; smaller problems spread better as single tiles.
-        grouped = pair || pool || halo || g_variant >= 2 || groups >= (int64_t)num_sms();
+        grouped = pair || pool || halo || (g_variant >= 2 && g_variant <= 5) || groups >= (int64_t)num_sms();
         if (halo) {
             // space-to-depth: the block map itself, [N][rows][a_row_bytes / 16 blocks][16 bytes]
             const cuuint64_t dims[4] = {s2d_halo ? 16u : (cuuint64_t)q.C, s2d_halo ? (cuuint64_t)(q.a_row_bytes / 16) : (cuuint64_t)q.W, (cuuint64_t)q.H,

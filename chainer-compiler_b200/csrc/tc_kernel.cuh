@@ -67,6 +67,18 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while the kernel
+// before it in the stream is still running.  launch_dependents lets the next kernel's CTAs be scheduled as soon as this
+// kernel's CTAs leave their SMs; dependency_wait blocks until the previous kernel has completed and its writes are visible.
+// Everything a CTA does before dependency_wait (barrier initialisation, tensor-memory allocation) overlaps the previous
+// kernel's tail; nothing before it may touch global memory that the previous kernel writes or reads.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
 // Bounded wait.  Returns false when the CTA is aborting (either this wait expired or another did).

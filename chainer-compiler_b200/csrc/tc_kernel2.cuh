@@ -22,6 +22,8 @@
 // staging tiles are multi-buffered as well.  Every wait is bounded exactly as in tc_kernel.cuh.
 #pragma once
 
+#include <utility>
+
 #include "tc_kernel.cuh"
 
 namespace chxq {
@@ -218,6 +220,8 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    pdl_launch_dependents();  // the next kernel's CTAs may take this SM as soon as this CTA leaves it
+    pdl_dependency_wait();    // from here on the previous kernel's output (this kernel's input) is complete and visible
 
     static_assert(!POOL || (BN == 64 && !RES), "fused pooling: 64-channel blocks without a residual");
     using PG = PoolGeom<HALO>;
@@ -703,6 +707,23 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
+// Launch with the programmatic-serialization attribute: the kernel may begin (up to its dependency wait) while the previous
+// kernel in the stream drains.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <int BN, int BK, int EPI, bool RES, bool HALO, bool POOL = false>
 int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p, int grid,
                 cudaStream_t s) {
@@ -715,8 +736,8 @@ int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
         CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
-    tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL><<<grid, 640, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
-    CHXQ_LAUNCH_CHECK();
+    CHXQ_CUDA(launch_pdl(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL>, grid, 640, Cfg::kSmemBytes, s, tmA, tmB, tmY, tmR, p));
+    count_launch(1);
     return CHXQ_OK;
 }
 

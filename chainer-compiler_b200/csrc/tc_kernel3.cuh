@@ -186,6 +186,8 @@ tc_igemm3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     cluster_sync_all();  // the partner's barriers are initialised before anything of this CTA can signal them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    pdl_launch_dependents();  // the next kernel's CTAs may take this SM as soon as this CTA leaves it
+    pdl_dependency_wait();    // from here on the previous kernel's output (this kernel's input) is complete and visible
 
     const int pos_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
     const int pos_pairs = (pos_tiles + 1) / 2;
@@ -616,8 +618,8 @@ int launch_one3(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
     const int rc = pair_slots<BK, EPI, RES>(&pairs);
     if (rc != CHXQ_OK) return rc;
     const int launch_pairs = items < pairs ? items : pairs;
-    tc_igemm3_kernel<BK, EPI, RES><<<2 * launch_pairs, 640, Cfg::kSmemBytes, s>>>(tmA, tmB, tmY, tmR, p);
-    CHXQ_LAUNCH_CHECK();
+    CHXQ_CUDA(launch_pdl(tc_igemm3_kernel<BK, EPI, RES>, 2 * launch_pairs, 640, Cfg::kSmemBytes, s, tmA, tmB, tmY, tmR, p));
+    count_launch(1);
     return CHXQ_OK;
 }
 

@@ -381,7 +381,7 @@ def test_grouped_tensor_core_kernel(pkg, ops, orc, dev, grouped_kernel, N, C, H,
     ]
     for c in cases:
         ref = run(1, c["zx"], c["zy"], **c["kw"])
-        for variant in (2, 3, 4, 7):  # 3, 4: halo tiles where the geometry allows them (3x3 and smaller, stride 1): planes, swizzled; 7: CTA pairs where eligible
+        for variant in (2, 3, 4, 7, 6):  # 3, 4: halo tiles where the geometry allows them (3x3 and smaller, stride 1): planes, swizzled; 7: CTA pairs where eligible; 6: as the default choice but never CTA pairs
             got = run(variant, c["zx"], c["zy"], **c["kw"])
             assert torch.equal(got, ref), (variant, c)
     acc = orc.conv_integer(x, w, 0, wz, (stride, stride), (pad, pad))
