@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--sustain-s", type=float, default=2.0, help="seconds of the sustained loop that follows the timed region")
     ap.add_argument("--tc-variant", type=int, default=0, choices=[0, 1, 2, 3, 4, 5, 6, 7],
                     help="tensor-core kernel choice (chxq_tc_variant): 0 by shape, 1 one tile per step, 2 grouped tiles")
+    ap.add_argument("--chain", action="store_true", help="run conv2 and conv3 of every bottleneck as one kernel (chxq_qlinear_conv_chain_packed)")
     ap.add_argument("--exact-requant", action="store_true",
                     help="requantize in the reference's operation order (multiply by x_scale*w_scale, divide by y_scale) instead of one "
                          "folded multiplier per channel")
@@ -278,6 +279,7 @@ def run_chxq(args):
 
     # Same seeded weights on every rank; every rank works on its own seeded images (weak scaling: 256 images per GPU).
     net = models.ResNet50Int8(batch=args.batch, device=dev, seed=0, image=IMAGE)
+    net.use_chain = args.chain
     fold = not args.exact_requant
     gop_per_image = 2.0 * net.macs_per_image() / 1e9
     eng = dp.InferenceEngine(net, world, fold=fold, rank=rank)

@@ -98,6 +98,8 @@ SIGNATURES = {
     "chxq_conv_prepack_bytes": (_sz, [_c.POINTER(ConvGeom)]),
     "chxq_conv_prepack": (_c.c_int, [_vp, _c.POINTER(ConvGeom), _vp, _i64, _vp, _sz, _c.POINTER(_i32), _vp]),
     "chxq_qlinear_conv_packed": (_c.c_int, [_vp, _vp, _c.POINTER(ConvGeom), _c.POINTER(QConvParams), _i32, _vp, _vp, _sz, _vp]),
+    "chxq_qlinear_conv_chain_packed": (_c.c_int, [_vp, _vp, _c.POINTER(ConvGeom), _c.POINTER(QConvParams), _i32, _vp, _c.POINTER(ConvGeom),
+                                                 _c.POINTER(QConvParams), _i32, _vp, _vp]),
     "chxq_quantize_qlinear_conv_packed": (_c.c_int, [_vp, _i32, _vp, _c.POINTER(ConvGeom), _c.POINTER(QConvParams), _i32, _vp, _vp, _sz, _vp]),
     "chxq_qlinear_conv_maxpool_packed": (_c.c_int, [_vp, _i32, _i32, _vp, _c.POINTER(ConvGeom), _c.POINTER(QConvParams), _i32, _i32, _i32, _i32, _i32, _vp,
                                                    _vp, _sz, _vp]),

@@ -255,12 +255,12 @@ __global__ void __launch_bounds__(256) s2d_repack_kernel(
                         const float4 f = __ldcs(reinterpret_cast<const float4*>(xf + off));
                         bool general = !qz.dv.fast;  // same arithmetic as quantize_vec16_kernel: division by a constant, add-based rounding
                         if (!general) {
-                            const float t0 = qdiv_unguarded(f.x, qz.dv, &general), t1 = qdiv_unguarded(f.y, qz.dv, &general);
-                            const float t2 = qdiv_unguarded(f.z, qz.dv, &general), t3 = qdiv_unguarded(f.w, qz.dv, &general);
                             if (qz.round_mode == 0) {
-                                px[0] = quantize_u8_up_bits(t0, qz.zp_f); px[1] = quantize_u8_up_bits(t1, qz.zp_f);
-                                px[2] = quantize_u8_up_bits(t2, qz.zp_f); px[3] = quantize_u8_up_bits(t3, qz.zp_f);
+                                const uint32_t packed = quantize4_u8_up(f, make_qdiv8(qz.dv, qz.zp_f), &general);
+                                px[0] = packed & 0xffu; px[1] = (packed >> 8) & 0xffu; px[2] = (packed >> 16) & 0xffu; px[3] = packed >> 24;
                             } else {
+                                const float t0 = qdiv_unguarded(f.x, qz.dv, &general), t1 = qdiv_unguarded(f.y, qz.dv, &general);
+                                const float t2 = qdiv_unguarded(f.z, qz.dv, &general), t3 = qdiv_unguarded(f.w, qz.dv, &general);
                                 px[0] = quantize_u8_rne_bits(t0, qz.zp_f); px[1] = quantize_u8_rne_bits(t1, qz.zp_f);
                                 px[2] = quantize_u8_rne_bits(t2, qz.zp_f); px[3] = quantize_u8_rne_bits(t3, qz.zp_f);
                             }
@@ -509,12 +509,16 @@ int pack_weights(const void* w, const chxq_conv_geom& g, const TcConvPlan& pl, c
 // Runs a planned convolution on the tensor-core kernel from a packed weight blob.
 int conv_tc_run(
         const void* x, const uint8_t* blob, const chxq_conv_geom& g, const TcConvPlan& pl, int x_zp, bool zw_zero, const EpiArgs& epi, void* y,
-        uint8_t* scratch, size_t scratch_bytes, cudaStream_t s, const S2dQuant* quant_in = nullptr, const PoolSpec* pool = nullptr) {
+        uint8_t* scratch, size_t scratch_bytes, cudaStream_t s, const S2dQuant* quant_in = nullptr, const PoolSpec* pool = nullptr,
+        TcProblem* plan_only = nullptr) {
     const ConvWs L = conv_ws_layout(g, pl);
     const int taps = g.KH * g.KW;
     const int64_t rows = (int64_t)g.N * g.Ho * g.Wo;
-    if (rows == 0) return CHXQ_OK;
+    if (rows == 0 && !plan_only) return CHXQ_OK;
     const bool im2col = needs_im2col(g, pl, x_zp);
+    // plan_only: describe the problem without launching anything -- only for layers that need no pass in front of the kernel
+    if (plan_only && (pl.path != kTcDirect || im2col || !zw_zero || rows == 0))
+        return set_error(CHXQ_ERR_UNSUPPORTED, "convolution: this layer needs a pass in front of the tensor-core kernel");
     if (g.group > 1 && (im2col || !zw_zero))
         return set_error(CHXQ_ERR_UNSUPPORTED,
                          "grouped convolution on the tensor-core path needs zero weight zero points and, with padding, a zero activation zero point");
@@ -600,6 +604,10 @@ int conv_tc_run(
             return set_error(CHXQ_ERR_UNSUPPORTED, "fused max pooling: the convolution must run on the direct or space-to-depth tensor-core path");
         p.Wb = 16; p.Hb = 8; p.Nb = 1;  // the pooling form's tiles, whatever the output extents (edges are masked)
         p.pool_ho = pool->ho; p.pool_wo = pool->wo;
+    }
+    if (plan_only) {
+        *plan_only = p;
+        return CHXQ_OK;
     }
     return launch_tc_igemm(p, s);
 }
@@ -1046,6 +1054,42 @@ extern "C" int chxq_qlinear_conv_packed(
     if (rc != CHXQ_OK) return rc;
     return conv_tc_run(x, static_cast<const uint8_t*>(packed), *g, pl, p->x_zero_point, (packed_flags & 2) != 0, epi, y,
                        static_cast<uint8_t*>(workspace), workspace_bytes, as_stream(stream));
+}
+
+// QLinearConv (g1, p1) followed by the 1x1 / stride-1 QLinearConv (g2, p2) that is its only reader, as one kernel: the map between
+// them is requantized tile by tile into shared memory and never written.
+extern "C" int chxq_qlinear_conv_chain_packed(
+        const void* x, const void* packed1, const chxq_conv_geom* g1, const chxq_qconv_params* p1, int32_t packed_flags1, const void* packed2,
+        const chxq_conv_geom* g2, const chxq_qconv_params* p2, int32_t packed_flags2, void* y, void* stream) {
+    const char* op = "QLinearConv+QLinearConv(packed)";
+    TcConvPlan pl1, pl2;
+    int rc = packed_common(op, x, packed1, g1, packed_flags1, &pl1);
+    if (rc != CHXQ_OK) return rc;
+    rc = packed_common(op, x, packed2, g2, packed_flags2, &pl2);
+    if (rc != CHXQ_OK) return rc;
+    CHXQ_CHECK_ARG(y != nullptr && p1 != nullptr && p2 != nullptr, "%s: null argument", op);
+    CHXQ_CHECK_ARG(g2->KH == 1 && g2->KW == 1 && g2->stride_h == 1 && g2->stride_w == 1 && g2->pad_top == 0 && g2->pad_left == 0 &&
+                           g2->pad_bottom == 0 && g2->pad_right == 0 && g2->group == 1,
+                   "%s: the second convolution must be 1x1, stride 1, without padding or groups", op);
+    CHXQ_CHECK_ARG(g2->N == g1->N && g2->C == g1->M && g2->H == g1->Ho && g2->W == g1->Wo, "%s: the second convolution does not read the first one's output", op);
+    CHXQ_CHECK_ARG(g2->x_dtype == CHXQ_UINT8 && p1->y_dtype == CHXQ_UINT8, "%s: the map between the convolutions must be uint8", op);
+    CHXQ_CHECK_ARG(p2->x_scale == p1->y_scale && p2->x_zero_point == p1->y_zero_point,
+                   "%s: the second convolution's input scale and zero point must be the first one's output scale and zero point", op);
+    CHXQ_CHECK_ARG(p1->residual == nullptr, "%s: only the second convolution may carry a residual tail", op);
+    if (g1->x_layout != CHXQ_NHWC || g2->y_layout != CHXQ_NHWC || (packed_flags1 & 2) == 0 || (packed_flags2 & 2) == 0 || p1->x_zero_point != 0 ||
+        p2->x_zero_point != 0 || !p1->fold_scales || !p2->fold_scales)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "%s: needs NHWC maps, zero weight and activation zero points and folded requantizations", op);
+    EpiArgs e1, e2;
+    rc = fill_requant(op, p1, g1, &e1);
+    if (rc != CHXQ_OK) return rc;
+    rc = fill_requant(op, p2, g2, &e2);
+    if (rc != CHXQ_OK) return rc;
+    TcProblem q1, q2;
+    rc = conv_tc_run(x, static_cast<const uint8_t*>(packed1), *g1, pl1, 0, true, e1, /*y=*/y, nullptr, 0, as_stream(stream), nullptr, nullptr, &q1);
+    if (rc != CHXQ_OK) return rc;
+    rc = conv_tc_run(x, static_cast<const uint8_t*>(packed2), *g2, pl2, 0, true, e2, y, nullptr, 0, as_stream(stream), nullptr, nullptr, &q2);
+    if (rc != CHXQ_OK) return rc;
+    return launch_tc_chain_igemm(q1, q2, as_stream(stream));
 }
 
 // QuantizeLinear(x; p->x_scale, p->x_zero_point, uint8, reference rounding or round-half-to-even) fused into the packed

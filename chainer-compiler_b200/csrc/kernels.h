@@ -80,6 +80,8 @@ struct TcProblem {
 };
 
 int launch_tc_igemm(const TcProblem& p, cudaStream_t s);
+// q1 followed by the 1x1 convolution q2 as one kernel (the map between them is never written); CHXQ_ERR_UNSUPPORTED when the pair has none.
+int launch_tc_chain_igemm(const TcProblem& q1, const TcProblem& q2, cudaStream_t s);
 
 // Tensor-core planning shared by pre-packing and execution.
 enum TcConvPath : int { kTcNone = 0, kTcDirect = 1, kTcIm2col = 2, kTcS2d = 3 };

@@ -21,6 +21,55 @@ __device__ __forceinline__ int cvt_rne_sat_u8(float t) {
     return (int)q;
 }
 
+// ---- packed pairs of floats (one 64-bit register) and the saturating scalar forms -----------------------------------
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ float lo_of(uint64_t v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi_of(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
+__device__ __forceinline__ uint64_t add_rm_x2(uint64_t a, uint64_t b) {  // round toward minus infinity
+    uint64_t d;
+    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t sub_x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul_x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma_x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma_rm_x2(uint64_t a, uint64_t b, uint64_t c) {  // round toward minus infinity
+    uint64_t d;
+    asm("fma.rm.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {  // clamp(fma(a, b, c), 0, 1)
+    float d;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float add_sat(float a, float b) {
+    float d;
+    asm("add.rn.sat.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+
 // Division by a scale that is constant for a whole kernel, without the per-element reciprocal of the general IEEE
 // sequence: q0 = x * r with r = RN(1/s) from the host, then two residual corrections q <- fma(fma(-q, s, x), r, q).
 // After the first correction the quotient is faithful; the second, from an exact residual, makes it the correctly
@@ -71,6 +120,41 @@ __device__ __forceinline__ float qdiv(float x, const QDiv& d) {
 __device__ __forceinline__ uint32_t quantize_u8_up_bits(float t, float zp_f) {
     t = __fadd_rn(__fadd_rn(t, zp_f), 0.5f);  // adding a zero zero point is exact
     return __float_as_uint(__fadd_rd(fminf(fmaxf(t, 0.f), 255.5f), 8388608.f)) & 0xffu;
+}
+
+// Four uint8 round-half-up quantizations at once, bit-identical to quantize_u8_up_bits(qdiv_unguarded(x)) per element, with
+// half the arithmetic instructions: the division runs on packed pairs (mul / fma .f32x2) and scaled by 2^-8 (divisor 256 s,
+// reciprocal r / 256 -- powers of two, so every intermediate is the unscaled one times 2^-8 exactly), so that the lower clamp
+// is the .sat of the add of the rounding half, the upper clamp one min against 255.5 / 256, and the floor an add toward minus
+// infinity against 2^15 (whose ulp is 2^-8): the byte is the low 8 bits of that sum.  *needs_general is raised when a
+// quotient is NaN or >= 1e18 in magnitude, as in qdiv_unguarded.
+struct QDiv8 {
+    uint64_t s2, r2, zp2;  // packed {256 s, 256 s}, {r / 256, r / 256}, {zp / 256, zp / 256}
+};
+__device__ __forceinline__ QDiv8 make_qdiv8(const QDiv& d, float zp_f) {
+    QDiv8 o;
+    const float s8 = __fmul_rn(d.s, 256.f), r8 = __fmul_rn(d.r, 0.00390625f), z8 = __fmul_rn(zp_f, 0.00390625f);
+    o.s2 = pack2(-s8, -s8);
+    o.r2 = pack2(r8, r8);
+    o.zp2 = pack2(z8, z8);
+    return o;
+}
+__device__ __forceinline__ uint32_t quantize4_u8_up(const float4 v, const QDiv8& d, bool* needs_general) {
+    const uint64_t xa = pack2(v.x, v.y), xb = pack2(v.z, v.w);
+    const uint64_t q0a = mul_x2(xa, d.r2), q0b = mul_x2(xb, d.r2);
+    uint64_t qa = fma_x2(fma_x2(q0a, d.s2, xa), d.r2, q0a), qb = fma_x2(fma_x2(q0b, d.s2, xb), d.r2, q0b);
+    qa = fma_x2(fma_x2(qa, d.s2, xa), d.r2, qa);
+    qb = fma_x2(fma_x2(qb, d.s2, xb), d.r2, qb);
+    const float lim = 3.90625e15f;  // 1e18 / 256
+    *needs_general = *needs_general || !(fabsf(lo_of(q0a)) < lim) || !(fabsf(hi_of(q0a)) < lim) || !(fabsf(lo_of(q0b)) < lim) ||
+                     !(fabsf(hi_of(q0b)) < lim);
+    const uint64_t ua = add_x2(qa, d.zp2), ub = add_x2(qb, d.zp2);
+    const float hi = 0.998046875f;  // 255.5 / 256
+    const float t0 = fminf(add_sat(lo_of(ua), 0.001953125f), hi), t1 = fminf(add_sat(hi_of(ua), 0.001953125f), hi);
+    const float t2 = fminf(add_sat(lo_of(ub), 0.001953125f), hi), t3 = fminf(add_sat(hi_of(ub), 0.001953125f), hi);
+    const uint64_t m2 = pack2(32768.f, 32768.f);
+    const uint64_t fa = add_rm_x2(pack2(t0, t1), m2), fb = add_rm_x2(pack2(t2, t3), m2);
+    return __byte_perm(__byte_perm((uint32_t)fa, (uint32_t)(fa >> 32), 0x0040), __byte_perm((uint32_t)fb, (uint32_t)(fb >> 32), 0x0040), 0x5410);
 }
 
 // uint8, round-half-to-even on a pre-divided value, conversion-free: saturate(rint(t) + zp).  (t + 1.5 * 2^23) - 1.5 * 2^23

@@ -56,6 +56,7 @@ template <bool kSigned, int kMode>
 __global__ void __launch_bounds__(kThreads) quantize_vec16_kernel(
         const float4* __restrict__ x, int64_t n4, float scale, QDiv dv, float zp_f, int has_zp, int round_mode, uint32_t* __restrict__ y) {
     const int64_t step = (int64_t)gridDim.x * blockDim.x * 4;
+    const QDiv8 dv8 = make_qdiv8(dv, zp_f);
     for (int64_t base = (int64_t)blockIdx.x * blockDim.x * 4 + threadIdx.x; base < n4; base += step) {
         float4 v[4];
 #pragma unroll
@@ -67,17 +68,23 @@ __global__ void __launch_bounds__(kThreads) quantize_vec16_kernel(
         for (int j = 0; j < 4; ++j) {
             const int64_t g = base + (int64_t)j * blockDim.x;
             uint32_t q0, q1, q2, q3;
-            if (kMode == 0 || kMode == 2) {
+            if (kMode == 0) {
                 bool general = false;  // one magnitude test for the four quotients; the rare group that fails is redone
+                const uint32_t packed = quantize4_u8_up(v[j], dv8, &general);
+                if (!general) {
+                    if (g < n4) __stcs(y + g, packed);
+                    continue;
+                }
+                q0 = (uint32_t)quantize_one<false>(v[j].x, scale, zp_f, has_zp != 0, round_mode);
+                q1 = (uint32_t)quantize_one<false>(v[j].y, scale, zp_f, has_zp != 0, round_mode);
+                q2 = (uint32_t)quantize_one<false>(v[j].z, scale, zp_f, has_zp != 0, round_mode);
+                q3 = (uint32_t)quantize_one<false>(v[j].w, scale, zp_f, has_zp != 0, round_mode);
+            } else if (kMode == 2) {
+                bool general = false;
                 const float t0 = qdiv_unguarded(v[j].x, dv, &general), t1 = qdiv_unguarded(v[j].y, dv, &general);
                 const float t2 = qdiv_unguarded(v[j].z, dv, &general), t3 = qdiv_unguarded(v[j].w, dv, &general);
-                if (kMode == 0) {
-                    q0 = quantize_u8_up_bits(t0, zp_f); q1 = quantize_u8_up_bits(t1, zp_f);
-                    q2 = quantize_u8_up_bits(t2, zp_f); q3 = quantize_u8_up_bits(t3, zp_f);
-                } else {
-                    q0 = quantize_u8_rne_bits(t0, zp_f); q1 = quantize_u8_rne_bits(t1, zp_f);
-                    q2 = quantize_u8_rne_bits(t2, zp_f); q3 = quantize_u8_rne_bits(t3, zp_f);
-                }
+                q0 = quantize_u8_rne_bits(t0, zp_f); q1 = quantize_u8_rne_bits(t1, zp_f);
+                q2 = quantize_u8_rne_bits(t2, zp_f); q3 = quantize_u8_rne_bits(t3, zp_f);
                 if (general) {
                     q0 = (uint32_t)quantize_one<false>(v[j].x, scale, zp_f, has_zp != 0, round_mode);
                     q1 = (uint32_t)quantize_one<false>(v[j].y, scale, zp_f, has_zp != 0, round_mode);

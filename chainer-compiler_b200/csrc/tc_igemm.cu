@@ -234,8 +234,8 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     p.epi = q.epi;
     p.y = q.y;
 #ifdef CHXQ_TL
-    if (!g_tl_buf) cudaMalloc(&g_tl_buf, 3 * 2048 * sizeof(long long));
-    cudaMemsetAsync(g_tl_buf, 0, 3 * 2048 * sizeof(long long), s);
+    if (!g_tl_buf) cudaMalloc(&g_tl_buf, 5 * 2048 * sizeof(long long));
+    cudaMemsetAsync(g_tl_buf, 0, 5 * 2048 * sizeof(long long), s);
     p.tl = g_tl_buf;
 #endif
     p.wait_limit_ns = (unsigned long long)g_wait_limit_ns.load(std::memory_order_relaxed);
@@ -446,6 +446,114 @@ int launch_tc_igemm(const TcProblem& q, cudaStream_t s) {
     return rc;
 }
 
+// Two convolutions as one kernel (tc_kernel4.cuh): q1 is any direct-path convolution with 64, 128 or 256 output channels and a folded
+// uint8 requantization, q2 the 1x1 / stride-1 convolution that is its only reader (q2.a is not used: the intermediate map stays in
+// shared memory).  CHXQ_ERR_UNSUPPORTED (without an error message being an error: the caller then runs the two layers) when
+// the pair has no kernel.
+int launch_tc_chain_igemm(const TcProblem& q1, const TcProblem& q2, cudaStream_t s) {
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const int mid = q1.cols;
+    const int bk = mid == 64 ? 64 : 128;
+    auto folded_u8 = [](const EpiArgs& e) {
+        return e.mode == kEpiRequant && !e.rq.y_signed && e.rq.round_mode == 0 && e.rq.fold != 0;
+    };
+    const bool ok = (mid == 64 || mid == 128 || mid == 256) && q1.bk == bk && q2.bk == bk && q1.group_cols == 0 && q1.a_row_bytes == 0 &&
+                    q1.col_corr == nullptr && q1.col_mul == nullptr && q2.col_corr == nullptr && q2.col_mul == nullptr && folded_u8(q1.epi) &&
+                    folded_u8(q2.epi) && q1.epi.residual == nullptr && q1.pool_ho == 0 && q2.pool_ho == 0 && q2.KH == 1 && q2.KW == 1 &&
+                    q2.c_pad == mid && q2.C == mid && q2.group_cols == 0 && !q2.a_signed && q2.cols >= 16 && q2.cols <= (mid == 64 ? 512 : 1024) &&
+                    q1.Wb * q1.Hb * q1.Nb == 128 && (q1.c_pad % bk) == 0 && (q1.a_cs % 16) == 0 && (q2.ldc % 16) == 0 &&
+                    (reinterpret_cast<uintptr_t>(q1.a) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q1.b) & 15u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(q2.b) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q2.y) & 15u) == 0 &&
+                    (q2.epi.residual == nullptr || (reinterpret_cast<uintptr_t>(q2.epi.residual) & 15u) == 0) &&
+                    !(q2.epi.residual != nullptr && q2.epi.rq.res_relu && q2.epi.rq.out_zp_f != 0.f) &&
+                    (int64_t)q1.Wo * q1.Ho * q1.No == (int64_t)q2.Wo * q2.Ho * q2.No;
+    if (!ok) return set_error(CHXQ_ERR_UNSUPPORTED, "two-convolution kernel: this pair of layers has no fused kernel");
+    if (q1.Wo <= 0 || q1.Ho <= 0 || q1.No <= 0) return CHXQ_OK;
+    tc::ChainParams p{};
+    p.Wb = q1.Wb; p.Hb = q1.Hb; p.Nb = q1.Nb;
+    p.tiles_w = (q1.Wo + q1.Wb - 1) / q1.Wb;
+    p.tiles_h = (q1.Ho + q1.Hb - 1) / q1.Hb;
+    p.tiles_n = (q1.No + q1.Nb - 1) / q1.Nb;
+    const int64_t pos_tiles = (int64_t)p.tiles_w * p.tiles_h * p.tiles_n;
+    if (pos_tiles >= (1ll << 31) / 16) return set_error(CHXQ_ERR_UNSUPPORTED, "two-convolution kernel: too many tiles");
+    p.KH = q1.KH; p.KW = q1.KW; p.pad_top = q1.pad_top; p.pad_left = q1.pad_left;
+    p.sw = q1.sw > 0 ? q1.sw : 1; p.sh = q1.sh > 0 ? q1.sh : 1;
+    if (p.sw > 8 || p.sh > 8 || q1.Wb * p.sw > 256 || q1.Hb * p.sh > 256)
+        return set_error(CHXQ_ERR_UNSUPPORTED, "two-convolution kernel: stride %d x %d does not fit a TMA box", p.sh, p.sw);
+    p.c_chunks = q1.c_pad / bk;
+    p.out_cols = q2.cols;
+    p.idesc1 = (2u << 4) | ((q1.a_signed ? 1u : 0u) << 7) | ((q1.b_signed ? 1u : 0u) << 10) | ((uint32_t)(mid >> 3) << 17) | ((128u >> 4) << 24);
+    p.idesc2 = (2u << 4) | ((q2.b_signed ? 1u : 0u) << 10) | ((uint32_t)(128 >> 3) << 17) | ((128u >> 4) << 24);
+    p.epi1 = q1.epi;
+    p.epi2 = q2.epi;
+#ifdef CHXQ_TL
+    if (!g_tl_buf) cudaMalloc(&g_tl_buf, 5 * 2048 * sizeof(long long));
+    cudaMemsetAsync(g_tl_buf, 0, 5 * 2048 * sizeof(long long), s);
+    p.tl = g_tl_buf;
+#endif
+    p.wait_limit_ns = (unsigned long long)g_wait_limit_ns.load(std::memory_order_relaxed);
+    p.status = device_status_ptr();
+    if (!p.status) return set_error(CHXQ_ERR_CUDA, "device status word is unavailable");
+
+    alignas(64) CUtensorMap tmA, tmB1, tmB2, tmY, tmR;
+    const cuuint32_t ones4[4] = {1, 1, 1, 1};
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)q1.C, (cuuint64_t)q1.W, (cuuint64_t)q1.H, (cuuint64_t)q1.N};
+        const cuuint64_t row_bytes = (cuuint64_t)q1.a_cs * q1.W;
+        const cuuint64_t strides[3] = {(cuuint64_t)q1.a_cs, row_bytes, row_bytes * q1.H};
+        const cuuint32_t box[4] = {(cuuint32_t)bk, (cuuint32_t)(q1.Wb * p.sw), (cuuint32_t)(q1.Hb * p.sh), (cuuint32_t)q1.Nb};
+        const cuuint32_t estr[4] = {1, (cuuint32_t)p.sw, (cuuint32_t)p.sh, 1};
+        CUresult r = encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q1.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            swizzle_for(bk), CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed with %d", (int)r);
+    }
+    {
+        const int taps = q1.KH * q1.KW;
+        const cuuint64_t dims[2] = {(cuuint64_t)taps * q1.c_pad, (cuuint64_t)mid};
+        const cuuint64_t strides[1] = {(cuuint64_t)taps * q1.c_pad};
+        const cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)mid};
+        CUresult r = encode(&tmB1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(q1.b), dims, strides, box, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            swizzle_for(bk), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(B1) failed with %d", (int)r);
+    }
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)mid, (cuuint64_t)q2.cols};
+        const cuuint64_t strides[1] = {(cuuint64_t)mid};
+        const cuuint32_t box[2] = {(cuuint32_t)bk, 128u};
+        CUresult r = encode(&tmB2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(q2.b), dims, strides, box, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            swizzle_for(bk), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(B2) failed with %d", (int)r);
+    }
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)q2.cols, (cuuint64_t)q1.Wo, (cuuint64_t)q1.Ho, (cuuint64_t)q1.No};
+        const cuuint64_t strides[3] = {(cuuint64_t)q2.ldc, (cuuint64_t)q2.ldc * q1.Wo, (cuuint64_t)q2.ldc * q1.Wo * q1.Ho};
+        const cuuint32_t box[4] = {128u, (cuuint32_t)p.Wb, (cuuint32_t)p.Hb, (cuuint32_t)p.Nb};
+        CUresult r = encode(&tmY, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, q2.y, dims, strides, box, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(Y) failed with %d", (int)r);
+        void* rbase = q2.epi.residual ? const_cast<uint8_t*>(q2.epi.residual) : q2.y;
+        r = encode(&tmR, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, rbase, dims, strides, box, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(R) failed with %d", (int)r);
+    }
+    const int grid = pos_tiles < num_sms() ? (int)pos_tiles : num_sms();
+    ProfRec rec{};
+    if (g_prof_on) {
+        CHXQ_CUDA(cudaEventCreate(&rec.e0));
+        CHXQ_CUDA(cudaEventCreate(&rec.e1));
+        rec.macs = q1.alg_macs + q2.alg_macs;
+        CHXQ_CUDA(cudaEventRecord(rec.e0, s));
+    }
+    const int rc = tc::launch_tc_chain(mid, q2.epi.residual != nullptr, tmA, tmB1, tmB2, tmY, tmR, p, grid, s);
+    if (g_prof_on) {
+        CHXQ_CUDA(cudaEventRecord(rec.e1, s));
+        std::lock_guard<std::mutex> lock(g_prof_mu);
+        g_prof.push_back(rec);
+    }
+    return rc;
+}
+
 }  // namespace chxq
 
 // Chooses between the two tensor-core kernels: 0 = by problem shape, 1 = always one tile per step, 2 = grouped tiles
@@ -459,7 +567,7 @@ extern "C" int chxq_tc_variant(int32_t variant) {
 #ifdef CHXQ_TL
 extern "C" int chxq_tl_read(long long* host) {
     cudaDeviceSynchronize();
-    return (int)cudaMemcpy(host, chxq::g_tl_buf, 3 * 2048 * sizeof(long long), cudaMemcpyDeviceToHost);
+    return (int)cudaMemcpy(host, chxq::g_tl_buf, 5 * 2048 * sizeof(long long), cudaMemcpyDeviceToHost);
 }
 #endif
 

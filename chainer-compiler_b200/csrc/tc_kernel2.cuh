@@ -52,50 +52,6 @@ __device__ __forceinline__ void fence_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// ---- packed pairs of floats (one 64-bit register) and the saturating scalar forms -----------------------------------
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-    uint64_t d;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
-    return d;
-}
-__device__ __forceinline__ float lo_of(uint64_t v) { return __uint_as_float((uint32_t)v); }
-__device__ __forceinline__ float hi_of(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
-__device__ __forceinline__ uint64_t add_rm_x2(uint64_t a, uint64_t b) {  // round toward minus infinity
-    uint64_t d;
-    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t sub_x2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t mul_x2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t fma_x2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t fma_rm_x2(uint64_t a, uint64_t b, uint64_t c) {  // round toward minus infinity
-    uint64_t d;
-    asm("fma.rm.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ float fma_sat(float a, float b, float c) {  // clamp(fma(a, b, c), 0, 1)
-    float d;
-    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-__device__ __forceinline__ float add_sat(float a, float b) {
-    float d;
-    asm("add.rn.sat.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
-    return d;
-}
-
 // HALO: the A operand of a KH x KW (<= 3 x 3), stride-1 convolution is staged once per tile and channel chunk as the halo
 // tile of an 8 x 16 block of output positions of one image -- (16 + KH - 1) x (8 + KW - 1) pixels -- instead of once per
 // tap: each tap is a shifted view of the same bytes.  The halo tile is stored WITHOUT swizzle as BK / 16 planes of
@@ -255,7 +211,10 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // Warp 0 loads the positions (and the residual tiles); without halo tiles warp 19 loads the weights.  One thread per
         // operand: a thread that issues a tensor copy is held until the copy engine takes it, and with one thread for both operands
         // the engine idles while that thread waits for the next free stage.  (Halo form: warp 0 loads both.)
-        if (lane == 0) {
+        // Tensor copies issued by one warp are processed one instruction after the other (each takes about one memory latency, whatever
+        // its size), but the copies of several lanes of ONE instruction run side by side: so the whole warp walks the loop, and the kR
+        // tiles of a stage (or of a residual group) are fetched by kR lanes in a single instruction.
+        if (HALO ? lane == 0 : true) {
             const bool is_a = warp == 0;
             int stage = 0, hstage = 0;
             uint32_t phase = 0, hphase = 0;
@@ -278,14 +237,30 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (int t = 0; t < kR; ++t) tile_origin(pg * kR + t, w0[t], h0[t], n0[t]);
                 }
+                // this lane's tile (non-halo form: lane t < kR fetches tile t)
+                int lw0 = w0[0], lh0 = h0[0], ln0 = n0[0];
+#pragma unroll
+                for (int t = 1; t < kR; ++t)
+                    if (lane == t) {
+                        lw0 = w0[t]; lh0 = h0[t]; ln0 = n0[t];
+                    }
                 const int gbase = p.group_cols > 0 ? (ct * BN / p.group_cols) * p.group_cin : 0;
                 if (RES && is_a) {
                     const int rb = it % Cfg::kBufs;
-                    if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / Cfg::kBufs) & 1u) ^ 1u, abort_flag, p.status, 5, 0)) break;
-                    mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
+                    if (HALO) {
+                        if (!mbar_wait(bempty_bar(rb), ((uint32_t)(it / Cfg::kBufs) & 1u) ^ 1u, abort_flag, p.status, 5, 0)) break;
+                        mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
 #pragma unroll
-                    for (int t = 0; t < kR; ++t)
-                        tma_load_4d(smem_u32(smem_out + (rb * kR + t) * Cfg::kTileOut), &tmR, rfull_bar(rb), ct * BN, w0[t], h0[t], n0[t]);
+                        for (int t = 0; t < kR; ++t)
+                            tma_load_4d(smem_u32(smem_out + (rb * kR + t) * Cfg::kTileOut), &tmR, rfull_bar(rb), ct * BN, w0[t], h0[t], n0[t]);
+                    } else {
+                        ok = __all_sync(0xffffffffu, mbar_wait(bempty_bar(rb), ((uint32_t)(it / Cfg::kBufs) & 1u) ^ 1u, abort_flag, p.status, 5, 0));
+                        if (!ok) break;
+                        if (lane == 0) mbar_expect_tx(rfull_bar(rb), kR * Cfg::kTileOut);
+                        __syncwarp();
+                        if (lane < kR) tma_load_4d(smem_u32(smem_out + (rb * kR + lane) * Cfg::kTileOut), &tmR, rfull_bar(rb), ct * BN, lw0, lh0, ln0);
+                        __syncwarp();
+                    }
                 }
                 if (HALO) {
                     // one halo tile per position tile and channel chunk, then one weight stage per tap
@@ -338,19 +313,18 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     for (int kh = 0; kh < p.KH && ok; ++kh)
                         for (int kw = 0; kw < p.KW && ok; ++kw)
                             for (int cc = 0; cc < p.c_chunks; ++cc, bcol += BK) {
-                                if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 0)) {
-                                    ok = false;
-                                    break;
-                                }
+                                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 0));
+                                if (!ok) break;
                                 if (is_a) {
-                                    mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);  // both operands' bytes
-#pragma unroll
-                                    for (int t = 0; t < kR; ++t)
-                                        tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA + t * 128 * BK), &tmA, full_bar(stage), gbase + cc * BK,
-                                                    w0[t] * p.sw - p.pad_left + kw, h0[t] * p.sh - p.pad_top + kh, n0[t]);
+                                    if (lane == 0) mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);  // both operands' bytes
+                                    __syncwarp();
+                                    if (lane < kR)
+                                        tma_load_4d(smem_u32(smem_a + stage * Cfg::kStageA + lane * 128 * BK), &tmA, full_bar(stage), gbase + cc * BK,
+                                                    lw0 * p.sw - p.pad_left + kw, lh0 * p.sh - p.pad_top + kh, ln0);
                                 } else {
-                                    tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), bcol, ct * BN);
+                                    if (lane == 0) tma_load_2d(smem_u32(smem_b + stage * Cfg::kStageB), &tmB, full_bar(stage), bcol, ct * BN);
                                 }
+                                __syncwarp();
                                 if (++stage == kStages) {
                                     stage = 0;
                                     phase ^= 1u;
@@ -668,26 +642,25 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // ---------------- store warp ----------------
         // One lane: waits until all sixteen epilogue warps have staged a group, issues its TMA stores, waits until they have
         // read the buffer and hands the buffer back (to the epilogue, or to the producer for the next residual tile).
-        if (!POOL && lane == 0) {  // the pooling form stores nothing by TMA: the epilogue warps pool and write
+        if (!POOL) {  // the pooling form stores nothing by TMA: the epilogue warps pool and write
+            // the whole warp walks the loop; the kR tiles of a group leave through kR lanes of one instruction (see the producers)
             int it = 0;
             for (int grp = blockIdx.x; grp < total_groups; grp += gridDim.x, ++it) {
                 const int ct = grp % p.col_tiles;
                 const int pg = grp / p.col_tiles;
                 const int buf = it % Cfg::kBufs;
-                if (!mbar_wait(bfull_bar(buf), (uint32_t)(it / Cfg::kBufs) & 1u, abort_flag, p.status, 8, 0)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(bfull_bar(buf), (uint32_t)(it / Cfg::kBufs) & 1u, abort_flag, p.status, 8, 0))) break;
                 uint8_t* out_buf = smem_out + buf * (kR * Cfg::kTileOut);
-#pragma unroll
-                for (int t = 0; t < kR; ++t) {
-                    const int pt = pg * kR + t;
-                    if (pt < pos_tiles) {
-                        int w0, h0, n0;
-                        tile_origin(pt, w0, h0, n0);
-                        tma_store_4d(&tmY, smem_u32(out_buf + t * Cfg::kTileOut), ct * BN, w0, h0, n0);
-                    }
+                const int pt = pg * kR + lane;
+                if (lane < kR && pt < pos_tiles) {
+                    int w0, h0, n0;
+                    tile_origin(pt, w0, h0, n0);
+                    tma_store_4d(&tmY, smem_u32(out_buf + lane * Cfg::kTileOut), ct * BN, w0, h0, n0);
+                    tma_store_commit();
                 }
-                tma_store_commit();
-                tma_store_wait_read<0>();
-                mbar_arrive(bempty_bar(buf));
+                tma_store_wait_read<0>();  // lanes without a store in flight pass at once
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bempty_bar(buf));
             }
             tma_store_wait_all();
         }

@@ -51,6 +51,25 @@ struct TcParams {
 #endif
 };
 
+// Parameters of the two-convolution kernel (tc_kernel4.cuh): a KH x KW convolution whose uint8 output feeds a 1x1 / stride-1
+// convolution, tile by tile through shared memory.  Position tiles, taps and strides describe the first convolution; the second
+// one has the same output positions.
+struct ChainParams {
+    int Wb, Hb, Nb;
+    int tiles_w, tiles_h, tiles_n;
+    int KH, KW, pad_top, pad_left;
+    int sw, sh;
+    int c_chunks;            // K tiles per tap of the first convolution
+    int out_cols;            // output channels of the second convolution
+    uint32_t idesc1, idesc2;  // instruction descriptors: N = the first convolution's channels, N = 128
+    EpiArgs epi1, epi2;      // folded uint8 requantizations; epi2 may carry the residual tail
+    int* status;
+    unsigned long long wait_limit_ns;
+#ifdef CHXQ_TL
+    long long* tl;  // timeline build: (code, clock) pairs of CTA 0: [MMA thread | epilogue warp 2 | store warp] x 2048 entries
+#endif
+};
+
 // Epilogue families (template parameter EPI): dead paths are compiled out, which keeps the unrolled per-element
 // code of each kernel small enough for the instruction cache.
 constexpr int kEpiKInt32 = 0;    // store the int32 accumulator
@@ -74,6 +93,10 @@ int launch_tc2_bk128(int bn, int epi, bool res, bool halo, const CUtensorMap& tm
 // weight block (128 rows), tmY / tmR boxes are 128 channels wide; items = position-tile pairs x 256-channel blocks.
 int launch_tc3_bk128(int epi, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p,
                      int items, cudaStream_t s);
+
+// Two-convolution kernel; mid = channels between the two convolutions (64, 128 or 256; K tile 64 bytes for 64, else 128).
+int launch_tc_chain(int mid, bool res, const CUtensorMap& tmA, const CUtensorMap& tmB1, const CUtensorMap& tmB2, const CUtensorMap& tmY,
+                    const CUtensorMap& tmR, const ChainParams& p, int grid, cudaStream_t s);
 
 int tc3_pair_slots(int* out);  // CTA pairs the current device keeps resident at once
 

@@ -93,6 +93,7 @@ class ResNet50Int8:
         self.fc_b = np.zeros(num_classes, np.float32)
         self.in_scale = np.float32(1.0 / 255.0)
         self.calibrated = False
+        self.use_chain = False  # conv2 -> conv3 of a bottleneck as one kernel (ops.QLinearConvChainPacked); off: not faster yet than the two kernels
         self._graph = None
 
     # ---- enumeration helpers -------------------------------------------------------------------
@@ -168,6 +169,28 @@ class ResNet50Int8:
                                      b=c.dev["bias"], residual=residual, res_scale=res_scale, res_zero_point=res_zp, res_relu=True,
                                      out_scale=out_scale, out_zero_point=0, out=out, fold_scales=fold)
 
+    def _conv_args(self, c, fold, **tail):
+        d = dict(x_scale=c.x_scale, x_zero_point=np.uint8(0), w_scale=c.dev["w_scale"], w_zero_point=c.dev["w_zp"], y_scale=c.y_scale,
+                 y_zero_point=np.uint8(c.y_zp), b=c.dev["bias"], fold_scales=fold)
+        d.update(tail)
+        return d
+
+    def _run_tail(self, b, h1, sc, sc_scale, sc_zp, fold):
+        """conv2 -> conv3 + residual join of one bottleneck.  With folded requantizations the two convolutions run as one kernel
+        (ops.QLinearConvChainPacked) where one exists for the block's width; bit-identical to the two calls."""
+        if fold and self.use_chain and b.get("chain", True):
+            try:
+                return ops.QLinearConvChainPacked(
+                    h1, b["conv2"].packed, self._conv_args(b["conv2"], fold), b["conv3"].packed,
+                    self._conv_args(b["conv3"], fold, residual=sc, res_scale=sc_scale, res_zero_point=sc_zp, res_relu=True, out_scale=b["out_scale"],
+                                    out_zero_point=0))
+            except _lib.ChxqError as e:
+                if e.code != _lib.ERR_UNSUPPORTED:
+                    raise
+                b["chain"] = False  # no fused kernel for this width: two calls from now on
+        h2 = self._run_conv(b["conv2"], h1, fold=fold)
+        return self._run_conv(b["conv3"], h2, residual=sc, res_scale=sc_scale, res_zp=sc_zp, out_scale=b["out_scale"], fold=fold)
+
     def calibrate(self, x):
         """Uploads and packs the weights, then walks the network once over the fp32 NCHW batch x to fix every scale."""
         assert tuple(x.shape) == (self.batch, 3, self.image, self.image) and x.dtype == torch.float32
@@ -234,16 +257,19 @@ class ResNet50Int8:
         h_scale = self.stem.y_scale
         for i, b in enumerate(self.blocks):
             h1 = self._run_conv(b["conv1"], h, fold=fold)
-            h2 = self._run_conv(b["conv2"], h1, fold=fold)
             if b["proj"] is not None:
                 sc = self._run_conv(b["proj"], h, fold=fold)
             else:
                 sc = h
             sc_scale, sc_zp = b["res"]
+            chained = fused and fold and not (taps is not None and detail)
+            h2 = None if chained else self._run_conv(b["conv2"], h1, fold=fold)
             if taps is not None and detail:
                 taps["b%d_h1" % i], taps["b%d_h2" % i], taps["b%d_sc" % i] = h1, h2, sc
                 taps["b%d_h3" % i] = self._run_conv(b["conv3"], h2, fold=fold)
-            if fused:
+            if chained:
+                h = self._run_tail(b, h1, sc, sc_scale, sc_zp, fold)
+            elif fused:
                 h = self._run_conv(b["conv3"], h2, residual=sc, res_scale=sc_scale, res_zp=sc_zp, out_scale=b["out_scale"], fold=fold)
             else:
                 h3 = self._run_conv(b["conv3"], h2)

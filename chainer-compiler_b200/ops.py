@@ -408,6 +408,44 @@ def QLinearConvPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y
     return y
 
 
+def QLinearConvChainPacked(x, packed1, conv1, packed2, conv2, out=None):
+    """Two QLinearConvPacked calls as one kernel: `packed1` / `conv1` describe a convolution with 64, 128 or 256 output channels,
+    `packed2` / `conv2` the 1x1, stride-1 convolution that is its only reader.  conv1 and conv2 are dicts of the keyword arguments
+    QLinearConvPacked takes after `packed` (x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b, clamp_hi_q,
+    fold_scales, and for conv2 the residual tail's residual, res_scale, res_zero_point, res_relu, out_scale, out_zero_point).  The
+    map between the two convolutions is never written.  Bit-identical to the two calls in sequence; raises
+    ChxqError(ERR_UNSUPPORTED) when the pair has no fused kernel (the caller then makes the two calls)."""
+    _require_cuda(x)
+    g1, g2 = packed1.g, packed2.g
+    if tuple(x.shape) != (g1.N, g1.C, g1.H, g1.W) or not _is_channels_last(x):
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConvChainPacked: x does not match the packed geometry / layout")
+    if not (packed1.eligible and packed2.eligible):
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "QLinearConvChainPacked: a geometry is not eligible for the packed tensor-core path")
+    keep = []
+    c1, c2 = dict(conv1), dict(conv2)
+    if c1.get("residual") is not None:
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConvChainPacked: only the second convolution may carry a residual tail")
+    residual = c2.get("residual")
+    _check_residual("QLinearConvChainPacked", residual, (g2.N, g2.M, g2.Ho, g2.Wo), True)
+
+    def params(pk, c, res):
+        return _qconv_params(x, pk.w, c["x_scale"], c["x_zero_point"], c["w_scale"], c.get("w_zero_point"), c["y_scale"], c["y_zero_point"], c.get("b"),
+                             c.get("round_mode", ROUND_REF), c.get("clamp_hi_q"), res, c.get("res_scale", 1.0), c.get("res_zero_point", 0),
+                             c.get("res_relu", True), c.get("out_scale", 1.0), c.get("out_zero_point", 0), keep, c.get("fold_scales", False))
+
+    p1, cy1 = params(packed1, c1, None)
+    p2, cy2 = params(packed2, c2, residual)
+    if cy1 != UINT8 or cy2 != UINT8:
+        raise ChxqError(_lib.ERR_UNSUPPORTED, "QLinearConvChainPacked: both outputs must be uint8")
+    shape = (g2.N, g2.M, g2.Ho, g2.Wo)
+    if out is not None and (tuple(out.shape) != shape or not _is_channels_last(out) or out.dtype != torch.uint8):
+        raise ChxqError(_lib.ERR_INVALID_ARGUMENT, "QLinearConvChainPacked: out must be a channels_last uint8 map of the output's shape")
+    y = out if out is not None else torch.empty(shape, dtype=torch.uint8, device=x.device, memory_format=torch.channels_last)
+    check(lib().chxq_qlinear_conv_chain_packed(_ptr(x), _ptr(packed1.blob), ctypes.byref(g1), ctypes.byref(p1), packed1.flags, _ptr(packed2.blob),
+                                               ctypes.byref(g2), ctypes.byref(p2), packed2.flags, _ptr(y), _stream()))
+    return y
+
+
 def QLinearConvMaxPoolPacked(x, packed, x_scale, x_zero_point, w_scale, w_zero_point, y_scale, y_zero_point, b=None, pool_kernel=3, pool_stride=2,
                              pool_pad=0, cover_all=False, round_mode=ROUND_REF, quant_round_mode=ROUND_REF, clamp_hi_q=None, out=None,
                              fold_scales=False):

@@ -218,6 +218,17 @@ int chxq_conv_prepack(const void* w, const chxq_conv_geom* g, const void* w_zero
 int chxq_qlinear_conv_packed(const void* x, const void* packed, const chxq_conv_geom* g, const chxq_qconv_params* p, int32_t packed_flags,
                              void* y, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Two QLinearConv ops as ONE kernel: (g1, p1) is a convolution with 64, 128 or 256 output channels, (g2, p2) the 1x1 / stride-1
+ * convolution that is its only reader (p2->x_scale / x_zero_point = p1->y_scale / y_zero_point); p2 may carry the residual tail.
+ * The map between them is requantized tile by tile into shared memory and is never written: the first layer's tensor-core work
+ * runs under the second layer's epilogue.  The reference runs the two ops one after the other (runtime/ops/quantize.cc:62-94);
+ * results are bit-identical to that sequence.  Needs NHWC maps, packed weights with zero weight zero points, zero activation zero
+ * points in front of both layers and folded requantizations; CHXQ_ERR_UNSUPPORTED otherwise -- run the two ops then.  No
+ * workspace. */
+int chxq_qlinear_conv_chain_packed(const void* x, const void* packed1, const chxq_conv_geom* g1, const chxq_qconv_params* p1, int32_t packed_flags1,
+                                   const void* packed2, const chxq_conv_geom* g2, const chxq_qconv_params* p2, int32_t packed_flags2, void* y,
+                                   void* stream);
+
 /* QuantizeLinear(x; p->x_scale, p->x_zero_point -> uint8, quant_round_mode) fused into the packed QLinearConv that consumes
  * it: x is the fp32 tensor (layout g->x_layout), the uint8 map never exists in memory.  Only for geometries on the
  * space-to-depth path (stride 2, at most 4 channels: network stems), CHXQ_ERR_UNSUPPORTED otherwise.  Bit-identical to
