@@ -38,7 +38,7 @@ def parse():
     ap.add_argument("--sustain-s", type=float, default=2.0, help="seconds of the sustained loop that follows the timed region")
     ap.add_argument("--tc-variant", type=int, default=0, choices=[0, 1, 2, 3, 4, 5, 6, 7],
                     help="tensor-core kernel choice (chxq_tc_variant): 0 by shape, 1 one tile per step, 2 grouped tiles")
-    ap.add_argument("--chain", action="store_true", help="run conv2 and conv3 of every bottleneck as one kernel (chxq_qlinear_conv_chain_packed)")
+    ap.add_argument("--no-chain", action="store_true", help="run conv2 and conv3 of every bottleneck as two kernels (default: one kernel where faster)")
     ap.add_argument("--exact-requant", action="store_true",
                     help="requantize in the reference's operation order (multiply by x_scale*w_scale, divide by y_scale) instead of one "
                          "folded multiplier per channel")
@@ -279,7 +279,7 @@ def run_chxq(args):
 
     # Same seeded weights on every rank; every rank works on its own seeded images (weak scaling: 256 images per GPU).
     net = models.ResNet50Int8(batch=args.batch, device=dev, seed=0, image=IMAGE)
-    net.use_chain = args.chain
+    net.use_chain = not args.no_chain
     fold = not args.exact_requant
     gop_per_image = 2.0 * net.macs_per_image() / 1e9
     eng = dp.InferenceEngine(net, world, fold=fold, rank=rank)
@@ -396,7 +396,7 @@ def run_chxq(args):
         probe_tops, probe_err = int8_probe(dev)
         share = (tms.value / prof_steps) / ms_per_step
         sus_tops = achieved * (ms_per_step / sus_ms_per_step)  # same kernels, same share of the step, at the sustained clocks
-        roof = {"bound": "tensor", "kernel": "tc_igemm2_kernel (tcgen05 kind::i8 implicit GEMM, grouped tiles, all 53 convolutions)",
+        roof = {"bound": "tensor", "kernel": "tc_igemm2_kernel + tc_igemm3_kernel + tc_chain_kernel (tcgen05 kind::i8 implicit GEMM: grouped tiles, CTA pairs, two convolutions per kernel; all 53 convolutions)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic, "traffic_note": traffic_note,
                 "peak_source": "2 x bf16_tflops (burst) of MEASURED_PEAKS.json (%s; the file has no int8 entry; int8 ops counted as 2 per MAC); of %s"
                                % (pk["source"], "measured" if pk["source"] == "measured" else "fallback"),

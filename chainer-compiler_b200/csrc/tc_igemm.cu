@@ -509,11 +509,13 @@ int launch_tc_chain_igemm(const TcProblem& q1, const TcProblem& q2, cudaStream_t
         if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed with %d", (int)r);
     }
     {
+        // four dimensions (the last two of extent 1): the kernel fetches positions and weights with one instruction form
         const int taps = q1.KH * q1.KW;
-        const cuuint64_t dims[2] = {(cuuint64_t)taps * q1.c_pad, (cuuint64_t)mid};
-        const cuuint64_t strides[1] = {(cuuint64_t)taps * q1.c_pad};
-        const cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)mid};
-        CUresult r = encode(&tmB1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(q1.b), dims, strides, box, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        const cuuint64_t row = (cuuint64_t)taps * q1.c_pad;
+        const cuuint64_t dims[4] = {row, (cuuint64_t)mid, 1, 1};
+        const cuuint64_t strides[3] = {row, row * mid, row * mid};
+        const cuuint32_t box[4] = {(cuuint32_t)bk, (cuuint32_t)mid, 1, 1};
+        CUresult r = encode(&tmB1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(q1.b), dims, strides, box, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             swizzle_for(bk), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(B1) failed with %d", (int)r);
     }

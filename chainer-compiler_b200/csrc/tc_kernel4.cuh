@@ -9,17 +9,18 @@
 // leaves the tensor pipe idle.  Here the first product of tile i + 1 is issued between the column passes of the second
 // product of tile i, so the tensor pipe works for one tile while the epilogue warps requantize the other.
 //
-// Roles (640 threads): warp 0 loads the positions of the first product and the weights of the second, warp 19 the weights of the
-// first, warp 1 issues all MMAs, warps 2-17 run both epilogues, warp 18 issues the TMA stores and the loads of the residual tiles.
+// Roles (640 threads): warp 0 loads both operands of the first product, warp 1 issues its MMAs, warp 19 issues the MMAs of the second
+// product and loads its weights, warps 2-17 run both epilogues, warp 18 issues the TMA stores and the loads of the residual tiles.
 //
 // Tensor memory (512 columns): [0, 256) the first product's accumulators (two buffers of MID columns, one when MID = 256),
 // [256, 512) two buffers of 128 columns for the second product, which runs in passes of 128 output channels.
 //
-// The two products have their own operand rings, and the MMA thread issues whichever is ready: the next pass of the second
-// product (its weights are in, the intermediate tile is written, an accumulator buffer is free) before the next K block of the
-// first product of a later tile.  So the first product runs ahead in the gaps the epilogue leaves, and neither the loads nor the
-// tensor pipe wait for the epilogue's pace.  The epilogue warps produce the NEXT tile's intermediate tile before the last pass of
-// the current one, so that the round trip through the tensor pipe for the next tile's first pass hides behind that pass.
+// The two products have their own operand rings and their own MMA threads, so neither waits for the other: the first product of the
+// next tiles runs ahead as far as its accumulator buffers allow, whatever the pace of the epilogue, and a pass of the second product is
+// issued the moment the epilogue hands an accumulator buffer back.  (One thread that polls both streams' barriers loses: a barrier test
+// costs ~150-200 cycles while the epilogue warps use the shared-memory pipe.)  The epilogue warps produce the NEXT tile's intermediate
+// tile before the last pass of the current one, so that the round trip through the tensor pipe for the next tile's first pass hides
+// behind that pass.
 //
 // Every wait is bounded as in tc_kernel.cuh.  Results are bit-identical to the two layers run one after the other.
 #pragma once
@@ -54,10 +55,10 @@ struct Tc4Config {
     static constexpr int kStageB = MID * BK;              // one K block of weights
     static constexpr int kStageBytes = kSub * (kStageA + kStageB);  // [kSub position blocks][kSub weight blocks]
     static constexpr int kSlot2 = 128 * BK;               // second ring: one K block of 128 output channels' weights per slot
-    static constexpr int kSlots2 = 2;
+    static constexpr int kSlots2 = 3;
     static constexpr int kA2Bytes = 128 * MID;            // the intermediate tile: kChunks2 swizzled [128][BK] blocks
     static constexpr int kTileOut = 128 * 128;            // one staged output (or residual) tile of a pass
-    static constexpr int kBufs = MID == 64 ? 3 : 2;
+    static constexpr int kBufs = MID == 256 ? 2 : 3;
     static constexpr int kOutBytes = kBufs * kTileOut;
     static constexpr int kD1Bufs = MID == 256 ? 1 : 2;
     static constexpr int kMaxOut = MID == 64 ? 512 : 1024;  // output channels of the second convolution the tables have room for
@@ -150,6 +151,7 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOffset);
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+    volatile int* passes_done = reinterpret_cast<volatile int*>(tmem_ptr_smem + 2);  // passes of the second product the epilogue has finished
     float* tab_ms1 = reinterpret_cast<float*>(smem + Cfg::kParamOffset);
     float* tab_bs1 = tab_ms1 + MID;
     float* tab_ms2 = tab_bs1 + MID;
@@ -195,6 +197,7 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             mbar_init(bempty_bar(b), 1);
         }
         *abort_flag = 0;
+        *passes_done = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -224,17 +227,18 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         w0 = tw * p.Wb; h0 = th * p.Hb; n0 = tn * p.Nb;
     };
 
-    if (warp == 0 || warp == 19) {
-        // ---------------- TMA producers: warp 0 the positions of the first product and the weights of the second, warp 19 the
-        // weights of the first.  The whole warp walks the loop; lane j < kSub of a stage fetches the stage's j-th K block (one
-        // instruction for all).  Warp 0 serves its two rings in turn, whichever has a free slot (non-blocking tests), so a full
-        // ring never holds up the other one.
-        const bool is_a = warp == 0;
-        // first ring
-        int t1 = 0, s1 = 0, stage = 0;
+    if (warp == 0) {
+        // ---------------- TMA producer of the first product ----------------
+        // The whole warp walks the loop and waits; the kSub position blocks and the kSub weight blocks of a stage are fetched by 2 kSub
+        // lanes of ONE instruction (the weights' map is declared with four dimensions so that both operands take the same instruction
+        // form): a thread sustains only one tensor copy per ~400 cycles, whatever the copy's size.
+        int stage = 0;
         uint32_t phase = 0;
-        int w0 = 0, h0 = 0, n0 = 0;
-        int l_cc = 0, l_kw = 0, l_kh = 0;  // this lane's K block of the current stage: (channel chunk, tap column, tap row)
+        bool ok = true;
+        const bool wlane = lane >= kSub;                 // this lane fetches weights
+        const int sub = wlane ? lane - kSub : lane;      // ... of the stage's sub-th K block
+        const CUtensorMap* my_map = wlane ? &tmB1 : &tmA;
+        int l_cc = 0, l_kw = 0, l_kh = 0;                // position lanes: (channel chunk, tap column, tap row) of this lane's K block
         auto lane_step = [&]() {
             if (++l_cc == p.c_chunks) {
                 l_cc = 0;
@@ -244,33 +248,26 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         };
-        auto start_tile = [&]() {
-            tile_origin(t1, w0, h0, n0);
+        for (int i = 0; i < my_tiles && ok; ++i) {
+            int w0, h0, n0;
+            tile_origin(i, w0, h0, n0);
             w0 = w0 * p.sw - p.pad_left;
             h0 = h0 * p.sh - p.pad_top;
             l_cc = 0; l_kw = 0; l_kh = 0;
             for (int j = 0; j < kSub; ++j)
-                if (j < lane) lane_step();
-        };
-        if (my_tiles > 0) start_tile();
-        // second ring (warp 0 only)
-        int t2 = is_a ? 0 : my_tiles, ps2 = 0, kc2 = 0, slot = 0;
-        uint32_t phase2 = 0;
-        uint64_t idle_since = 0;
-        uint32_t idle_spins = 0;
-        while (t1 < my_tiles || t2 < my_tiles) {
-            bool did = false;
-            if (t1 < my_tiles && __all_sync(0xffffffffu, mbar_test(empty_bar(stage), phase ^ 1u) != 0)) {
-                const int kb0 = s1 * kSub;
+                if (j < sub) lane_step();
+            for (int s = 0; s < num_st && ok; ++s) {
+                const int kb0 = s * kSub;
                 const int nsub = num_kb - kb0 < kSub ? num_kb - kb0 : kSub;
+                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1, 0, limit));
+                if (!ok) break;
                 uint8_t* st = ring + stage * Cfg::kStageBytes;
-                if (is_a) {
-                    if (lane == 0) mbar_expect_tx(full_bar(stage), (uint32_t)(nsub * (Cfg::kStageA + Cfg::kStageB)));  // both operands' bytes
-                    __syncwarp();
-                    if (lane < nsub) tma_load_4d(smem_u32(st + lane * Cfg::kStageA), &tmA, full_bar(stage), l_cc * BK, w0 + l_kw, h0 + l_kh, n0);
-                } else {
-                    if (lane < nsub) tma_load_2d(smem_u32(st + kSub * Cfg::kStageA + lane * Cfg::kStageB), &tmB1, full_bar(stage), (kb0 + lane) * BK, 0);
-                }
+                if (lane == 0) mbar_expect_tx(full_bar(stage), (uint32_t)(nsub * (Cfg::kStageA + Cfg::kStageB)));
+                __syncwarp();
+                const uint32_t dst = smem_u32(wlane ? st + kSub * Cfg::kStageA + sub * Cfg::kStageB : st + sub * Cfg::kStageA);
+                const int c0 = wlane ? (kb0 + sub) * BK : l_cc * BK;
+                const int c1 = wlane ? 0 : w0 + l_kw, c2 = wlane ? 0 : h0 + l_kh, c3 = wlane ? 0 : n0;
+                if (lane < 2 * kSub && sub < nsub) tma_load_4d(dst, my_map, full_bar(stage), c0, c1, c2, c3);
 #pragma unroll
                 for (int j = 0; j < kSub; ++j) lane_step();
                 __syncwarp();
@@ -278,157 +275,137 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     stage = 0;
                     phase ^= 1u;
                 }
-                if (++s1 == num_st) {
-                    s1 = 0;
-                    if (++t1 < my_tiles) start_tile();
-                }
-                did = true;
-            }
-            if (t2 < my_tiles && __all_sync(0xffffffffu, mbar_test(empty2_bar(slot), phase2 ^ 1u) != 0)) {
-                if (lane == 0) {
-                    mbar_expect_tx(full2_bar(slot), Cfg::kSlot2);
-                    tma_load_2d(smem_u32(ring2 + slot * Cfg::kSlot2), &tmB2, full2_bar(slot), kc2 * BK, ps2 * 128);
-                }
-                __syncwarp();
-                if (++slot == Cfg::kSlots2) {
-                    slot = 0;
-                    phase2 ^= 1u;
-                }
-                if (++kc2 == Cfg::kChunks2) {
-                    kc2 = 0;
-                    if (++ps2 == passes) {
-                        ps2 = 0;
-                        ++t2;
-                    }
-                }
-                did = true;
-            }
-            if (did) {
-                idle_spins = 0;
-            } else {
-                __nanosleep(64);
-                if (++idle_spins >= 256u) {  // bounded wait: no slot came free for a long time
-                    idle_spins = 128u;
-                    bool stop = *abort_flag != 0;
-                    const uint64_t now = global_timer_ns();
-                    if (idle_since == 0) idle_since = now;
-                    if (now - idle_since > limit) {
-                        *abort_flag = 1;
-                        atomicCAS(p.status, 0, 1);
-                        stop = true;
-                    }
-                    if (__any_sync(0xffffffffu, stop)) break;
-                } else if (idle_spins == 1u) {
-                    idle_since = 0;
-                }
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        // Two streams of work, each in its own order: (1) the first product, tile by tile, one ring stage at a time; (2) the second
-        // product, one K block of one pass at a time.  Whichever has everything it needs is issued, the second product first.
+        // ---------------- MMA thread of the first product ----------------
         if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
             const uint32_t desc_hi = kmajor_desc_hi<BK>();
             const uint32_t ring_lo = kmajor_desc_lo(smem_u32(ring));
-            const uint32_t ring2_lo = kmajor_desc_lo(smem_u32(ring2));
-            const uint32_t a2_lo = kmajor_desc_lo(smem_u32(smem_a2));
-            // stream 1
-            int t1 = 0, s1 = 0, stage = 0;
-            uint32_t phase = 0;
-            bool d1_ok = false;  // the accumulator buffer of tile t1 has been handed back by the epilogue
-            // stream 2
-            int t2 = 0, ps2 = 0, kc2 = 0, slot = 0, g2 = 0;
-            uint32_t phase2 = 0;
-            bool a2_ok = false, d2_ok = false;
 #ifdef CHXQ_TL
             int tl_n = 0;
 #endif
-            uint64_t idle_since = 0;
-            uint32_t idle_spins = 0;
-            while (t1 < my_tiles || t2 < my_tiles) {
-                bool did = false;
-                if (t2 < my_tiles) {
-                    // the second product of tile t2: needs the intermediate tile (first K block of the first pass), a free accumulator
-                    // buffer (first K block of a pass) and the weights' K block
-                    if (!a2_ok) a2_ok = mbar_test(a2full_bar(), (uint32_t)t2 & 1u) != 0;
-                    if (a2_ok && !d2_ok) d2_ok = mbar_test(d2empty_bar(g2 & 1), (((uint32_t)g2 >> 1) & 1u) ^ 1u) != 0;
-                    if (a2_ok && d2_ok && mbar_test(full2_bar(slot), phase2)) {
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int b1 = kD1Bufs == 2 ? (i & 1) : 0;
+                const uint32_t use = (uint32_t)(i / kD1Bufs);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(b1 * MID);
+                // the epilogue has read the accumulators this buffer held before
+                if (!mbar_wait(d1empty_bar(b1), (use & 1u) ^ 1u, abort_flag, p.status, 2, 0, limit)) break;
+                tc_fence_after();
+                CHXQ_TL4(0, 1000, 400);
+                for (int s = 0; s < num_st; ++s) {
+                    // Pacing.  This product runs up to two tiles ahead of the epilogue and could issue a tile's MMAs in one burst, behind
+                    // which the second product's next pass would queue in the tensor pipe while the epilogue warps wait for it.  So stage s
+                    // of tile i goes out only once the epilogue has finished the matching share of the passes of tile i - 2.  Only timing
+                    // depends on this: after a bounded number of polls the stage is issued anyway.
+                    if (i >= 2) {
+                        const int target = (i - 2) * passes + (s * passes) / num_st;
+                        for (int spin = 0; spin < 4096 && *passes_done < target; ++spin) __nanosleep(64);
+                    }
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3, 0, limit)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_lo = ring_lo + (uint32_t)(stage * (Cfg::kStageBytes >> 4));
+                    const uint32_t b_lo = a_lo + (uint32_t)((kSub * Cfg::kStageA) >> 4);
+                    const int nsub = num_kb - s * kSub < kSub ? num_kb - s * kSub : kSub;
+#pragma unroll
+                    for (int j = 0; j < kSub; ++j)
+                        if (j < nsub) {
+#pragma unroll
+                            for (int k = 0; k < BK / 32; ++k)
+                                umma_i8_lohi(tmem_d, a_lo + (uint32_t)(j * (Cfg::kStageA >> 4) + k * 2), desc_hi, b_lo + (uint32_t)(j * (Cfg::kStageB >> 4) + k * 2),
+                                             desc_hi, p.idesc1, (s > 0 || j > 0 || k > 0) ? 1u : 0u);
+                        }
+                    umma_commit(empty_bar(stage));
+                    CHXQ_TL4(0, 1000, 800 + s);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(d1full_bar(b1));
+                CHXQ_TL4(0, 1000, 500);
+            }
+        }
+    } else if (warp == 19) {
+        // ---------------- MMA thread of the second product; it also fetches that product's weights ----------------
+        // One K block of 128 output channels' weights per slot of the second ring.  A slot is refilled as soon as the MMAs that read it
+        // have completed, with the K block kSlots2 blocks ahead: by then the next pass waits for the epilogue anyway.
+        if (lane == 0) {
+            const uint32_t desc_hi = kmajor_desc_hi<BK>();
+            const uint32_t ring2_lo = kmajor_desc_lo(smem_u32(ring2));
+            const uint32_t a2_lo = kmajor_desc_lo(smem_u32(smem_a2));
+            const int total = my_tiles * passes * Cfg::kChunks2;  // K blocks of this CTA, in order
+            int ld_ps = 0, ld_kc = 0, ld_n = 0, ld_slot = 0;
+            uint32_t ld_phase = 0;
+            bool ok = true;
+            // fetches the next K block in order into the next slot (whose previous MMAs must have completed)
+            auto load_next = [&]() {
+                if (!mbar_wait(empty2_bar(ld_slot), ld_phase ^ 1u, abort_flag, p.status, 15, 0, limit)) {
+                    ok = false;
+                    return;
+                }
+                mbar_expect_tx(full2_bar(ld_slot), Cfg::kSlot2);
+                tma_load_2d(smem_u32(ring2 + ld_slot * Cfg::kSlot2), &tmB2, full2_bar(ld_slot), ld_kc * BK, ld_ps * 128);
+                ++ld_n;
+                if (++ld_slot == Cfg::kSlots2) {
+                    ld_slot = 0;
+                    ld_phase ^= 1u;
+                }
+                if (++ld_kc == Cfg::kChunks2) {
+                    ld_kc = 0;
+                    if (++ld_ps == passes) ld_ps = 0;
+                }
+            };
+            for (int n = 0; n < Cfg::kSlots2 && n < total && ok; ++n) load_next();
+#ifdef CHXQ_TL
+            int tl_n = 0;
+#endif
+            int slot = 0, g = 0;
+            uint32_t phase2 = 0;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                // the intermediate tile of this CTA's i-th tile is in shared memory
+                if (!mbar_wait(a2full_bar(), (uint32_t)i & 1u, abort_flag, p.status, 11, 0, limit)) break;
+                for (int ps = 0; ps < passes && ok; ++ps, ++g) {
+                    const int d2 = g & 1;
+                    CHXQ_TL4(8192, 1000, 100 + ps);
+                    if (!mbar_wait(d2empty_bar(d2), (((uint32_t)g >> 1) & 1u) ^ 1u, abort_flag, p.status, 12, 0, limit)) {
+                        ok = false;
+                        break;
+                    }
+                    CHXQ_TL4(8192, 1000, 150 + ps);
+                    const uint32_t tmem_d = tmem_base + 256u + (uint32_t)(d2 * 128);
+                    for (int kc = 0; kc < Cfg::kChunks2; ++kc) {
+                        while (ld_n <= g * Cfg::kChunks2 + kc && ok) load_next();  // (only when a pass has more K blocks than the ring runs ahead)
+                        if (!ok) break;
+                        if (!mbar_wait(full2_bar(slot), phase2, abort_flag, p.status, 16, 0, limit)) {
+                            ok = false;
+                            break;
+                        }
                         tc_fence_after();
-                        if (kc2 == 0) CHXQ_TL4(0, 1000, 200 + ps2);
-                        const uint32_t tmem_d = tmem_base + 256u + (uint32_t)((g2 & 1) * 128);
-                        const uint32_t a_lo = a2_lo + (uint32_t)(kc2 * ((128 * BK) >> 4));
+                        const uint32_t a_lo = a2_lo + (uint32_t)(kc * ((128 * BK) >> 4));
                         const uint32_t b_lo = ring2_lo + (uint32_t)(slot * (Cfg::kSlot2 >> 4));
 #pragma unroll
-                        for (int k = 0; k < BK / 32; ++k) umma_i8_lohi(tmem_d, a_lo + k * 2, desc_hi, b_lo + k * 2, desc_hi, p.idesc2, (kc2 > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < BK / 32; ++k) umma_i8_lohi(tmem_d, a_lo + k * 2, desc_hi, b_lo + k * 2, desc_hi, p.idesc2, (kc > 0 || k > 0) ? 1u : 0u);
                         umma_commit(empty2_bar(slot));
                         if (++slot == Cfg::kSlots2) {
                             slot = 0;
                             phase2 ^= 1u;
                         }
-                        if (++kc2 == Cfg::kChunks2) {
-                            kc2 = 0;
-                            umma_commit(d2full_bar(g2 & 1));
-                            CHXQ_TL4(0, 1000, 300 + ps2);
-                            ++g2;
-                            d2_ok = false;
-                            if (++ps2 == passes) {
-                                ps2 = 0;
-                                ++t2;
-                                a2_ok = false;
-                            }
-                        }
-                        did = true;
                     }
-                }
-                if (!did && t1 < my_tiles) {
-                    // the first product of tile t1: needs its accumulator buffer back (first stage) and the stage's operands
-                    const int b1 = kD1Bufs == 2 ? (t1 & 1) : 0;
-                    if (!d1_ok) d1_ok = s1 > 0 || mbar_test(d1empty_bar(b1), (((uint32_t)(t1 / kD1Bufs)) & 1u) ^ 1u) != 0;
-                    if (d1_ok && mbar_test(full_bar(stage), phase)) {
-                        tc_fence_after();
-                        if (s1 == 0) CHXQ_TL4(0, 1000, 400);
-                        const uint32_t tmem_d = tmem_base + (uint32_t)(b1 * MID);
-                        const uint32_t a_lo = ring_lo + (uint32_t)(stage * (Cfg::kStageBytes >> 4));
-                        const uint32_t b_lo = a_lo + (uint32_t)((kSub * Cfg::kStageA) >> 4);
-                        const int nsub = num_kb - s1 * kSub < kSub ? num_kb - s1 * kSub : kSub;
-#pragma unroll
-                        for (int j = 0; j < kSub; ++j)
-                            if (j < nsub) {
-#pragma unroll
-                                for (int k = 0; k < BK / 32; ++k)
-                                    umma_i8_lohi(tmem_d, a_lo + (uint32_t)(j * (Cfg::kStageA >> 4) + k * 2), desc_hi,
-                                                 b_lo + (uint32_t)(j * (Cfg::kStageB >> 4) + k * 2), desc_hi, p.idesc1, (s1 > 0 || j > 0 || k > 0) ? 1u : 0u);
-                            }
-                        umma_commit(empty_bar(stage));
-                        if (++stage == kStages) {
-                            stage = 0;
-                            phase ^= 1u;
-                        }
-                        if (++s1 == num_st) {
-                            umma_commit(d1full_bar(b1));
-                            CHXQ_TL4(0, 1000, 500);
-                            s1 = 0;
-                            ++t1;
-                            d1_ok = false;
-                        }
-                        did = true;
-                    }
-                }
-                if (did) {
-                    idle_spins = 0;
-                } else if (++idle_spins >= 1024u) {
-                    // bounded wait: nothing became ready for a long time
-                    idle_spins = 512u;
-                    if (*abort_flag) break;
-                    const uint64_t now = global_timer_ns();
-                    if (idle_since == 0) idle_since = now;
-                    if (now - idle_since > limit) {
-                        *abort_flag = 1;
-                        atomicCAS(p.status, 0, 3);
-                        break;
-                    }
-                } else if (idle_spins == 1u) {
-                    idle_since = 0;
+                    if (!ok) break;
+                    umma_commit(d2full_bar(d2));
+                    CHXQ_TL4(8192, 1000, 300 + ps);
+                    // refill the slots whose last readers are the MMAs of EARLIER passes (complete by now): the thread never waits for the
+                    // MMAs it has just issued, so the next pass can go out the moment the epilogue hands its accumulator buffer back
+                    const int issued = (g + 1) * Cfg::kChunks2;
+                    while (ld_n < total && ld_n - Cfg::kSlots2 < issued - Cfg::kChunks2 && ok) load_next();
+                    CHXQ_TL4(8192, 1000, 350 + ps);
                 }
             }
         }
@@ -567,50 +544,40 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (!alive) break;
                 }
                 alive = second_epilogue(i, ps);
+                if (e == 0 && lane == 0) *passes_done = i * passes + ps + 1;
             }
         }
     } else if (warp == 18) {
         // ---------------- store warp: TMA stores of the staged passes, and the loads of the residual tiles ----------------
-        // The whole warp walks the loop; stores and loads are issued by the lanes in turn (see the producers).  A lane that has no
-        // store in flight passes the wait for its bulk groups at once, so the warp's wait is the wait of the lane that just stored.
-        {
+        if (lane == 0) {
             const int total = my_tiles * passes;
-            uint32_t turn = 0;
 #ifdef CHXQ_TL
-            int tl_n = (lane == 0) ? 0 : 1 << 30;
+            int tl_n = 0;
 #endif
             auto residual_load = [&](int g) {
                 const int i = g / passes, ps = g - i * passes, b = g % kBufs;
                 int w0, h0, n0;
                 tile_origin(i, w0, h0, n0);
-                if (lane == (turn & 31u)) {
-                    mbar_expect_tx(rfull_bar(b), Cfg::kTileOut);
-                    tma_load_4d(smem_u32(smem_out + b * Cfg::kTileOut), &tmR, rfull_bar(b), ps * 128, w0, h0, n0);
-                }
-                ++turn;
-                __syncwarp();
+                mbar_expect_tx(rfull_bar(b), Cfg::kTileOut);
+                tma_load_4d(smem_u32(smem_out + b * Cfg::kTileOut), &tmR, rfull_bar(b), ps * 128, w0, h0, n0);
             };
             if (RES)
                 for (int g = 0; g < kBufs && g < total; ++g) residual_load(g);
             for (int g = 0; g < total; ++g) {
                 const int i = g / passes, ps = g - i * passes, b = g % kBufs;
                 CHXQ_TL4(4096, 1000, 1);
-                if (!__all_sync(0xffffffffu, mbar_wait(bfull_bar(b), (uint32_t)(g / kBufs) & 1u, abort_flag, p.status, 8, 0, limit))) break;
+                if (!mbar_wait(bfull_bar(b), (uint32_t)(g / kBufs) & 1u, abort_flag, p.status, 8, 0, limit)) break;
                 CHXQ_TL4(4096, 1000, 2);
                 int w0, h0, n0;
                 tile_origin(i, w0, h0, n0);
-                if (lane == (turn & 31u)) {
-                    tma_store_4d(&tmY, smem_u32(smem_out + b * Cfg::kTileOut), ps * 128, w0, h0, n0);
-                    tma_store_commit();
-                }
-                ++turn;
+                tma_store_4d(&tmY, smem_u32(smem_out + b * Cfg::kTileOut), ps * 128, w0, h0, n0);
+                tma_store_commit();
                 tma_store_wait_read<0>();
-                __syncwarp();
                 CHXQ_TL4(4096, 1000, 3);
                 if (RES) {
                     if (g + kBufs < total) residual_load(g + kBufs);  // the buffer is free: fetch the residual tile of its next use
                 } else {
-                    if (lane == 0) mbar_arrive(bempty_bar(b));
+                    mbar_arrive(bempty_bar(b));
                 }
             }
             tma_store_wait_all();

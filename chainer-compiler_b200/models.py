@@ -93,7 +93,7 @@ class ResNet50Int8:
         self.fc_b = np.zeros(num_classes, np.float32)
         self.in_scale = np.float32(1.0 / 255.0)
         self.calibrated = False
-        self.use_chain = False  # conv2 -> conv3 of a bottleneck as one kernel (ops.QLinearConvChainPacked); off: not faster yet than the two kernels
+        self.use_chain = True  # conv2 -> conv3 of a bottleneck as one kernel (ops.QLinearConvChainPacked) where that is faster
         self._graph = None
 
     # ---- enumeration helpers -------------------------------------------------------------------
@@ -178,7 +178,9 @@ class ResNet50Int8:
     def _run_tail(self, b, h1, sc, sc_scale, sc_zp, fold):
         """conv2 -> conv3 + residual join of one bottleneck.  With folded requantizations the two convolutions run as one kernel
         (ops.QLinearConvChainPacked) where one exists for the block's width; bit-identical to the two calls."""
-        if fold and self.use_chain and b.get("chain", True):
+        # (measured at batch 256: one kernel wins for 64 and 128 channels between the layers, 140 against 153 us and 79 against 90 us per
+        # block; at 256 channels the pair of kernels on CTA pairs is as fast, 63 us)
+        if fold and self.use_chain and b.get("chain", b["conv2"].cout <= 128):
             try:
                 return ops.QLinearConvChainPacked(
                     h1, b["conv2"].packed, self._conv_args(b["conv2"], fold), b["conv3"].packed,
