@@ -58,6 +58,8 @@ struct Tc4Config {
     static constexpr int kSlots2 = 3;
     static constexpr int kA2Bytes = 128 * MID;            // the intermediate tile: kChunks2 swizzled [128][BK] blocks
     static constexpr int kTileOut = 128 * 128;            // one staged output (or residual) tile of a pass
+    // staging buffers (up to four): a residual tile is fetched into a buffer as soon as the store of the pass that used it before has
+    // read it (measured: four buffers are no faster than three and cost a stage of the first ring)
     static constexpr int kBufs = MID == 256 ? 2 : 3;
     static constexpr int kOutBytes = kBufs * kTileOut;
     static constexpr int kD1Bufs = MID == 256 ? 1 : 2;
@@ -66,7 +68,7 @@ struct Tc4Config {
     static constexpr int kBudget = 225 * 1024;
     static constexpr int kStagesRaw = (kBudget - kSlots2 * kSlot2 - kA2Bytes - kOutBytes - kParamBytes - 512) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-    static constexpr int kNumBars = 2 * kStages + 2 * kSlots2 + 18;
+    static constexpr int kNumBars = 2 * kStages + 2 * kSlots2 + 21;
     static constexpr int kRing2Offset = kStages * kStageBytes;
     static constexpr int kA2Offset = kRing2Offset + kSlots2 * kSlot2;
     static constexpr int kOutOffset = kA2Offset + kA2Bytes;
@@ -166,10 +168,10 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     auto d2empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 6 + a); };
     auto a2full_bar = [&]() { return bar_base + 8u * (2 * kStages + 8); };
     auto rfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 9 + b); };
-    auto bfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 12 + b); };
-    auto bempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 15 + b); };
-    auto full2_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 18 + s); };
-    auto empty2_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 18 + Cfg::kSlots2 + s); };
+    auto bfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 13 + b); };
+    auto bempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 17 + b); };
+    auto full2_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 21 + s); };
+    auto empty2_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 21 + Cfg::kSlots2 + s); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -188,12 +190,12 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             mbar_init(d1full_bar(a), 1);
             mbar_init(d1empty_bar(a), 16);  // one arrival per epilogue warp
             mbar_init(d2full_bar(a), 1);
-            mbar_init(d2empty_bar(a), 16);
+            mbar_init(d2empty_bar(a), 8);   // the eight epilogue warps of the group that drains this buffer
         }
         mbar_init(a2full_bar(), 16);
-        for (int b = 0; b < 3; ++b) {
+        for (int b = 0; b < 4; ++b) {
             mbar_init(rfull_bar(b), 1);
-            mbar_init(bfull_bar(b), 16);
+            mbar_init(bfull_bar(b), 8);
             mbar_init(bempty_bar(b), 1);
         }
         *abort_flag = 0;
@@ -480,7 +482,11 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             CHXQ_TL4(2048, 1000, 12);
             return true;
         };
-        // ---- second product: pass ps (128 output channels) of the i-th tile -> staged bytes
+        // ---- second product: pass ps (128 output channels) of the i-th tile -> staged bytes.  The sixteen warps form two groups of
+        // eight (two warps per lane quarter); a pass belongs to the group of its accumulator buffer, whose warps take four 16-channel
+        // chunks each.  While one group waits (for its accumulators, for the residual tile, for its tensor-memory loads) the other one
+        // works, and a warp passes its barriers once per four chunks.
+        const int grp = sub >> 1, sg = sub & 1;
         auto second_epilogue = [&](int i, int ps) -> bool {
             const int g = i * passes + ps;
             const int d2 = g & 1;
@@ -498,24 +504,29 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint8_t* out_buf = smem_out + buf * Cfg::kTileOut;
             const int col0 = ps * 128;
             uint32_t ra[16], rb[16];
-            const bool v0 = col0 + sub * 16 < p.out_cols, v1 = col0 + (4 + sub) * 16 < p.out_cols;  // warp-uniform; beyond: clipped by the store
+            auto chunk_of = [&](int j) { return sg + 2 * j; };
+            auto valid = [&](int j) { return col0 + chunk_of(j) * 16 < p.out_cols; };  // warp-uniform; beyond: clipped by the store
+            auto work = [&](uint32_t (&r)[16], int j) {
+                const int ch = chunk_of(j);
+                uint8_t* cell = out_buf + staged_offset<128>(row, ch);
+                uint4 resv = make_uint4(0u, 0u, 0u, 0u);
+                if (RES) resv = *reinterpret_cast<const uint4*>(cell);
+                *reinterpret_cast<uint4*>(cell) = fold_chunk16<RES>(r, tab_ms2 + col0 + ch * 16, tab_bs2 + col0 + ch * 16, resv, hp2x2, fr2, fc2, fa);
+            };
             __syncwarp();
-            if (v0) {
-                tmem_ld_32x32b_x16(taddr + (uint32_t)(sub * 16), ra);
-                tmem_ld_wait16(ra);
-                if (v1) tmem_ld_32x32b_x16(taddr + (uint32_t)((4 + sub) * 16), rb);
-                uint8_t* cell = out_buf + staged_offset<128>(row, sub);
-                uint4 resv = make_uint4(0u, 0u, 0u, 0u);
-                if (RES) resv = *reinterpret_cast<const uint4*>(cell);
-                *reinterpret_cast<uint4*>(cell) = fold_chunk16<RES>(ra, tab_ms2 + col0 + sub * 16, tab_bs2 + col0 + sub * 16, resv, hp2x2, fr2, fc2, fa);
-            }
-            if (v1) {
-                tmem_ld_wait16(rb);
-                uint8_t* cell = out_buf + staged_offset<128>(row, 4 + sub);
-                uint4 resv = make_uint4(0u, 0u, 0u, 0u);
-                if (RES) resv = *reinterpret_cast<const uint4*>(cell);
-                *reinterpret_cast<uint4*>(cell) =
-                        fold_chunk16<RES>(rb, tab_ms2 + col0 + (4 + sub) * 16, tab_bs2 + col0 + (4 + sub) * 16, resv, hp2x2, fr2, fc2, fa);
+            if (valid(0)) tmem_ld_32x32b_x16(taddr + (uint32_t)(chunk_of(0) * 16), ra);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool v = valid(j);
+                if (j & 1) {
+                    if (v) tmem_ld_wait16(rb);
+                    if (j + 1 < 4 && valid(j + 1)) tmem_ld_32x32b_x16(taddr + (uint32_t)(chunk_of(j + 1) * 16), ra);
+                    if (v) work(rb, j);
+                } else {
+                    if (v) tmem_ld_wait16(ra);
+                    if (j + 1 < 4 && valid(j + 1)) tmem_ld_32x32b_x16(taddr + (uint32_t)(chunk_of(j + 1) * 16), rb);
+                    if (v) work(ra, j);
+                }
             }
             tc_fence_before();
             fence_async_smem();  // staged bytes become visible to the TMA store
@@ -523,6 +534,7 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (lane == 0) {
                 mbar_arrive(d2empty_bar(d2));
                 mbar_arrive(bfull_bar(buf));
+                if (sg == 0 && quarter == 0) atomicAdd(const_cast<int*>(passes_done), 1);  // one warp per group keeps the count
             }
             CHXQ_TL4(2048, 1000, 80 + ps);
             return true;
@@ -533,8 +545,9 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         bool alive = my_tiles > 0 && first_epilogue(0);
         for (int i = 0; i < my_tiles && alive; ++i) {
             for (int ps = 0; ps < passes && alive; ++ps) {
+                const int g = i * passes + ps;
                 if (ps == passes - 1 && i + 1 < my_tiles) {
-                    const int g = i * passes + ps;
+                    // both groups: the last pass's accumulators are complete, so every MMA that read the intermediate tile has run
                     const bool got = mbar_wait(d2full_bar(g & 1), (uint32_t)(g >> 1) & 1u, abort_flag, p.status, 14, 32, limit);
                     if (!__all_sync(0xffffffffu, got)) {
                         alive = false;
@@ -543,8 +556,7 @@ tc_chain_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     alive = first_epilogue(i + 1);
                     if (!alive) break;
                 }
-                alive = second_epilogue(i, ps);
-                if (e == 0 && lane == 0) *passes_done = i * passes + ps + 1;
+                if ((g & 1) == grp) alive = second_epilogue(i, ps);
             }
         }
     } else if (warp == 18) {
