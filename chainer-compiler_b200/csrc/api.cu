@@ -215,12 +215,13 @@ struct S2dQuant {
     int has_zp, round_mode;
     QDiv dv;  // constant-divisor form of scale (fast path of the QuantizeLinear kernels)
 };
-template <bool kQuant>
+template <bool kQuant, int kC = 0>  // kC: the channel count when known at compile time (3: the byte positions of a block become constants)
 __global__ void __launch_bounds__(256) s2d_repack_kernel(
-        const void* __restrict__ xv, int N, int C, int H, int W, int64_t es_n, int64_t es_c, int64_t es_h, int64_t es_w, int t0h, int t0w,
+        const void* __restrict__ xv, int N, int C_rt, int H, int W, int64_t es_n, int64_t es_c, int64_t es_h, int64_t es_w, int t0h, int t0w,
         int rows2, int cols2, uint32_t pad_byte, S2dQuant qz, uint4* __restrict__ out) {
     // One thread per PAIR of horizontally adjacent blocks: their four input pixels per (row, channel) are contiguous in a
     // W-contiguous map and come in as one 32-bit (uint8) or 128-bit (fp32) load away from the borders.
+    const int C = kC > 0 ? kC : C_rt;
     const uint8_t* x = static_cast<const uint8_t*>(xv);
     const float* xf = static_cast<const float*>(xv);
     const int pairs = (cols2 + 1) / 2;
@@ -246,7 +247,9 @@ __global__ void __launch_bounds__(256) s2d_repack_kernel(
     for (int dy = 0; dy < 2; ++dy) {
         const int yy = 2 * (r + t0h) + dy;
         const bool row_in = yy >= 0 && yy < H;
-        for (int c = 0; c < C; ++c) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // at most four channels on this path; unrolled so that the loads of all channels are in flight together
+            if (c >= C) break;
             uint32_t px[4] = {pad_byte, pad_byte, pad_byte, pad_byte};
             if (row_in) {
                 const int64_t off = (int64_t)n * es_n + (int64_t)yy * es_h + (int64_t)c * es_c + (int64_t)xx0 * es_w;
@@ -538,7 +541,11 @@ int conv_tc_run(
     if (pl.path == kTcS2d) {
         uint8_t* A = scratch;
         if (quant_in && !zw_zero) return set_error(CHXQ_ERR_UNSUPPORTED, "fused QuantizeLinear + QLinearConv needs zero weight zero points");
-        if (quant_in)
+        if (quant_in && g.C == 3)
+            s2d_repack_kernel<true, 3><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
+                    x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), *quant_in,
+                    reinterpret_cast<uint4*>(A));
+        else if (quant_in)
             s2d_repack_kernel<true><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
                     x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), *quant_in,
                     reinterpret_cast<uint4*>(A));
