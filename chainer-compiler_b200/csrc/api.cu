@@ -462,7 +462,7 @@ int validate_geom(const char* op, const chxq_conv_geom* g) {
 }
 
 struct ConvWs {
-    size_t pack_off, wsum_off, zw_off, flag_off, pack_total;  // packed-weight blob
+    size_t pack_off, wsum_off, zw_off, flag_off, dw_off, pack_total;  // packed-weight blob (dw_off: depthwise 3x3 only, [M][12] raw taps)
     size_t im2col_bytes, rowsum_bytes;
 };
 
@@ -473,6 +473,8 @@ ConvWs conv_ws_layout(const chxq_conv_geom& g, const TcConvPlan& pl) {
     w.wsum_off = off; off += align_up((size_t)g.M * 4, 256);
     w.zw_off = off; off += align_up((size_t)g.M * 4, 256);
     w.flag_off = off; off += 256;
+    w.dw_off = off;
+    if (pl.diag && g.KH == 3 && g.KW == 3) off += align_up((size_t)g.M * 12, 256);  // the nine taps of a channel, 12 bytes apart (row-dp4a kernel)
     w.pack_total = off;
     const size_t rows = (size_t)g.N * g.Ho * g.Wo;
     w.im2col_bytes = pl.path == kTcS2d ? align_up((size_t)g.N * pl.rows2 * pl.cols2 * 16 + 256, 1024) : align_up(rows * (size_t)pl.a_pitch, 1024);
@@ -492,8 +494,11 @@ int pack_weights(const void* w, const chxq_conv_geom& g, const TcConvPlan& pl, c
     int32_t* flag = reinterpret_cast<int32_t*>(blob + L.flag_off);
     CHXQ_CUDA(cudaMemsetAsync(flag, 0, 4, s));
     const int cg = g.C / g.group;
-    if (pl.diag)
+    if (pl.diag) {
         pack_weights_diag_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, taps, blob + L.pack_off);
+        if (g.KH == 3 && g.KW == 3)  // [M][9] -> [M][12]
+            CHXQ_CUDA(cudaMemcpy2DAsync(blob + L.dw_off, 12, w, 9, 9, (size_t)g.M, cudaMemcpyDeviceToDevice, s));
+    }
     else if (pl.path == kTcS2d)
         pack_weights_s2d_kernel<<<blocks_for((int64_t)g.M * pl.k_total), 256, 0, s>>>(static_cast<const uint8_t*>(w), g.M, g.C, g.KH, g.KW, g.pad_top,
                                                                                       g.pad_left, pl.t0h, pl.t0w, pl.kw2, pl.bk, pl.k_total,
@@ -519,6 +524,13 @@ int conv_tc_run(
     const int64_t rows = (int64_t)g.N * g.Ho * g.Wo;
     if (rows == 0 && !plan_only) return CHXQ_OK;
     const bool im2col = needs_im2col(g, pl, x_zp);
+    // Depthwise 3x3 over a zero-point-0 uint8 map: the CUDA-core row-dp4a kernel (raw taps kept beside the diagonal-block pack) runs
+    // only on request (chxq_tc_variant 1).  Measured at batch 512 it ties the diagonal blocks on the tensor pipe at 144 channels, 56 x 56
+    // (0.30 to 0.35 against 0.345 ms) and loses at stride 2 and on 14 x 14 and 7 x 7 maps, so packed weights stay on the tensor pipe;
+    // the op-signature entry, which has no packed weights, runs the row kernel.
+    const int variant = tc_variant_value();
+    if (pl.diag && zw_zero && !plan_only && !quant_in && !pool && variant == 1 && depthwise3x3_eligible(g, x, y, x_zp, epi))
+        return launch_depthwise3x3(x, blob + L.dw_off, 12, 1, 0, g, epi, y, s);
     // plan_only: describe the problem without launching anything -- only for layers that need no pass in front of the kernel
     if (plan_only && (pl.path != kTcDirect || im2col || !zw_zero || rows == 0))
         return set_error(CHXQ_ERR_UNSUPPORTED, "convolution: this layer needs a pass in front of the tensor-core kernel");
@@ -666,6 +678,9 @@ int conv_dispatch(
     CHXQ_CHECK_ARG(x && w && y, "%s: null buffer", op);
     CHXQ_CHECK_ARG(path == CHXQ_PATH_AUTO || path == CHXQ_PATH_SIMT || path == CHXQ_PATH_TENSOR, "%s: bad path", op);
     const int xz = has_x_zp ? x_zp : 0;
+    // 3x3 depthwise with symmetric weights (a null zero-point array) over a zero-point-0 map: the row-dp4a kernel
+    if (path == CHXQ_PATH_AUTO && g->group > 1 && zw.ptr == nullptr && depthwise3x3_eligible(*g, x, y, xz, epi))
+        return launch_depthwise3x3(x, w, g->KH * g->KW, 1, 0, *g, epi, y, s);
     if (path == CHXQ_PATH_AUTO && g->group > 1 && epi.mode == kEpiRequant && depthwise_eligible(*g, x, y, epi.residual))
         return launch_depthwise(x, w, *g, xz, zw.ptr, zw.len, epi, y, s);
     // NCHW in, NCHW out (the reference's signature): NHWC inside, transposes around it, when the caller's workspace has room.

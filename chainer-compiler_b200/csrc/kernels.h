@@ -30,6 +30,12 @@ int launch_im2col(const void* x, const chxq_conv_geom& g, int c_pitch, int k_pad
 
 // ---- depthwise kernel (depthwise.cu): group == C == M, NHWC, requantizing epilogue ----
 bool depthwise_eligible(const chxq_conv_geom& g, const void* x, const void* y, const void* residual);
+// 3x3 depthwise on uint8 maps with zero point 0 and symmetric weights (dw3x3_rows_kernel); w: OIHW weights (row stride 9, tap stride 1,
+// w_diag 0) or the diagonal-block pack of the tensor-core path (row stride k_total, tap stride 64, w_diag 1)
+bool depthwise3x3_eligible(const chxq_conv_geom& g, const void* x, const void* y, int x_zp, const EpiArgs& epi);
+int launch_depthwise3x3(const void* x, const void* w, int w_row_stride, int w_tap_stride, int w_diag, const chxq_conv_geom& g, const EpiArgs& epi,
+                        void* y, cudaStream_t s);
+int tc_variant_value();  // chxq_tc_variant's current setting
 int launch_depthwise(
         const void* x, const void* w, const chxq_conv_geom& g, int x_zp, const void* w_zp, int64_t w_zp_len, const EpiArgs& epi, void* y,
         cudaStream_t s);

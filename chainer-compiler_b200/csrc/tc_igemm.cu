@@ -89,6 +89,10 @@ int pick_bn(int cols, int64_t pos_tiles) {
 
 }  // namespace
 
+int tc_variant_value() {
+    return g_variant.load(std::memory_order_relaxed);
+}
+
 int choose_bk(int k) {
     // 64- or 128-byte K tiles, whichever pads K less (128 on a tie): the part of a tile beyond the operand is TMA zero fill, not
     // traffic, and only these two tile sizes have the grouped kernel.

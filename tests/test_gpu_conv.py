@@ -449,7 +449,7 @@ def test_grouped_conv_tensor_core_packed(pkg, ops, orc, dev, N, C, H, W, M, grou
     wz0 = np.zeros(M, np.int8)
     acc = orc.conv_integer(x, w, 0, wz0, (stride, stride), (pad, pad), group)
     for fold in (False, True):
-        for variant in (1, 2, 3, 4):
+        for variant in (0, 1, 2, 3, 4):  # 1: 3x3 depthwise layers run on the row-dp4a CUDA-core kernel; the others keep the diagonal blocks on the tensor cores
             assert pkg.lib().chxq_tc_variant(variant) == 0
             yq = ops.QLinearConvPacked(xt, pk, 0.02, np.uint8(0), _t(ws_, dev), _t(wz0, dev), 0.05, np.uint8(20), b=_t(bias, dev), fold_scales=fold,
                                        clamp_hi_q=200)
@@ -538,3 +538,29 @@ def test_conv_with_fused_max_pooling(pkg, ops, orc, dev, case):
     pk128 = ops.PackedConv(_t(w128, dev), _t(wz64, dev), x128.shape)
     with pytest.raises(_lib.ChxqError):
         ops.QLinearConvMaxPoolPacked(x128, pk128, 0.02, np.uint8(0), _t(ws64, dev), _t(wz64, dev), 0.05, np.uint8(2))
+
+
+@pytest.mark.parametrize("N,C,H,W,stride,pad,wdtype", [
+    (2, 20, 13, 11, 1, 1, np.int8),      # 20 channels: five words per position; odd, non-square map
+    (3, 96, 17, 15, 2, 1, np.int8),      # stride 2, odd map
+    (1, 36, 30, 30, 1, 1, np.int8),      # more than one strip of rows
+    (2, 144, 56, 56, 2, 1, np.int8),     # a MobileNetV2 shape
+    (2, 32, 9, 9, 1, 0, np.int8),        # no padding
+    (2, 16, 8, 12, 1, 1, np.uint8),      # uint8 weights with zero point 0
+])
+def test_depthwise3x3_row_kernel_through_the_op_signature(ops, orc, dev, N, C, H, W, stride, pad, wdtype):
+    """3x3 depthwise QLinearConv with symmetric weights over a zero-point-0 map (the row-dp4a kernel), called through the op's own
+    signature on NHWC maps: bit-exact against the integer-domain oracle in both requantization forms, with a ReLU6-style clamp."""
+    rng = np.random.default_rng(C * 3 + H)
+    x = _rand(rng, (N, C, H, W), np.uint8)
+    w = _rand(rng, (C, 1, 3, 3), wdtype) if wdtype == np.int8 else rng.integers(0, 256, (C, 1, 3, 3)).astype(np.uint8)
+    ws_ = rng.uniform(0.0005, 0.002, C).astype(np.float32)
+    bias = _rand(rng, C, np.int32, -3000, 3000)
+    wz = np.zeros(C, wdtype)
+    acc = orc.conv_integer(x, w, 0, wz, (stride, stride), (pad, pad), C)
+    for fold in (False, True):
+        want = orc.requantize(acc, 0.02, ws_, 0.05, 7, bias=bias, channel_axis=1, fold=fold, clamp_hi_q=180)
+        y = ops.QLinearConv(_t(x, dev, True), 0.02, np.uint8(0), _t(w, dev), _t(ws_, dev), _t(wz, dev), 0.05, np.uint8(7), _t(bias, dev), (stride, stride),
+                            (pad, pad), C, fold_scales=fold, clamp_hi_q=180)
+        ops.device_status()
+        assert np.array_equal(y.cpu().numpy(), want), (fold, int((y.cpu().numpy() != want).sum()))
