@@ -524,13 +524,16 @@ int conv_tc_run(
     const int64_t rows = (int64_t)g.N * g.Ho * g.Wo;
     if (rows == 0 && !plan_only) return CHXQ_OK;
     const bool im2col = needs_im2col(g, pl, x_zp);
-    // Depthwise 3x3 over a zero-point-0 uint8 map: the CUDA-core row-dp4a kernel (raw taps kept beside the diagonal-block pack) runs
-    // only on request (chxq_tc_variant 1).  Measured at batch 512 it ties the diagonal blocks on the tensor pipe at 144 channels, 56 x 56
-    // (0.30 to 0.35 against 0.345 ms) and loses at stride 2 and on 14 x 14 and 7 x 7 maps, so packed weights stay on the tensor pipe;
-    // the op-signature entry, which has no packed weights, runs the row kernel.
+    // Depthwise 3x3 over a zero-point-0 uint8 map: the CUDA-core row-dp4a kernel with TMA-staged rows (raw taps kept beside the
+    // diagonal-block pack) moves each byte once instead of paying 64x the multiply-accumulates on the tensor pipe; measured at batch 512
+    // it is ahead on maps of 14 x 14 and larger and behind on 7 x 7 ones (two stages per image).  chxq_tc_variant 1 takes the CUDA-core
+    // kernels wherever they are eligible, 2..5 never.
     const int variant = tc_variant_value();
-    if (pl.diag && zw_zero && !plan_only && !quant_in && !pool && variant == 1 && depthwise3x3_eligible(g, x, y, x_zp, epi))
-        return launch_depthwise3x3(x, blob + L.dw_off, 12, 1, 0, g, epi, y, s);
+    if (pl.diag && zw_zero && !plan_only && !quant_in && !pool && !(variant >= 2 && variant <= 5) && depthwise3x3_eligible(g, x, y, x_zp, epi)) {
+        const bool staged = depthwise3x3_staged_eligible(g, x, y, x_zp, epi);
+        if (staged && (variant == 1 || g.Ho >= 14)) return launch_depthwise3x3_staged(x, blob + L.dw_off, 12, 1, 0, g, epi, y, s);
+        if (variant == 1) return launch_depthwise3x3(x, blob + L.dw_off, 12, 1, 0, g, epi, y, s);
+    }
     // plan_only: describe the problem without launching anything -- only for layers that need no pass in front of the kernel
     if (plan_only && (pl.path != kTcDirect || im2col || !zw_zero || rows == 0))
         return set_error(CHXQ_ERR_UNSUPPORTED, "convolution: this layer needs a pass in front of the tensor-core kernel");
@@ -679,8 +682,10 @@ int conv_dispatch(
     CHXQ_CHECK_ARG(path == CHXQ_PATH_AUTO || path == CHXQ_PATH_SIMT || path == CHXQ_PATH_TENSOR, "%s: bad path", op);
     const int xz = has_x_zp ? x_zp : 0;
     // 3x3 depthwise with symmetric weights (a null zero-point array) over a zero-point-0 map: the row-dp4a kernel
-    if (path == CHXQ_PATH_AUTO && g->group > 1 && zw.ptr == nullptr && depthwise3x3_eligible(*g, x, y, xz, epi))
+    if (path == CHXQ_PATH_AUTO && g->group > 1 && zw.ptr == nullptr && depthwise3x3_eligible(*g, x, y, xz, epi)) {
+        if (depthwise3x3_staged_eligible(*g, x, y, xz, epi)) return launch_depthwise3x3_staged(x, w, g->KH * g->KW, 1, 0, *g, epi, y, s);
         return launch_depthwise3x3(x, w, g->KH * g->KW, 1, 0, *g, epi, y, s);
+    }
     if (path == CHXQ_PATH_AUTO && g->group > 1 && epi.mode == kEpiRequant && depthwise_eligible(*g, x, y, epi.residual))
         return launch_depthwise(x, w, *g, xz, zw.ptr, zw.len, epi, y, s);
     // NCHW in, NCHW out (the reference's signature): NHWC inside, transposes around it, when the caller's workspace has room.

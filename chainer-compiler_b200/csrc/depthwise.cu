@@ -8,8 +8,11 @@
 //
 // The reference runs this as `group` separate fp32 convolutions plus a concatenate
 // (runtime/chainerx_util.cc:328-339): 960 launches for one MobileNetV2 layer.
+#include <algorithm>
+
 #include "common.h"
 #include "kernels.h"
+#include "tc_kernel.cuh"
 
 namespace chxq {
 namespace {
@@ -173,6 +176,89 @@ __device__ __forceinline__ int dot4(uint32_t xw, uint32_t ww, int acc) {
     return d;
 }
 
+// What a thread keeps for its four channels: the taps as one word per (kernel row, channel) and the requantization per channel.
+template <bool kWSigned>
+struct Dw3Lane {
+    uint32_t wr[3][4];
+    float ms[4], bs[4];
+    int bias[4];
+    float hp;
+    bool fold;
+    RequantParams rq;
+
+    __device__ __forceinline__ void setup(const uint8_t* __restrict__ w, const Dw3Desc& d, const EpiArgs& epi, int c0) {
+        if (d.w_row_stride == 12 && d.w_tap_stride == 1 && (reinterpret_cast<uintptr_t>(w) & 3u) == 0) {
+            // the nine taps of a channel in three aligned words: (t0 t1 t2 t3) (t4 t5 t6 t7) (t8 . . .)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t* wc = reinterpret_cast<const uint32_t*>(w + (int64_t)(c0 + c) * 12);
+                const uint32_t a = __ldg(wc), b = __ldg(wc + 1), e = __ldg(wc + 2);
+                wr[0][c] = a & 0x00ffffffu;
+                wr[1][c] = __byte_perm(a, b, 0x4543) & 0x00ffffffu;   // t3 t4 t5
+                wr[2][c] = __byte_perm(b, e, 0x4432) & 0x00ffffffu;   // t6 t7 t8
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint8_t* wc = w + (int64_t)(c0 + c) * d.w_row_stride + (d.w_diag ? ((c0 + c) & 63) : 0);
+#pragma unroll
+                for (int kh = 0; kh < 3; ++kh)
+                    wr[kh][c] = (uint32_t)wc[(kh * 3) * d.w_tap_stride] | ((uint32_t)wc[(kh * 3 + 1) * d.w_tap_stride] << 8) |
+                                ((uint32_t)wc[(kh * 3 + 2) * d.w_tap_stride] << 16);
+            }
+        }
+        rq = epi.rq;
+        fold = rq.fold != 0;
+        hp = fold_hi_ph(rq);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            bias[c] = epi.bias ? epi.bias[c0 + c] : 0;
+            ms[c] = epi_mult(epi, c0 + c);
+            bs[c] = 0.f;
+            if (fold) {
+                const FoldCh fc = fold_channel(bias[c], __fdiv_rn(ms[c], rq.y_scale), rq);
+                ms[c] = fc.ms;
+                bs[c] = fc.bs;
+            }
+        }
+    }
+
+    // the four per-channel neighbour words of a row, from the words of the window's three columns
+    static __device__ __forceinline__ void permute(uint32_t (&r)[4], uint32_t x0, uint32_t x1, uint32_t x2) {
+        r[0] = __byte_perm(__byte_perm(x0, x1, 0x0040), x2, 0x0410);
+        r[1] = __byte_perm(__byte_perm(x0, x1, 0x0051), x2, 0x0510);
+        r[2] = __byte_perm(__byte_perm(x0, x1, 0x0062), x2, 0x0610);
+        r[3] = __byte_perm(__byte_perm(x0, x1, 0x0073), x2, 0x0710);
+    }
+
+    // the output word of a position from the permuted words of its three input rows
+    __device__ __forceinline__ uint32_t word(const uint32_t (&r0)[4], const uint32_t (&r1)[4], const uint32_t (&r2)[4]) const {
+        uint32_t q[4];
+        if (fold) {
+            // the dot products start from the bits of 1.5 * 2^23: |sum| <= 9 * 255 * 255 < 2^22, so the integer sum lands in the mantissa
+            // and (bits as float) - 1.5 * 2^23 IS float(sum), exactly, without a conversion; the placed integer (at most 255) is the low
+            // byte of the last multiply-add's bits, which the packing permutes pick directly
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                int acc = dot4<kWSigned>(r0[c], wr[0][c], 0x4b400000);
+                acc = dot4<kWSigned>(r1[c], wr[1][c], acc);
+                acc = dot4<kWSigned>(r2[c], wr[2][c], acc);
+                const float f = __fsub_rn(__int_as_float(acc), 12582912.f);
+                q[c] = __float_as_uint(__fmaf_rd(__saturatef(__fmaf_rn(f, ms[c], bs[c])), hp, 8388608.f));
+            }
+            return __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            int acc = dot4<kWSigned>(r0[c], wr[0][c], 0);
+            acc = dot4<kWSigned>(r1[c], wr[1][c], acc);
+            acc = dot4<kWSigned>(r2[c], wr[2][c], acc);
+            q[c] = requant_u8_up_fast(acc, bias[c], ms[c], false, 0u, rq);
+        }
+        return (q[0] & 0xffu) | ((q[1] & 0xffu) << 8) | ((q[2] & 0xffu) << 16) | (q[3] << 24);
+    }
+};
+
 template <int S, bool kWSigned>
 __global__ void __launch_bounds__(256) dw3x3_rows_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ w, Dw3Desc d, EpiArgs epi,
                                                          uint8_t* __restrict__ y) {
@@ -183,120 +269,192 @@ __global__ void __launch_bounds__(256) dw3x3_rows_kernel(const uint8_t* __restri
     const int c0 = cw * 4;
     const int h_begin = blockIdx.y * d.rows_per_strip;
     const int h_end = min(d.Ho, h_begin + d.rows_per_strip);
-    // weights: one word per (kernel row, channel)
-    uint32_t wr[3][4];
-    if (d.w_row_stride == 12 && d.w_tap_stride == 1 && (reinterpret_cast<uintptr_t>(w) & 3u) == 0) {
-        // the nine taps of a channel in three aligned words: (t0 t1 t2 t3) (t4 t5 t6 t7) (t8 . . .)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const uint32_t* wc = reinterpret_cast<const uint32_t*>(w + (int64_t)(c0 + c) * 12);
-            const uint32_t a = __ldg(wc), b = __ldg(wc + 1), e = __ldg(wc + 2);
-            wr[0][c] = a & 0x00ffffffu;
-            wr[1][c] = __byte_perm(a, b, 0x4543) & 0x00ffffffu;   // t3 t4 t5
-            wr[2][c] = __byte_perm(b, e, 0x4432) & 0x00ffffffu;   // t6 t7 t8
-        }
-    } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const uint8_t* wc = w + (int64_t)(c0 + c) * d.w_row_stride + (d.w_diag ? ((c0 + c) & 63) : 0);
-#pragma unroll
-            for (int kh = 0; kh < 3; ++kh)
-                wr[kh][c] = (uint32_t)wc[(kh * 3) * d.w_tap_stride] | ((uint32_t)wc[(kh * 3 + 1) * d.w_tap_stride] << 8) |
-                            ((uint32_t)wc[(kh * 3 + 2) * d.w_tap_stride] << 16);
-        }
-    }
-    // requantization per channel
-    const RequantParams rq = epi.rq;
-    const bool fold = rq.fold != 0;
-    float ms[4], bs[4];
-    int bias[4];
-    const float hp = fold_hi_ph(rq);
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        bias[c] = epi.bias ? epi.bias[c0 + c] : 0;
-        ms[c] = epi_mult(epi, c0 + c);
-        bs[c] = 0.f;
-        if (fold) {
-            const FoldCh fc = fold_channel(bias[c], __fdiv_rn(ms[c], rq.y_scale), rq);
-            ms[c] = fc.ms;
-            bs[c] = fc.bs;
-        }
-    }
+    Dw3Lane<kWSigned> ln;
+    ln.setup(w, d, epi, c0);
     const int wi0 = wo * S - d.pl;
     const bool in0 = wi0 >= 0 && wi0 < d.W, in1 = wi0 + 1 >= 0 && wi0 + 1 < d.W, in2 = wi0 + 2 >= 0 && wi0 + 2 < d.W;
     const int64_t x_row = (int64_t)d.W * d.x_cs, y_row = (int64_t)d.Wo * d.y_cs;  // bytes between rows
     // small maps: a thread walks several images, so that the set-up above (weights, per-channel requantization) is paid once per ~28 rows
     for (int n = blockIdx.z * d.images_per_thread; n < min(d.N, (int)(blockIdx.z + 1) * d.images_per_thread); ++n) {
-    const uint8_t* xn = x + (int64_t)n * d.H * x_row + (int64_t)wi0 * d.x_cs + c0;
-    uint8_t* yp = y + ((int64_t)n * d.Ho + h_begin) * y_row + (int64_t)wo * d.y_cs + c0;
-    // raw words of an input row's three columns (zeros outside the map: the padding of a zero-point-0 map); fetched one row ahead of
-    // their use, so that the loads of the next row are in flight while the current one is worked on
-    struct Raw {
-        uint32_t x0, x1, x2;
-    };
-    auto fetch = [&](int hi) {
-        Raw r{0u, 0u, 0u};
-        if (hi >= 0 && hi < d.H) {
-            const uint8_t* row = xn + hi * x_row;
-            if (in0) r.x0 = __ldg(reinterpret_cast<const uint32_t*>(row));
-            if (in1) r.x1 = __ldg(reinterpret_cast<const uint32_t*>(row + d.x_cs));
-            if (in2) r.x2 = __ldg(reinterpret_cast<const uint32_t*>(row + 2 * d.x_cs));
+        const uint8_t* xn = x + (int64_t)n * d.H * x_row + (int64_t)wi0 * d.x_cs + c0;
+        uint8_t* yp = y + ((int64_t)n * d.Ho + h_begin) * y_row + (int64_t)wo * d.y_cs + c0;
+        // raw words of an input row's three columns (zeros outside the map: the padding of a zero-point-0 map); fetched one row ahead
+        // of their use, so that the loads of the next row are in flight while the current one is worked on
+        struct Raw {
+            uint32_t x0, x1, x2;
+        };
+        auto fetch = [&](int hi) {
+            Raw r{0u, 0u, 0u};
+            if (hi >= 0 && hi < d.H) {
+                const uint8_t* row = xn + hi * x_row;
+                if (in0) r.x0 = __ldg(reinterpret_cast<const uint32_t*>(row));
+                if (in1) r.x1 = __ldg(reinterpret_cast<const uint32_t*>(row + d.x_cs));
+                if (in2) r.x2 = __ldg(reinterpret_cast<const uint32_t*>(row + 2 * d.x_cs));
+            }
+            return r;
+        };
+        auto permute = [&](uint32_t (&r)[4], const Raw& v) { Dw3Lane<kWSigned>::permute(r, v.x0, v.x1, v.x2); };
+        auto emit = [&](const uint32_t (&r0)[4], const uint32_t (&r1)[4], const uint32_t (&r2)[4]) {
+            *reinterpret_cast<uint32_t*>(yp) = ln.word(r0, r1, r2);
+            yp += y_row;
+        };
+        uint32_t ra[4], rb[4], rc[4];
+        int ho = h_begin;
+        if (ho >= h_end) return;
+        if (S == 1) {
+            const int base = ho - d.pt;  // input row of the first tap of output row h_begin
+            Raw v = fetch(base);
+            Raw v1 = fetch(base + 1);
+            Raw nx = fetch(base + 2);
+            permute(ra, v);
+            permute(rb, v1);
+            int hn = base + 3;  // next input row to fetch
+            while (true) {
+                permute(rc, nx); nx = fetch(hn++); emit(ra, rb, rc); if (++ho >= h_end) break;
+                permute(ra, nx); nx = fetch(hn++); emit(rb, rc, ra); if (++ho >= h_end) break;
+                permute(rb, nx); nx = fetch(hn++); emit(rc, ra, rb); if (++ho >= h_end) break;
+            }
+        } else {
+            const int base = 2 * ho - d.pt;
+            Raw v = fetch(base);
+            Raw p1 = fetch(base + 1), p2 = fetch(base + 2);
+            permute(ra, v);
+            int hn = base + 3;
+            while (true) {
+                permute(rb, p1); permute(rc, p2); p1 = fetch(hn); p2 = fetch(hn + 1); hn += 2; emit(ra, rb, rc); if (++ho >= h_end) break;
+                permute(ra, p1); permute(rb, p2); p1 = fetch(hn); p2 = fetch(hn + 1); hn += 2; emit(rc, ra, rb); if (++ho >= h_end) break;
+                permute(rc, p1); permute(ra, p2); p1 = fetch(hn); p2 = fetch(hn + 1); hn += 2; emit(rb, rc, ra); if (++ho >= h_end) break;
+            }
         }
-        return r;
-    };
-    // the four per-channel neighbour words of a row
-    auto permute = [&](uint32_t (&r)[4], const Raw& v) {
-        r[0] = __byte_perm(__byte_perm(v.x0, v.x1, 0x0040), v.x2, 0x0410);
-        r[1] = __byte_perm(__byte_perm(v.x0, v.x1, 0x0051), v.x2, 0x0510);
-        r[2] = __byte_perm(__byte_perm(v.x0, v.x1, 0x0062), v.x2, 0x0610);
-        r[3] = __byte_perm(__byte_perm(v.x0, v.x1, 0x0073), v.x2, 0x0710);
-    };
-    auto emit = [&](int ho, const uint32_t (&r0)[4], const uint32_t (&r1)[4], const uint32_t (&r2)[4]) {
-        uint32_t q[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            int acc = dot4<kWSigned>(r0[c], wr[0][c], 0);
-            acc = dot4<kWSigned>(r1[c], wr[1][c], acc);
-            acc = dot4<kWSigned>(r2[c], wr[2][c], acc);
-            if (fold)
-                q[c] = (uint32_t)fold_place(__saturatef(__fmaf_rn((float)acc, ms[c], bs[c])), hp);
-            else
-                q[c] = requant_u8_up_fast(acc, bias[c], ms[c], false, 0u, rq);
+    }  // images
+}
+
+// ---- the same arithmetic, input rows staged in shared memory by TMA ----------------------------------------------------------------------
+// The kernel above keeps four bytes per thread in flight (its next row's own word; the two neighbours are other threads' words), a few KB
+// per SM: far too little to cover DRAM latency at HBM bandwidth.  Here a producer thread streams the input through a ring of shared-memory
+// stages with TMA -- boxes of cb channel bytes x (wt - 1) * S + 3 columns x six rows, zero fill outside the map (the padding of a zero-point-0
+// map) and beyond the last channel -- so tens of KB per SM are in flight and nothing but the output word lives in registers between rows.
+// A CTA owns wt output columns x cb / 4 channel words (one consumer thread each) and walks the rows of images_per_cta images; six input
+// rows are two periods of the three-slot row window at stride 1 and one at stride 2, so a stage is straight-line code.  Every wait is
+// bounded: after wait_limit_ns without progress the thread sets the abort flag and the device status word and the CTA returns.
+struct Dw3Staged {
+    int N, C, H, W, Ho, Wo, pt, pl;
+    int y_cs;
+    int cb, wt, wbox;
+    int col_tiles;
+    int images_per_cta;
+    int chunks;      // stages per image: ceil(((Ho - 1) * S + 3) / 6)
+    int consumers;   // consumer threads: cb / 4 * wt rounded up to whole warps
+    int stage_stride;
+    int* status;
+    unsigned long long wait_limit_ns;
+};
+constexpr int kDwRows = 6, kDwStages = 4;
+
+template <int S, bool kWSigned>
+__global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ w, const Dw3Desc wd,
+                                                           const Dw3Staged d, const EpiArgs epi, uint8_t* __restrict__ y) {
+    using namespace tc;
+    extern __shared__ uint8_t dw_smem_raw[];
+    uint8_t* smem = dw_smem_raw + ((128u - (smem_u32(dw_smem_raw) & 127u)) & 127u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDwStages * d.stage_stride);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kDwStages);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kDwStages + s); };
+    const int consumer_warps = d.consumers >> 5;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kDwStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), consumer_warps);
         }
-        const uint32_t word = (q[0] & 0xffu) | ((q[1] & 0xffu) << 8) | ((q[2] & 0xffu) << 16) | (q[3] << 24);
-        (void)ho;
-        *reinterpret_cast<uint32_t*>(yp) = word;
-        yp += y_row;
-    };
-    uint32_t ra[4], rb[4], rc[4];
-    int ho = h_begin;
-    if (ho >= h_end) return;
-    if (S == 1) {
-        const int base = ho - d.pt;  // input row of the first tap of output row h_begin
-        Raw v = fetch(base);
-        Raw v1 = fetch(base + 1);
-        Raw nx = fetch(base + 2);
-        permute(ra, v);
-        permute(rb, v1);
-        int hn = base + 3;  // next input row to fetch
-        while (true) {
-            permute(rc, nx); nx = fetch(hn++); emit(ho, ra, rb, rc); if (++ho >= h_end) break;
-            permute(ra, nx); nx = fetch(hn++); emit(ho, rb, rc, ra); if (++ho >= h_end) break;
-            permute(rb, nx); nx = fetch(hn++); emit(ho, rc, ra, rb); if (++ho >= h_end) break;
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    const int ct = blockIdx.x % d.col_tiles, cblk = blockIdx.x / d.col_tiles;
+    const int n_begin = blockIdx.y * d.images_per_cta;
+    const int n_end = min(d.N, n_begin + d.images_per_cta);
+    const int total = (n_end - n_begin) * d.chunks;
+    const uint32_t stage_bytes = (uint32_t)(kDwRows * d.wbox * d.cb);
+
+    if ((int)threadIdx.x >= d.consumers) {
+        // ---------------- producer: one lane streams the boxes ----------------
+        if ((int)threadIdx.x == d.consumers) {
+            const int wi0 = ct * d.wt * S - d.pl;
+            int g = 0;
+            for (int n = n_begin; n < n_end; ++n) {
+                for (int k = 0; k < d.chunks; ++k, ++g) {
+                    const int st = g % kDwStages;
+                    if (g >= kDwStages && !mbar_wait(empty_bar(st), (uint32_t)(g / kDwStages - 1) & 1u, abort_flag, d.status, 31, 0, d.wait_limit_ns)) {
+                        n = n_end;
+                        break;
+                    }
+                    mbar_expect_tx(full_bar(st), stage_bytes);
+                    tma_load_4d(smem_u32(smem + st * d.stage_stride), &tmX, full_bar(st), cblk * d.cb, wi0, k * kDwRows - d.pt, n);
+                }
+            }
+            // leave only when the copies issued have landed (bounded): the CTA's shared memory must outlive them
+            for (int i = max(0, g - kDwStages); i < g; ++i) {
+                const uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(full_bar(i % kDwStages), (uint32_t)(i / kDwStages) & 1u))
+                    if (global_timer_ns() - t0 > d.wait_limit_ns) break;
+            }
         }
-    } else {
-        const int base = 2 * ho - d.pt;
-        Raw v = fetch(base);
-        Raw p1 = fetch(base + 1), p2 = fetch(base + 2);
-        permute(ra, v);
-        int hn = base + 3;
-        while (true) {
-            permute(rb, p1); permute(rc, p2); p1 = fetch(hn); p2 = fetch(hn + 1); hn += 2; emit(ho, ra, rb, rc); if (++ho >= h_end) break;
-            permute(ra, p1); permute(rb, p2); p1 = fetch(hn); p2 = fetch(hn + 1); hn += 2; emit(ho, rc, ra, rb); if (++ho >= h_end) break;
-            permute(rc, p1); permute(ra, p2); p1 = fetch(hn); p2 = fetch(hn + 1); hn += 2; emit(ho, rb, rc, ra); if (++ho >= h_end) break;
+        return;
+    }
+    // ---------------- consumers ----------------
+    const int words = d.cb >> 2;
+    const int j = (int)threadIdx.x / words, cw = (int)threadIdx.x - j * words;
+    const int wo = ct * d.wt + j;
+    const int c0 = cblk * d.cb + cw * 4;
+    const bool active = j < d.wt && wo < d.Wo && c0 < d.C;
+    Dw3Lane<kWSigned> ln;
+    if (active) ln.setup(w, wd, epi, c0);
+    const int lane = threadIdx.x & 31;
+    const uint32_t row_bytes = (uint32_t)(d.wbox * d.cb);
+    const uint32_t my_off = (uint32_t)((S * j) * d.cb + cw * 4);
+    const int64_t y_row = (int64_t)d.Wo * d.y_cs;
+    uint32_t r0[4], r1[4], r2[4];
+    int g = 0;
+    for (int n = n_begin; n < n_end; ++n) {
+        uint8_t* yn = y + (int64_t)n * d.Ho * y_row + (int64_t)wo * d.y_cs + c0;
+        for (int k = 0; k < d.chunks; ++k, ++g) {
+            const int st = g % kDwStages;
+            if (!mbar_wait(full_bar(st), (uint32_t)(g / kDwStages) & 1u, abort_flag, d.status, 32, 32, d.wait_limit_ns)) return;
+            if (active) {
+                const uint8_t* base = smem + st * d.stage_stride + my_off;
+                auto load = [&](uint32_t (&r)[4], int t) {
+                    const uint8_t* p = base + t * row_bytes;
+                    Dw3Lane<kWSigned>::permute(r, *reinterpret_cast<const uint32_t*>(p), *reinterpret_cast<const uint32_t*>(p + d.cb),
+                                               *reinterpret_cast<const uint32_t*>(p + 2 * d.cb));
+                };
+                auto emit = [&](int ho, const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) {
+                    if (ho >= 0 && ho < d.Ho) *reinterpret_cast<uint32_t*>(yn + ho * y_row) = ln.word(a0, a1, a2);
+                };
+                if (S == 1) {
+                    const int ho = k * kDwRows - 2;  // output row completed by the stage's first input row
+                    load(r0, 0); emit(ho, r1, r2, r0);
+                    load(r1, 1); emit(ho + 1, r2, r0, r1);
+                    load(r2, 2); emit(ho + 2, r0, r1, r2);
+                    load(r0, 3); emit(ho + 3, r1, r2, r0);
+                    load(r1, 4); emit(ho + 4, r2, r0, r1);
+                    load(r2, 5); emit(ho + 5, r0, r1, r2);
+                } else {
+                    const int ho = k * 3 - 1;
+                    load(r0, 0); emit(ho, r1, r2, r0);
+                    load(r1, 1);
+                    load(r2, 2); emit(ho + 1, r0, r1, r2);
+                    load(r0, 3);
+                    load(r1, 4); emit(ho + 2, r2, r0, r1);
+                    load(r2, 5);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(st));
         }
     }
-    }  // images
 }
 
 }  // namespace
@@ -374,6 +532,78 @@ int launch_depthwise3x3(const void* x, const void* w, int w_row_stride, int w_ta
     }
     CHXQ_LAUNCH_CHECK();
     return CHXQ_OK;
+}
+
+// Staged form: needs what the row kernel needs and a map TMA can describe (16-byte aligned base and pixel pitch).
+bool depthwise3x3_staged_eligible(const chxq_conv_geom& g, const void* x, const void* y, int x_zp, const EpiArgs& epi) {
+    const int xcs = g.x_cstride > 0 ? g.x_cstride : g.C;
+    return depthwise3x3_eligible(g, x, y, x_zp, epi) && xcs % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && g.C >= 16;
+}
+
+int launch_depthwise3x3_staged(const void* x, const void* w, int w_row_stride, int w_tap_stride, int w_diag, const chxq_conv_geom& g,
+                               const EpiArgs& epi, void* y, cudaStream_t s) {
+    if ((int64_t)g.N * g.Ho * g.Wo == 0) return CHXQ_OK;
+    const int S = g.stride_h;
+    // block shape: cb channel bytes x wt output columns, one consumer thread per (channel word, column), at most 256 of them; the best
+    // product of lane use (channels and columns that exist / those the blocks cover), box reuse (columns used / columns fetched) and
+    // warp fill, with a mild preference for large blocks
+    int best_cb = 0, best_wt = 0;
+    double best = -1.0;
+    // (at least 64 channel bytes per pixel where the map has them: shorter pieces waste DRAM sectors and TMA's per-row work)
+    for (int cb = std::min(64, (g.C + 15) / 16 * 16); cb <= 256 && cb < g.C + 16; cb += 16) {
+        for (int wt = 1; wt <= g.Wo && (cb / 4) * wt <= 256; ++wt) {
+            const int wbox = (wt - 1) * S + 3;
+            if (wbox > 256 || (int64_t)kDwRows * wbox * cb > 16 * 1024) continue;
+            const int threads = (cb / 4) * wt, padded = (threads + 31) / 32 * 32;
+            const double lanes = (double)g.C / ((g.C + cb - 1) / cb * cb) * (double)g.Wo / ((g.Wo + wt - 1) / wt * wt);
+            const double reuse = (double)(wt * S) / wbox;
+            const double score = lanes * (reuse < 1.0 ? reuse : 1.0) * ((double)threads / padded) * (0.75 + 0.25 * padded / 256.0);
+            if (score > best) {
+                best = score;
+                best_cb = cb;
+                best_wt = wt;
+            }
+        }
+    }
+    if (best_cb == 0) return set_error(CHXQ_ERR_UNSUPPORTED, "depthwise 3x3: no block shape for this map");
+    Dw3Desc wd{};
+    wd.C = g.C;
+    wd.w_row_stride = w_row_stride; wd.w_tap_stride = w_tap_stride; wd.w_diag = w_diag;
+    Dw3Staged d{};
+    d.N = g.N; d.C = g.C; d.H = g.H; d.W = g.W; d.Ho = g.Ho; d.Wo = g.Wo; d.pt = g.pad_top; d.pl = g.pad_left;
+    d.y_cs = g.y_cstride > 0 ? g.y_cstride : g.M;
+    d.cb = best_cb; d.wt = best_wt; d.wbox = (best_wt - 1) * S + 3;
+    d.col_tiles = (g.Wo + d.wt - 1) / d.wt;
+    const int ch_blocks = (g.C + d.cb - 1) / d.cb;
+    d.chunks = ((g.Ho - 1) * S + 3 + kDwRows - 1) / kDwRows;
+    d.consumers = ((d.cb / 4) * d.wt + 31) / 32 * 32;
+    d.stage_stride = (kDwRows * d.wbox * d.cb + 127) / 128 * 128;
+    const int64_t blocks_x = (int64_t)d.col_tiles * ch_blocks;
+    // short maps: a CTA walks several images, so that its ring fills and a thread's set-up is paid once per ~8 stages -- as long as the
+    // grid still has a few CTAs per SM slot
+    const int64_t ipc_cap = std::max<int64_t>(1, (int64_t)g.N * blocks_x / 888);
+    d.images_per_cta = (int)std::max<int64_t>(1, std::min<int64_t>((8 + d.chunks - 1) / d.chunks, ipc_cap));
+    d.status = device_status_ptr();
+    if (!d.status) return set_error(CHXQ_ERR_CUDA, "device status word is unavailable");
+    d.wait_limit_ns = (unsigned long long)tc::wait_limit_ns_value();
+    const int xcs = g.x_cstride > 0 ? g.x_cstride : g.C;
+    alignas(64) CUtensorMap tmX;
+    const int rc = tc::encode_nhwc_box_map(&tmX, x, g.C, g.W, g.H, g.N, xcs, d.cb, d.wbox, kDwRows);
+    if (rc != CHXQ_OK) return rc;
+    const size_t smem = 128 + (size_t)kDwStages * d.stage_stride + 2 * kDwStages * 8 + 16;
+    dim3 grid((unsigned)blocks_x, (unsigned)((g.N + d.images_per_cta - 1) / d.images_per_cta));
+    const unsigned block = (unsigned)d.consumers + 32u;
+    const bool ws = g.w_dtype == CHXQ_INT8;
+    const uint8_t* wb = static_cast<const uint8_t*>(w);
+    uint8_t* yb = static_cast<uint8_t*>(y);
+    auto run = [&](auto kernel) -> int {
+        if (smem > 48 * 1024) CHXQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kernel<<<grid, block, smem, s>>>(tmX, wb, wd, d, epi, yb);
+        CHXQ_LAUNCH_CHECK();
+        return CHXQ_OK;
+    };
+    if (S == 1) return ws ? run(dw3x3_staged_kernel<1, true>) : run(dw3x3_staged_kernel<1, false>);
+    return ws ? run(dw3x3_staged_kernel<2, true>) : run(dw3x3_staged_kernel<2, false>);
 }
 
 }  // namespace chxq

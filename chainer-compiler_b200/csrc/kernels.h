@@ -35,6 +35,10 @@ bool depthwise_eligible(const chxq_conv_geom& g, const void* x, const void* y, c
 bool depthwise3x3_eligible(const chxq_conv_geom& g, const void* x, const void* y, int x_zp, const EpiArgs& epi);
 int launch_depthwise3x3(const void* x, const void* w, int w_row_stride, int w_tap_stride, int w_diag, const chxq_conv_geom& g, const EpiArgs& epi,
                         void* y, cudaStream_t s);
+// the same with the input rows staged in shared memory by TMA (dw3x3_staged_kernel): needs a 16-byte aligned map with a 16-byte pixel pitch
+bool depthwise3x3_staged_eligible(const chxq_conv_geom& g, const void* x, const void* y, int x_zp, const EpiArgs& epi);
+int launch_depthwise3x3_staged(const void* x, const void* w, int w_row_stride, int w_tap_stride, int w_diag, const chxq_conv_geom& g,
+                               const EpiArgs& epi, void* y, cudaStream_t s);
 int tc_variant_value();  // chxq_tc_variant's current setting
 int launch_depthwise(
         const void* x, const void* w, const chxq_conv_geom& g, int x_zp, const void* w_zp, int64_t w_zp_len, const EpiArgs& epi, void* y,

@@ -93,6 +93,25 @@ int tc_variant_value() {
     return g_variant.load(std::memory_order_relaxed);
 }
 
+namespace tc {
+long long wait_limit_ns_value() {
+    return g_wait_limit_ns.load(std::memory_order_relaxed);
+}
+
+int encode_nhwc_box_map(CUtensorMap* out, const void* base, int C, int W, int H, int N, int64_t cs, int box_c, int box_w, int box_h) {
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)cs, (cuuint64_t)cs * W, (cuuint64_t)cs * W * H};
+    const cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)box_w, (cuuint32_t)box_h, 1u};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(CHXQ_ERR_CUDA, "cuTensorMapEncodeTiled(NHWC box) failed with %d", (int)r);
+    return CHXQ_OK;
+}
+}  // namespace tc
+
 int choose_bk(int k) {
     // 64- or 128-byte K tiles, whichever pads K less (128 on a tie): the part of a tile beyond the operand is TMA zero fill, not
     // traffic, and only these two tile sizes have the grouped kernel.

@@ -100,5 +100,10 @@ int launch_tc_chain(int mid, bool res, const CUtensorMap& tmA, const CUtensorMap
 
 int tc3_pair_slots(int* out);  // CTA pairs the current device keeps resident at once
 
+long long wait_limit_ns_value();  // limit of the bounded device-side waits (chxq_tc_test_hooks; default 2 s)
+// Unswizzled tensor map over an NHWC uint8 map {C, W, H, N} with cs bytes between pixels (a multiple of 16, base 16-byte aligned); a box is
+// box_c bytes (a multiple of 16) x box_w pixels x box_h rows of one image; reads outside the map fill 0.
+int encode_nhwc_box_map(CUtensorMap* out, const void* base, int C, int W, int H, int N, int64_t cs, int box_c, int box_w, int box_h);
+
 }  // namespace tc
 }  // namespace chxq

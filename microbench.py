@@ -128,16 +128,16 @@ def run(which, dev, emit_line=None, gemm_sizes=(1024, 4096, 8192, 16384), mobile
     if "mobilenet" in which:
         B = 512
         x = torch.rand((B, 3, 224, 224), generator=torch.Generator().manual_seed(1)).to(dev)
-        # default: depthwise layers as diagonal blocks on the tensor cores; second run (on request): the 3x3 ones on the row-dp4a
-        # CUDA-core kernel (chxq_tc_variant 1)
-        for variant in ((0, 1) if mobilenet_cuda_cores else (0,)):
+        # default: 3x3 depthwise layers on the CUDA-core row kernel (rows staged by TMA) except on 7 x 7 maps; second run (on request):
+        # all of them as diagonal blocks on the tensor cores (chxq_tc_variant 3)
+        for variant in ((0, 3) if mobilenet_cuda_cores else (0,)):
             check(pkg.lib().chxq_tc_variant(variant))
             net = models.MobileNetV2Int8(B, dev, seed=0)
             net.calibrate(x)
             graph, logits = net.capture(x, fold=True)
             ms = timeit(graph.replay)
             dense, dw = net.macs_per_image()
-            emit("MobileNetV2-1.0 int8, batch 512, depthwise on %s, folded requantization" % ("CUDA cores (row-dp4a kernel)" if variant else "tensor cores (diagonal blocks)"), ms,
+            emit("MobileNetV2-1.0 int8, batch 512, depthwise on %s, folded requantization" % ("tensor cores (diagonal blocks)" if variant else "CUDA cores (row-dp4a kernel, TMA-staged rows; 7x7 maps on tensor cores)"), ms,
                  img_per_s=B / ms * 1e3, gmac_per_image=(dense + dw) / 1e9)
             del net, graph, logits
             torch.cuda.empty_cache()
@@ -153,14 +153,14 @@ def run(which, dev, emit_line=None, gemm_sizes=(1024, 4096, 8192, 16384), mobile
             y = ops.QLinearConv(x, 0.02, np.uint8(0), w, ws, wz, 0.05, np.uint8(0), None, (s, s), (1, 1), C)
             nbytes = x.numel() + y.numel()
             ms = timeit(lambda: ops.QLinearConv(x, 0.02, np.uint8(0), w, ws, wz, 0.05, np.uint8(0), None, (s, s), (1, 1), C))
-            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, op signature (row-dp4a kernel)" % (C, H, H, s, N), ms, gbs=nbytes / ms / 1e6)
+            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, op signature (row-dp4a kernel, rows staged by TMA)" % (C, H, H, s, N), ms, gbs=nbytes / ms / 1e6)
             pk = ops.PackedConv(w, wz, x.shape, (s, s), (1, 1), group=C)
             ms = timeit(lambda: ops.QLinearConvPacked(x, pk, 0.02, np.uint8(0), ws, wz, 0.05, np.uint8(0), fold_scales=True))
-            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, packed entry, tensor cores (diagonal blocks)" % (C, H, H, s, N), ms, gbs=nbytes / ms / 1e6)
-            check(pkg.lib().chxq_tc_variant(1))
+            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, packed entry, the library's choice" % (C, H, H, s, N), ms, gbs=nbytes / ms / 1e6)
+            check(pkg.lib().chxq_tc_variant(3))
             ms = timeit(lambda: ops.QLinearConvPacked(x, pk, 0.02, np.uint8(0), ws, wz, 0.05, np.uint8(0), fold_scales=True))
             check(pkg.lib().chxq_tc_variant(0))
-            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, packed entry, row-dp4a kernel on request" % (C, H, H, s, N), ms,
+            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, packed entry, tensor cores (diagonal blocks) on request" % (C, H, H, s, N), ms,
                  gbs=nbytes / ms / 1e6)
     if "nchw" in which:
         # the literal drop-in call of the reference's op (NCHW in, NCHW out, unpacked weights) on a res3 3x3 layer, beside the

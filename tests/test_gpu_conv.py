@@ -547,10 +547,16 @@ def test_conv_with_fused_max_pooling(pkg, ops, orc, dev, case):
     (2, 144, 56, 56, 2, 1, np.int8),     # a MobileNetV2 shape
     (2, 32, 9, 9, 1, 0, np.int8),        # no padding
     (2, 16, 8, 12, 1, 1, np.uint8),      # uint8 weights with zero point 0
+    (520, 960, 7, 7, 1, 1, np.int8),     # staged kernel: a CTA walks two images; seven channel blocks, the last one partly beyond the map
+    (260, 576, 14, 14, 2, 1, np.int8),   # staged kernel, stride 2, several images per CTA
+    (3, 144, 56, 56, 1, 1, np.int8),     # staged kernel: ten stages per image, column tiles with halo columns from their neighbours
+    (2, 32, 112, 112, 1, 1, np.int8),    # staged kernel: 32-byte channel blocks, nineteen stages (the ring wraps four times)
+    (2, 48, 11, 70, 2, 0, np.uint8),     # staged kernel: wide map, ragged last column tile, no padding, uint8 weights
 ])
 def test_depthwise3x3_row_kernel_through_the_op_signature(ops, orc, dev, N, C, H, W, stride, pad, wdtype):
-    """3x3 depthwise QLinearConv with symmetric weights over a zero-point-0 map (the row-dp4a kernel), called through the op's own
-    signature on NHWC maps: bit-exact against the integer-domain oracle in both requantization forms, with a ReLU6-style clamp."""
+    """3x3 depthwise QLinearConv with symmetric weights over a zero-point-0 map (the row-dp4a kernels: rows staged by TMA where the
+    channel count is a multiple of 16, plain loads elsewhere), called through the op's own signature on NHWC maps: bit-exact against
+    the integer-domain oracle in both requantization forms, with a ReLU6-style clamp."""
     rng = np.random.default_rng(C * 3 + H)
     x = _rand(rng, (N, C, H, W), np.uint8)
     w = _rand(rng, (C, 1, 3, 3), wdtype) if wdtype == np.int8 else rng.integers(0, 256, (C, 1, 3, 3)).astype(np.uint8)
