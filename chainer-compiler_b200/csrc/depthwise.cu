@@ -232,9 +232,11 @@ struct Dw3Lane {
     }
 
     // the output word of a position from the permuted words of its three input rows
+    // (kFold: 1 = folded requantization, 0 = reference order, -1 = whichever the call asks for, decided per word)
+    template <int kFold = -1>
     __device__ __forceinline__ uint32_t word(const uint32_t (&r0)[4], const uint32_t (&r1)[4], const uint32_t (&r2)[4]) const {
         uint32_t q[4];
-        if (fold) {
+        if (kFold == 1 || (kFold < 0 && fold)) {
             // the dot products start from the bits of 1.5 * 2^23: |sum| <= 9 * 255 * 255 < 2^22, so the integer sum lands in the mantissa
             // and (bits as float) - 1.5 * 2^23 IS float(sum), exactly, without a conversion; the placed integer (at most 255) is the low
             // byte of the last multiply-add's bits, which the packing permutes pick directly
@@ -351,7 +353,7 @@ struct Dw3Staged {
 };
 constexpr int kDwRows = 6, kDwStages = 4;
 
-template <int S, bool kWSigned>
+template <int S, bool kWSigned, bool kFold>
 __global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ w, const Dw3Desc wd,
                                                            const Dw3Staged d, const EpiArgs epi, uint8_t* __restrict__ y) {
     using namespace tc;
@@ -413,9 +415,14 @@ __global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant
     Dw3Lane<kWSigned> ln;
     if (active) ln.setup(w, wd, epi, c0);
     const int lane = threadIdx.x & 31;
-    const uint32_t row_bytes = (uint32_t)(d.wbox * d.cb);
-    const uint32_t my_off = (uint32_t)((S * j) * d.cb + cw * 4);
+    const uint32_t row_bytes = (uint32_t)(d.wbox * d.cb), cb1 = (uint32_t)d.cb, cb2 = 2u * (uint32_t)d.cb;
+    const uint32_t my_base = smem_u32(smem) + (uint32_t)((S * j) * d.cb + cw * 4);  // shared-memory address of the window's first word in stage 0
     const int64_t y_row = (int64_t)d.Wo * d.y_cs;
+    auto lds = [](uint32_t addr) {
+        uint32_t v;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+        return v;
+    };
     uint32_t r0[4], r1[4], r2[4];
     int g = 0;
     for (int n = n_begin; n < n_end; ++n) {
@@ -424,31 +431,58 @@ __global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant
             const int st = g % kDwStages;
             if (!mbar_wait(full_bar(st), (uint32_t)(g / kDwStages) & 1u, abort_flag, d.status, 32, 32, d.wait_limit_ns)) return;
             if (active) {
-                const uint8_t* base = smem + st * d.stage_stride + my_off;
-                auto load = [&](uint32_t (&r)[4], int t) {
-                    const uint8_t* p = base + t * row_bytes;
-                    Dw3Lane<kWSigned>::permute(r, *reinterpret_cast<const uint32_t*>(p), *reinterpret_cast<const uint32_t*>(p + d.cb),
-                                               *reinterpret_cast<const uint32_t*>(p + 2 * d.cb));
+                uint32_t addr = my_base + (uint32_t)(st * d.stage_stride);
+                auto load = [&](uint32_t (&r)[4]) {
+                    Dw3Lane<kWSigned>::permute(r, lds(addr), lds(addr + cb1), lds(addr + cb2));
+                    addr += row_bytes;
                 };
-                auto emit = [&](int ho, const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) {
-                    if (ho >= 0 && ho < d.Ho) *reinterpret_cast<uint32_t*>(yn + ho * y_row) = ln.word(a0, a1, a2);
-                };
-                if (S == 1) {
-                    const int ho = k * kDwRows - 2;  // output row completed by the stage's first input row
-                    load(r0, 0); emit(ho, r1, r2, r0);
-                    load(r1, 1); emit(ho + 1, r2, r0, r1);
-                    load(r2, 2); emit(ho + 2, r0, r1, r2);
-                    load(r0, 3); emit(ho + 3, r1, r2, r0);
-                    load(r1, 4); emit(ho + 4, r2, r0, r1);
-                    load(r2, 5); emit(ho + 5, r0, r1, r2);
+                // ho: output row completed by the stage's first input row; a stage in the middle of an image stores every row it completes,
+                // the first and the last ones check each row against the map
+                const int ho = S == 1 ? k * kDwRows - 2 : k * 3 - 1;
+                constexpr int kOut = S == 1 ? 6 : 3;
+                uint8_t* yp = yn + (int64_t)ho * y_row;
+                if (ho >= 0 && ho + kOut <= d.Ho) {
+                    auto emit = [&](const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) {
+                        *reinterpret_cast<uint32_t*>(yp) = ln.template word<kFold ? 1 : 0>(a0, a1, a2);
+                        yp += y_row;
+                    };
+                    if (S == 1) {
+                        load(r0); emit(r1, r2, r0);
+                        load(r1); emit(r2, r0, r1);
+                        load(r2); emit(r0, r1, r2);
+                        load(r0); emit(r1, r2, r0);
+                        load(r1); emit(r2, r0, r1);
+                        load(r2); emit(r0, r1, r2);
+                    } else {
+                        load(r0); emit(r1, r2, r0);
+                        load(r1);
+                        load(r2); emit(r0, r1, r2);
+                        load(r0);
+                        load(r1); emit(r2, r0, r1);
+                        load(r2);
+                    }
                 } else {
-                    const int ho = k * 3 - 1;
-                    load(r0, 0); emit(ho, r1, r2, r0);
-                    load(r1, 1);
-                    load(r2, 2); emit(ho + 1, r0, r1, r2);
-                    load(r0, 3);
-                    load(r1, 4); emit(ho + 2, r2, r0, r1);
-                    load(r2, 5);
+                    int h = ho;
+                    auto emit = [&](const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) {
+                        if (h >= 0 && h < d.Ho) *reinterpret_cast<uint32_t*>(yp) = ln.template word<kFold ? 1 : 0>(a0, a1, a2);
+                        yp += y_row;
+                        ++h;
+                    };
+                    if (S == 1) {
+                        load(r0); emit(r1, r2, r0);
+                        load(r1); emit(r2, r0, r1);
+                        load(r2); emit(r0, r1, r2);
+                        load(r0); emit(r1, r2, r0);
+                        load(r1); emit(r2, r0, r1);
+                        load(r2); emit(r0, r1, r2);
+                    } else {
+                        load(r0); emit(r1, r2, r0);
+                        load(r1);
+                        load(r2); emit(r0, r1, r2);
+                        load(r0);
+                        load(r1); emit(r2, r0, r1);
+                        load(r2);
+                    }
                 }
             }
             __syncwarp();
@@ -602,8 +636,12 @@ int launch_depthwise3x3_staged(const void* x, const void* w, int w_row_stride, i
         CHXQ_LAUNCH_CHECK();
         return CHXQ_OK;
     };
-    if (S == 1) return ws ? run(dw3x3_staged_kernel<1, true>) : run(dw3x3_staged_kernel<1, false>);
-    return ws ? run(dw3x3_staged_kernel<2, true>) : run(dw3x3_staged_kernel<2, false>);
+    if (epi.rq.fold != 0) {
+        if (S == 1) return ws ? run(dw3x3_staged_kernel<1, true, true>) : run(dw3x3_staged_kernel<1, false, true>);
+        return ws ? run(dw3x3_staged_kernel<2, true, true>) : run(dw3x3_staged_kernel<2, false, true>);
+    }
+    if (S == 1) return ws ? run(dw3x3_staged_kernel<1, true, false>) : run(dw3x3_staged_kernel<1, false, false>);
+    return ws ? run(dw3x3_staged_kernel<2, true, false>) : run(dw3x3_staged_kernel<2, false, false>);
 }
 
 }  // namespace chxq
