@@ -180,6 +180,7 @@ __device__ __forceinline__ int dot4(uint32_t xw, uint32_t ww, int acc) {
 template <bool kWSigned>
 struct Dw3Lane {
     uint32_t wr[3][4];
+    uint32_t wr2[3][4];  // the same taps one byte up: for a window that starts at the second byte of the row words
     float ms[4], bs[4];
     int bias[4];
     float hp;
@@ -207,6 +208,10 @@ struct Dw3Lane {
                                 ((uint32_t)wc[(kh * 3 + 2) * d.w_tap_stride] << 16);
             }
         }
+#pragma unroll
+        for (int kh = 0; kh < 3; ++kh)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) wr2[kh][c] = wr[kh][c] << 8;
         rq = epi.rq;
         fold = rq.fold != 0;
         hp = fold_hi_ph(rq);
@@ -232,29 +237,39 @@ struct Dw3Lane {
     }
 
     // the output word of a position from the permuted words of its three input rows
-    // (kFold: 1 = folded requantization, 0 = reference order, -1 = whichever the call asks for, decided per word)
-    template <int kFold = -1>
+    // (kFold: 1 = folded requantization, 0 = reference order, -1 = whichever the call asks for, decided per word; kShift: the window
+    // starts at the second byte of the words -- the right-hand one of two columns that share their row words -- so the taps move up a byte)
+    template <int kFold = -1, int kShift = 0>
     __device__ __forceinline__ uint32_t word(const uint32_t (&r0)[4], const uint32_t (&r1)[4], const uint32_t (&r2)[4]) const {
         uint32_t q[4];
+        const uint32_t (&wt)[3][4] = kShift ? wr2 : wr;
         if (kFold == 1 || (kFold < 0 && fold)) {
             // the dot products start from the bits of 1.5 * 2^23: |sum| <= 9 * 255 * 255 < 2^22, so the integer sum lands in the mantissa
             // and (bits as float) - 1.5 * 2^23 IS float(sum), exactly, without a conversion; the placed integer (at most 255) is the low
-            // byte of the last multiply-add's bits, which the packing permutes pick directly
+            // byte of the last multiply-add's bits, which the packing permutes pick directly.  Two channels per packed-float instruction
+            // where the operation has a packed form.
+            const uint64_t m15 = pack2(12582912.f, 12582912.f), m23 = pack2(8388608.f, 8388608.f), hp2 = pack2(hp, hp);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                int acc = dot4<kWSigned>(r0[c], wr[0][c], 0x4b400000);
-                acc = dot4<kWSigned>(r1[c], wr[1][c], acc);
-                acc = dot4<kWSigned>(r2[c], wr[2][c], acc);
-                const float f = __fsub_rn(__int_as_float(acc), 12582912.f);
-                q[c] = __float_as_uint(__fmaf_rd(__saturatef(__fmaf_rn(f, ms[c], bs[c])), hp, 8388608.f));
+            for (int c = 0; c < 4; c += 2) {
+                int a0 = dot4<kWSigned>(r0[c], wt[0][c], 0x4b400000);
+                int a1 = dot4<kWSigned>(r0[c + 1], wt[0][c + 1], 0x4b400000);
+                a0 = dot4<kWSigned>(r1[c], wt[1][c], a0);
+                a1 = dot4<kWSigned>(r1[c + 1], wt[1][c + 1], a1);
+                a0 = dot4<kWSigned>(r2[c], wt[2][c], a0);
+                a1 = dot4<kWSigned>(r2[c + 1], wt[2][c + 1], a1);
+                const uint64_t f2 = sub_x2(pack2(__int_as_float(a0), __int_as_float(a1)), m15);
+                const float t0 = fma_sat(lo_of(f2), ms[c], bs[c]), t1 = fma_sat(hi_of(f2), ms[c + 1], bs[c + 1]);
+                const uint64_t q2 = fma_rm_x2(pack2(t0, t1), hp2, m23);
+                q[c] = (uint32_t)q2;
+                q[c + 1] = (uint32_t)(q2 >> 32);
             }
             return __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            int acc = dot4<kWSigned>(r0[c], wr[0][c], 0);
-            acc = dot4<kWSigned>(r1[c], wr[1][c], acc);
-            acc = dot4<kWSigned>(r2[c], wr[2][c], acc);
+            int acc = dot4<kWSigned>(r0[c], wt[0][c], 0);
+            acc = dot4<kWSigned>(r1[c], wt[1][c], acc);
+            acc = dot4<kWSigned>(r2[c], wt[2][c], acc);
             q[c] = requant_u8_up_fast(acc, bias[c], ms[c], false, 0u, rq);
         }
         return (q[0] & 0xffu) | ((q[1] & 0xffu) << 8) | ((q[2] & 0xffu) << 16) | (q[3] << 24);
@@ -353,8 +368,8 @@ struct Dw3Staged {
 };
 constexpr int kDwRows = 6, kDwStages = 4;
 
-template <int S, bool kWSigned, bool kFold>
-__global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ w, const Dw3Desc wd,
+template <int S, bool kWSigned, bool kFold, int kCols>
+__global__ void __launch_bounds__(288, (kCols == 2 && kFold) ? 3 : 1) dw3x3_staged_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ w, const Dw3Desc wd,
                                                            const Dw3Staged d, const EpiArgs epi, uint8_t* __restrict__ y) {
     using namespace tc;
     extern __shared__ uint8_t dw_smem_raw[];
@@ -407,16 +422,22 @@ __global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant
         return;
     }
     // ---------------- consumers ----------------
+    // kCols == 2 (stride 1): a thread owns two neighbouring output columns.  The four pixel words of their windows are byte-transposed
+    // into one word per channel (eight permutes for both columns instead of eight per column), which the left column multiplies by
+    // (w0, w1, w2, 0) and the right one by (0, w0, w1, w2).
+    static_assert(kCols == 1 || (kCols == 2 && S == 1), "two columns per thread: stride 1 only");
     const int words = d.cb >> 2;
     const int j = (int)threadIdx.x / words, cw = (int)threadIdx.x - j * words;
-    const int wo = ct * d.wt + j;
+    const int jc = j * kCols;            // first of the thread's output columns within the tile
+    const int wo = ct * d.wt + jc;
     const int c0 = cblk * d.cb + cw * 4;
-    const bool active = j < d.wt && wo < d.Wo && c0 < d.C;
+    const bool active = jc < d.wt && wo < d.Wo && c0 < d.C;
+    const bool second = kCols == 2 && jc + 1 < d.wt && wo + 1 < d.Wo;
     Dw3Lane<kWSigned> ln;
     if (active) ln.setup(w, wd, epi, c0);
     const int lane = threadIdx.x & 31;
-    const uint32_t row_bytes = (uint32_t)(d.wbox * d.cb), cb1 = (uint32_t)d.cb, cb2 = 2u * (uint32_t)d.cb;
-    const uint32_t my_base = smem_u32(smem) + (uint32_t)((S * j) * d.cb + cw * 4);  // shared-memory address of the window's first word in stage 0
+    const uint32_t row_bytes = (uint32_t)(d.wbox * d.cb), cb1 = (uint32_t)d.cb, cb2 = 2u * (uint32_t)d.cb, cb3 = 3u * (uint32_t)d.cb;
+    const uint32_t my_base = smem_u32(smem) + (uint32_t)((S * jc) * d.cb + cw * 4);  // shared-memory address of the window's first word in stage 0
     const int64_t y_row = (int64_t)d.Wo * d.y_cs;
     auto lds = [](uint32_t addr) {
         uint32_t v;
@@ -433,7 +454,17 @@ __global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant
             if (active) {
                 uint32_t addr = my_base + (uint32_t)(st * d.stage_stride);
                 auto load = [&](uint32_t (&r)[4]) {
-                    Dw3Lane<kWSigned>::permute(r, lds(addr), lds(addr + cb1), lds(addr + cb2));
+                    if (kCols == 1) {
+                        Dw3Lane<kWSigned>::permute(r, lds(addr), lds(addr + cb1), lds(addr + cb2));
+                    } else {
+                        const uint32_t p0 = lds(addr), p1 = lds(addr + cb1), p2 = lds(addr + cb2), p3 = lds(addr + cb3);
+                        const uint32_t u0 = __byte_perm(p0, p1, 0x5140), u1 = __byte_perm(p0, p1, 0x7362);
+                        const uint32_t v0 = __byte_perm(p2, p3, 0x5140), v1 = __byte_perm(p2, p3, 0x7362);
+                        r[0] = __byte_perm(u0, v0, 0x5410);
+                        r[1] = __byte_perm(u0, v0, 0x7632);
+                        r[2] = __byte_perm(u1, v1, 0x5410);
+                        r[3] = __byte_perm(u1, v1, 0x7632);
+                    }
                     addr += row_bytes;
                 };
                 // ho: output row completed by the stage's first input row; a stage in the middle of an image stores every row it completes,
@@ -441,11 +472,13 @@ __global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant
                 const int ho = S == 1 ? k * kDwRows - 2 : k * 3 - 1;
                 constexpr int kOut = S == 1 ? 6 : 3;
                 uint8_t* yp = yn + (int64_t)ho * y_row;
+                auto put = [&](bool ok, const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) {
+                    if (ok) *reinterpret_cast<uint32_t*>(yp) = ln.template word<kFold ? 1 : 0, 0>(a0, a1, a2);
+                    if (kCols == 2 && ok && second) *reinterpret_cast<uint32_t*>(yp + d.y_cs) = ln.template word<kFold ? 1 : 0, 1>(a0, a1, a2);
+                    yp += y_row;
+                };
                 if (ho >= 0 && ho + kOut <= d.Ho) {
-                    auto emit = [&](const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) {
-                        *reinterpret_cast<uint32_t*>(yp) = ln.template word<kFold ? 1 : 0>(a0, a1, a2);
-                        yp += y_row;
-                    };
+                    auto emit = [&](const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) { put(true, a0, a1, a2); };
                     if (S == 1) {
                         load(r0); emit(r1, r2, r0);
                         load(r1); emit(r2, r0, r1);
@@ -464,8 +497,7 @@ __global__ void __launch_bounds__(288) dw3x3_staged_kernel(const __grid_constant
                 } else {
                     int h = ho;
                     auto emit = [&](const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) {
-                        if (h >= 0 && h < d.Ho) *reinterpret_cast<uint32_t*>(yp) = ln.template word<kFold ? 1 : 0>(a0, a1, a2);
-                        yp += y_row;
+                        put(h >= 0 && h < d.Ho, a0, a1, a2);
                         ++h;
                     };
                     if (S == 1) {
@@ -578,6 +610,7 @@ int launch_depthwise3x3_staged(const void* x, const void* w, int w_row_stride, i
                                const EpiArgs& epi, void* y, cudaStream_t s) {
     if ((int64_t)g.N * g.Ho * g.Wo == 0) return CHXQ_OK;
     const int S = g.stride_h;
+    const int cols = (S == 1 && epi.rq.fold != 0) ? 2 : 1;  // output columns per consumer thread (two: the folded form at stride 1)
     // block shape: cb channel bytes x wt output columns, one consumer thread per (channel word, column), at most 256 of them; the best
     // product of lane use (channels and columns that exist / those the blocks cover), box reuse (columns used / columns fetched) and
     // warp fill, with a mild preference for large blocks
@@ -585,10 +618,10 @@ int launch_depthwise3x3_staged(const void* x, const void* w, int w_row_stride, i
     double best = -1.0;
     // (at least 64 channel bytes per pixel where the map has them: shorter pieces waste DRAM sectors and TMA's per-row work)
     for (int cb = std::min(64, (g.C + 15) / 16 * 16); cb <= 256 && cb < g.C + 16; cb += 16) {
-        for (int wt = 1; wt <= g.Wo && (cb / 4) * wt <= 256; ++wt) {
-            const int wbox = (wt - 1) * S + 3;
+        for (int wt = 1; wt <= g.Wo && (cb / 4) * ((wt + cols - 1) / cols) <= 256; ++wt) {
+            const int wbox = ((wt + cols - 1) / cols * cols - 1) * S + 3;
             if (wbox > 256 || (int64_t)kDwRows * wbox * cb > 16 * 1024) continue;
-            const int threads = (cb / 4) * wt, padded = (threads + 31) / 32 * 32;
+            const int threads = (cb / 4) * ((wt + cols - 1) / cols), padded = (threads + 31) / 32 * 32;
             const double lanes = (double)g.C / ((g.C + cb - 1) / cb * cb) * (double)g.Wo / ((g.Wo + wt - 1) / wt * wt);
             const double reuse = (double)(wt * S) / wbox;
             const double score = lanes * (reuse < 1.0 ? reuse : 1.0) * ((double)threads / padded) * (0.75 + 0.25 * padded / 256.0);
@@ -606,11 +639,11 @@ int launch_depthwise3x3_staged(const void* x, const void* w, int w_row_stride, i
     Dw3Staged d{};
     d.N = g.N; d.C = g.C; d.H = g.H; d.W = g.W; d.Ho = g.Ho; d.Wo = g.Wo; d.pt = g.pad_top; d.pl = g.pad_left;
     d.y_cs = g.y_cstride > 0 ? g.y_cstride : g.M;
-    d.cb = best_cb; d.wt = best_wt; d.wbox = (best_wt - 1) * S + 3;
+    d.cb = best_cb; d.wt = best_wt; d.wbox = ((best_wt + cols - 1) / cols * cols - 1) * S + 3;
     d.col_tiles = (g.Wo + d.wt - 1) / d.wt;
     const int ch_blocks = (g.C + d.cb - 1) / d.cb;
     d.chunks = ((g.Ho - 1) * S + 3 + kDwRows - 1) / kDwRows;
-    d.consumers = ((d.cb / 4) * d.wt + 31) / 32 * 32;
+    d.consumers = ((d.cb / 4) * ((d.wt + cols - 1) / cols) + 31) / 32 * 32;
     d.stage_stride = (kDwRows * d.wbox * d.cb + 127) / 128 * 128;
     const int64_t blocks_x = (int64_t)d.col_tiles * ch_blocks;
     // short maps: a CTA walks several images, so that its ring fills and a thread's set-up is paid once per ~8 stages -- as long as the
@@ -637,11 +670,11 @@ int launch_depthwise3x3_staged(const void* x, const void* w, int w_row_stride, i
         return CHXQ_OK;
     };
     if (epi.rq.fold != 0) {
-        if (S == 1) return ws ? run(dw3x3_staged_kernel<1, true, true>) : run(dw3x3_staged_kernel<1, false, true>);
-        return ws ? run(dw3x3_staged_kernel<2, true, true>) : run(dw3x3_staged_kernel<2, false, true>);
+        if (S == 1) return ws ? run(dw3x3_staged_kernel<1, true, true, 2>) : run(dw3x3_staged_kernel<1, false, true, 2>);
+        return ws ? run(dw3x3_staged_kernel<2, true, true, 1>) : run(dw3x3_staged_kernel<2, false, true, 1>);
     }
-    if (S == 1) return ws ? run(dw3x3_staged_kernel<1, true, false>) : run(dw3x3_staged_kernel<1, false, false>);
-    return ws ? run(dw3x3_staged_kernel<2, true, false>) : run(dw3x3_staged_kernel<2, false, false>);
+    if (S == 1) return ws ? run(dw3x3_staged_kernel<1, true, false, 1>) : run(dw3x3_staged_kernel<1, false, false, 1>);
+    return ws ? run(dw3x3_staged_kernel<2, true, false, 1>) : run(dw3x3_staged_kernel<2, false, false, 1>);
 }
 
 }  // namespace chxq
