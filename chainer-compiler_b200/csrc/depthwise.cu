@@ -1,12 +1,18 @@
-// Depthwise QLinearConv (group == C == M) on NHWC u8/s8 maps: HBM-bound, so the kernel is built
-// around moving each byte once.  A CTA owns an 8x8 tile of output positions x 64 channels; the input
-// halo tile is staged into shared memory with 128-bit loads (positions in the convolution's padding
-// are filled with the activation zero point, i.e. 0 after zero-point subtraction, which is where the
-// reference pads: runtime/ops/quantize.cc:65-72 dequantizes before chainerx::Conv zero-pads), the
-// per-channel taps are staged as 32-bit (w - w_zp), every thread accumulates 16 channels of one position in registers
-// (one byte permute and one integer multiply-add per tap and channel) and stores one 128-bit word of requantized output.
+// Depthwise QLinearConv (group == C == M) on NHWC u8/s8 maps: HBM-bound work, so the kernels are built around moving each byte once.
+// Three kernels:
+//   depthwise_kernel      any kernel size up to 5x5, strides up to 4, either operand type, zero points, residual tail.  A CTA owns an
+//                         8x8 tile of output positions x 64 channels; the input halo tile is staged into shared memory with 128-bit loads
+//                         (positions in the convolution's padding are filled with the activation zero point, i.e. 0 after zero-point
+//                         subtraction, which is where the reference pads: runtime/ops/quantize.cc:65-72 dequantizes before
+//                         chainerx::Conv zero-pads), the per-channel taps are staged as 32-bit (w - w_zp), every thread accumulates 16
+//                         channels of one position in registers and stores one 128-bit word of requantized output.
+//   dw3x3_rows_kernel     3x3, stride 1 or 2, uint8 map with zero point 0, symmetric weights: a row of three taps is one dp4a; plain
+//                         loads (any channel count that is a multiple of four).
+//   dw3x3_staged_kernel   the same arithmetic with the input rows streamed through shared memory by TMA (16-byte aligned maps); two
+//                         output columns per thread at stride 1.  The one MobileNetV2's layers run on.
+// All three accumulate exact int32 sums and share the requantization of every other convolution path, so their outputs are identical.
 //
-// The reference runs this as `group` separate fp32 convolutions plus a concatenate
+// The reference runs a depthwise layer as `group` separate fp32 convolutions plus a concatenate
 // (runtime/chainerx_util.cc:328-339): 960 launches for one MobileNetV2 layer.
 #include <algorithm>
 

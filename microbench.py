@@ -153,7 +153,7 @@ def run(which, dev, emit_line=None, gemm_sizes=(1024, 4096, 8192, 16384), mobile
             y = ops.QLinearConv(x, 0.02, np.uint8(0), w, ws, wz, 0.05, np.uint8(0), None, (s, s), (1, 1), C)
             nbytes = x.numel() + y.numel()
             ms = timeit(lambda: ops.QLinearConv(x, 0.02, np.uint8(0), w, ws, wz, 0.05, np.uint8(0), None, (s, s), (1, 1), C))
-            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, op signature (row-dp4a kernel, rows staged by TMA)" % (C, H, H, s, N), ms, gbs=nbytes / ms / 1e6)
+            emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, op signature, reference-order requantization (row-dp4a kernel, rows staged by TMA)" % (C, H, H, s, N), ms, gbs=nbytes / ms / 1e6)
             pk = ops.PackedConv(w, wz, x.shape, (s, s), (1, 1), group=C)
             ms = timeit(lambda: ops.QLinearConvPacked(x, pk, 0.02, np.uint8(0), ws, wz, 0.05, np.uint8(0), fold_scales=True))
             emit("depthwise 3x3 QLinearConv C%d %dx%d stride %d batch %d, packed entry, the library's choice" % (C, H, H, s, N), ms, gbs=nbytes / ms / 1e6)
