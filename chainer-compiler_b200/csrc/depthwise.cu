@@ -479,8 +479,8 @@ __global__ void __launch_bounds__(288, (kCols == 2 && kFold) ? 3 : 1) dw3x3_stag
                 constexpr int kOut = S == 1 ? 6 : 3;
                 uint8_t* yp = yn + (int64_t)ho * y_row;
                 auto put = [&](bool ok, const uint32_t (&a0)[4], const uint32_t (&a1)[4], const uint32_t (&a2)[4]) {
-                    if (ok) *reinterpret_cast<uint32_t*>(yp) = ln.template word<kFold ? 1 : 0, 0>(a0, a1, a2);
-                    if (kCols == 2 && ok && second) *reinterpret_cast<uint32_t*>(yp + d.y_cs) = ln.template word<kFold ? 1 : 0, 1>(a0, a1, a2);
+                    if (ok) *reinterpret_cast<uint32_t*>(yp) = ln.template word<kFold ? 1 : -1, 0>(a0, a1, a2);
+                    if (kCols == 2 && ok && second) *reinterpret_cast<uint32_t*>(yp + d.y_cs) = ln.template word<kFold ? 1 : -1, 1>(a0, a1, a2);
                     yp += y_row;
                 };
                 if (ho >= 0 && ho + kOut <= d.Ho) {
