@@ -224,18 +224,21 @@ __global__ void __launch_bounds__(256) s2d_repack_kernel(
     const int C = kC > 0 ? kC : C_rt;
     const uint8_t* x = static_cast<const uint8_t*>(xv);
     const float* xf = static_cast<const float*>(xv);
-    const int pairs = (cols2 + 1) / 2;
+    // (pairs start at an odd block where the first input column of block 0 is not a multiple of four pixels from the row start -- an odd
+    // first tap offset -- so that the pair's four pixels stay one aligned load; the block in front of the row is not stored)
+    const int shift = t0w & 1;
+    const int pairs = (cols2 + shift + 1) / 2;
     const int64_t total = (int64_t)N * rows2 * pairs;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     int b0, r, n;
     if (total < (1ll << 31)) {  // 32-bit index arithmetic where it fits: 64-bit divisions are an order of magnitude dearer
         unsigned q = (unsigned)idx;
-        b0 = 2 * (int)(q % (unsigned)pairs); q /= (unsigned)pairs;
+        b0 = 2 * (int)(q % (unsigned)pairs) - shift; q /= (unsigned)pairs;
         r = (int)(q % (unsigned)rows2);
         n = (int)(q / (unsigned)rows2);
     } else {
-        b0 = 2 * (int)(idx % pairs);
+        b0 = 2 * (int)(idx % pairs) - shift;
         const int64_t q = idx / pairs;
         r = (int)(q % rows2);
         n = (int)(q / rows2);
@@ -243,6 +246,42 @@ __global__ void __launch_bounds__(256) s2d_repack_kernel(
     const bool base_ok = (reinterpret_cast<uintptr_t>(xv) & 15u) == 0;
     uint32_t word[2][4] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};
     const int xx0 = 2 * (b0 + t0w);
+    if (kQuant && kC == 3) {
+        // Three fp32 planes, away from the borders, reference rounding: six 128-bit loads, each quantized to one word of four pixels, and
+        // the twelve bytes of a block (row, column, channel order) gathered from those words with seven byte permutes per block.
+        const int yy0 = 2 * (r + t0h);
+        const int64_t off0 = (int64_t)n * es_n + (int64_t)yy0 * es_h + (int64_t)xx0;
+        if (es_w == 1 && base_ok && qz.dv.fast && qz.round_mode == 0 && yy0 >= 0 && yy0 + 1 < H && xx0 >= 0 && xx0 + 3 < W &&
+            ((off0 | es_h | es_c) & 3) == 0) {
+            const QDiv8 d8 = make_qdiv8(qz.dv, qz.zp_f);
+            float4 f[2][3];
+#pragma unroll
+            for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+                for (int c = 0; c < 3; ++c) f[dy][c] = __ldcs(reinterpret_cast<const float4*>(xf + off0 + dy * es_h + c * es_c));
+            bool general = false;
+            uint32_t P[2][3];
+#pragma unroll
+            for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+                for (int c = 0; c < 3; ++c) P[dy][c] = quantize4_u8_up(f[dy][c], d8, &general);
+            if (!general) {
+                const int64_t o = ((int64_t)n * rows2 + r) * cols2 + b0;
+                uint4 a, b;
+                a.x = __byte_perm(__byte_perm(P[0][0], P[0][1], 0x1040), P[0][2], 0x3410);
+                a.y = __byte_perm(__byte_perm(P[0][1], P[0][2], 0x0051), __byte_perm(P[1][0], P[1][1], 0x0040), 0x5410);
+                a.z = __byte_perm(__byte_perm(P[1][0], P[1][1], 0x0510), P[1][2], 0x5214);
+                a.w = 0u;
+                b.x = __byte_perm(__byte_perm(P[0][0], P[0][1], 0x3062), P[0][2], 0x3610);
+                b.y = __byte_perm(__byte_perm(P[0][1], P[0][2], 0x0073), __byte_perm(P[1][0], P[1][1], 0x0062), 0x5410);
+                b.z = __byte_perm(__byte_perm(P[1][0], P[1][1], 0x0730), P[1][2], 0x7216);
+                b.w = 0u;
+                if (b0 >= 0) out[o] = a;
+                if (b0 + 1 < cols2) out[o + 1] = b;
+                return;
+            }
+        }
+    }
 #pragma unroll
     for (int dy = 0; dy < 2; ++dy) {
         const int yy = 2 * (r + t0h) + dy;
@@ -296,7 +335,7 @@ __global__ void __launch_bounds__(256) s2d_repack_kernel(
         }
     }
     const int64_t o = ((int64_t)n * rows2 + r) * cols2 + b0;
-    out[o] = make_uint4(word[0][0], word[0][1], word[0][2], word[0][3]);
+    if (b0 >= 0) out[o] = make_uint4(word[0][0], word[0][1], word[0][2], word[0][3]);
     if (b0 + 1 < cols2) out[o + 1] = make_uint4(word[1][0], word[1][1], word[1][2], word[1][3]);
 }
 
@@ -526,12 +565,11 @@ int conv_tc_run(
     const bool im2col = needs_im2col(g, pl, x_zp);
     // Depthwise 3x3 over a zero-point-0 uint8 map: the CUDA-core row-dp4a kernel with TMA-staged rows (raw taps kept beside the
     // diagonal-block pack) moves each byte once instead of paying 64x the multiply-accumulates on the tensor pipe; measured at batch 512
-    // it is ahead on maps of 14 x 14 and larger and behind on 7 x 7 ones (two stages per image).  chxq_tc_variant 1 takes the CUDA-core
-    // kernels wherever they are eligible, 2..5 never.
+    // it is 1.1x (7 x 7 maps) to 3.8x (112 x 112) faster.  chxq_tc_variant 1 also takes the plain-load row kernel for maps TMA cannot
+    // describe, 2..5 keep the diagonal blocks.
     const int variant = tc_variant_value();
     if (pl.diag && zw_zero && !plan_only && !quant_in && !pool && !(variant >= 2 && variant <= 5) && depthwise3x3_eligible(g, x, y, x_zp, epi)) {
-        const bool staged = depthwise3x3_staged_eligible(g, x, y, x_zp, epi);
-        if (staged && (variant == 1 || g.Ho >= 14)) return launch_depthwise3x3_staged(x, blob + L.dw_off, 12, 1, 0, g, epi, y, s);
+        if (depthwise3x3_staged_eligible(g, x, y, x_zp, epi)) return launch_depthwise3x3_staged(x, blob + L.dw_off, 12, 1, 0, g, epi, y, s);
         if (variant == 1) return launch_depthwise3x3(x, blob + L.dw_off, 12, 1, 0, g, epi, y, s);
     }
     // plan_only: describe the problem without launching anything -- only for layers that need no pass in front of the kernel
@@ -557,15 +595,15 @@ int conv_tc_run(
         uint8_t* A = scratch;
         if (quant_in && !zw_zero) return set_error(CHXQ_ERR_UNSUPPORTED, "fused QuantizeLinear + QLinearConv needs zero weight zero points");
         if (quant_in && g.C == 3)
-            s2d_repack_kernel<true, 3><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
+            s2d_repack_kernel<true, 3><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + (pl.t0w & 1) + 1) / 2)), 256, 0, s>>>(
                     x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), *quant_in,
                     reinterpret_cast<uint4*>(A));
         else if (quant_in)
-            s2d_repack_kernel<true><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
+            s2d_repack_kernel<true><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + (pl.t0w & 1) + 1) / 2)), 256, 0, s>>>(
                     x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), *quant_in,
                     reinterpret_cast<uint4*>(A));
         else
-            s2d_repack_kernel<false><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + 1) / 2)), 256, 0, s>>>(
+            s2d_repack_kernel<false><<<blocks_for((int64_t)g.N * pl.rows2 * ((pl.cols2 + (pl.t0w & 1) + 1) / 2)), 256, 0, s>>>(
                     x, g.N, g.C, g.H, g.W, es_n, es_c, es_h, es_w, pl.t0h, pl.t0w, pl.rows2, pl.cols2, (uint32_t)(x_zp & 0xff), S2dQuant{}, reinterpret_cast<uint4*>(A));
         CHXQ_LAUNCH_CHECK();
         if (!zw_zero) {

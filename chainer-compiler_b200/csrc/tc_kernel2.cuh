@@ -113,7 +113,11 @@ struct PoolGeom {
     static constexpr int kTileW = HALO ? 8 : 16, kTileH = HALO ? 16 : 8;  // positions of one tile
     static constexpr int kW = kTileW - 1, kH = kTileH - 1;                 // pooled positions a group owns
 };
-template <int BN, int BK, int EPI, bool RES, bool HALO, bool POOL = false>
+// NARROW = V > 0: the operator has at most V x 16 output channels (V = 1 or 2; one column tile).  With every fourth chunk per warp only V
+// of the four warps of a lane quarter would have work, so the units (chunk, tile) are dealt out tile by tile instead: warp `sub` takes
+// chunk sub % V of tiles (sub + 4 u) / V, and still needs the parameters of one chunk only (cache slot 0).  A template argument, because
+// the same choice made at run time cost every other layer 3-8 %.
+template <int BN, int BK, int EPI, bool RES, bool HALO, bool POOL = false, int NARROW = 0>
 __global__ void __launch_bounds__(640, 1)
 tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const TcParams p) {
@@ -431,6 +435,8 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // quarter take every fourth 16-channel chunk.  A unit of work is (chunk, tile): 16 accumulators in, 16 bytes out.
         constexpr int kMine = BN / 64;  // chunks per warp
         constexpr int kUnits = kMine * kR;
+        constexpr bool kFlat = NARROW > 0;
+        constexpr int kV = NARROW > 0 ? NARROW : 1;
         const int e = warp - 2;         // 0..15
         const int quarter = warp & 3;
         const int sub = e >> 2;
@@ -466,7 +472,7 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (ct != cached_ct) {
                 __syncwarp();
                 for (int j = lane; j < BN / 4; j += 32) {
-                    const int c = col0 + ((j >> 4) * 4 + sub) * 16 + (j & 15);
+                    const int c = col0 + (kFlat ? (sub % kV) : ((j >> 4) * 4 + sub)) * 16 + (j & 15);
                     float m = 0.f;
                     uint32_t add = 0u, corr = 0u;
                     if (c < p.cols) {
@@ -504,8 +510,8 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 // One unit: 16 accumulators of (chunk i, tile t) in registers -> 16 staged bytes.  The per-channel multiplier
                 // and additive term come from the per-warp cache four channels at a time.
                 auto process = [&](uint32_t (&r)[16], const int u) {
-                    const int i = u / kR, t = u % kR;
-                    const int ch = i * 4 + sub;
+                    const int i = kFlat ? 0 : u / kR, t = kFlat ? (sub + 4 * u) / kV : u % kR;
+                    const int ch = kFlat ? sub % kV : i * 4 + sub;
                     uint8_t* cell = out_buf + t * Cfg::kTileOut + staged_offset<BN>(row, ch);
                     uint4 resv = make_uint4(0u, 0u, 0u, 0u);
                     if (RES) resv = *reinterpret_cast<const uint4*>(cell);
@@ -569,8 +575,12 @@ tc_igemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                     *reinterpret_cast<uint4*>(cell) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
                 };
-                auto unit_valid = [&](int u) { return col0 + ((u / kR) * 4 + sub) * 16 < p.cols; };  // warp-uniform; beyond: clipped by the store
-                auto unit_taddr = [&](int u) { return taddr + (uint32_t)((u % kR) * BN + ((u / kR) * 4 + sub) * 16); };
+                auto unit_valid = [&](int u) {  // warp-uniform; columns beyond the operator's are clipped by the store
+                    return kFlat ? (sub + 4 * u) / kV < kR : col0 + ((u / kR) * 4 + sub) * 16 < p.cols;
+                };
+                auto unit_taddr = [&](int u) {
+                    return kFlat ? taddr + (uint32_t)(((sub + 4 * u) / kV) * BN + (sub % kV) * 16) : taddr + (uint32_t)((u % kR) * BN + ((u / kR) * 4 + sub) * 16);
+                };
                 // The TMEM read of unit u + 1 is in flight while unit u is processed.
                 uint32_t ra[16], rb[16];
                 __syncwarp();
@@ -697,7 +707,7 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t sme
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-template <int BN, int BK, int EPI, bool RES, bool HALO, bool POOL = false>
+template <int BN, int BK, int EPI, bool RES, bool HALO, bool POOL = false, int NARROW = 0>
 int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcParams& p, int grid,
                 cudaStream_t s) {
     using Cfg = Tc2Config<BN, BK, RES, HALO>;
@@ -706,10 +716,10 @@ int launch_one2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
     int dev = 0;
     CHXQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
-        CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        CHXQ_CUDA(cudaFuncSetAttribute(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL, NARROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
-    CHXQ_CUDA(launch_pdl(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL>, grid, 640, Cfg::kSmemBytes, s, tmA, tmB, tmY, tmR, p));
+    CHXQ_CUDA(launch_pdl(tc_igemm2_kernel<BN, BK, EPI, RES, HALO, POOL, NARROW>, grid, 640, Cfg::kSmemBytes, s, tmA, tmB, tmY, tmR, p));
     count_launch(1);
     return CHXQ_OK;
 }
@@ -741,6 +751,13 @@ int launch_bk2(int bn, int epi, bool res, bool halo, const CUtensorMap& tmA, con
             }
         }
         return CHXQ_ERR_UNSUPPORTED;
+    }
+    if (bn == 64 && epi == kEpiKU8Fold && p.col_tiles == 1 && p.cols <= 32) {  // narrow operators (MobileNetV2's projections)
+        if (p.cols <= 16)
+            return res ? launch_one2<64, BK, kEpiKU8Fold, true, false, false, 1>(tmA, tmB, tmY, tmR, p, grid, s)
+                       : launch_one2<64, BK, kEpiKU8Fold, false, false, false, 1>(tmA, tmB, tmY, tmR, p, grid, s);
+        return res ? launch_one2<64, BK, kEpiKU8Fold, true, false, false, 2>(tmA, tmB, tmY, tmR, p, grid, s)
+                   : launch_one2<64, BK, kEpiKU8Fold, false, false, false, 2>(tmA, tmB, tmY, tmR, p, grid, s);
     }
     switch (key) {
         case 0: return launch_one2<64, BK, kEpiKU8, false, false>(tmA, tmB, tmY, tmR, p, grid, s);

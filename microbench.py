@@ -128,8 +128,8 @@ def run(which, dev, emit_line=None, gemm_sizes=(1024, 4096, 8192, 16384), mobile
     if "mobilenet" in which:
         B = 512
         x = torch.rand((B, 3, 224, 224), generator=torch.Generator().manual_seed(1)).to(dev)
-        # default: 3x3 depthwise layers on the CUDA-core row kernel (rows staged by TMA) except on 7 x 7 maps; second run (on request):
-        # all of them as diagonal blocks on the tensor cores (chxq_tc_variant 3)
+        # default: 3x3 depthwise layers on the CUDA-core row kernel (rows staged by TMA); second run (on request): all of them as
+        # diagonal blocks on the tensor cores (chxq_tc_variant 3)
         for variant in ((0, 3) if mobilenet_cuda_cores else (0,)):
             check(pkg.lib().chxq_tc_variant(variant))
             net = models.MobileNetV2Int8(B, dev, seed=0)
@@ -137,7 +137,7 @@ def run(which, dev, emit_line=None, gemm_sizes=(1024, 4096, 8192, 16384), mobile
             graph, logits = net.capture(x, fold=True)
             ms = timeit(graph.replay)
             dense, dw = net.macs_per_image()
-            emit("MobileNetV2-1.0 int8, batch 512, depthwise on %s, folded requantization" % ("tensor cores (diagonal blocks)" if variant else "CUDA cores (row-dp4a kernel, TMA-staged rows; 7x7 maps on tensor cores)"), ms,
+            emit("MobileNetV2-1.0 int8, batch 512, depthwise on %s, folded requantization" % ("tensor cores (diagonal blocks)" if variant else "CUDA cores (row-dp4a kernel, TMA-staged rows)"), ms,
                  img_per_s=B / ms * 1e3, gmac_per_image=(dense + dw) / 1e9)
             del net, graph, logits
             torch.cuda.empty_cache()

@@ -342,6 +342,9 @@ GROUPED_CASES = [
     (3, 64, 20, 13, 64, 3, 1, 1),    # halo tiles: ragged in both directions (13 = 8 + 5 columns, 20 = 16 + 4 rows)
     (2, 128, 16, 16, 192, 3, 1, 1),  # halo tiles, two channel chunks of 64, 128-channel blocks with a ragged last block
     (2, 64, 9, 12, 64, 2, 1, 0),     # halo tiles, 2 x 2 window without padding
+    (5, 32, 20, 20, 16, 1, 1, 0),    # 16 output channels: one chunk per tile, dealt out tile by tile (folded form); ragged last group
+    (3, 96, 15, 15, 32, 1, 1, 0),    # 32 output channels, K tile 128
+    (2, 144, 17, 9, 32, 3, 1, 1),    # 32 output channels, 3 x 3 window
 ]
 
 
