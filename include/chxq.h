@@ -55,7 +55,7 @@ extern "C" {
 #define CHXQ_NHWC 1
 
 /* Kernel family selection (argument `path`). */
-#define CHXQ_PATH_AUTO 0   /* tensor-core kernel when the problem is eligible, else SIMT */
+#define CHXQ_PATH_AUTO 0   /* tensor-core kernel when the problem is eligible (depthwise layers: the CUDA-core depthwise kernels), else SIMT */
 #define CHXQ_PATH_SIMT 1   /* general CUDA-core kernels (any shape, layout, zero point) */
 #define CHXQ_PATH_TENSOR 2 /* tcgen05 kernels only; CHXQ_ERR_UNSUPPORTED when not eligible */
 
