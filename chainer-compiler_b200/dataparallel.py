@@ -7,6 +7,7 @@ at all (its only collective use is ChainerMN in a training example).
 """
 import os
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -135,10 +136,15 @@ class InferenceEngine:
     Results: every rank holds the logits of the whole job on the device after a step (all-gather).  The host copy is
     what the rank needs: rank 0 receives the whole job's logits, the other ranks their own rows."""
 
-    def __init__(self, net, world=1, fold=False, rank=0):
+    def __init__(self, net, world=1, fold=False, rank=0, input_dtype=torch.float32):
+        """input_dtype: torch.float32 -- the network's own input, quantized on the device by the stem's fused QuantizeLinear -- or
+        torch.uint8 -- batches the host has already quantized with the network's input scale (QuantizeLinear(x, net.in_scale, 0));
+        the results are the same bytes, a quarter of the bytes cross PCIe."""
         self.net, self.world, self.fold, self.rank = net, world, fold, rank
+        assert input_dtype in (torch.float32, torch.uint8)
+        self.input_dtype = input_dtype
         dev = net.device
-        self.x_dev = torch.empty((net.batch, 3, net.image, net.image), dtype=torch.float32, device=dev)
+        self.x_dev = torch.empty((net.batch, 3, net.image, net.image), dtype=input_dtype, device=dev)
         self.graph = None
         self.logits = None
         self.all_logits = None
@@ -149,8 +155,16 @@ class InferenceEngine:
     def prepare(self, calib_x):
         """Calibrates on calib_x and captures the two graphs.  The device-resident input of step_device is self.x_dev (call
         set_resident_input after changing it)."""
-        self.x_dev.copy_(calib_x)
-        self.net.calibrate(self.x_dev)
+        if self.input_dtype == torch.float32:
+            self.x_dev.copy_(calib_x)
+            self.net.calibrate(self.x_dev)
+        else:
+            from . import ops
+            calib_dev = calib_x.to(self.net.device)
+            if not self.net.calibrated:
+                self.net.calibrate(calib_dev)
+            self.x_dev.copy_(ops.QuantizeLinear(calib_dev, self.net.in_scale, np.uint8(0)))
+            del calib_dev
         dev = self.net.device
         idx = dev.index if dev.index is not None else torch.cuda.current_device()
         self.comm_stream = torch.cuda.Stream(dev)
@@ -173,7 +187,7 @@ class InferenceEngine:
         self.graph, self.logits, self.all_logits, self.host_logits = s0["graph"], s0["logits"], s0["all"], s0["host"]
 
     def set_resident_input(self, x):
-        """Makes x (device or pinned host, fp32 NCHW) the input of both slots for step_device."""
+        """Makes x (device or pinned host, NCHW, the engine's input dtype) the input of both slots for step_device."""
         for s in self.slots:
             s["x"].copy_(x)
 
@@ -211,7 +225,8 @@ class InferenceEngine:
         return s["all"] if (self.world > 1 and self.rank == 0) else s["logits"]
 
     def run_host(self, x_host_pinned):
-        """Public end-to-end call: pinned host fp32 NCHW batch in, host logits out (rank 0: the whole job's; others: own rows)."""
+        """Public end-to-end call: pinned host NCHW batch (the engine's input dtype) in, host logits out (rank 0: the whole job's;
+        others: own rows)."""
         s = self.slots[0]
         compute = torch.cuda.current_stream()
         s["x"].copy_(x_host_pinned, non_blocking=True)
@@ -225,7 +240,7 @@ class InferenceEngine:
 
     # ---- pipelined end-to-end call ------------------------------------------------------------------------------------
     def run_stream(self, batches):
-        """Public streaming call: an iterable of pinned host fp32 NCHW batches in, one host logits array out per batch, in
+        """Public streaming call: an iterable of pinned host NCHW batches (the engine's input dtype) in, one host logits array out per batch, in
         order (rank 0: the whole job's rows; other ranks: their own).  Batch i+1 crosses PCIe while batch i computes and batch
         i-1's logits are gathered and copied back.  The returned array of batch i is valid until batch i+2 is submitted."""
         compute = torch.cuda.current_stream()

@@ -214,3 +214,23 @@ def test_engine_stream_matches_single_calls(pkg, dev):
         eng.drain()
         torch.cuda.synchronize()
         assert torch.equal(out.cpu(), want[0])
+
+
+def test_engine_uint8_host_batches_give_the_same_logits(pkg, ops, dev):
+    """An engine fed batches the host has already quantized (QuantizeLinear with the network's input scale) returns the logits of
+    the fp32-input engine bit for bit: the stem reads the uint8 NCHW map directly instead of quantizing on the fly."""
+    from chainer_compiler_b200 import models, dataparallel as dp
+    net = models.ResNet50Int8(batch=2, device=dev, seed=2, image=64, num_classes=16, width_mult=0.25)
+    gen = torch.Generator().manual_seed(4)
+    calib = torch.rand((2, 3, 64, 64), generator=gen)
+    eng = dp.InferenceEngine(net, 1, fold=True)
+    eng.prepare(calib.to(dev))
+    eng8 = dp.InferenceEngine(net, 1, fold=True, input_dtype=torch.uint8)
+    eng8.prepare(calib)
+    batches = [torch.rand((2, 3, 64, 64), generator=gen).pin_memory() for _ in range(3)]
+    qbatches = [ops.QuantizeLinear(b.to(dev), net.in_scale, np.uint8(0)).cpu().pin_memory() for b in batches]
+    want = [eng.run_host(b).clone() for b in batches]
+    got = [h.clone() for h in eng8.run_stream(qbatches)]
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    ops.device_status()
